@@ -1,0 +1,283 @@
+"""ctypes binding of ``libaltob200.so`` (the C ABI declared in ``include/altob200.h``).
+
+There is no CPU fallback: if the shared library is missing, or a call returns a negative
+status, an exception is raised.  Every wrapper takes torch tensors only to read their
+device pointers and launches on the calling thread's current CUDA stream, as the
+reference's Triton launches do (forward on the caller's thread, backward on the autograd
+engine's device thread).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from pathlib import Path
+from typing import Optional, Sequence
+
+import torch
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libaltob200.so"
+
+# enums of include/altob200.h
+FMT_NVFP4, FMT_MXFP4, FMT_MXFP8_E4M3, FMT_MXFP8_E5M2 = 0, 1, 2, 3
+DT_BF16, DT_F32 = 0, 1
+SCALE_PLAIN, SCALE_PACKED = 1, 2
+ROUND_RTN, ROUND_SR_BITS, ROUND_SR_PHILOX = 0, 1, 2
+AMAX_SCRATCH_BYTES = 16
+
+E_SHAPE, E_ALIGN, E_TIMEOUT, E_CUDA, E_UNSUPPORTED, E_LIMIT = -1, -2, -3, -4, -5, -6
+
+#: every symbol the header declares (checked by the CPU test-suite)
+EXPORTED_SYMBOLS = (
+    "altob200_version",
+    "altob200_status_string",
+    "altob200_packed_scale_bytes",
+    "altob200_status_read",
+    "altob200_amax",
+    "altob200_quantize_rowwise",
+    "altob200_quantize_colwise",
+    "altob200_quantize_2d",
+    "altob200_dequantize",
+    "altob200_rht",
+    "altob200_gemm_blockscaled",
+    "altob200_grouped_gemm_blockscaled",
+)
+
+
+class QuantParams(C.Structure):
+    _fields_ = [
+        ("format", C.c_int32),
+        ("in_dtype", C.c_int32),
+        ("rounding", C.c_int32),
+        ("scale_flags", C.c_int32),
+        ("outer_scale", C.c_void_p),
+        ("rand_bits", C.c_void_p),
+        ("philox_seed", C.c_uint64),
+        ("philox_offset", C.c_uint64),
+        ("rht_n", C.c_int32),
+        ("rht_perm", C.POINTER(C.c_int32)),
+        ("rht_sign", C.POINTER(C.c_int32)),
+    ]
+
+
+class Altob200Error(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: {status_string(status)} (status {status})")
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def _declare(lib):
+    vp, i32, i64 = C.c_void_p, C.c_int32, C.c_int64
+    lib.altob200_version.restype = C.c_int
+    lib.altob200_status_string.restype = C.c_char_p
+    lib.altob200_status_string.argtypes = [C.c_int]
+    lib.altob200_packed_scale_bytes.restype = C.c_size_t
+    lib.altob200_packed_scale_bytes.argtypes = [i64, i64]
+    lib.altob200_status_read.restype = C.c_int
+    lib.altob200_status_read.argtypes = [vp, C.POINTER(i32)]
+    lib.altob200_amax.restype = C.c_int
+    lib.altob200_amax.argtypes = [vp, i32, i64, i64, i64, i32, C.POINTER(i32), C.POINTER(i32), vp, vp, vp, vp]
+    for name in ("altob200_quantize_rowwise", "altob200_quantize_colwise"):
+        f = getattr(lib, name)
+        f.restype = C.c_int
+        f.argtypes = [vp, i64, i64, i64, C.POINTER(QuantParams), vp, vp, vp, vp]
+    lib.altob200_quantize_2d.restype = C.c_int
+    lib.altob200_quantize_2d.argtypes = [vp, i64, i64, i64, C.POINTER(QuantParams), vp, vp, vp, vp, vp, vp]
+    lib.altob200_dequantize.restype = C.c_int
+    lib.altob200_dequantize.argtypes = [vp, vp, vp, i32, i32, i64, i64, i32, vp, i64, vp]
+    lib.altob200_rht.restype = C.c_int
+    lib.altob200_rht.argtypes = [vp, i32, i64, i64, i64, i32, C.POINTER(i32), C.POINTER(i32), vp, i64, vp]
+    lib.altob200_gemm_blockscaled.restype = C.c_int
+    lib.altob200_gemm_blockscaled.argtypes = [i32, i32, i64, i64, i64, vp, vp, vp, vp, vp, vp, i32, vp, i64, vp]
+    lib.altob200_grouped_gemm_blockscaled.restype = C.c_int
+    lib.altob200_grouped_gemm_blockscaled.argtypes = [i32, i32, i64, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp,
+                                                      i32, vp, i64, vp]
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not LIB_PATH.exists():
+                    raise RuntimeError(
+                        f"{LIB_PATH} is missing: build it with `python -m alto_b200.build` "
+                        "(there is no CPU or PyTorch fallback for this path)")
+                handle = C.CDLL(str(LIB_PATH))
+                _declare(handle)
+                _lib = handle
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return lib().altob200_status_string(int(status)).decode()
+
+
+def _check(status: int, where: str) -> None:
+    if status != 0:
+        raise Altob200Error(status, where)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _dt(t: torch.dtype) -> int:
+    if t == torch.bfloat16:
+        return DT_BF16
+    if t == torch.float32:
+        return DT_F32
+    raise AssertionError(f"unsupported high-precision dtype {t}")
+
+
+def _require_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("alto_b200 kernels run on CUDA tensors only (no CPU fallback)")
+
+
+def packed_scale_bytes(rows: int, ncols: int) -> int:
+    return int(lib().altob200_packed_scale_bytes(rows, ncols))
+
+
+def block_of(fmt: int) -> int:
+    return 16 if fmt == FMT_NVFP4 else 32
+
+
+def is_fp4(fmt: int) -> bool:
+    return fmt in (FMT_NVFP4, FMT_MXFP4)
+
+
+def _i32_array(v: Optional[Sequence[int]]):
+    if v is None:
+        return None
+    return (C.c_int32 * len(v))(*[int(x) for x in v])
+
+
+class Rht:
+    """Host description of a randomised Hadamard transform W = (diag(sign) H)[perm][:, perm]."""
+
+    def __init__(self, n: int, perm: Sequence[int], sign: Sequence[int]):
+        self.n = int(n)
+        self.perm = [int(p) for p in perm]
+        self.sign = [int(s) for s in sign]
+        self._perm_c = _i32_array(self.perm)
+        self._sign_c = _i32_array(self.sign)
+
+
+def _params(fmt, x, rounding, outer_scale, rand_bits, rht: Optional[Rht], flags) -> QuantParams:
+    p = QuantParams()
+    p.format = fmt
+    p.in_dtype = _dt(x.dtype)
+    p.rounding = rounding
+    p.scale_flags = flags
+    p.outer_scale = _ptr(outer_scale)
+    p.rand_bits = _ptr(rand_bits)
+    p.philox_seed = 0
+    p.philox_offset = 0
+    if rht is not None:
+        p.rht_n = rht.n
+        p.rht_perm = rht._perm_c
+        p.rht_sign = rht._sign_c
+    else:
+        p.rht_n = 0
+    return p
+
+
+def status_read() -> tuple:
+    """Synchronises the current stream and returns (status, [kernel, block, site, 0])."""
+    detail = (C.c_int32 * 4)()
+    st = lib().altob200_status_read(_stream(), detail)
+    return st, list(detail)
+
+
+def amax(x: torch.Tensor, amax_bits: torch.Tensor, outer_scale: Optional[torch.Tensor], scratch: torch.Tensor,
+         rht: Optional[Rht] = None) -> None:
+    """x: [rows, cols] (last dim contiguous).  amax_bits: uint32/int32 [2]; outer_scale: float32 [2] or None;
+    scratch: zeroed device buffer of AMAX_SCRATCH_BYTES."""
+    _require_cuda(x, amax_bits, outer_scale, scratch)
+    assert x.dim() == 2 and x.stride(1) == 1
+    _check(lib().altob200_amax(x.data_ptr(), _dt(x.dtype), x.shape[0], x.shape[1], x.stride(0),
+                               rht.n if rht else 0, rht._perm_c if rht else None, rht._sign_c if rht else None,
+                               amax_bits.data_ptr(), _ptr(outer_scale), scratch.data_ptr(), _stream()),
+           "altob200_amax")
+
+
+def quantize_rowwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, rounding=ROUND_RTN,
+                     outer_scale=None, rand_bits=None) -> None:
+    _require_cuda(x, codes, scale_plain, scale_packed, outer_scale, rand_bits)
+    assert x.dim() == 2 and x.stride(1) == 1
+    flags = (SCALE_PLAIN if scale_plain is not None else 0) | (SCALE_PACKED if scale_packed is not None else 0)
+    p = _params(fmt, x, rounding, outer_scale, rand_bits, None, flags)
+    _check(lib().altob200_quantize_rowwise(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), C.byref(p),
+                                           codes.data_ptr(), _ptr(scale_plain), _ptr(scale_packed), _stream()),
+           "altob200_quantize_rowwise")
+
+
+def quantize_colwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, rounding=ROUND_RTN,
+                     outer_scale=None, rand_bits=None, rht: Optional[Rht] = None) -> None:
+    _require_cuda(x, codes, scale_plain, scale_packed, outer_scale, rand_bits)
+    assert x.dim() == 2 and x.stride(1) == 1
+    flags = (SCALE_PLAIN if scale_plain is not None else 0) | (SCALE_PACKED if scale_packed is not None else 0)
+    p = _params(fmt, x, rounding, outer_scale, rand_bits, rht, flags)
+    _check(lib().altob200_quantize_colwise(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), C.byref(p),
+                                           codes.data_ptr(), _ptr(scale_plain), _ptr(scale_packed), _stream()),
+           "altob200_quantize_colwise")
+
+
+def quantize_2d(w, fmt, codes_k, codes_t=None, scale_plain=None, scale_packed_k=None, scale_packed_t=None, *,
+                outer_scale=None) -> None:
+    _require_cuda(w, codes_k, codes_t, scale_plain, scale_packed_k, scale_packed_t, outer_scale)
+    assert w.dim() == 2 and w.stride(1) == 1
+    p = _params(fmt, w, ROUND_RTN, outer_scale, None, None, 0)
+    _check(lib().altob200_quantize_2d(w.data_ptr(), w.shape[0], w.shape[1], w.stride(0), C.byref(p),
+                                      codes_k.data_ptr(), _ptr(codes_t), _ptr(scale_plain), _ptr(scale_packed_k),
+                                      _ptr(scale_packed_t), _stream()),
+           "altob200_quantize_2d")
+
+
+def dequantize(codes, scale_plain, fmt, is_2d, rows, cols, out, outer_scale=None) -> None:
+    _require_cuda(codes, scale_plain, out, outer_scale)
+    assert out.dim() == 2 and out.stride(1) == 1
+    _check(lib().altob200_dequantize(codes.data_ptr(), scale_plain.data_ptr(), _ptr(outer_scale), fmt,
+                                     1 if is_2d else 0, rows, cols, _dt(out.dtype), out.data_ptr(), out.stride(0),
+                                     _stream()),
+           "altob200_dequantize")
+
+
+def rht_apply(x, y, rht: Rht) -> None:
+    _require_cuda(x, y)
+    assert x.dim() == 2 and x.stride(1) == 1 and y.stride(1) == 1 and x.dtype == y.dtype
+    _check(lib().altob200_rht(x.data_ptr(), _dt(x.dtype), x.shape[0], x.shape[1], x.stride(0), rht.n, rht._perm_c,
+                              rht._sign_c, y.data_ptr(), y.stride(0), _stream()),
+           "altob200_rht")
+
+
+def gemm_blockscaled(fmt_a, fmt_b, M, N, K, a_codes, a_scales, b_codes, b_scales, out, alpha_a=None,
+                     alpha_b=None) -> None:
+    _require_cuda(a_codes, a_scales, b_codes, b_scales, out, alpha_a, alpha_b)
+    assert out.dim() == 2 and out.stride(1) == 1
+    _check(lib().altob200_gemm_blockscaled(fmt_a, fmt_b, M, N, K, a_codes.data_ptr(), a_scales.data_ptr(),
+                                           b_codes.data_ptr(), b_scales.data_ptr(), _ptr(alpha_a), _ptr(alpha_b),
+                                           _dt(out.dtype), out.data_ptr(), out.stride(0), _stream()),
+           "altob200_gemm_blockscaled")
+
+
+def grouped_gemm_blockscaled(fmt_a, fmt_b, M, N, K, num_experts, a_codes, a_scales, b_codes, b_scales,
+                             group_expert, out, alpha_a=None, alpha_b=None) -> None:
+    _require_cuda(a_codes, a_scales, b_codes, b_scales, group_expert, out, alpha_a, alpha_b)
+    assert out.dim() == 2 and out.stride(1) == 1 and group_expert.dtype == torch.int32
+    _check(lib().altob200_grouped_gemm_blockscaled(fmt_a, fmt_b, M, N, K, num_experts, a_codes.data_ptr(),
+                                                   a_scales.data_ptr(), b_codes.data_ptr(), b_scales.data_ptr(),
+                                                   group_expert.data_ptr(), _ptr(alpha_a), _ptr(alpha_b),
+                                                   _dt(out.dtype), out.data_ptr(), out.stride(0), _stream()),
+           "altob200_grouped_gemm_blockscaled")

@@ -1,0 +1,250 @@
+// Device-side arithmetic shared by the quantizer kernels: scale derivation, E2M1 / FP8
+// encode and decode, exact division, packed-scale addressing.
+//
+// Every function restates arithmetic of the reference so that codes and scales are
+// bit-identical to it; the citation next to each function names the reference lines.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/altob200.h"
+
+namespace altob200 {
+
+// ---------------------------------------------------------------------------------------
+// host helpers
+// ---------------------------------------------------------------------------------------
+#define ALTOB200_CUDA_CHECK(expr)                 \
+  do {                                            \
+    cudaError_t _e = (expr);                      \
+    if (_e != cudaSuccess) return ALTOB200_ECUDA; \
+  } while (0)
+
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---------------------------------------------------------------------------------------
+// bit casts
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t f2u(float f) { return __float_as_uint(f); }
+__device__ __forceinline__ float u2f(uint32_t u) { return __uint_as_float(u); }
+
+// bf16 pair (little endian: element 0 in the low half) -> two floats, exact.
+__device__ __forceinline__ float bf16lo_to_f32(uint32_t w) { return u2f(w << 16); }
+__device__ __forceinline__ float bf16hi_to_f32(uint32_t w) { return u2f(w & 0xFFFF0000u); }
+
+// float -> bf16 bits, round to nearest even (what Tensor.to(torch.bfloat16) does).
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+// ---------------------------------------------------------------------------------------
+// packed scale layout (tiles of 128 rows x 4 scale columns, 512 bytes each)
+// ---------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ int64_t packed_scale_offset(int64_t r, int64_t c,
+                                                                int64_t ncol_tiles) {
+  const int64_t tile = (r >> 7) * ncol_tiles + (c >> 2);
+  return tile * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c & 3);
+}
+
+// ---------------------------------------------------------------------------------------
+// E8M0 scale from a block amax, computed on the BITS of the amax in the input dtype.
+//   alto/kernels/fp4/mxfp4/mxfp_quantization.py:79-95  (mbits=1, target_max_pow2=2)
+//   alto/kernels/mxfp8/mxfp8_quantization.py:70-78      (e4m3: 3/8, e5m2: 2/15)
+// `amax_bits` is the non-negative amax as bf16 bits (IS_BF16) or fp32 bits.
+// ---------------------------------------------------------------------------------------
+template <bool IS_BF16>
+__device__ __forceinline__ uint32_t e8m0_from_amax_bits(uint32_t amax_bits, int mbits,
+                                                        int target_max_pow2) {
+  int e;
+  if (IS_BF16) {
+    // int16 arithmetic in the reference: wrap to 16 bits, arithmetic shift.
+    const int32_t v = (int32_t)(int16_t)(((amax_bits + (1u << (7 - mbits - 1))) & 0xFF80u));
+    e = (v >> 7) - target_max_pow2;
+  } else {
+    const int32_t v = (int32_t)((amax_bits + (1u << (23 - mbits - 1))) & 0xFF800000u);
+    e = (v >> 23) - target_max_pow2;
+  }
+  e = e < 1 ? 1 : e;
+  return (uint32_t)e & 0xFFu;  // .to(uint8)
+}
+
+// ---------------------------------------------------------------------------------------
+// float -> E4M3 (float8_e4m3fn) round-to-nearest-even for inputs already clamped to
+// [2^-6, 448] (all normal in E4M3), returned both as the byte and as the fp32 value.
+//   alto/kernels/fp4/nvfp4/nvfp_quantization.py:278-282
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float round_to_e4m3_grid(float x, uint32_t* code) {
+  uint32_t b = f2u(x);
+  b += 0x7FFFFu + ((b >> 20) & 1u);  // RNE on the 20 dropped mantissa bits
+  b &= 0xFFF00000u;
+  // E4M3 bias 7: exponent field = e32 - 127 + 7
+  const uint32_t e8 = (b >> 23) - 120u;
+  *code = (e8 << 3) | ((b >> 20) & 7u);
+  return u2f(b);
+}
+
+// NVFP4 block scales (inner on the E4M3 grid, quant = inner * outer).
+//   alto/kernels/fp4/nvfp4/nvfp_quantization.py:255-289
+__device__ __forceinline__ void nvfp4_block_scale(float amax, bool use_outer, float outer,
+                                                  float* inner, float* quant, uint32_t* code) {
+  if (amax != amax) amax = 0.0f;  // NaN amax -> 0
+  float raw = use_outer ? __fdiv_rn(__fdiv_rn(amax, outer), 6.0f) : __fdiv_rn(amax, 6.0f);
+  raw = fminf(fmaxf(raw, 0.015625f), 448.0f);
+  const float in = round_to_e4m3_grid(raw, code);
+  *inner = in;
+  *quant = use_outer ? __fmul_rn(in, outer) : in;
+}
+
+// ---------------------------------------------------------------------------------------
+// Exact fp32 division x / q.
+//
+// For a bf16-valued numerator the sequence  y = x*r; e = fma(-y, q, x); y' = fma(e, r, y)
+// with r = RN(1/q) returns the correctly rounded quotient (checked exhaustively over all
+// 2^7 numerator and 2^23 denominator mantissas); it needs q and the quotient to stay away
+// from the subnormal range, which callers guarantee by testing q once per block
+// (`div_fast_ok`).  The sign of x is copied so that -0.0 keeps its sign bit as IEEE
+// division does (the reference ORs that sign into the code, triton_fp4_ops.py:40-41,90-92).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ bool div_fast_ok(float q) {
+  const uint32_t e = (f2u(q) >> 23) & 0xFFu;
+  return e >= 67u && e <= 187u;  // 2^-60 <= q < 2^61
+}
+__device__ __forceinline__ float div_bf16_num(float x, float q, float r) {
+  const float y = __fmul_rn(x, r);
+  const float e = __fmaf_rn(-y, q, x);
+  const float y2 = __fmaf_rn(e, r, y);
+  return u2f((f2u(y2) & 0x7FFFFFFFu) | (f2u(x) & 0x80000000u));
+}
+
+// ---------------------------------------------------------------------------------------
+// E2M1 encode, round to nearest even, saturating.  Bit-for-bit restatement of
+//   alto/kernels/fp4/fp4_common/triton_fp4_ops.py:26-93 with USE_SR=False.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t e2m1_rtn_bits(float v) {
+  uint32_t qx = f2u(v);
+  const uint32_t s = qx & 0x80000000u;
+  qx ^= s;
+  const float a = u2f(qx);
+  uint32_t code;
+  if (a >= 6.0f) {
+    code = 7u;
+  } else if (a < 1.0f) {
+    // denormal range of E2M1: add 2^22 so that the fp32 adder rounds to a multiple of 0.5
+    const float d = __fadd_rn(a, u2f(149u << 23));
+    code = (f2u(d) - (149u << 23)) & 0xFFu;
+  } else {
+    // normal range (a NaN also lands here, as it does through the reference's masks)
+    const uint32_t mant_odd = (qx >> 22) & 1u;
+    const uint32_t n = qx + (uint32_t)((1 - 127) << 23) + ((1u << 21) - 1u) + mant_odd;
+    code = (n >> 22) & 0xFFu;
+  }
+  return (code | (s >> 28)) & 0xFFu;
+}
+
+// Two floats -> one byte of E2M1 codes (v0 in the low nibble) with the hardware
+// converter.  Identical to e2m1_rtn_bits for every finite input (round to nearest even on
+// the E2M1 grid including its subnormal 0.5, saturation to 6, sign of zero kept).
+__device__ __forceinline__ uint32_t e2m1x2_rtn_hw(float v0, float v1) {
+  uint16_t r;
+  asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }"
+      : "=h"(r)
+      : "f"(v1), "f"(v0));
+  return (uint32_t)r;
+}
+
+// ---------------------------------------------------------------------------------------
+// E2M1 encode with stochastic rounding from 32 random bits.  Restatement of
+//   alto/kernels/fp4/fp4_common/triton_fp4_ops.py:26-93 with USE_SR=True.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t e2m1_sr_bits(float v, uint32_t rnd) {
+  uint32_t qx = f2u(v);
+  const uint32_t s = qx & 0x80000000u;
+  qx ^= s;
+  const float a = u2f(qx);
+  uint32_t code;
+  if (a >= 6.0f) {
+    code = 7u;
+  } else if (a < 1.0f) {
+    if (a < 0.5f) {
+      // threshold_low = uint32(a * fp32(2^33 - 2)); the constant rounds to 2^33 in fp32.
+      const uint32_t thr = __float2uint_rz(__fmul_rn(a, 8589934592.0f));
+      code = (rnd <= thr) ? 1u : 0u;
+    } else {
+      // threshold_high = uint32((2a - 1) * fp32(2^32 - 1)); the constant rounds to 2^32.
+      const uint32_t thr = __float2uint_rz(__fmul_rn(__fadd_rn(__fmul_rn(a, 2.0f), -1.0f), 4294967296.0f));
+      code = (rnd <= thr) ? 2u : 1u;
+    }
+  } else {
+    uint32_t n = qx + (uint32_t)((1 - 127) << 23) + (rnd & 0x3FFFFFu);
+    code = (n >> 22) & 0xFFu;
+  }
+  return (code | (s >> 28)) & 0xFFu;
+}
+
+// E2M1 decode to fp32 (alto/kernels/fp4/fp4_common/triton_fp4_ops.py:100-132).
+__device__ __forceinline__ float e2m1_decode(uint32_t c) {
+  const uint32_t s = (c & 8u) << 28;
+  const uint32_t m = c & 7u;
+  uint32_t bits;
+  if (m == 0u) bits = 0u;
+  else if (m == 1u) bits = 0x3F000000u;
+  else bits = (((m >> 1) - 1u + 127u) << 23) | ((m & 1u) << 22);
+  return u2f(bits | s);
+}
+
+// ---------------------------------------------------------------------------------------
+// FP8 encode: saturating round-to-nearest-even (the emulation clamps to +-max and then
+// casts, tests/unittest/mxfp8/utils.py:126-132; the Triton cast saturates natively,
+// alto/kernels/mxfp8/mxfp8_quantization.py:263-281).  v0 goes to the low byte.
+// ---------------------------------------------------------------------------------------
+template <bool E5M2>
+__device__ __forceinline__ uint32_t fp8x2_rtn_hw(float v0, float v1) {
+  uint16_t r;
+  if (E5M2) {
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(v1), "f"(v0));
+  } else {
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(v1), "f"(v0));
+  }
+  return (uint32_t)r;
+}
+
+// Two FP8 bytes (low byte first) -> two floats; exact (both formats embed in fp16).
+template <bool E5M2>
+__device__ __forceinline__ float2 fp8x2_decode(uint32_t c) {
+  uint32_t h2;
+  const uint16_t c16 = (uint16_t)c;
+  if (E5M2) {
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(h2) : "h"(c16));
+  } else {
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(c16));
+  }
+  const __half2 h = *reinterpret_cast<const __half2*>(&h2);
+  return __half22float2(h);
+}
+
+// ---------------------------------------------------------------------------------------
+// Philox-4x32-10 with the counter/key convention of triton.language.randint4x(seed, offset):
+// counter = (offset_lo, offset_hi? 0, 0, 0), key = (seed_lo, seed_hi).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                              uint32_t k0, uint32_t k1, uint32_t out[4]) {
+  const uint32_t A = 0xD2511F53u, B = 0xCD9E8D57u, KA = 0x9E3779B9u, KB = 0xBB67AE85u;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t _c0 = c0, _c2 = c2;
+    c0 = __umulhi(B, _c2) ^ c1 ^ k0;
+    c2 = __umulhi(A, _c0) ^ c3 ^ k1;
+    c1 = B * _c2;
+    c3 = A * _c0;
+    k0 += KA;
+    k1 += KB;
+  }
+  out[0] = c0;
+  out[1] = c1;
+  out[2] = c2;
+  out[3] = c3;
+}
+
+}  // namespace altob200

@@ -1,0 +1,622 @@
+// Block-scaled GEMM for sm_100a:  D[m, n] = alpha * sum_k A[m, k] * B[n, k]
+//
+// Both operands are stored with the reduction axis contiguous (FP4: two codes per byte,
+// FP8: one byte per element) and carry one scale per 16 (NVFP4, UE4M3) or 32 (MXFP4 /
+// MXFP8, UE8M0) elements in the packed layout described in altob200.h.
+//
+// Structure of one CTA (192 threads, persistent over output tiles of 128 x BN):
+//   warp 0      : producer.  One elected lane issues, per k-stage, two tiled TMA loads
+//                 (A: 128 rows x 128 bytes, B: BN rows x 128 bytes, 128-byte swizzle) and
+//                 the bulk copies of the stage's scale tiles, all completing on the
+//                 stage's "full" mbarrier.
+//   warp 1      : MMA issuer.  Owns tensor memory (512 columns).  Per stage it copies
+//                 the scale tiles shared memory -> tensor memory (tcgen05.cp) and issues
+//                 four tcgen05.mma (each consumes 32 bytes of K per row), then commits to
+//                 the stage's "empty" mbarrier; after the last stage of a tile it commits
+//                 to the accumulator's "full" mbarrier.
+//   warps 2..5  : epilogue.  Each warp reads its 32-lane quarter of the accumulator with
+//                 tcgen05.ld, multiplies by alpha, converts and stores its rows.
+// Every mbarrier wait is bounded by a wall-clock limit; a wait that gives up records
+// {kernel, block, site} in a device status word, raises a CTA-wide abort flag, and all
+// roles fall through to the common teardown that frees tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace altob200 {
+
+__device__ int g_status[4] = {0, 0, 0, 0};
+
+constexpr int BM = 128;
+constexpr int STAGE_K_BYTES = 128;
+constexpr int NUM_THREADS = 192;
+constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // 4 s per wait
+
+enum { KIND_NVF4 = 0, KIND_MXF4 = 1, KIND_MXF8 = 2 };
+
+template <int KIND>
+struct Kind;
+template <>
+struct Kind<KIND_NVF4> {
+  static constexpr int SF_TILES = 4;  // 512-byte scale tiles per 128 rows per stage
+  static constexpr int ELEMS_PER_BYTE = 2, BLOCK = 16;
+};
+template <>
+struct Kind<KIND_MXF4> {
+  static constexpr int SF_TILES = 2;
+  static constexpr int ELEMS_PER_BYTE = 2, BLOCK = 32;
+};
+template <>
+struct Kind<KIND_MXF8> {
+  static constexpr int SF_TILES = 1;
+  static constexpr int ELEMS_PER_BYTE = 1, BLOCK = 32;
+};
+
+struct GemmArgs {
+  int64_t M, N, K;       // K in elements
+  int64_t k_bytes;       // bytes per operand row
+  const uint8_t* sfa;    // packed scales of A
+  const uint8_t* sfb;    // packed scales of B (per expert: stride sfb_expert_stride)
+  int64_t nct;           // scale tiles per 128-row block = ceil(K / BLOCK / 4)
+  const float* alpha_a;
+  const float* alpha_b;
+  void* d;
+  int64_t ldd;
+  int out_bf16;
+  // grouped mode (num_experts > 0): B rows are [num_experts * N], group_expert[m / 128]
+  int num_experts;
+  const int32_t* group_expert;
+  int64_t sfb_expert_stride;
+  uint32_t idesc[4];     // instruction descriptors of the four MMAs of a stage
+};
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false (and raises the abort flag) when the limit passes or when
+// another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0x3FFu) == 0) {
+      if (*abort_flag != 0) return false;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (atomicCAS(&g_status[0], 0, ALTOB200_ETIMEOUT_DEVICE) == 0) {
+          g_status[1] = 1;  // kernel id: gemm
+          g_status[2] = (int)blockIdx.x;
+          g_status[3] = site;
+        }
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate, uint32_t sfa, uint32_t sfb) {
+  if (KIND == KIND_NVF4) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else if (KIND == KIND_MXF4) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);      // start address
+  d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
+  d |= (uint64_t)1 << 46;                       // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+  return d;
+}
+// Descriptor of one 512-byte scale tile: 32 rows x 16 bytes, no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)(128 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+// ---------------------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------------------
+template <int KIND, int BN>
+struct Cfg {
+  static constexpr int SF_TILES = Kind<KIND>::SF_TILES;
+  static constexpr int NB = BN / 128;                        // 128-row blocks of B per tile
+  static constexpr int A_BYTES = BM * STAGE_K_BYTES;         // 16 KiB
+  static constexpr int B_BYTES = BN * STAGE_K_BYTES;
+  static constexpr int SFA_BYTES = SF_TILES * 512;
+  static constexpr int SFB_BYTES = NB * SF_TILES * 512;
+  // rounded up so that every stage starts on a 1024-byte boundary (128-byte swizzle atom)
+  static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024 * 1024;
+  static constexpr int SF_COLS_A = SF_TILES * 4;             // tensor-memory columns per stage
+  static constexpr int SF_COLS_B = SF_TILES * 4 * NB;
+  static constexpr int ACC_STAGES = (BN <= 128) ? 2 : 1;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_SF_BASE = ACC_STAGES * BN;
+  static constexpr int TMEM_COLS_USED = TMEM_SF_BASE + STAGES * (SF_COLS_A + SF_COLS_B);
+  static_assert(TMEM_COLS_USED <= 512, "tensor memory budget");
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const GemmArgs args) {
+  using C = Cfg<KIND, BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // operand stages need 1024-byte alignment for the 128-byte swizzle
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + C::STAGES;
+  uint64_t* acc_full = bars + 2 * C::STAGES;
+  uint64_t* acc_empty = acc_full + C::ACC_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::ACC_STAGES);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t tiles_m = (args.M + BM - 1) / BM;
+  const int64_t tiles_n = (args.N + BN - 1) / BN;
+  const int64_t n_tiles = tiles_m * tiles_n;
+  const int k_stages = (int)((args.k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES);
+  const int64_t n_row_blocks = (args.N + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < C::ACC_STAGES; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // Scale staging areas start from zero so that a stage whose K range is ragged never
+  // feeds uninitialised bytes (a NaN scale would poison the zero-filled codes).
+  for (int s = 0; s < C::STAGES; ++s) {
+    uint32_t* z = reinterpret_cast<uint32_t*>(smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+    for (int i = threadIdx.x; i < (C::SFA_BYTES + C::SFB_BYTES) / 4; i += NUM_THREADS) z[i] = 0u;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+        const int64_t mb = tile % tiles_m, nb = tile / tiles_m;
+        int64_t b_row0 = nb * BN;          // row of the B tensor map
+        const uint8_t* sfb = args.sfb;
+        if (args.num_experts > 0) {
+          const int e = __ldg(args.group_expert + mb);
+          if (e < 0) continue;             // padding group: no loads, epilogue writes zeros
+          b_row0 += (int64_t)e * args.N;
+          sfb += (int64_t)e * args.sfb_expert_stride;
+        }
+        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+          const int s = it % C::STAGES;
+          if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 1)) { alive = false; break; }
+          uint8_t* st = smem + s * C::STAGE_BYTES;
+          int64_t sf_tiles = args.nct - (int64_t)ks * C::SF_TILES;
+          if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
+          const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
+          // 128-row blocks of B that exist (the last tile of a ragged N has fewer)
+          int nb_valid = (int)(n_row_blocks - nb * C::NB);
+          if (nb_valid > C::NB) nb_valid = C::NB;
+          mbar_expect_tx(&full_bar[s], C::A_BYTES + C::B_BYTES + sf_bytes * (1 + nb_valid));
+          tma_load_2d(st, &tmap_a, ks * STAGE_K_BYTES, (int32_t)(mb * BM), &full_bar[s]);
+          tma_load_2d(st + C::A_BYTES, &tmap_b, ks * STAGE_K_BYTES, (int32_t)b_row0, &full_bar[s]);
+          const int64_t cb0 = (int64_t)ks * C::SF_TILES;
+          bulk_load(st + C::A_BYTES + C::B_BYTES, args.sfa + (mb * args.nct + cb0) * 512, sf_bytes, &full_bar[s]);
+#pragma unroll
+          for (int j = 0; j < C::NB; ++j)
+            if (j < nb_valid)
+              bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + j * C::SFA_BYTES,
+                        sfb + ((nb * C::NB + j) * args.nct + cb0) * 512, sf_bytes, &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, tile_it = 0;
+      bool alive = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+        if (args.num_experts > 0 && __ldg(args.group_expert + (tile % tiles_m)) < 0) continue;
+        const int acc = tile_it % C::ACC_STAGES;
+        if (!mbar_wait(&acc_empty[acc], ((tile_it / C::ACC_STAGES) & 1) ^ 1, abort_flag, 2)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+          const int s = it % C::STAGES;
+          if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 3)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
+          const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
+          // scale tiles: tile t of A -> 4 columns; tile t of B row block j -> columns t*4*NB + 4j
+#pragma unroll
+          for (int t = 0; t < C::SF_TILES; ++t) {
+            tc_cp_sf(sfa_t + t * 4, make_desc_sf(st + C::A_BYTES + C::B_BYTES + t * 512));
+#pragma unroll
+            for (int j = 0; j < C::NB; ++j)
+              tc_cp_sf(sfb_t + t * 4 * C::NB + j * 4,
+                       make_desc_sf(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + j * C::SFA_BYTES + t * 512));
+          }
+          const uint64_t a_desc = make_desc_sw128(st);
+          const uint64_t b_desc = make_desc_sw128(st + C::A_BYTES);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // MMA j covers bytes [32j, 32j+32) of the stage; its scale tile and byte offset
+            // inside the tile depend on how many scales one MMA consumes.
+            const int t = (KIND == KIND_NVF4) ? j : (KIND == KIND_MXF4 ? (j >> 1) : 0);
+            tc_mma<KIND>(d_tmem, a_desc + 2 * j, b_desc + 2 * j, args.idesc[j], (ks | j) != 0 ? 1u : 0u,
+                         sfa_t + t * 4, sfb_t + t * 4 * C::NB);
+          }
+          tc_commit(&empty_bar[s]);
+        }
+        if (alive) tc_commit(&acc_full[acc]);
+        ++tile_it;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int quad = warp & 3;  // tensor-memory lane quarter this warp may read
+    float alpha = 1.0f;
+    if (args.alpha_a != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_a));
+    if (args.alpha_b != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_b));
+    uint32_t tile_it = 0;
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      const int64_t mb = tile % tiles_m, nb = tile / tiles_m;
+      const int64_t row = mb * BM + quad * 32 + lane;
+      const bool pad_group = args.num_experts > 0 && __ldg(args.group_expert + mb) < 0;
+      const int acc = tile_it % C::ACC_STAGES;
+      if (!pad_group) {
+        if (!mbar_wait(&acc_full[acc], (tile_it / C::ACC_STAGES) & 1, abort_flag, 4)) break;
+        tc_fence_after();
+      }
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        uint32_t r[32];
+        if (!pad_group) {
+          tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + cc * 32, r);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (cc == BN / 32 - 1 && !pad_group) {
+          // all of this warp's reads of the accumulator are done
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+        const int64_t col0 = nb * BN + cc * 32;
+        if (row < args.M && col0 < args.N) {
+          const bool full = col0 + 32 <= args.N;
+          if (args.out_bf16) {
+            __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(args.d) + row * args.ldd + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  o[q] = f32_to_bf16_bits(__fmul_rn(u2f(r[8 * j + 2 * q]), alpha)) |
+                         (f32_to_bf16_bits(__fmul_rn(u2f(r[8 * j + 2 * q + 1]), alpha)) << 16);
+                reinterpret_cast<uint4*>(drow)[j] = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < args.N; ++j)
+                drow[j] = __float2bfloat16_rn(__fmul_rn(u2f(r[j]), alpha));
+            }
+          } else {
+            float* drow = reinterpret_cast<float*>(args.d) + row * args.ldd + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<float4*>(drow)[j] =
+                    make_float4(__fmul_rn(u2f(r[4 * j]), alpha), __fmul_rn(u2f(r[4 * j + 1]), alpha),
+                                __fmul_rn(u2f(r[4 * j + 2]), alpha), __fmul_rn(u2f(r[4 * j + 3]), alpha));
+            } else {
+              for (int j = 0; j < 32 && col0 + j < args.N; ++j) drow[j] = __fmul_rn(u2f(r[j]), alpha);
+            }
+          }
+        }
+      }
+      if (!pad_group) ++tile_it;
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2D uint8 tensor map over [rows, row_bytes] with a box of [box_rows, 128 bytes].
+static int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return ALTOB200_ECUDA;
+  cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)STAGE_K_BYTES, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+// Instruction descriptor of a block-scaled MMA (bit layout: b_sf_id [4,6), a_format [7,10),
+// b_format [10,13), n/8 [17,23), scale format [23], m/16 [24,29), a_sf_id [29,31)).
+static uint32_t make_idesc(int kind, int fmt_a, int fmt_b, int n, int sf_id) {
+  uint32_t af, bf, sfmt;
+  if (kind == KIND_MXF8) {
+    af = fmt_a == ALTOB200_FMT_MXFP8_E5M2 ? 1u : 0u;
+    bf = fmt_b == ALTOB200_FMT_MXFP8_E5M2 ? 1u : 0u;
+    sfmt = 1u;
+  } else {
+    af = bf = 1u;  // E2M1
+    sfmt = kind == KIND_NVF4 ? 0u : 1u;
+  }
+  uint32_t d = 0;
+  d |= (uint32_t)sf_id << 4;
+  d |= af << 7;
+  d |= bf << 10;
+  d |= (uint32_t)(n >> 3) << 17;
+  d |= sfmt << 23;
+  d |= (uint32_t)(BM >> 4) << 24;
+  d |= (uint32_t)sf_id << 29;
+  return d;
+}
+
+static int sm_count_gemm() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 148;
+  }
+  return n;
+}
+
+template <int KIND, int BN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, cudaStream_t st) {
+  using C = Cfg<KIND, BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    ALTOB200_CUDA_CHECK(cudaFuncSetAttribute(gemm_blockscaled_kernel<KIND, BN>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    attr_set = true;
+  }
+  const int64_t tiles = ceil_div(args.M, BM) * ceil_div(args.N, BN);
+  int64_t grid = sm_count_gemm();
+  if (grid > tiles) grid = tiles;
+  gemm_blockscaled_kernel<KIND, BN><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, args);
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N, int64_t K, int32_t num_experts,
+                       const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
+                       const int32_t* group_expert, const float* alpha_a, const float* alpha_b,
+                       int32_t out_dtype, void* d, int64_t ldd, void* stream) {
+  if (a_codes == nullptr || b_codes == nullptr || a_scales == nullptr || b_scales == nullptr || d == nullptr)
+    return ALTOB200_EINVAL_SHAPE;
+  int kind;
+  if (format_a == ALTOB200_FMT_NVFP4 && format_b == ALTOB200_FMT_NVFP4) kind = KIND_NVF4;
+  else if (format_a == ALTOB200_FMT_MXFP4 && format_b == ALTOB200_FMT_MXFP4) kind = KIND_MXF4;
+  else if ((format_a == ALTOB200_FMT_MXFP8_E4M3 || format_a == ALTOB200_FMT_MXFP8_E5M2) &&
+           (format_b == ALTOB200_FMT_MXFP8_E4M3 || format_b == ALTOB200_FMT_MXFP8_E5M2)) kind = KIND_MXF8;
+  else return ALTOB200_EUNSUPPORTED;
+  const int epb = kind == KIND_MXF8 ? 1 : 2;
+  const int block = kind == KIND_NVF4 ? 16 : 32;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || ldd < N) return ALTOB200_EINVAL_SHAPE;
+  if (num_experts > 0 && (M % 128 != 0 || group_expert == nullptr)) return ALTOB200_EINVAL_SHAPE;
+  const int64_t k_bytes = K / epb;
+  if (k_bytes % 16 != 0) return ALTOB200_EINVAL_SHAPE;
+  const int osz = out_dtype == ALTOB200_DT_BF16 ? 2 : 4;
+  if ((reinterpret_cast<uintptr_t>(a_codes) & 15) || (reinterpret_cast<uintptr_t>(b_codes) & 15) ||
+      (reinterpret_cast<uintptr_t>(a_scales) & 15) || (reinterpret_cast<uintptr_t>(b_scales) & 15) ||
+      (reinterpret_cast<uintptr_t>(d) & 15) || (ldd * osz) % 16 != 0)
+    return ALTOB200_EINVAL_ALIGN;
+  if (M >= (1ll << 31) || N * (num_experts > 0 ? num_experts : 1) >= (1ll << 31) || k_bytes >= (1ll << 31))
+    return ALTOB200_ELIMIT;
+
+  const int BN = N <= 128 ? 128 : 256;
+  const int64_t b_rows = N * (num_experts > 0 ? num_experts : 1);
+  CUtensorMap ta, tb;
+  int rc = make_tmap(&ta, a_codes, M, k_bytes, BM);
+  if (rc != ALTOB200_OK) return rc;
+  rc = make_tmap(&tb, b_codes, b_rows, k_bytes, BN);
+  if (rc != ALTOB200_OK) return rc;
+
+  GemmArgs g;
+  g.M = M; g.N = N; g.K = K; g.k_bytes = k_bytes;
+  g.sfa = (const uint8_t*)a_scales; g.sfb = (const uint8_t*)b_scales;
+  g.nct = ceil_div(K / block, 4);
+  g.alpha_a = alpha_a; g.alpha_b = alpha_b;
+  g.d = d; g.ldd = ldd; g.out_bf16 = out_dtype == ALTOB200_DT_BF16;
+  g.num_experts = num_experts; g.group_expert = group_expert;
+  g.sfb_expert_stride = (int64_t)altob200_packed_scale_bytes(N, K / block);
+  for (int j = 0; j < 4; ++j) {
+    const int sf_id = kind == KIND_NVF4 ? 0 : (kind == KIND_MXF4 ? (j & 1) * 2 : j);
+    g.idesc[j] = make_idesc(kind, format_a, format_b, BN, sf_id);
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH(KD)                                                    \
+  return BN == 128 ? launch_gemm<KD, 128>(ta, tb, g, st) : launch_gemm<KD, 256>(ta, tb, g, st)
+  switch (kind) {
+    case KIND_NVF4: LAUNCH(KIND_NVF4);
+    case KIND_MXF4: LAUNCH(KIND_MXF4);
+    default: LAUNCH(KIND_MXF8);
+  }
+#undef LAUNCH
+}
+
+}  // namespace altob200
+
+using namespace altob200;
+
+extern "C" {
+
+int altob200_gemm_blockscaled(int32_t format_a, int32_t format_b, int64_t M, int64_t N, int64_t K,
+                              const void* a_codes, const void* a_scales, const void* b_codes,
+                              const void* b_scales, const float* alpha_a, const float* alpha_b,
+                              int32_t out_dtype, void* d, int64_t ldd, void* stream) {
+  return gemm_common(format_a, format_b, M, N, K, 0, a_codes, a_scales, b_codes, b_scales, nullptr, alpha_a,
+                     alpha_b, out_dtype, d, ldd, stream);
+}
+
+int altob200_grouped_gemm_blockscaled(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
+                                      int64_t K, int32_t num_experts, const void* a_codes,
+                                      const void* a_scales, const void* b_codes,
+                                      const void* b_scales, const int32_t* group_expert,
+                                      const float* alpha_a, const float* alpha_b,
+                                      int32_t out_dtype, void* d, int64_t ldd, void* stream) {
+  if (num_experts <= 0) return ALTOB200_EINVAL_SHAPE;
+  return gemm_common(format_a, format_b, M, N, K, num_experts, a_codes, a_scales, b_codes, b_scales,
+                     group_expert, alpha_a, alpha_b, out_dtype, d, ldd, stream);
+}
+
+int altob200_status_read(void* stream, int32_t detail[4]) {
+  cudaStream_t st = (cudaStream_t)stream;
+  int h[4] = {0, 0, 0, 0};
+  if (cudaStreamSynchronize(st) != cudaSuccess) return ALTOB200_ECUDA;
+  if (cudaMemcpyFromSymbol(h, g_status, sizeof(h)) != cudaSuccess) return ALTOB200_ECUDA;
+  if (h[0] != 0) {
+    const int z[4] = {0, 0, 0, 0};
+    if (cudaMemcpyToSymbol(g_status, z, sizeof(z)) != cudaSuccess) return ALTOB200_ECUDA;
+  }
+  if (detail != nullptr) {
+    detail[0] = h[1]; detail[1] = h[2]; detail[2] = h[3]; detail[3] = 0;
+  }
+  return h[0];
+}
+
+}  // extern "C"

@@ -1,0 +1,1229 @@
+// Bandwidth kernels of the low-precision linear path: block quantizers (row-wise,
+// column-wise with the optional randomised Hadamard transform, 2D with dual packing),
+// tensor amax, dequantizers and the standalone Hadamard transform.
+//
+// Work layout (all kernels are HBM bound; every global access is a full 32-byte sector
+// or better, and every thread keeps one quantisation block or a fixed part of it in
+// registers):
+//   row-wise  : a warp owns 512 contiguous elements of one row, a lane 16 of them
+//               (two 128-bit loads for bf16).  NVFP4 blocks (16) live in one lane, MX
+//               blocks (32) in a lane pair.
+//   col-wise  : a CTA owns a 256-row x 64-column tile; a lane owns two adjacent columns
+//               of one block of rows, so the Hadamard butterfly and the block amax need
+//               no shuffles.  Codes are transposed through shared memory so that every
+//               output row receives 128 contiguous bytes.
+//   2D        : a CTA owns 128 rows x 4 blocks of columns; segment and block maxima go
+//               through shared memory, and the tile is written in both packings.
+#include "common.cuh"
+
+namespace altob200 {
+
+// ---------------------------------------------------------------------------------------
+// format traits
+// ---------------------------------------------------------------------------------------
+template <int FMT>
+struct Fmt;
+template <>
+struct Fmt<ALTOB200_FMT_NVFP4> {
+  static constexpr int B = 16;
+  static constexpr bool FP4 = true, MX = false, E5M2 = false;
+  static constexpr int MBITS = 0, TMAX = 0;
+};
+template <>
+struct Fmt<ALTOB200_FMT_MXFP4> {
+  static constexpr int B = 32;
+  static constexpr bool FP4 = true, MX = true, E5M2 = false;
+  static constexpr int MBITS = 1, TMAX = 2;
+};
+template <>
+struct Fmt<ALTOB200_FMT_MXFP8_E4M3> {
+  static constexpr int B = 32;
+  static constexpr bool FP4 = false, MX = true, E5M2 = false;
+  static constexpr int MBITS = 3, TMAX = 8;
+};
+template <>
+struct Fmt<ALTOB200_FMT_MXFP8_E5M2> {
+  static constexpr int B = 32;
+  static constexpr bool FP4 = false, MX = true, E5M2 = true;
+  static constexpr int MBITS = 2, TMAX = 15;
+};
+
+// Scale of one quantisation block, in the forms the element loop needs.
+struct BlockScale {
+  float q;        // divisor applied to the elements
+  float r;        // reciprocal used by the fast paths
+  bool fast;      // fast path valid
+  uint32_t byte;  // stored scale byte (E8M0 exponent or E4M3 code)
+  float plain;    // NVFP4: inner scale as fp32 (plain layout)
+};
+
+// amax_abs_bits: max over the block of (bits & 0x7FFF..) in the input dtype's bit width
+// (bf16 bits or fp32 bits); integer max propagates NaN like torch.amax does.
+template <int FMT, bool IN_BF16>
+__device__ __forceinline__ BlockScale make_block_scale(uint32_t amax_abs_bits, bool use_outer,
+                                                       float outer) {
+  using F = Fmt<FMT>;
+  BlockScale s;
+  if (F::MX) {
+    const uint32_t e = e8m0_from_amax_bits<IN_BF16>(amax_abs_bits, F::MBITS, F::TMAX);
+    s.byte = e;
+    s.q = u2f(e << 23);
+    s.fast = e <= 253u;
+    s.r = u2f((254u - e) << 23);
+    s.plain = 0.0f;
+  } else {
+    const float amax = IN_BF16 ? u2f(amax_abs_bits << 16) : u2f(amax_abs_bits);
+    nvfp4_block_scale(amax, use_outer, outer, &s.plain, &s.q, &s.byte);
+    s.fast = IN_BF16 && div_fast_ok(s.q);
+    s.r = __frcp_rn(s.q);
+  }
+  return s;
+}
+
+template <int FMT, bool IN_BF16>
+__device__ __forceinline__ float scale_elem(float x, const BlockScale& s) {
+  if (Fmt<FMT>::MX) return s.fast ? __fmul_rn(x, s.r) : __fdiv_rn(x, s.q);
+  return s.fast ? div_bf16_num(x, s.q, s.r) : __fdiv_rn(x, s.q);
+}
+
+// Quantise 2 scaled values into one FP4 byte (v0 low nibble).
+template <int ROUND>
+__device__ __forceinline__ uint32_t fp4_pair(float v0, float v1, uint32_t r0, uint32_t r1) {
+  if (ROUND == ALTOB200_ROUND_RTN) return e2m1x2_rtn_hw(v0, v1);
+  return e2m1_sr_bits(v0, r0) | (e2m1_sr_bits(v1, r1) << 4);
+}
+
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t w) {
+  return __vmaxu2(acc, w & 0x7FFF7FFFu);
+}
+__device__ __forceinline__ uint32_t fold_bf16x2(uint32_t acc) {
+  const uint32_t lo = acc & 0xFFFFu, hi = acc >> 16;
+  return lo > hi ? lo : hi;
+}
+
+// =======================================================================================
+// Row-wise quantizer
+// =======================================================================================
+struct RowwiseArgs {
+  const void* x;
+  int64_t rows, cols, ld;
+  uint8_t* codes;
+  void* scale_plain;
+  uint8_t* scale_packed;
+  int64_t ncol_tiles;  // ceil(cols / B / 4)
+  const float* outer;
+  const uint32_t* rand_bits;
+};
+
+template <int FMT, bool IN_BF16, int ROUND>
+__global__ void __launch_bounds__(256) quantize_rowwise_kernel(RowwiseArgs a) {
+  using F = Fmt<FMT>;
+  constexpr int LPB = F::B / 16;  // lanes per block
+  const int lane = threadIdx.x & 31;
+  const int64_t chunks_per_row = (a.cols + 511) >> 9;
+  const int64_t n_tasks = a.rows * chunks_per_row;
+  const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const bool use_outer = (!F::MX) && a.outer != nullptr;
+  const float outer = use_outer ? __ldg(a.outer) : 1.0f;
+  const int64_t half_cols = a.cols >> 1;
+
+  for (int64_t task = warp0; task < n_tasks; task += n_warps) {
+    const int64_t row = task / chunks_per_row;
+    const int64_t chunk = task - row * chunks_per_row;
+    const int64_t col = (chunk << 9) + lane * 16;
+    const bool active = col < a.cols;
+
+    float v[16];
+    uint32_t amax_bits = 0;
+    if (IN_BF16) {
+      uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
+      if (active) {
+        const uint4* p = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const __nv_bfloat16*>(a.x) + row * a.ld + col);
+        w0 = __ldg(p);
+        w1 = __ldg(p + 1);
+      }
+      const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      uint32_t acc = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc = absmax_bf16x2(acc, w[j]);
+        v[2 * j] = bf16lo_to_f32(w[j]);
+        v[2 * j + 1] = bf16hi_to_f32(w[j]);
+      }
+      amax_bits = fold_bf16x2(acc);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (active)
+          f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) +
+                                                    row * a.ld + col) + j);
+        v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const uint32_t b = f2u(v[j]) & 0x7FFFFFFFu;
+        amax_bits = b > amax_bits ? b : amax_bits;
+      }
+    }
+    if (LPB == 2) {
+      const uint32_t o = __shfl_xor_sync(0xFFFFFFFFu, amax_bits, 1);
+      amax_bits = o > amax_bits ? o : amax_bits;
+    }
+    const BlockScale s = make_block_scale<FMT, IN_BF16>(amax_bits, use_outer, outer);
+
+    // random bits (explicit mode): 8 words per plane for this lane's 8 element pairs
+    uint32_t r0[8], r1[8];
+    if (ROUND == ALTOB200_ROUND_SR_BITS) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) r0[j] = r1[j] = 0;
+      if (active) {
+        const uint4* p0 = reinterpret_cast<const uint4*>(a.rand_bits + row * half_cols + (col >> 1));
+        const uint4* p1 = reinterpret_cast<const uint4*>(a.rand_bits + a.rows * half_cols +
+                                                         row * half_cols + (col >> 1));
+        const uint4 a0 = __ldg(p0), a1 = __ldg(p0 + 1), b0 = __ldg(p1), b1 = __ldg(p1 + 1);
+        r0[0] = a0.x; r0[1] = a0.y; r0[2] = a0.z; r0[3] = a0.w;
+        r0[4] = a1.x; r0[5] = a1.y; r0[6] = a1.z; r0[7] = a1.w;
+        r1[0] = b0.x; r1[1] = b0.y; r1[2] = b0.z; r1[3] = b0.w;
+        r1[4] = b1.x; r1[5] = b1.y; r1[6] = b1.z; r1[7] = b1.w;
+      }
+    }
+
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = scale_elem<FMT, IN_BF16>(v[j], s);
+
+    if (F::FP4) {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= fp4_pair<ROUND>(v[2 * j], v[2 * j + 1], r0[j], r1[j]) << (8 * j);
+        hi |= fp4_pair<ROUND>(v[8 + 2 * j], v[9 + 2 * j], r0[4 + j], r1[4 + j]) << (8 * j);
+      }
+      if (active)
+        *reinterpret_cast<uint2*>(a.codes + row * half_cols + (col >> 1)) = make_uint2(lo, hi);
+    } else {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = fp8x2_rtn_hw<F::E5M2>(v[4 * j], v[4 * j + 1]) |
+               (fp8x2_rtn_hw<F::E5M2>(v[4 * j + 2], v[4 * j + 3]) << 16);
+      if (active)
+        *reinterpret_cast<uint4*>(a.codes + row * a.cols + col) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+
+    // scales
+    const int64_t kb = (chunk << 9) / F::B + lane / LPB;  // scale column of this lane
+    const bool holder = active && (lane % LPB == 0);
+    if (a.scale_plain != nullptr && holder) {
+      if (F::MX)
+        reinterpret_cast<uint8_t*>(a.scale_plain)[row * (a.cols / F::B) + kb] = (uint8_t)s.byte;
+      else
+        reinterpret_cast<float*>(a.scale_plain)[row * (a.cols / F::B) + kb] = s.plain;
+    }
+    if (a.scale_packed != nullptr) {
+      uint32_t word = holder ? s.byte : 0u;
+      word |= __shfl_down_sync(0xFFFFFFFFu, word, LPB) << 8;
+      word |= __shfl_down_sync(0xFFFFFFFFu, word, 2 * LPB) << 16;
+      if ((lane % (4 * LPB) == 0) && (kb < a.ncol_tiles * 4))
+        *reinterpret_cast<uint32_t*>(a.scale_packed + packed_scale_offset(row, kb, a.ncol_tiles)) = word;
+    }
+  }
+}
+
+// =======================================================================================
+// Hadamard helpers (n = 16, Sylvester ordering, in registers)
+// =======================================================================================
+struct RhtParams {
+  int n;           // 0 or 16
+  int8_t pinv[16]; // slot k reads row pinv[k] of the block
+  int8_t perm[16]; // output position i takes slot perm[i]
+  float sign[16];  // sign applied to slot k after the butterfly
+};
+
+__device__ __forceinline__ void hadamard16(float* z) {
+#pragma unroll
+  for (int h = 1; h < 16; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if ((i & h) == 0) {
+        const float a = z[i], b = z[i + h];
+        z[i] = __fadd_rn(a, b);
+        z[i + h] = __fsub_rn(a, b);
+      }
+    }
+  }
+}
+
+// =======================================================================================
+// Column-wise quantizer (axis 0) with optional Hadamard transform
+// =======================================================================================
+struct ColwiseArgs {
+  const void* x;
+  int64_t rows, cols, ld;
+  uint8_t* codes;       // [cols, rows/2] or [cols, rows]
+  void* scale_plain;    // [cols, rows/B]
+  uint8_t* scale_packed;
+  int64_t ncol_tiles;   // ceil(rows / B / 4)
+  const float* outer;
+  const uint32_t* rand_bits;  // [2][cols][rows/2]
+  RhtParams rht;
+};
+
+constexpr int COL_TM = 256;  // rows per CTA tile
+constexpr int COL_TN = 64;   // columns per CTA tile
+
+template <int FMT, bool IN_BF16, int ROUND, bool RHT>
+__global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
+  using F = Fmt<FMT>;
+  constexpr int B = F::B;
+  constexpr int NBLK = COL_TM / B;          // row blocks per tile (16 or 8)
+  constexpr int ITERS = NBLK / 8;           // per warp
+  constexpr int ROW_BYTES = F::FP4 ? COL_TM / 2 : COL_TM;  // bytes per output row per tile
+  constexpr int BLK_BYTES = F::FP4 ? B / 2 : B;            // bytes per block per column
+  // codes staged as [block][column][BLK_BYTES]; scales as [column][NBLK]
+  __shared__ __align__(16) uint8_t s_codes[COL_TN * ROW_BYTES];
+  __shared__ __align__(16) uint8_t s_sf[COL_TN * NBLK];
+  __shared__ float s_sf_plain[Fmt<FMT>::MX ? 1 : COL_TN * NBLK];
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t m0 = (int64_t)blockIdx.y * COL_TM;
+  const int64_t n0 = (int64_t)blockIdx.x * COL_TN;
+  const int64_t c = n0 + 2 * lane;  // first of this lane's two columns
+  const bool col_ok = c < a.cols;   // cols is even, so c+1 is valid too
+  const bool use_outer = (!F::MX) && a.outer != nullptr;
+  const float outer = use_outer ? __ldg(a.outer) : 1.0f;
+  const int64_t half_rows = a.rows >> 1;
+
+#pragma unroll 1
+  for (int it = 0; it < ITERS; ++it) {
+    const int blk = warp * ITERS + it;
+    const int64_t mb = m0 + (int64_t)blk * B;
+    const bool ok = col_ok && mb < a.rows;  // rows % B == 0
+    float v0[B], v1[B];
+    // ---- load (slot k <- row pinv[k] when the transform is on) ----
+#pragma unroll
+    for (int k = 0; k < B; ++k) {
+      const int src = RHT ? ((k & ~15) + a.rht.pinv[k & 15]) : k;
+      float f0 = 0.f, f1 = 0.f;
+      if (ok) {
+        if (IN_BF16) {
+          const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(
+              reinterpret_cast<const __nv_bfloat16*>(a.x) + (mb + src) * a.ld + c));
+          f0 = bf16lo_to_f32(w);
+          f1 = bf16hi_to_f32(w);
+        } else {
+          const float2 f = __ldg(reinterpret_cast<const float2*>(
+              reinterpret_cast<const float*>(a.x) + (mb + src) * a.ld + c));
+          f0 = f.x;
+          f1 = f.y;
+        }
+      }
+      v0[k] = f0;
+      v1[k] = f1;
+    }
+    // ---- transform: y = (H z) / sqrt(16), rounded to the input dtype ----
+    if (RHT) {
+#pragma unroll
+      for (int g = 0; g < B; g += 16) {
+        hadamard16(v0 + g);
+        hadamard16(v1 + g);
+      }
+#pragma unroll
+      for (int k = 0; k < B; ++k) {
+        const float sg = 0.25f * a.rht.sign[k & 15];  // +-1/sqrt(16), exact
+        v0[k] = __fmul_rn(v0[k], sg);
+        v1[k] = __fmul_rn(v1[k], sg);
+        if (IN_BF16) {
+          v0[k] = u2f(f32_to_bf16_bits(v0[k]) << 16);
+          v1[k] = u2f(f32_to_bf16_bits(v1[k]) << 16);
+        }
+      }
+    }
+    // ---- block amax on the bits of the (possibly rounded) values ----
+    uint32_t am0 = 0, am1 = 0;
+#pragma unroll
+    for (int k = 0; k < B; ++k) {
+      const uint32_t b0 = f2u(v0[k]) & 0x7FFFFFFFu, b1 = f2u(v1[k]) & 0x7FFFFFFFu;
+      am0 = b0 > am0 ? b0 : am0;
+      am1 = b1 > am1 ? b1 : am1;
+    }
+    if (IN_BF16) {
+      am0 >>= 16;
+      am1 >>= 16;
+    }
+    const BlockScale s0 = make_block_scale<FMT, IN_BF16>(am0, use_outer, outer);
+    const BlockScale s1 = make_block_scale<FMT, IN_BF16>(am1, use_outer, outer);
+
+    // ---- quantise in slot order ----
+    if (F::FP4) {
+#pragma unroll
+      for (int h = 0; h < B / 16; ++h) {
+        uint64_t w0 = 0, w1 = 0;  // nibble j = code of slot 16h + j
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int k = 16 * h + j;
+          const float q0 = scale_elem<FMT, IN_BF16>(v0[k], s0);
+          const float q1 = scale_elem<FMT, IN_BF16>(v1[k], s1);
+          uint32_t c0, c1;
+          if (ROUND == ALTOB200_ROUND_RTN) {
+            // the hardware converter takes one value of each column per call
+            const uint32_t b = e2m1x2_rtn_hw(q0, q1);
+            c0 = b & 0xFu;
+            c1 = b >> 4;
+          } else {
+            // the output position of a slot decides which random word it consumes
+            const int pos = RHT ? (16 * h + a.rht.pinv[j]) : k;
+            uint32_t rr0 = 0, rr1 = 0;
+            if (ok) {
+              const int64_t plane = (int64_t)(pos & 1) * a.cols * half_rows;
+              const int64_t idx = (mb + pos) >> 1;
+              rr0 = __ldg(a.rand_bits + plane + c * half_rows + idx);
+              rr1 = __ldg(a.rand_bits + plane + (c + 1) * half_rows + idx);
+            }
+            c0 = e2m1_sr_bits(q0, rr0);
+            c1 = e2m1_sr_bits(q1, rr1);
+          }
+          w0 |= (uint64_t)c0 << (4 * j);
+          w1 |= (uint64_t)c1 << (4 * j);
+        }
+        uint64_t o0 = w0, o1 = w1;
+        if (RHT) {  // output position i takes slot perm[i]
+          o0 = o1 = 0;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            o0 |= ((w0 >> (4 * a.rht.perm[i])) & 0xFull) << (4 * i);
+            o1 |= ((w1 >> (4 * a.rht.perm[i])) & 0xFull) << (4 * i);
+          }
+        }
+        uint8_t* d = s_codes + ((size_t)blk * COL_TN + 2 * lane) * BLK_BYTES + 8 * h;
+        *reinterpret_cast<uint2*>(d) = make_uint2((uint32_t)o0, (uint32_t)(o0 >> 32));
+        *reinterpret_cast<uint2*>(d + BLK_BYTES) = make_uint2((uint32_t)o1, (uint32_t)(o1 >> 32));
+      }
+    } else {
+      // FP8: one byte per element, no transform (the reference asserts that MXFP8 runs
+      // without Hadamard, alto/kernels/dispatch/tensor.py:448-454)
+      uint8_t* d = s_codes + ((size_t)blk * COL_TN + 2 * lane) * BLK_BYTES;
+#pragma unroll
+      for (int k = 0; k < B; k += 4) {
+        float q0[4], q1[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          q0[j] = scale_elem<FMT, IN_BF16>(v0[k + j], s0);
+          q1[j] = scale_elem<FMT, IN_BF16>(v1[k + j], s1);
+        }
+        *reinterpret_cast<uint32_t*>(d + k) = fp8x2_rtn_hw<F::E5M2>(q0[0], q0[1]) |
+                                              (fp8x2_rtn_hw<F::E5M2>(q0[2], q0[3]) << 16);
+        *reinterpret_cast<uint32_t*>(d + BLK_BYTES + k) =
+            fp8x2_rtn_hw<F::E5M2>(q1[0], q1[1]) | (fp8x2_rtn_hw<F::E5M2>(q1[2], q1[3]) << 16);
+      }
+    }
+    s_sf[(2 * lane) * NBLK + blk] = ok ? (uint8_t)s0.byte : 0;
+    s_sf[(2 * lane + 1) * NBLK + blk] = ok ? (uint8_t)s1.byte : 0;
+    if (!F::MX) {
+      s_sf_plain[(2 * lane) * NBLK + blk] = s0.plain;
+      s_sf_plain[(2 * lane + 1) * NBLK + blk] = s1.plain;
+    }
+  }
+  __syncthreads();
+
+  // ---- write codes: output row n gets ROW_BYTES contiguous bytes, 16 bytes per thread ----
+  constexpr int CHUNKS = ROW_BYTES / 16;  // 8 (FP4) or 16 (FP8) per output row
+  for (int t = threadIdx.x; t < COL_TN * CHUNKS; t += 256) {
+    const int n = t / CHUNKS, ch = t - n * CHUNKS;
+    const int64_t col = n0 + n;
+    const int64_t mrow = m0 + (int64_t)ch * (F::FP4 ? 32 : 16);  // first row covered by this chunk
+    if (col >= a.cols || mrow >= a.rows) continue;
+    // a 16-byte chunk covers 32 rows (FP4) or 16 rows (FP8)
+    uint4 o;
+    if (BLK_BYTES >= 16) {
+      const int blk = (ch * 16) / BLK_BYTES, off = (ch * 16) % BLK_BYTES;
+      o = *reinterpret_cast<const uint4*>(s_codes + ((size_t)blk * COL_TN + n) * BLK_BYTES + off);
+    } else {  // BLK_BYTES == 8: two blocks per chunk
+      const uint2 lo = *reinterpret_cast<const uint2*>(s_codes + ((size_t)(2 * ch) * COL_TN + n) * 8);
+      const uint2 hi = *reinterpret_cast<const uint2*>(s_codes + ((size_t)(2 * ch + 1) * COL_TN + n) * 8);
+      o = make_uint4(lo.x, lo.y, hi.x, hi.y);
+    }
+    uint8_t* dst = a.codes + col * (F::FP4 ? half_rows : a.rows) + (F::FP4 ? (m0 >> 1) : m0) + ch * 16;
+    const int64_t rows_left = a.rows - mrow;
+    if (rows_left >= (F::FP4 ? 32 : 16)) {
+      *reinterpret_cast<uint4*>(dst) = o;
+    } else {  // ragged tail: rows_left is a multiple of B = 16 here (NVFP4 only)
+      *reinterpret_cast<uint2*>(dst) = make_uint2(o.x, o.y);
+    }
+  }
+  // ---- write scales ----
+  const int64_t nkb = a.rows / B;
+  if (a.scale_plain != nullptr) {
+    for (int t = threadIdx.x; t < COL_TN * NBLK; t += 256) {
+      const int n = t / NBLK, b = t - n * NBLK;
+      const int64_t col = n0 + n, kb = m0 / B + b;
+      if (col < a.cols && kb < nkb) {
+        if (F::MX) reinterpret_cast<uint8_t*>(a.scale_plain)[col * nkb + kb] = s_sf[n * NBLK + b];
+        else reinterpret_cast<float*>(a.scale_plain)[col * nkb + kb] = s_sf_plain[n * NBLK + b];
+      }
+    }
+  }
+  if (a.scale_packed != nullptr) {
+    for (int t = threadIdx.x; t < COL_TN * (NBLK / 4); t += 256) {
+      const int n = t / (NBLK / 4), qd = t - n * (NBLK / 4);
+      const int64_t col = n0 + n, kb = m0 / B + qd * 4;
+      if (col < a.cols && kb < a.ncol_tiles * 4) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (kb + j < nkb) word |= (uint32_t)s_sf[n * NBLK + qd * 4 + j] << (8 * j);
+        *reinterpret_cast<uint32_t*>(a.scale_packed + packed_scale_offset(col, kb, a.ncol_tiles)) = word;
+      }
+    }
+  }
+}
+
+// =======================================================================================
+// 2D block quantizer with dual packing
+// =======================================================================================
+struct Quant2dArgs {
+  const void* w;
+  int64_t rows, cols, ld;
+  uint8_t* codes_k;   // [rows, cols/2] or [rows, cols]
+  uint8_t* codes_t;   // [cols, rows/2] or [cols, rows]
+  void* scale_plain;  // [rows/B, cols/B]
+  uint8_t* packed_k;  // rows=rows, ncols=cols/B
+  uint8_t* packed_t;  // rows=cols, ncols=rows/B
+  int64_t nct_k, nct_t;
+  const float* outer;
+};
+
+template <int FMT, bool IN_BF16>
+__global__ void __launch_bounds__(128 * Fmt<FMT>::B / 4) quantize_2d_kernel(Quant2dArgs a) {
+  using F = Fmt<FMT>;
+  constexpr int B = F::B;
+  constexpr int TR = 128;           // tile rows
+  constexpr int TC = 4 * B;         // tile cols (64 or 128)
+  constexpr int SEGS = TC / 16;     // 16-element segments per row (4 or 8)
+  constexpr int NBR = TR / B, NBC = 4;
+  constexpr int EB = F::FP4 ? 2 : 1;  // elements per byte
+  constexpr int KROW = TC / EB;       // bytes per tile row in K packing (+16 pad)
+  __shared__ uint32_t s_segmax[TR][SEGS];
+  __shared__ float s_q[NBR][NBC], s_r[NBR][NBC], s_plain[NBR][NBC];
+  __shared__ uint8_t s_byte[NBR][NBC], s_fast[NBR][NBC];
+  __shared__ __align__(16) uint8_t s_tile[TR][KROW + 16];
+
+  const int t = threadIdx.x;
+  const int r = t / SEGS, sg = t % SEGS;
+  const int64_t row = (int64_t)blockIdx.y * TR + r;
+  const int64_t col = (int64_t)blockIdx.x * TC + sg * 16;
+  const bool ok = row < a.rows && col < a.cols;  // cols % 16 == 0
+  const bool use_outer = (!F::MX) && a.outer != nullptr;
+  const float outer = use_outer ? __ldg(a.outer) : 1.0f;
+
+  float v[16];
+  uint32_t amax_bits = 0;
+  if (IN_BF16) {
+    uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
+    if (ok) {
+      const uint4* p = reinterpret_cast<const uint4*>(
+          reinterpret_cast<const __nv_bfloat16*>(a.w) + row * a.ld + col);
+      w0 = __ldg(p);
+      w1 = __ldg(p + 1);
+    }
+    const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    uint32_t acc = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      acc = absmax_bf16x2(acc, w[j]);
+      v[2 * j] = bf16lo_to_f32(w[j]);
+      v[2 * j + 1] = bf16hi_to_f32(w[j]);
+    }
+    amax_bits = fold_bf16x2(acc);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ok)
+        f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + row * a.ld + col) + j);
+      v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t b = f2u(v[j]) & 0x7FFFFFFFu;
+      amax_bits = b > amax_bits ? b : amax_bits;
+    }
+  }
+  s_segmax[r][sg] = amax_bits;
+  __syncthreads();
+  if (t < NBR * NBC) {
+    const int br = t / NBC, bc = t % NBC;
+    uint32_t m = 0;
+    for (int i = 0; i < B; ++i)
+      for (int j = 0; j < B / 16; ++j) {
+        const uint32_t x = s_segmax[br * B + i][bc * (B / 16) + j];
+        m = x > m ? x : m;
+      }
+    const BlockScale s = make_block_scale<FMT, IN_BF16>(m, use_outer, outer);
+    s_q[br][bc] = s.q; s_r[br][bc] = s.r; s_plain[br][bc] = s.plain;
+    s_byte[br][bc] = (uint8_t)s.byte; s_fast[br][bc] = s.fast ? 1 : 0;
+    const int64_t gbr = (int64_t)blockIdx.y * NBR + br, gbc = (int64_t)blockIdx.x * NBC + bc;
+    if (a.scale_plain != nullptr && gbr < a.rows / B && gbc < a.cols / B) {
+      if (F::MX) reinterpret_cast<uint8_t*>(a.scale_plain)[gbr * (a.cols / B) + gbc] = (uint8_t)s.byte;
+      else reinterpret_cast<float*>(a.scale_plain)[gbr * (a.cols / B) + gbc] = s.plain;
+    }
+  }
+  __syncthreads();
+  {
+    const int br = r / B, bc = (sg * 16) / B;
+    BlockScale s;
+    s.q = s_q[br][bc]; s.r = s_r[br][bc]; s.fast = s_fast[br][bc] != 0; s.byte = 0; s.plain = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = scale_elem<FMT, IN_BF16>(v[j], s);
+    if (F::FP4) {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= e2m1x2_rtn_hw(v[2 * j], v[2 * j + 1]) << (8 * j);
+        hi |= e2m1x2_rtn_hw(v[8 + 2 * j], v[9 + 2 * j]) << (8 * j);
+      }
+      *reinterpret_cast<uint2*>(&s_tile[r][sg * 8]) = make_uint2(lo, hi);
+      if (ok) *reinterpret_cast<uint2*>(a.codes_k + row * (a.cols >> 1) + (col >> 1)) = make_uint2(lo, hi);
+    } else {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = fp8x2_rtn_hw<F::E5M2>(v[4 * j], v[4 * j + 1]) |
+               (fp8x2_rtn_hw<F::E5M2>(v[4 * j + 2], v[4 * j + 3]) << 16);
+      *reinterpret_cast<uint4*>(&s_tile[r][sg * 16]) = make_uint4(o[0], o[1], o[2], o[3]);
+      if (ok) *reinterpret_cast<uint4*>(a.codes_k + row * a.cols + col) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  // packed scales for the K packing: one word (4 block columns) per row
+  if (a.packed_k != nullptr && sg == 0 && row < a.rows) {
+    const int br = r / B;
+    const int64_t kb = (int64_t)blockIdx.x * NBC;
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (kb + j < a.cols / B) word |= (uint32_t)s_byte[br][j] << (8 * j);
+    if (kb < a.nct_k * 4)
+      *reinterpret_cast<uint32_t*>(a.packed_k + packed_scale_offset(row, kb, a.nct_k)) = word;
+  }
+  __syncthreads();
+  // transposed packing: output row = tile column k, 128 tile rows along the packed axis
+  if (a.codes_t != nullptr) {
+    constexpr int OUT_BYTES = TR / EB;       // bytes per output row per tile (64 or 128)
+    constexpr int CH = OUT_BYTES / 8;        // 8-byte chunks per output row
+    for (int i = t; i < TC * CH; i += blockDim.x) {
+      const int k = i / CH, ch = i - k * CH;
+      const int64_t gk = (int64_t)blockIdx.x * TC + k;
+      if (gk >= a.cols) continue;
+      uint32_t lo = 0, hi = 0;
+      if (F::FP4) {
+        // 8 output bytes = 16 tile rows; byte j pairs rows 2j (low nibble) and 2j+1
+        const int rb = ch * 16;
+        const int sh = (k & 1) * 4;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t c0 = (s_tile[rb + 2 * j][k >> 1] >> sh) & 0xFu;
+          const uint32_t c1 = (s_tile[rb + 2 * j + 1][k >> 1] >> sh) & 0xFu;
+          const uint32_t b = c0 | (c1 << 4);
+          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+        }
+        const int64_t grow = (int64_t)blockIdx.y * TR + rb;
+        if (grow < a.rows)  // rows % 16 == 0
+          *reinterpret_cast<uint2*>(a.codes_t + gk * (a.rows >> 1) + (grow >> 1)) = make_uint2(lo, hi);
+      } else {
+        const int rb = ch * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t b = s_tile[rb + j][k];
+          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+        }
+        const int64_t grow = (int64_t)blockIdx.y * TR + rb;
+        if (grow < a.rows)  // rows % 32 == 0
+          *reinterpret_cast<uint2*>(a.codes_t + gk * a.rows + grow) = make_uint2(lo, hi);
+      }
+    }
+  }
+  if (a.packed_t != nullptr) {
+    // rows = tile columns (TC), scale columns = tile row blocks (NBR = 8 or 4)
+    for (int i = t; i < TC * (NBR / 4); i += blockDim.x) {
+      const int k = i / (NBR / 4), qd = i - k * (NBR / 4);
+      const int64_t gk = (int64_t)blockIdx.x * TC + k;
+      const int64_t kb = (int64_t)blockIdx.y * NBR + qd * 4;
+      if (gk >= a.cols || kb >= a.nct_t * 4) continue;
+      uint32_t word = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (kb + j < a.rows / B) word |= (uint32_t)s_byte[qd * 4 + j][k / B] << (8 * j);
+      *reinterpret_cast<uint32_t*>(a.packed_t + packed_scale_offset(gk, kb, a.nct_t)) = word;
+    }
+  }
+}
+
+// =======================================================================================
+// Tensor amax (plain and Hadamard-transformed) with the outer-scale finalisation
+// =======================================================================================
+struct AmaxArgs {
+  const void* x;
+  int64_t rows, cols, ld;
+  uint32_t* amax_bits;   // [2], zero on entry
+  float* outer_scale;    // [2] or NULL
+  uint32_t* counter;     // scratch, zero on entry, zero on exit
+  RhtParams rht;
+};
+
+__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const uint32_t t = __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    v = t > v ? t : v;
+  }
+  return v;
+}
+
+// outer = max(nan_to_num(amax) / (448 * 6), 1e-30)
+//   alto/kernels/fp4/nvfp4/nvfp_quantization.py:484-487
+__device__ __forceinline__ float outer_from_amax_bits(uint32_t bits) {
+  float amax = u2f(bits);
+  if (bits > 0x7F800000u) amax = 0.0f;               // NaN -> 0
+  if (bits == 0x7F800000u) amax = 3.4028234663852886e38f;  // nan_to_num(+inf) -> float max
+  return fmaxf(__fdiv_rn(amax, 2688.0f), 1.0e-30f);
+}
+
+template <bool IN_BF16, bool RHT>
+__global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
+  __shared__ uint32_t s_red[2][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t am_plain = 0, am_rht = 0;
+  if (!RHT) {
+    // flat pass, 16 bytes per thread per step; rows are contiguous when ld == cols
+    const int64_t vec = IN_BF16 ? 8 : 4;
+    const int64_t vec_per_row = a.cols / vec;
+    const int64_t total = a.rows * vec_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t row = i / vec_per_row, cv = i - row * vec_per_row;
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(
+          reinterpret_cast<const uint8_t*>(a.x) + (row * a.ld + cv * vec) * (IN_BF16 ? 2 : 4)));
+      if (IN_BF16) {
+        uint32_t acc = absmax_bf16x2(0, w.x);
+        acc = absmax_bf16x2(acc, w.y);
+        acc = absmax_bf16x2(acc, w.z);
+        acc = absmax_bf16x2(acc, w.w);
+        const uint32_t m = fold_bf16x2(acc) << 16;
+        am_plain = m > am_plain ? m : am_plain;
+      } else {
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t b = ws[j] & 0x7FFFFFFFu;
+          am_plain = b > am_plain ? b : am_plain;
+        }
+      }
+    }
+  } else {
+    // column pass: 16-row groups x 2 columns per lane, as in the column-wise quantizer
+    const int64_t groups = a.rows >> 4;
+    const int64_t col_tiles = (a.cols + 63) >> 6;
+    const int64_t n_tasks = groups * col_tiles;
+    const int64_t warp0 = (int64_t)blockIdx.x * 8 + warp, n_warps = (int64_t)gridDim.x * 8;
+    for (int64_t task = warp0; task < n_tasks; task += n_warps) {
+      const int64_t g = task / col_tiles, ct = task - g * col_tiles;
+      const int64_t c = (ct << 6) + 2 * lane;
+      if (c >= a.cols) continue;
+      float v0[16], v1[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const int src = a.rht.pinv[k];
+        float f0, f1;
+        if (IN_BF16) {
+          const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(
+              reinterpret_cast<const __nv_bfloat16*>(a.x) + ((g << 4) + src) * a.ld + c));
+          f0 = bf16lo_to_f32(w);
+          f1 = bf16hi_to_f32(w);
+        } else {
+          const float2 f = __ldg(reinterpret_cast<const float2*>(
+              reinterpret_cast<const float*>(a.x) + ((g << 4) + src) * a.ld + c));
+          f0 = f.x;
+          f1 = f.y;
+        }
+        const uint32_t b0 = f2u(f0) & 0x7FFFFFFFu, b1 = f2u(f1) & 0x7FFFFFFFu;
+        am_plain = b0 > am_plain ? b0 : am_plain;
+        am_plain = b1 > am_plain ? b1 : am_plain;
+        v0[k] = f0;
+        v1[k] = f1;
+      }
+      hadamard16(v0);
+      hadamard16(v1);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        // the row signs of the transform do not change magnitudes
+        float y0 = __fmul_rn(v0[k], 0.25f), y1 = __fmul_rn(v1[k], 0.25f);
+        uint32_t b0, b1;
+        if (IN_BF16) {
+          b0 = (f32_to_bf16_bits(y0) & 0x7FFFu) << 16;
+          b1 = (f32_to_bf16_bits(y1) & 0x7FFFu) << 16;
+        } else {
+          b0 = f2u(y0) & 0x7FFFFFFFu;
+          b1 = f2u(y1) & 0x7FFFFFFFu;
+        }
+        am_rht = b0 > am_rht ? b0 : am_rht;
+        am_rht = b1 > am_rht ? b1 : am_rht;
+      }
+    }
+  }
+  am_plain = warp_max_u32(am_plain);
+  am_rht = warp_max_u32(am_rht);
+  if (lane == 0) {
+    s_red[0][warp] = am_plain;
+    s_red[1][warp] = am_rht;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t p = 0, h = 0;
+    for (int i = 0; i < 8; ++i) {
+      p = s_red[0][i] > p ? s_red[0][i] : p;
+      h = s_red[1][i] > h ? s_red[1][i] : h;
+    }
+    atomicMax(a.amax_bits, p);
+    if (RHT) atomicMax(a.amax_bits + 1, h);
+    __threadfence();
+    const uint32_t ticket = atomicAdd(a.counter, 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence();
+      const uint32_t fp = atomicMax(a.amax_bits, 0u), fh = atomicMax(a.amax_bits + 1, 0u);
+      if (a.outer_scale != nullptr) {
+        a.outer_scale[0] = outer_from_amax_bits(fp);
+        if (RHT) a.outer_scale[1] = outer_from_amax_bits(fh);
+      }
+      *a.counter = 0u;
+    }
+  }
+}
+
+// =======================================================================================
+// Dequantizer (row-major codes, plain scales)
+// =======================================================================================
+struct DequantArgs {
+  const uint8_t* codes;
+  const void* scales;
+  const float* outer;
+  int64_t rows, cols, ld_out;
+  void* out;
+  int is_2d;
+};
+
+template <int FMT, bool OUT_BF16>
+__global__ void __launch_bounds__(256) dequantize_kernel(DequantArgs a) {
+  using F = Fmt<FMT>;
+  const int64_t segs_per_row = a.cols >> 4;
+  const int64_t total = a.rows * segs_per_row;
+  const float outer = (!F::MX && a.outer != nullptr) ? __ldg(a.outer) : 1.0f;
+  const bool use_outer = (!F::MX && a.outer != nullptr);
+  const int64_t nsc = a.cols / F::B;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / segs_per_row, sg = i - row * segs_per_row;
+    const int64_t col = sg << 4;
+    const int64_t srow = a.is_2d ? row / F::B : row;
+    float s;
+    if (F::MX) {
+      s = u2f((uint32_t)reinterpret_cast<const uint8_t*>(a.scales)[srow * nsc + col / F::B] << 23);
+    } else {
+      s = reinterpret_cast<const float*>(a.scales)[srow * nsc + col / F::B];
+      if (use_outer) s = __fmul_rn(s, outer);
+    }
+    float v[16];
+    if (F::FP4) {
+      const uint2 w = __ldg(reinterpret_cast<const uint2*>(a.codes + row * (a.cols >> 1) + (col >> 1)));
+      const uint32_t ws[2] = {w.x, w.y};
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        v[j] = __fmul_rn(e2m1_decode((ws[j >> 3] >> (4 * (j & 7))) & 0xFu), s);
+    } else {
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(a.codes + row * a.cols + col));
+      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float2 f = fp8x2_decode<F::E5M2>((ws[j >> 1] >> (16 * (j & 1))) & 0xFFFFu);
+        v[2 * j] = __fmul_rn(f.x, s);
+        v[2 * j + 1] = __fmul_rn(f.y, s);
+      }
+    }
+    if (OUT_BF16) {
+      uint32_t o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        o[j] = f32_to_bf16_bits(v[2 * j]) | (f32_to_bf16_bits(v[2 * j + 1]) << 16);
+      uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + row * a.ld_out + col);
+      d[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    } else {
+      float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + row * a.ld_out + col);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) d[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+  }
+}
+
+// =======================================================================================
+// Standalone randomised Hadamard transform (n = 16)
+// =======================================================================================
+struct RhtArgs {
+  const void* x;
+  void* y;
+  int64_t rows, cols, ld, ld_y;
+  RhtParams rht;
+};
+
+template <bool IN_BF16>
+__global__ void __launch_bounds__(256) rht_kernel(RhtArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t groups = a.rows >> 4;
+  const int64_t col_tiles = (a.cols + 63) >> 6;
+  const int64_t n_tasks = groups * col_tiles;
+  const int64_t warp0 = (int64_t)blockIdx.x * 8 + warp, n_warps = (int64_t)gridDim.x * 8;
+  for (int64_t task = warp0; task < n_tasks; task += n_warps) {
+    const int64_t g = task / col_tiles, ct = task - g * col_tiles;
+    const int64_t c = (ct << 6) + 2 * lane;
+    if (c >= a.cols) continue;
+    float v0[16], v1[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int src = a.rht.pinv[k];
+      float f0, f1;
+      if (IN_BF16) {
+        const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(
+            reinterpret_cast<const __nv_bfloat16*>(a.x) + ((g << 4) + src) * a.ld + c));
+        f0 = bf16lo_to_f32(w);
+        f1 = bf16hi_to_f32(w);
+      } else {
+        const float2 f = __ldg(reinterpret_cast<const float2*>(
+            reinterpret_cast<const float*>(a.x) + ((g << 4) + src) * a.ld + c));
+        f0 = f.x;
+        f1 = f.y;
+      }
+      v0[k] = f0;
+      v1[k] = f1;
+    }
+    hadamard16(v0);
+    hadamard16(v1);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      // slot k is output row pinv[k] of the group (y[i] = sign[perm[i]] * u[perm[i]])
+      const int64_t orow = (g << 4) + a.rht.pinv[k];
+      const float sg = 0.25f * a.rht.sign[k];
+      const float y0 = __fmul_rn(v0[k], sg), y1 = __fmul_rn(v1[k], sg);
+      if (IN_BF16) {
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(a.y) + orow * a.ld_y + c) =
+            f32_to_bf16_bits(y0) | (f32_to_bf16_bits(y1) << 16);
+      } else {
+        *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.y) + orow * a.ld_y + c) = make_float2(y0, y1);
+      }
+    }
+  }
+}
+
+// =======================================================================================
+// host side
+// =======================================================================================
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 148;
+  }
+  return n;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int fill_rht(RhtParams* r, int n, const int32_t* perm, const int32_t* sign) {
+  r->n = n;
+  if (n == 0) {
+    for (int i = 0; i < 16; ++i) { r->pinv[i] = (int8_t)i; r->perm[i] = (int8_t)i; r->sign[i] = 1.0f; }
+    return ALTOB200_OK;
+  }
+  if (n != 16) return ALTOB200_EUNSUPPORTED;
+  if (perm == nullptr || sign == nullptr) return ALTOB200_EINVAL_SHAPE;
+  bool seen[16] = {false};
+  for (int i = 0; i < 16; ++i) {
+    if (perm[i] < 0 || perm[i] > 15 || seen[perm[i]]) return ALTOB200_EINVAL_SHAPE;
+    if (sign[i] != 1 && sign[i] != -1) return ALTOB200_EINVAL_SHAPE;
+    seen[perm[i]] = true;
+  }
+  // W[i][j] = sign[perm[i]] * H[perm[i]][perm[j]]:  z[k] = x[pinv[k]],  y[i] = sign[perm[i]] * (H z)[perm[i]]
+  for (int i = 0; i < 16; ++i) {
+    r->perm[i] = (int8_t)perm[i];
+    r->pinv[perm[i]] = (int8_t)i;
+    r->sign[i] = (float)sign[i];
+  }
+  return ALTOB200_OK;
+}
+
+template <int FMT, bool IN_BF16>
+static int launch_rowwise(const RowwiseArgs& a, int rounding, cudaStream_t st) {
+  const int64_t tasks = a.rows * ((a.cols + 511) >> 9);
+  int64_t blocks = ceil_div(tasks, 8);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  if (rounding == ALTOB200_ROUND_RTN)
+    quantize_rowwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN><<<(unsigned)blocks, 256, 0, st>>>(a);
+  else if (rounding == ALTOB200_ROUND_SR_BITS && Fmt<FMT>::FP4)
+    quantize_rowwise_kernel<FMT, IN_BF16, Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN>
+        <<<(unsigned)blocks, 256, 0, st>>>(a);
+  else
+    return ALTOB200_EUNSUPPORTED;
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+template <int FMT, bool IN_BF16>
+static int launch_colwise(const ColwiseArgs& a, int rounding, cudaStream_t st) {
+  dim3 grid((unsigned)ceil_div(a.cols, COL_TN), (unsigned)ceil_div(a.rows, COL_TM));
+  const bool rht = a.rht.n != 0;
+  if (!Fmt<FMT>::FP4 && (rht || rounding != ALTOB200_ROUND_RTN)) return ALTOB200_EUNSUPPORTED;
+  if (rounding == ALTOB200_ROUND_RTN) {
+    if (rht) quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, Fmt<FMT>::FP4><<<grid, 256, 0, st>>>(a);
+    else quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, false><<<grid, 256, 0, st>>>(a);
+  } else if (rounding == ALTOB200_ROUND_SR_BITS) {
+    constexpr int R = Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN;
+    if (rht) quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4><<<grid, 256, 0, st>>>(a);
+    else quantize_colwise_kernel<FMT, IN_BF16, R, false><<<grid, 256, 0, st>>>(a);
+  } else {
+    return ALTOB200_EUNSUPPORTED;
+  }
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+template <int FMT, bool IN_BF16>
+static int launch_2d(const Quant2dArgs& a, cudaStream_t st) {
+  constexpr int TC = 4 * Fmt<FMT>::B;
+  dim3 grid((unsigned)ceil_div(a.cols, TC), (unsigned)ceil_div(a.rows, 128));
+  quantize_2d_kernel<FMT, IN_BF16><<<grid, 128 * Fmt<FMT>::B / 4, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+#define DISPATCH_FMT_DT(fmt, dt, CALL)                                                      \
+  do {                                                                                      \
+    const bool _bf = (dt) == ALTOB200_DT_BF16;                                              \
+    switch (fmt) {                                                                          \
+      case ALTOB200_FMT_NVFP4:                                                              \
+        return _bf ? CALL(ALTOB200_FMT_NVFP4, true) : CALL(ALTOB200_FMT_NVFP4, false);      \
+      case ALTOB200_FMT_MXFP4:                                                              \
+        return _bf ? CALL(ALTOB200_FMT_MXFP4, true) : CALL(ALTOB200_FMT_MXFP4, false);      \
+      case ALTOB200_FMT_MXFP8_E4M3:                                                         \
+        return _bf ? CALL(ALTOB200_FMT_MXFP8_E4M3, true) : CALL(ALTOB200_FMT_MXFP8_E4M3, false); \
+      case ALTOB200_FMT_MXFP8_E5M2:                                                         \
+        return _bf ? CALL(ALTOB200_FMT_MXFP8_E5M2, true) : CALL(ALTOB200_FMT_MXFP8_E5M2, false); \
+      default:                                                                              \
+        return ALTOB200_EUNSUPPORTED;                                                       \
+    }                                                                                       \
+  } while (0)
+
+static int block_of(int fmt) { return fmt == ALTOB200_FMT_NVFP4 ? 16 : 32; }
+static bool is_fp4(int fmt) { return fmt == ALTOB200_FMT_NVFP4 || fmt == ALTOB200_FMT_MXFP4; }
+
+// Zero a packed-scale buffer when the tile grid has padding the kernels do not visit.
+static int clear_packed_if_padded(void* buf, int64_t rows, int64_t ncols, cudaStream_t st) {
+  if (buf == nullptr) return ALTOB200_OK;
+  if ((rows & 127) == 0 && (ncols & 3) == 0) return ALTOB200_OK;
+  ALTOB200_CUDA_CHECK(cudaMemsetAsync(buf, 0, altob200_packed_scale_bytes(rows, ncols), st));
+  return ALTOB200_OK;
+}
+
+}  // namespace altob200
+
+using namespace altob200;
+
+extern "C" {
+
+int altob200_version(void) { return 1; }
+
+const char* altob200_status_string(int status) {
+  switch (status) {
+    case ALTOB200_OK: return "ok";
+    case ALTOB200_EINVAL_SHAPE: return "invalid shape or size contract";
+    case ALTOB200_EINVAL_ALIGN: return "misaligned pointer or leading dimension";
+    case ALTOB200_ETIMEOUT_DEVICE: return "bounded device-side wait timed out";
+    case ALTOB200_ECUDA: return "CUDA call failed";
+    case ALTOB200_EUNSUPPORTED: return "unsupported configuration";
+    case ALTOB200_ELIMIT: return "size exceeds a fixed maximum";
+    default: return "unknown status";
+  }
+}
+
+size_t altob200_packed_scale_bytes(int64_t rows, int64_t ncols) {
+  return (size_t)(ceil_div(rows, 128) * ceil_div(ncols, 4) * 512);
+}
+
+int altob200_quantize_rowwise(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                              const altob200_quant_params* p, void* codes, void* scale_plain,
+                              void* scale_packed, void* stream) {
+  if (x == nullptr || p == nullptr || codes == nullptr) return ALTOB200_EINVAL_SHAPE;
+  const int B = block_of(p->format);
+  if (rows <= 0 || cols <= 0 || cols % B != 0 || ld < cols) return ALTOB200_EINVAL_SHAPE;
+  const int esz = p->in_dtype == ALTOB200_DT_BF16 ? 2 : 4;
+  if (!aligned16(x) || (ld * esz) % 16 != 0 || !aligned16(codes)) return ALTOB200_EINVAL_ALIGN;
+  if (p->rounding == ALTOB200_ROUND_SR_BITS && (p->rand_bits == nullptr || !aligned16(p->rand_bits)))
+    return ALTOB200_EINVAL_ALIGN;
+  if (p->rht_n != 0) return ALTOB200_EUNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  RowwiseArgs a;
+  a.x = x; a.rows = rows; a.cols = cols; a.ld = ld;
+  a.codes = (uint8_t*)codes; a.scale_plain = scale_plain; a.scale_packed = (uint8_t*)scale_packed;
+  a.ncol_tiles = ceil_div(cols / B, 4);
+  a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
+  int rc = clear_packed_if_padded(scale_packed, rows, cols / B, st);
+  if (rc != ALTOB200_OK) return rc;
+  const int rounding = p->rounding;
+#define CALL_ROW(F, BF) launch_rowwise<F, BF>(a, rounding, st)
+  DISPATCH_FMT_DT(p->format, p->in_dtype, CALL_ROW);
+#undef CALL_ROW
+}
+
+int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                              const altob200_quant_params* p, void* codes, void* scale_plain,
+                              void* scale_packed, void* stream) {
+  if (x == nullptr || p == nullptr || codes == nullptr) return ALTOB200_EINVAL_SHAPE;
+  const int B = block_of(p->format);
+  if (rows <= 0 || cols <= 0 || rows % B != 0 || cols % 8 != 0 || ld < cols) return ALTOB200_EINVAL_SHAPE;
+  if (p->rht_n != 0 && rows % p->rht_n != 0) return ALTOB200_EINVAL_SHAPE;
+  // every output row must start on a 16-byte boundary
+  const int64_t out_row_bytes = is_fp4(p->format) ? rows / 2 : rows;
+  if (out_row_bytes % 8 != 0) return ALTOB200_EINVAL_SHAPE;
+  const int esz = p->in_dtype == ALTOB200_DT_BF16 ? 2 : 4;
+  if (!aligned16(x) || (ld * esz) % 16 != 0 || !aligned16(codes) || out_row_bytes % 16 != 0)
+    return ALTOB200_EINVAL_ALIGN;
+  if (p->rounding == ALTOB200_ROUND_SR_BITS && p->rand_bits == nullptr) return ALTOB200_EINVAL_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  ColwiseArgs a;
+  a.x = x; a.rows = rows; a.cols = cols; a.ld = ld;
+  a.codes = (uint8_t*)codes; a.scale_plain = scale_plain; a.scale_packed = (uint8_t*)scale_packed;
+  a.ncol_tiles = ceil_div(rows / B, 4);
+  a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
+  int rc = fill_rht(&a.rht, p->rht_n, p->rht_perm, p->rht_sign);
+  if (rc != ALTOB200_OK) return rc;
+  rc = clear_packed_if_padded(scale_packed, cols, rows / B, st);
+  if (rc != ALTOB200_OK) return rc;
+  const int rounding = p->rounding;
+#define CALL_COL(F, BF) launch_colwise<F, BF>(a, rounding, st)
+  DISPATCH_FMT_DT(p->format, p->in_dtype, CALL_COL);
+#undef CALL_COL
+}
+
+int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
+                         const altob200_quant_params* p, void* codes_k, void* codes_t,
+                         void* scale_plain, void* scale_packed_k, void* scale_packed_t,
+                         void* stream) {
+  if (w == nullptr || p == nullptr || codes_k == nullptr) return ALTOB200_EINVAL_SHAPE;
+  const int B = block_of(p->format);
+  if (rows <= 0 || cols <= 0 || rows % B != 0 || cols % B != 0 || ld < cols) return ALTOB200_EINVAL_SHAPE;
+  if (p->rounding != ALTOB200_ROUND_RTN || p->rht_n != 0) return ALTOB200_EUNSUPPORTED;
+  const int esz = p->in_dtype == ALTOB200_DT_BF16 ? 2 : 4;
+  if (!aligned16(w) || (ld * esz) % 16 != 0 || !aligned16(codes_k)) return ALTOB200_EINVAL_ALIGN;
+  if (codes_t != nullptr && !aligned16(codes_t)) return ALTOB200_EINVAL_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  Quant2dArgs a;
+  a.w = w; a.rows = rows; a.cols = cols; a.ld = ld;
+  a.codes_k = (uint8_t*)codes_k; a.codes_t = (uint8_t*)codes_t; a.scale_plain = scale_plain;
+  a.packed_k = (uint8_t*)scale_packed_k; a.packed_t = (uint8_t*)scale_packed_t;
+  a.nct_k = ceil_div(cols / B, 4); a.nct_t = ceil_div(rows / B, 4);
+  a.outer = p->outer_scale;
+  int rc = clear_packed_if_padded(scale_packed_k, rows, cols / B, st);
+  if (rc != ALTOB200_OK) return rc;
+  rc = clear_packed_if_padded(scale_packed_t, cols, rows / B, st);
+  if (rc != ALTOB200_OK) return rc;
+#define CALL_2D(F, BF) launch_2d<F, BF>(a, st)
+  DISPATCH_FMT_DT(p->format, p->in_dtype, CALL_2D);
+#undef CALL_2D
+}
+
+int altob200_amax(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, int64_t ld,
+                  int32_t rht_n, const int32_t* rht_perm, const int32_t* rht_sign,
+                  uint32_t* amax_bits, float* outer_scale, void* scratch, void* stream) {
+  if (x == nullptr || amax_bits == nullptr || scratch == nullptr) return ALTOB200_EINVAL_SHAPE;
+  if (rows <= 0 || cols <= 0 || cols % 8 != 0 || ld < cols) return ALTOB200_EINVAL_SHAPE;
+  if (rht_n != 0 && rows % rht_n != 0) return ALTOB200_EINVAL_SHAPE;
+  const int esz = in_dtype == ALTOB200_DT_BF16 ? 2 : 4;
+  if (!aligned16(x) || (ld * esz) % 16 != 0) return ALTOB200_EINVAL_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  AmaxArgs a;
+  a.x = x; a.rows = rows; a.cols = cols; a.ld = ld;
+  a.amax_bits = amax_bits; a.outer_scale = outer_scale; a.counter = (uint32_t*)scratch;
+  int rc = fill_rht(&a.rht, rht_n, rht_perm, rht_sign);
+  if (rc != ALTOB200_OK) return rc;
+  ALTOB200_CUDA_CHECK(cudaMemsetAsync(amax_bits, 0, 2 * sizeof(uint32_t), st));
+  const int64_t work = rht_n ? (rows / 16) * ceil_div(cols, 64) / 8 + 1
+                             : rows * cols / (16 / esz) / 256 + 1;
+  int64_t blocks = work;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  const bool bf = in_dtype == ALTOB200_DT_BF16;
+  if (rht_n) {
+    if (bf) amax_kernel<true, true><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else amax_kernel<false, true><<<(unsigned)blocks, 256, 0, st>>>(a);
+  } else {
+    if (bf) amax_kernel<true, false><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else amax_kernel<false, false><<<(unsigned)blocks, 256, 0, st>>>(a);
+  }
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+int altob200_dequantize(const void* codes, const void* scale_plain, const float* outer_scale,
+                        int32_t format, int32_t is_2d, int64_t rows, int64_t cols,
+                        int32_t out_dtype, void* out, int64_t ld_out, void* stream) {
+  if (codes == nullptr || scale_plain == nullptr || out == nullptr) return ALTOB200_EINVAL_SHAPE;
+  const int B = block_of(format);
+  if (rows <= 0 || cols <= 0 || cols % B != 0 || ld_out < cols) return ALTOB200_EINVAL_SHAPE;
+  if (is_2d && rows % B != 0) return ALTOB200_EINVAL_SHAPE;
+  const int esz = out_dtype == ALTOB200_DT_BF16 ? 2 : 4;
+  if (!aligned16(codes) || !aligned16(out) || (ld_out * esz) % 16 != 0) return ALTOB200_EINVAL_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  DequantArgs a;
+  a.codes = (const uint8_t*)codes; a.scales = scale_plain; a.outer = outer_scale;
+  a.rows = rows; a.cols = cols; a.ld_out = ld_out; a.out = out; a.is_2d = is_2d;
+  int64_t blocks = ceil_div(rows * (cols / 16), 256);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  const bool bf = out_dtype == ALTOB200_DT_BF16;
+#define LAUNCH_DQ(F)                                                              \
+  if (bf) dequantize_kernel<F, true><<<(unsigned)blocks, 256, 0, st>>>(a);        \
+  else dequantize_kernel<F, false><<<(unsigned)blocks, 256, 0, st>>>(a);          \
+  break;
+  switch (format) {
+    case ALTOB200_FMT_NVFP4: LAUNCH_DQ(ALTOB200_FMT_NVFP4)
+    case ALTOB200_FMT_MXFP4: LAUNCH_DQ(ALTOB200_FMT_MXFP4)
+    case ALTOB200_FMT_MXFP8_E4M3: LAUNCH_DQ(ALTOB200_FMT_MXFP8_E4M3)
+    case ALTOB200_FMT_MXFP8_E5M2: LAUNCH_DQ(ALTOB200_FMT_MXFP8_E5M2)
+    default: return ALTOB200_EUNSUPPORTED;
+  }
+#undef LAUNCH_DQ
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+int altob200_rht(const void* x, int32_t dtype, int64_t rows, int64_t cols, int64_t ld,
+                 int32_t rht_n, const int32_t* rht_perm, const int32_t* rht_sign, void* y,
+                 int64_t ld_y, void* stream) {
+  if (x == nullptr || y == nullptr) return ALTOB200_EINVAL_SHAPE;
+  if (rht_n != 16) return ALTOB200_EUNSUPPORTED;
+  if (rows <= 0 || cols <= 0 || rows % 16 != 0 || cols % 8 != 0 || ld < cols || ld_y < cols)
+    return ALTOB200_EINVAL_SHAPE;
+  const int esz = dtype == ALTOB200_DT_BF16 ? 2 : 4;
+  if (!aligned16(x) || !aligned16(y) || (ld * esz) % 16 != 0 || (ld_y * esz) % 16 != 0)
+    return ALTOB200_EINVAL_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  RhtArgs a;
+  a.x = x; a.y = y; a.rows = rows; a.cols = cols; a.ld = ld; a.ld_y = ld_y;
+  int rc = fill_rht(&a.rht, rht_n, rht_perm, rht_sign);
+  if (rc != ALTOB200_OK) return rc;
+  int64_t blocks = (rows / 16) * ceil_div(cols, 64) / 8 + 1;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (dtype == ALTOB200_DT_BF16) rht_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(a);
+  else rht_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,220 @@
+/*
+ * altob200 -- C ABI of the B200 (sm_100a) low-precision linear path.
+ *
+ * The reference (AMD-AGI/ALTO) has no FFI for this path: its seam is a set of
+ * Python callables backed by Triton kernels.  Each entry point below names the
+ * reference callable whose device work it replaces (path inside the reference
+ * project : line).  All pointers are DEVICE pointers unless stated otherwise,
+ * all sizes are in elements unless stated otherwise, `stream` is a
+ * cudaStream_t passed as void*, and every function returns 0 on success or a
+ * negative ALTOB200_E* code.  Nothing here allocates device memory unless the
+ * comment of the function says so; outputs are owned by the caller.
+ *
+ * Quantised data layouts
+ * ----------------------
+ *  codes (FP4)  : uint8, two E2M1 codes per byte, the element with the even
+ *                 index along the quantisation axis in the low nibble
+ *                 (alto/kernels/fp4/mxfp4/mxfp_quantization.py:184-186).
+ *  codes (FP8)  : one byte per element (float8_e4m3fn or float8_e5m2).
+ *  plain scales : row-major [rows, cols/block] (1D) or [rows/block, cols/block]
+ *                 (2D); MXFP4/MXFP8: uint8 E8M0 exponent, NVFP4: float32 value
+ *                 on the E4M3 grid (alto/kernels/fp4/nvfp4/nvfp_quantization.py:558).
+ *  packed scales: the layout the tcgen05 block-scaled MMA reads from tensor
+ *                 memory: uint8 (E8M0 or E4M3), tiles of 128 rows x 4 scale
+ *                 columns = 512 bytes, tile (rb, cb) at ((rb * ceil(ncols/4)) + cb) * 512,
+ *                 element (r, c) of a tile at (r % 32) * 16 + (r / 32) * 4 + c.
+ *                 Rows and columns are padded to multiples of 128 and 4; padded
+ *                 entries are written as zero.  Size: altob200_packed_scale_bytes().
+ */
+#ifndef ALTOB200_H_
+#define ALTOB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+#define ALTOB200_OK 0
+#define ALTOB200_EINVAL_SHAPE (-1)   /* a size/divisibility contract is violated      */
+#define ALTOB200_EINVAL_ALIGN (-2)   /* a pointer or leading dimension is misaligned  */
+#define ALTOB200_ETIMEOUT_DEVICE (-3) /* a bounded device-side wait gave up           */
+#define ALTOB200_ECUDA (-4)          /* a CUDA runtime/driver call failed             */
+#define ALTOB200_EUNSUPPORTED (-5)   /* valid request this build does not implement   */
+#define ALTOB200_ELIMIT (-6)         /* a size exceeds a stated fixed maximum         */
+
+/* ---- enums (plain ints in the ABI) ------------------------------------- */
+/* element formats */
+#define ALTOB200_FMT_NVFP4 0      /* E2M1, block 16, E4M3 inner scale (+fp32 outer) */
+#define ALTOB200_FMT_MXFP4 1      /* E2M1, block 32, E8M0 scale                     */
+#define ALTOB200_FMT_MXFP8_E4M3 2 /* E4M3, block 32, E8M0 scale                     */
+#define ALTOB200_FMT_MXFP8_E5M2 3 /* E5M2, block 32, E8M0 scale                     */
+/* high-precision dtypes */
+#define ALTOB200_DT_BF16 0
+#define ALTOB200_DT_F32 1
+/* scale output layouts */
+#define ALTOB200_SCALE_PLAIN 1
+#define ALTOB200_SCALE_PACKED 2
+/* rounding */
+#define ALTOB200_ROUND_RTN 0
+#define ALTOB200_ROUND_SR_BITS 1   /* stochastic rounding, caller supplies 32 random bits per element */
+#define ALTOB200_ROUND_SR_PHILOX 2 /* stochastic rounding, Philox-4x32-10 generated in the kernel     */
+
+int altob200_version(void);
+const char* altob200_status_string(int status);
+
+/* Bytes of a packed scale buffer for `rows` x `ncols` scale entries. */
+size_t altob200_packed_scale_bytes(int64_t rows, int64_t ncols);
+
+/* Reads (and clears) the sticky device-side status word written by kernels
+ * whose bounded waits gave up.  Synchronises `stream`.  Returns 0 or
+ * ALTOB200_ETIMEOUT_DEVICE; `detail` (host, may be NULL) receives
+ * {kernel id, block id, wait site, 0}. */
+int altob200_status_read(void* stream, int32_t detail[4]);
+
+/* ---- quantizer parameters ---------------------------------------------- */
+typedef struct altob200_quant_params {
+  int32_t format;      /* ALTOB200_FMT_*                                             */
+  int32_t in_dtype;    /* ALTOB200_DT_*                                              */
+  int32_t rounding;    /* ALTOB200_ROUND_*                                           */
+  int32_t scale_flags; /* ALTOB200_SCALE_PLAIN | ALTOB200_SCALE_PACKED               */
+  /* NVFP4 tensorwise outer scale (device float[1]) or NULL when outer scaling is off
+   * (alto/kernels/fp4/nvfp4/nvfp_quantization.py:273-287).                         */
+  const float* outer_scale;
+  /* ROUND_SR_BITS: device uint32 [2][rows_q][cols_q/2] in the quantisation-axis-last
+   * view; plane 0 feeds even elements, plane 1 odd elements
+   * (alto/kernels/fp4/fp4_common/triton_fp4_ops.py:13-19,
+   *  alto/kernels/fp4/mxfp4/mxfp_quantization.py:128-132,184-186).                  */
+  const uint32_t* rand_bits;
+  uint64_t philox_seed;   /* ROUND_SR_PHILOX */
+  uint64_t philox_offset; /* ROUND_SR_PHILOX */
+  /* Randomised Hadamard transform applied along the row axis before an axis-0
+   * quantisation (alto/kernels/hadamard_transform/transform.py:115-142).  0 = off,
+   * else the block size n (16).  The n x n matrix is W = (diag(sign) H_n)[perm][:, perm]
+   * with H_n the Sylvester matrix; `rht_perm[i]` and `rht_sign[i]` (+1/-1) are HOST
+   * arrays of length n.                                                              */
+  int32_t rht_n;
+  const int32_t* rht_perm;
+  const int32_t* rht_sign;
+} altob200_quant_params;
+
+/*
+ * Absolute maximum of a [rows, cols] matrix with leading dimension `ld`
+ * (elements).  Replaces the three eager kernels of compute_dynamic_outer_scale
+ * (alto/kernels/fp4/nvfp4/nvfp_quantization.py:460-487).
+ *
+ *  amax_bits[0] <- max |x|            (fp32 bit pattern, NaN elements ignored)
+ *  amax_bits[1] <- max |bf16(W x/sqrt(n))| over row blocks of n when p->rht_n != 0
+ *  outer_scale[i] <- max(amax_i / (448 * 6), 1e-30) for i in {0,1} when non-NULL
+ *
+ * `scratch` is device memory of at least ALTOB200_AMAX_SCRATCH_BYTES that must be
+ * zero before the first call; the kernel leaves it zeroed again.
+ */
+#define ALTOB200_AMAX_SCRATCH_BYTES 16
+int altob200_amax(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, int64_t ld,
+                  int32_t rht_n, const int32_t* rht_perm, const int32_t* rht_sign,
+                  uint32_t* amax_bits, float* outer_scale, void* scratch, void* stream);
+
+/*
+ * 1D block quantisation along the last (contiguous) axis of x[rows, cols].
+ * Replaces convert_to_mxfp4 / convert_to_nvfp4 / convert_to_mxfp8 with axis=-1,
+ * is_2d_block=False (alto/kernels/fp4/mxfp4/mxfp_quantization.py:411-484,
+ * alto/kernels/fp4/nvfp4/nvfp_quantization.py:491-630,
+ * alto/kernels/mxfp8/mxfp8_quantization.py:483-586).
+ *   codes       : [rows, cols/2] (FP4) or [rows, cols] (FP8), row-major
+ *   scale_plain : [rows, cols/block] (uint8 or float32), may be NULL
+ *   scale_packed: packed layout with rows=rows, ncols=cols/block, may be NULL
+ */
+int altob200_quantize_rowwise(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                              const altob200_quant_params* p, void* codes, void* scale_plain,
+                              void* scale_packed, void* stream);
+
+/*
+ * 1D block quantisation along axis 0 (blocks of consecutive ROWS) of
+ * x[rows, cols], optionally preceded by the randomised Hadamard transform over
+ * row blocks of p->rht_n.  Replaces the axis=0 calls of the same reference
+ * functions, whose physical output is the transposed matrix
+ * (alto/kernels/fp4/mxfp4/mxfp_quantization.py:439-443,484):
+ *   codes       : [cols, rows/2] (FP4) or [cols, rows] (FP8), row-major
+ *   scale_plain : [cols, rows/block]
+ *   scale_packed: packed layout with rows=cols, ncols=rows/block
+ */
+int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                              const altob200_quant_params* p, void* codes, void* scale_plain,
+                              void* scale_packed, void* stream);
+
+/*
+ * 2D block quantisation (block x block tiles share one scale) of w[rows, cols].
+ * Replaces the is_2d_block=True calls (same reference functions).  2D scales do
+ * not depend on the axis, so one read of w produces both operand packings:
+ *   codes_k       : [rows, cols/2]  (packed along cols; forward operand)
+ *   codes_t       : [cols, rows/2]  (packed along rows; dgrad operand), may be NULL
+ *   scale_plain   : [rows/block, cols/block], may be NULL
+ *   scale_packed_k: packed layout rows=rows, ncols=cols/block (2D scale broadcast per row), may be NULL
+ *   scale_packed_t: packed layout rows=cols, ncols=rows/block, may be NULL
+ */
+int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
+                         const altob200_quant_params* p, void* codes_k, void* codes_t,
+                         void* scale_plain, void* scale_packed_k, void* scale_packed_t,
+                         void* stream);
+
+/*
+ * Dequantisation of row-major codes[rows, cols(/2)] with plain scales.
+ * Replaces convert_from_mxfp4 / convert_from_nvfp4 / convert_from_mxfp8
+ * (alto/kernels/fp4/mxfp4/mxfp_quantization.py:488-545,
+ *  alto/kernels/fp4/nvfp4/nvfp_quantization.py:634-711,
+ *  alto/kernels/mxfp8/mxfp8_quantization.py:590-663) for the axis-last view;
+ * `is_2d` selects [rows/block, cols/block] scales.
+ */
+int altob200_dequantize(const void* codes, const void* scale_plain, const float* outer_scale,
+                        int32_t format, int32_t is_2d, int64_t rows, int64_t cols,
+                        int32_t out_dtype, void* out, int64_t ld_out, void* stream);
+
+/*
+ * Randomised Hadamard transform alone: y = bf16/f32( (W x_block) / sqrt(n) ) over
+ * row blocks of n (alto/kernels/hadamard_transform/transform.py:115-142, left_mul=True).
+ */
+int altob200_rht(const void* x, int32_t dtype, int64_t rows, int64_t cols, int64_t ld,
+                 int32_t rht_n, const int32_t* rht_perm, const int32_t* rht_sign, void* y,
+                 int64_t ld_y, void* stream);
+
+/*
+ * Block-scaled GEMM on tcgen05:  D[m, n] = alpha * sum_k A[m, k] * B[n, k]
+ * with A and B both stored reduction-axis-contiguous ("NT"), packed scales, fp32
+ * accumulation in tensor memory.  Replaces blockwise_mxfp4_gemm
+ * (alto/kernels/fp4/mxfp4/mxfp_linear.py:143-255), blockwise_mxfp8_gemm
+ * (alto/kernels/mxfp8/mxfp8_linear.py:153-296) and the dequantise + bf16 matmul of
+ * the NVFP4 path (alto/kernels/fp4/nvfp4/nvfp_linear.py:90,247-248).
+ *   a_codes [M, K/2 or K], a_scales packed(rows=M, ncols=K/block)
+ *   b_codes [N, K/2 or K], b_scales packed(rows=N, ncols=K/block)
+ *   alpha   : device float pointers multiplied together (either may be NULL = 1.0);
+ *             NVFP4 passes the two tensorwise outer scales.
+ *   d       : [M, N] row-major, out_dtype bf16 or f32, leading dimension ldd.
+ * K must be a multiple of the format block; M, N arbitrary (multiples of 8).
+ */
+int altob200_gemm_blockscaled(int32_t format_a, int32_t format_b, int64_t M, int64_t N, int64_t K,
+                              const void* a_codes, const void* a_scales, const void* b_codes,
+                              const void* b_scales, const float* alpha_a, const float* alpha_b,
+                              int32_t out_dtype, void* d, int64_t ldd, void* stream);
+
+/*
+ * Grouped (MoE) variant: rows of A are grouped in runs of 128 that share one
+ * expert; `group_expert[g]` (device int32, length M/128, -1 = padding rows that
+ * produce zeros) selects B[e] of shape [N, K].  Replaces
+ * mxfp4_grouped_gemm_forward / backward_inputs
+ * (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_forward.py:201,
+ *  alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_backward.py:399).
+ */
+int altob200_grouped_gemm_blockscaled(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
+                                      int64_t K, int32_t num_experts, const void* a_codes,
+                                      const void* a_scales, const void* b_codes,
+                                      const void* b_scales, const int32_t* group_expert,
+                                      const float* alpha_a, const float* alpha_b,
+                                      int32_t out_dtype, void* d, int64_t ldd, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALTOB200_H_ */
