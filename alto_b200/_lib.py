@@ -174,7 +174,7 @@ class Rht:
         self._sign_c = _i32_array(self.sign)
 
 
-def _params(fmt, x, rounding, outer_scale, rand_bits, rht: Optional[Rht], flags) -> QuantParams:
+def _params(fmt, x, rounding, outer_scale, rand_bits, rht: Optional[Rht], flags, philox=(0, 0)) -> QuantParams:
     p = QuantParams()
     p.format = fmt
     p.in_dtype = _dt(x.dtype)
@@ -182,8 +182,8 @@ def _params(fmt, x, rounding, outer_scale, rand_bits, rht: Optional[Rht], flags)
     p.scale_flags = flags
     p.outer_scale = _ptr(outer_scale)
     p.rand_bits = _ptr(rand_bits)
-    p.philox_seed = 0
-    p.philox_offset = 0
+    p.philox_seed = int(philox[0]) & 0xFFFFFFFFFFFFFFFF
+    p.philox_offset = int(philox[1]) & 0xFFFFFFFFFFFFFFFF
     if rht is not None:
         p.rht_n = rht.n
         p.rht_perm = rht._perm_c
@@ -213,22 +213,22 @@ def amax(x: torch.Tensor, amax_bits: torch.Tensor, outer_scale: Optional[torch.T
 
 
 def quantize_rowwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, rounding=ROUND_RTN,
-                     outer_scale=None, rand_bits=None) -> None:
+                     outer_scale=None, rand_bits=None, philox=(0, 0)) -> None:
     _require_cuda(x, codes, scale_plain, scale_packed, outer_scale, rand_bits)
     assert x.dim() == 2 and x.stride(1) == 1
     flags = (SCALE_PLAIN if scale_plain is not None else 0) | (SCALE_PACKED if scale_packed is not None else 0)
-    p = _params(fmt, x, rounding, outer_scale, rand_bits, None, flags)
+    p = _params(fmt, x, rounding, outer_scale, rand_bits, None, flags, philox)
     _check(lib().altob200_quantize_rowwise(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), C.byref(p),
                                            codes.data_ptr(), _ptr(scale_plain), _ptr(scale_packed), _stream()),
            "altob200_quantize_rowwise")
 
 
 def quantize_colwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, rounding=ROUND_RTN,
-                     outer_scale=None, rand_bits=None, rht: Optional[Rht] = None) -> None:
+                     outer_scale=None, rand_bits=None, rht: Optional[Rht] = None, philox=(0, 0)) -> None:
     _require_cuda(x, codes, scale_plain, scale_packed, outer_scale, rand_bits)
     assert x.dim() == 2 and x.stride(1) == 1
     flags = (SCALE_PLAIN if scale_plain is not None else 0) | (SCALE_PACKED if scale_packed is not None else 0)
-    p = _params(fmt, x, rounding, outer_scale, rand_bits, rht, flags)
+    p = _params(fmt, x, rounding, outer_scale, rand_bits, rht, flags, philox)
     _check(lib().altob200_quantize_colwise(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), C.byref(p),
                                            codes.data_ptr(), _ptr(scale_plain), _ptr(scale_packed), _stream()),
            "altob200_quantize_colwise")

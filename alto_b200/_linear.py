@@ -1,0 +1,258 @@
+"""Format-independent engine of the low-precision linear: operand preparation (one fused
+quantize launch per operand use) and the three block-scaled GEMMs.
+
+All three reference autograd functions share this structure
+(alto/kernels/fp4/nvfp4/nvfp_linear.py:53-278, alto/kernels/fp4/mxfp4/mxfp_linear.py:266-570,
+alto/kernels/mxfp8/mxfp8_linear.py:305-439):
+
+  forward : X along K, W along K                      -> Y  = Xq Wq^T
+            saves X along M (after the optional Hadamard rotation) and W along N
+  backward: dY along N                                -> dX = dYq Wq       (reduction over N)
+            (H) dY along M                            -> dW = dYq^T Xq     (reduction over M)
+
+Every GEMM operand is stored with its reduction axis contiguous and carries its scales in
+the packed layout the tensor cores read, so the quantizers write exactly what the GEMM
+consumes and nothing is dequantised.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+# ---------------------------------------------------------------------------------------
+# scratch and random-bit plumbing
+# ---------------------------------------------------------------------------------------
+_scratch = {}
+
+
+def amax_scratch(device: torch.device) -> torch.Tensor:
+    """Zeroed per-(device, stream) scratch of the amax kernel (the kernel leaves it zeroed)."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _scratch.get(key)
+    if buf is None:
+        buf = torch.zeros(L.AMAX_SCRATCH_BYTES // 4, dtype=torch.int32, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+_sr_bits_provider: Optional[Callable[[str, Tuple[int, ...], torch.device], torch.Tensor]] = None
+
+
+@contextlib.contextmanager
+def explicit_sr_bits(provider: Callable[[str, Tuple[int, ...], torch.device], torch.Tensor]):
+    """Within the context, stochastic rounding inside the linear functions consumes the random
+    words returned by ``provider(name, shape, device)`` (int32 tensor of ``shape`` =
+    [2, rows, cols/2] in the quantisation-axis-last view; names: "dy_n", "dy_m") instead of
+    generating Philox words in the kernel.  Used to check bit parity against the oracle."""
+    global _sr_bits_provider
+    prev = _sr_bits_provider
+    _sr_bits_provider = provider
+    try:
+        yield
+    finally:
+        _sr_bits_provider = prev
+
+
+def draw_philox() -> Tuple[int, int]:
+    """Seed and offset from the global CPU generator, as the reference draws them when none is
+    given (alto/kernels/fp4/nvfp4/nvfp_quantization.py:587-590)."""
+    v = torch.randint(0, 2 ** 31 - 1, (2,))
+    return int(v[0]), int(v[1])
+
+
+def sr_args(use_sr: bool, name: str, rows: int, cols: int, device) -> dict:
+    if not use_sr:
+        return dict(rounding=L.ROUND_RTN)
+    if _sr_bits_provider is not None:
+        bits = _sr_bits_provider(name, (2, rows, cols // 2), device)
+        return dict(rounding=L.ROUND_SR_BITS, rand_bits=bits.contiguous())
+    return dict(rounding=L.ROUND_SR_PHILOX, philox=draw_philox())
+
+
+RTN = dict(rounding=L.ROUND_RTN)
+
+# ---------------------------------------------------------------------------------------
+# operands
+# ---------------------------------------------------------------------------------------
+
+
+class Operand:
+    """Codes + packed scales (+ NVFP4 outer scale) of one GEMM operand [rows, k], k contiguous."""
+
+    __slots__ = ("codes", "scales", "outer", "rows", "k", "fmt")
+
+    def __init__(self, codes, scales, outer, rows, k, fmt):
+        self.codes, self.scales, self.outer, self.rows, self.k, self.fmt = codes, scales, outer, rows, k, fmt
+
+
+def as_2d_rows(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16 != 0 or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    return x2
+
+
+def outer_scales(x2: torch.Tensor, use_outer: bool, rht: Optional[L.Rht]) -> Optional[torch.Tensor]:
+    """[outer(x), outer(H x)] from ONE read of x, or None when outer scaling is off."""
+    if not use_outer:
+        return None
+    amax_bits = torch.empty(2, dtype=torch.int32, device=x2.device)
+    outer = torch.empty(2, dtype=torch.float32, device=x2.device)
+    L.amax(x2, amax_bits, outer, amax_scratch(x2.device), rht)
+    return outer
+
+
+def _packed(rows: int, ncols: int, device) -> torch.Tensor:
+    return torch.empty(L.packed_scale_bytes(rows, ncols), dtype=torch.uint8, device=device)
+
+
+def _code_cols(fmt: int, n: int) -> int:
+    return n // 2 if L.is_fp4(fmt) else n
+
+
+def quant_rows(x2, fmt, outer, sr: dict) -> Operand:
+    R, Cc = x2.shape
+    codes = torch.empty(R, _code_cols(fmt, Cc), dtype=torch.uint8, device=x2.device)
+    sf = _packed(R, Cc // L.block_of(fmt), x2.device)
+    L.quantize_rowwise(x2, fmt, codes, None, sf, outer_scale=outer, **sr)
+    return Operand(codes, sf, outer, R, Cc, fmt)
+
+
+def quant_cols(x2, fmt, outer, rht, sr: dict) -> Operand:
+    R, Cc = x2.shape
+    codes = torch.empty(Cc, _code_cols(fmt, R), dtype=torch.uint8, device=x2.device)
+    sf = _packed(Cc, R // L.block_of(fmt), x2.device)
+    L.quantize_colwise(x2, fmt, codes, None, sf, outer_scale=outer, rht=rht, **sr)
+    return Operand(codes, sf, outer, Cc, R, fmt)
+
+
+def quant_2d(x2, fmt, outer, want_t: bool) -> Tuple[Operand, Optional[Operand]]:
+    R, Cc = x2.shape
+    b = L.block_of(fmt)
+    ck = torch.empty(R, _code_cols(fmt, Cc), dtype=torch.uint8, device=x2.device)
+    sk = _packed(R, Cc // b, x2.device)
+    ct = torch.empty(Cc, _code_cols(fmt, R), dtype=torch.uint8, device=x2.device) if want_t else None
+    stt = _packed(Cc, R // b, x2.device) if want_t else None
+    L.quantize_2d(x2, fmt, ck, ct, None, sk, stt, outer_scale=outer)
+    return Operand(ck, sk, outer, R, Cc, fmt), (Operand(ct, stt, outer, Cc, R, fmt) if want_t else None)
+
+
+def gemm(a: Operand, b: Operand, out_dtype: torch.dtype) -> torch.Tensor:
+    """D[a.rows, b.rows] = alpha * A B^T, alpha = product of the operands' outer scales."""
+    assert a.k == b.k
+    out = torch.empty(a.rows, b.rows, dtype=out_dtype, device=a.codes.device)
+    L.gemm_blockscaled(a.fmt, b.fmt, a.rows, b.rows, a.k, a.codes, a.scales, b.codes, b.scales, out, a.outer,
+                       b.outer)
+    return out
+
+
+def check_dims(name: str, M: int, K: int, N: int) -> None:
+    torch._check(K % 32 == 0, lambda: f"{name} on B200 requires in_features ({K}) divisible by 32")
+    torch._check(N % 32 == 0, lambda: f"{name} on B200 requires out_features ({N}) divisible by 32")
+    torch._check(M % 32 == 0, lambda: (
+        f"{name} on B200 requires the token count ({M}) divisible by 32: the wgrad operands are quantised "
+        "in blocks along the token axis and stored in 16-byte aligned rows"))
+
+
+def forward_operands(x2, w2, fmt, *, use_2dblock_x, use_2dblock_w, use_outer_scale, rht):
+    """Returns (x_k, x_m, w_k, w_t): X along K (fprop), X along M after the optional Hadamard
+    rotation (wgrad), W along K (fprop), W along N (dgrad)."""
+    ox = outer_scales(x2, use_outer_scale, None if use_2dblock_x else rht)
+    ow = outer_scales(w2, use_outer_scale, None)
+    if use_2dblock_x:
+        x_k, x_m = quant_2d(x2, fmt, None if ox is None else ox[0:1], True)
+    else:
+        x_k = quant_rows(x2, fmt, None if ox is None else ox[0:1], RTN)
+        o_m = None if ox is None else (ox[1:2] if rht is not None else ox[0:1])
+        x_m = quant_cols(x2, fmt, o_m, rht, RTN)
+    if use_2dblock_w:
+        w_k, w_t = quant_2d(w2, fmt, None if ow is None else ow[0:1], True)
+    else:
+        w_k = quant_rows(w2, fmt, None if ow is None else ow[0:1], RTN)
+        w_t = quant_cols(w2, fmt, None if ow is None else ow[0:1], None, RTN)
+    return x_k, x_m, w_k, w_t
+
+
+def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, rht):
+    """dY along N for dgrad and (after the optional Hadamard rotation) along M for wgrad."""
+    M, N = g2.shape
+    og = outer_scales(g2, use_outer_scale, None if use_2dblock_x else rht)
+    if use_2dblock_x:
+        if use_sr_grad:
+            raise NotImplementedError("stochastic rounding with use_2dblock_x=True is not implemented")
+        return quant_2d(g2, fmt, None if og is None else og[0:1], True)
+    g_n = quant_rows(g2, fmt, None if og is None else og[0:1], sr_args(use_sr_grad, "dy_n", M, N, g2.device))
+    o_m = None if og is None else (og[1:2] if rht is not None else og[0:1])
+    g_m = quant_cols(g2, fmt, o_m, rht, sr_args(use_sr_grad, "dy_m", N, M, g2.device))
+    return g_n, g_m
+
+
+def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock_w, use_sr_grad, use_outer_scale,
+                   hadamard_transform):
+    """Shared body of the three autograd ``forward`` methods."""
+    if not x.is_cuda:
+        raise RuntimeError(f"{name} runs on CUDA tensors only (no CPU fallback)")
+    original_shape = x.shape
+    x2 = as_2d_rows(x.detach())
+    w2 = as_2d_rows(weight.detach())
+    M, K = x2.shape
+    N = w2.shape[0]
+    check_dims(name, M, K, N)
+    rht = hadamard_transform.device_params() if (hadamard_transform is not None and not use_2dblock_x) else None
+    x_k, x_m, w_k, w_t = forward_operands(x2, w2, fmt, use_2dblock_x=use_2dblock_x, use_2dblock_w=use_2dblock_w,
+                                          use_outer_scale=use_outer_scale, rht=rht)
+    y = gemm(x_k, w_k, x.dtype)
+    extra_x = [x_m.outer] if x_m.outer is not None else []
+    extra_w = [w_t.outer] if w_t.outer is not None else []
+    ctx.save_for_backward(x_m.codes, x_m.scales, *extra_x, w_t.codes, w_t.scales, *extra_w)
+    ctx.dims = (M, K, N)
+    ctx.fmt = fmt
+    ctx.use_2dblock_x = use_2dblock_x
+    ctx.use_sr_grad = use_sr_grad
+    ctx.use_outer_scale = use_outer_scale
+    ctx.rht = rht
+    return y.view(*original_shape[:-1], N)
+
+
+def linear_backward(ctx, grad_output):
+    """Shared body of the three autograd ``backward`` methods; returns (dX, dW)."""
+    M, K, N = ctx.dims
+    saved = ctx.saved_tensors
+    if ctx.use_outer_scale:
+        xc, xs, xo, wc, ws, wo = saved
+    else:
+        (xc, xs, wc, ws), xo, wo = saved, None, None
+    x_m = Operand(xc, xs, xo, K, M, ctx.fmt)
+    w_t = Operand(wc, ws, wo, K, N, ctx.fmt)
+    original_shape = grad_output.shape
+    g2 = as_2d_rows(grad_output)
+    g_n, g_m = backward_operands(g2, ctx.fmt, use_2dblock_x=ctx.use_2dblock_x, use_sr_grad=ctx.use_sr_grad,
+                                 use_outer_scale=ctx.use_outer_scale, rht=ctx.rht)
+    grad_inputs = grad_weights = None
+    if ctx.needs_input_grad[0]:
+        grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
+    if ctx.needs_input_grad[1]:
+        grad_weights = gemm(g_m, x_m, grad_output.dtype)
+    return grad_inputs, grad_weights
+
+
+def pack_plain_scales(scales: torch.Tensor, rows: int, is_2d: bool, block: int) -> torch.Tensor:
+    """Plain scales ([rows, K/block], or [rows/block, K/block] when ``is_2d``; uint8 exponents or
+    fp32 values on the E4M3 grid) -> the packed layout of the GEMM.  Pure data movement on a
+    tensor that is 1/16 or 1/32 of the operand; done with tensor ops."""
+    s = scales
+    if s.dtype == torch.float32:
+        s = s.to(torch.float8_e4m3fn).view(torch.uint8)
+    assert s.dtype == torch.uint8
+    if is_2d:
+        s = s.repeat_interleave(block, dim=0)
+    assert s.shape[0] == rows, f"scale rows {s.shape[0]} != operand rows {rows}"
+    ncols = s.shape[1]
+    rt, ct = (rows + 127) // 128, (ncols + 3) // 4
+    buf = torch.zeros(rt * 128, ct * 4, dtype=torch.uint8, device=s.device)
+    buf[:rows, :ncols] = s
+    return buf.view(rt, 4, 32, ct, 4).permute(0, 3, 2, 1, 4).contiguous().view(-1)

@@ -113,6 +113,7 @@ struct RowwiseArgs {
   int64_t ncol_tiles;  // ceil(cols / B / 4)
   const float* outer;
   const uint32_t* rand_bits;
+  uint64_t philox_seed, philox_offset;
 };
 
 template <int FMT, bool IN_BF16, int ROUND>
@@ -188,6 +189,17 @@ __global__ void __launch_bounds__(256) quantize_rowwise_kernel(RowwiseArgs a) {
         r0[4] = a1.x; r0[5] = a1.y; r0[6] = a1.z; r0[7] = a1.w;
         r1[0] = b0.x; r1[1] = b0.y; r1[2] = b0.z; r1[3] = b0.w;
         r1[4] = b1.x; r1[5] = b1.y; r1[6] = b1.z; r1[7] = b1.w;
+      }
+    } else if (ROUND == ALTOB200_ROUND_SR_PHILOX) {
+      // one Philox call feeds two element pairs: call index = pair index / 2
+      const uint64_t q0 = a.philox_offset + (uint64_t)((row * half_cols + (col >> 1)) >> 1);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t o[4];
+        const uint64_t ctr = q0 + i;
+        philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u, (uint32_t)a.philox_seed,
+                      (uint32_t)(a.philox_seed >> 32), o);
+        r0[2 * i] = o[0]; r1[2 * i] = o[1]; r0[2 * i + 1] = o[2]; r1[2 * i + 1] = o[3];
       }
     }
 
@@ -268,6 +280,7 @@ struct ColwiseArgs {
   int64_t ncol_tiles;   // ceil(rows / B / 4)
   const float* outer;
   const uint32_t* rand_bits;  // [2][cols][rows/2]
+  uint64_t philox_seed, philox_offset;
   RhtParams rht;
 };
 
@@ -286,6 +299,7 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
   __shared__ __align__(16) uint8_t s_codes[COL_TN * ROW_BYTES];
   __shared__ __align__(16) uint8_t s_sf[COL_TN * NBLK];
   __shared__ float s_sf_plain[Fmt<FMT>::MX ? 1 : COL_TN * NBLK];
+  __shared__ float s_perm[(RHT && ROUND != ALTOB200_ROUND_RTN) ? 16 : 1][2][256];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t m0 = (int64_t)blockIdx.y * COL_TM;
@@ -332,9 +346,10 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
       }
 #pragma unroll
       for (int k = 0; k < B; ++k) {
-        const float sg = 0.25f * a.rht.sign[k & 15];  // +-1/sqrt(16), exact
-        v0[k] = __fmul_rn(v0[k], sg);
-        v1[k] = __fmul_rn(v1[k], sg);
+        // +-1/sqrt(16) is exact; adding +0 turns a -0 product into the +0 a dot product yields
+        const float sg = 0.25f * a.rht.sign[k & 15];
+        v0[k] = __fadd_rn(__fmul_rn(v0[k], sg), 0.0f);
+        v1[k] = __fadd_rn(__fmul_rn(v1[k], sg), 0.0f);
         if (IN_BF16) {
           v0[k] = u2f(f32_to_bf16_bits(v0[k]) << 16);
           v1[k] = u2f(f32_to_bf16_bits(v1[k]) << 16);
@@ -360,12 +375,62 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
     if (F::FP4) {
 #pragma unroll
       for (int h = 0; h < B / 16; ++h) {
-        uint64_t w0 = 0, w1 = 0;  // nibble j = code of slot 16h + j
+        // With stochastic rounding the random word belongs to the OUTPUT position, so the
+        // transformed values are first moved from slot order to position order through a
+        // private shared-memory column (static register index, dynamic address).
+        constexpr bool TO_POS = RHT && ROUND != ALTOB200_ROUND_RTN;
+        float y0[16], y1[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int k = 16 * h + j;
-          const float q0 = scale_elem<FMT, IN_BF16>(v0[k], s0);
-          const float q1 = scale_elem<FMT, IN_BF16>(v1[k], s1);
+          y0[j] = v0[16 * h + j];
+          y1[j] = v1[16 * h + j];
+        }
+        if (TO_POS) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            s_perm[a.rht.pinv[j]][0][threadIdx.x] = y0[j];
+            s_perm[a.rht.pinv[j]][1][threadIdx.x] = y1[j];
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            y0[j] = s_perm[j][0][threadIdx.x];
+            y1[j] = s_perm[j][1][threadIdx.x];
+          }
+        }
+        // random words by position: r0[i]/r1[i] for column c / c+1
+        uint32_t r0[16], r1[16];
+        if (ROUND == ALTOB200_ROUND_SR_BITS) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            r0[i] = r1[i] = 0;
+            if (ok) {
+              const int64_t plane = (int64_t)(i & 1) * a.cols * half_rows;
+              const int64_t idx = (mb + 16 * h + i) >> 1;
+              r0[i] = __ldg(a.rand_bits + plane + c * half_rows + idx);
+              r1[i] = __ldg(a.rand_bits + plane + (c + 1) * half_rows + idx);
+            }
+          }
+        } else if (ROUND == ALTOB200_ROUND_SR_PHILOX) {
+          const uint64_t p0 = (uint64_t)(c * half_rows + ((mb + 16 * h) >> 1));        // pair index, column c
+          const uint64_t p1 = (uint64_t)((c + 1) * half_rows + ((mb + 16 * h) >> 1));  // column c + 1
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t o[4];
+            uint64_t ctr = a.philox_offset + (p0 >> 1) + i;
+            philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u, (uint32_t)a.philox_seed,
+                          (uint32_t)(a.philox_seed >> 32), o);
+            r0[4 * i] = o[0]; r0[4 * i + 1] = o[1]; r0[4 * i + 2] = o[2]; r0[4 * i + 3] = o[3];
+            ctr = a.philox_offset + (p1 >> 1) + i;
+            philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u, (uint32_t)a.philox_seed,
+                          (uint32_t)(a.philox_seed >> 32), o);
+            r1[4 * i] = o[0]; r1[4 * i + 1] = o[1]; r1[4 * i + 2] = o[2]; r1[4 * i + 3] = o[3];
+          }
+        }
+        uint64_t w0 = 0, w1 = 0;  // nibble j = code of entry j (slot order, or position order if TO_POS)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float q0 = scale_elem<FMT, IN_BF16>(y0[j], s0);
+          const float q1 = scale_elem<FMT, IN_BF16>(y1[j], s1);
           uint32_t c0, c1;
           if (ROUND == ALTOB200_ROUND_RTN) {
             // the hardware converter takes one value of each column per call
@@ -373,23 +438,14 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
             c0 = b & 0xFu;
             c1 = b >> 4;
           } else {
-            // the output position of a slot decides which random word it consumes
-            const int pos = RHT ? (16 * h + a.rht.pinv[j]) : k;
-            uint32_t rr0 = 0, rr1 = 0;
-            if (ok) {
-              const int64_t plane = (int64_t)(pos & 1) * a.cols * half_rows;
-              const int64_t idx = (mb + pos) >> 1;
-              rr0 = __ldg(a.rand_bits + plane + c * half_rows + idx);
-              rr1 = __ldg(a.rand_bits + plane + (c + 1) * half_rows + idx);
-            }
-            c0 = e2m1_sr_bits(q0, rr0);
-            c1 = e2m1_sr_bits(q1, rr1);
+            c0 = e2m1_sr_bits(q0, r0[j]);
+            c1 = e2m1_sr_bits(q1, r1[j]);
           }
           w0 |= (uint64_t)c0 << (4 * j);
           w1 |= (uint64_t)c1 << (4 * j);
         }
         uint64_t o0 = w0, o1 = w1;
-        if (RHT) {  // output position i takes slot perm[i]
+        if (RHT && !TO_POS) {  // output position i takes slot perm[i]
           o0 = o1 = 0;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -913,7 +969,7 @@ __global__ void __launch_bounds__(256) rht_kernel(RhtArgs a) {
       // slot k is output row pinv[k] of the group (y[i] = sign[perm[i]] * u[perm[i]])
       const int64_t orow = (g << 4) + a.rht.pinv[k];
       const float sg = 0.25f * a.rht.sign[k];
-      const float y0 = __fmul_rn(v0[k], sg), y1 = __fmul_rn(v1[k], sg);
+      const float y0 = __fadd_rn(__fmul_rn(v0[k], sg), 0.0f), y1 = __fadd_rn(__fmul_rn(v1[k], sg), 0.0f);
       if (IN_BF16) {
         *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(a.y) + orow * a.ld_y + c) =
             f32_to_bf16_bits(y0) | (f32_to_bf16_bits(y1) << 16);
@@ -974,6 +1030,9 @@ static int launch_rowwise(const RowwiseArgs& a, int rounding, cudaStream_t st) {
   else if (rounding == ALTOB200_ROUND_SR_BITS && Fmt<FMT>::FP4)
     quantize_rowwise_kernel<FMT, IN_BF16, Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN>
         <<<(unsigned)blocks, 256, 0, st>>>(a);
+  else if (rounding == ALTOB200_ROUND_SR_PHILOX && Fmt<FMT>::FP4)
+    quantize_rowwise_kernel<FMT, IN_BF16, Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_PHILOX : ALTOB200_ROUND_RTN>
+        <<<(unsigned)blocks, 256, 0, st>>>(a);
   else
     return ALTOB200_EUNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
@@ -989,6 +1048,10 @@ static int launch_colwise(const ColwiseArgs& a, int rounding, cudaStream_t st) {
     else quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, false><<<grid, 256, 0, st>>>(a);
   } else if (rounding == ALTOB200_ROUND_SR_BITS) {
     constexpr int R = Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN;
+    if (rht) quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4><<<grid, 256, 0, st>>>(a);
+    else quantize_colwise_kernel<FMT, IN_BF16, R, false><<<grid, 256, 0, st>>>(a);
+  } else if (rounding == ALTOB200_ROUND_SR_PHILOX) {
+    constexpr int R = Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_PHILOX : ALTOB200_ROUND_RTN;
     if (rht) quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4><<<grid, 256, 0, st>>>(a);
     else quantize_colwise_kernel<FMT, IN_BF16, R, false><<<grid, 256, 0, st>>>(a);
   } else {
@@ -1075,6 +1138,7 @@ int altob200_quantize_rowwise(const void* x, int64_t rows, int64_t cols, int64_t
   a.codes = (uint8_t*)codes; a.scale_plain = scale_plain; a.scale_packed = (uint8_t*)scale_packed;
   a.ncol_tiles = ceil_div(cols / B, 4);
   a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
+  a.philox_seed = p->philox_seed; a.philox_offset = p->philox_offset;
   int rc = clear_packed_if_padded(scale_packed, rows, cols / B, st);
   if (rc != ALTOB200_OK) return rc;
   const int rounding = p->rounding;
@@ -1103,6 +1167,7 @@ int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t
   a.codes = (uint8_t*)codes; a.scale_plain = scale_plain; a.scale_packed = (uint8_t*)scale_packed;
   a.ncol_tiles = ceil_div(rows / B, 4);
   a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
+  a.philox_seed = p->philox_seed; a.philox_offset = p->philox_offset;
   int rc = fill_rht(&a.rht, p->rht_n, p->rht_perm, p->rht_sign);
   if (rc != ALTOB200_OK) return rc;
   rc = clear_packed_if_padded(scale_packed, cols, rows / B, st);

@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the low-precision linear hot path on B200.
+
+Workload (BASELINE.json configs[1]): NVFP4 linear forward + dgrad + wgrad at the Llama-3-8B
+MLP-up shape -- X[8192,4096] ~ N(0,1), W[14336,4096] ~ N(0,0.02), dY[8192,14336] ~ N(0,1e-3),
+bf16; E4M3 block-16 scales + FP32 tensorwise outer scale; W in 16x16 blocks; 16-point
+randomised Hadamard on the wgrad operands; stochastic rounding of the gradients.  Data are
+seeded synthetic tensors of those shapes and distributions.
+
+One "step" = one forward + backward through the public autograd entry point
+(``alto_b200.nvfp4._to_nvfp4_then_scaled_mm``): 5 amax/quantize passes and 3 block-scaled
+GEMMs.  FLOPs counted: 3 * 2*M*N*K (quantizer work is in the time, not in the FLOPs).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Under torchrun (N > 1) every rank runs the same per-GPU workload on its own batch (data
+parallel replicas, no collective on the path); the timed region is bracketed by a barrier and
+``torch.cuda.synchronize()``, timed with CUDA events, and the maximum over ranks is used.
+``--impl reference`` times the CPU restatement of the reference's PyTorch emulation path
+(``oracle/``) on the host cores on a bounded row-sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch
+
+M, K, N = 8192, 4096, 14336
+FLOPS_PER_STEP = 3 * 2 * M * N * K
+METRIC = "nvfp4_linear_fwd_dgrad_wgrad_tflops"
+UNIT = "TFLOP/s"
+CONFIG = {
+    "workload": "NVFP4 linear fwd+dgrad+wgrad, Llama-3-8B MLP-up: X[8192,4096] W[14336,4096] dY[8192,14336] bf16; "
+                "1D-16 activations/grads, 2D 16x16 weights, E4M3 inner + FP32 tensorwise outer scale, "
+                "RHT-16 on wgrad operands, SR on gradients",
+    "shape": {"M": M, "K": K, "N": N},
+    "l2_policy": "per-step inputs (400 MB) exceed the 126 MB L2; no explicit flush",
+    "parallelism": "data-parallel replicas, one process per GPU, no data-path collective",
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+CPU_SAMPLE_ROWS = 256      # token rows of the CPU sample
+CPU_SAMPLE_FEATS = 1024    # output features (rows of W) of the CPU sample
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------------------------------
+# clocks sampler (nvidia-smi, read only)
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the oracle (port of the reference's PyTorch emulation path) on a row sample
+# ------------------------------------------------------------------------------------------
+def cpu_sample_inputs(rows: int):
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(rows, K, generator=g).bfloat16()
+    nf = CPU_SAMPLE_FEATS
+    w = (torch.randn(nf, K, generator=g) * 0.02).bfloat16()
+    dy = (torch.randn(rows, nf, generator=g) * 1e-3).bfloat16()
+    rn = torch.randint(0, 2 ** 32, (2, rows, nf // 2), generator=g, dtype=torch.int64)
+    rm = torch.randint(0, 2 ** 32, (2, nf, rows // 2), generator=g, dtype=torch.int64)
+    return x, w, dy, rn, rm
+
+
+def cpu_step(inputs, W_had):
+    from oracle import alto_oracle as O
+    x, w, dy, rn, rm = inputs
+    return O.nvfp4_linear(x, w, dy, use_2dblock_w=True, use_outer=True, W_had=W_had, rand_dy_n=rn, rand_dy_m=rm)
+
+
+def cpu_baseline(rows: int, reps: int = 1):
+    from oracle import alto_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    W_had, _, _ = O.random_hadamard(16, torch.Generator().manual_seed(0))
+    inputs = cpu_sample_inputs(rows)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        cpu_step(inputs, W_had)
+    dt = (time.perf_counter() - t0) / reps
+    flops = 3 * 2 * rows * CPU_SAMPLE_FEATS * K
+    return {"value": flops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{rows} of {M} token rows x {CPU_SAMPLE_FEATS} of {N} output features (K={K} full): quantize + "
+                      f"Hadamard + dequantize + fp32 matmuls of one fwd+dgrad+wgrad step, {dt:.2f} s per step"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import alto_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    W_had, _, _ = O.random_hadamard(16, torch.Generator().manual_seed(0))
+    rows = CPU_SAMPLE_ROWS
+    inputs = cpu_sample_inputs(rows)
+    for _ in range(args.warmup):
+        cpu_step(inputs, W_had)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(inputs, W_had)
+    dt = time.perf_counter() - t0
+    flops = 3 * 2 * rows * CPU_SAMPLE_FEATS * K * args.steps
+    val = flops / dt / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 codes, e4m3 scales, fp32 accumulate)", "data": "synthetic",
+        "config": CONFIG,
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"each step = {rows} of {M} token rows x {CPU_SAMPLE_FEATS} of {N} output features, CPU "
+                                   "restatement of the reference's PyTorch emulation path (quantize, Hadamard, "
+                                   "dequantize, fp32 matmul)"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+class KernelTimer:
+    """Wraps the C-ABI launch wrappers with CUDA events on the launching (current) stream."""
+
+    def __init__(self):
+        self.records = []
+        self.enabled = False
+        self.launches = 0
+
+    def wrap(self, mod, name, family, work):
+        orig = getattr(mod, name)
+        timer = self
+
+        def wrapped(*a, **kw):
+            timer.launches += 1
+            if not timer.enabled:
+                return orig(*a, **kw)
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = orig(*a, **kw)
+            e1.record()
+            timer.records.append((family, work(*a, **kw), e0, e1))
+            return r
+
+        setattr(mod, name, wrapped)
+
+    def summary(self):
+        out = {}
+        for fam, work, e0, e1 in self.records:
+            d = out.setdefault(fam, {"launches": 0, "ms": 0.0, "work": 0.0})
+            d["launches"] += 1
+            d["ms"] += e0.elapsed_time(e1)
+            d["work"] += work
+        return out
+
+
+def run_ours(args):
+    from alto_b200 import _lib as L
+    from alto_b200 import nvfp4 as NV
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    peaks, peak_src = load_peaks()
+    NV.HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)
+
+    timer = KernelTimer()
+    fp4_bytes = lambda r, c: r * c * (2 + 0.5 + 1.0 / 16)  # noqa: E731  bf16 in, codes + scales out
+    timer.wrap(L, "amax", "amax", lambda x, *a, **k: x.numel() * 2.0)
+    timer.wrap(L, "quantize_rowwise", "quantize_rowwise", lambda x, *a, **k: fp4_bytes(*x.shape))
+    timer.wrap(L, "quantize_colwise", "quantize_colwise", lambda x, *a, **k: fp4_bytes(*x.shape))
+    timer.wrap(L, "quantize_2d", "quantize_2d",
+               lambda x, *a, **k: x.numel() * (2 + 2 * (0.5 + 1.0 / 16)))
+    timer.wrap(L, "gemm_blockscaled", "gemm", lambda fa, fb, m, n, k, *a, **kw: 2.0 * m * n * k)
+
+    g = torch.Generator(device=dev).manual_seed(rank)
+    gw = torch.Generator(device=dev).manual_seed(12345)  # identical weights on every rank
+    x = torch.randn(M, K, generator=g, device=dev, dtype=torch.float32).bfloat16().requires_grad_(True)
+    w = (torch.randn(N, K, generator=gw, device=dev, dtype=torch.float32) * 0.02).bfloat16().requires_grad_(True)
+    dy = (torch.randn(M, N, generator=g, device=dev, dtype=torch.float32) * 1e-3).bfloat16()
+
+    def step():
+        x.grad = None
+        w.grad = None
+        y = NV._to_nvfp4_then_scaled_mm(x, w, False, True, True, use_outer_scale=True, use_hadamard=True)
+        y.backward(dy)
+        return y
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    n0 = timer.launches
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = timer.launches - n0
+    st, detail = L.status_read()
+    if st != 0:
+        raise RuntimeError(f"device-side wait timed out: {detail}")
+    t = torch.tensor([ms], device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    value = world * FLOPS_PER_STEP * args.steps / (ms * 1e-3) / 1e12
+
+    # ---- per-kernel timing pass (events around every launch; not part of the headline) ----
+    timer.enabled = True
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    timer.enabled = False
+    fam = timer.summary()
+    kernels = {}
+    for name, d in fam.items():
+        avg_ms = d["ms"] / d["launches"]
+        if name == "gemm":
+            kernels[name] = {"launches_per_step": d["launches"] // args.steps, "avg_ms": avg_ms,
+                             "tflops": d["work"] / d["launches"] / (avg_ms * 1e-3) / 1e12}
+        else:
+            kernels[name] = {"launches_per_step": d["launches"] // args.steps, "avg_ms": avg_ms,
+                             "gbs": d["work"] / d["launches"] / (avg_ms * 1e-3) / 1e9,
+                             "frac_of_hbm_peak": d["work"] / d["launches"] / (avg_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    fp4_peak = 4.0 * peaks["bf16_tflops_sustained"]
+    gemm_tf = kernels["gemm"]["tflops"]
+    roofline = {"bound": "tensor", "achieved": gemm_tf, "peak": fp4_peak, "unit": "TFLOP/s",
+                "frac": gemm_tf / fp4_peak, "traffic": None,
+                "kernel": "gemm_blockscaled_kernel<NVF4,256> (3 launches per step, 962 GFLOP each)",
+                "peak_source": f"4 x {peak_src} sustained bf16 cuBLAS throughput (dense FP4 proxy); nominal dense FP4 9000"}
+
+    # ---- end to end through the public API with host buffers ----
+    xh = x.detach().cpu().pin_memory()
+    wh = w.detach().cpu().pin_memory()
+    dyh = dy.cpu().pin_memory()
+    yh = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    dxh = torch.empty(M, K, dtype=torch.bfloat16).pin_memory()
+    dwh = torch.empty(N, K, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        with torch.no_grad():
+            x.copy_(xh, non_blocking=True)
+            w.copy_(wh, non_blocking=True)
+            dy.copy_(dyh, non_blocking=True)
+        y = step()
+        yh.copy_(y.detach(), non_blocking=True)
+        dxh.copy_(x.grad, non_blocking=True)
+        dwh.copy_(w.grad, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    h2d = (x.numel() + w.numel() + dy.numel()) * 2
+    d2h = (yh.numel() + dxh.numel() + dwh.numel()) * 2
+    e2e = {"value": world * FLOPS_PER_STEP * args.steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4 (e2m1 codes, e4m3 scales, fp32 accumulate)", "data": "synthetic", "config": CONFIG,
+        "frac_of_fp4_peak": value / world / fp4_peak, "roofline": roofline, "kernels": kernels, "e2e": e2e,
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(CPU_SAMPLE_ROWS)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

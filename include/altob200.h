@@ -88,8 +88,15 @@ typedef struct altob200_quant_params {
    * (alto/kernels/fp4/fp4_common/triton_fp4_ops.py:13-19,
    *  alto/kernels/fp4/mxfp4/mxfp_quantization.py:128-132,184-186).                  */
   const uint32_t* rand_bits;
-  uint64_t philox_seed;   /* ROUND_SR_PHILOX */
-  uint64_t philox_offset; /* ROUND_SR_PHILOX */
+  /* ROUND_SR_PHILOX: Philox-4x32-10 with key = (seed lo, seed hi) and counter =
+   * (c lo, c hi, 0, 0), c = philox_offset + q, where q = (pair index) / 2 and the pair
+   * index is r * (cols_q / 2) + c / 2 in the quantisation-axis-last view.  The four
+   * output words feed, in order, the even and odd element of pair 2q and the even and
+   * odd element of pair 2q+1.  (The generator is the one triton.language.randint4x uses,
+   * alto/kernels/fp4/fp4_common/triton_fp4_ops.py:13-19; the word-to-element mapping is
+   * this library's own and uses all four words of a call.)                            */
+  uint64_t philox_seed;
+  uint64_t philox_offset;
   /* Randomised Hadamard transform applied along the row axis before an axis-0
    * quantisation (alto/kernels/hadamard_transform/transform.py:115-142).  0 = off,
    * else the block size n (16).  The n x n matrix is W = (diag(sign) H_n)[perm][:, perm]
@@ -147,7 +154,10 @@ int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t
 
 /*
  * 2D block quantisation (block x block tiles share one scale) of w[rows, cols].
- * Replaces the is_2d_block=True calls (same reference functions).  2D scales do
+ * Replaces the is_2d_block=True calls of the same reference functions (scale
+ * derivation: alto/kernels/fp4/mxfp4/mxfp_quantization.py:44-57,
+ * alto/kernels/fp4/nvfp4/nvfp_quantization.py:246-251,
+ * alto/kernels/mxfp8/mxfp8_quantization.py:36-78).  2D scales do
  * not depend on the axis, so one read of w produces both operand packings:
  *   codes_k       : [rows, cols/2]  (packed along cols; forward operand)
  *   codes_t       : [cols, rows/2]  (packed along rows; dgrad operand), may be NULL

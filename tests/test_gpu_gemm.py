@@ -1,0 +1,221 @@
+"""GPU tests of the tcgen05 block-scaled GEMM and of the three linear autograd functions.
+
+GEMM results are compared with the oracle's dequantize-then-fp32-matmul definition:
+relative Frobenius error <= 1e-3 (the tolerance the task states); in practice the fp32-output
+kernel agrees to ~1e-7 because products of FP4/FP8 codes and block scales are exact and only
+the fp32 accumulation order differs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import alto_oracle as O
+from tests.helpers import rand_u32, reference_data
+
+pytestmark = pytest.mark.gpu
+REL_TOL = 1e-3
+
+
+def _dev():
+    return torch.device("cuda")
+
+
+def _u32dev(r):
+    return torch.from_numpy((r.numpy() & 0xFFFFFFFF).astype(np.uint32).view(np.int32)).to(_dev())
+
+
+def _rel(got, exp):
+    got = got.detach().float().cpu()
+    return ((got - exp).norm() / exp.norm().clamp(min=1e-30)).item()
+
+
+def _snr(got, ref):
+    got = got.detach().float().cpu()
+    ref = ref.float()
+    return (10 * torch.log10(ref.pow(2).sum() / (got - ref).pow(2).sum().clamp(min=1e-30))).item()
+
+
+# ------------------------------------------------------------------------------------------
+# raw GEMM on synthetic codes and scales
+# ------------------------------------------------------------------------------------------
+
+def _operand(rows, K, kind, seed):
+    """Random codes and scale bytes; returns (codes bytes [rows, K/2 or K], scale bytes [rows, K/block],
+    dequantised fp32 [rows, K])."""
+    g = torch.Generator().manual_seed(seed)
+    if kind == "nvfp4":
+        c = torch.randint(0, 16, (rows, K), generator=g, dtype=torch.uint8)
+        sf = torch.randint(0x20, 0x48, (rows, K // 16), generator=g, dtype=torch.uint8)
+        dq = O.e2m1_decode(c) * sf.view(torch.float8_e4m3fn).float().repeat_interleave(16, 1)
+        return O.pack_nibbles(c), sf, dq
+    if kind == "mxfp4":
+        c = torch.randint(0, 16, (rows, K), generator=g, dtype=torch.uint8)
+        sf = torch.randint(120, 134, (rows, K // 32), generator=g, dtype=torch.uint8)
+        dq = O.e2m1_decode(c) * (sf.to(torch.int32) << 23).view(torch.float32).repeat_interleave(32, 1)
+        return O.pack_nibbles(c), sf, dq
+    dt = torch.float8_e4m3fn if kind == "e4m3" else torch.float8_e5m2
+    v = (torch.randn(rows, K, generator=g) * 4).to(dt)
+    sf = torch.randint(120, 134, (rows, K // 32), generator=g, dtype=torch.uint8)
+    dq = v.float() * (sf.to(torch.int32) << 23).view(torch.float32).repeat_interleave(32, 1)
+    return v.view(torch.uint8), sf, dq
+
+
+_FMT = {"nvfp4": 0, "mxfp4": 1, "e4m3": 2, "e5m2": 3}
+
+
+@pytest.mark.parametrize("kind", ["nvfp4", "mxfp4", "e4m3", "e5m2"])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (128, 256, 1024), (256, 512, 2048), (160, 96, 512),
+                                   (384, 640, 768), (2048, 2048, 2048), (512, 1024, 2880)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_matches_dequantised_fp32_matmul(kind, M, N, K, out_dtype):
+    from alto_b200 import _lib as L
+    if kind != "nvfp4" and K % 32:
+        pytest.skip("K must be a multiple of the block")
+    if out_dtype == torch.bfloat16 and (M, N, K) not in [(256, 512, 2048), (160, 96, 512)]:
+        pytest.skip("bf16 output checked on two shapes")
+    ac, asf, adq = _operand(M, K, kind, 1)
+    bc, bsf, bdq = _operand(N, K, kind, 2)
+    ref = O.gemm_nt_fp32(adq, bdq)
+    d = _dev()
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=d)
+    alpha = torch.tensor([0.5], device=d)
+    L.gemm_blockscaled(_FMT[kind], _FMT[kind], M, N, K, ac.to(d), O.pack_scale_bytes(asf).to(d), bc.to(d),
+                       O.pack_scale_bytes(bsf).to(d), out, alpha, None)
+    st, detail = L.status_read()
+    assert st == 0, f"device status {st} {detail}"
+    ref = ref * 0.5
+    if out_dtype == torch.bfloat16:
+        ref = ref.bfloat16().float()
+    assert not torch.isnan(out).any()
+    assert _rel(out, ref) <= REL_TOL
+
+
+def test_gemm_mixed_fp8_formats():
+    """Forward operands E4M3 with E5M2 gradients (one operand of each format in a GEMM)."""
+    from alto_b200 import _lib as L
+    M, N, K = 256, 384, 1024
+    ac, asf, adq = _operand(M, K, "e5m2", 3)
+    bc, bsf, bdq = _operand(N, K, "e4m3", 4)
+    d = _dev()
+    out = torch.empty(M, N, dtype=torch.float32, device=d)
+    L.gemm_blockscaled(3, 2, M, N, K, ac.to(d), O.pack_scale_bytes(asf).to(d), bc.to(d),
+                       O.pack_scale_bytes(bsf).to(d), out)
+    assert _rel(out, O.gemm_nt_fp32(adq, bdq)) <= REL_TOL
+
+
+def test_gemm_rejects_bad_arguments():
+    from alto_b200 import _lib as L
+    d = _dev()
+    a = torch.zeros(128, 64, dtype=torch.uint8, device=d)
+    s = torch.zeros(512 * 2, dtype=torch.uint8, device=d)
+    out = torch.empty(128, 128, dtype=torch.float32, device=d)
+    with pytest.raises(L.Altob200Error) as e:
+        L.gemm_blockscaled(0, 0, 128, 128, 144, a, s, a, s, out)  # K not a multiple of 32
+    assert e.value.status == L.E_SHAPE
+    with pytest.raises(L.Altob200Error) as e:
+        L.gemm_blockscaled(0, 1, 128, 128, 128, a, s, a, s, out)  # NVFP4 x MXFP4
+    assert e.value.status == L.E_UNSUPPORTED
+
+
+def test_public_gemm_ops_with_plain_scales():
+    """blockwise_mxfp4_gemm / blockwise_mxfp8_gemm take the reference's plain scale layouts."""
+    from alto_b200 import mxfp4 as MX, mxfp8 as M8
+    d = _dev()
+    x = reference_data((256, 512), torch.bfloat16, 1).to(d)
+    w = reference_data((384, 512), torch.bfloat16, 2).to(d)
+    for is2d_w in (False, True):
+        xq, xs = MX.convert_to_mxfp4(x)
+        wq, ws = MX.convert_to_mxfp4(w, is_2d_block=is2d_w)
+        y = MX.blockwise_mxfp4_gemm(xq, xs, wq, ws, trans_b=True, use_2dblock_b=is2d_w)
+        ref = MX.convert_from_mxfp4(xq, xs).cpu() @ MX.convert_from_mxfp4(wq, ws, is_2d_block=is2d_w).cpu().t()
+        assert _rel(y, ref) <= REL_TOL
+        xq, xs = M8.convert_to_mxfp8(x)
+        wq, ws = M8.convert_to_mxfp8(w, is_2d_block=is2d_w)
+        y = M8.blockwise_mxfp8_gemm(xq, xs, wq, ws, trans_b=True, use_2dblock_b=is2d_w)
+        ref = M8.convert_from_mxfp8(xq, xs).cpu() @ M8.convert_from_mxfp8(wq, ws, is_2d_block=is2d_w).cpu().t()
+        assert _rel(y, ref) <= REL_TOL
+    # wgrad form: both operands quantised along axis 0 (transposed views), trans_a
+    g = reference_data((256, 384), torch.bfloat16, 3).to(d)
+    gq, gs = M8.convert_to_mxfp8(g, axis=0)
+    xq, xs = M8.convert_to_mxfp8(x, axis=0)
+    dw = M8.blockwise_mxfp8_gemm(gq, gs, xq, xs, trans_a=True)
+    ref = M8.convert_from_mxfp8(gq, gs, axis=0).cpu().t() @ M8.convert_from_mxfp8(xq, xs, axis=0).cpu()
+    assert _rel(dw, ref) <= REL_TOL
+
+
+# ------------------------------------------------------------------------------------------
+# linear autograd functions against the oracle orchestration
+# ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,K,N", [(256, 512, 384), (1024, 2048, 1536)])
+@pytest.mark.parametrize("use_2dblock_w", [True, False])
+def test_nvfp4_linear_matches_oracle(M, K, N, use_2dblock_w):
+    """The recipe of the headline benchmark: 1D activations, tensorwise outer scale, 16-point
+    randomised Hadamard on the wgrad operands, stochastic rounding of gradients from explicit
+    random bits.  fp32 inputs make the function return fp32, so the comparison is not limited by
+    the bf16 rounding of the outputs."""
+    from alto_b200 import nvfp4 as NV
+    NV.HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)
+    g = torch.Generator().manual_seed(0)
+    W, perm, sign = O.random_hadamard(16, g)
+    x = reference_data((M, K), torch.float32, 21, outliers=False).bfloat16().float()
+    w = (reference_data((N, K), torch.float32, 22, outliers=False) * 0.02).bfloat16().float()
+    dy = (reference_data((M, N), torch.float32, 23, outliers=False) * 1e-3).bfloat16().float()
+    rn, rm = rand_u32((2, M, N // 2), 31), rand_u32((2, N, M // 2), 32)
+    # bf16-valued inputs keep the Hadamard sums exact, so the oracle's dot products and the
+    # kernel's butterfly agree bit for bit and every operand is identical on both sides
+    yo, dxo, dwo = O.nvfp4_linear(x.bfloat16(), w.bfloat16(), dy.bfloat16(), use_2dblock_w=use_2dblock_w, W_had=W,
+                                  rand_dy_n=rn, rand_dy_m=rm)
+    d = _dev()
+    xd = x.bfloat16().to(d).requires_grad_(True)
+    wd = w.bfloat16().to(d).requires_grad_(True)
+    bits = {"dy_n": _u32dev(rn), "dy_m": _u32dev(rm)}
+    with NV.explicit_sr_bits(lambda name, shape, dev: bits[name]):
+        y = NV._to_nvfp4_then_scaled_mm(xd, wd, False, use_2dblock_w, True, use_outer_scale=True, use_hadamard=True)
+        y.backward(dy.bfloat16().to(d))
+    # outputs are bf16: compare with the oracle rounded the same way
+    assert _rel(y, yo.bfloat16().float()) <= REL_TOL
+    assert _rel(xd.grad, dxo.bfloat16().float()) <= REL_TOL
+    assert _rel(wd.grad, dwo.bfloat16().float()) <= REL_TOL
+
+
+@pytest.mark.parametrize("scheme", ["nvfp4", "mxfp4", "mxfp8_e4m3", "mxfp8_e5m2"])
+def test_linear_snr_against_high_precision(scheme):
+    """SNR floors of the reference's own autograd tests (tests/unittest/mxfp4/test_mxfp_linear.py:189-197,
+    tests/unittest/mxfp8/test_mxfp8_linear.py:177-186, alto/kernels/fp4/testing_utils.py:53-103)."""
+    from alto_b200 import mxfp4 as MX, mxfp8 as M8, nvfp4 as NV
+    M, K, N = 512, 1024, 768
+    d = _dev()
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device=d, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(N, K, device=d, dtype=torch.bfloat16) * 0.05).requires_grad_(True)
+    dy = torch.randn(M, N, device=d, dtype=torch.bfloat16)
+    NV.HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)
+    if scheme == "nvfp4":
+        y = NV._to_nvfp4_then_scaled_mm(x, w, False, True, False, use_outer_scale=True, use_hadamard=True)
+        floors = (12.0, 12.0, 12.0)
+    elif scheme == "mxfp4":
+        y = MX._to_mxfp4_then_scaled_mm(x, w, False, True, False, False, "none", True)
+        floors = (8.4, 8.4, 8.4)
+    else:
+        v = scheme.split("_")[1]
+        y = M8._to_mxfp8_then_scaled_mm(x, w, v, False, False, True)
+        floors = (24.0, 15.0, 15.0) if v == "e4m3" else (19.0, 12.0, 12.0)
+    y.backward(dy)
+    xf, wf, dyf = x.detach().float().cpu(), w.detach().float().cpu(), dy.float().cpu()
+    assert _snr(y, xf @ wf.t()) > floors[0]
+    assert _snr(x.grad, dyf @ wf) > floors[1]
+    assert _snr(w.grad, dyf.t() @ xf) > floors[2]
+
+
+def test_linear_shape_contracts():
+    from alto_b200 import nvfp4 as NV
+    d = _dev()
+    w = torch.zeros(64, 64, dtype=torch.bfloat16, device=d)
+    with pytest.raises(RuntimeError):
+        NV._to_nvfp4_then_scaled_mm(torch.zeros(24, 64, dtype=torch.bfloat16, device=d), w, False, True, False)
+    with pytest.raises(NotImplementedError):
+        NV._to_nvfp4_then_scaled_mm(torch.zeros(32, 64, dtype=torch.bfloat16, device=d), w, False, True, False,
+                                    use_dge=True)
+    x3 = torch.randn(2, 32, 64, dtype=torch.bfloat16, device=d)
+    y = NV._to_nvfp4_then_scaled_mm(x3, w, False, True, False)
+    assert y.shape == (2, 32, 64) and y.dtype == torch.bfloat16

@@ -1,0 +1,283 @@
+"""GPU parity tests of the quantizer kernels: CUDA path (through the C ABI) vs the CPU oracle and
+the committed reference vectors.  Codes, scales and packed layouts are compared bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import alto_oracle as O
+from tests.helpers import case_input, golden_cases, load_golden, rand_u32, reference_data, tensor_from_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda")
+
+
+def _u32dev(r):
+    return torch.from_numpy((r.numpy() & 0xFFFFFFFF).astype(np.uint32).view(np.int32)).to(_dev())
+
+
+def _same(got: torch.Tensor, exp, what=""):
+    got = got.detach().cpu()
+    if isinstance(exp, np.ndarray):
+        exp = torch.from_numpy(exp.copy())
+    if got.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        got = got.view(torch.uint8)
+    if exp.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        exp = exp.view(torch.uint8)
+    assert tuple(got.shape) == tuple(exp.shape), f"{what}: shape {tuple(got.shape)} vs {tuple(exp.shape)}"
+    if got.dtype.is_floating_point:
+        bad = ~((got == exp) | (got.isnan() & exp.isnan()))
+    else:
+        bad = got != exp.to(got.dtype)
+    assert int(bad.sum()) == 0, f"{what}: {int(bad.sum())} of {got.numel()} entries differ"
+
+
+# ------------------------------------------------------------------------------------------
+# committed reference vectors (outputs of the reference's own code)
+# ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("z,m", list(golden_cases("nvfp4")), ids=lambda v: v[0] if isinstance(v, tuple) else "")
+def test_nvfp4_kernel_matches_reference_vectors(z, m):
+    from alto_b200 import nvfp4 as NV
+    tag, shape, dt, axis, is2d = m
+    x = case_input(z, m).to(_dev())
+    outer = z[tag + "_outer"]
+    outer_d = torch.from_numpy(outer.copy()).to(_dev()) if outer.size else None
+    if outer_d is not None:
+        _same(NV.compute_dynamic_outer_scale(x), outer, "outer scale")
+        buf = torch.zeros(1, dtype=torch.float32, device=_dev())
+        q, s = NV.convert_to_nvfp4(x, axis=axis, is_2d_block=is2d, outer_scale=buf, update_outer_scale=True)
+        _same(buf, outer, "outer scale refreshed in place")
+    else:
+        q, s = NV.convert_to_nvfp4(x, axis=axis, is_2d_block=is2d, update_outer_scale=False)
+    _same(s, z[tag + "_s"], "scales")
+    _same(q, z[tag + "_q"], "codes")
+    dq = NV.convert_from_nvfp4(q, s, torch.float32, axis=axis, is_2d_block=is2d, outer_scale=outer_d)
+    _same(dq, z[tag + "_dq"], "dequantised")
+
+
+@pytest.mark.parametrize("z,m", list(golden_cases("mxfp4")), ids=lambda v: v[0] if isinstance(v, tuple) else "")
+def test_mxfp4_kernel_matches_reference_vectors(z, m):
+    from alto_b200 import mxfp4 as MX
+    tag, shape, dt, axis, is2d = m
+    x = case_input(z, m).to(_dev())
+    q, s = MX.convert_to_mxfp4(x, axis=axis, is_2d_block=is2d)
+    _same(s, z[tag + "_s"], "scales")
+    _same(q, z[tag + "_q"], "codes")
+    _same(MX.convert_from_mxfp4(q, s, torch.float32, axis=axis, is_2d_block=is2d), z[tag + "_dq"], "dequantised")
+
+
+@pytest.mark.parametrize("z,m", list(golden_cases("mxfp4sr")), ids=lambda v: v[0] if isinstance(v, tuple) else "")
+def test_mxfp4_stochastic_rounding_matches_reference_kernel(z, m):
+    """Same random words as the reference's Triton kernel consumed -> same codes."""
+    from alto_b200 import mxfp4 as MX
+    tag, shape, dt, axis, is2d = m
+    x = case_input(z, m).to(_dev())
+    rand = torch.from_numpy(z[tag + "_rand"].view(np.int32).copy()).to(_dev())
+    q, s = MX.convert_to_mxfp4(x, axis=axis, use_sr=True, rand_bits=rand)
+    _same(s, z[tag + "_s"], "scales")
+    _same(q, z[tag + "_q"], "codes")
+
+
+@pytest.mark.parametrize("z,m", list(golden_cases("mxfp8")), ids=lambda v: v[0] if isinstance(v, tuple) else "")
+def test_mxfp8_kernel_matches_reference_vectors(z, m):
+    from alto_b200 import mxfp8 as M8
+    tag, shape, dt, axis, is2d, fmt = m
+    x = case_input(z, m).to(_dev())
+    q, s = M8.convert_to_mxfp8(x, mxfp_format=fmt, axis=axis, is_2d_block=is2d)
+    _same(s, z[tag + "_s"], "scales")
+    _same(q, z[tag + "_q"], "codes")
+    _same(M8.convert_from_mxfp8(q, s, torch.float32, axis=axis, is_2d_block=is2d), z[tag + "_dq"], "dequantised")
+    _same(M8.calculate_mxfp8_scales(x, mxfp_format=fmt, axis=axis, is_2d_block=is2d), z[tag + "_s"], "scale op")
+
+
+def test_hadamard_kernel_matches_reference_vectors():
+    from alto_b200 import _lib as L
+    z, _ = load_golden()
+    W = torch.from_numpy(z["rht16_W"])
+    g = torch.Generator().manual_seed(0)
+    W2, perm, sign = O.random_hadamard(16, g)
+    assert torch.equal(W, W2)
+    x = tensor_from_bits(z["rht16_x"], torch.bfloat16).to(_dev())
+    y = torch.empty_like(x)
+    L.rht_apply(x, y, L.Rht(16, perm.tolist(), [int(v) for v in sign.tolist()]))
+    assert np.array_equal(y.cpu().view(torch.int16).numpy().view(np.uint16), z["rht16_y"])
+
+
+def test_hadamard_factory_matches_reference_draws():
+    from alto_b200.hadamard import HadamardFactory
+    z, _ = load_golden()
+    HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)
+    t = HadamardFactory.create_transform(device=_dev())
+    assert torch.equal(t.matrix().cpu(), torch.from_numpy(z["rht16_W"]))
+    x = tensor_from_bits(z["rht16_x"], torch.bfloat16).to(_dev())
+    y = t(x, left_mul=True)
+    assert np.array_equal(y.cpu().view(torch.int16).numpy().view(np.uint16), z["rht16_y"])
+    HadamardFactory.configure(block_size=32)
+    t32 = HadamardFactory.create_transform(device=_dev())
+    with pytest.raises(NotImplementedError):
+        t32(x, left_mul=True)
+    HadamardFactory.configure(block_size=16, seed=0)
+
+
+# ------------------------------------------------------------------------------------------
+# oracle parity at the reference tests' shapes and at larger, ragged and special inputs
+# ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("shape", [(128, 64), (2048, 2048), (4, 128, 64), (150, 64), (96, 2880)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("outer", [False, True])
+def test_nvfp4_rowwise(shape, dtype, outer):
+    from alto_b200 import nvfp4 as NV
+    x = reference_data(shape, dtype, 1234)
+    oc = O.compute_dynamic_outer_scale(x) if outer else None
+    qo, so = O.quantize_nvfp4(x, 16, -1, False, oc)
+    q, s = NV.convert_to_nvfp4(x.to(_dev()), update_outer_scale=outer)
+    _same(s, so, "scales")
+    _same(q, qo, "codes")
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "e4m3", "e5m2"])
+@pytest.mark.parametrize("shape,axis,is2d", [((128, 64), -1, False), ((2048, 2048), -1, False), ((4, 128, 64), -2, False),
+                                             ((2048, 2048), 0, False), ((2048, 2048), -1, True), ((256, 2880), -1, False),
+                                             ((2048, 1024), 0, True)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_mx_formats(fmt, shape, axis, is2d, dtype):
+    from alto_b200 import mxfp4 as MX, mxfp8 as M8
+    x = reference_data(shape, dtype, 1234)
+    if fmt == "mxfp4":
+        qo, so = O.quantize_mxfp4(x, 32, axis, is2d)
+        q, s = MX.convert_to_mxfp4(x.to(_dev()), axis=axis, is_2d_block=is2d)
+    else:
+        qo, so = O.quantize_mxfp8(x, 32, fmt, axis, is2d)
+        q, s = M8.convert_to_mxfp8(x.to(_dev()), mxfp_format=fmt, axis=axis, is_2d_block=is2d)
+    _same(s, so, "scales")
+    _same(q, qo, "codes")
+
+
+@pytest.mark.parametrize("shape", [(128, 64), (2048, 1024), (512, 200)])
+@pytest.mark.parametrize("mode", ["rtn", "sr_bits", "sr_philox"])
+@pytest.mark.parametrize("use_rht", [False, True])
+def test_nvfp4_colwise_with_hadamard_and_sr(shape, mode, use_rht):
+    """Axis-0 quantisation, optionally after the 16-point randomised Hadamard transform, with
+    round-to-nearest, explicit random bits, and in-kernel Philox."""
+    from alto_b200 import _lib as L
+    M, N = shape
+    x = reference_data(shape, torch.bfloat16, 7, outliers=False)
+    g = torch.Generator().manual_seed(3)
+    W, perm, sign = O.random_hadamard(16, g)
+    rht = L.Rht(16, perm.tolist(), [int(v) for v in sign.tolist()]) if use_rht else None
+    xin = O.rht_apply(x, W) if use_rht else x
+    outer = O.compute_dynamic_outer_scale(xin)
+    rand, kw = None, {}
+    if mode == "sr_bits":
+        rand = rand_u32((2, N, M // 2), 11)
+        kw = dict(rounding=L.ROUND_SR_BITS, rand_bits=_u32dev(rand))
+    elif mode == "sr_philox":
+        seed, off = 0x1234567890AB, 77
+        ctr = torch.arange(N * (M // 2) // 2, dtype=torch.int64) + off
+        zz = torch.zeros_like(ctr)
+        o = O.philox4x32_10(ctr & 0xFFFFFFFF, ctr >> 32, zz, zz, torch.full_like(ctr, seed & 0xFFFFFFFF),
+                            torch.full_like(ctr, seed >> 32))
+        # call q feeds pairs 2q (words 0,1) and 2q+1 (words 2,3); word parity = element parity
+        rand = torch.stack([torch.stack([o[0], o[2]], 1).reshape(N, M // 2),
+                            torch.stack([o[1], o[3]], 1).reshape(N, M // 2)])
+        kw = dict(rounding=L.ROUND_SR_PHILOX, philox=(seed, off))
+    qo, so = O.quantize_nvfp4(xin, 16, 0, False, outer, rand)
+    xd = x.to(_dev())
+    codes = torch.empty(N, M // 2, dtype=torch.uint8, device=_dev())
+    plain = torch.empty(N, M // 16, dtype=torch.float32, device=_dev())
+    packed = torch.full((L.packed_scale_bytes(N, M // 16),), 0xAB, dtype=torch.uint8, device=_dev())
+    L.quantize_colwise(xd, L.FMT_NVFP4, codes, plain, packed, outer_scale=outer.to(_dev()), rht=rht, **kw)
+    _same(plain, so.t(), "scales")
+    _same(codes, qo.t(), "codes")
+    _same(packed, O.pack_scale_bytes(O.e4m3_byte(so.t().contiguous())), "packed scales")
+
+
+def test_nvfp4_rowwise_stochastic_rounding_bits_and_philox():
+    from alto_b200 import nvfp4 as NV
+    x = reference_data((256, 512), torch.bfloat16, 4)
+    r = rand_u32((2, 256, 256), 5)
+    qo, _ = O.quantize_nvfp4(x, 16, -1, False, None, r)
+    q, _ = NV.convert_to_nvfp4(x.to(_dev()), update_outer_scale=False, use_sr=True, rand_bits=_u32dev(r))
+    _same(q, qo, "explicit bits")
+    q_rtn, _ = O.quantize_nvfp4(x, 16, -1, False, None)
+    assert (q_rtn != qo).float().mean() > 0.05
+    seed, off = 987654321, 12345
+    ctr = torch.arange(256 * 256 // 2, dtype=torch.int64) + off
+    zz = torch.zeros_like(ctr)
+    o = O.philox4x32_10(ctr & 0xFFFFFFFF, ctr >> 32, zz, zz, torch.full_like(ctr, seed & 0xFFFFFFFF),
+                        torch.full_like(ctr, seed >> 32))
+    rp = torch.stack([torch.stack([o[0], o[2]], 1).reshape(256, 256), torch.stack([o[1], o[3]], 1).reshape(256, 256)])
+    qo, _ = O.quantize_nvfp4(x, 16, -1, False, None, rp)
+    q, _ = NV.convert_to_nvfp4(x.to(_dev()), update_outer_scale=False, use_sr=True, philox_seed=seed,
+                               philox_offset=off)
+    _same(q, qo, "philox")
+
+
+@pytest.mark.parametrize("shape", [(128, 64), (256, 320), (1024, 2048), (144, 80)])
+def test_nvfp4_2d_dual_packing_and_packed_scales(shape):
+    from alto_b200 import _lib as L
+    R, Cc = shape
+    x = (reference_data(shape, torch.bfloat16, 9, outliers=False) * 0.02).to(torch.bfloat16)
+    oc = O.compute_dynamic_outer_scale(x)
+    d = _dev()
+    ck = torch.empty(R, Cc // 2, dtype=torch.uint8, device=d)
+    ct = torch.empty(Cc, R // 2, dtype=torch.uint8, device=d)
+    plain = torch.empty(R // 16, Cc // 16, dtype=torch.float32, device=d)
+    pk = torch.full((L.packed_scale_bytes(R, Cc // 16),), 0xAB, dtype=torch.uint8, device=d)
+    pt = torch.full((L.packed_scale_bytes(Cc, R // 16),), 0xAB, dtype=torch.uint8, device=d)
+    L.quantize_2d(x.to(d), L.FMT_NVFP4, ck, ct, plain, pk, pt, outer_scale=oc.to(d))
+    qo, so = O.quantize_nvfp4(x, 16, -1, True, oc)
+    qt, _ = O.quantize_nvfp4(x, 16, 0, True, oc)
+    _same(plain, so, "scales")
+    _same(ck, qo, "codes packed along columns")
+    _same(ct, qt.t(), "codes packed along rows")
+    sb = O.e4m3_byte(so)
+    _same(pk, O.pack_scale_bytes(sb.repeat_interleave(16, 0)), "packed scales (row operand)")
+    _same(pt, O.pack_scale_bytes(sb.t().repeat_interleave(16, 0)), "packed scales (transposed operand)")
+
+
+def test_nvfp4_special_values():
+    """The reference's edge cases (tests/unittest/nvfp4/test_nvfp_quantization.py:167-339)."""
+    from alto_b200 import nvfp4 as NV
+    d = _dev()
+    zeros = torch.zeros(64, 64, dtype=torch.bfloat16, device=d)
+    q, s = NV.convert_to_nvfp4(zeros, update_outer_scale=False)
+    assert torch.all(s == 2.0 ** -6) and torch.all(q == 0)
+    big = torch.full((64, 64), 5000.0, dtype=torch.bfloat16, device=d)
+    q, s = NV.convert_to_nvfp4(big, update_outer_scale=False)
+    assert torch.all(s == 448.0) and torch.all(q == 0x77)
+    buf = torch.zeros(1, dtype=torch.float32, device=d)
+    q, s = NV.convert_to_nvfp4(zeros, outer_scale=buf)
+    assert buf.item() == pytest.approx(1e-30) and (s * buf).min().item() > 1.17e-38
+    x = torch.randn(64, 64, device=d).bfloat16()
+    x.view(-1)[7] = float("nan")
+    q, s = NV.convert_to_nvfp4(x, update_outer_scale=False)
+    assert torch.isfinite(s).all()
+    assert torch.isfinite(NV.convert_from_nvfp4(q, s)).all()
+    assert NV.compute_dynamic_outer_scale(x).item() == pytest.approx(1e-30)
+    neg0 = torch.full((16, 16), -0.0, dtype=torch.bfloat16, device=d)
+    q, _ = NV.convert_to_nvfp4(neg0, update_outer_scale=False)
+    assert torch.all(q == 0x88)
+
+
+def test_contract_violations_raise_before_launch():
+    from alto_b200 import _lib as L, mxfp8 as M8, nvfp4 as NV
+    d = _dev()
+    with pytest.raises(RuntimeError):
+        NV.convert_to_nvfp4(torch.zeros(16, 24, dtype=torch.bfloat16, device=d))
+    with pytest.raises(AssertionError):
+        NV.convert_to_nvfp4(torch.zeros(16, 32, dtype=torch.float16, device=d))
+    with pytest.raises(NotImplementedError):
+        NV.convert_to_nvfp4(torch.zeros(16, 32, dtype=torch.bfloat16, device=d), scale_format="ue5m3")
+    with pytest.raises(AssertionError):
+        M8.convert_to_mxfp8(torch.zeros(32, 32, dtype=torch.bfloat16, device=d), use_sr=True)
+    with pytest.raises(RuntimeError):
+        NV.convert_to_nvfp4(torch.zeros(16, 32, dtype=torch.bfloat16))  # CPU tensor: no fallback
+    x = torch.zeros(64, 64, dtype=torch.bfloat16, device=d)
+    with pytest.raises(L.Altob200Error) as e:
+        L.quantize_rowwise(x[:, 1:33], L.FMT_NVFP4, torch.empty(64, 16, dtype=torch.uint8, device=d))
+    assert e.value.status == L.E_ALIGN
