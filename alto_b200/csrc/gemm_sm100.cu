@@ -4,22 +4,29 @@
 // FP8: one byte per element) and carry one scale per 16 (NVFP4, UE4M3) or 32 (MXFP4 /
 // MXFP8, UE8M0) elements in the packed layout described in altob200.h.
 //
-// Structure of one CTA (192 threads, persistent over output tiles of 128 x BN):
+// Structure of one CTA (320 threads, persistent over output tiles of 128 x BN):
 //   warp 0      : producer.  One elected lane issues, per k-stage, two tiled TMA loads
 //                 (A: 128 rows x 128 bytes, B: BN rows x 128 bytes, 128-byte swizzle) and
 //                 the bulk copies of the stage's scale tiles, all completing on the
 //                 stage's "full" mbarrier.
-//   warp 1      : MMA issuer.  Owns tensor memory (512 columns).  Per stage it copies
-//                 the scale tiles shared memory -> tensor memory (tcgen05.cp) and issues
+//   warp 1      : MMA issuer.  Owns tensor memory (512 columns).  Per stage one thread issues
 //                 four tcgen05.mma (each consumes 32 bytes of K per row), then commits to
 //                 the stage's "empty" mbarrier; after the last stage of a tile it commits
 //                 to the accumulator's "full" mbarrier.
+//   warps 6..9  : scale transfer.  Each warp owns one 32-lane quarter of tensor memory and,
+//                 per stage, moves the stage's scale tiles shared memory -> registers ->
+//                 tensor memory (tcgen05.st), then arrives on the stage's "scales ready"
+//                 mbarrier.  (A tcgen05.cp in the MMA issuer's stream costs a pipeline
+//                 bubble of ~500 cycles per stage at every copy -> MMA boundary; measured.)
 //   warps 2..5  : epilogue.  Each warp reads its 32-lane quarter of the accumulator with
-//                 tcgen05.ld, multiplies by alpha, converts and stores its rows.
+//                 tcgen05.ld, multiplies by alpha, converts, writes 32 rows x 128 bytes into a
+//                 128-byte-swizzled staging buffer and hands it to a TMA store (which also
+//                 clips ragged M/N edges); two staging buffers per warp keep stores in flight.
 // Every mbarrier wait is bounded by a wall-clock limit; a wait that gives up records
 // {kernel, block, site} in a device status word, raises a CTA-wide abort flag, and all
 // roles fall through to the common teardown that frees tensor memory.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -29,7 +36,7 @@ __device__ int g_status[4] = {0, 0, 0, 0};
 
 constexpr int BM = 128;
 constexpr int STAGE_K_BYTES = 128;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // producer, MMA issuer, 4 epilogue warps, 4 scale-transfer warps
 constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // 4 s per wait
 
 enum { KIND_NVF4 = 0, KIND_MXF4 = 1, KIND_MXF8 = 2 };
@@ -68,6 +75,9 @@ struct GemmArgs {
   const int32_t* group_expert;
   int64_t sfb_expert_stride;
   uint32_t idesc[4];     // instruction descriptors of the four MMAs of a stage
+  // profiling switches (env ALTOB200_GEMM_DEBUG, results are then WRONG): 1 = copy scales only in the
+  // first stage of a tile, 2 = skip the global stores, 4 = stop loading operands once the ring is full
+  int debug;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -140,14 +150,26 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
       : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const void* smem_src, const CUtensorMap* map, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
-}
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 template <int KIND>
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -184,7 +206,19 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tc_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c),
+               "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// High 32 bits of the operand descriptor (stride byte offset, version, swizzle); the low word
+// holds the start address >> 4 (and the unused leading offset), so moving to another stage or
+// 32-byte K slice is one 32-bit add for the single issuing thread.
+constexpr uint32_t DESC_SW128_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint64_t desc_of(uint32_t hi, uint32_t lo) { return ((uint64_t)hi << 32) | lo; }
 
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
@@ -196,15 +230,6 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
   d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
   return d;
 }
-// Descriptor of one 512-byte scale tile: 32 rows x 16 bytes, no swizzle, 8-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
-  d |= (uint64_t)(128 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  return d;
-}
-
 // ---------------------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------------------
@@ -221,26 +246,29 @@ struct Cfg {
   static constexpr int SF_COLS_A = SF_TILES * 4;             // tensor-memory columns per stage
   static constexpr int SF_COLS_B = SF_TILES * 4 * NB;
   static constexpr int ACC_STAGES = (BN <= 128) ? 2 : 1;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (BN == 256) ? 3 : 5;
+  static constexpr int EPI_BYTES = 4 /*warps*/ * 2 /*buffers*/ * 4096;  // 32 rows x 128 bytes each
   static constexpr int TMEM_SF_BASE = ACC_STAGES * BN;
   static constexpr int TMEM_COLS_USED = TMEM_SF_BASE + STAGES * (SF_COLS_A + SF_COLS_B);
   static_assert(TMEM_COLS_USED <= 512, "tensor memory budget");
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
 template <int KIND, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                        const GemmArgs args) {
+                        const __grid_constant__ CUtensorMap tmap_d, const GemmArgs args) {
   using C = Cfg<KIND, BN>;
   extern __shared__ uint8_t smem_raw[];
   // operand stages need 1024-byte alignment for the 128-byte swizzle
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* epi = smem + C::STAGES * C::STAGE_BYTES;  // 1024-byte aligned staging of the epilogue
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + C::EPI_BYTES);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + C::STAGES;
-  uint64_t* acc_full = bars + 2 * C::STAGES;
+  uint64_t* sf_full = bars + 2 * C::STAGES;
+  uint64_t* acc_full = bars + 3 * C::STAGES;
   uint64_t* acc_empty = acc_full + C::ACC_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::ACC_STAGES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -256,6 +284,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      mbar_init(&sf_full[s], 4);
     }
     for (int a = 0; a < C::ACC_STAGES; ++a) {
       mbar_init(&acc_full[a], 1);
@@ -306,6 +335,10 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
           // 128-row blocks of B that exist (the last tile of a ragged N has fewer)
           int nb_valid = (int)(n_row_blocks - nb * C::NB);
           if (nb_valid > C::NB) nb_valid = C::NB;
+          if ((args.debug & 4) && it >= (uint32_t)C::STAGES) {
+            mbar_arrive(&full_bar[s]);
+            continue;
+          }
           mbar_expect_tx(&full_bar[s], C::A_BYTES + C::B_BYTES + sf_bytes * (1 + nb_valid));
           tma_load_2d(st, &tmap_a, ks * STAGE_K_BYTES, (int32_t)(mb * BM), &full_bar[s]);
           tma_load_2d(st + C::A_BYTES, &tmap_b, ks * STAGE_K_BYTES, (int32_t)b_row0, &full_bar[s]);
@@ -324,6 +357,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     if (lane == 0) {
       uint32_t it = 0, tile_it = 0;
       bool alive = true;
+      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t idesc[4] = {args.idesc[0], args.idesc[1], args.idesc[2], args.idesc[3]};
       for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
         if (args.num_experts > 0 && __ldg(args.group_expert + (tile % tiles_m)) < 0) continue;
         const int acc = tile_it % C::ACC_STAGES;
@@ -333,33 +368,59 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         for (int ks = 0; ks < k_stages; ++ks, ++it) {
           const int s = it % C::STAGES;
           if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 3)) { alive = false; break; }
+          if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 5)) { alive = false; break; }
           tc_fence_after();
-          const uint32_t st = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;  // stage address / 16
           const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
           const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
-          // scale tiles: tile t of A -> 4 columns; tile t of B row block j -> columns t*4*NB + 4j
-#pragma unroll
-          for (int t = 0; t < C::SF_TILES; ++t) {
-            tc_cp_sf(sfa_t + t * 4, make_desc_sf(st + C::A_BYTES + C::B_BYTES + t * 512));
-#pragma unroll
-            for (int j = 0; j < C::NB; ++j)
-              tc_cp_sf(sfb_t + t * 4 * C::NB + j * 4,
-                       make_desc_sf(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + j * C::SFA_BYTES + t * 512));
-          }
-          const uint64_t a_desc = make_desc_sw128(st);
-          const uint64_t b_desc = make_desc_sw128(st + C::A_BYTES);
+          const uint32_t a_lo = st4 | 0x10000u;
+          const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             // MMA j covers bytes [32j, 32j+32) of the stage; its scale tile and byte offset
             // inside the tile depend on how many scales one MMA consumes.
             const int t = (KIND == KIND_NVF4) ? j : (KIND == KIND_MXF4 ? (j >> 1) : 0);
-            tc_mma<KIND>(d_tmem, a_desc + 2 * j, b_desc + 2 * j, args.idesc[j], (ks | j) != 0 ? 1u : 0u,
-                         sfa_t + t * 4, sfb_t + t * 4 * C::NB);
+            tc_mma<KIND>(d_tmem, desc_of(DESC_SW128_HI, a_lo + 2 * j), desc_of(DESC_SW128_HI, b_lo + 2 * j), idesc[j],
+                         (ks | j) != 0 ? 1u : 0u, sfa_t + t * 4, sfb_t + t * 4 * C::NB);
           }
           tc_commit(&empty_bar[s]);
         }
         if (alive) tc_commit(&acc_full[acc]);
         ++tile_it;
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------ scale transfer ------------------------------
+    // Tile t of A -> columns [4t, 4t+4) of the stage's A-scale area; tile t of B row block j ->
+    // columns [4 NB t + 4 j, +4) of its B-scale area.  Lane l of every quarter holds scale row
+    // l of each 512-byte tile (16 bytes = 4 columns), i.e. the 4x replicated layout the MMA reads.
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t it = 0;
+    bool alive = true;
+    for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+      if (args.num_experts > 0 && __ldg(args.group_expert + (tile % tiles_m)) < 0) continue;
+      for (int ks = 0; ks < k_stages; ++ks, ++it) {
+        const int s = it % C::STAGES;
+        if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 6)) { alive = false; break; }
+        const uint8_t* sf = smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
+        const uint32_t sfa_t = tmem_base + lane_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
+        const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
+        if (!((args.debug & 1) && ks > 0)) {
+#pragma unroll
+          for (int t = 0; t < C::SF_TILES; ++t) {
+            const uint4 a = *reinterpret_cast<const uint4*>(sf + t * 512);
+            tc_st4(sfa_t + t * 4, a.x, a.y, a.z, a.w);
+#pragma unroll
+            for (int j = 0; j < C::NB; ++j) {
+              const uint4 b = *reinterpret_cast<const uint4*>(sf + C::SFA_BYTES + j * C::SFA_BYTES + t * 512);
+              tc_st4(sfb_t + t * 4 * C::NB + j * 4, b.x, b.y, b.z, b.w);
+            }
+          }
+          tc_wait_st();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sf_full[s]);
       }
     }
   } else {
@@ -368,67 +429,80 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     float alpha = 1.0f;
     if (args.alpha_a != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_a));
     if (args.alpha_b != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_b));
-    uint32_t tile_it = 0;
+    const uint32_t stage_buf = smem_u32(epi) + (uint32_t)(warp - 2) * 8192u;
+    const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;  // this lane's 128-byte row (buffer 0)
+    const uint32_t sw = (uint32_t)(lane & 7);                   // 128-byte swizzle: 16-byte chunk c -> c ^ (row & 7)
+    const int CH = args.out_bf16 ? 64 : 32;                     // output columns per 128-byte row
+    const int n_chunks = BN / CH;
+    uint32_t tile_it = 0, store_it = 0;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
       const int64_t mb = tile % tiles_m, nb = tile / tiles_m;
-      const int64_t row = mb * BM + quad * 32 + lane;
+      const int64_t row0 = mb * BM + quad * 32;
       const bool pad_group = args.num_experts > 0 && __ldg(args.group_expert + mb) < 0;
       const int acc = tile_it % C::ACC_STAGES;
       if (!pad_group) {
         if (!mbar_wait(&acc_full[acc], (tile_it / C::ACC_STAGES) & 1, abort_flag, 4)) break;
         tc_fence_after();
       }
+      const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
+      for (int cc = 0; cc < n_chunks; ++cc, ++store_it) {
+        const uint32_t buf_off = (store_it & 1u) * 4096u;
+        // the TMA store issued two chunks ago from this buffer must have finished reading it
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
         uint32_t r[32];
-        if (!pad_group) {
-          tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + cc * 32, r);
-          tc_wait_ld();
-        } else {
+        if (args.out_bf16) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0u;
+          for (int h = 0; h < 2; ++h) {
+            if (!pad_group) {
+              tc_ld32(t_acc + cc * 64 + h * 32, r);
+              tc_wait_ld();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t o[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                o[q] = f32_to_bf16_bits(__fmul_rn(u2f(r[8 * j + 2 * q]), alpha)) |
+                       (f32_to_bf16_bits(__fmul_rn(u2f(r[8 * j + 2 * q + 1]), alpha)) << 16);
+              st_shared_v4(my_row + buf_off + ((((uint32_t)(h * 4 + j)) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+            }
+          }
+        } else {
+          if (!pad_group) {
+            tc_ld32(t_acc + cc * 32, r);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(my_row + buf_off + ((((uint32_t)j) ^ sw) << 4), f2u(__fmul_rn(u2f(r[4 * j]), alpha)),
+                         f2u(__fmul_rn(u2f(r[4 * j + 1]), alpha)), f2u(__fmul_rn(u2f(r[4 * j + 2]), alpha)),
+                         f2u(__fmul_rn(u2f(r[4 * j + 3]), alpha)));
         }
-        if (cc == BN / 32 - 1 && !pad_group) {
+        if (cc == n_chunks - 1 && !pad_group) {
           // all of this warp's reads of the accumulator are done
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[acc]);
         }
-        const int64_t col0 = nb * BN + cc * 32;
-        if (row < args.M && col0 < args.N) {
-          const bool full = col0 + 32 <= args.N;
-          if (args.out_bf16) {
-            __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(args.d) + row * args.ldd + col0;
-            if (full) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint32_t o[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  o[q] = f32_to_bf16_bits(__fmul_rn(u2f(r[8 * j + 2 * q]), alpha)) |
-                         (f32_to_bf16_bits(__fmul_rn(u2f(r[8 * j + 2 * q + 1]), alpha)) << 16);
-                reinterpret_cast<uint4*>(drow)[j] = make_uint4(o[0], o[1], o[2], o[3]);
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < args.N; ++j)
-                drow[j] = __float2bfloat16_rn(__fmul_rn(u2f(r[j]), alpha));
-            }
-          } else {
-            float* drow = reinterpret_cast<float*>(args.d) + row * args.ldd + col0;
-            if (full) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<float4*>(drow)[j] =
-                    make_float4(__fmul_rn(u2f(r[4 * j]), alpha), __fmul_rn(u2f(r[4 * j + 1]), alpha),
-                                __fmul_rn(u2f(r[4 * j + 2]), alpha), __fmul_rn(u2f(r[4 * j + 3]), alpha));
-            } else {
-              for (int j = 0; j < 32 && col0 + j < args.N; ++j) drow[j] = __fmul_rn(u2f(r[j]), alpha);
-            }
-          }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        const int64_t col0 = nb * BN + (int64_t)cc * CH;
+        if (lane == 0 && row0 < args.M && col0 < args.N && !(args.debug & 2)) {
+          tma_store_2d(epi + (warp - 2) * 8192 + buf_off, &tmap_d, (int32_t)col0, (int32_t)row0);
+          bulk_commit();
         }
       }
       if (!pad_group) ++tile_it;
     }
+    if (lane == 0) bulk_wait_all();
   }
 
   // ------------------------------ teardown ------------------------------
@@ -457,6 +531,21 @@ static EncodeTiledFn get_encode_fn() {
       fn = reinterpret_cast<EncodeTiledFn>(p);
   }
   return fn;
+}
+
+// 2D tensor map of the output [M, N] (bf16 or fp32): box of 32 rows x 128 bytes, 128-byte swizzle.
+static int make_tmap_out(CUtensorMap* m, void* base, int64_t M, int64_t N, int64_t ldd, bool bf16) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return ALTOB200_ECUDA;
+  const int esz = bf16 ? 2 : 4;
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)(ldd * esz)};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 
 // 2D uint8 tensor map over [rows, row_bytes] with a box of [box_rows, 128 bytes].
@@ -507,7 +596,8 @@ static int sm_count_gemm() {
 }
 
 template <int KIND, int BN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmArgs& args,
+                       cudaStream_t st) {
   using C = Cfg<KIND, BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -518,7 +608,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
   const int64_t tiles = ceil_div(args.M, BM) * ceil_div(args.N, BN);
   int64_t grid = sm_count_gemm();
   if (grid > tiles) grid = tiles;
-  gemm_blockscaled_kernel<KIND, BN><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, args);
+  gemm_blockscaled_kernel<KIND, BN><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, td, args);
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 
@@ -555,6 +645,9 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
   if (rc != ALTOB200_OK) return rc;
   rc = make_tmap(&tb, b_codes, b_rows, k_bytes, BN);
   if (rc != ALTOB200_OK) return rc;
+  CUtensorMap td;
+  rc = make_tmap_out(&td, d, M, N, ldd, out_dtype == ALTOB200_DT_BF16);
+  if (rc != ALTOB200_OK) return rc;
 
   GemmArgs g;
   g.M = M; g.N = N; g.K = K; g.k_bytes = k_bytes;
@@ -568,9 +661,15 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
     const int sf_id = kind == KIND_NVF4 ? 0 : (kind == KIND_MXF4 ? (j & 1) * 2 : j);
     g.idesc[j] = make_idesc(kind, format_a, format_b, BN, sf_id);
   }
+  static int debug_flags = -1;
+  if (debug_flags < 0) {
+    const char* e = getenv("ALTOB200_GEMM_DEBUG");
+    debug_flags = e ? atoi(e) : 0;
+  }
+  g.debug = debug_flags;
   cudaStream_t st = (cudaStream_t)stream;
 #define LAUNCH(KD)                                                    \
-  return BN == 128 ? launch_gemm<KD, 128>(ta, tb, g, st) : launch_gemm<KD, 256>(ta, tb, g, st)
+  return BN == 128 ? launch_gemm<KD, 128>(ta, tb, td, g, st) : launch_gemm<KD, 256>(ta, tb, td, g, st)
   switch (kind) {
     case KIND_NVF4: LAUNCH(KIND_NVF4);
     case KIND_MXF4: LAUNCH(KIND_MXF4);
