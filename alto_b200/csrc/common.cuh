@@ -159,28 +159,24 @@ __device__ __forceinline__ uint32_t e2m1x2_rtn_hw(float v0, float v1) {
 //   alto/kernels/fp4/fp4_common/triton_fp4_ops.py:26-93 with USE_SR=True.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t e2m1_sr_bits(float v, uint32_t rnd) {
-  uint32_t qx = f2u(v);
-  const uint32_t s = qx & 0x80000000u;
-  qx ^= s;
-  const float a = u2f(qx);
-  uint32_t code;
-  if (a >= 6.0f) {
-    code = 7u;
-  } else if (a < 1.0f) {
-    if (a < 0.5f) {
-      // threshold_low = uint32(a * fp32(2^33 - 2)); the constant rounds to 2^33 in fp32.
-      const uint32_t thr = __float2uint_rz(__fmul_rn(a, 8589934592.0f));
-      code = (rnd <= thr) ? 1u : 0u;
-    } else {
-      // threshold_high = uint32((2a - 1) * fp32(2^32 - 1)); the constant rounds to 2^32.
-      const uint32_t thr = __float2uint_rz(__fmul_rn(__fadd_rn(__fmul_rn(a, 2.0f), -1.0f), 4294967296.0f));
-      code = (rnd <= thr) ? 2u : 1u;
-    }
-  } else {
-    uint32_t n = qx + (uint32_t)((1 - 127) << 23) + (rnd & 0x3FFFFFu);
-    code = (n >> 22) & 0xFFu;
-  }
-  return (code | (s >> 28)) & 0xFFu;
+  // Branch-free; every arm is a handful of instructions and the selects keep the warp converged.
+  const uint32_t vb = f2u(v);
+  const uint32_t ab = vb & 0x7FFFFFFFu;
+  const float a = u2f(ab);
+  // normal range [1, 6): add 22 random bits below the kept mantissa bit, rebias, truncate
+  const uint32_t cn = (ab + (rnd & 0x3FFFFFu) - (126u << 23)) >> 22;
+  // E2M1-subnormal range [0, 1): 2a = k + frac with k in {0, 1}; the reference compares the random
+  // word with uint32(a * fp32(2^33 - 2)) for a < 0.5 and with uint32((2a - 1) * fp32(2^32 - 1))
+  // otherwise; both constants round to powers of two in fp32, so both thresholds are
+  // trunc(frac * 2^32), and the codes are k + (rnd <= threshold).
+  const float a2 = __fadd_rn(a, a);
+  const bool k = a2 >= 1.0f;
+  const float frac = k ? __fadd_rn(a2, -1.0f) : a2;
+  const uint32_t thr = __float2uint_rz(__fmul_rn(frac, 4294967296.0f));
+  const uint32_t cd = (rnd <= thr ? 1u : 0u) + (k ? 1u : 0u);
+  uint32_t code = a < 1.0f ? cd : cn;
+  code = a >= 6.0f ? 7u : code;
+  return (code & 0xFu) | ((vb >> 28) & 8u);
 }
 
 // E2M1 decode to fp32 (alto/kernels/fp4/fp4_common/triton_fp4_ops.py:100-132).

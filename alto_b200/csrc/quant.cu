@@ -93,6 +93,19 @@ __device__ __forceinline__ uint32_t fp4_pair(float v0, float v1, uint32_t r0, ui
   return e2m1_sr_bits(v0, r0) | (e2m1_sr_bits(v1, r1) << 4);
 }
 
+// Quotient and remainder with a 32-bit divide whenever the operands fit (a 64-bit divide costs
+// several dozen instructions per task).
+__device__ __forceinline__ void divmod_fast(int64_t t, int64_t d, int64_t* q, int64_t* r) {
+  if ((((uint64_t)t | (uint64_t)d) >> 32) == 0) {
+    const uint32_t qq = (uint32_t)t / (uint32_t)d;
+    *q = qq;
+    *r = (uint32_t)t - qq * (uint32_t)d;
+  } else {
+    *q = t / d;
+    *r = t - *q * d;
+  }
+}
+
 __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t w) {
   return __vmaxu2(acc, w & 0x7FFF7FFFu);
 }
@@ -130,8 +143,8 @@ __global__ void __launch_bounds__(256) quantize_rowwise_kernel(RowwiseArgs a) {
   const int64_t half_cols = a.cols >> 1;
 
   for (int64_t task = warp0; task < n_tasks; task += n_warps) {
-    const int64_t row = task / chunks_per_row;
-    const int64_t chunk = task - row * chunks_per_row;
+    int64_t row, chunk;
+    divmod_fast(task, chunks_per_row, &row, &chunk);
     const int64_t col = (chunk << 9) + lane * 16;
     const bool active = col < a.cols;
 
@@ -756,11 +769,18 @@ __global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
     const int64_t vec = IN_BF16 ? 8 : 4;
     const int64_t vec_per_row = a.cols / vec;
     const int64_t total = a.rows * vec_per_row;
+    const bool dense = a.ld == a.cols;  // contiguous rows: no index arithmetic per load
+#pragma unroll 4
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
-      const int64_t row = i / vec_per_row, cv = i - row * vec_per_row;
+      int64_t off = i * vec;
+      if (!dense) {
+        int64_t row, cv;
+        divmod_fast(i, vec_per_row, &row, &cv);
+        off = row * a.ld + cv * vec;
+      }
       const uint4 w = __ldg(reinterpret_cast<const uint4*>(
-          reinterpret_cast<const uint8_t*>(a.x) + (row * a.ld + cv * vec) * (IN_BF16 ? 2 : 4)));
+          reinterpret_cast<const uint8_t*>(a.x) + off * (IN_BF16 ? 2 : 4)));
       if (IN_BF16) {
         uint32_t acc = absmax_bf16x2(0, w.x);
         acc = absmax_bf16x2(acc, w.y);
@@ -784,7 +804,8 @@ __global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
     const int64_t n_tasks = groups * col_tiles;
     const int64_t warp0 = (int64_t)blockIdx.x * 8 + warp, n_warps = (int64_t)gridDim.x * 8;
     for (int64_t task = warp0; task < n_tasks; task += n_warps) {
-      const int64_t g = task / col_tiles, ct = task - g * col_tiles;
+      int64_t g, ct;
+      divmod_fast(task, col_tiles, &g, &ct);
       const int64_t c = (ct << 6) + 2 * lane;
       if (c >= a.cols) continue;
       float v0[16], v1[16];
@@ -879,7 +900,8 @@ __global__ void __launch_bounds__(256) dequantize_kernel(DequantArgs a) {
   const int64_t nsc = a.cols / F::B;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / segs_per_row, sg = i - row * segs_per_row;
+    int64_t row, sg;
+    divmod_fast(i, segs_per_row, &row, &sg);
     const int64_t col = sg << 4;
     const int64_t srow = a.is_2d ? row / F::B : row;
     float s;
@@ -940,7 +962,8 @@ __global__ void __launch_bounds__(256) rht_kernel(RhtArgs a) {
   const int64_t n_tasks = groups * col_tiles;
   const int64_t warp0 = (int64_t)blockIdx.x * 8 + warp, n_warps = (int64_t)gridDim.x * 8;
   for (int64_t task = warp0; task < n_tasks; task += n_warps) {
-    const int64_t g = task / col_tiles, ct = task - g * col_tiles;
+    int64_t g, ct;
+    divmod_fast(task, col_tiles, &g, &ct);
     const int64_t c = (ct << 6) + 2 * lane;
     if (c >= a.cols) continue;
     float v0[16], v1[16];
