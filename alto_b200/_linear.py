@@ -17,6 +17,7 @@ consumes and nothing is dequantised.
 from __future__ import annotations
 
 import contextlib
+import os
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -191,6 +192,34 @@ def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, r
     return g_n, g_m
 
 
+# ---------------------------------------------------------------------------------------
+# overlap of quantizers (ALU work) with GEMMs (tensor-core work)
+# ---------------------------------------------------------------------------------------
+#: The persistent GEMM leaves the SMs' issue slots and ALUs almost idle, and a quantizer that
+#: needs little shared memory can be resident next to it.  With OVERLAP on, the quantizer whose
+#: output is not needed by the next GEMM is launched on a side stream right after that GEMM:
+#:   forward : fprop GEMM   ||  X along M (needed only in backward)
+#:   backward: wgrad GEMM   ||  dY along N (needed by the dgrad GEMM that follows)
+#: Results are identical; only the launch order differs.  ALTO_B200_OVERLAP=0 turns it off.
+OVERLAP = os.environ.get("ALTO_B200_OVERLAP", "1") != "0"
+_side_streams = {}
+
+
+def _side_stream(device: torch.device) -> torch.cuda.Stream:
+    s = _side_streams.get(device.index)
+    if s is None:
+        s = torch.cuda.Stream(device=device)
+        _side_streams[device.index] = s
+    return s
+
+
+def _keep_for(stream, *tensors) -> None:
+    """Tell the caching allocator that ``tensors`` are also in use on ``stream``."""
+    for t in tensors:
+        if t is not None:
+            t.record_stream(stream)
+
+
 def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock_w, use_sr_grad, use_outer_scale,
                    hadamard_transform):
     """Shared body of the three autograd ``forward`` methods."""
@@ -203,9 +232,33 @@ def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock
     N = w2.shape[0]
     check_dims(name, M, K, N)
     rht = hadamard_transform.device_params() if (hadamard_transform is not None and not use_2dblock_x) else None
-    x_k, x_m, w_k, w_t = forward_operands(x2, w2, fmt, use_2dblock_x=use_2dblock_x, use_2dblock_w=use_2dblock_w,
-                                          use_outer_scale=use_outer_scale, rht=rht)
-    y = gemm(x_k, w_k, x.dtype)
+    ctx.xm_ready = None
+    if OVERLAP and not use_2dblock_x:
+        main = torch.cuda.current_stream(x2.device)
+        side = _side_stream(x2.device)
+        ox = outer_scales(x2, use_outer_scale, rht)
+        ow = outer_scales(w2, use_outer_scale, None)
+        x_k = quant_rows(x2, fmt, None if ox is None else ox[0:1], RTN)
+        if use_2dblock_w:
+            w_k, w_t = quant_2d(w2, fmt, None if ow is None else ow[0:1], True)
+        else:
+            w_k = quant_rows(w2, fmt, None if ow is None else ow[0:1], RTN)
+            w_t = quant_cols(w2, fmt, None if ow is None else ow[0:1], None, RTN)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        y = gemm(x_k, w_k, x.dtype)  # submitted first so that its CTAs take the SMs first
+        o_m = None if ox is None else (ox[1:2] if rht is not None else ox[0:1])
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            x_m = quant_cols(x2, fmt, o_m, rht, RTN)
+        ctx.xm_ready = torch.cuda.Event()
+        ctx.xm_ready.record(side)
+        _keep_for(side, x2, ox)
+        _keep_for(main, x_m.codes, x_m.scales)
+    else:
+        x_k, x_m, w_k, w_t = forward_operands(x2, w2, fmt, use_2dblock_x=use_2dblock_x, use_2dblock_w=use_2dblock_w,
+                                              use_outer_scale=use_outer_scale, rht=rht)
+        y = gemm(x_k, w_k, x.dtype)
     extra_x = [x_m.outer] if x_m.outer is not None else []
     extra_w = [w_t.outer] if w_t.outer is not None else []
     ctx.save_for_backward(x_m.codes, x_m.scales, *extra_x, w_t.codes, w_t.scales, *extra_w)
@@ -230,12 +283,37 @@ def linear_backward(ctx, grad_output):
     w_t = Operand(wc, ws, wo, K, N, ctx.fmt)
     original_shape = grad_output.shape
     g2 = as_2d_rows(grad_output)
+    main = torch.cuda.current_stream(g2.device)
+    if ctx.xm_ready is not None:
+        main.wait_event(ctx.xm_ready)
+    need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+    grad_inputs = grad_weights = None
+    if OVERLAP and not ctx.use_2dblock_x and need_dx and need_dw:
+        fmt, rht = ctx.fmt, ctx.rht
+        side = _side_stream(g2.device)
+        og = outer_scales(g2, ctx.use_outer_scale, rht)
+        sr_n = sr_args(ctx.use_sr_grad, "dy_n", M, N, g2.device)  # drawn in the same order as without overlap
+        sr_m = sr_args(ctx.use_sr_grad, "dy_m", N, M, g2.device)
+        o_m = None if og is None else (og[1:2] if rht is not None else og[0:1])
+        g_m = quant_cols(g2, fmt, o_m, rht, sr_m)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        grad_weights = gemm(g_m, x_m, grad_output.dtype)  # wgrad first; dY along N is quantised beside it
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            g_n = quant_rows(g2, fmt, None if og is None else og[0:1], sr_n)
+        done = torch.cuda.Event()
+        done.record(side)
+        _keep_for(side, g2, og, sr_n.get("rand_bits"))
+        _keep_for(main, g_n.codes, g_n.scales)
+        main.wait_event(done)
+        grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
+        return grad_inputs, grad_weights
     g_n, g_m = backward_operands(g2, ctx.fmt, use_2dblock_x=ctx.use_2dblock_x, use_sr_grad=ctx.use_sr_grad,
                                  use_outer_scale=ctx.use_outer_scale, rht=ctx.rht)
-    grad_inputs = grad_weights = None
-    if ctx.needs_input_grad[0]:
+    if need_dx:
         grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
-    if ctx.needs_input_grad[1]:
+    if need_dw:
         grad_weights = gemm(g_m, x_m, grad_output.dtype)
     return grad_inputs, grad_weights
 

@@ -243,4 +243,35 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t
   out[3] = c3;
 }
 
+// Same generator with the ten round keys precomputed on the host (they depend on the seed only),
+// so that each round is two wide multiplies and two three-input XORs; counter words 2 and 3 are 0.
+struct PhiloxKeys {
+  uint32_t k[20];  // k[2i], k[2i+1]: key of round i
+};
+static inline void philox_make_keys(uint64_t seed, PhiloxKeys* pk) {
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  for (int i = 0; i < 10; ++i) {
+    pk->k[2 * i] = k0;
+    pk->k[2 * i + 1] = k1;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+__device__ __forceinline__ void philox4x32_10_keys(uint32_t c0, uint32_t c1, const PhiloxKeys& pk, uint32_t out[4]) {
+  const uint32_t A = 0xD2511F53u, B = 0xCD9E8D57u;
+  uint32_t c2 = 0u, c3 = 0u;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint64_t pb = (uint64_t)B * c2, pa = (uint64_t)A * c0;
+    c0 = (uint32_t)(pb >> 32) ^ c1 ^ pk.k[2 * i];
+    c2 = (uint32_t)(pa >> 32) ^ c3 ^ pk.k[2 * i + 1];
+    c1 = (uint32_t)pb;
+    c3 = (uint32_t)pa;
+  }
+  out[0] = c0;
+  out[1] = c1;
+  out[2] = c2;
+  out[3] = c3;
+}
+
 }  // namespace altob200

@@ -127,6 +127,7 @@ struct RowwiseArgs {
   const float* outer;
   const uint32_t* rand_bits;
   uint64_t philox_seed, philox_offset;
+  PhiloxKeys pk;
 };
 
 template <int FMT, bool IN_BF16, int ROUND>
@@ -210,8 +211,7 @@ __global__ void __launch_bounds__(256) quantize_rowwise_kernel(RowwiseArgs a) {
       for (int i = 0; i < 4; ++i) {
         uint32_t o[4];
         const uint64_t ctr = q0 + i;
-        philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u, (uint32_t)a.philox_seed,
-                      (uint32_t)(a.philox_seed >> 32), o);
+        philox4x32_10_keys((uint32_t)ctr, (uint32_t)(ctr >> 32), a.pk, o);
         r0[2 * i] = o[0]; r1[2 * i] = o[1]; r0[2 * i + 1] = o[2]; r1[2 * i + 1] = o[3];
       }
     }
@@ -294,6 +294,7 @@ struct ColwiseArgs {
   const float* outer;
   const uint32_t* rand_bits;  // [2][cols][rows/2]
   uint64_t philox_seed, philox_offset;
+  PhiloxKeys pk;
   RhtParams rht;
 };
 
@@ -430,12 +431,10 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
           for (int i = 0; i < 4; ++i) {
             uint32_t o[4];
             uint64_t ctr = a.philox_offset + (p0 >> 1) + i;
-            philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u, (uint32_t)a.philox_seed,
-                          (uint32_t)(a.philox_seed >> 32), o);
+            philox4x32_10_keys((uint32_t)ctr, (uint32_t)(ctr >> 32), a.pk, o);
             r0[4 * i] = o[0]; r0[4 * i + 1] = o[1]; r0[4 * i + 2] = o[2]; r0[4 * i + 3] = o[3];
             ctr = a.philox_offset + (p1 >> 1) + i;
-            philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u, (uint32_t)a.philox_seed,
-                          (uint32_t)(a.philox_seed >> 32), o);
+            philox4x32_10_keys((uint32_t)ctr, (uint32_t)(ctr >> 32), a.pk, o);
             r1[4 * i] = o[0]; r1[4 * i + 1] = o[1]; r1[4 * i + 2] = o[2]; r1[4 * i + 3] = o[3];
           }
         }
@@ -1162,6 +1161,7 @@ int altob200_quantize_rowwise(const void* x, int64_t rows, int64_t cols, int64_t
   a.ncol_tiles = ceil_div(cols / B, 4);
   a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
   a.philox_seed = p->philox_seed; a.philox_offset = p->philox_offset;
+  philox_make_keys(p->philox_seed, &a.pk);
   int rc = clear_packed_if_padded(scale_packed, rows, cols / B, st);
   if (rc != ALTOB200_OK) return rc;
   const int rounding = p->rounding;
@@ -1191,6 +1191,7 @@ int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t
   a.ncol_tiles = ceil_div(rows / B, 4);
   a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
   a.philox_seed = p->philox_seed; a.philox_offset = p->philox_offset;
+  philox_make_keys(p->philox_seed, &a.pk);
   int rc = fill_rht(&a.rht, p->rht_n, p->rht_perm, p->rht_sign);
   if (rc != ALTOB200_OK) return rc;
   rc = clear_packed_if_padded(scale_packed, cols, rows / B, st);
