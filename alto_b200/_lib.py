@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "altob200_packed_scale_bytes",
     "altob200_status_read",
     "altob200_amax",
+    "altob200_amax_noalloc",
     "altob200_quantize_rowwise",
     "altob200_quantize_colwise",
     "altob200_quantize_2d",
@@ -81,6 +82,8 @@ def _declare(lib):
     lib.altob200_status_read.argtypes = [vp, C.POINTER(i32)]
     lib.altob200_amax.restype = C.c_int
     lib.altob200_amax.argtypes = [vp, i32, i64, i64, i64, i32, C.POINTER(i32), C.POINTER(i32), vp, vp, vp, vp]
+    lib.altob200_amax_noalloc.restype = C.c_int
+    lib.altob200_amax_noalloc.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp]
     for name in ("altob200_quantize_rowwise", "altob200_quantize_colwise"):
         f = getattr(lib, name)
         f.restype = C.c_int
@@ -210,6 +213,20 @@ def amax(x: torch.Tensor, amax_bits: torch.Tensor, outer_scale: Optional[torch.T
                                rht.n if rht else 0, rht._perm_c if rht else None, rht._sign_c if rht else None,
                                amax_bits.data_ptr(), _ptr(outer_scale), scratch.data_ptr(), _stream()),
            "altob200_amax")
+
+
+NOALLOC_MAX_BYTES = 512 << 20
+
+
+def amax_noalloc(x: torch.Tensor, amax_bits: torch.Tensor, outer_scale: Optional[torch.Tensor]) -> None:
+    """Tensor amax (and NVFP4 outer scale) through the entry point that needs no scratch buffer from
+    the caller and allocates nothing: its working memory is a fixed array inside the library.  Inputs
+    above NOALLOC_MAX_BYTES are refused; calls that may overlap on one GPU must not be issued."""
+    _require_cuda(x, amax_bits, outer_scale)
+    assert x.dim() == 2 and x.stride(1) == 1
+    _check(lib().altob200_amax_noalloc(x.data_ptr(), _dt(x.dtype), x.shape[0], x.shape[1], x.stride(0),
+                                       amax_bits.data_ptr(), _ptr(outer_scale), _stream()),
+           "altob200_amax_noalloc")
 
 
 def quantize_rowwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, rounding=ROUND_RTN,

@@ -878,6 +878,99 @@ __global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
 }
 
 // =======================================================================================
+// Tensor amax without any caller- or library-allocated scratch
+// =======================================================================================
+// Partial maxima (one word per block) and the completion counter live in this file-scope array.
+// Every GPU that loads the library holds these bytes until the process exits.
+constexpr int NOALLOC_MAX_BLOCKS = 8192;
+constexpr int NOALLOC_VEC_PER_THREAD = 16;  // 16-byte vectors per thread -> 64 KiB of input per block
+struct NoallocScratch {
+  uint32_t counter;
+  uint32_t pad[63];
+  uint32_t partial[NOALLOC_MAX_BLOCKS];
+};
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoallocScratch)];
+
+struct AmaxNoallocArgs {
+  const void* x;
+  int64_t rows, cols, ld;
+  uint32_t* amax_bits;   // [1]
+  float* outer_scale;    // [1] or NULL
+  NoallocScratch* scratch;
+};
+
+template <bool IN_BF16>
+__global__ void __launch_bounds__(256) amax_noalloc_kernel(AmaxNoallocArgs a) {
+  __shared__ uint32_t s_red[8];
+  __shared__ bool s_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t vec = IN_BF16 ? 8 : 4;
+  const int64_t vec_per_row = a.cols / vec;
+  const int64_t total = a.rows * vec_per_row;
+  const bool dense = a.ld == a.cols;
+  uint32_t am = 0;
+  const int64_t base = (int64_t)blockIdx.x * (256 * NOALLOC_VEC_PER_THREAD) + threadIdx.x;
+#pragma unroll 4
+  for (int j = 0; j < NOALLOC_VEC_PER_THREAD; ++j) {
+    const int64_t i = base + (int64_t)j * 256;
+    if (i >= total) break;
+    int64_t off = i * vec;
+    if (!dense) {
+      int64_t row, cv;
+      divmod_fast(i, vec_per_row, &row, &cv);
+      off = row * a.ld + cv * vec;
+    }
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(
+        reinterpret_cast<const uint8_t*>(a.x) + off * (IN_BF16 ? 2 : 4)));
+    if (IN_BF16) {
+      uint32_t acc = absmax_bf16x2(0, w.x);
+      acc = absmax_bf16x2(acc, w.y);
+      acc = absmax_bf16x2(acc, w.z);
+      acc = absmax_bf16x2(acc, w.w);
+      const uint32_t m = fold_bf16x2(acc) << 16;
+      am = m > am ? m : am;
+    } else {
+      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t b = ws[q] & 0x7FFFFFFFu;
+        am = b > am ? b : am;
+      }
+    }
+  }
+  am = warp_max_u32(am);
+  if (lane == 0) s_red[warp] = am;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t m = 0;
+    for (int i = 0; i < 8; ++i) m = s_red[i] > m ? s_red[i] : m;
+    a.scratch->partial[blockIdx.x] = m;
+    __threadfence();
+    s_last = atomicAdd(&a.scratch->counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_last) {  // the last block to finish folds every block's partial maximum
+    __threadfence();
+    uint32_t m = 0;
+    for (unsigned i = threadIdx.x; i < gridDim.x; i += 256) {
+      const uint32_t p = *reinterpret_cast<volatile uint32_t*>(&a.scratch->partial[i]);
+      m = p > m ? p : m;
+    }
+    m = warp_max_u32(m);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t f = 0;
+      for (int i = 0; i < 8; ++i) f = s_red[i] > f ? s_red[i] : f;
+      a.amax_bits[0] = f;
+      if (a.outer_scale != nullptr) a.outer_scale[0] = outer_from_amax_bits(f);
+      a.scratch->counter = 0u;  // ready for the next call
+    }
+  }
+}
+
+// =======================================================================================
 // Dequantizer (row-major codes, plain scales)
 // =======================================================================================
 struct DequantArgs {
@@ -1312,6 +1405,42 @@ int altob200_rht(const void* x, int32_t dtype, int64_t rows, int64_t cols, int64
   if (blocks > cap) blocks = cap;
   if (dtype == ALTOB200_DT_BF16) rht_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(a);
   else rht_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+int altob200_amax_noalloc(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, int64_t ld,
+                          uint32_t* amax_bits, float* outer_scale, void* stream) {
+  if (x == nullptr || amax_bits == nullptr) return ALTOB200_EINVAL_SHAPE;
+  if (rows <= 0 || cols <= 0 || cols % 8 != 0 || ld < cols) return ALTOB200_EINVAL_SHAPE;
+  if (in_dtype != ALTOB200_DT_BF16 && in_dtype != ALTOB200_DT_F32) return ALTOB200_EUNSUPPORTED;
+  const int esz = in_dtype == ALTOB200_DT_BF16 ? 2 : 4;
+  if (!aligned16(x) || (ld * esz) % 16 != 0) return ALTOB200_EINVAL_ALIGN;
+  // the fixed array has one slot per block of 64 KiB of input
+  if (rows > ALTOB200_NOALLOC_MAX_BYTES / esz / cols) return ALTOB200_ELIMIT;
+  // Set-up, once per device, with that device current: the array's name is only a host-side
+  // handle, the kernel needs the device address behind it.
+  static void* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  ALTOB200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ALTOB200_ELIMIT;
+  if (scratch_of_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    ALTOB200_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    if (ptr == nullptr) return ALTOB200_ECUDA;
+    scratch_of_device[dev] = ptr;
+  }
+  NoallocScratch* scratch = reinterpret_cast<NoallocScratch*>(scratch_of_device[dev]);
+  cudaStream_t st = (cudaStream_t)stream;
+  // the counter must start at zero even if an earlier launch never finished
+  ALTOB200_CUDA_CHECK(cudaMemsetAsync(&scratch->counter, 0, sizeof(uint32_t), st));
+  AmaxNoallocArgs a;
+  a.x = x; a.rows = rows; a.cols = cols; a.ld = ld;
+  a.amax_bits = amax_bits; a.outer_scale = outer_scale; a.scratch = scratch;
+  const int64_t total_vec = rows * (cols / (16 / esz));
+  const int64_t blocks = ceil_div(total_vec, 256 * NOALLOC_VEC_PER_THREAD);
+  if (blocks > NOALLOC_MAX_BLOCKS) return ALTOB200_ELIMIT;
+  if (in_dtype == ALTOB200_DT_BF16) amax_noalloc_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(a);
+  else amax_noalloc_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 

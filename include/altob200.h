@@ -125,6 +125,35 @@ int altob200_amax(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, i
                   uint32_t* amax_bits, float* outer_scale, void* scratch, void* stream);
 
 /*
+ * Absolute maximum of a [rows, cols] matrix (and the NVFP4 outer scale derived from
+ * it) for callers that must not allocate device memory and cannot hand over a
+ * scratch buffer of their own -- for example a step that runs inside a memory pool
+ * which is already fully planned, a plugin living in another runtime's address
+ * space, or an inference server whose allocator is frozen after start-up.  This
+ * entry point has no counterpart in the reference; it computes what altob200_amax
+ * computes without a Hadamard transform:
+ *
+ *  amax_bits[0]   <- max |x| as an fp32 bit pattern
+ *  outer_scale[0] <- max(amax / (448 * 6), 1e-30) when non-NULL
+ *
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.  Its working
+ * memory (one partial maximum per thread block and a completion counter, about
+ * 33 KiB) is a fixed array inside the library's device image; every GPU that loads
+ * the library keeps those bytes until the process exits.  Consequences:
+ *  - the input is limited to ALTOB200_NOALLOC_MAX_BYTES (one array slot per 64 KiB
+ *    of input); larger inputs are refused with ALTOB200_ELIMIT before any launch;
+ *  - the first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current); make that first call before
+ *    starting any stream capture;
+ *  - all calls on one device share the array: two calls whose kernels may overlap on
+ *    the GPU (different streams, no dependency between them) race and give wrong
+ *    results; calls on one stream are safe, and each call resets what it needs.
+ */
+#define ALTOB200_NOALLOC_MAX_BYTES (512ll << 20)
+int altob200_amax_noalloc(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, int64_t ld,
+                          uint32_t* amax_bits, float* outer_scale, void* stream);
+
+/*
  * 1D block quantisation along the last (contiguous) axis of x[rows, cols].
  * Replaces convert_to_mxfp4 / convert_to_nvfp4 / convert_to_mxfp8 with axis=-1,
  * is_2d_block=False (alto/kernels/fp4/mxfp4/mxfp_quantization.py:411-484,
