@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = (
     "altob200_rht",
     "altob200_gemm_blockscaled",
     "altob200_grouped_gemm_blockscaled",
+    "altob200_grouped_gemm_wgrad_blockscaled",
 )
 
 
@@ -101,6 +102,13 @@ def _declare(lib):
                                                       i32, vp, i64, vp]
 
 
+def _declare_more(lib):
+    vp, i32, i64 = C.c_void_p, C.c_int32, C.c_int64
+    lib.altob200_grouped_gemm_wgrad_blockscaled.restype = C.c_int
+    lib.altob200_grouped_gemm_wgrad_blockscaled.argtypes = [i32, i32, i64, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp,
+                                                            i32, vp, i64, vp]
+
+
 def lib():
     """The loaded library; raises if it has not been built."""
     global _lib
@@ -113,6 +121,7 @@ def lib():
                         "(there is no CPU or PyTorch fallback for this path)")
                 handle = C.CDLL(str(LIB_PATH))
                 _declare(handle)
+                _declare_more(handle)
                 _lib = handle
     return _lib
 
@@ -298,3 +307,16 @@ def grouped_gemm_blockscaled(fmt_a, fmt_b, M, N, K, num_experts, a_codes, a_scal
                                                    group_expert.data_ptr(), _ptr(alpha_a), _ptr(alpha_b),
                                                    _dt(out.dtype), out.data_ptr(), out.stride(0), _stream()),
            "altob200_grouped_gemm_blockscaled")
+
+
+def grouped_gemm_wgrad_blockscaled(fmt_a, fmt_b, M, N, K, num_experts, a_codes, a_scales, b_codes, b_scales, k_offs,
+                                   out, alpha_a=None, alpha_b=None) -> None:
+    """out[e] = A[:, range_e] @ B[:, range_e]^T with range_e = [k_offs[e-1], k_offs[e]) along the shared
+    reduction axis of length K; out is [num_experts, M, N]."""
+    _require_cuda(a_codes, a_scales, b_codes, b_scales, k_offs, out, alpha_a, alpha_b)
+    assert out.dim() == 3 and out.stride(2) == 1 and out.stride(0) == M * out.stride(1)
+    assert k_offs.dtype == torch.int32 and k_offs.numel() == num_experts
+    _check(lib().altob200_grouped_gemm_wgrad_blockscaled(
+        fmt_a, fmt_b, M, N, K, num_experts, a_codes.data_ptr(), a_scales.data_ptr(), b_codes.data_ptr(),
+        b_scales.data_ptr(), k_offs.data_ptr(), _ptr(alpha_a), _ptr(alpha_b), _dt(out.dtype), out.data_ptr(),
+        out.stride(1), _stream()), "altob200_grouped_gemm_wgrad_blockscaled")

@@ -74,6 +74,10 @@ struct GemmArgs {
   int num_experts;
   const int32_t* group_expert;
   int64_t sfb_expert_stride;
+  // K-range mode (k_offs != NULL): batch entry e reduces over elements [k_offs[e-1], k_offs[e]) of
+  // the shared operands and writes D[e] (grouped wgrad); `num_batches` entries, ranges multiples of 128
+  const int32_t* k_offs;
+  int num_batches;
   uint32_t idesc[4];     // instruction descriptors of the four MMAs of a stage
   // profiling switches (env ALTOB200_GEMM_DEBUG, results are then WRONG): 1 = copy scales only in the
   // first stage of a tile, 2 = skip the global stores, 4 = stop loading operands once the ring is full
@@ -153,6 +157,12 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
 __device__ __forceinline__ void tma_store_2d(const void* smem_src, const CUtensorMap* map, int32_t x, int32_t y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const void* smem_src, const CUtensorMap* map, int32_t x, int32_t y,
+                                             int32_t z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -255,6 +265,58 @@ struct Cfg {
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
+// What one output tile needs, identically derived by every role of the CTA.
+struct TileInfo {
+  int64_t mb, nb;      // tile coordinates
+  int batch;           // z coordinate of the output (K-range mode), else 0
+  int k_stages;        // stages of 128 bytes of K
+  int last_mmas;       // MMAs issued in the last stage (a K range may end half-way through a stage)
+  int64_t k_byte0;     // first byte of the K range in an operand row
+  int64_t sf_tile0;    // first 512-byte scale tile of the K range
+  int64_t b_row0;      // first row of the B tile in its tensor map
+  const uint8_t* sfb;  // packed scales of B for this tile's expert
+  bool skip;           // nothing to contract: the epilogue writes zeros
+};
+
+template <int KIND, int BN>
+__device__ __forceinline__ TileInfo decode_tile(const GemmArgs& args, int64_t tile, int64_t tiles_m, int64_t tiles_n,
+                                                int k_stages_dense) {
+  TileInfo t;
+  const int64_t per_batch = tiles_m * tiles_n;
+  const int64_t e = args.k_offs != nullptr ? tile / per_batch : 0;
+  const int64_t rem = tile - e * per_batch;
+  t.mb = rem % tiles_m;
+  t.nb = rem / tiles_m;
+  t.batch = (int)e;
+  t.k_stages = k_stages_dense;
+  t.last_mmas = 4;
+  t.k_byte0 = 0;
+  t.sf_tile0 = 0;
+  t.b_row0 = t.nb * BN;
+  t.sfb = args.sfb;
+  t.skip = false;
+  if (args.k_offs != nullptr) {
+    constexpr int EPB = Kind<KIND>::ELEMS_PER_BYTE;
+    const int64_t k0 = e > 0 ? __ldg(args.k_offs + e - 1) : 0;
+    const int64_t k1 = __ldg(args.k_offs + e);
+    const int64_t bytes = (k1 - k0) / EPB;
+    t.skip = bytes <= 0;
+    t.k_stages = (int)((bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES);
+    const int64_t tail = bytes - (int64_t)(t.k_stages - 1) * STAGE_K_BYTES;
+    t.last_mmas = (int)((tail + 31) / 32);
+    t.k_byte0 = k0 / EPB;
+    t.sf_tile0 = k0 / (Kind<KIND>::BLOCK * 4);
+  } else if (args.num_experts > 0) {
+    const int ex = __ldg(args.group_expert + t.mb);
+    t.skip = ex < 0;
+    if (!t.skip) {
+      t.b_row0 += (int64_t)ex * args.N;
+      t.sfb += (int64_t)ex * args.sfb_expert_stride;
+    }
+  }
+  return t;
+}
+
 template <int KIND, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -276,7 +338,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t tiles_m = (args.M + BM - 1) / BM;
   const int64_t tiles_n = (args.N + BN - 1) / BN;
-  const int64_t n_tiles = tiles_m * tiles_n;
+  const int64_t n_tiles = tiles_m * tiles_n * (args.k_offs != nullptr ? args.num_batches : 1);
   const int k_stages = (int)((args.k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES);
   const int64_t n_row_blocks = (args.N + 127) / 128;
 
@@ -316,39 +378,34 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       uint32_t it = 0;
       bool alive = true;
       for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-        const int64_t mb = tile % tiles_m, nb = tile / tiles_m;
-        int64_t b_row0 = nb * BN;          // row of the B tensor map
-        const uint8_t* sfb = args.sfb;
-        if (args.num_experts > 0) {
-          const int e = __ldg(args.group_expert + mb);
-          if (e < 0) continue;             // padding group: no loads, epilogue writes zeros
-          b_row0 += (int64_t)e * args.N;
-          sfb += (int64_t)e * args.sfb_expert_stride;
-        }
-        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+        const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+        if (ti.skip) continue;  // nothing to load: the epilogue writes zeros
+        const int64_t mb = ti.mb, nb = ti.nb;
+        // 128-row blocks of B that exist (the last tile of a ragged N has fewer)
+        int nb_valid = (int)(n_row_blocks - nb * C::NB);
+        if (nb_valid > C::NB) nb_valid = C::NB;
+        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int s = it % C::STAGES;
           if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 1)) { alive = false; break; }
           uint8_t* st = smem + s * C::STAGE_BYTES;
-          int64_t sf_tiles = args.nct - (int64_t)ks * C::SF_TILES;
+          const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
+          int64_t sf_tiles = args.nct - cb0;
           if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
           const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
-          // 128-row blocks of B that exist (the last tile of a ragged N has fewer)
-          int nb_valid = (int)(n_row_blocks - nb * C::NB);
-          if (nb_valid > C::NB) nb_valid = C::NB;
           if ((args.debug & 4) && it >= (uint32_t)C::STAGES) {
             mbar_arrive(&full_bar[s]);
             continue;
           }
+          const int32_t kx = (int32_t)(ti.k_byte0 + (int64_t)ks * STAGE_K_BYTES);
           mbar_expect_tx(&full_bar[s], C::A_BYTES + C::B_BYTES + sf_bytes * (1 + nb_valid));
-          tma_load_2d(st, &tmap_a, ks * STAGE_K_BYTES, (int32_t)(mb * BM), &full_bar[s]);
-          tma_load_2d(st + C::A_BYTES, &tmap_b, ks * STAGE_K_BYTES, (int32_t)b_row0, &full_bar[s]);
-          const int64_t cb0 = (int64_t)ks * C::SF_TILES;
+          tma_load_2d(st, &tmap_a, kx, (int32_t)(mb * BM), &full_bar[s]);
+          tma_load_2d(st + C::A_BYTES, &tmap_b, kx, (int32_t)ti.b_row0, &full_bar[s]);
           bulk_load(st + C::A_BYTES + C::B_BYTES, args.sfa + (mb * args.nct + cb0) * 512, sf_bytes, &full_bar[s]);
 #pragma unroll
           for (int j = 0; j < C::NB; ++j)
             if (j < nb_valid)
               bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + j * C::SFA_BYTES,
-                        sfb + ((nb * C::NB + j) * args.nct + cb0) * 512, sf_bytes, &full_bar[s]);
+                        ti.sfb + ((nb * C::NB + j) * args.nct + cb0) * 512, sf_bytes, &full_bar[s]);
         }
       }
     }
@@ -360,12 +417,14 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       const uint32_t smem_base = smem_u32(smem);
       const uint32_t idesc[4] = {args.idesc[0], args.idesc[1], args.idesc[2], args.idesc[3]};
       for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-        if (args.num_experts > 0 && __ldg(args.group_expert + (tile % tiles_m)) < 0) continue;
+        const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+        if (ti.skip) continue;
         const int acc = tile_it % C::ACC_STAGES;
         if (!mbar_wait(&acc_empty[acc], ((tile_it / C::ACC_STAGES) & 1) ^ 1, abort_flag, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+          const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
           const int s = it % C::STAGES;
           if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 3)) { alive = false; break; }
           if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 5)) { alive = false; break; }
@@ -380,6 +439,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             // MMA j covers bytes [32j, 32j+32) of the stage; its scale tile and byte offset
             // inside the tile depend on how many scales one MMA consumes.
             const int t = (KIND == KIND_NVF4) ? j : (KIND == KIND_MXF4 ? (j >> 1) : 0);
+            if (j < n_mma)
             tc_mma<KIND>(d_tmem, desc_of(DESC_SW128_HI, a_lo + 2 * j), desc_of(DESC_SW128_HI, b_lo + 2 * j), idesc[j],
                          (ks | j) != 0 ? 1u : 0u, sfa_t + t * 4, sfb_t + t * 4 * C::NB);
           }
@@ -398,8 +458,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     uint32_t it = 0;
     bool alive = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-      if (args.num_experts > 0 && __ldg(args.group_expert + (tile % tiles_m)) < 0) continue;
-      for (int ks = 0; ks < k_stages; ++ks, ++it) {
+      const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+      if (ti.skip) continue;
+      for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
         const int s = it % C::STAGES;
         if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 6)) { alive = false; break; }
         const uint8_t* sf = smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
@@ -436,9 +497,10 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const int n_chunks = BN / CH;
     uint32_t tile_it = 0, store_it = 0;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      const int64_t mb = tile % tiles_m, nb = tile / tiles_m;
+      const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+      const int64_t mb = ti.mb, nb = ti.nb;
       const int64_t row0 = mb * BM + quad * 32;
-      const bool pad_group = args.num_experts > 0 && __ldg(args.group_expert + mb) < 0;
+      const bool pad_group = ti.skip;
       const int acc = tile_it % C::ACC_STAGES;
       if (!pad_group) {
         if (!mbar_wait(&acc_full[acc], (tile_it / C::ACC_STAGES) & 1, abort_flag, 4)) break;
@@ -496,7 +558,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         __syncwarp();
         const int64_t col0 = nb * BN + (int64_t)cc * CH;
         if (lane == 0 && row0 < args.M && col0 < args.N && !(args.debug & 2)) {
-          tma_store_2d(epi + (warp - 2) * 8192 + buf_off, &tmap_d, (int32_t)col0, (int32_t)row0);
+          tma_store_3d(epi + (warp - 2) * 8192 + buf_off, &tmap_d, (int32_t)col0, (int32_t)row0, ti.batch);
           bulk_commit();
         }
       }
@@ -533,16 +595,17 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2D tensor map of the output [M, N] (bf16 or fp32): box of 32 rows x 128 bytes, 128-byte swizzle.
-static int make_tmap_out(CUtensorMap* m, void* base, int64_t M, int64_t N, int64_t ldd, bool bf16) {
+// 3D tensor map of the output [batches, M, N] (bf16 or fp32): box of 1 x 32 rows x 128 bytes,
+// 128-byte swizzle.  The batch coordinate keeps a ragged tile of one batch entry out of the next.
+static int make_tmap_out(CUtensorMap* m, void* base, int64_t batches, int64_t M, int64_t N, int64_t ldd, bool bf16) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return ALTOB200_ECUDA;
   const int esz = bf16 ? 2 : 4;
-  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-  cuuint64_t strides[1] = {(cuuint64_t)(ldd * esz)};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32u};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides,
+  cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)batches};
+  cuuint64_t strides[2] = {(cuuint64_t)(ldd * esz), (cuuint64_t)(M * ldd * esz)};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / esz), 32u, 1u};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? ALTOB200_OK : ALTOB200_ECUDA;
@@ -605,7 +668,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set = true;
   }
-  const int64_t tiles = ceil_div(args.M, BM) * ceil_div(args.N, BN);
+  const int64_t tiles = ceil_div(args.M, BM) * ceil_div(args.N, BN) * (args.k_offs != nullptr ? args.num_batches : 1);
   int64_t grid = sm_count_gemm();
   if (grid > tiles) grid = tiles;
   gemm_blockscaled_kernel<KIND, BN><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, td, args);
@@ -615,7 +678,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
 static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N, int64_t K, int32_t num_experts,
                        const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
                        const int32_t* group_expert, const float* alpha_a, const float* alpha_b,
-                       int32_t out_dtype, void* d, int64_t ldd, void* stream) {
+                       int32_t out_dtype, void* d, int64_t ldd, void* stream, const int32_t* k_offs = nullptr,
+                       int32_t num_batches = 1) {
   if (a_codes == nullptr || b_codes == nullptr || a_scales == nullptr || b_scales == nullptr || d == nullptr)
     return ALTOB200_EINVAL_SHAPE;
   int kind;
@@ -627,7 +691,7 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
   const int epb = kind == KIND_MXF8 ? 1 : 2;
   const int block = kind == KIND_NVF4 ? 16 : 32;
   if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || ldd < N) return ALTOB200_EINVAL_SHAPE;
-  if (num_experts > 0 && (M % 128 != 0 || group_expert == nullptr)) return ALTOB200_EINVAL_SHAPE;
+  if (num_experts > 0 && group_expert == nullptr) return ALTOB200_EINVAL_SHAPE;
   const int64_t k_bytes = K / epb;
   if (k_bytes % 16 != 0) return ALTOB200_EINVAL_SHAPE;
   const int osz = out_dtype == ALTOB200_DT_BF16 ? 2 : 4;
@@ -646,7 +710,7 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
   rc = make_tmap(&tb, b_codes, b_rows, k_bytes, BN);
   if (rc != ALTOB200_OK) return rc;
   CUtensorMap td;
-  rc = make_tmap_out(&td, d, M, N, ldd, out_dtype == ALTOB200_DT_BF16);
+  rc = make_tmap_out(&td, d, k_offs != nullptr ? num_batches : 1, M, N, ldd, out_dtype == ALTOB200_DT_BF16);
   if (rc != ALTOB200_OK) return rc;
 
   GemmArgs g;
@@ -657,6 +721,7 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
   g.d = d; g.ldd = ldd; g.out_bf16 = out_dtype == ALTOB200_DT_BF16;
   g.num_experts = num_experts; g.group_expert = group_expert;
   g.sfb_expert_stride = (int64_t)altob200_packed_scale_bytes(N, K / block);
+  g.k_offs = k_offs; g.num_batches = num_batches;
   for (int j = 0; j < 4; ++j) {
     const int sf_id = kind == KIND_NVF4 ? 0 : (kind == KIND_MXF4 ? (j & 1) * 2 : j);
     g.idesc[j] = make_idesc(kind, format_a, format_b, BN, sf_id);
@@ -701,6 +766,16 @@ int altob200_grouped_gemm_blockscaled(int32_t format_a, int32_t format_b, int64_
   if (num_experts <= 0) return ALTOB200_EINVAL_SHAPE;
   return gemm_common(format_a, format_b, M, N, K, num_experts, a_codes, a_scales, b_codes, b_scales,
                      group_expert, alpha_a, alpha_b, out_dtype, d, ldd, stream);
+}
+
+int altob200_grouped_gemm_wgrad_blockscaled(int32_t format_a, int32_t format_b, int64_t M, int64_t N, int64_t K,
+                                            int32_t num_experts, const void* a_codes, const void* a_scales,
+                                            const void* b_codes, const void* b_scales, const int32_t* k_offs,
+                                            const float* alpha_a, const float* alpha_b, int32_t out_dtype,
+                                            void* d, int64_t ldd, void* stream) {
+  if (num_experts <= 0 || k_offs == nullptr) return ALTOB200_EINVAL_SHAPE;
+  return gemm_common(format_a, format_b, M, N, K, 0, a_codes, a_scales, b_codes, b_scales, nullptr, alpha_a,
+                     alpha_b, out_dtype, d, ldd, stream, k_offs, num_experts);
 }
 
 int altob200_status_read(void* stream, int32_t detail[4]) {

@@ -1,0 +1,194 @@
+"""MoE grouped GEMMs with MXFP4 / NVFP4 / MXFP8 operands on B200.
+
+Boundary functions of the dispatch layer, same names and arguments as the reference:
+  _quantize_then_mxfp_scaled_grouped_mm   (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/functional.py:11-38)
+  _quantize_then_nvfp4_scaled_grouped_mm  (alto/kernels/fp4/nvfp4/nvfp_grouped_gemm/functional.py:134-167)
+  _quantize_then_mxfp8_scaled_grouped_mm  (alto/kernels/mxfp8/mxfp8_grouped_gemm/functional.py:48-81)
+
+``A`` is the routed token buffer [M_buf, K], sorted by expert; ``B`` the expert weights in dispatch
+layout [E, K, N]; ``offs`` the int32 cumulative token counts per expert, every count a multiple
+of 128 (ALIGN_SIZE_M) and ``offs[-1] <= M_buf``.  Rows past ``offs[-1]`` give zero output and zero
+gradient.  The three contractions
+
+    Y[m]  = X[m]  . W[e(m)]^T          dX[m] = dY[m] . W[e(m)]          dW[e] = sum_{m in e} dY[m]^T X[m]
+
+run on the block-scaled tensor-core kernel: forward and dgrad pick the expert's weight tile per
+128-row group, wgrad reduces over each expert's token range.  Operand preparation is that of
+the dense linear (alto/kernels/fp4/nvfp4/nvfp_grouped_gemm/autograd.py:66-250): whole-buffer
+quantisation, one tensorwise outer scale for the token buffer and one for the whole weight stack.
+Nothing synchronises with the host: expert ids per group are derived from ``offs`` on the device.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+from . import _linear as E
+from .hadamard import HadamardFactory, HadamardTransform
+from .nvfp4 import _check_scale_format, unwrap_weight_wrapper
+
+ALIGN_SIZE_M = 128
+
+
+def create_indices_from_offsets_nosync(m_offsets: torch.Tensor) -> torch.Tensor:
+    """Expert id of every routed row (alto/kernels/dsgemm_utils.py:97-112).  Unlike the reference's
+    helper of the same name this one is kept for API parity only: it needs ``offs[-1]`` on the host."""
+    total = int(m_offsets[-1])
+    rows = torch.arange(total, device=m_offsets.device, dtype=torch.int32)
+    return torch.bucketize(rows, m_offsets, right=True, out_int32=True)
+
+
+def group_experts_from_offsets(offs: torch.Tensor, m_buf: int) -> torch.Tensor:
+    """int32 [ceil(m_buf / 128)]: expert of each 128-row group, -1 for groups past ``offs[-1]``.
+    Computed on the device, no host synchronisation."""
+    n_groups = (m_buf + ALIGN_SIZE_M - 1) // ALIGN_SIZE_M
+    starts = torch.arange(n_groups, device=offs.device, dtype=torch.int32) * ALIGN_SIZE_M
+    e = torch.bucketize(starts, offs.to(torch.int32), right=True, out_int32=True)
+    return torch.where(e >= offs.numel(), torch.full_like(e, -1), e).contiguous()
+
+
+def _stack(ops):
+    """Per-expert operands -> one operand whose rows are the experts' rows stacked."""
+    first = ops[0]
+    codes = torch.stack([o.codes for o in ops]).reshape(-1, first.codes.shape[-1])
+    scales = torch.cat([o.scales for o in ops])
+    return E.Operand(codes, scales, first.outer, first.rows * len(ops), first.k, first.fmt)
+
+
+def _quant_weight_stack(w3: torch.Tensor, fmt: int, use_2dblock_w: bool, use_outer_scale: bool):
+    """[E, N, K] -> (W along K stacked [E*N, K], W along N stacked [E*K, N]), one outer scale for all."""
+    n_exp, N, K = w3.shape
+    ow = E.outer_scales(w3.reshape(n_exp * N, K), use_outer_scale, None)
+    outer = None if ow is None else ow[0:1]
+    ks, ts = [], []
+    for e in range(n_exp):
+        we = w3[e]
+        if use_2dblock_w:
+            k_op, t_op = E.quant_2d(we, fmt, outer, True)
+        else:
+            k_op = E.quant_rows(we, fmt, outer, E.RTN)
+            t_op = E.quant_cols(we, fmt, outer, None, E.RTN)
+        ks.append(k_op)
+        ts.append(t_op)
+    return _stack(ks), _stack(ts)
+
+
+def _grouped_gemm(a: E.Operand, b_stack: E.Operand, n_out: int, num_experts: int, group_expert, out_dtype):
+    out = torch.empty(a.rows, n_out, dtype=out_dtype, device=a.codes.device)
+    L.grouped_gemm_blockscaled(a.fmt, b_stack.fmt, a.rows, n_out, a.k, num_experts, a.codes, a.scales, b_stack.codes,
+                               b_stack.scales, group_expert, out, a.outer, b_stack.outer)
+    return out
+
+
+class GroupedLinearFunction(torch.autograd.Function):
+    """Shared autograd function of the three grouped paths; ``weights`` is canonical [E, N, K]."""
+
+    @staticmethod
+    def forward(ctx, inputs, weights, offs, fmt, fmt_grad, use_2dblock_x, use_2dblock_w, use_sr_grad,
+                use_outer_scale, hadamard_transform):
+        if not inputs.is_cuda:
+            raise RuntimeError("grouped GEMM runs on CUDA tensors only (no CPU fallback)")
+        weights = unwrap_weight_wrapper(weights)
+        if weights.dtype != inputs.dtype:
+            weights = weights.to(dtype=inputs.dtype)
+        assert inputs.dim() == 2 and weights.dim() == 3, "expected inputs [M, K] and weights [E, N, K]"
+        M, K = inputs.shape
+        n_exp, N, K2 = weights.shape
+        assert K == K2, f"inner dimensions differ: {K} vs {K2}"
+        torch._check(offs is not None and offs.numel() == n_exp, lambda: "offs must hold one entry per expert")
+        E.check_dims("grouped GEMM", M, K, N)
+        if use_2dblock_x:
+            raise NotImplementedError("use_2dblock_x=True is not implemented for the grouped path")
+        x2 = E.as_2d_rows(inputs.detach())
+        w3 = weights.detach().contiguous()
+        offs32 = offs.to(torch.int32).contiguous()
+        group_expert = group_experts_from_offsets(offs32, M)
+        rht = hadamard_transform.device_params() if hadamard_transform is not None else None
+
+        ox = E.outer_scales(x2, use_outer_scale, rht)
+        x_k = E.quant_rows(x2, fmt, None if ox is None else ox[0:1], E.RTN)
+        o_m = None if ox is None else (ox[1:2] if rht is not None else ox[0:1])
+        x_m = E.quant_cols(x2, fmt, o_m, rht, E.RTN)
+        w_k, w_t = _quant_weight_stack(w3, fmt, use_2dblock_w, use_outer_scale)
+        y = _grouped_gemm(x_k, w_k, N, n_exp, group_expert, inputs.dtype)
+
+        extra_x = [x_m.outer] if x_m.outer is not None else []
+        extra_w = [w_t.outer] if w_t.outer is not None else []
+        ctx.save_for_backward(x_m.codes, x_m.scales, *extra_x, w_t.codes, w_t.scales, *extra_w, group_expert, offs32)
+        ctx.dims = (M, K, N, n_exp)
+        ctx.fmt, ctx.fmt_grad = fmt, fmt_grad
+        ctx.use_sr_grad, ctx.use_outer_scale, ctx.rht = use_sr_grad, use_outer_scale, rht
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        M, K, N, n_exp = ctx.dims
+        saved = ctx.saved_tensors
+        if ctx.use_outer_scale:
+            xc, xs, xo, wc, ws, wo, group_expert, offs32 = saved
+        else:
+            (xc, xs, wc, ws, group_expert, offs32), xo, wo = saved, None, None
+        x_m = E.Operand(xc, xs, xo, K, M, ctx.fmt)
+        w_t = E.Operand(wc, ws, wo, n_exp * K, N, ctx.fmt)
+        g2 = E.as_2d_rows(grad_output)
+        og = E.outer_scales(g2, ctx.use_outer_scale, ctx.rht)
+        g_n = E.quant_rows(g2, ctx.fmt_grad, None if og is None else og[0:1],
+                           E.sr_args(ctx.use_sr_grad, "dy_n", M, N, g2.device))
+        o_m = None if og is None else (og[1:2] if ctx.rht is not None else og[0:1])
+        g_m = E.quant_cols(g2, ctx.fmt_grad, o_m, ctx.rht, E.sr_args(ctx.use_sr_grad, "dy_m", N, M, g2.device))
+        grad_inputs = grad_weights = None
+        if ctx.needs_input_grad[0]:
+            grad_inputs = _grouped_gemm(g_n, w_t, K, n_exp, group_expert, grad_output.dtype)
+        if ctx.needs_input_grad[1]:
+            grad_weights = torch.empty(n_exp, N, K, dtype=grad_output.dtype, device=g2.device)
+            L.grouped_gemm_wgrad_blockscaled(g_m.fmt, x_m.fmt, N, K, M, n_exp, g_m.codes, g_m.scales, x_m.codes,
+                                             x_m.scales, offs32, grad_weights, g_m.outer, x_m.outer)
+        return grad_inputs, grad_weights, None, None, None, None, None, None, None, None
+
+
+def _hadamard(use_hadamard: bool, use_2dblock_x: bool, device) -> Optional[HadamardTransform]:
+    if not use_hadamard:
+        return None
+    assert not use_2dblock_x, "Hadamard transform can only be applied when use_2dblock_x=False."
+    with torch.no_grad():
+        return HadamardFactory.create_transform(device=device)
+
+
+def _quantize_then_mxfp_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2dblock_w: bool, use_sr_grad: bool,
+                                          use_dge: bool, use_hadamard: bool, clip_mode: str,
+                                          use_macro_block_scaling: bool, use_uos: bool = False) -> torch.Tensor:
+    if use_dge or use_uos or clip_mode != "none":
+        raise NotImplementedError("use_dge / use_uos / clip_mode are not implemented on the B200 path")
+    if use_macro_block_scaling:
+        raise NotImplementedError("two_level_scaling='blockwise' (macro-block scaling) is not implemented inside "
+                                  "the B200 GEMM")
+    return GroupedLinearFunction.apply(A, B.transpose(-2, -1), offs, L.FMT_MXFP4, L.FMT_MXFP4, use_2dblock_x,
+                                       use_2dblock_w, bool(use_sr_grad), False,
+                                       _hadamard(use_hadamard, use_2dblock_x, B.device))
+
+
+def _quantize_then_nvfp4_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2dblock_w: bool, use_sr_grad: bool,
+                                           use_outer_scale: bool = False, use_hadamard: bool = False,
+                                           use_dge: bool = False, scale_format: str = "e4m3") -> torch.Tensor:
+    _check_scale_format(scale_format)
+    if use_dge:
+        raise NotImplementedError("use_dge is not implemented on the B200 path")
+    return GroupedLinearFunction.apply(A, B.transpose(-2, -1), offs, L.FMT_NVFP4, L.FMT_NVFP4, use_2dblock_x,
+                                       use_2dblock_w, use_sr_grad, use_outer_scale,
+                                       _hadamard(use_hadamard, use_2dblock_x, B.device))
+
+
+_FP8 = {"e4m3": L.FMT_MXFP8_E4M3, "e5m2": L.FMT_MXFP8_E5M2}
+
+
+def _quantize_then_mxfp8_scaled_grouped_mm(A, B, offs, *, use_2dblock_x: bool = False, use_2dblock_w: bool = True,
+                                           use_sr_grad: bool = False, fwd_format: str = "e4m3",
+                                           bwd_grad_format: str = "e4m3") -> torch.Tensor:
+    if fwd_format not in _FP8 or bwd_grad_format not in _FP8:
+        raise ValueError(f"Unsupported FP8 format: {fwd_format} / {bwd_grad_format}")
+    if use_sr_grad:
+        raise NotImplementedError("MXFP8 stochastic rounding exists only as gfx950 instructions in the reference")
+    return GroupedLinearFunction.apply(A, B.transpose(-2, -1), offs, _FP8[fwd_format], _FP8[bwd_grad_format],
+                                       use_2dblock_x, use_2dblock_w, False, False, None)

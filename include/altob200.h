@@ -240,7 +240,7 @@ int altob200_gemm_blockscaled(int32_t format_a, int32_t format_b, int64_t M, int
 
 /*
  * Grouped (MoE) variant: rows of A are grouped in runs of 128 that share one
- * expert; `group_expert[g]` (device int32, length M/128, -1 = padding rows that
+ * expert; `group_expert[g]` (device int32, length ceil(M/128), -1 = padding rows that
  * produce zeros) selects B[e] of shape [N, K].  Replaces
  * mxfp4_grouped_gemm_forward / backward_inputs
  * (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_forward.py:201,
@@ -252,6 +252,24 @@ int altob200_grouped_gemm_blockscaled(int32_t format_a, int32_t format_b, int64_
                                       const void* b_scales, const int32_t* group_expert,
                                       const float* alpha_a, const float* alpha_b,
                                       int32_t out_dtype, void* d, int64_t ldd, void* stream);
+
+/*
+ * Grouped weight gradient: dW[e][m, n] = alpha * sum over k in [k_offs[e-1], k_offs[e]) of
+ * A[m, k] * B[n, k], for e in [0, num_experts) (k_offs[-1] = 0).  A and B are the
+ * axis-0 quantised gradient and activation ([N_out, tokens] and [K_in, tokens], token
+ * axis contiguous); `k_offs` (device int32, cumulative, every entry a multiple of 128)
+ * gives each expert's token range; experts with an empty range receive zeros.  Replaces
+ * mxfp4_grouped_gemm_backward_weights (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_backward.py:501)
+ * and the per-expert loop of the NVFP4 path
+ * (alto/kernels/fp4/nvfp4/nvfp_grouped_gemm/cg_backward.py:126-141).
+ *   d : [num_experts, M, N] row-major, leading dimension ldd (elements).
+ * K here is the total number of tokens (the length of the shared reduction axis).
+ */
+int altob200_grouped_gemm_wgrad_blockscaled(int32_t format_a, int32_t format_b, int64_t M, int64_t N, int64_t K,
+                                            int32_t num_experts, const void* a_codes, const void* a_scales,
+                                            const void* b_codes, const void* b_scales, const int32_t* k_offs,
+                                            const float* alpha_a, const float* alpha_b, int32_t out_dtype,
+                                            void* d, int64_t ldd, void* stream);
 
 #ifdef __cplusplus
 }
