@@ -40,6 +40,8 @@ EXPORTED_SYMBOLS = (
     "altob200_quantize_2d",
     "altob200_dequantize",
     "altob200_rht",
+    "altob200_macro_block_scaling",
+    "altob200_macro_block_descaling",
     "altob200_gemm_blockscaled",
     "altob200_grouped_gemm_blockscaled",
     "altob200_grouped_gemm_wgrad_blockscaled",
@@ -107,6 +109,10 @@ def _declare_more(lib):
     lib.altob200_grouped_gemm_wgrad_blockscaled.restype = C.c_int
     lib.altob200_grouped_gemm_wgrad_blockscaled.argtypes = [i32, i32, i64, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp,
                                                             i32, vp, i64, vp]
+    lib.altob200_macro_block_scaling.restype = C.c_int
+    lib.altob200_macro_block_scaling.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, vp]
+    lib.altob200_macro_block_descaling.restype = C.c_int
+    lib.altob200_macro_block_descaling.argtypes = [vp, vp, i32, i64, i64, i64, i32, vp, vp]
 
 
 def lib():
@@ -286,6 +292,28 @@ def rht_apply(x, y, rht: Rht) -> None:
     _check(lib().altob200_rht(x.data_ptr(), _dt(x.dtype), x.shape[0], x.shape[1], x.stride(0), rht.n, rht._perm_c,
                               rht._sign_c, y.data_ptr(), y.stride(0), _stream()),
            "altob200_rht")
+
+
+MACRO_LAST, MACRO_2D, MACRO_ROWS = 0, 1, 2
+
+
+def macro_block_scaling(x, y, scale, mode: int) -> None:
+    """x, y: contiguous [batch, rows, cols]; scale: uint8, shaped as the header says for `mode`."""
+    _require_cuda(x, y, scale)
+    assert x.dim() == 3 and x.is_contiguous() and y.is_contiguous() and x.dtype == y.dtype and x.shape == y.shape
+    assert scale.dtype == torch.uint8 and scale.is_contiguous()
+    _check(lib().altob200_macro_block_scaling(x.data_ptr(), _dt(x.dtype), x.shape[0], x.shape[1], x.shape[2], mode,
+                                              y.data_ptr(), scale.data_ptr(), _stream()),
+           "altob200_macro_block_scaling")
+
+
+def macro_block_descaling(y, scale, x, mode: int) -> None:
+    _require_cuda(x, y, scale)
+    assert y.dim() == 3 and x.is_contiguous() and y.is_contiguous() and x.dtype == y.dtype and x.shape == y.shape
+    assert scale.dtype == torch.uint8 and scale.is_contiguous()
+    _check(lib().altob200_macro_block_descaling(y.data_ptr(), scale.data_ptr(), _dt(y.dtype), y.shape[0], y.shape[1],
+                                                y.shape[2], mode, x.data_ptr(), _stream()),
+           "altob200_macro_block_descaling")
 
 
 def gemm_blockscaled(fmt_a, fmt_b, M, N, K, a_codes, a_scales, b_codes, b_scales, out, alpha_a=None,

@@ -1,0 +1,232 @@
+// Macro-block (128) two-level scaling and descaling.
+//
+// Per block of 128 elements along the last axis of each row (1D) or per 128 x 128 tile (2D):
+//   amax  = max(|x| as fp32, 1e-12)
+//   bits  = fp32 bits of (6.0 / amax) & 0x007F8000      (the top 8 mantissa bits)
+//   code  = bits >> 15                                   (uint8, stored)
+//   s     = float(bits | 127 << 23)                      (a factor in [1, 2))
+//   y     = cast(x * s)     descaling:  x = cast(y / float(code << 15 | 127 << 23))
+// which restates the reference's Triton kernels (fp32 multiply, then the cast)
+//   alto/kernels/fp4/mxfp4/macro_block_scaling.py:35-96 and :100-146.
+// Elements past the end of a ragged last block do not take part in the amax.
+//
+// Work layout: 1D - a warp owns one (row, block) task, a lane 4 contiguous elements; the block
+// maximum is a warp shuffle reduction.  2D - a CTA of 256 threads owns one tile, a warp 16 rows;
+// the tile maximum goes through shared memory.  Both are one read and one write per element.
+#include "common.cuh"
+
+namespace altob200 {
+
+struct MacroArgs {
+  const void* x;       // [batch, rows, cols] contiguous
+  void* y;             // same shape
+  uint8_t* scale;      // 1D: [batch, rows, nblk]   2D: [batch, ceil(rows/128), nblk]
+  int64_t batch, rows, cols, nblk;
+  int vec;             // rows start on a 4-element boundary: 4-wide loads and stores are legal
+};
+
+__device__ __forceinline__ float macro_factor_from_amax(float amax, uint32_t* code) {
+  amax = fmaxf(amax, 1e-12f);
+  const uint32_t bits = f2u(__fdiv_rn(6.0f, amax)) & 0x007F8000u;
+  *code = bits >> 15;
+  return u2f(bits + (127u << 23));
+}
+__device__ __forceinline__ float macro_factor_from_code(uint32_t code) { return u2f((code << 15) + (127u << 23)); }
+
+template <bool IN_BF16>
+__device__ __forceinline__ void load4(const void* base, int64_t off, int valid, bool vec, float v[4]) {
+  // `valid` elements (0..4) starting at element offset `off` exist; the rest read as zero
+  if (valid == 4 && vec) {
+    if (IN_BF16) {
+      const uint2 w = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + off));
+      v[0] = bf16lo_to_f32(w.x); v[1] = bf16hi_to_f32(w.x); v[2] = bf16lo_to_f32(w.y); v[3] = bf16hi_to_f32(w.y);
+    } else {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off));
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j] = 0.0f;
+      if (j < valid) {
+        if (IN_BF16) v[j] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[off + j]);
+        else v[j] = reinterpret_cast<const float*>(base)[off + j];
+      }
+    }
+  }
+}
+
+template <bool IN_BF16>
+__device__ __forceinline__ void store4(void* base, int64_t off, int valid, bool vec, const float v[4]) {
+  if (valid == 4 && vec) {
+    if (IN_BF16) {
+      const uint32_t a = f32_to_bf16_bits(v[0]) | (f32_to_bf16_bits(v[1]) << 16);
+      const uint32_t b = f32_to_bf16_bits(v[2]) | (f32_to_bf16_bits(v[3]) << 16);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(base) + off) = make_uint2(a, b);
+    } else {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + off) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  } else {
+    for (int j = 0; j < valid; ++j) {
+      if (IN_BF16) reinterpret_cast<__nv_bfloat16*>(base)[off + j] = __float2bfloat16_rn(v[j]);
+      else reinterpret_cast<float*>(base)[off + j] = v[j];
+    }
+  }
+}
+
+__device__ __forceinline__ float warp_max_f32(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+// ---- 1D: one warp per (row, 128-column block) ----
+template <bool IN_BF16, bool DESCALE>
+__global__ void __launch_bounds__(256) macro_scale_1d_kernel(MacroArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t n_tasks = a.batch * a.rows * a.nblk;
+  const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = (int64_t)gridDim.x * 8;
+  for (int64_t task = warp0; task < n_tasks; task += n_warps) {
+    const int64_t row = task / a.nblk, blk = task - row * a.nblk;  // row counts over batch * rows
+    const int64_t col = blk * 128 + lane * 4;
+    int valid = (int)(a.cols - col);
+    valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
+    float v[4];
+    load4<IN_BF16>(a.x, row * a.cols + col, valid, a.vec, v);
+    float f;
+    if (DESCALE) {
+      f = macro_factor_from_code(a.scale[row * a.nblk + blk]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = __fdiv_rn(v[j], f);
+    } else {
+      float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+      m = warp_max_f32(m);
+      uint32_t code;
+      f = macro_factor_from_amax(m, &code);
+      if (lane == 0) a.scale[row * a.nblk + blk] = (uint8_t)code;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = __fmul_rn(v[j], f);
+    }
+    store4<IN_BF16>(a.y, row * a.cols + col, valid, a.vec, v);
+  }
+}
+
+// ---- 2D and column blocks: one CTA per 128 x 128 tile ----
+// COLS = false: one factor per tile.  COLS = true: one factor per column of the tile (blocks of
+// 128 run down the rows, the reference's axis=0 on a matrix); scale is [batch, cols, ceil(rows/128)].
+template <bool IN_BF16, bool DESCALE, bool COLS>
+__global__ void __launch_bounds__(256) macro_scale_tile_kernel(MacroArgs a) {
+  __shared__ float s_max[COLS ? 8 * 128 : 8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t b = blockIdx.z, tm = blockIdx.y, tn = blockIdx.x;
+  const int64_t mtiles = (a.rows + 127) / 128;
+  const int64_t col = tn * 128 + lane * 4;
+  int valid = (int)(a.cols - col);
+  valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
+  float v[16][4];
+  float cm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int64_t r = tm * 128 + warp * 16 + i;
+    const int vr = r < a.rows ? valid : 0;
+    load4<IN_BF16>(a.x, (b * a.rows + (r < a.rows ? r : 0)) * a.cols + col, vr, a.vec, v[i]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) cm[j] = fmaxf(cm[j], fabsf(v[i][j]));
+  }
+  float f[4];
+  if (COLS) {
+    // factor index: [batch, cols, mtiles]
+    if (DESCALE) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        f[j] = j < valid ? macro_factor_from_code(a.scale[(b * a.cols + col + j) * mtiles + tm]) : 1.0f;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s_max[warp * 128 + lane * 4 + j] = cm[j];
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float t = s_max[lane * 4 + j];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) t = fmaxf(t, s_max[w * 128 + lane * 4 + j]);
+        uint32_t code;
+        f[j] = macro_factor_from_amax(t, &code);
+        if (warp == 0 && j < valid) a.scale[(b * a.cols + col + j) * mtiles + tm] = (uint8_t)code;
+      }
+    }
+  } else {
+    const int64_t sidx = (b * mtiles + tm) * a.nblk + tn;
+    float ft;
+    if (DESCALE) {
+      ft = macro_factor_from_code(a.scale[sidx]);
+    } else {
+      float m = warp_max_f32(fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3])));
+      if (lane == 0) s_max[warp] = m;
+      __syncthreads();
+      float t = s_max[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) t = fmaxf(t, s_max[i]);
+      uint32_t code;
+      ft = macro_factor_from_amax(t, &code);
+      if (threadIdx.x == 0) a.scale[sidx] = (uint8_t)code;
+    }
+    f[0] = f[1] = f[2] = f[3] = ft;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int64_t r = tm * 128 + warp * 16 + i;
+    if (r >= a.rows) break;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[i][j] = DESCALE ? __fdiv_rn(v[i][j], f[j]) : __fmul_rn(v[i][j], f[j]);
+    store4<IN_BF16>(a.y, (b * a.rows + r) * a.cols + col, valid, a.vec, v[i]);
+  }
+}
+
+template <bool BF, bool DESCALE>
+static void launch_mode(const MacroArgs& a, int32_t mode, cudaStream_t st) {
+  if (mode == 0) {
+    int64_t blocks = ceil_div(a.batch * a.rows * a.nblk, 8);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    macro_scale_1d_kernel<BF, DESCALE><<<(unsigned)blocks, 256, 0, st>>>(a);
+  } else {
+    dim3 grid((unsigned)a.nblk, (unsigned)ceil_div(a.rows, 128), (unsigned)a.batch);
+    if (mode == 1) macro_scale_tile_kernel<BF, DESCALE, false><<<grid, 256, 0, st>>>(a);
+    else macro_scale_tile_kernel<BF, DESCALE, true><<<grid, 256, 0, st>>>(a);
+  }
+}
+
+static int macro_launch(const void* x, int32_t dtype, int64_t batch, int64_t rows, int64_t cols, int32_t mode,
+                        void* y, uint8_t* scale, bool descale, cudaStream_t st) {
+  if (x == nullptr || y == nullptr || scale == nullptr) return ALTOB200_EINVAL_SHAPE;
+  if (batch <= 0 || rows <= 0 || cols <= 0) return ALTOB200_EINVAL_SHAPE;
+  if (dtype != ALTOB200_DT_BF16 && dtype != ALTOB200_DT_F32) return ALTOB200_EUNSUPPORTED;
+  MacroArgs a;
+  // 4-wide accesses need every row to start on a 4-element boundary; otherwise element accesses
+  a.vec = (cols % 4 == 0) && !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15);
+  a.x = x; a.y = y; a.scale = scale; a.batch = batch; a.rows = rows; a.cols = cols; a.nblk = ceil_div(cols, 128);
+  if (mode < 0 || mode > 2) return ALTOB200_EUNSUPPORTED;
+  if (mode != 0 && (ceil_div(rows, 128) > 65535 || batch > 65535)) return ALTOB200_ELIMIT;
+  if (dtype == ALTOB200_DT_BF16) {
+    if (descale) launch_mode<true, true>(a, mode, st); else launch_mode<true, false>(a, mode, st);
+  } else {
+    if (descale) launch_mode<false, true>(a, mode, st); else launch_mode<false, false>(a, mode, st);
+  }
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+}  // namespace altob200
+
+extern "C" {
+
+int altob200_macro_block_scaling(const void* x, int32_t dtype, int64_t batch, int64_t rows, int64_t cols,
+                                 int32_t mode, void* y, uint8_t* scale, void* stream) {
+  return altob200::macro_launch(x, dtype, batch, rows, cols, mode, y, scale, false, (cudaStream_t)stream);
+}
+
+int altob200_macro_block_descaling(const void* y, const uint8_t* scale, int32_t dtype, int64_t batch, int64_t rows,
+                                   int64_t cols, int32_t mode, void* x, void* stream) {
+  return altob200::macro_launch(y, dtype, batch, rows, cols, mode, x, const_cast<uint8_t*>(scale), true,
+                                (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -15,6 +15,7 @@ from . import _lib as L
 from . import _linear as E
 from . import _quant as Q
 from .hadamard import HadamardFactory, HadamardTransform
+from .macro_block_scaling import macro_block_descaling, macro_block_scaling
 from .nvfp4 import unwrap_weight_wrapper
 
 BLOCK_SIZE_DEFAULT = 32
@@ -115,6 +116,61 @@ def blockwise_mxfp4_gemm(
     return out
 
 
+def _macro_qdq(t: torch.Tensor, axis: int, is_2d: bool, use_sr: bool = False) -> torch.Tensor:
+    """macro-block scale -> MXFP4 quantise -> dequantise -> macro-block descale, in t's dtype: what
+    the reference's two-level ("blockwise") MXFP4 recipe feeds its matmuls
+    (alto/kernels/fp4/mxfp4/mxfp_linear.py:301-302, 335-354)."""
+    scaled, mbs = macro_block_scaling(t, axis=axis, use_2d_block=is_2d)
+    q, s = convert_to_mxfp4(scaled, axis=axis, is_2d_block=is_2d, use_sr=use_sr)
+    dq = convert_from_mxfp4(q, s, t.dtype, axis=axis, is_2d_block=is_2d)
+    return macro_block_descaling(dq, mbs, axis=axis, use_2d_block=is_2d)
+
+
+def _macro_forward(ctx, x, weight, use_2dblock_x, use_2dblock_w, use_sr_grad, hadamard_transform):
+    """Two-level scaled forward.  The macro factors are not powers of two and differ per row and
+    per 128 columns, so they cannot ride on the E8M0 scales of the block-scaled MMA; the reference
+    itself refuses this recipe on its FP4 matrix cores and multiplies the de-quantised, de-scaled
+    operands in the input dtype (alto/kernels/fp4/mxfp4/mxfp_linear.py:321-356).  Same here: the
+    quantise / de-quantise chain runs in this library's kernels, the matmul is a plain bf16 GEMM."""
+    original_shape = x.shape
+    x2 = x.detach().reshape(-1, original_shape[-1])
+    w2 = weight.detach()
+    M, K = x2.shape
+    N = w2.shape[0]
+    E.check_dims("MXFP4LinearFunction", M, K, N)
+    x_dq = _macro_qdq(x2, -1, use_2dblock_x)
+    w_dq = _macro_qdq(w2, -1, use_2dblock_w)
+    y = x_dq @ w_dq.t()
+    if not use_2dblock_w:
+        w_dq = _macro_qdq(w2, 0, False)
+    if not use_2dblock_x:
+        xm = hadamard_transform(x2, left_mul=True) if hadamard_transform is not None else x2
+        x_dq = _macro_qdq(xm, 0, False)
+    ctx.save_for_backward(x_dq, w_dq)
+    ctx.macro = True
+    ctx.use_2dblock_x = use_2dblock_x
+    ctx.use_sr_grad = use_sr_grad
+    ctx.hadamard_transform = hadamard_transform
+    return y.view(*original_shape[:-1], N)
+
+
+def _macro_backward(ctx, grad_output):
+    """alto/kernels/fp4/mxfp4/mxfp_linear.py:436-540, the branch without FP4 matrix cores."""
+    x_dq, w_dq = ctx.saved_tensors
+    original_shape = grad_output.shape
+    g2 = grad_output.reshape(-1, original_shape[-1])
+    if ctx.use_2dblock_x:
+        g_dq = _macro_qdq(g2, -1, True, ctx.use_sr_grad)
+        g_m_dq = g_dq
+    else:
+        g_dq = _macro_qdq(g2, -1, False, ctx.use_sr_grad)
+        gm = ctx.hadamard_transform(g2, left_mul=True) if ctx.hadamard_transform is not None else g2
+        g_m_dq = _macro_qdq(gm, 0, False, ctx.use_sr_grad)
+    grad_inputs = g_dq @ w_dq
+    grad_weights = g_m_dq.t() @ x_dq
+    return grad_inputs.view(*original_shape[:-1], -1), grad_weights
+
+
 class MXFP4LinearFunction(torch.autograd.Function):
     """Same argument list as the reference's autograd function
     (alto/kernels/fp4/mxfp4/mxfp_linear.py:266-284)."""
@@ -126,18 +182,22 @@ class MXFP4LinearFunction(torch.autograd.Function):
         _check_options(clip_mode, use_uos)
         if use_dge:
             raise NotImplementedError("use_dge is not implemented on the B200 path")
-        if use_macro_block_scaling:
-            raise NotImplementedError("use_macro_block_scaling is not implemented on the B200 path")
         weight = unwrap_weight_wrapper(weight)
         if weight.dtype != x.dtype:
             weight = weight.to(dtype=x.dtype)
+        ctx.macro = False
+        if use_macro_block_scaling:
+            if not x.is_cuda:
+                raise RuntimeError("MXFP4LinearFunction runs on CUDA tensors only (no CPU fallback)")
+            return _macro_forward(ctx, x, weight, use_2dblock_x, use_2dblock_w, bool(use_sr_grad),
+                                  hadamard_transform)
         return E.linear_forward(ctx, "MXFP4LinearFunction", x, weight, L.FMT_MXFP4, use_2dblock_x=use_2dblock_x,
                                 use_2dblock_w=use_2dblock_w, use_sr_grad=bool(use_sr_grad), use_outer_scale=False,
                                 hadamard_transform=hadamard_transform)
 
     @staticmethod
     def backward(ctx, grad_output):
-        gi, gw = E.linear_backward(ctx, grad_output)
+        gi, gw = _macro_backward(ctx, grad_output) if ctx.macro else E.linear_backward(ctx, grad_output)
         return gi, gw, None, None, None, None, None, None, None, None
 
 

@@ -220,6 +220,30 @@ int altob200_rht(const void* x, int32_t dtype, int64_t rows, int64_t cols, int64
                  int64_t ld_y, void* stream);
 
 /*
+ * Macro-block two-level scaling for MXFP4: before the E8M0 quantiser, each block of 128
+ * elements is multiplied by a factor in [1, 2) whose top 8 mantissa bits are those of
+ * 6 / amax(block); the 8 bits are stored as one uint8 per block.  Replaces macro_block_scaling
+ * (alto/kernels/fp4/mxfp4/macro_block_scaling.py:35-96, host wrapper :236-288, public
+ * op :423-428).  x and y are contiguous [batch, rows, cols] of `dtype`; any cols (4-wide
+ * accesses are used when cols is a multiple of 4 and both pointers are 16-byte aligned).
+ *   mode 0: blocks along the last axis;   scale [batch, rows, ceil(cols/128)]
+ *   mode 1: 128 x 128 tiles;              scale [batch, ceil(rows/128), ceil(cols/128)]
+ *   mode 2: blocks down the row axis (the reference's axis=0 on a matrix, which it reaches
+ *           through a transposed view);   scale [batch, cols, ceil(rows/128)]
+ * Ragged last blocks take their amax over the elements that exist.
+ */
+int altob200_macro_block_scaling(const void* x, int32_t dtype, int64_t batch, int64_t rows, int64_t cols,
+                                 int32_t mode, void* y, uint8_t* scale, void* stream);
+
+/*
+ * Inverse of the above: x = y / factor(scale).  Replaces macro_block_descaling
+ * (alto/kernels/fp4/mxfp4/macro_block_scaling.py:100-146, host wrapper :345-420, public
+ * op :431-437).
+ */
+int altob200_macro_block_descaling(const void* y, const uint8_t* scale, int32_t dtype, int64_t batch, int64_t rows,
+                                   int64_t cols, int32_t mode, void* x, void* stream);
+
+/*
  * Block-scaled GEMM on tcgen05:  D[m, n] = alpha * sum_k A[m, k] * B[n, k]
  * with A and B both stored reduction-axis-contiguous ("NT"), packed scales, fp32
  * accumulation in tensor memory.  Replaces blockwise_mxfp4_gemm

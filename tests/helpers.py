@@ -32,6 +32,28 @@ def golden_cases(prefix: str):
             yield z, m
 
 
+MACRO_GOLDEN = GOLDEN.with_name("macro_block_vectors.npz")
+
+
+def macro_cases():
+    """(npz, (tag, shape, dtype, axis, use_2d_block)) for every macro-block scaling vector."""
+    z = np.load(MACRO_GOLDEN, allow_pickle=False)
+    for m in ast.literal_eval(str(z["meta"])):
+        yield z, m
+
+
+def bits_equal(t: torch.Tensor, arr: np.ndarray) -> bool:
+    """Bit-for-bit comparison of a (CPU or CUDA) tensor with a stored array (bf16 stored as uint16)."""
+    t = t.detach().cpu().contiguous()
+    if tuple(t.shape) != tuple(arr.shape):
+        return False
+    if t.dtype == torch.bfloat16:
+        return np.array_equal(t.view(torch.int16).numpy().view(np.uint16), arr)
+    if t.dtype == torch.float32:
+        return np.array_equal(t.numpy().view(np.uint32), arr.view(np.uint32))
+    return np.array_equal(t.numpy(), arr)
+
+
 def case_input(z, m) -> torch.Tensor:
     return tensor_from_bits(z[m[0] + "_x"], _DT[m[2]])
 

@@ -1,0 +1,134 @@
+"""Macro-block (128) two-level scaling: the oracle against the reference kernel's outputs (CPU), and
+the CUDA kernels against both (GPU).  Everything is bit-exact.  Cases and properties follow the
+reference's tests/unittest/mxfp4/test_macro_block_scaling.py:36-58 (shapes with ragged blocks,
+axis -1 / -2, 1-D and 2-D blocks, bf16 and fp32, factor in [1, 2], round trip)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import alto_oracle as O
+from tests.helpers import bits_equal, case_input, macro_cases
+
+_IDS = lambda v: v[0] if isinstance(v, tuple) else ""  # noqa: E731
+
+
+@pytest.mark.parametrize("z,m", list(macro_cases()), ids=_IDS)
+def test_oracle_matches_reference_kernel(z, m):
+    tag, shape, dt, axis, is2d = m
+    x = case_input(z, m)
+    y, s = O.macro_block_scaling(x, axis, is2d)
+    assert bits_equal(s, z[tag + "_s"])
+    assert bits_equal(y, z[tag + "_y"])
+    xr = O.macro_block_descaling(y, s, axis, is2d)
+    assert bits_equal(xr, z[tag + "_xr"])
+
+
+def test_scale_shape_rule():
+    from alto_b200.macro_block_scaling import macro_scale_shape
+    assert macro_scale_shape((513, 385), -1, False) == (513, 4)
+    assert macro_scale_shape((513, 385), -2, False) == (385, 5)
+    assert macro_scale_shape((513, 385), -2, True) == (4, 5)
+    assert macro_scale_shape((2, 513, 385), -1, True) == (2, 5, 4)
+    assert macro_scale_shape((2, 513, 385), -2, False) == (2, 385, 5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("z,m", list(macro_cases()), ids=_IDS)
+def test_cuda_matches_reference_kernel(z, m):
+    from alto_b200.macro_block_scaling import macro_block_descaling, macro_block_scaling
+    tag, shape, dt, axis, is2d = m
+    x = case_input(z, m).cuda()
+    y, s = macro_block_scaling(x, axis=axis, use_2d_block=is2d)
+    assert y.dtype == x.dtype and s.dtype == torch.uint8
+    assert bits_equal(s, z[tag + "_s"])
+    assert bits_equal(y, z[tag + "_y"])
+    xr = macro_block_descaling(y, s, axis=axis, use_2d_block=is2d)
+    assert bits_equal(xr, z[tag + "_xr"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(1024, 2048), (513, 385), (2, 513, 385)])
+@pytest.mark.parametrize("axis", [-1, -2])
+@pytest.mark.parametrize("is2d", [False, True])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+def test_cuda_matches_oracle_and_round_trips(shape, axis, is2d, dt):
+    from alto_b200.macro_block_scaling import macro_block_descaling, macro_block_scaling, macro_scale_shape
+    g = torch.Generator().manual_seed(hash((shape, axis, is2d)) & 0xFFFF)
+    x = torch.randn(shape, generator=g).to(dt)
+    y, s = macro_block_scaling(x.cuda(), axis=axis, use_2d_block=is2d)
+    assert y.shape == x.shape and tuple(s.shape) == macro_scale_shape(shape, axis, is2d)
+    y_o, s_o = O.macro_block_scaling(x, axis, is2d)
+    assert torch.equal(s.cpu(), s_o)
+    assert torch.equal(y.cpu().view(torch.int16 if dt == torch.bfloat16 else torch.int32),
+                       y_o.view(torch.int16 if dt == torch.bfloat16 else torch.int32))
+    factor = ((s.to(torch.int32) << 15) + (127 << 23)).view(torch.float32)
+    assert torch.all(factor >= 1) and torch.all(factor <= 2)
+    xr = macro_block_descaling(y, s, axis=axis, use_2d_block=is2d)
+    assert xr.dtype == x.dtype and xr.shape == x.shape
+    assert torch.equal(xr.cpu(), O.macro_block_descaling(y_o, s_o, axis, is2d))
+    if dt == torch.bfloat16:
+        assert torch.allclose(xr.cpu(), x, rtol=1e-2, atol=1e-3)
+    else:
+        assert torch.allclose(xr.cpu(), x, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("axis,is2d", [(-1, False), (0, False), (-1, True)])
+def test_macro_qdq_chain_is_bit_exact(axis, is2d):
+    """scale -> quantise -> dequantise -> descale through the public ops equals the oracle's chain."""
+    from alto_b200.mxfp4 import _macro_qdq
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(256, 384, generator=g) * torch.exp(torch.randn(256, 1, generator=g))).to(torch.bfloat16)
+    got = _macro_qdq(x.cuda(), axis, is2d).cpu()
+    want = O.macro_qdq(x, axis, is2d)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("use_2dblock_x,use_2dblock_w,use_hadamard", [(False, True, True), (False, False, False),
+                                                                      (True, True, False)])
+def test_two_level_blockwise_linear_matches_oracle(use_2dblock_x, use_2dblock_w, use_hadamard):
+    """two_level_scaling='blockwise': operands are bit-identical to the oracle's, so the only
+    difference is the bf16 GEMM's accumulation order and output rounding (rel. Frobenius 1e-2 =
+    a few bf16 ulps; the reference's own test of this recipe uses rtol 1e-2)."""
+    from alto_b200 import mxfp4 as MX
+    from alto_b200.hadamard import HadamardFactory
+    M, K, N = 256, 384, 128
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    dy = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=3)
+    xd = x.cuda().requires_grad_(True)
+    wd = w.cuda().requires_grad_(True)
+    y = MX._to_mxfp4_then_scaled_mm(xd, wd, use_2dblock_x, use_2dblock_w, False, False, "none", use_hadamard,
+                                    use_macro_block_scaling=True)
+    y.backward(dy.cuda())
+    W_had = None
+    if use_hadamard:
+        HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=3)
+        W_had = HadamardFactory.create_transform(device=torch.device("cuda")).matrix().cpu()
+    yo, dxo, dwo = O.mxfp4_macro_linear(x, w, dy, use_2dblock_x=use_2dblock_x, use_2dblock_w=use_2dblock_w,
+                                        W_had=W_had)
+
+    def rel(a, b):
+        return ((a.float().cpu() - b).norm() / b.norm()).item()
+
+    assert y.dtype == torch.bfloat16 and y.shape == (M, N)
+    assert rel(y, yo) <= 1e-2 and rel(xd.grad, dxo) <= 1e-2 and rel(wd.grad, dwo) <= 1e-2
+
+
+@pytest.mark.gpu
+def test_refusals():
+    from alto_b200.macro_block_scaling import macro_block_descaling, macro_block_scaling
+    x = torch.randn(2, 4, 128, 128, device="cuda")
+    with pytest.raises(AssertionError):
+        macro_block_scaling(x)
+    x3 = torch.randn(2, 128, 128, device="cuda")
+    with pytest.raises(NotImplementedError):
+        macro_block_scaling(x3, axis=0)
+    y, s = macro_block_scaling(x3)
+    with pytest.raises(AssertionError, match="Unexpected scale shape"):
+        macro_block_descaling(y, s, use_2d_block=True)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        macro_block_scaling(torch.randn(128, 128))
