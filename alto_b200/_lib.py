@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = (
     "altob200_rht",
     "altob200_macro_block_scaling",
     "altob200_macro_block_descaling",
+    "altob200_gather_rows",
     "altob200_gemm_blockscaled",
     "altob200_grouped_gemm_blockscaled",
     "altob200_grouped_gemm_wgrad_blockscaled",
@@ -113,6 +114,8 @@ def _declare_more(lib):
     lib.altob200_macro_block_scaling.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, vp]
     lib.altob200_macro_block_descaling.restype = C.c_int
     lib.altob200_macro_block_descaling.argtypes = [vp, vp, i32, i64, i64, i64, i32, vp, vp]
+    lib.altob200_gather_rows.restype = C.c_int
+    lib.altob200_gather_rows.argtypes = [vp, i64, i64, vp, i64, vp, vp]
 
 
 def lib():
@@ -314,6 +317,18 @@ def macro_block_descaling(y, scale, x, mode: int) -> None:
     _check(lib().altob200_macro_block_descaling(y.data_ptr(), scale.data_ptr(), _dt(y.dtype), y.shape[0], y.shape[1],
                                                 y.shape[2], mode, x.data_ptr(), _stream()),
            "altob200_macro_block_descaling")
+
+
+def gather_rows(src: torch.Tensor, index: torch.Tensor, out_rows: Optional[int] = None) -> torch.Tensor:
+    """out[i] = src[index[i]] for index[i] >= 0, else a zero row.  src: [rows, cols] contiguous with
+    rows of a multiple of 16 bytes; index: int32 on the same device."""
+    _require_cuda(src, index)
+    assert src.dim() == 2 and src.is_contiguous() and index.dtype == torch.int32 and index.is_contiguous()
+    n = int(index.numel() if out_rows is None else out_rows)
+    out = torch.empty(n, src.shape[1], dtype=src.dtype, device=src.device)
+    _check(lib().altob200_gather_rows(src.data_ptr(), src.shape[0], src.shape[1] * src.element_size(),
+                                      index.data_ptr(), n, out.data_ptr(), _stream()), "altob200_gather_rows")
+    return out
 
 
 def gemm_blockscaled(fmt_a, fmt_b, M, N, K, a_codes, a_scales, b_codes, b_scales, out, alpha_a=None,

@@ -1,0 +1,283 @@
+"""Multi-GPU forms of the low-precision linear path (one process per GPU, ``torch.distributed``).
+
+Three ways the path shards, each with exactly the exchange it needs and nothing more:
+
+* data parallel replicas        -- every rank runs the full linear on its own batch; the only
+  exchange is the all-reduce of the weight gradients (``allreduce_gradients``).
+* column-sharded linear         -- W [N, K] split along N; forward and wgrad are local, dgrad is a
+  sum over ranks (``column_sharded_linear``: all-reduce of dX in backward).  N / world must be a
+  multiple of 32 so that 2-D weight blocks never straddle ranks.
+* expert parallel MoE           -- experts split across ranks, tokens exchanged by all-to-all with
+  variable splits each way (``ExpertParallelDispatcher``), local rows sorted by expert and padded
+  to runs of 128 for the grouped GEMMs.
+
+The reference has no multi-GPU code of its own for this path: it relies on its TorchTitan fork
+(alto/modifiers/lpt/base.py:194-201 swaps the token dispatcher so that per-expert row counts are
+padded to ALIGN_SIZE_M = 128; alto/kernels/dispatch/tensor.py:159-211 are the FSDP hooks).  The
+semantics here are those of stock TorchTitan's expert-parallel dispatch (tokens sorted by expert,
+all-to-all by owner rank, local re-sort by expert, padding rows of zeros, weighted combine).
+
+Quantisation placement: everything that depends on which rows sit next to each other (token-axis
+blocks, the Hadamard rotation along tokens, the tensorwise amax) runs after the exchange on local
+data, so a rank's results are bit-identical to a single-GPU run on the same local rows.
+
+Data always sits in local HBM before a kernel reads it: the exchanges are NCCL collectives, no
+kernel of this library reads a peer's memory.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+
+__all__ = ["allreduce_gradients", "shard_rows", "column_sharded_linear", "ExpertParallelDispatcher",
+           "permute_pad_plan", "ALIGN_SIZE_M"]
+
+ALIGN_SIZE_M = 128
+
+
+def _world(group) -> int:
+    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+
+def _rank(group) -> int:
+    return dist.get_rank(group) if dist.is_available() and dist.is_initialized() else 0
+
+
+# ------------------------------------------------------------------------------------------
+# data parallel: all-reduce of weight gradients
+# ------------------------------------------------------------------------------------------
+def allreduce_gradients(params: Sequence[torch.Tensor], group=None, bucket_bytes: int = 64 << 20,
+                        average: bool = True) -> int:
+    """Sums (or averages) ``p.grad`` over the ranks of ``group`` in buckets of ``bucket_bytes``:
+    each bucket is one flat all-reduce, issued asynchronously so that copy-in of the next bucket
+    overlaps the reduction of the previous one.  Returns the number of collectives issued.
+
+    Buckets are sized for launch latency and overlap, not for link count: NVSwitch gives every
+    peer full bandwidth, and NCCL reduces inside the switch when it can."""
+    world = _world(group)
+    grads = [p.grad for p in params if p.grad is not None]
+    if world == 1 or not grads:
+        return 0
+    buckets: List[List[torch.Tensor]] = [[]]
+    size = 0
+    for g in grads:
+        nbytes = g.numel() * g.element_size()
+        if buckets[-1] and (size + nbytes > bucket_bytes or g.dtype != buckets[-1][0].dtype):
+            buckets.append([])
+            size = 0
+        buckets[-1].append(g)
+        size += nbytes
+    pending = []
+    for b in buckets:
+        flat = torch.cat([g.reshape(-1) for g in b])
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=True)
+        pending.append((work, flat, b))
+    for work, flat, b in pending:
+        work.wait()
+        if average:
+            flat.div_(world)
+        off = 0
+        for g in b:
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()
+    return len(pending)
+
+
+# ------------------------------------------------------------------------------------------
+# column-sharded linear
+# ------------------------------------------------------------------------------------------
+def shard_rows(w: torch.Tensor, group=None, multiple: int = 32) -> torch.Tensor:
+    """This rank's rows [r * N / world, (r + 1) * N / world) of w [N, K] (a view)."""
+    world, rank = _world(group), _rank(group)
+    N = w.shape[0]
+    torch._check(N % world == 0 and (N // world) % multiple == 0,
+                 lambda: f"out_features {N} must split into {world} shards that are multiples of {multiple}")
+    n = N // world
+    return w[rank * n:(rank + 1) * n]
+
+
+class _CopyToShards(torch.autograd.Function):
+    """Identity in forward; in backward the partial input gradients of the shards are summed."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, grad):
+        if _world(ctx.group) > 1:
+            grad = grad.contiguous()
+            dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=ctx.group)
+        return grad, None
+
+
+def column_sharded_linear(x: torch.Tensor, w_shard: torch.Tensor, linear_fn: Callable, group=None) -> torch.Tensor:
+    """Y_r = linear_fn(x, W_r) with W_r this rank's [N / world, K] shard; x is replicated.
+
+    Forward has no exchange (the concatenation of the Y_r along N is implicit in the sharding of
+    whatever consumes them), wgrad is local (dY_r, x), and dgrad dX = sum_r dY_r W_r is one
+    all-reduce of the bf16 partials.  ``linear_fn(a, b)`` is one of the boundary functions with its
+    recipe bound, e.g. ``lambda a, b: _to_mxfp8_then_scaled_mm(a, b, "e4m3", False, False, True)``."""
+    return linear_fn(_CopyToShards.apply(x, group), w_shard)
+
+
+# ------------------------------------------------------------------------------------------
+# expert parallel: dispatch / combine
+# ------------------------------------------------------------------------------------------
+def permute_pad_plan(recv_counts: torch.Tensor, align: int = ALIGN_SIZE_M):
+    """Row plan of the local re-sort after the dispatch all-to-all.
+
+    ``recv_counts`` (CPU int64 [sources, local_experts]): rows received from each source rank for
+    each local expert; the receive buffer holds them source-major, expert-minor.  Returns CPU
+    tensors ``(index, inverse, offs)``: ``index`` int32 [M_pad] gives for every row of the
+    expert-major, padded layout its row in the receive buffer (-1 = padding row); ``inverse``
+    int32 [rows_received] is the opposite map; ``offs`` int32 [local_experts] are the cumulative
+    padded row counts the grouped GEMMs take (every count a multiple of ``align``)."""
+    c = recv_counts.to(torch.int64)
+    S, E = c.shape
+    per_expert = c.sum(0)
+    padded = (per_expert + align - 1) // align * align
+    offs = torch.cumsum(padded, 0)
+    pad_start = offs - padded                                   # [E]
+    recv_start = (torch.cumsum(c.reshape(-1), 0) - c.reshape(-1)).reshape(S, E)
+    within = torch.cumsum(c, 0) - c                             # rows of expert e from earlier sources
+    dst_start = pad_start.unsqueeze(0) + within                 # [S, E]
+    total = int(c.sum())
+    m_pad = int(offs[-1]) if E > 0 else 0
+    index = torch.full((m_pad,), -1, dtype=torch.int32)
+    inverse = torch.empty(total, dtype=torch.int32)
+    if total > 0:
+        counts = c.reshape(-1)
+        block = torch.repeat_interleave(torch.arange(S * E), counts)          # block id of every received row
+        pos = torch.arange(total) - recv_start.reshape(-1)[block]             # position inside its block
+        dst = dst_start.reshape(-1)[block] + pos
+        inverse.copy_(dst.to(torch.int32))
+        index[dst] = torch.arange(total, dtype=torch.int32)
+    return index, inverse, offs.to(torch.int32)
+
+
+class _GatherRows(torch.autograd.Function):
+    """out[i] = x[index[i]] (zeros where index < 0); ``index`` uses every row of x at most once, so
+    the gradient is the gather by the opposite map ``inverse``."""
+
+    @staticmethod
+    def forward(ctx, x, index, inverse):
+        ctx.save_for_backward(index, inverse)
+        return L.gather_rows(x.contiguous(), index)
+
+    @staticmethod
+    def backward(ctx, grad):
+        index, inverse = ctx.saved_tensors
+        return L.gather_rows(grad.contiguous(), inverse), None, None
+
+
+class _ReplicateSorted(torch.autograd.Function):
+    """Routed rows sorted by expert: out[i] = x[order[i] // k].  A token feeds k routed rows, so the
+    gradient gathers the routed rows back into token order and sums each token's k rows."""
+
+    @staticmethod
+    def forward(ctx, x, token_of_sorted, inv_order, k):
+        ctx.save_for_backward(inv_order)
+        ctx.k = k
+        return L.gather_rows(x.contiguous(), token_of_sorted)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (inv_order,) = ctx.saved_tensors
+        g = L.gather_rows(grad.contiguous(), inv_order)
+        return g.view(-1, ctx.k, g.shape[-1]).sum(1).to(grad.dtype), None, None, None
+
+
+class _AllToAllRows(torch.autograd.Function):
+    """Variable-split all-to-all of rows; the gradient is the same exchange with the splits swapped."""
+
+    @staticmethod
+    def forward(ctx, x, out_splits, in_splits, group):
+        ctx.out_splits, ctx.in_splits, ctx.group = out_splits, in_splits, group
+        out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))
+        dist.all_to_all_single(out, x.contiguous(), out_splits, in_splits, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        out = grad.new_empty((sum(ctx.in_splits),) + tuple(grad.shape[1:]))
+        dist.all_to_all_single(out, grad.contiguous(), ctx.in_splits, ctx.out_splits, group=ctx.group)
+        return out, None, None, None
+
+
+class _DispatchState:
+    __slots__ = ("k", "tokens", "inv_order", "in_splits", "out_splits", "index", "inverse", "offs")
+
+
+class ExpertParallelDispatcher:
+    """Token exchange of an expert-parallel MoE layer around the grouped GEMMs.
+
+    ``num_experts`` experts are split evenly over the ranks of ``group`` (rank r owns experts
+    [r * E / world, (r + 1) * E / world)); tokens are data parallel.
+
+        x_local, offs, state = d.dispatch(x, expert_ids)       # x [T, D], expert_ids [T, k]
+        h = experts(x_local, offs)                              # grouped GEMMs on [M_pad, D]
+        out = d.combine(h, state, scores)                       # [T, D'] = sum_k scores * h(routed row)
+
+    dispatch: routed rows sorted by expert -> per-expert counts exchanged -> row all-to-all ->
+    local re-sort to expert-major order with every expert's run padded to ``align`` rows (zeros).
+    combine is the inverse followed by the score-weighted sum over each token's k routed rows.
+    Both are differentiable.  One host synchronisation per dispatch (the split sizes of the
+    all-to-all live on the host); with a single rank the all-to-alls are skipped."""
+
+    def __init__(self, num_experts: int, group=None, align: int = ALIGN_SIZE_M):
+        self.group = group
+        self.world = _world(group)
+        self.rank = _rank(group)
+        torch._check(num_experts % self.world == 0,
+                     lambda: f"{num_experts} experts do not split over {self.world} ranks")
+        self.num_experts = num_experts
+        self.local_experts = num_experts // self.world
+        self.align = align
+
+    def dispatch(self, x: torch.Tensor, expert_ids: torch.Tensor):
+        assert x.dim() == 2 and expert_ids.dim() == 2 and expert_ids.shape[0] == x.shape[0]
+        T, k = expert_ids.shape
+        dev = x.device
+        flat = expert_ids.reshape(-1).to(torch.int64)
+        order = torch.argsort(flat, stable=True)
+        inv_order = torch.empty_like(order)
+        inv_order[order] = torch.arange(order.numel(), device=dev)
+        counts = torch.bincount(flat, minlength=self.num_experts)            # rows per global expert
+        send = counts.view(self.world, self.local_experts)
+        if self.world > 1:
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send.contiguous(), group=self.group)
+        else:
+            recv = send
+        send_h, recv_h = send.cpu(), recv.cpu()                              # the one host synchronisation
+        st = _DispatchState()
+        st.k, st.tokens = k, T
+        st.inv_order = inv_order.to(torch.int32)
+        st.in_splits = [int(v) for v in send_h.sum(1)]
+        st.out_splits = [int(v) for v in recv_h.sum(1)]
+        index, inverse, offs = permute_pad_plan(recv_h, self.align)
+        st.index, st.inverse, st.offs = index.to(dev), inverse.to(dev), offs.to(dev)
+        token_of_sorted = torch.div(order, k, rounding_mode="floor").to(torch.int32)
+        rows = _ReplicateSorted.apply(x, token_of_sorted, st.inv_order, k)
+        if self.world > 1:
+            rows = _AllToAllRows.apply(rows, st.out_splits, st.in_splits, self.group)
+        x_local = _GatherRows.apply(rows, st.index, st.inverse)
+        return x_local, st.offs, st
+
+    def combine(self, y_local: torch.Tensor, state: _DispatchState, scores: Optional[torch.Tensor] = None):
+        rows = _GatherRows.apply(y_local, state.inverse, state.index)
+        if self.world > 1:
+            rows = _AllToAllRows.apply(rows, state.in_splits, state.out_splits, self.group)
+        # back to routed-row order (token-major, k minor): a permutation, so its own inverse map
+        order = torch.argsort(state.inv_order.to(torch.int64)).to(torch.int32)
+        routed = _GatherRows.apply(rows, state.inv_order, order)
+        routed = routed.view(state.tokens, state.k, routed.shape[-1])
+        if scores is not None:
+            routed = routed * scores.to(routed.dtype).unsqueeze(-1)
+        return routed.sum(1)

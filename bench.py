@@ -397,7 +397,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shape", default=None, metavar="M,K,N",
+                    help="run the same step at another shape (profiling captures on a small case); the "
+                         "headline workload is the default")
     args = ap.parse_args()
+    if args.shape:
+        global M, K, N, FLOPS_PER_STEP
+        M, K, N = (int(v) for v in args.shape.split(","))
+        FLOPS_PER_STEP = 3 * 2 * M * N * K
+        CONFIG["shape"] = {"M": M, "K": K, "N": N}
+        CONFIG["workload"] = f"NOT the headline workload: same NVFP4 step at M={M} K={K} N={N}"
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -244,6 +244,18 @@ int altob200_macro_block_descaling(const void* y, const uint8_t* scale, int32_t 
                                    int64_t cols, int32_t mode, void* x, void* stream);
 
 /*
+ * Row gather with zero fill: dst[i] = index[i] >= 0 ? src[index[i]] : zeros, rows of row_bytes
+ * (a multiple of 16; both pointers 16-byte aligned).  The MoE token path around the grouped
+ * GEMMs: sort routed rows by expert and pad each expert's run to a multiple of 128 rows (index
+ * -1), and the inverse.  The reference leaves this to its TorchTitan fork's token dispatcher
+ * (call sites alto/modifiers/lpt/base.py:194-201, alto/kernels/dispatch/tensor.py:224-263); the
+ * grouped kernels fix the result's form (alto/kernels/fp4/fp4_common/grouped_utils.py:81-94).
+ * `index` is device int32 [out_rows]; entries outside [0, src_rows) give zero rows.
+ */
+int altob200_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes, const int32_t* index,
+                         int64_t out_rows, void* dst, void* stream);
+
+/*
  * Block-scaled GEMM on tcgen05:  D[m, n] = alpha * sum_k A[m, k] * B[n, k]
  * with A and B both stored reduction-axis-contiguous ("NT"), packed scales, fp32
  * accumulation in tensor memory.  Replaces blockwise_mxfp4_gemm

@@ -1,0 +1,153 @@
+"""Host logic of the multi-GPU forms of the path, run as 2 gloo ranks on CPU: the expert-parallel
+dispatch / combine plan and exchanges, the column-sharded linear's dgrad all-reduce and the bucketed
+gradient all-reduce.  The CUDA row gather is replaced by a tensor-op stand-in (the device kernel
+itself is checked in the GPU tests); no other kernel is involved.  The reference pins none of this
+(it lives in its TorchTitan fork); the checks are against a single-process dense computation."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from alto_b200 import distributed as D
+
+
+def _gather_rows_cpu(src, index, out_rows=None):
+    idx = index.to(torch.int64)
+    ok = (idx >= 0) & (idx < src.shape[0])
+    out = src[idx.clamp(0, max(src.shape[0] - 1, 0))] if src.shape[0] > 0 else src.new_zeros(idx.numel(), src.shape[1])
+    return torch.where(ok.unsqueeze(1), out, torch.zeros_like(out))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(rank, world, port, fn, args):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        D.L.gather_rows = _gather_rows_cpu
+        fn(rank, world, *args)
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn(fn, *args, world=2):
+    mp.spawn(_run, args=(world, _free_port(), fn, args), nprocs=world, join=True)
+
+
+# ---------------------------------------------------------------------------------------------
+def test_permute_pad_plan_layout():
+    c = torch.tensor([[3, 0, 130], [2, 0, 1]])        # 2 sources x 3 local experts
+    index, inverse, offs = D.permute_pad_plan(c, 128)
+    assert offs.tolist() == [128, 128, 128 + 256]
+    assert index.numel() == 384 and inverse.numel() == 136
+    # expert 0: 3 rows of source 0 (receive rows 0..2) then 2 rows of source 1 (rows 133, 134)
+    assert index[:5].tolist() == [0, 1, 2, 133, 134] and (index[5:128] == -1).all()
+    # expert 2 starts at 128: 130 rows of source 0 (receive rows 3..132) then row 135 of source 1
+    assert index[128:258].tolist() == list(range(3, 133)) and index[258].item() == 135
+    assert (index[259:] == -1).all()
+    ok = index >= 0
+    assert torch.equal(inverse[index[ok].long()].long(), torch.nonzero(ok).squeeze(1))
+    # no rows at all
+    index, inverse, offs = D.permute_pad_plan(torch.zeros(2, 3, dtype=torch.int64))
+    assert index.numel() == 0 and inverse.numel() == 0 and offs.tolist() == [0, 0, 0]
+
+
+def _experts(x_local, offs, W):
+    """Per-expert matmul over runs given by cumulative `offs` (padding rows are zeros in, zeros out)."""
+    out = x_local.new_zeros(x_local.shape[0], W.shape[-1])
+    start = 0
+    for e in range(offs.numel()):
+        end = int(offs[e])
+        out[start:end] = x_local[start:end] @ W[e]
+        start = end
+    return out
+
+
+def _ep_worker(rank, world, num_experts, T, k, Dm, Do):
+    g = torch.Generator().manual_seed(100 + rank)
+    gw = torch.Generator().manual_seed(7)
+    W = torch.randn(num_experts, Dm, Do, generator=gw, dtype=torch.float64)
+    x = torch.randn(T, Dm, generator=g, dtype=torch.float64, requires_grad=True)
+    logits = torch.randn(T, num_experts, generator=g, dtype=torch.float64)
+    scores, ids = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    d = D.ExpertParallelDispatcher(num_experts)
+    x_local, offs, st = d.dispatch(x, ids)
+    E_local = num_experts // world
+    assert offs.numel() == E_local and x_local.shape[0] == int(offs[-1])
+    counts = torch.diff(offs, prepend=offs.new_zeros(1))
+    assert (counts % 128 == 0).all()
+    W_local = W[rank * E_local:(rank + 1) * E_local]
+    h = _experts(x_local, offs.cpu(), W_local)
+    out = d.combine(h, st, scores)
+    # dense single-process reference on this rank's tokens
+    xr = x.detach().clone().requires_grad_(True)
+    ref = sum(scores[:, j:j + 1] * torch.einsum("td,tdo->to", xr, W[ids[:, j]]) for j in range(k))
+    assert torch.allclose(out, ref, rtol=1e-12, atol=1e-12)
+    wsum = torch.randn(T, Do, generator=g, dtype=torch.float64)
+    (out * wsum).sum().backward()
+    (ref * wsum).sum().backward()
+    assert torch.allclose(x.grad, xr.grad, rtol=1e-12, atol=1e-12)
+
+
+@pytest.mark.parametrize("num_experts,k", [(4, 2), (8, 4)])
+def test_expert_parallel_dispatch_combine_two_ranks(num_experts, k):
+    _spawn(_ep_worker, num_experts, 96, k, 16, 24)
+
+
+def test_expert_parallel_single_rank_matches_dense():
+    D.L.gather_rows, keep = _gather_rows_cpu, D.L.gather_rows
+    try:
+        g = torch.Generator().manual_seed(3)
+        W = torch.randn(4, 8, 8, generator=g, dtype=torch.float64)
+        x = torch.randn(40, 8, generator=g, dtype=torch.float64)
+        ids = torch.randint(0, 4, (40, 2), generator=g)
+        d = D.ExpertParallelDispatcher(4)
+        xl, offs, st = d.dispatch(x, ids)
+        out = d.combine(_experts(xl, offs, W), st, None)
+        ref = sum(torch.einsum("td,tdo->to", x, W[ids[:, j]]) for j in range(2))
+        assert torch.allclose(out, ref, rtol=1e-12, atol=1e-12)
+    finally:
+        D.L.gather_rows = keep
+
+
+def _column_worker(rank, world):
+    g = torch.Generator().manual_seed(5)  # replicated inputs
+    x = torch.randn(24, 32, generator=g, dtype=torch.float64, requires_grad=True)
+    W = torch.randn(64, 32, generator=g, dtype=torch.float64)
+    dy = torch.randn(24, 64, generator=g, dtype=torch.float64)
+    w_r = D.shard_rows(W).clone().requires_grad_(True)
+    n = 64 // world
+    y_r = D.column_sharded_linear(x, w_r, torch.nn.functional.linear)
+    assert torch.allclose(y_r, (x.detach() @ W.t())[:, rank * n:(rank + 1) * n])
+    y_r.backward(dy[:, rank * n:(rank + 1) * n])
+    assert torch.allclose(x.grad, dy @ W, rtol=1e-12, atol=1e-12)             # summed over the shards
+    assert torch.allclose(w_r.grad, (dy.t() @ x.detach())[rank * n:(rank + 1) * n])
+    with pytest.raises(RuntimeError):
+        D.shard_rows(torch.zeros(48, 8))  # 24 rows per rank: not a multiple of 32
+
+
+def test_column_sharded_linear_two_ranks():
+    _spawn(_column_worker)
+
+
+def _allreduce_worker(rank, world):
+    ps = [torch.nn.Parameter(torch.zeros(n)) for n in (10, 1000, 7)]
+    for i, p in enumerate(ps):
+        p.grad = torch.full_like(p, float(rank + 1 + i))
+    ps.append(torch.nn.Parameter(torch.zeros(3)))  # no grad: skipped
+    n = D.allreduce_gradients(ps, bucket_bytes=4032)
+    assert n == 2  # 40 B | 4000 B + 28 B: the second tensor does not fit beside the first
+    for i, p in enumerate(ps[:3]):
+        assert torch.allclose(p.grad, torch.full_like(p, (1 + i + 2 + i) / 2))
+
+
+def test_bucketed_gradient_allreduce_two_ranks():
+    _spawn(_allreduce_worker)

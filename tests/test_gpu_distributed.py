@@ -1,0 +1,160 @@
+"""GPU tests of the multi-GPU forms of the path.
+
+One GPU: the row-gather kernel, and the expert-parallel dispatcher with a single rank feeding the
+grouped GEMMs.  Two GPUs (skipped when fewer are visible): two NCCL ranks as child processes --
+the column-sharded MXFP8 linear (dgrad all-reduce) and the expert-parallel MoE (two all-to-alls
+each way) against single-GPU runs of the same kernels.  NVLS is switched off in the children: a
+rank that dies while bound to an NVLink multicast object can fault its peers."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda")
+
+
+@pytest.mark.parametrize("dtype,cols", [(torch.bfloat16, 2880), (torch.float32, 20), (torch.uint8, 48)])
+def test_gather_rows_matches_index_select(dtype, cols):
+    from alto_b200 import _lib as L
+    g = torch.Generator().manual_seed(0)
+    src = (torch.randn(300, cols, generator=g) * 50).to(dtype).cuda()
+    index = torch.randint(-1, 300, (1000,), generator=g, dtype=torch.int32)
+    index[5] = 300      # out of range -> zero row
+    out = L.gather_rows(src, index.cuda())
+    idx = index.long()
+    ok = (idx >= 0) & (idx < 300)
+    want = torch.where(ok.unsqueeze(1).cuda(), src[idx.clamp(0, 299).cuda()], torch.zeros((), dtype=dtype, device="cuda"))
+    assert torch.equal(out, want)
+    assert L.gather_rows(src, index[:0].cuda()).shape == (0, cols)
+    with pytest.raises(L.Altob200Error):
+        L.gather_rows(src[:, :cols - 1].contiguous(), index.cuda())  # rows not a multiple of 16 bytes
+
+
+def _moe(x, ids, scores, W13, W2, dispatcher):
+    from alto_b200.grouped import _quantize_then_mxfp8_scaled_grouped_mm as gmm
+    xl, offs, st = dispatcher.dispatch(x, ids)
+    h = gmm(xl, W13.transpose(-2, -1), offs)
+    h = torch.nn.functional.silu(h)
+    y = gmm(h, W2.transpose(-2, -1), offs)
+    return dispatcher.combine(y, st, scores)
+
+
+def _moe_inputs(seed, T, D, H, E, k, dev):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, D, generator=g).bfloat16().to(dev)
+    logits = torch.randn(T, E, generator=g)
+    scores, ids = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    gw = torch.Generator().manual_seed(99)
+    W13 = (torch.randn(E, H, D, generator=gw) * 0.05).bfloat16().to(dev)
+    W2 = (torch.randn(E, D, H, generator=gw) * 0.05).bfloat16().to(dev)
+    return x, ids.to(dev), scores.bfloat16().to(dev), W13, W2
+
+
+def test_single_rank_dispatcher_feeds_grouped_gemms():
+    """dispatch -> grouped MXFP8 GEMMs -> combine equals the same GEMMs on rows sorted and padded by
+    hand with tensor ops, bit for bit, and gradients reach the tokens."""
+    from alto_b200.distributed import ExpertParallelDispatcher
+    from alto_b200.grouped import _quantize_then_mxfp8_scaled_grouped_mm as gmm
+    d = _dev()
+    T, D, H, E, k = 512, 256, 384, 4, 2
+    x, ids, scores, W13, W2 = _moe_inputs(1, T, D, H, E, k, d)
+    x.requires_grad_(True)
+    out = _moe(x, ids, scores, W13, W2, ExpertParallelDispatcher(E))
+    out.float().sum().backward()
+    assert out.shape == (T, D) and torch.isfinite(out).all() and torch.isfinite(x.grad).all()
+    # by hand
+    flat = ids.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=E)
+    padded = (counts + 127) // 128 * 128
+    offs = torch.cumsum(padded, 0).to(torch.int32)
+    rows = x.detach()[order // k]
+    xl = torch.zeros(int(offs[-1]), D, dtype=x.dtype, device=d)
+    start_sorted = torch.cumsum(counts, 0) - counts
+    start_pad = torch.cumsum(padded, 0) - padded
+    e_of = flat[order]
+    dst = start_pad[e_of] + (torch.arange(order.numel(), device=d) - start_sorted[e_of])
+    xl[dst] = rows
+    y = gmm(torch.nn.functional.silu(gmm(xl, W13.transpose(-2, -1), offs)), W2.transpose(-2, -1), offs)
+    routed = torch.empty(T * k, D, dtype=y.dtype, device=d)
+    routed[order] = y[dst]
+    want = (routed.view(T, k, D) * scores.unsqueeze(-1)).sum(1)
+    assert torch.equal(out.detach(), want)
+
+
+# ---------------------------------------------------------------------------------------------
+# two ranks over NCCL
+# ---------------------------------------------------------------------------------------------
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _two_rank_worker(rank, world, port):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from alto_b200 import distributed as D
+        from alto_b200 import mxfp8 as M8
+        fn = lambda a, b: M8._to_mxfp8_then_scaled_mm(a, b, "e4m3", False, False, True)  # noqa: E731
+        # ---- column-sharded MXFP8 linear ----
+        g = torch.Generator().manual_seed(5)
+        x = torch.randn(256, 512, generator=g).bfloat16().to(dev).requires_grad_(True)
+        W = (torch.randn(256, 512, generator=g) * 0.05).bfloat16().to(dev)
+        dy = torch.randn(256, 256, generator=g).bfloat16().to(dev)
+        n = 256 // world
+        w_r = D.shard_rows(W).clone().requires_grad_(True)
+        y_r = D.column_sharded_linear(x, w_r, fn)
+        y_r.backward(dy[:, rank * n:(rank + 1) * n])
+        # single-GPU runs of every shard on this rank: forward identical, dgrad = sum of the partials
+        partial = []
+        for r in range(world):
+            xs = x.detach().clone().requires_grad_(True)
+            ws = W[r * n:(r + 1) * n].clone().requires_grad_(True)
+            ys = fn(xs, ws)
+            ys.backward(dy[:, r * n:(r + 1) * n])
+            partial.append(xs.grad)
+            if r == rank:
+                assert torch.equal(ys, y_r) and torch.equal(ws.grad, w_r.grad)
+        want = (partial[0].float() + partial[1].float())
+        assert torch.allclose(x.grad.float(), want, rtol=2e-2, atol=1e-2 * want.abs().max().item())
+        # ---- expert-parallel MoE: every rank has its own tokens ----
+        import tests.test_gpu_distributed as T_
+        xt, ids, scores, W13, W2 = T_._moe_inputs(10 + rank, 384, 256, 384, 4, 2, dev)
+        xt.requires_grad_(True)
+        E_local = 4 // world
+        ep = D.ExpertParallelDispatcher(4)
+        out = T_._moe(xt, ids, scores, W13[rank * E_local:(rank + 1) * E_local],
+                      W2[rank * E_local:(rank + 1) * E_local], ep)
+        out.float().sum().backward()
+        # the same tokens through all four experts on this GPU alone: forward and the token gradient
+        # are row-local (row-wise MXFP8 blocks), hence bit-identical
+        x1 = xt.detach().clone().requires_grad_(True)
+        one = D.ExpertParallelDispatcher.__new__(D.ExpertParallelDispatcher)
+        one.group, one.world, one.rank, one.num_experts, one.local_experts, one.align = None, 1, 0, 4, 4, 128
+        out1 = T_._moe(x1, ids, scores, W13, W2, one)
+        out1.float().sum().backward()
+        assert torch.equal(out, out1)
+        assert torch.equal(xt.grad, x1.grad)
+        # ---- bucketed gradient all-reduce ----
+        p = torch.nn.Parameter(torch.zeros(1000, device=dev))
+        p.grad = torch.full_like(p, float(rank))
+        assert D.allreduce_gradients([p]) == 1 and torch.allclose(p.grad, torch.full_like(p, 0.5))
+        torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_nccl_column_sharded_and_expert_parallel():
+    import torch.multiprocessing as mp
+    mp.spawn(_two_rank_worker, args=(2, _free_port()), nprocs=2, join=True)
