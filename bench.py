@@ -50,6 +50,12 @@ CONFIG = {
     "overlap": "two quantizers run on a side stream beside the fprop and wgrad GEMMs (ALTO_B200_OVERLAP=0 disables)",
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM bytes (read + write) per GEMM launch at the default shape, from the one-pass ncu capture
+# summarised under profiles/: (79.2+181.7 + 91.1+80.4 + 126.0+45.4) MB / 3.  Part of each output is
+# still in the write-back L2 when the kernel ends, so this is below the algorithmic figure.
+GEMM_DRAM_BYTES_PER_LAUNCH = 201.3e6
+# codes + packed scales of both operands + bf16 output, mean of fprop / wgrad / dgrad
+GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (52.0e6 + 234.9e6 + 84.9e6 + 117.4e6 + 99.1e6 + 67.1e6) / 3
 CPU_SAMPLE_ROWS = 256      # token rows of the CPU sample
 CPU_SAMPLE_FEATS = 1024    # output features (rows of W) of the CPU sample
 
@@ -335,9 +341,14 @@ def run_ours(args):
                              "gbs": d["work"] / d["launches"] / (avg_ms * 1e-3) / 1e9,
                              "frac_of_hbm_peak": d["work"] / d["launches"] / (avg_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     fp4_peak = 4.0 * peaks["bf16_tflops_sustained"]
+    default_shape = (M, K, N) == (8192, 4096, 14336)
     gemm_tf = kernels["gemm"]["tflops"]
     roofline = {"bound": "tensor", "achieved": gemm_tf, "peak": fp4_peak, "unit": "TFLOP/s",
-                "frac": gemm_tf / fp4_peak, "traffic": None,
+                "frac": gemm_tf / fp4_peak, "traffic": GEMM_DRAM_BYTES_PER_LAUNCH if default_shape else None,
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one-pass capture of this "
+                                  "command, mean of the step's three GEMM launches "
+                                  "(profiles/launch_list_nvfp4_linear_bench.md); algorithmic operand + output "
+                                  f"bytes per launch {GEMM_ALGORITHMIC_BYTES_PER_LAUNCH:.4g}",
                 "kernel": "gemm_blockscaled_kernel<NVF4,256> (3 launches per step, 962 GFLOP each)",
                 "peak_source": f"4 x {peak_src} sustained bf16 cuBLAS throughput (dense FP4 proxy); nominal dense FP4 9000"}
 
