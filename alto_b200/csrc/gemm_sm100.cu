@@ -26,6 +26,7 @@
 // {kernel, block, site} in a device status word, raises a CTA-wide abort flag, and all
 // roles fall through to the common teardown that frees tensor memory.
 #include <cuda.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -37,6 +38,7 @@ __device__ int g_status[4] = {0, 0, 0, 0};
 constexpr int BM = 128;
 constexpr int STAGE_K_BYTES = 128;
 constexpr int NUM_THREADS = 320;  // producer, MMA issuer, 4 epilogue warps, 4 scale-transfer warps
+constexpr int NUM_THREADS_PAIR = 448;  // pair kernel: 4 more epilogue warps (each group drains 128 columns)
 constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // 4 s per wait
 
 enum { KIND_NVF4 = 0, KIND_MXF4 = 1, KIND_MXF8 = 2 };
@@ -218,6 +220,21 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+#define ALTOB200_R8(r, o) "=r"(r[o]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]), \
+                         "=r"(r[o + 6]), "=r"(r[o + 7])
+__device__ __forceinline__ void tc_ld64(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : ALTOB200_R8(r, 0), ALTOB200_R8(r, 8), ALTOB200_R8(r, 16), ALTOB200_R8(r, 24), ALTOB200_R8(r, 32),
+        ALTOB200_R8(r, 40), ALTOB200_R8(r, 48), ALTOB200_R8(r, 56)
+      : "r"(taddr)
+      : "memory");
+}
+#undef ALTOB200_R8
 __device__ __forceinline__ void tc_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c),
                "r"(d)
@@ -242,6 +259,108 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
   d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
   return d;
 }
+// ---------------------------------------------------------------------------------------
+// epilogue of one tile for one warp (its 32 accumulator rows), shared by both kernels
+// ---------------------------------------------------------------------------------------
+// The accumulator is drained in units of one 128-byte output row chunk (64 bf16 or 32 fp32 columns).
+// The tensor-memory load of unit c+1 is in flight while unit c is scaled, converted, written to the
+// 128-byte-swizzled staging buffer and handed to a TMA store; `release` (the arrival that gives the
+// accumulator back to the MMA issuer) runs as soon as the last load has landed, before the last unit
+// is converted.  Two 4 KB staging buffers per warp alternate; `store_it` carries the alternation
+// across tiles.
+template <int BN, class Release>
+__device__ __forceinline__ void epilogue_tile(uint32_t t_acc, bool have_acc, float alpha, bool out_bf16,
+                                              uint8_t* epi_warp, int lane, const CUtensorMap* tmap_d, int64_t row0,
+                                              int64_t col_base, int batch, int64_t M, int64_t N, bool store_enabled,
+                                              bool convert_enabled, uint32_t& store_it, Release release) {
+  const uint32_t my_row = smem_u32(epi_warp) + (uint32_t)lane * 128u;  // this lane's 128-byte row (buffer 0)
+  const uint32_t sw = (uint32_t)(lane & 7);                            // 16-byte chunk c -> c ^ (row & 7)
+  auto stage_and_store = [&](int c, int cols_per_unit) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    const int64_t col0 = col_base + (int64_t)c * cols_per_unit;
+    if (lane == 0 && row0 < M && col0 < N && store_enabled) {
+      tma_store_3d(epi_warp + (store_it & 1u) * 4096u, tmap_d, (int32_t)col0, (int32_t)row0, batch);
+      bulk_commit();
+    }
+    ++store_it;
+  };
+  if (out_bf16) {
+    // loads of 32 columns (half an output row chunk), two register buffers; a store every second load
+    constexpr int NC = BN / 32;
+    uint32_t rb[2][32];
+    if (have_acc) tc_ld32(t_acc, rb[0]);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      uint32_t* r = rb[c & 1];
+      const int h = c & 1;
+      if (have_acc) {
+        tc_wait_ld();
+        if (c + 1 < NC) {
+          tc_ld32(t_acc + (c + 1) * 32, rb[(c + 1) & 1]);
+        } else {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) release();
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = 0u;
+      }
+      if (h == 0) {
+        // the TMA store issued two chunks ago from this buffer must have finished reading it
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+      }
+      const uint32_t buf = my_row + (store_it & 1u) * 4096u;
+      if (convert_enabled)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          // one packed conversion per pair (round to nearest even, low half = first element)
+          const __nv_bfloat162 p2 = __floats2bfloat162_rn(__fmul_rn(u2f(r[8 * j + 2 * q]), alpha),
+                                                          __fmul_rn(u2f(r[8 * j + 2 * q + 1]), alpha));
+          o[q] = *reinterpret_cast<const uint32_t*>(&p2);
+        }
+        st_shared_v4(buf + ((((uint32_t)(h * 4 + j)) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+      }
+      if (h == 1) stage_and_store(c >> 1, 64);
+    }
+  } else {
+    constexpr int NC = BN / 32;
+    uint32_t rb[2][32];
+    if (have_acc) tc_ld32(t_acc, rb[0]);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      uint32_t* r = rb[c & 1];
+      if (have_acc) {
+        tc_wait_ld();
+        if (c + 1 < NC) {
+          tc_ld32(t_acc + (c + 1) * 32, rb[(c + 1) & 1]);
+        } else {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) release();
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = 0u;
+      }
+      if (lane == 0) bulk_wait_read<1>();
+      __syncwarp();
+      const uint32_t buf = my_row + (store_it & 1u) * 4096u;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        st_shared_v4(buf + ((((uint32_t)j) ^ sw) << 4), f2u(__fmul_rn(u2f(r[4 * j]), alpha)),
+                     f2u(__fmul_rn(u2f(r[4 * j + 1]), alpha)), f2u(__fmul_rn(u2f(r[4 * j + 2]), alpha)),
+                     f2u(__fmul_rn(u2f(r[4 * j + 3]), alpha)));
+      stage_and_store(c, 32);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------------------
@@ -524,61 +643,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         ++tile_it;
         continue;
       }
-#pragma unroll 1
-      for (int cc = 0; cc < n_chunks; ++cc, ++store_it) {
-        const uint32_t buf_off = (store_it & 1u) * 4096u;
-        // the TMA store issued two chunks ago from this buffer must have finished reading it
-        if (lane == 0) bulk_wait_read<1>();
-        __syncwarp();
-        uint32_t r[32];
-        if (args.out_bf16) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (!pad_group) {
-              tc_ld32(t_acc + cc * 64 + h * 32, r);
-              tc_wait_ld();
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) r[j] = 0u;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint32_t o[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                o[q] = f32_to_bf16_bits(__fmul_rn(u2f(r[8 * j + 2 * q]), alpha)) |
-                       (f32_to_bf16_bits(__fmul_rn(u2f(r[8 * j + 2 * q + 1]), alpha)) << 16);
-              st_shared_v4(my_row + buf_off + ((((uint32_t)(h * 4 + j)) ^ sw) << 4), o[0], o[1], o[2], o[3]);
-            }
-          }
-        } else {
-          if (!pad_group) {
-            tc_ld32(t_acc + cc * 32, r);
-            tc_wait_ld();
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = 0u;
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            st_shared_v4(my_row + buf_off + ((((uint32_t)j) ^ sw) << 4), f2u(__fmul_rn(u2f(r[4 * j]), alpha)),
-                         f2u(__fmul_rn(u2f(r[4 * j + 1]), alpha)), f2u(__fmul_rn(u2f(r[4 * j + 2]), alpha)),
-                         f2u(__fmul_rn(u2f(r[4 * j + 3]), alpha)));
-        }
-        if (cc == n_chunks - 1 && !pad_group) {
-          // all of this warp's reads of the accumulator are done
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        const int64_t col0 = nb * BN + (int64_t)cc * CH;
-        if (lane == 0 && row0 < args.M && col0 < args.N && !(args.debug & 2)) {
-          tma_store_3d(epi + (warp - 2) * 8192 + buf_off, &tmap_d, (int32_t)col0, (int32_t)row0, ti.batch);
-          bulk_commit();
-        }
-      }
+      epilogue_tile<BN>(t_acc, !pad_group, alpha, args.out_bf16 != 0, epi + (warp - 2) * 8192, lane, &tmap_d, row0,
+                        nb * BN, ti.batch, args.M, args.N, !(args.debug & 2), !(args.debug & 32), store_it,
+                        [&]() { mbar_arrive(&acc_empty[acc]); });
       if (!pad_group) ++tile_it;
     }
     if (lane == 0) bulk_wait_all();
@@ -590,6 +657,336 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// CTA-pair kernel (tcgen05 cta_group::2)
+// ---------------------------------------------------------------------------------------
+// Two CTAs of a cluster share one 256 x 256 output tile: CTA r of the pair holds rows
+// [128 r, 128 r + 128) of A, rows [128 r, 128 r + 128) of the B tile (half of its 256 N-columns) and,
+// in its own tensor memory, the accumulator of its 128 output rows over all 256 columns.  One
+// thread of the even CTA (the leader) issues every MMA for both; the instruction reads A and the
+// B halves from both CTAs' shared memory at the same offsets.  Per 128x256x64 of work a CTA thus
+// reads 8 KB of shared memory instead of 12 KB, and TMA writes 8 KB instead of 12 KB, which is what
+// bounds the single-CTA kernel.  Scale factors: every CTA needs SFA of its own rows and SFB of all
+// 256 columns in its own tensor memory; its scale-transfer warps put them there as before.
+//
+// Synchronisation (all mbarriers live in shared memory of the CTA named):
+//   full[s]     leader   operand bytes of both CTAs (TMA from the peer completes on the leader's barrier)
+//   sfs_full[s] each CTA its own scale bytes, for its scale-transfer warps
+//   sf_full[s]  leader   8 arrivals: the 4 scale-transfer warps of each CTA
+//   empty[s]    each CTA arrival by the leader's commit (sent to both CTAs)
+//   acc_full    each CTA arrival by the leader's commit (sent to both CTAs)
+//   acc_empty   leader   16 arrivals: the 8 epilogue warps of each CTA
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Arrival without a cluster-scope release.  What the waiting side consumes after these arrivals
+// is tensor memory, whose writes (tcgen05.st) and reads (tcgen05.ld) the arriving warp has already
+// completed with tcgen05.wait and ordered with tcgen05.fence::before_thread_sync; a release fence at
+// cluster scope in front of every arrival costs about a microsecond per stage (measured).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// tiled load into this CTA's shared memory whose bytes complete on a barrier given as a
+// shared::cluster address (the leader's)
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
+// arrival on the barrier at this offset in both CTAs of the pair once all prior MMAs of this thread finish
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(mask)
+      : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate, uint32_t sfa, uint32_t sfb) {
+  if (KIND == KIND_NVF4) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else if (KIND == KIND_MXF4) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  }
+}
+
+template <int KIND>
+struct CfgPair {
+  static constexpr int BN = 256;                             // columns of the pair's tile
+  static constexpr int SF_TILES = Kind<KIND>::SF_TILES;
+  static constexpr int NB = 2;                               // 128-row blocks of B scales (all 256 columns)
+  static constexpr int A_BYTES = BM * STAGE_K_BYTES;         // this CTA's 128 rows of A
+  static constexpr int B_BYTES = 128 * STAGE_K_BYTES;        // this CTA's half of the B tile
+  static constexpr int SFA_BYTES = SF_TILES * 512;
+  static constexpr int SFB_BYTES = NB * SF_TILES * 512;
+  static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024 * 1024;
+  static constexpr int SF_COLS_A = SF_TILES * 4;
+  static constexpr int SF_COLS_B = SF_TILES * 4 * NB;
+  static constexpr int STAGES = 4;
+  static constexpr int EPI_WARPS = 8;                        // two warps per tensor-memory lane quarter
+  static constexpr int EPI_BYTES = EPI_WARPS * 2 * 4096;
+  static constexpr int TMEM_SF_BASE = BN;
+  static constexpr int TMEM_COLS_USED = TMEM_SF_BASE + STAGES * (SF_COLS_A + SF_COLS_B);
+  static_assert(TMEM_COLS_USED <= 512, "tensor memory budget");
+  static constexpr int NUM_BARS = 5 * STAGES + 2;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+template <int KIND, bool OUT_BF16>
+__global__ void __launch_bounds__(NUM_THREADS_PAIR, 1)
+gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                             const __grid_constant__ CUtensorMap tmap_d, const GemmArgs args) {
+  using C = CfgPair<KIND>;
+  constexpr int BN = C::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi = smem + C::STAGES * C::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + C::EPI_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + C::STAGES;
+  uint64_t* sfs_full = bars + 2 * C::STAGES;
+  uint64_t* sf_full = bars + 3 * C::STAGES;
+  uint64_t* acc_full = bars + 4 * C::STAGES;
+  uint64_t* acc_empty = acc_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();      // 0 = leader
+  const bool leader = rank == 0;
+  const int64_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int64_t tiles_m = (args.M + 2 * BM - 1) / (2 * BM);    // tiles of 256 rows
+  const int64_t tiles_n = (args.N + BN - 1) / BN;
+  const int64_t n_tiles = tiles_m * tiles_n * (args.k_offs != nullptr ? args.num_batches : 1);
+  const int k_stages = (int)((args.k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES);
+  const int64_t n_row_blocks = (args.N + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+      mbar_init(&sfs_full[s], 1);
+      mbar_init(&sf_full[s], 8);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 2 * C::EPI_WARPS);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int s = 0; s < C::STAGES; ++s) {
+    uint32_t* z = reinterpret_cast<uint32_t*>(smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+    for (int i = threadIdx.x; i < (C::SFA_BYTES + C::SFB_BYTES) / 4; i += NUM_THREADS_PAIR) z[i] = 0u;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) {
+    // both CTAs of the pair execute the paired allocation, with the same destination offset
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers are initialised before anything can arrive on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ producer (each CTA loads its own halves) ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int64_t tile = pair; tile < n_tiles && alive; tile += n_pairs) {
+        const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+        if (ti.skip) continue;
+        const int64_t mb = ti.mb * 2 + rank;          // this CTA's 128-row block of A
+        const int64_t nb = ti.nb;
+        int nb_valid = (int)(n_row_blocks - nb * C::NB);
+        if (nb_valid > C::NB) nb_valid = C::NB;
+        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+          const int s = it % C::STAGES;
+          if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 11)) { alive = false; break; }
+          uint8_t* st = smem + s * C::STAGE_BYTES;
+          const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
+          int64_t sf_tiles = args.nct - cb0;
+          if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
+          const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
+          const int32_t kx = (int32_t)(ti.k_byte0 + (int64_t)ks * STAGE_K_BYTES);
+          // a CTA whose rows of A lie past M has no scale row block to load; its rows are never stored
+          const bool sfa_exists = mb * BM < args.M;
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * (C::A_BYTES + C::B_BYTES));
+          mbar_expect_tx(&sfs_full[s], sf_bytes * ((sfa_exists ? 1 : 0) + nb_valid));
+          const uint32_t full_leader = mapa_u32(smem_u32(&full_bar[s]), 0);
+          tma_load_2d_pair(st, &tmap_a, kx, (int32_t)(mb * BM), full_leader);
+          tma_load_2d_pair(st + C::A_BYTES, &tmap_b, kx, (int32_t)(ti.b_row0 + rank * 128), full_leader);
+          if (sfa_exists)
+            bulk_load(st + C::A_BYTES + C::B_BYTES, args.sfa + (mb * args.nct + cb0) * 512, sf_bytes, &sfs_full[s]);
+#pragma unroll
+          for (int j = 0; j < C::NB; ++j)
+            if (j < nb_valid)
+              bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + j * C::SFA_BYTES,
+                        ti.sfb + ((nb * C::NB + j) * args.nct + cb0) * 512, sf_bytes, &sfs_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (lane == 0 && leader) {
+      uint32_t it = 0, tile_it = 0;
+      bool alive = true;
+      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t idesc[4] = {args.idesc[0], args.idesc[1], args.idesc[2], args.idesc[3]};
+      for (int64_t tile = pair; tile < n_tiles && alive; tile += n_pairs) {
+        const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+        if (ti.skip) continue;
+        if (!mbar_wait(acc_empty, (tile_it & 1) ^ 1, abort_flag, 12)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base;
+        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+          const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
+          const int s = it % C::STAGES;
+          if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 13)) { alive = false; break; }
+          if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 15)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;
+          const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
+          const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
+          const uint32_t a_lo = st4 | 0x10000u;
+          const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int t = (KIND == KIND_NVF4) ? j : (KIND == KIND_MXF4 ? (j >> 1) : 0);
+            if (j < n_mma)
+              tc_mma_pair<KIND>(d_tmem, desc_of(DESC_SW128_HI, a_lo + 2 * j), desc_of(DESC_SW128_HI, b_lo + 2 * j),
+                                idesc[j], (ks | j) != 0 ? 1u : 0u, sfa_t + t * 4, sfb_t + t * 4 * C::NB);
+          }
+          tc_commit_pair(&empty_bar[s]);
+        }
+        if (alive) tc_commit_pair(acc_full);
+        ++tile_it;
+      }
+    }
+  } else if (warp >= 6 && warp < 10) {
+    // ------------------------------ scale transfer (each CTA into its own tensor memory) ------------------------------
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t it = 0;
+    bool alive = true;
+    for (int64_t tile = pair; tile < n_tiles && alive; tile += n_pairs) {
+      const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+      if (ti.skip) continue;
+      for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+        const int s = it % C::STAGES;
+        if (!mbar_wait(&sfs_full[s], (it / C::STAGES) & 1, abort_flag, 16)) { alive = false; break; }
+        const uint8_t* sf = smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
+        const uint32_t sfa_t = tmem_base + lane_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
+        const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
+#pragma unroll
+        for (int t = 0; t < C::SF_TILES; ++t) {
+          const uint4 a = *reinterpret_cast<const uint4*>(sf + t * 512);
+          tc_st4(sfa_t + t * 4, a.x, a.y, a.z, a.w);
+#pragma unroll
+          for (int j = 0; j < C::NB; ++j) {
+            const uint4 b = *reinterpret_cast<const uint4*>(sf + C::SFA_BYTES + j * C::SFA_BYTES + t * 512);
+            tc_st4(sfb_t + t * 4 * C::NB + j * 4, b.x, b.y, b.z, b.w);
+          }
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(&sf_full[s]);
+          else mbar_arrive_cluster_relaxed(mapa_u32(smem_u32(&sf_full[s]), 0));
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (each CTA stores its own 128 rows) ------------------------------
+    // Warps 2-5 drain columns [0, 128) of the accumulator, warps 10-13 columns [128, 256); a warp may
+    // read the tensor-memory lane quarter (warp index mod 4).
+    const int quad = warp & 3;
+    const int half = warp >= 10 ? 1 : 0;
+    const int epi_idx = half * 4 + (warp - (half ? 10 : 2));
+    float alpha = 1.0f;
+    if (args.alpha_a != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_a));
+    if (args.alpha_b != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_b));
+    const uint32_t acc_empty_leader = mapa_u32(smem_u32(acc_empty), 0);
+    uint32_t tile_it = 0, store_it = 0;
+    for (int64_t tile = pair; tile < n_tiles; tile += n_pairs) {
+      const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+      const int64_t nb = ti.nb;
+      const int64_t row0 = (ti.mb * 2 + rank) * BM + quad * 32;
+      const bool pad_group = ti.skip;
+      if (!pad_group) {
+        if (!mbar_wait(acc_full, tile_it & 1, abort_flag, 14)) break;
+        tc_fence_after();
+      }
+      const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 128;
+      if ((args.debug & 8) && !pad_group) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(acc_empty);
+          else mbar_arrive_cluster_relaxed(acc_empty_leader);
+        }
+        ++tile_it;
+        continue;
+      }
+      epilogue_tile<128>(t_acc, !pad_group, alpha, OUT_BF16, epi + epi_idx * 8192, lane, &tmap_d, row0,
+                         nb * BN + half * 128, ti.batch, args.M, args.N, !(args.debug & 2), !(args.debug & 32),
+                         store_it, [&]() {
+                           if (leader) mbar_arrive(acc_empty);
+                           else mbar_arrive_cluster_relaxed(acc_empty_leader);
+                         });
+      if (!pad_group) ++tile_it;
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+
+  // ------------------------------ teardown ------------------------------
+  // Neither CTA may leave while its peer can still arrive on its barriers or read its shared memory.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
   }
 }
 
@@ -644,7 +1041,7 @@ static int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t row
 
 // Instruction descriptor of a block-scaled MMA (bit layout: b_sf_id [4,6), a_format [7,10),
 // b_format [10,13), n/8 [17,23), scale format [23], m/16 [24,29), a_sf_id [29,31)).
-static uint32_t make_idesc(int kind, int fmt_a, int fmt_b, int n, int sf_id) {
+static uint32_t make_idesc(int kind, int fmt_a, int fmt_b, int m, int n, int sf_id) {
   uint32_t af, bf, sfmt;
   if (kind == KIND_MXF8) {
     af = fmt_a == ALTOB200_FMT_MXFP8_E5M2 ? 1u : 0u;
@@ -660,7 +1057,7 @@ static uint32_t make_idesc(int kind, int fmt_a, int fmt_b, int n, int sf_id) {
   d |= bf << 10;
   d |= (uint32_t)(n >> 3) << 17;
   d |= sfmt << 23;
-  d |= (uint32_t)(BM >> 4) << 24;
+  d |= (uint32_t)(m >> 4) << 24;
   d |= (uint32_t)sf_id << 29;
   return d;
 }
@@ -692,6 +1089,46 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 
+// CTA-pair kernel: clusters of two CTAs, as many clusters as the device can hold at once.
+template <int KIND, bool OUT_BF16>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmArgs& args,
+                            cudaStream_t st) {
+  using C = CfgPair<KIND>;
+  static int max_clusters = 0;  // 0 = not asked yet, < 0 = the device cannot run the pair kernel
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NUM_THREADS_PAIR, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_clusters == 0) {
+    ALTOB200_CUDA_CHECK(cudaFuncSetAttribute(gemm_blockscaled_pair_kernel<KIND, OUT_BF16>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    cfg.gridDim = dim3(2 * (unsigned)sm_count_gemm(), 1, 1);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_blockscaled_pair_kernel<KIND, OUT_BF16>, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      max_clusters = -1;
+    } else {
+      max_clusters = n;
+    }
+    if (args.debug & 16) fprintf(stderr, "altob200: pair kernel, %d clusters of 2 resident\n", max_clusters);
+  }
+  if (max_clusters < 0) return ALTOB200_EUNSUPPORTED;
+  const int64_t tiles =
+      ceil_div(args.M, 2 * BM) * ceil_div(args.N, C::BN) * (args.k_offs != nullptr ? args.num_batches : 1);
+  int64_t clusters = max_clusters;
+  if (clusters > tiles) clusters = tiles;
+  cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, OUT_BF16>, ta, tb, td, args);
+  return e == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
 static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N, int64_t K, int32_t num_experts,
                        const void* a_codes, const void* a_scales, const void* b_codes, const void* b_scales,
                        const int32_t* group_expert, const float* alpha_a, const float* alpha_b,
@@ -720,11 +1157,20 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
     return ALTOB200_ELIMIT;
 
   const int BN = N <= 128 ? 128 : 256;
+  // The CTA-pair kernel serves dense and K-range problems; rows grouped by expert in runs of 128
+  // could put two experts' rows into one 256-row pair tile, so that mode stays on the single-CTA
+  // kernel.  ALTOB200_GEMM_PAIR=0 forces the single-CTA kernel everywhere.
+  static int pair_env = -1;
+  if (pair_env < 0) {
+    const char* e = getenv("ALTOB200_GEMM_PAIR");
+    pair_env = e ? atoi(e) : 1;
+  }
+  const bool use_pair = pair_env != 0 && num_experts == 0 && N > 128 && M > 128;
   const int64_t b_rows = N * (num_experts > 0 ? num_experts : 1);
   CUtensorMap ta, tb;
   int rc = make_tmap(&ta, a_codes, M, k_bytes, BM);
   if (rc != ALTOB200_OK) return rc;
-  rc = make_tmap(&tb, b_codes, b_rows, k_bytes, BN);
+  rc = make_tmap(&tb, b_codes, b_rows, k_bytes, use_pair ? 128 : BN);
   if (rc != ALTOB200_OK) return rc;
   CUtensorMap td;
   rc = make_tmap_out(&td, d, k_offs != nullptr ? num_batches : 1, M, N, ldd, out_dtype == ALTOB200_DT_BF16);
@@ -743,8 +1189,8 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
     // Measured on B200 at 8192x4096x14336 and 14336x4096x8192 (NVFP4): groups of 6-8 row tiles are
     // 8 % faster than walking the whole M axis first (which re-reads A once per wave); 2-4 and 12-16
     // are within 3 % of that; the short-K fprop shape does not care.
-    const int64_t tiles_m = ceil_div(M, BM);
-    int64_t gm = 8;
+    const int64_t tiles_m = ceil_div(M, use_pair ? 2 * BM : BM);
+    int64_t gm = use_pair ? 4 : 8;
     static int gm_env = -1;
     if (gm_env < 0) {
       const char* e = getenv("ALTOB200_GEMM_GROUP_M");
@@ -760,7 +1206,7 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
   }
   for (int j = 0; j < 4; ++j) {
     const int sf_id = kind == KIND_NVF4 ? 0 : (kind == KIND_MXF4 ? (j & 1) * 2 : j);
-    g.idesc[j] = make_idesc(kind, format_a, format_b, BN, sf_id);
+    g.idesc[j] = make_idesc(kind, format_a, format_b, use_pair ? 2 * BM : BM, BN, sf_id);
   }
   static int debug_flags = -1;
   if (debug_flags < 0) {
@@ -769,6 +1215,17 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
   }
   g.debug = debug_flags;
   cudaStream_t st = (cudaStream_t)stream;
+  if (use_pair) {
+    const bool obf = g.out_bf16 != 0;
+    switch (kind) {
+      case KIND_NVF4: return obf ? launch_gemm_pair<KIND_NVF4, true>(ta, tb, td, g, st)
+                                 : launch_gemm_pair<KIND_NVF4, false>(ta, tb, td, g, st);
+      case KIND_MXF4: return obf ? launch_gemm_pair<KIND_MXF4, true>(ta, tb, td, g, st)
+                                 : launch_gemm_pair<KIND_MXF4, false>(ta, tb, td, g, st);
+      default: return obf ? launch_gemm_pair<KIND_MXF8, true>(ta, tb, td, g, st)
+                          : launch_gemm_pair<KIND_MXF8, false>(ta, tb, td, g, st);
+    }
+  }
 #define LAUNCH(KD)                                                    \
   return BN == 128 ? launch_gemm<KD, 128>(ta, tb, td, g, st) : launch_gemm<KD, 256>(ta, tb, td, g, st)
   switch (kind) {

@@ -769,17 +769,29 @@ __global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
     const int64_t vec_per_row = a.cols / vec;
     const int64_t total = a.rows * vec_per_row;
     const bool dense = a.ld == a.cols;  // contiguous rows: no index arithmetic per load
-#pragma unroll 4
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
+    auto load = [&](int64_t i) -> uint4 {
       int64_t off = i * vec;
       if (!dense) {
         int64_t row, cv;
         divmod_fast(i, vec_per_row, &row, &cv);
         off = row * a.ld + cv * vec;
       }
-      const uint4 w = __ldg(reinterpret_cast<const uint4*>(
-          reinterpret_cast<const uint8_t*>(a.x) + off * (IN_BF16 ? 2 : 4)));
+      return __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.x) + off * (IN_BF16 ? 2 : 4)));
+    };
+    // four independent 16-byte loads are issued before any of them is consumed: the pass is a pure
+    // stream and needs bytes in flight, not arithmetic
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i0 < total; i0 += 4 * stride) {
+      uint4 wv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t i = i0 + u * stride;
+        wv[u] = i < total ? load(i) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+      const uint4 w = wv[u];
       if (IN_BF16) {
         uint32_t acc = absmax_bf16x2(0, w.x);
         acc = absmax_bf16x2(acc, w.y);
@@ -794,6 +806,7 @@ __global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
           const uint32_t b = ws[j] & 0x7FFFFFFFu;
           am_plain = b > am_plain ? b : am_plain;
         }
+      }
       }
     }
   } else {
