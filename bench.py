@@ -349,7 +349,7 @@ def run_ours(args):
                                   "command, mean of the step's three GEMM launches "
                                   "(profiles/launch_list_nvfp4_linear_bench.md); algorithmic operand + output "
                                   f"bytes per launch {GEMM_ALGORITHMIC_BYTES_PER_LAUNCH:.4g}",
-                "kernel": "gemm_blockscaled_kernel<NVF4,256> (3 launches per step, 962 GFLOP each)",
+                "kernel": "gemm_blockscaled_pair_kernel<NVF4,bf16> (tcgen05 cta_group::2; 3 launches per step, 962 GFLOP each)",
                 "peak_source": f"4 x {peak_src} sustained bf16 cuBLAS throughput (dense FP4 proxy); nominal dense FP4 9000"}
 
     # ---- end to end through the public API with host buffers ----
