@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "altob200_quantize_2d",
     "altob200_dequantize",
     "altob200_rht",
+    "altob200_rht_dense",
     "altob200_macro_block_scaling",
     "altob200_macro_block_descaling",
     "altob200_gather_rows",
@@ -114,6 +115,8 @@ def _declare_more(lib):
     lib.altob200_macro_block_scaling.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, vp]
     lib.altob200_macro_block_descaling.restype = C.c_int
     lib.altob200_macro_block_descaling.argtypes = [vp, vp, i32, i64, i64, i64, i32, vp, vp]
+    lib.altob200_rht_dense.restype = C.c_int
+    lib.altob200_rht_dense.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i64, vp]
     lib.altob200_gather_rows.restype = C.c_int
     lib.altob200_gather_rows.argtypes = [vp, i64, i64, vp, i64, vp, vp]
 
@@ -295,6 +298,15 @@ def rht_apply(x, y, rht: Rht) -> None:
     _check(lib().altob200_rht(x.data_ptr(), _dt(x.dtype), x.shape[0], x.shape[1], x.stride(0), rht.n, rht._perm_c,
                               rht._sign_c, y.data_ptr(), y.stride(0), _stream()),
            "altob200_rht")
+
+
+def rht_dense(x, y, w: torch.Tensor) -> None:
+    """y = cast((w @ x_block) / sqrt(n)) over row blocks of n = w.shape[0] in {16, 32, 64}; w: fp32 device."""
+    _require_cuda(x, y, w)
+    assert x.dim() == 2 and x.stride(1) == 1 and y.stride(1) == 1 and x.dtype == y.dtype
+    assert w.dtype == torch.float32 and w.is_contiguous() and w.dim() == 2 and w.shape[0] == w.shape[1]
+    _check(lib().altob200_rht_dense(x.data_ptr(), _dt(x.dtype), x.shape[0], x.shape[1], x.stride(0), w.shape[0],
+                                    w.data_ptr(), y.data_ptr(), y.stride(0), _stream()), "altob200_rht_dense")
 
 
 MACRO_LAST, MACRO_2D, MACRO_ROWS = 0, 1, 2

@@ -159,7 +159,27 @@ def check_dims(name: str, M: int, K: int, N: int) -> None:
         "in blocks along the token axis and stored in 16-byte aligned rows"))
 
 
-def forward_operands(x2, w2, fmt, *, use_2dblock_x, use_2dblock_w, use_outer_scale, rht):
+def split_transform(hadamard_transform, use_2dblock_x: bool):
+    """-> (rht, dense): launch parameters for the quantizers' fused 16-point butterfly, or the
+    transform object itself when it has to run as its own (dense) kernel; both None without one."""
+    if hadamard_transform is None or use_2dblock_x:
+        return None, None
+    if hadamard_transform.is_fused:
+        return hadamard_transform.device_params(), None
+    return None, hadamard_transform
+
+
+def cols_operand(t2, fmt, use_outer_scale, o, rht, dense, sr: dict) -> Operand:
+    """t2 quantised along its token axis after the optional rotation.  ``o`` = outer_scales(t2, .., rht)."""
+    if dense is not None:
+        th = dense(t2, left_mul=True)          # bf16(H t), as the reference materialises it
+        oh = outer_scales(th, use_outer_scale, None)
+        return quant_cols(th, fmt, None if oh is None else oh[0:1], None, sr)
+    o_m = None if o is None else (o[1:2] if rht is not None else o[0:1])
+    return quant_cols(t2, fmt, o_m, rht, sr)
+
+
+def forward_operands(x2, w2, fmt, *, use_2dblock_x, use_2dblock_w, use_outer_scale, rht, dense=None):
     """Returns (x_k, x_m, w_k, w_t): X along K (fprop), X along M after the optional Hadamard
     rotation (wgrad), W along K (fprop), W along N (dgrad)."""
     ox = outer_scales(x2, use_outer_scale, None if use_2dblock_x else rht)
@@ -168,8 +188,7 @@ def forward_operands(x2, w2, fmt, *, use_2dblock_x, use_2dblock_w, use_outer_sca
         x_k, x_m = quant_2d(x2, fmt, None if ox is None else ox[0:1], True)
     else:
         x_k = quant_rows(x2, fmt, None if ox is None else ox[0:1], RTN)
-        o_m = None if ox is None else (ox[1:2] if rht is not None else ox[0:1])
-        x_m = quant_cols(x2, fmt, o_m, rht, RTN)
+        x_m = cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, RTN)
     if use_2dblock_w:
         w_k, w_t = quant_2d(w2, fmt, None if ow is None else ow[0:1], True)
     else:
@@ -178,7 +197,7 @@ def forward_operands(x2, w2, fmt, *, use_2dblock_x, use_2dblock_w, use_outer_sca
     return x_k, x_m, w_k, w_t
 
 
-def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, rht):
+def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, rht, dense=None):
     """dY along N for dgrad and (after the optional Hadamard rotation) along M for wgrad."""
     M, N = g2.shape
     og = outer_scales(g2, use_outer_scale, None if use_2dblock_x else rht)
@@ -187,8 +206,7 @@ def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, r
             raise NotImplementedError("stochastic rounding with use_2dblock_x=True is not implemented")
         return quant_2d(g2, fmt, None if og is None else og[0:1], True)
     g_n = quant_rows(g2, fmt, None if og is None else og[0:1], sr_args(use_sr_grad, "dy_n", M, N, g2.device))
-    o_m = None if og is None else (og[1:2] if rht is not None else og[0:1])
-    g_m = quant_cols(g2, fmt, o_m, rht, sr_args(use_sr_grad, "dy_m", N, M, g2.device))
+    g_m = cols_operand(g2, fmt, use_outer_scale, og, rht, dense, sr_args(use_sr_grad, "dy_m", N, M, g2.device))
     return g_n, g_m
 
 
@@ -231,9 +249,9 @@ def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock
     M, K = x2.shape
     N = w2.shape[0]
     check_dims(name, M, K, N)
-    rht = hadamard_transform.device_params() if (hadamard_transform is not None and not use_2dblock_x) else None
+    rht, dense = split_transform(hadamard_transform, use_2dblock_x)
     ctx.xm_ready = None
-    if OVERLAP and not use_2dblock_x:
+    if OVERLAP and not use_2dblock_x and dense is None:
         main = torch.cuda.current_stream(x2.device)
         side = _side_stream(x2.device)
         ox = outer_scales(x2, use_outer_scale, rht)
@@ -257,7 +275,7 @@ def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock
         _keep_for(main, x_m.codes, x_m.scales)
     else:
         x_k, x_m, w_k, w_t = forward_operands(x2, w2, fmt, use_2dblock_x=use_2dblock_x, use_2dblock_w=use_2dblock_w,
-                                              use_outer_scale=use_outer_scale, rht=rht)
+                                              use_outer_scale=use_outer_scale, rht=rht, dense=dense)
         y = gemm(x_k, w_k, x.dtype)
     extra_x = [x_m.outer] if x_m.outer is not None else []
     extra_w = [w_t.outer] if w_t.outer is not None else []
@@ -268,6 +286,7 @@ def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock
     ctx.use_sr_grad = use_sr_grad
     ctx.use_outer_scale = use_outer_scale
     ctx.rht = rht
+    ctx.dense_transform = dense
     return y.view(*original_shape[:-1], N)
 
 
@@ -288,7 +307,7 @@ def linear_backward(ctx, grad_output):
         main.wait_event(ctx.xm_ready)
     need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
     grad_inputs = grad_weights = None
-    if OVERLAP and not ctx.use_2dblock_x and need_dx and need_dw:
+    if OVERLAP and not ctx.use_2dblock_x and need_dx and need_dw and ctx.dense_transform is None:
         fmt, rht = ctx.fmt, ctx.rht
         side = _side_stream(g2.device)
         og = outer_scales(g2, ctx.use_outer_scale, rht)
@@ -310,7 +329,7 @@ def linear_backward(ctx, grad_output):
         grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
         return grad_inputs, grad_weights
     g_n, g_m = backward_operands(g2, ctx.fmt, use_2dblock_x=ctx.use_2dblock_x, use_sr_grad=ctx.use_sr_grad,
-                                 use_outer_scale=ctx.use_outer_scale, rht=ctx.rht)
+                                 use_outer_scale=ctx.use_outer_scale, rht=ctx.rht, dense=ctx.dense_transform)
     if need_dx:
         grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
     if need_dw:

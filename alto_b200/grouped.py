@@ -105,12 +105,11 @@ class GroupedLinearFunction(torch.autograd.Function):
         w3 = weights.detach().contiguous()
         offs32 = offs.to(torch.int32).contiguous()
         group_expert = group_experts_from_offsets(offs32, M)
-        rht = hadamard_transform.device_params() if hadamard_transform is not None else None
+        rht, dense = E.split_transform(hadamard_transform, False)
 
         ox = E.outer_scales(x2, use_outer_scale, rht)
         x_k = E.quant_rows(x2, fmt, None if ox is None else ox[0:1], E.RTN)
-        o_m = None if ox is None else (ox[1:2] if rht is not None else ox[0:1])
-        x_m = E.quant_cols(x2, fmt, o_m, rht, E.RTN)
+        x_m = E.cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, E.RTN)
         w_k, w_t = _quant_weight_stack(w3, fmt, use_2dblock_w, use_outer_scale)
         y = _grouped_gemm(x_k, w_k, N, n_exp, group_expert, inputs.dtype)
 
@@ -119,7 +118,7 @@ class GroupedLinearFunction(torch.autograd.Function):
         ctx.save_for_backward(x_m.codes, x_m.scales, *extra_x, w_t.codes, w_t.scales, *extra_w, group_expert, offs32)
         ctx.dims = (M, K, N, n_exp)
         ctx.fmt, ctx.fmt_grad = fmt, fmt_grad
-        ctx.use_sr_grad, ctx.use_outer_scale, ctx.rht = use_sr_grad, use_outer_scale, rht
+        ctx.use_sr_grad, ctx.use_outer_scale, ctx.rht, ctx.dense_transform = use_sr_grad, use_outer_scale, rht, dense
         return y
 
     @staticmethod
@@ -136,8 +135,8 @@ class GroupedLinearFunction(torch.autograd.Function):
         og = E.outer_scales(g2, ctx.use_outer_scale, ctx.rht)
         g_n = E.quant_rows(g2, ctx.fmt_grad, None if og is None else og[0:1],
                            E.sr_args(ctx.use_sr_grad, "dy_n", M, N, g2.device))
-        o_m = None if og is None else (og[1:2] if ctx.rht is not None else og[0:1])
-        g_m = E.quant_cols(g2, ctx.fmt_grad, o_m, ctx.rht, E.sr_args(ctx.use_sr_grad, "dy_m", N, M, g2.device))
+        g_m = E.cols_operand(g2, ctx.fmt_grad, ctx.use_outer_scale, og, ctx.rht, ctx.dense_transform,
+                             E.sr_args(ctx.use_sr_grad, "dy_m", N, M, g2.device))
         grad_inputs = grad_weights = None
         if ctx.needs_input_grad[0]:
             grad_inputs = _grouped_gemm(g_n, w_t, K, n_exp, group_expert, grad_output.dtype)

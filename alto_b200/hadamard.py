@@ -10,7 +10,10 @@ which the +-1 row-sign vector and then the permutation are drawn, and
 The CUDA kernels take the transform as (n, perm, sign): for the Sylvester base matrix
 ``weight = diag(sign) @ H_n`` (alto/kernels/hadamard_transform/hadamard.py:130-161), so
 ``y[i] = sign[perm[i]] * (H_n z)[perm[i]]`` with ``z[perm[j]] = x[j]`` and the product by
-H_n is an in-register butterfly.  n = 16 is implemented on the device; other sizes raise.
+H_n is an in-register butterfly fused into the quantizers (n = 16).  Every other matrix of size
+16, 32 (the reference's default, a table matrix that is not of Sylvester type) or 64 runs through
+a dense transform kernel that materialises bf16(H x), as the reference does, followed by a plain
+quantizer; other sizes raise.
 """
 from __future__ import annotations
 
@@ -125,6 +128,8 @@ class HadamardTransform:
         self.perm = perm
         self._scale = torch.tensor(weight.size(0), dtype=torch.float64).sqrt()
         self._rht: Optional[L.Rht] = None
+        self._fusable: Optional[bool] = None
+        self._dev = {}
 
     @property
     def n(self) -> int:
@@ -136,21 +141,39 @@ class HadamardTransform:
             w = w[self.perm][:, self.perm]
         return w
 
+    @property
+    def is_fused(self) -> bool:
+        """True when the quantizer kernels can apply the transform themselves: a row-signed
+        Sylvester matrix of size 16 (in-register butterfly).  Any other matrix of size 16, 32 or 64
+        goes through the dense transform kernel followed by a plain quantizer."""
+        if self._fusable is None:
+            ok = self.n == 16
+            if ok:
+                w = self.weight.detach().float().cpu()
+                ok = bool(torch.equal(torch.diag(w[:, 0]) @ w, _sylvester(16)))
+            self._fusable = ok
+        return self._fusable
+
     def device_params(self) -> L.Rht:
-        """(n, perm, sign) for the kernels; raises when the weight is not diag(sign) @ Sylvester_16."""
+        """(n, perm, sign) for the fused kernels; raises when the transform is not fusable."""
         if self._rht is None:
+            if not self.is_fused:
+                raise NotImplementedError("this Hadamard matrix is not a row-signed Sylvester matrix of size 16; "
+                                          "use the transform itself (dense kernel)")
             n = self.n
-            if n != 16:
-                raise NotImplementedError(
-                    f"the device Hadamard transform is implemented for block_size 16, got {n} "
-                    "(configure HadamardFactory(block_size=16))")
-            w = self.weight.detach().float().cpu()
-            sign = w[:, 0].clone()
-            if not torch.equal(torch.diag(sign) @ w, _sylvester(n)):
-                raise NotImplementedError("Hadamard weight is not a row-signed Sylvester matrix")
+            sign = self.weight.detach().float().cpu()[:, 0].clone()
             perm = self.perm.cpu().tolist() if self.perm is not None else list(range(n))
             self._rht = L.Rht(n, perm, [int(v) for v in sign.tolist()])
         return self._rht
+
+    def device_matrix(self, device) -> Tensor:
+        """weight[perm][:, perm] as fp32 on ``device`` (uploaded once per transform and device)."""
+        key = str(device)
+        if key not in self._dev:
+            if self.n not in (16, 32, 64):
+                raise NotImplementedError(f"Hadamard block sizes 16, 32 and 64 are implemented, got {self.n}")
+            self._dev[key] = self.matrix().detach().float().contiguous().to(device)
+        return self._dev[key]
 
     def __call__(self, value: Tensor, inverse: bool = False, left_mul: bool = False) -> Tensor:
         if not value.is_cuda:
@@ -158,8 +181,13 @@ class HadamardTransform:
         if inverse or not left_mul:
             raise NotImplementedError("only left_mul=True, inverse=False is on the low-precision linear path")
         assert value.dim() == 2, "left_mul expects a [tokens, hidden] matrix"
+        torch._check(value.shape[0] % self.n == 0,
+                     lambda: f"the token count ({value.shape[0]}) must be a multiple of the Hadamard size {self.n}")
         x = value if (value.stride(1) == 1 and (value.stride(0) * value.element_size()) % 16 == 0) \
             else value.contiguous()
         y = torch.empty_like(x, memory_format=torch.contiguous_format)
-        L.rht_apply(x, y, self.device_params())
+        if self.is_fused:
+            L.rht_apply(x, y, self.device_params())
+        else:
+            L.rht_dense(x, y, self.device_matrix(x.device))
         return y

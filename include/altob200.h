@@ -220,6 +220,17 @@ int altob200_rht(const void* x, int32_t dtype, int64_t rows, int64_t cols, int64
                  int64_t ld_y, void* stream);
 
 /*
+ * The same transform with an arbitrary n x n matrix W = weight[perm][:, perm] given on the
+ * device (fp32, row-major), n in {16, 32, 64}: y = cast((W x_block) * fp32(1 / sqrt(n))), the
+ * way PyTorch evaluates the reference's division by the 0-dim sqrt(n) tensor on CUDA
+ * (alto/kernels/hadamard_transform/transform.py:115-142; matrix construction
+ * alto/kernels/hadamard_transform/hadamard.py:63-161, whose table matrices, e.g. the default
+ * n = 32, are not of Sylvester type).  rows must be a multiple of n.
+ */
+int altob200_rht_dense(const void* x, int32_t dtype, int64_t rows, int64_t cols, int64_t ld, int32_t n,
+                       const float* w, void* y, int64_t ld_y, void* stream);
+
+/*
  * Macro-block two-level scaling for MXFP4: before the E8M0 quantiser, each block of 128
  * elements is multiplied by a factor in [1, 2) whose top 8 mantissa bits are those of
  * 6 / amax(block); the 8 bits are stored as one uint8 per block.  Replaces macro_block_scaling

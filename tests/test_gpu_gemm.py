@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from oracle import alto_oracle as O
-from tests.helpers import rand_u32, reference_data
+from tests.helpers import load_golden, rand_u32, reference_data
 
 pytestmark = pytest.mark.gpu
 REL_TOL = 1e-3
@@ -176,6 +176,35 @@ def test_nvfp4_linear_matches_oracle(M, K, N, use_2dblock_w):
     assert _rel(y, yo.bfloat16().float()) <= REL_TOL
     assert _rel(xd.grad, dxo.bfloat16().float()) <= REL_TOL
     assert _rel(wd.grad, dwo.bfloat16().float()) <= REL_TOL
+
+
+def test_nvfp4_linear_with_default_hadamard_size_32():
+    """The reference's default HadamardFactory block size is 32, whose table matrix is not of
+    Sylvester type: the rotation runs as the dense kernel and materialises bf16(H x) like the
+    reference; everything downstream is identical to the oracle's operands."""
+    from alto_b200 import nvfp4 as NV
+    M, K, N = 256, 512, 384
+    NV.HadamardFactory.configure(block_size=32, randomized=True, dtype=torch.float32, seed=0)
+    try:
+        z, _ = load_golden()
+        W = torch.from_numpy(z["rht32_W"])
+        x = reference_data((M, K), torch.float32, 41, outliers=False).bfloat16()
+        w = (reference_data((N, K), torch.float32, 42, outliers=False) * 0.02).bfloat16()
+        dy = (reference_data((M, N), torch.float32, 43, outliers=False) * 1e-3).bfloat16()
+        rn, rm = rand_u32((2, M, N // 2), 51), rand_u32((2, N, M // 2), 52)
+        yo, dxo, dwo = O.nvfp4_linear(x, w, dy, use_2dblock_w=True, W_had=W, rand_dy_n=rn, rand_dy_m=rm)
+        d = _dev()
+        xd = x.to(d).requires_grad_(True)
+        wd = w.to(d).requires_grad_(True)
+        bits = {"dy_n": _u32dev(rn), "dy_m": _u32dev(rm)}
+        with NV.explicit_sr_bits(lambda name, shape, dev: bits[name]):
+            y = NV._to_nvfp4_then_scaled_mm(xd, wd, False, True, True, use_outer_scale=True, use_hadamard=True)
+            y.backward(dy.to(d))
+        assert _rel(y, yo.bfloat16().float()) <= REL_TOL
+        assert _rel(xd.grad, dxo.bfloat16().float()) <= REL_TOL
+        assert _rel(wd.grad, dwo.bfloat16().float()) <= REL_TOL
+    finally:
+        NV.HadamardFactory.configure(block_size=16)
 
 
 @pytest.mark.parametrize("scheme", ["nvfp4", "mxfp4", "mxfp8_e4m3", "mxfp8_e5m2"])

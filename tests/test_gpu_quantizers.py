@@ -124,10 +124,48 @@ def test_hadamard_factory_matches_reference_draws():
     x = tensor_from_bits(z["rht16_x"], torch.bfloat16).to(_dev())
     y = t(x, left_mul=True)
     assert np.array_equal(y.cpu().view(torch.int16).numpy().view(np.uint16), z["rht16_y"])
-    HadamardFactory.configure(block_size=32)
-    t32 = HadamardFactory.create_transform(device=_dev())
-    with pytest.raises(NotImplementedError):
-        t32(x, left_mul=True)
+    HadamardFactory.configure(block_size=16)
+
+
+@pytest.mark.parametrize("n", [16, 32])
+def test_dense_hadamard_kernel(n):
+    """The reference's default block size 32 uses a table matrix that is not of Sylvester type: the
+    dense transform kernel must give what the reference's own tensor ops give on this GPU (fp32 matmul,
+    division by the 0-dim sqrt(n) tensor, cast), bit for bit, and the oracle's restatement of it."""
+    from alto_b200 import _lib as L
+    from alto_b200.hadamard import HadamardFactory
+    z, _ = load_golden()
+    HadamardFactory.configure(block_size=n, randomized=True, dtype=torch.float32, seed=0)
+    t = HadamardFactory.create_transform(device=_dev())
+    W = torch.from_numpy(z[f"rht{n}_W"])
+    assert torch.equal(t.matrix().cpu(), W)
+    assert t.is_fused == (n == 16)
+    x = tensor_from_bits(z[f"rht{n}_x"], torch.bfloat16).to(_dev())
+    y = torch.empty_like(x)
+    L.rht_dense(x, y, W.to(_dev()))
+    want = O.rht_apply(x.cpu(), W)
+    assert torch.equal(y.cpu().view(torch.int16), want.view(torch.int16))
+    assert torch.equal(t(x, left_mul=True), y)   # fused butterfly (16) or dense kernel (32): same values
+    # the reference's formula with PyTorch's own CUDA kernels (transform.py:133-141)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        scale = torch.tensor(n, dtype=torch.float64).sqrt()
+        M_, N_ = x.shape
+        ref = ((W.to(_dev()).float() @ x.float().view(M_ // n, n, N_)) / scale).view(M_, N_).to(x.dtype)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert torch.equal(y, ref)
+    # vectors made on CPU (true division): identical for 16, within one bf16 ulp in rare places for 32
+    gold = tensor_from_bits(z[f"rht{n}_y"], torch.bfloat16)
+    d = (y.cpu().view(torch.int16).int() - gold.view(torch.int16).int()).abs()
+    assert d.max().item() <= (0 if n == 16 else 1) and (d != 0).float().mean().item() < 1e-3
+    HadamardFactory.configure(block_size=16)
+    # fp32 input and a ragged last column
+    xf = torch.randn(64, 37, device=_dev())
+    yf = torch.empty_like(xf)
+    L.rht_dense(xf, yf, W.to(_dev()))
+    assert torch.allclose(yf.cpu(), O.rht_apply(xf.cpu(), W), rtol=1e-6, atol=1e-6)
     HadamardFactory.configure(block_size=16, seed=0)
 
 

@@ -82,8 +82,14 @@ def test_hadamard_matches_reference(n):
     z, _ = load_golden()
     W = torch.from_numpy(z[f"rht{n}_W"])
     x = tensor_from_bits(z[f"rht{n}_x"], torch.bfloat16)
-    y = O.rht_apply(x, W)
+    # the vectors were made by the reference's code on CPU, where PyTorch divides by sqrt(n); on
+    # CUDA it multiplies by the reciprocal (the oracle's default).  Both must hold for n = 16; for
+    # n = 32 the two may differ by one bf16 ulp where the fp32 value sits on a rounding boundary.
+    y = O.rht_apply(x, W, cuda_division=False)
     assert np.array_equal(y.view(torch.int16).numpy().view(np.uint16), z[f"rht{n}_y"])
+    y_cuda = O.rht_apply(x, W)
+    diff = (y_cuda.view(torch.int16).int() - y.view(torch.int16).int()).abs()
+    assert diff.max().item() <= (0 if n == 16 else 1) and (diff != 0).float().mean().item() < 1e-3
     # the factory draws the sign vector first and the permutation second from one generator
     g = torch.Generator().manual_seed(0)
     base = None if n == 16 else _file_hadamard(32)
