@@ -213,13 +213,17 @@ def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, r
 # ---------------------------------------------------------------------------------------
 # overlap of quantizers (ALU work) with GEMMs (tensor-core work)
 # ---------------------------------------------------------------------------------------
-#: The persistent GEMM leaves the SMs' issue slots and ALUs almost idle, and a quantizer that
-#: needs little shared memory can be resident next to it.  With OVERLAP on, the quantizer whose
-#: output is not needed by the next GEMM is launched on a side stream right after that GEMM:
+#: With OVERLAP on, the quantizer whose output is not needed by the next GEMM is launched on a side
+#: stream right after that GEMM:
 #:   forward : fprop GEMM   ||  X along M (needed only in backward)
 #:   backward: wgrad GEMM   ||  dY along N (needed by the dgrad GEMM that follows)
-#: Results are identical; only the launch order differs.  ALTO_B200_OVERLAP=0 turns it off.
-OVERLAP = os.environ.get("ALTO_B200_OVERLAP", "1") != "0"
+#: Results are identical; only the launch order differs.  This paid off (1.72 -> 1.57 ms per bench
+#: step) while the GEMM was the 320-thread single-CTA kernel, next to which a quantizer CTA is
+#: resident on the same SM.  The CTA-pair GEMM takes a whole SM (448 threads x 128 registers), so a
+#: concurrent quantizer can only take SMs away from it, and its static tile schedule then waits for
+#: the clusters that started late: measured 1.58-1.73 ms with the side stream against 1.57 ms
+#: without.  Hence off by default; ALTO_B200_OVERLAP=1 turns it on.
+OVERLAP = os.environ.get("ALTO_B200_OVERLAP", "0") == "1"
 _side_streams = {}
 
 

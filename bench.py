@@ -47,13 +47,14 @@ CONFIG = {
     "shape": {"M": M, "K": K, "N": N},
     "l2_policy": "per-step inputs (400 MB) exceed the 126 MB L2; no explicit flush",
     "parallelism": "data-parallel replicas, one process per GPU, no data-path collective",
-    "overlap": "two quantizers run on a side stream beside the fprop and wgrad GEMMs (ALTO_B200_OVERLAP=0 disables)",
+    "overlap": "none: the 11 kernels of a step run back to back on one stream (ALTO_B200_OVERLAP=1 moves two "
+               "quantizers to a side stream; not faster with the CTA-pair GEMM)",
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes (read + write) per GEMM launch at the default shape, from the one-pass ncu capture
-# summarised under profiles/: (79.2+181.7 + 91.1+80.4 + 126.0+45.4) MB / 3.  Part of each output is
-# still in the write-back L2 when the kernel ends, so this is below the algorithmic figure.
-GEMM_DRAM_BYTES_PER_LAUNCH = 201.3e6
+# summarised under profiles/: (123.0+193.6 + 85.0+81.6 + 127.3+47.6) MB / 3.  Part of each output is
+# still in the write-back L2 when the kernel ends; part of each input is found there.
+GEMM_DRAM_BYTES_PER_LAUNCH = 219.3e6
 # codes + packed scales of both operands + bf16 output, mean of fprop / wgrad / dgrad
 GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (52.0e6 + 234.9e6 + 84.9e6 + 117.4e6 + 99.1e6 + 67.1e6) / 3
 CPU_SAMPLE_ROWS = 256      # token rows of the CPU sample
