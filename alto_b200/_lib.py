@@ -63,6 +63,8 @@ class QuantParams(C.Structure):
         ("rht_n", C.c_int32),
         ("rht_perm", C.POINTER(C.c_int32)),
         ("rht_sign", C.POINTER(C.c_int32)),
+        ("clip_mode", C.c_int32),
+        ("use_uos", C.c_int32),
     ]
 
 
@@ -198,8 +200,14 @@ class Rht:
         self._sign_c = _i32_array(self.sign)
 
 
-def _params(fmt, x, rounding, outer_scale, rand_bits, rht: Optional[Rht], flags, philox=(0, 0)) -> QuantParams:
+CLIP_MODES = {"none": 0, "static": 1, "dynamic": 2}
+
+
+def _params(fmt, x, rounding, outer_scale, rand_bits, rht: Optional[Rht], flags, philox=(0, 0),
+            clip_mode: str = "none", use_uos: bool = False) -> QuantParams:
     p = QuantParams()
+    p.clip_mode = CLIP_MODES[clip_mode]
+    p.use_uos = 1 if use_uos else 0
     p.format = fmt
     p.in_dtype = _dt(x.dtype)
     p.rounding = rounding
@@ -251,43 +259,44 @@ def amax_noalloc(x: torch.Tensor, amax_bits: torch.Tensor, outer_scale: Optional
 
 
 def quantize_rowwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, rounding=ROUND_RTN,
-                     outer_scale=None, rand_bits=None, philox=(0, 0)) -> None:
+                     outer_scale=None, rand_bits=None, philox=(0, 0), clip_mode="none", use_uos=False) -> None:
     _require_cuda(x, codes, scale_plain, scale_packed, outer_scale, rand_bits)
     assert x.dim() == 2 and x.stride(1) == 1
     flags = (SCALE_PLAIN if scale_plain is not None else 0) | (SCALE_PACKED if scale_packed is not None else 0)
-    p = _params(fmt, x, rounding, outer_scale, rand_bits, None, flags, philox)
+    p = _params(fmt, x, rounding, outer_scale, rand_bits, None, flags, philox, clip_mode, use_uos)
     _check(lib().altob200_quantize_rowwise(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), C.byref(p),
                                            codes.data_ptr(), _ptr(scale_plain), _ptr(scale_packed), _stream()),
            "altob200_quantize_rowwise")
 
 
 def quantize_colwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, rounding=ROUND_RTN,
-                     outer_scale=None, rand_bits=None, rht: Optional[Rht] = None, philox=(0, 0)) -> None:
+                     outer_scale=None, rand_bits=None, rht: Optional[Rht] = None, philox=(0, 0),
+                     clip_mode="none", use_uos=False) -> None:
     _require_cuda(x, codes, scale_plain, scale_packed, outer_scale, rand_bits)
     assert x.dim() == 2 and x.stride(1) == 1
     flags = (SCALE_PLAIN if scale_plain is not None else 0) | (SCALE_PACKED if scale_packed is not None else 0)
-    p = _params(fmt, x, rounding, outer_scale, rand_bits, rht, flags, philox)
+    p = _params(fmt, x, rounding, outer_scale, rand_bits, rht, flags, philox, clip_mode, use_uos)
     _check(lib().altob200_quantize_colwise(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), C.byref(p),
                                            codes.data_ptr(), _ptr(scale_plain), _ptr(scale_packed), _stream()),
            "altob200_quantize_colwise")
 
 
 def quantize_2d(w, fmt, codes_k, codes_t=None, scale_plain=None, scale_packed_k=None, scale_packed_t=None, *,
-                outer_scale=None) -> None:
+                outer_scale=None, clip_mode="none", use_uos=False) -> None:
     _require_cuda(w, codes_k, codes_t, scale_plain, scale_packed_k, scale_packed_t, outer_scale)
     assert w.dim() == 2 and w.stride(1) == 1
-    p = _params(fmt, w, ROUND_RTN, outer_scale, None, None, 0)
+    p = _params(fmt, w, ROUND_RTN, outer_scale, None, None, 0, (0, 0), clip_mode, use_uos)
     _check(lib().altob200_quantize_2d(w.data_ptr(), w.shape[0], w.shape[1], w.stride(0), C.byref(p),
                                       codes_k.data_ptr(), _ptr(codes_t), _ptr(scale_plain), _ptr(scale_packed_k),
                                       _ptr(scale_packed_t), _stream()),
            "altob200_quantize_2d")
 
 
-def dequantize(codes, scale_plain, fmt, is_2d, rows, cols, out, outer_scale=None) -> None:
+def dequantize(codes, scale_plain, fmt, is_2d, rows, cols, out, outer_scale=None, static_clip=False) -> None:
     _require_cuda(codes, scale_plain, out, outer_scale)
     assert out.dim() == 2 and out.stride(1) == 1
     _check(lib().altob200_dequantize(codes.data_ptr(), scale_plain.data_ptr(), _ptr(outer_scale), fmt,
-                                     1 if is_2d else 0, rows, cols, _dt(out.dtype), out.data_ptr(), out.stride(0),
+                                     (1 if is_2d else 0) | (2 if static_clip else 0), rows, cols, _dt(out.dtype), out.data_ptr(), out.stride(0),
                                      _stream()),
            "altob200_dequantize")
 

@@ -115,30 +115,31 @@ def _code_cols(fmt: int, n: int) -> int:
     return n // 2 if L.is_fp4(fmt) else n
 
 
-def quant_rows(x2, fmt, outer, sr: dict) -> Operand:
+def quant_rows(x2, fmt, outer, sr: dict, use_uos: bool = False) -> Operand:
     R, Cc = x2.shape
     codes = torch.empty(R, _code_cols(fmt, Cc), dtype=torch.uint8, device=x2.device)
     sf = _packed(R, Cc // L.block_of(fmt), x2.device)
-    L.quantize_rowwise(x2, fmt, codes, None, sf, outer_scale=outer, **sr)
+    L.quantize_rowwise(x2, fmt, codes, None, sf, outer_scale=outer, use_uos=use_uos, **sr)
     return Operand(codes, sf, outer, R, Cc, fmt)
 
 
-def quant_cols(x2, fmt, outer, rht, sr: dict) -> Operand:
+def quant_cols(x2, fmt, outer, rht, sr: dict, use_uos: bool = False, clip_mode: str = "none") -> Operand:
     R, Cc = x2.shape
     codes = torch.empty(Cc, _code_cols(fmt, R), dtype=torch.uint8, device=x2.device)
     sf = _packed(Cc, R // L.block_of(fmt), x2.device)
-    L.quantize_colwise(x2, fmt, codes, None, sf, outer_scale=outer, rht=rht, **sr)
+    L.quantize_colwise(x2, fmt, codes, None, sf, outer_scale=outer, rht=rht, use_uos=use_uos, clip_mode=clip_mode,
+                       **sr)
     return Operand(codes, sf, outer, Cc, R, fmt)
 
 
-def quant_2d(x2, fmt, outer, want_t: bool) -> Tuple[Operand, Optional[Operand]]:
+def quant_2d(x2, fmt, outer, want_t: bool, use_uos: bool = False) -> Tuple[Operand, Optional[Operand]]:
     R, Cc = x2.shape
     b = L.block_of(fmt)
     ck = torch.empty(R, _code_cols(fmt, Cc), dtype=torch.uint8, device=x2.device)
     sk = _packed(R, Cc // b, x2.device)
     ct = torch.empty(Cc, _code_cols(fmt, R), dtype=torch.uint8, device=x2.device) if want_t else None
     stt = _packed(Cc, R // b, x2.device) if want_t else None
-    L.quantize_2d(x2, fmt, ck, ct, None, sk, stt, outer_scale=outer)
+    L.quantize_2d(x2, fmt, ck, ct, None, sk, stt, outer_scale=outer, use_uos=use_uos)
     return Operand(ck, sk, outer, R, Cc, fmt), (Operand(ct, stt, outer, Cc, R, fmt) if want_t else None)
 
 
@@ -169,44 +170,50 @@ def split_transform(hadamard_transform, use_2dblock_x: bool):
     return None, hadamard_transform
 
 
-def cols_operand(t2, fmt, use_outer_scale, o, rht, dense, sr: dict) -> Operand:
-    """t2 quantised along its token axis after the optional rotation.  ``o`` = outer_scales(t2, .., rht)."""
+def cols_operand(t2, fmt, use_outer_scale, o, rht, dense, sr: dict, use_uos: bool = False,
+                 clip_mode: str = "none") -> Operand:
+    """t2 quantised along its token axis after the optional rotation.  ``o`` = outer_scales(t2, .., rht).
+    The MXFP4 clip mode applies to these operands only (alto/kernels/fp4/mxfp4/mxfp_linear.py:383-390, 491-498)."""
     if dense is not None:
         th = dense(t2, left_mul=True)          # bf16(H t), as the reference materialises it
         oh = outer_scales(th, use_outer_scale, None)
-        return quant_cols(th, fmt, None if oh is None else oh[0:1], None, sr)
+        return quant_cols(th, fmt, None if oh is None else oh[0:1], None, sr, use_uos, clip_mode)
     o_m = None if o is None else (o[1:2] if rht is not None else o[0:1])
-    return quant_cols(t2, fmt, o_m, rht, sr)
+    return quant_cols(t2, fmt, o_m, rht, sr, use_uos, clip_mode)
 
 
-def forward_operands(x2, w2, fmt, *, use_2dblock_x, use_2dblock_w, use_outer_scale, rht, dense=None):
+def forward_operands(x2, w2, fmt, *, use_2dblock_x, use_2dblock_w, use_outer_scale, rht, dense=None,
+                     use_uos=False, clip_mode="none"):
     """Returns (x_k, x_m, w_k, w_t): X along K (fprop), X along M after the optional Hadamard
     rotation (wgrad), W along K (fprop), W along N (dgrad)."""
     ox = outer_scales(x2, use_outer_scale, None if use_2dblock_x else rht)
     ow = outer_scales(w2, use_outer_scale, None)
     if use_2dblock_x:
-        x_k, x_m = quant_2d(x2, fmt, None if ox is None else ox[0:1], True)
+        x_k, x_m = quant_2d(x2, fmt, None if ox is None else ox[0:1], True, use_uos)
     else:
-        x_k = quant_rows(x2, fmt, None if ox is None else ox[0:1], RTN)
-        x_m = cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, RTN)
+        x_k = quant_rows(x2, fmt, None if ox is None else ox[0:1], RTN, use_uos)
+        x_m = cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, RTN, use_uos, clip_mode)
     if use_2dblock_w:
-        w_k, w_t = quant_2d(w2, fmt, None if ow is None else ow[0:1], True)
+        w_k, w_t = quant_2d(w2, fmt, None if ow is None else ow[0:1], True, use_uos)
     else:
-        w_k = quant_rows(w2, fmt, None if ow is None else ow[0:1], RTN)
-        w_t = quant_cols(w2, fmt, None if ow is None else ow[0:1], None, RTN)
+        w_k = quant_rows(w2, fmt, None if ow is None else ow[0:1], RTN, use_uos)
+        w_t = quant_cols(w2, fmt, None if ow is None else ow[0:1], None, RTN, use_uos)
     return x_k, x_m, w_k, w_t
 
 
-def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, rht, dense=None):
+def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, rht, dense=None, use_uos=False,
+                      clip_mode="none"):
     """dY along N for dgrad and (after the optional Hadamard rotation) along M for wgrad."""
     M, N = g2.shape
     og = outer_scales(g2, use_outer_scale, None if use_2dblock_x else rht)
     if use_2dblock_x:
         if use_sr_grad:
             raise NotImplementedError("stochastic rounding with use_2dblock_x=True is not implemented")
-        return quant_2d(g2, fmt, None if og is None else og[0:1], True)
-    g_n = quant_rows(g2, fmt, None if og is None else og[0:1], sr_args(use_sr_grad, "dy_n", M, N, g2.device))
-    g_m = cols_operand(g2, fmt, use_outer_scale, og, rht, dense, sr_args(use_sr_grad, "dy_m", N, M, g2.device))
+        return quant_2d(g2, fmt, None if og is None else og[0:1], True, use_uos)
+    g_n = quant_rows(g2, fmt, None if og is None else og[0:1], sr_args(use_sr_grad, "dy_n", M, N, g2.device),
+                     use_uos)
+    g_m = cols_operand(g2, fmt, use_outer_scale, og, rht, dense, sr_args(use_sr_grad, "dy_m", N, M, g2.device),
+                       use_uos, clip_mode)
     return g_n, g_m
 
 
@@ -243,7 +250,7 @@ def _keep_for(stream, *tensors) -> None:
 
 
 def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock_w, use_sr_grad, use_outer_scale,
-                   hadamard_transform):
+                   hadamard_transform, use_uos: bool = False, clip_mode: str = "none"):
     """Shared body of the three autograd ``forward`` methods."""
     if not x.is_cuda:
         raise RuntimeError(f"{name} runs on CUDA tensors only (no CPU fallback)")
@@ -255,7 +262,8 @@ def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock
     check_dims(name, M, K, N)
     rht, dense = split_transform(hadamard_transform, use_2dblock_x)
     ctx.xm_ready = None
-    if OVERLAP and not use_2dblock_x and dense is None:
+    plain = not use_uos and clip_mode == "none"
+    if OVERLAP and not use_2dblock_x and dense is None and plain:
         main = torch.cuda.current_stream(x2.device)
         side = _side_stream(x2.device)
         ox = outer_scales(x2, use_outer_scale, rht)
@@ -279,7 +287,8 @@ def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock
         _keep_for(main, x_m.codes, x_m.scales)
     else:
         x_k, x_m, w_k, w_t = forward_operands(x2, w2, fmt, use_2dblock_x=use_2dblock_x, use_2dblock_w=use_2dblock_w,
-                                              use_outer_scale=use_outer_scale, rht=rht, dense=dense)
+                                              use_outer_scale=use_outer_scale, rht=rht, dense=dense,
+                                              use_uos=use_uos, clip_mode=clip_mode)
         y = gemm(x_k, w_k, x.dtype)
     extra_x = [x_m.outer] if x_m.outer is not None else []
     extra_w = [w_t.outer] if w_t.outer is not None else []
@@ -291,6 +300,7 @@ def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock
     ctx.use_outer_scale = use_outer_scale
     ctx.rht = rht
     ctx.dense_transform = dense
+    ctx.use_uos, ctx.clip_mode = use_uos, clip_mode
     return y.view(*original_shape[:-1], N)
 
 
@@ -311,7 +321,8 @@ def linear_backward(ctx, grad_output):
         main.wait_event(ctx.xm_ready)
     need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
     grad_inputs = grad_weights = None
-    if OVERLAP and not ctx.use_2dblock_x and need_dx and need_dw and ctx.dense_transform is None:
+    plain = not ctx.use_uos and ctx.clip_mode == "none"
+    if OVERLAP and not ctx.use_2dblock_x and need_dx and need_dw and ctx.dense_transform is None and plain:
         fmt, rht = ctx.fmt, ctx.rht
         side = _side_stream(g2.device)
         og = outer_scales(g2, ctx.use_outer_scale, rht)
@@ -333,11 +344,15 @@ def linear_backward(ctx, grad_output):
         grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
         return grad_inputs, grad_weights
     g_n, g_m = backward_operands(g2, ctx.fmt, use_2dblock_x=ctx.use_2dblock_x, use_sr_grad=ctx.use_sr_grad,
-                                 use_outer_scale=ctx.use_outer_scale, rht=ctx.rht, dense=ctx.dense_transform)
+                                 use_outer_scale=ctx.use_outer_scale, rht=ctx.rht, dense=ctx.dense_transform,
+                                 use_uos=ctx.use_uos, clip_mode=ctx.clip_mode)
     if need_dx:
         grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
     if need_dw:
         grad_weights = gemm(g_m, x_m, grad_output.dtype)
+        if ctx.clip_mode == "static":
+            # both wgrad operands were scaled by 3/4 (alto/kernels/fp4/mxfp4/mxfp_linear.py:543-544)
+            grad_weights *= (16.0 / 9.0)
     return grad_inputs, grad_weights
 
 

@@ -35,8 +35,10 @@ def _rand_planes(rand_bits: Optional[torch.Tensor], rows: int, cols: int):
 
 def quantize(x: torch.Tensor, fmt: int, axis: int, is_2d: bool, *, outer_scale: Optional[torch.Tensor] = None,
              rounding: int = L.ROUND_RTN, rand_bits: Optional[torch.Tensor] = None, philox=(0, 0),
-             rht: Optional[L.Rht] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+             rht: Optional[L.Rht] = None, clip_mode: str = "none",
+             use_uos: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Returns (codes, plain scales) with the reference's logical shapes and transposed views."""
+    opts = dict(clip_mode=clip_mode, use_uos=use_uos)
     if not x.is_cuda:
         raise RuntimeError("alto_b200 quantizers run on CUDA tensors only (no CPU fallback)")
     block = L.block_of(fmt)
@@ -59,7 +61,7 @@ def quantize(x: torch.Tensor, fmt: int, axis: int, is_2d: bool, *, outer_scale: 
         scales = torch.empty(nb, M // block, N // block, dtype=scale_dtype, device=dev)
         for b in range(nb):
             L.quantize_2d(x3[b], fmt, codes_k[b], None if codes_t is None else codes_t[b], scales[b],
-                          outer_scale=outer_scale)
+                          outer_scale=outer_scale, **opts)
         if a == -1:
             codes = codes_k.reshape(*lead, M, codes_k.shape[-1])
         else:  # physical [N, M/2], returned as its transpose like the reference
@@ -75,7 +77,7 @@ def quantize(x: torch.Tensor, fmt: int, axis: int, is_2d: bool, *, outer_scale: 
         codes = torch.empty(R, N // 2 if fp4 else N, dtype=torch.uint8, device=dev)
         scales = torch.empty(R, N // block, dtype=scale_dtype, device=dev)
         L.quantize_rowwise(x2, fmt, codes, scales, None, rounding=rounding, outer_scale=outer_scale,
-                           rand_bits=_rand_planes(rand_bits, R, N), philox=philox)
+                           rand_bits=_rand_planes(rand_bits, R, N), philox=philox, **opts)
         return (codes.reshape(*x.shape[:-1], codes.shape[-1]).view(_CODE_DTYPE[fmt]),
                 scales.reshape(*x.shape[:-1], N // block))
 
@@ -91,14 +93,14 @@ def quantize(x: torch.Tensor, fmt: int, axis: int, is_2d: bool, *, outer_scale: 
             xb = xb.contiguous()
         L.quantize_colwise(xb, fmt, codes[b], scales[b], None, rounding=rounding, outer_scale=outer_scale,
                            rand_bits=None if rb is None else rb[:, b].contiguous(), rht=rht,
-                           philox=(philox[0], philox[1] + b * (N * M // 4)))
+                           philox=(philox[0], philox[1] + b * (N * M // 4)), **opts)
     codes = codes.reshape(*lead, N, codes.shape[-1]).transpose(-1, -2)
     scales = scales.reshape(*lead, N, M // block).transpose(-1, -2)
     return codes.view(_CODE_DTYPE[fmt]), scales
 
 
 def dequantize(codes: torch.Tensor, scales: torch.Tensor, fmt: int, axis: int, is_2d: bool, out_dtype: torch.dtype,
-               outer_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+               outer_scale: Optional[torch.Tensor] = None, static_clip: bool = False) -> torch.Tensor:
     if not codes.is_cuda:
         raise RuntimeError("alto_b200 dequantizers run on CUDA tensors only (no CPU fallback)")
     assert out_dtype in (torch.float32, torch.bfloat16)
@@ -120,5 +122,5 @@ def dequantize(codes: torch.Tensor, scales: torch.Tensor, fmt: int, axis: int, i
     out = torch.empty(c3.shape[0], c3.shape[1], cols, dtype=out_dtype, device=codes.device)
     osc = None if outer_scale is None else outer_scale.to(device=codes.device, dtype=torch.float32).reshape(1)
     for b in range(c3.shape[0]):
-        L.dequantize(c3[b], s3[b], fmt, is_2d, c3.shape[1], cols, out[b], osc)
+        L.dequantize(c3[b], s3[b], fmt, is_2d, c3.shape[1], cols, out[b], osc, static_clip)
     return out.reshape(*shp[:-1], cols).transpose(a, -1)

@@ -80,6 +80,64 @@ __device__ __forceinline__ BlockScale make_block_scale(uint32_t amax_abs_bits, b
   return s;
 }
 
+// ---------------------------------------------------------------------------------------
+// Options of the MXFP4 quantizer (alto/kernels/fp4/mxfp4/mxfp_quantization.py:29-95, 321-322;
+// arithmetic as in the reference's emulation, tests/unittest/mxfp4/utils.py:320-358, which works
+// in the input dtype: with bf16 inputs every intermediate is rounded to bf16).
+//   clip 1 (static) : elements are multiplied by 3/4 before encoding; the scale is unchanged
+//   clip 2 (dynamic): the scale is taken from 2.92247856/6 * std(block) + 1e-8 instead of the amax,
+//                     with target exponent 0 instead of 2
+//   uos             : scale = ceil(log2(amax / 7.25)) + 127 (128 for an all-zero block)
+// ---------------------------------------------------------------------------------------
+struct MxOpts {
+  int clip;
+  int uos;
+};
+
+template <bool IN_BF16>
+__device__ __forceinline__ float round_in(float v) {
+  return IN_BF16 ? u2f(f32_to_bf16_bits(v) << 16) : v;
+}
+
+// E8M0 byte of an MX block from its statistics.  `amax_abs_bits` as in make_block_scale; `sum` and
+// `sumsq` (of the squares rounded to the input dtype) over the n elements are used by clip 2 only.
+template <int FMT, bool IN_BF16>
+__device__ __forceinline__ BlockScale make_block_scale_opts(uint32_t amax_abs_bits, float sum, float sumsq, int n,
+                                                            MxOpts o) {
+  using F = Fmt<FMT>;
+  float max_abs = IN_BF16 ? u2f(amax_abs_bits << 16) : u2f(amax_abs_bits);
+  int tmax = F::TMAX;
+  if (o.clip == 2) {
+    const float inv_n = 1.0f / (float)n;
+    const float mean_sq = round_in<IN_BF16>(__fmul_rn(sumsq, inv_n));
+    const float mean = round_in<IN_BF16>(__fmul_rn(sum, inv_n));
+    const float var = round_in<IN_BF16>(__fsub_rn(mean_sq, round_in<IN_BF16>(__fmul_rn(mean, mean))));
+    const float sd = round_in<IN_BF16>(__fsqrt_rn(var));
+    max_abs = round_in<IN_BF16>(__fadd_rn(round_in<IN_BF16>(__fmul_rn(sd, (float)(2.92247856 / 6.0))), 1e-8f));
+    tmax = 0;
+  }
+  uint32_t e;
+  if (o.uos) {
+    const float r = round_in<IN_BF16>(__fdiv_rn(max_abs, 7.25f));
+    float s = ceilf(round_in<IN_BF16>(log2f(r)));
+    if (max_abs == 0.0f) s = 1.0f;
+    s += 127.0f;
+    // NaN compares false everywhere and converts to 0, which the clamp turns into 1
+    e = s < 1.0f ? 1u : (s > 255.0f ? 255u : (uint32_t)s);
+    if (!(s == s)) e = 1u;
+  } else {
+    const uint32_t bits = IN_BF16 ? (f2u(max_abs) >> 16) : f2u(max_abs);
+    e = e8m0_from_amax_bits<IN_BF16>(bits, F::MBITS, tmax);
+  }
+  BlockScale s;
+  s.byte = e;
+  s.q = u2f(e << 23);
+  s.fast = e <= 253u;
+  s.r = u2f((254u - e) << 23);
+  s.plain = 0.0f;
+  return s;
+}
+
 template <int FMT, bool IN_BF16>
 __device__ __forceinline__ float scale_elem(float x, const BlockScale& s) {
   if (Fmt<FMT>::MX) return s.fast ? __fmul_rn(x, s.r) : __fdiv_rn(x, s.q);
@@ -128,6 +186,7 @@ struct RowwiseArgs {
   const uint32_t* rand_bits;
   uint64_t philox_seed, philox_offset;
   PhiloxKeys pk;
+  MxOpts mx;
 };
 
 template <int FMT, bool IN_BF16, int ROUND>
@@ -187,7 +246,28 @@ __global__ void __launch_bounds__(256) quantize_rowwise_kernel(RowwiseArgs a) {
       const uint32_t o = __shfl_xor_sync(0xFFFFFFFFu, amax_bits, 1);
       amax_bits = o > amax_bits ? o : amax_bits;
     }
-    const BlockScale s = make_block_scale<FMT, IN_BF16>(amax_bits, use_outer, outer);
+    BlockScale s;
+    if (F::MX && (a.mx.clip | a.mx.uos)) {
+      float sum = 0.0f, sumsq = 0.0f;
+      if (a.mx.clip == 2) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          sum = __fadd_rn(sum, v[j]);
+          sumsq = __fadd_rn(sumsq, round_in<IN_BF16>(__fmul_rn(v[j], v[j])));
+        }
+        if (LPB == 2) {
+          sum = __fadd_rn(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, 1));
+          sumsq = __fadd_rn(sumsq, __shfl_xor_sync(0xFFFFFFFFu, sumsq, 1));
+        }
+      }
+      s = make_block_scale_opts<FMT, IN_BF16>(amax_bits, sum, sumsq, F::B, a.mx);
+      if (a.mx.clip == 1) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = round_in<IN_BF16>(__fmul_rn(v[j], 0.75f));
+      }
+    } else {
+      s = make_block_scale<FMT, IN_BF16>(amax_bits, use_outer, outer);
+    }
 
     // random bits (explicit mode): 8 words per plane for this lane's 8 element pairs
     uint32_t r0[8], r1[8];
@@ -296,6 +376,7 @@ struct ColwiseArgs {
   uint64_t philox_seed, philox_offset;
   PhiloxKeys pk;
   RhtParams rht;
+  MxOpts mx;
 };
 
 constexpr int COL_TM = 256;  // rows per CTA tile
@@ -382,8 +463,31 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
       am0 >>= 16;
       am1 >>= 16;
     }
-    const BlockScale s0 = make_block_scale<FMT, IN_BF16>(am0, use_outer, outer);
-    const BlockScale s1 = make_block_scale<FMT, IN_BF16>(am1, use_outer, outer);
+    BlockScale s0, s1;
+    if (F::MX && (a.mx.clip | a.mx.uos)) {
+      float sum0 = 0.0f, sq0 = 0.0f, sum1 = 0.0f, sq1 = 0.0f;
+      if (a.mx.clip == 2) {
+#pragma unroll
+        for (int k = 0; k < B; ++k) {
+          sum0 = __fadd_rn(sum0, v0[k]);
+          sq0 = __fadd_rn(sq0, round_in<IN_BF16>(__fmul_rn(v0[k], v0[k])));
+          sum1 = __fadd_rn(sum1, v1[k]);
+          sq1 = __fadd_rn(sq1, round_in<IN_BF16>(__fmul_rn(v1[k], v1[k])));
+        }
+      }
+      s0 = make_block_scale_opts<FMT, IN_BF16>(am0, sum0, sq0, B, a.mx);
+      s1 = make_block_scale_opts<FMT, IN_BF16>(am1, sum1, sq1, B, a.mx);
+      if (a.mx.clip == 1) {
+#pragma unroll
+        for (int k = 0; k < B; ++k) {
+          v0[k] = round_in<IN_BF16>(__fmul_rn(v0[k], 0.75f));
+          v1[k] = round_in<IN_BF16>(__fmul_rn(v1[k], 0.75f));
+        }
+      }
+    } else {
+      s0 = make_block_scale<FMT, IN_BF16>(am0, use_outer, outer);
+      s1 = make_block_scale<FMT, IN_BF16>(am1, use_outer, outer);
+    }
 
     // ---- quantise in slot order ----
     if (F::FP4) {
@@ -561,6 +665,7 @@ struct Quant2dArgs {
   uint8_t* packed_t;  // rows=cols, ncols=rows/B
   int64_t nct_k, nct_t;
   const float* outer;
+  MxOpts mx;          // clip 0/1 and uos (the dynamic clip needs block sums and is 1-D only)
 };
 
 template <int FMT, bool IN_BF16>
@@ -629,7 +734,9 @@ __global__ void __launch_bounds__(128 * Fmt<FMT>::B / 4) quantize_2d_kernel(Quan
         const uint32_t x = s_segmax[br * B + i][bc * (B / 16) + j];
         m = x > m ? x : m;
       }
-    const BlockScale s = make_block_scale<FMT, IN_BF16>(m, use_outer, outer);
+    const BlockScale s = (F::MX && (a.mx.clip | a.mx.uos))
+                             ? make_block_scale_opts<FMT, IN_BF16>(m, 0.0f, 0.0f, B * B, a.mx)
+                             : make_block_scale<FMT, IN_BF16>(m, use_outer, outer);
     s_q[br][bc] = s.q; s_r[br][bc] = s.r; s_plain[br][bc] = s.plain;
     s_byte[br][bc] = (uint8_t)s.byte; s_fast[br][bc] = s.fast ? 1 : 0;
     const int64_t gbr = (int64_t)blockIdx.y * NBR + br, gbc = (int64_t)blockIdx.x * NBC + bc;
@@ -643,6 +750,10 @@ __global__ void __launch_bounds__(128 * Fmt<FMT>::B / 4) quantize_2d_kernel(Quan
     const int br = r / B, bc = (sg * 16) / B;
     BlockScale s;
     s.q = s_q[br][bc]; s.r = s_r[br][bc]; s.fast = s_fast[br][bc] != 0; s.byte = 0; s.plain = 0.f;
+    if (F::MX && a.mx.clip == 1) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = round_in<IN_BF16>(__fmul_rn(v[j], 0.75f));
+    }
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = scale_elem<FMT, IN_BF16>(v[j], s);
     if (F::FP4) {
@@ -993,6 +1104,7 @@ struct DequantArgs {
   int64_t rows, cols, ld_out;
   void* out;
   int is_2d;
+  int static_clip;  // MXFP4: decoded values are multiplied by 4/3 in the output dtype before scaling
 };
 
 template <int FMT, bool OUT_BF16>
@@ -1021,8 +1133,12 @@ __global__ void __launch_bounds__(256) dequantize_kernel(DequantArgs a) {
       const uint2 w = __ldg(reinterpret_cast<const uint2*>(a.codes + row * (a.cols >> 1) + (col >> 1)));
       const uint32_t ws[2] = {w.x, w.y};
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        v[j] = __fmul_rn(e2m1_decode((ws[j >> 3] >> (4 * (j & 7))) & 0xFu), s);
+      for (int j = 0; j < 16; ++j) {
+        float d = e2m1_decode((ws[j >> 3] >> (4 * (j & 7))) & 0xFu);
+        // tests/unittest/mxfp4/utils.py:381-384: cast, times 4/3 in the output dtype, then the scale
+        if (a.static_clip) d = round_in<OUT_BF16>(__fmul_rn(d, (float)(4.0 / 3.0)));
+        v[j] = __fmul_rn(d, s);
+      }
     } else {
       const uint4 w = __ldg(reinterpret_cast<const uint4*>(a.codes + row * a.cols + col));
       const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
@@ -1224,6 +1340,16 @@ static int clear_packed_if_padded(void* buf, int64_t rows, int64_t ncols, cudaSt
   return ALTOB200_OK;
 }
 
+// clip_mode / use_uos exist for MXFP4 only, as in the reference
+static int fill_mx_opts(MxOpts* o, const altob200_quant_params* p, bool allow_dynamic) {
+  o->clip = p->clip_mode;
+  o->uos = p->use_uos != 0 ? 1 : 0;
+  if (o->clip < ALTOB200_CLIP_NONE || o->clip > ALTOB200_CLIP_DYNAMIC) return ALTOB200_EINVAL_SHAPE;
+  if ((o->clip | o->uos) != 0 && p->format != ALTOB200_FMT_MXFP4) return ALTOB200_EUNSUPPORTED;
+  if (o->clip == ALTOB200_CLIP_DYNAMIC && !allow_dynamic) return ALTOB200_EUNSUPPORTED;
+  return ALTOB200_OK;
+}
+
 }  // namespace altob200
 
 using namespace altob200;
@@ -1268,7 +1394,9 @@ int altob200_quantize_rowwise(const void* x, int64_t rows, int64_t cols, int64_t
   a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
   a.philox_seed = p->philox_seed; a.philox_offset = p->philox_offset;
   philox_make_keys(p->philox_seed, &a.pk);
-  int rc = clear_packed_if_padded(scale_packed, rows, cols / B, st);
+  int rc = fill_mx_opts(&a.mx, p, true);
+  if (rc != ALTOB200_OK) return rc;
+  rc = clear_packed_if_padded(scale_packed, rows, cols / B, st);
   if (rc != ALTOB200_OK) return rc;
   const int rounding = p->rounding;
 #define CALL_ROW(F, BF) launch_rowwise<F, BF>(a, rounding, st)
@@ -1300,6 +1428,8 @@ int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t
   philox_make_keys(p->philox_seed, &a.pk);
   int rc = fill_rht(&a.rht, p->rht_n, p->rht_perm, p->rht_sign);
   if (rc != ALTOB200_OK) return rc;
+  rc = fill_mx_opts(&a.mx, p, true);
+  if (rc != ALTOB200_OK) return rc;
   rc = clear_packed_if_padded(scale_packed, cols, rows / B, st);
   if (rc != ALTOB200_OK) return rc;
   const int rounding = p->rounding;
@@ -1326,7 +1456,9 @@ int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
   a.packed_k = (uint8_t*)scale_packed_k; a.packed_t = (uint8_t*)scale_packed_t;
   a.nct_k = ceil_div(cols / B, 4); a.nct_t = ceil_div(rows / B, 4);
   a.outer = p->outer_scale;
-  int rc = clear_packed_if_padded(scale_packed_k, rows, cols / B, st);
+  int rc = fill_mx_opts(&a.mx, p, false);
+  if (rc != ALTOB200_OK) return rc;
+  rc = clear_packed_if_padded(scale_packed_k, rows, cols / B, st);
   if (rc != ALTOB200_OK) return rc;
   rc = clear_packed_if_padded(scale_packed_t, cols, rows / B, st);
   if (rc != ALTOB200_OK) return rc;
@@ -1372,13 +1504,15 @@ int altob200_dequantize(const void* codes, const void* scale_plain, const float*
   if (codes == nullptr || scale_plain == nullptr || out == nullptr) return ALTOB200_EINVAL_SHAPE;
   const int B = block_of(format);
   if (rows <= 0 || cols <= 0 || cols % B != 0 || ld_out < cols) return ALTOB200_EINVAL_SHAPE;
-  if (is_2d && rows % B != 0) return ALTOB200_EINVAL_SHAPE;
+  if ((is_2d & 1) && rows % B != 0) return ALTOB200_EINVAL_SHAPE;
   const int esz = out_dtype == ALTOB200_DT_BF16 ? 2 : 4;
   if (!aligned16(codes) || !aligned16(out) || (ld_out * esz) % 16 != 0) return ALTOB200_EINVAL_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
   DequantArgs a;
   a.codes = (const uint8_t*)codes; a.scales = scale_plain; a.outer = outer_scale;
-  a.rows = rows; a.cols = cols; a.ld_out = ld_out; a.out = out; a.is_2d = is_2d;
+  a.rows = rows; a.cols = cols; a.ld_out = ld_out; a.out = out; a.is_2d = is_2d & 1;
+  a.static_clip = (is_2d >> 1) & 1;
+  if (a.static_clip && format != ALTOB200_FMT_MXFP4) return ALTOB200_EUNSUPPORTED;
   int64_t blocks = ceil_div(rows * (cols / 16), 256);
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;

@@ -21,13 +21,11 @@ from .nvfp4 import unwrap_weight_wrapper
 BLOCK_SIZE_DEFAULT = 32
 
 
-def _check_options(clip_mode: str, use_uos: bool) -> None:
+def _check_options(clip_mode: str, use_uos: bool, is_2d_block: bool = False) -> None:
     if clip_mode not in ("none", "static", "dynamic"):
         raise ValueError(f"Invalid clip mode: {clip_mode}")
-    if clip_mode != "none":
-        raise NotImplementedError(f"clip_mode={clip_mode!r} is not implemented on the B200 path")
-    if use_uos:
-        raise NotImplementedError("use_uos=True is not implemented on the B200 path")
+    if clip_mode == "dynamic" and is_2d_block:
+        raise NotImplementedError("clip_mode='dynamic' with 2-D blocks is not implemented on the B200 path")
 
 
 def convert_to_mxfp4(
@@ -49,7 +47,7 @@ def convert_to_mxfp4(
     assert not is_2d_block or data_hp.size(-2) % block_size == 0
     assert data_hp.dtype in [torch.float32, torch.bfloat16]
     assert block_size == BLOCK_SIZE_DEFAULT, f"MXFP4 kernels are built for block_size 32, got {block_size}"
-    _check_options(clip_mode, use_uos)
+    _check_options(clip_mode, use_uos, is_2d_block)
     rounding, philox = L.ROUND_RTN, (0, 0)
     if use_sr:
         if rand_bits is not None:
@@ -60,7 +58,7 @@ def convert_to_mxfp4(
             philox = (drawn[0] if philox_seed is None else philox_seed,
                       drawn[1] if philox_offset is None else philox_offset)
     return Q.quantize(data_hp, L.FMT_MXFP4, axis, is_2d_block, rounding=rounding,
-                      rand_bits=rand_bits if use_sr else None, philox=philox)
+                      rand_bits=rand_bits if use_sr else None, philox=philox, clip_mode=clip_mode, use_uos=use_uos)
 
 
 def convert_from_mxfp4(
@@ -76,7 +74,8 @@ def convert_from_mxfp4(
     assert output_dtype in [torch.float32, torch.bfloat16]
     assert block_size == BLOCK_SIZE_DEFAULT
     _check_options(clip_mode, False)
-    return Q.dequantize(data_lp, scales, L.FMT_MXFP4, axis, is_2d_block, output_dtype)
+    return Q.dequantize(data_lp, scales, L.FMT_MXFP4, axis, is_2d_block, output_dtype,
+                        static_clip=clip_mode == "static")
 
 
 def blockwise_mxfp4_gemm(
@@ -189,11 +188,13 @@ class MXFP4LinearFunction(torch.autograd.Function):
         if use_macro_block_scaling:
             if not x.is_cuda:
                 raise RuntimeError("MXFP4LinearFunction runs on CUDA tensors only (no CPU fallback)")
+            if clip_mode != "none" or use_uos:
+                raise NotImplementedError("clip_mode / use_uos together with macro-block scaling are not implemented")
             return _macro_forward(ctx, x, weight, use_2dblock_x, use_2dblock_w, bool(use_sr_grad),
                                   hadamard_transform)
         return E.linear_forward(ctx, "MXFP4LinearFunction", x, weight, L.FMT_MXFP4, use_2dblock_x=use_2dblock_x,
                                 use_2dblock_w=use_2dblock_w, use_sr_grad=bool(use_sr_grad), use_outer_scale=False,
-                                hadamard_transform=hadamard_transform)
+                                hadamard_transform=hadamard_transform, use_uos=bool(use_uos), clip_mode=clip_mode)
 
     @staticmethod
     def backward(ctx, grad_output):

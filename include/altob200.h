@@ -74,6 +74,10 @@ size_t altob200_packed_scale_bytes(int64_t rows, int64_t ncols);
  * {kernel id, block id, wait site, 0}. */
 int altob200_status_read(void* stream, int32_t detail[4]);
 
+#define ALTOB200_CLIP_NONE 0
+#define ALTOB200_CLIP_STATIC 1
+#define ALTOB200_CLIP_DYNAMIC 2
+
 /* ---- quantizer parameters ---------------------------------------------- */
 typedef struct altob200_quant_params {
   int32_t format;      /* ALTOB200_FMT_*                                             */
@@ -105,6 +109,14 @@ typedef struct altob200_quant_params {
   int32_t rht_n;
   const int32_t* rht_perm;
   const int32_t* rht_sign;
+  /* MXFP4 only (alto/kernels/fp4/mxfp4/mxfp_quantization.py:29-95, 321-322, 420-438):
+   * clip_mode STATIC multiplies the elements by 3/4 before encoding (scale unchanged);
+   * DYNAMIC takes the scale from 2.92247856/6 * std(block) + 1e-8 with target exponent 0
+   * (1-D blocks only); use_uos != 0 computes the scale as ceil(log2(amax / 7.25)) + 127.
+   * Arithmetic is done in the input dtype, as in the reference's emulation
+   * (tests/unittest/mxfp4/utils.py:320-358).                                          */
+  int32_t clip_mode;
+  int32_t use_uos;
 } altob200_quant_params;
 
 /*
@@ -205,7 +217,9 @@ int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
  * (alto/kernels/fp4/mxfp4/mxfp_quantization.py:488-545,
  *  alto/kernels/fp4/nvfp4/nvfp_quantization.py:634-711,
  *  alto/kernels/mxfp8/mxfp8_quantization.py:590-663) for the axis-last view;
- * `is_2d` selects [rows/block, cols/block] scales.
+ * `is_2d`: bit 0 selects [rows/block, cols/block] scales; bit 1 (MXFP4 only) is the static
+ * clip of the reference's dequantizer: decoded values times 4/3 in the output dtype before the
+ * scale (alto/kernels/fp4/mxfp4/mxfp_quantization.py:404-405).
  */
 int altob200_dequantize(const void* codes, const void* scale_plain, const float* outer_scale,
                         int32_t format, int32_t is_2d, int64_t rows, int64_t cols,
