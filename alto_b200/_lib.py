@@ -44,6 +44,7 @@ EXPORTED_SYMBOLS = (
     "altob200_macro_block_scaling",
     "altob200_macro_block_descaling",
     "altob200_gather_rows",
+    "altob200_dge_scale",
     "altob200_gemm_blockscaled",
     "altob200_grouped_gemm_blockscaled",
     "altob200_grouped_gemm_wgrad_blockscaled",
@@ -121,6 +122,8 @@ def _declare_more(lib):
     lib.altob200_rht_dense.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i64, vp]
     lib.altob200_gather_rows.restype = C.c_int
     lib.altob200_gather_rows.argtypes = [vp, i64, i64, vp, i64, vp, vp]
+    lib.altob200_dge_scale.restype = C.c_int
+    lib.altob200_dge_scale.argtypes = [vp, i32, i64, i64, i64, vp, C.POINTER(C.c_float), vp]
 
 
 def lib():
@@ -338,6 +341,17 @@ def macro_block_descaling(y, scale, x, mode: int) -> None:
     _check(lib().altob200_macro_block_descaling(y.data_ptr(), scale.data_ptr(), _dt(y.dtype), y.shape[0], y.shape[1],
                                                 y.shape[2], mode, x.data_ptr(), _stream()),
            "altob200_macro_block_descaling")
+
+
+def dge_scale(dw: torch.Tensor, codes_t: torch.Tensor, lut16: Sequence[float]) -> None:
+    """In place: dw[n, k] *= lut16[code of W[n, k]], codes_t = packed [K, N/2] weight operand."""
+    _require_cuda(dw, codes_t)
+    assert dw.dim() == 2 and dw.stride(1) == 1 and codes_t.is_contiguous() and len(lut16) == 16
+    N, K = dw.shape
+    assert codes_t.numel() == K * (N // 2), "codes_t must be the [K, N/2] packing of the weight"
+    lut = (C.c_float * 16)(*[float(v) for v in lut16])
+    _check(lib().altob200_dge_scale(dw.data_ptr(), _dt(dw.dtype), N, K, dw.stride(0), codes_t.data_ptr(), lut,
+                                    _stream()), "altob200_dge_scale")
 
 
 def gather_rows(src: torch.Tensor, index: torch.Tensor, out_rows: Optional[int] = None) -> torch.Tensor:

@@ -23,6 +23,7 @@ from typing import Callable, Optional, Tuple
 import torch
 
 from . import _lib as L
+from . import dge
 
 # ---------------------------------------------------------------------------------------
 # scratch and random-bit plumbing
@@ -250,7 +251,7 @@ def _keep_for(stream, *tensors) -> None:
 
 
 def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock_w, use_sr_grad, use_outer_scale,
-                   hadamard_transform, use_uos: bool = False, clip_mode: str = "none"):
+                   hadamard_transform, use_uos: bool = False, clip_mode: str = "none", use_dge: bool = False):
     """Shared body of the three autograd ``forward`` methods."""
     if not x.is_cuda:
         raise RuntimeError(f"{name} runs on CUDA tensors only (no CPU fallback)")
@@ -300,7 +301,7 @@ def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock
     ctx.use_outer_scale = use_outer_scale
     ctx.rht = rht
     ctx.dense_transform = dense
-    ctx.use_uos, ctx.clip_mode = use_uos, clip_mode
+    ctx.use_uos, ctx.clip_mode, ctx.use_dge = use_uos, clip_mode, use_dge
     return y.view(*original_shape[:-1], N)
 
 
@@ -342,6 +343,8 @@ def linear_backward(ctx, grad_output):
         _keep_for(main, g_n.codes, g_n.scales)
         main.wait_event(done)
         grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
+        if ctx.use_dge:
+            grad_weights = dge.apply_to_weight_grad(grad_weights, w_t.codes)
         return grad_inputs, grad_weights
     g_n, g_m = backward_operands(g2, ctx.fmt, use_2dblock_x=ctx.use_2dblock_x, use_sr_grad=ctx.use_sr_grad,
                                  use_outer_scale=ctx.use_outer_scale, rht=ctx.rht, dense=ctx.dense_transform,
@@ -353,6 +356,8 @@ def linear_backward(ctx, grad_output):
         if ctx.clip_mode == "static":
             # both wgrad operands were scaled by 3/4 (alto/kernels/fp4/mxfp4/mxfp_linear.py:543-544)
             grad_weights *= (16.0 / 9.0)
+        if ctx.use_dge:
+            grad_weights = dge.apply_to_weight_grad(grad_weights, w_t.codes)
     return grad_inputs, grad_weights
 
 

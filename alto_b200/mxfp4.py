@@ -179,8 +179,6 @@ class MXFP4LinearFunction(torch.autograd.Function):
                 use_macro_block_scaling, hadamard_transform: Optional[HadamardTransform] = None,
                 use_uos: bool = False):
         _check_options(clip_mode, use_uos)
-        if use_dge:
-            raise NotImplementedError("use_dge is not implemented on the B200 path")
         weight = unwrap_weight_wrapper(weight)
         if weight.dtype != x.dtype:
             weight = weight.to(dtype=x.dtype)
@@ -188,13 +186,15 @@ class MXFP4LinearFunction(torch.autograd.Function):
         if use_macro_block_scaling:
             if not x.is_cuda:
                 raise RuntimeError("MXFP4LinearFunction runs on CUDA tensors only (no CPU fallback)")
-            if clip_mode != "none" or use_uos:
-                raise NotImplementedError("clip_mode / use_uos together with macro-block scaling are not implemented")
+            if clip_mode != "none" or use_uos or use_dge:
+                raise NotImplementedError("clip_mode / use_uos / use_dge together with macro-block scaling are not "
+                                          "implemented")
             return _macro_forward(ctx, x, weight, use_2dblock_x, use_2dblock_w, bool(use_sr_grad),
                                   hadamard_transform)
         return E.linear_forward(ctx, "MXFP4LinearFunction", x, weight, L.FMT_MXFP4, use_2dblock_x=use_2dblock_x,
                                 use_2dblock_w=use_2dblock_w, use_sr_grad=bool(use_sr_grad), use_outer_scale=False,
-                                hadamard_transform=hadamard_transform, use_uos=bool(use_uos), clip_mode=clip_mode)
+                                hadamard_transform=hadamard_transform, use_uos=bool(use_uos), clip_mode=clip_mode,
+                                use_dge=bool(use_dge))
 
     @staticmethod
     def backward(ctx, grad_output):

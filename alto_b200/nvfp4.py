@@ -179,8 +179,6 @@ class NVFP4LinearFunction(torch.autograd.Function):
                 use_outer_scale: bool, hadamard_transform: Optional[HadamardTransform] = None,
                 use_dge: bool = False, scale_format: str = "e4m3"):
         _check_scale_format(scale_format)
-        if use_dge:
-            raise NotImplementedError("use_dge is not implemented on the B200 path")
         weight = unwrap_weight_wrapper(weight)
         if weight.dtype != x.dtype:
             weight = weight.to(dtype=x.dtype)
@@ -195,7 +193,8 @@ class NVFP4LinearFunction(torch.autograd.Function):
                 f"BLOCK_SIZE_DEFAULT ({BLOCK_SIZE_DEFAULT}) when use_2dblock_x=False."))
         return E.linear_forward(ctx, "NVFP4LinearFunction", x, weight, L.FMT_NVFP4, use_2dblock_x=use_2dblock_x,
                                 use_2dblock_w=use_2dblock_w, use_sr_grad=use_sr_grad,
-                                use_outer_scale=use_outer_scale, hadamard_transform=hadamard_transform)
+                                use_outer_scale=use_outer_scale, hadamard_transform=hadamard_transform,
+                                use_dge=bool(use_dge))
 
     @staticmethod
     def backward(ctx, grad_output):

@@ -269,6 +269,17 @@ int altob200_macro_block_descaling(const void* y, const uint8_t* scale, int32_t 
                                    int64_t cols, int32_t mode, void* x, void* stream);
 
 /*
+ * DGE factor on a weight gradient, in place: dw[n, k] = cast(float(dw[n, k]) * lut[code(W[n, k])]).
+ * Replaces `grad_weights * dge_bwd(w_fp4_values, float4_e2m1fn_x2)` (alto/kernels/dge/dge.py:81-93;
+ * alto/kernels/fp4/nvfp4/nvfp_linear.py:250-268, alto/kernels/fp4/mxfp4/mxfp_linear.py:546-566):
+ * the bin value of a weight element is one of sixteen numbers, so the factor is a table over its
+ * E2M1 code.  `codes_t` is the packed weight operand of the dgrad GEMM, [K, N/2] with element n in
+ * nibble n & 1; `lut16` is a HOST array of 16 floats indexed by the 4-bit code.
+ */
+int altob200_dge_scale(void* dw, int32_t dtype, int64_t N, int64_t K, int64_t ld, const void* codes_t,
+                       const float* lut16, void* stream);
+
+/*
  * Row gather with zero fill: dst[i] = index[i] >= 0 ? src[index[i]] : zeros, rows of row_bytes
  * (a multiple of 16; both pointers 16-byte aligned).  The MoE token path around the grouped
  * GEMMs: sort routed rows by expert and pad each expert's run to a multiple of 128 rows (index

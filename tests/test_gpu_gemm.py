@@ -236,6 +236,44 @@ def test_linear_snr_against_high_precision(scheme):
     assert _snr(w.grad, dyf.t() @ xf) > floors[2]
 
 
+@pytest.mark.parametrize("scheme", ["nvfp4", "mxfp4"])
+def test_dge_scales_the_weight_gradient_like_the_reference(scheme):
+    """use_dge multiplies dW by dge_bwd(FP4 bin values of W) (alto/kernels/dge/dge.py:81-93;
+    alto/kernels/fp4/nvfp4/nvfp_linear.py:250-268).  On bin values the reference's formula gives one
+    number, 1/k = 0.2, for all sixteen codes; dX and Y are untouched."""
+    from alto_b200 import dge, mxfp4 as MX, nvfp4 as NV
+    d = _dev()
+    table = dge.fp4_bin_table(d, torch.bfloat16)
+    assert len(table) == 16 and all(abs(t - 0.2) < 1e-6 for t in table)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(128, 256, generator=g).bfloat16().to(d)
+    w = (torch.randn(192, 256, generator=g) * 0.05).bfloat16().to(d)
+    dy = torch.randn(128, 192, generator=g).bfloat16().to(d)
+    outs = []
+    for use_dge in (False, True):
+        xd, wd = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        if scheme == "nvfp4":
+            y = NV._to_nvfp4_then_scaled_mm(xd, wd, False, True, False, use_outer_scale=True, use_dge=use_dge)
+        else:
+            y = MX._to_mxfp4_then_scaled_mm(xd, wd, False, True, False, use_dge, "none", False)
+        y.backward(dy)
+        outs.append((y.detach(), xd.grad, wd.grad))
+    (y0, dx0, dw0), (y1, dx1, dw1) = outs
+    assert torch.equal(y0, y1) and torch.equal(dx0, dx1)
+    # the reference's expression with tensor ops on this device: decode W's codes with unit scales in
+    # the gradient's dtype, dge_bwd on them, multiply
+    if scheme == "nvfp4":
+        q, _ = NV.convert_to_nvfp4(w, is_2d_block=True, outer_scale=NV.compute_dynamic_outer_scale(w))
+    else:
+        q, _ = MX.convert_to_mxfp4(w, is_2d_block=True)
+    codes = q.view(torch.uint8)
+    nib = torch.stack((codes & 0xF, codes >> 4), dim=-1).reshape(codes.shape[0], -1).long()
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6], device=d)
+    w_fp4_values = lut[nib].to(torch.bfloat16)
+    want = (dw0 * dge.dge_bwd_fp4(w_fp4_values)).to(torch.bfloat16)
+    assert torch.equal(dw1, want)
+
+
 def test_linear_shape_contracts():
     from alto_b200 import nvfp4 as NV
     d = _dev()
@@ -244,7 +282,7 @@ def test_linear_shape_contracts():
         NV._to_nvfp4_then_scaled_mm(torch.zeros(24, 64, dtype=torch.bfloat16, device=d), w, False, True, False)
     with pytest.raises(NotImplementedError):
         NV._to_nvfp4_then_scaled_mm(torch.zeros(32, 64, dtype=torch.bfloat16, device=d), w, False, True, False,
-                                    use_dge=True)
+                                    scale_format="ue5m3")
     x3 = torch.randn(2, 32, 64, dtype=torch.bfloat16, device=d)
     y = NV._to_nvfp4_then_scaled_mm(x3, w, False, True, False)
     assert y.shape == (2, 32, 64) and y.dtype == torch.bfloat16
