@@ -1,0 +1,187 @@
+"""``torch.ops`` registration of the quantizer and GEMM ops, with shape functions.
+
+The reference exposes these as ``torch.library.triton_op`` ops with ``register_fake`` shape functions
+-- ``torch.ops.torchtitan.{convert_to_mxfp4, convert_from_mxfp4, blockwise_mxfp4_gemm}``
+(alto/kernels/fp4/mxfp4/mxfp_quantization.py:410,548-585; mxfp_linear.py:143) and
+``torch.ops.alto.{convert_to_nvfp4, convert_from_nvfp4, convert_to_mxfp8, convert_from_mxfp8,
+calculate_mxfp8_scales, blockwise_mxfp8_gemm}`` -- so that traced callers keep working.  The same
+ops are registered here as ``torch.library.custom_op`` around this package's functions.  By default
+they go under the namespace ``alto_b200``; a build that does not import the reference can claim the
+reference's own names with ``register("torchtitan", "alto")``.
+
+Arguments follow the reference ops; ``output_dtype`` is passed as a ``torch.dtype``.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import mxfp4 as _mx4
+from . import mxfp8 as _mx8
+from . import nvfp4 as _nv4
+
+_registered = set()
+
+
+def _axis_last_shape(t: torch.Tensor, axis: int):
+    shp = list(t.shape)
+    a = axis % len(shp)
+    shp[a], shp[-1] = shp[-1], shp[a]
+    return shp
+
+
+def _quant_shapes(x, block, axis, is_2d, fp4):
+    """(codes shape, scales shape) in the reference's logical (un-transposed) coordinates."""
+    v = _axis_last_shape(x, axis)
+    codes = list(v)
+    codes[-1] = v[-1] // 2 if fp4 else v[-1]
+    scales = list(v)
+    scales[-1] = v[-1] // block
+    if is_2d:
+        scales[-2] = v[-2] // block
+    a = axis % x.dim()
+
+    def back(s):
+        s = list(s)
+        s[a], s[-1] = s[-1], s[a]
+        return s
+
+    return back(codes), back(scales)
+
+
+def register(mxfp4_namespace: str = "alto_b200", namespace: str = "alto_b200") -> None:
+    """Registers the ops (idempotent per namespace pair)."""
+    key = (mxfp4_namespace, namespace)
+    if key in _registered:
+        return
+    _registered.add(key)
+    op = torch.library.custom_op
+
+    # ---------------- MXFP4 ----------------
+    @op(f"{mxfp4_namespace}::convert_to_mxfp4", mutates_args=())
+    def convert_to_mxfp4(data_hp: torch.Tensor, block_size: int = 32, axis: int = -1, is_2d_block: bool = False,
+                         use_sr: bool = False, use_asm: Optional[bool] = None, philox_seed: Optional[int] = None,
+                         philox_offset: Optional[int] = None, clip_mode: str = "none",
+                         use_uos: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+        return _mx4.convert_to_mxfp4(data_hp, block_size, axis, is_2d_block, use_sr, use_asm, philox_seed,
+                                     philox_offset, clip_mode, use_uos)
+
+    @convert_to_mxfp4.register_fake
+    def _(data_hp, block_size=32, axis=-1, is_2d_block=False, use_sr=False, use_asm=None, philox_seed=None,
+          philox_offset=None, clip_mode="none", use_uos=False):
+        c, s = _quant_shapes(data_hp, block_size, axis, is_2d_block, True)
+        return data_hp.new_empty(c, dtype=torch.uint8), data_hp.new_empty(s, dtype=torch.uint8)
+
+    @op(f"{mxfp4_namespace}::convert_from_mxfp4", mutates_args=())
+    def convert_from_mxfp4(data_lp: torch.Tensor, scales: torch.Tensor, output_dtype: torch.dtype = torch.float32,
+                           block_size: int = 32, axis: int = -1, is_2d_block: bool = False,
+                           use_asm: Optional[bool] = None, clip_mode: str = "none") -> torch.Tensor:
+        return _mx4.convert_from_mxfp4(data_lp, scales, output_dtype, block_size, axis, is_2d_block, use_asm,
+                                       clip_mode).contiguous()
+
+    @convert_from_mxfp4.register_fake
+    def _(data_lp, scales, output_dtype=torch.float32, block_size=32, axis=-1, is_2d_block=False, use_asm=None,
+          clip_mode="none"):
+        shp = list(data_lp.shape)
+        shp[axis % len(shp)] *= 2
+        return data_lp.new_empty(shp, dtype=output_dtype)
+
+    @op(f"{mxfp4_namespace}::blockwise_mxfp4_gemm", mutates_args=())
+    def blockwise_mxfp4_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch.Tensor,
+                             trans_a: bool = False, trans_b: bool = False, k_pack_a: bool = True,
+                             k_pack_b: bool = True, use_2dblock_a: bool = False, use_2dblock_b: bool = False,
+                             block_size: int = 32, output_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        return _mx4.blockwise_mxfp4_gemm(a, a_s, b, b_s, trans_a, trans_b, k_pack_a, k_pack_b, use_2dblock_a,
+                                         use_2dblock_b, block_size, output_dtype)
+
+    @blockwise_mxfp4_gemm.register_fake
+    def _(a, a_s, b, b_s, trans_a=False, trans_b=False, k_pack_a=True, k_pack_b=True, use_2dblock_a=False,
+          use_2dblock_b=False, block_size=32, output_dtype=torch.float32):
+        M = a.shape[1] if trans_a else a.shape[0]
+        N = b.shape[0] if trans_b else b.shape[1]
+        return a.new_empty((M, N), dtype=output_dtype)
+
+    # ---------------- NVFP4 ----------------
+    # the reference declares no mutation for this op although `update_outer_scale` refreshes a
+    # caller-supplied outer_scale buffer in place (nvfp_quantization.py:490, 572-575); same here
+    @op(f"{namespace}::convert_to_nvfp4", mutates_args=())
+    def convert_to_nvfp4(data_hp: torch.Tensor, block_size: int = 16, axis: int = -1, is_2d_block: bool = False,
+                         outer_scale: Optional[torch.Tensor] = None, update_outer_scale: bool = True,
+                         scale_format: str = "e4m3", use_sr: bool = False, philox_seed: Optional[int] = None,
+                         philox_offset: Optional[int] = None,
+                         use_asm: Optional[bool] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        return _nv4.convert_to_nvfp4(data_hp, block_size, axis, is_2d_block, outer_scale, update_outer_scale,
+                                     scale_format, use_sr, philox_seed, philox_offset, use_asm)
+
+    @convert_to_nvfp4.register_fake
+    def _(data_hp, block_size=16, axis=-1, is_2d_block=False, outer_scale=None, update_outer_scale=True,
+          scale_format="e4m3", use_sr=False, philox_seed=None, philox_offset=None, use_asm=None):
+        c, s = _quant_shapes(data_hp, block_size, axis, is_2d_block, True)
+        return data_hp.new_empty(c, dtype=torch.uint8), data_hp.new_empty(s, dtype=torch.float32)
+
+    @op(f"{namespace}::convert_from_nvfp4", mutates_args=())
+    def convert_from_nvfp4(data_lp: torch.Tensor, scales: torch.Tensor, output_dtype: torch.dtype = torch.float32,
+                           block_size: int = 16, axis: int = -1, is_2d_block: bool = False,
+                           outer_scale: Optional[torch.Tensor] = None, scale_format: str = "e4m3",
+                           use_asm: Optional[bool] = None) -> torch.Tensor:
+        return _nv4.convert_from_nvfp4(data_lp, scales, output_dtype, block_size, axis, is_2d_block, outer_scale,
+                                       scale_format, use_asm).contiguous()
+
+    @convert_from_nvfp4.register_fake
+    def _(data_lp, scales, output_dtype=torch.float32, block_size=16, axis=-1, is_2d_block=False, outer_scale=None,
+          scale_format="e4m3", use_asm=None):
+        shp = list(data_lp.shape)
+        shp[axis % len(shp)] *= 2
+        return data_lp.new_empty(shp, dtype=output_dtype)
+
+    # ---------------- MXFP8 ----------------
+    @op(f"{namespace}::convert_to_mxfp8", mutates_args=())
+    def convert_to_mxfp8(data_hp: torch.Tensor, block_size: int = 32, mxfp_format: str = "e4m3", axis: int = -1,
+                         is_2d_block: bool = False, use_sr: bool = False, use_asm: Optional[bool] = None,
+                         philox_seed: Optional[int] = None,
+                         philox_offset: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        return _mx8.convert_to_mxfp8(data_hp, block_size, mxfp_format, axis, is_2d_block, use_sr, use_asm,
+                                     philox_seed, philox_offset)
+
+    @convert_to_mxfp8.register_fake
+    def _(data_hp, block_size=32, mxfp_format="e4m3", axis=-1, is_2d_block=False, use_sr=False, use_asm=None,
+          philox_seed=None, philox_offset=None):
+        c, s = _quant_shapes(data_hp, block_size, axis, is_2d_block, False)
+        dt = torch.float8_e4m3fn if mxfp_format == "e4m3" else torch.float8_e5m2
+        return data_hp.new_empty(c, dtype=dt), data_hp.new_empty(s, dtype=torch.uint8)
+
+    @op(f"{namespace}::convert_from_mxfp8", mutates_args=())
+    def convert_from_mxfp8(data_lp: torch.Tensor, scales: torch.Tensor, output_dtype: torch.dtype = torch.float32,
+                           block_size: int = 32, axis: int = -1, is_2d_block: bool = False,
+                           use_asm: Optional[bool] = None) -> torch.Tensor:
+        return _mx8.convert_from_mxfp8(data_lp, scales, output_dtype, block_size, axis, is_2d_block,
+                                       use_asm).contiguous()
+
+    @convert_from_mxfp8.register_fake
+    def _(data_lp, scales, output_dtype=torch.float32, block_size=32, axis=-1, is_2d_block=False, use_asm=None):
+        return data_lp.new_empty(list(data_lp.shape), dtype=output_dtype)
+
+    @op(f"{namespace}::calculate_mxfp8_scales", mutates_args=())
+    def calculate_mxfp8_scales(data_hp: torch.Tensor, block_size: int = 32, mxfp_format: str = "e4m3",
+                               axis: int = -1, is_2d_block: bool = False) -> torch.Tensor:
+        return _mx8.calculate_mxfp8_scales(data_hp, block_size, mxfp_format, axis, is_2d_block).contiguous()
+
+    @calculate_mxfp8_scales.register_fake
+    def _(data_hp, block_size=32, mxfp_format="e4m3", axis=-1, is_2d_block=False):
+        return data_hp.new_empty(_quant_shapes(data_hp, block_size, axis, is_2d_block, False)[1], dtype=torch.uint8)
+
+    @op(f"{namespace}::blockwise_mxfp8_gemm", mutates_args=())
+    def blockwise_mxfp8_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch.Tensor,
+                             trans_a: bool = False, trans_b: bool = False, use_2dblock_a: bool = False,
+                             use_2dblock_b: bool = False, block_size: int = 32,
+                             output_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        return _mx8.blockwise_mxfp8_gemm(a, a_s, b, b_s, trans_a, trans_b, use_2dblock_a, use_2dblock_b, block_size,
+                                         output_dtype)
+
+    @blockwise_mxfp8_gemm.register_fake
+    def _(a, a_s, b, b_s, trans_a=False, trans_b=False, use_2dblock_a=False, use_2dblock_b=False, block_size=32,
+          output_dtype=torch.float32):
+        M = a.shape[1] if trans_a else a.shape[0]
+        N = b.shape[0] if trans_b else b.shape[1]
+        return a.new_empty((M, N), dtype=output_dtype)

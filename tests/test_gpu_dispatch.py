@@ -46,6 +46,22 @@ def test_converted_linear_matches_boundary_function(scheme, kw):
     assert torch.equal(y, y2 + ref_b)
 
 
+def test_registered_torch_ops_run_the_cuda_path():
+    from alto_b200 import mxfp4, nvfp4, torch_ops
+    torch_ops.register()
+    d = _dev()
+    x = torch.randn(64, 128, device=d).bfloat16()
+    q, s = torch.ops.alto_b200.convert_to_mxfp4(x, axis=0)
+    q2, s2 = mxfp4.convert_to_mxfp4(x, axis=0)
+    assert torch.equal(q, q2) and torch.equal(s, s2)
+    dq = torch.ops.alto_b200.convert_from_mxfp4(q, s, torch.bfloat16, axis=0)
+    assert torch.equal(dq, mxfp4.convert_from_mxfp4(q2, s2, torch.bfloat16, axis=0))
+    outer = torch.zeros(1, device=d)
+    qn, sn = torch.ops.alto_b200.convert_to_nvfp4(x, outer_scale=outer)
+    assert outer.item() > 0                      # refreshed in place, as the reference op does
+    assert torch.equal(qn, nvfp4.convert_to_nvfp4(x, outer_scale=outer, update_outer_scale=False)[0])
+
+
 class _Experts(nn.Module):
     """Minimal stand-in for TorchTitan's GroupedExperts: w1 [E, hidden, dim] used as x @ w1^T."""
 
