@@ -39,6 +39,7 @@ EXPORTED_SYMBOLS = (
     "altob200_quantize_colwise",
     "altob200_quantize_2d",
     "altob200_dequantize",
+    "altob200_philox_tile",
     "altob200_rht",
     "altob200_rht_dense",
     "altob200_macro_block_scaling",
@@ -66,6 +67,8 @@ class QuantParams(C.Structure):
         ("rht_sign", C.POINTER(C.c_int32)),
         ("clip_mode", C.c_int32),
         ("use_uos", C.c_int32),
+        ("rand_tile_rows", C.c_int64),
+        ("rand_tile_pairs", C.c_int64),
     ]
 
 
@@ -122,6 +125,8 @@ def _declare_more(lib):
     lib.altob200_rht_dense.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i64, vp]
     lib.altob200_gather_rows.restype = C.c_int
     lib.altob200_gather_rows.argtypes = [vp, i64, i64, vp, i64, vp, vp]
+    lib.altob200_philox_tile.restype = C.c_int
+    lib.altob200_philox_tile.argtypes = [C.c_uint64, C.c_uint64, i64, i64, vp, vp]
     lib.altob200_dge_scale.restype = C.c_int
     lib.altob200_dge_scale.argtypes = [vp, i32, i64, i64, i64, vp, C.POINTER(C.c_float), vp]
 
@@ -207,10 +212,11 @@ CLIP_MODES = {"none": 0, "static": 1, "dynamic": 2}
 
 
 def _params(fmt, x, rounding, outer_scale, rand_bits, rht: Optional[Rht], flags, philox=(0, 0),
-            clip_mode: str = "none", use_uos: bool = False) -> QuantParams:
+            clip_mode: str = "none", use_uos: bool = False, rand_tile=(0, 0)) -> QuantParams:
     p = QuantParams()
     p.clip_mode = CLIP_MODES[clip_mode]
     p.use_uos = 1 if use_uos else 0
+    p.rand_tile_rows, p.rand_tile_pairs = int(rand_tile[0]), int(rand_tile[1])
     p.format = fmt
     p.in_dtype = _dt(x.dtype)
     p.rounding = rounding
@@ -226,6 +232,20 @@ def _params(fmt, x, rounding, outer_scale, rand_bits, rht: Optional[Rht], flags,
     else:
         p.rht_n = 0
     return p
+
+
+def philox_tile(seed: int, offset: int, tile_rows: int, tile_pairs: int, device) -> torch.Tensor:
+    """The reference's [2][tile_rows][tile_pairs] table of stochastic-rounding words for (seed, offset)."""
+    out = torch.empty(2, tile_rows, tile_pairs, dtype=torch.int32, device=device)
+    _require_cuda(out)
+    _check(lib().altob200_philox_tile(int(seed) & 0xFFFFFFFFFFFFFFFF, int(offset) & 0xFFFFFFFFFFFFFFFF, tile_rows,
+                                      tile_pairs, out.data_ptr(), _stream()), "altob200_philox_tile")
+    return out
+
+
+def sr_tile_dims(view_rows: int, view_cols: int) -> tuple:
+    """(BLOCK_M, BLOCK_N / 2) of the reference quantizer launch for a [view_rows, view_cols] axis-last view."""
+    return (64 if view_rows >= 64 else view_rows), (64 if view_cols >= 64 else view_cols) // 2
 
 
 def status_read() -> tuple:
@@ -262,11 +282,12 @@ def amax_noalloc(x: torch.Tensor, amax_bits: torch.Tensor, outer_scale: Optional
 
 
 def quantize_rowwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, rounding=ROUND_RTN,
-                     outer_scale=None, rand_bits=None, philox=(0, 0), clip_mode="none", use_uos=False) -> None:
+                     outer_scale=None, rand_bits=None, philox=(0, 0), clip_mode="none", use_uos=False,
+                     rand_tile=(0, 0)) -> None:
     _require_cuda(x, codes, scale_plain, scale_packed, outer_scale, rand_bits)
     assert x.dim() == 2 and x.stride(1) == 1
     flags = (SCALE_PLAIN if scale_plain is not None else 0) | (SCALE_PACKED if scale_packed is not None else 0)
-    p = _params(fmt, x, rounding, outer_scale, rand_bits, None, flags, philox, clip_mode, use_uos)
+    p = _params(fmt, x, rounding, outer_scale, rand_bits, None, flags, philox, clip_mode, use_uos, rand_tile)
     _check(lib().altob200_quantize_rowwise(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), C.byref(p),
                                            codes.data_ptr(), _ptr(scale_plain), _ptr(scale_packed), _stream()),
            "altob200_quantize_rowwise")
@@ -274,11 +295,11 @@ def quantize_rowwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, roun
 
 def quantize_colwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, rounding=ROUND_RTN,
                      outer_scale=None, rand_bits=None, rht: Optional[Rht] = None, philox=(0, 0),
-                     clip_mode="none", use_uos=False) -> None:
+                     clip_mode="none", use_uos=False, rand_tile=(0, 0)) -> None:
     _require_cuda(x, codes, scale_plain, scale_packed, outer_scale, rand_bits)
     assert x.dim() == 2 and x.stride(1) == 1
     flags = (SCALE_PLAIN if scale_plain is not None else 0) | (SCALE_PACKED if scale_packed is not None else 0)
-    p = _params(fmt, x, rounding, outer_scale, rand_bits, rht, flags, philox, clip_mode, use_uos)
+    p = _params(fmt, x, rounding, outer_scale, rand_bits, rht, flags, philox, clip_mode, use_uos, rand_tile)
     _check(lib().altob200_quantize_colwise(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), C.byref(p),
                                            codes.data_ptr(), _ptr(scale_plain), _ptr(scale_packed), _stream()),
            "altob200_quantize_colwise")

@@ -72,7 +72,14 @@ def sr_args(use_sr: bool, name: str, rows: int, cols: int, device) -> dict:
     if _sr_bits_provider is not None:
         bits = _sr_bits_provider(name, (2, rows, cols // 2), device)
         return dict(rounding=L.ROUND_SR_BITS, rand_bits=bits.contiguous())
-    return dict(rounding=L.ROUND_SR_PHILOX, philox=draw_philox())
+    # The reference's scheme: (seed, offset) drawn from the global CPU generator, one table of
+    # Philox words per quantizer launch, repeated over its 64 x 64 tiles (rows x cols is the
+    # quantisation-axis-last view).  The table costs one tiny launch and replaces ~15 instructions
+    # of Philox per element inside the quantizer by cached loads.
+    seed, offset = draw_philox()
+    tile = L.sr_tile_dims(rows, cols)
+    return dict(rounding=L.ROUND_SR_BITS, rand_bits=L.philox_tile(seed, offset, tile[0], tile[1], device),
+                rand_tile=tile)
 
 
 RTN = dict(rounding=L.ROUND_RTN)

@@ -76,8 +76,15 @@ def quantize(x: torch.Tensor, fmt: int, axis: int, is_2d: bool, *, outer_scale: 
         R = x2.shape[0]
         codes = torch.empty(R, N // 2 if fp4 else N, dtype=torch.uint8, device=dev)
         scales = torch.empty(R, N // block, dtype=scale_dtype, device=dev)
-        L.quantize_rowwise(x2, fmt, codes, scales, None, rounding=rounding, outer_scale=outer_scale,
-                           rand_bits=_rand_planes(rand_bits, R, N), philox=philox, **opts)
+        if rounding == L.ROUND_SR_PHILOX:
+            # the reference's words for (seed, offset): one table per launch, repeated over its tiles
+            tile = L.sr_tile_dims(R, N)
+            L.quantize_rowwise(x2, fmt, codes, scales, None, rounding=L.ROUND_SR_BITS, outer_scale=outer_scale,
+                               rand_bits=L.philox_tile(philox[0], philox[1], tile[0], tile[1], dev), rand_tile=tile,
+                               **opts)
+        else:
+            L.quantize_rowwise(x2, fmt, codes, scales, None, rounding=rounding, outer_scale=outer_scale,
+                               rand_bits=_rand_planes(rand_bits, R, N), philox=philox, **opts)
         return (codes.reshape(*x.shape[:-1], codes.shape[-1]).view(_CODE_DTYPE[fmt]),
                 scales.reshape(*x.shape[:-1], N // block))
 
@@ -87,10 +94,22 @@ def quantize(x: torch.Tensor, fmt: int, axis: int, is_2d: bool, *, outer_scale: 
     codes = torch.empty(nb, N, M // 2 if fp4 else M, dtype=torch.uint8, device=dev)
     scales = torch.empty(nb, N, M // block, dtype=scale_dtype, device=dev)
     rb = None if rand_bits is None else _rand_planes(rand_bits, nb * N, M).reshape(2, nb, N, M // 2)
+    table, tile = None, (0, 0)
+    if rounding == L.ROUND_SR_PHILOX:
+        # the reference flattens the leading dimensions into the rows of the axis-last view [nb * N, M]
+        tile = L.sr_tile_dims(nb * N, M)
+        if nb > 1 and N % tile[0] != 0:
+            raise NotImplementedError("stochastic rounding of a batched tensor whose rows do not fill whole "
+                                      "64-row tiles per batch entry is not implemented")
+        table = L.philox_tile(philox[0], philox[1], tile[0], tile[1], dev)
     for b in range(nb):
         xb = x3[b]
         if xb.stride(-1) != 1 or (xb.stride(0) * xb.element_size()) % 16 != 0:
             xb = xb.contiguous()
+        if table is not None:
+            L.quantize_colwise(xb, fmt, codes[b], scales[b], None, rounding=L.ROUND_SR_BITS, outer_scale=outer_scale,
+                               rand_bits=table, rand_tile=tile, rht=rht, **opts)
+            continue
         L.quantize_colwise(xb, fmt, codes[b], scales[b], None, rounding=rounding, outer_scale=outer_scale,
                            rand_bits=None if rb is None else rb[:, b].contiguous(), rht=rht,
                            philox=(philox[0], philox[1] + b * (N * M // 4)), **opts)

@@ -184,6 +184,8 @@ struct RowwiseArgs {
   int64_t ncol_tiles;  // ceil(cols / B / 4)
   const float* outer;
   const uint32_t* rand_bits;
+  // rand_bits as a periodic tile [2][tile_rows][tile_pairs] (0 = full planes [2][rows][cols/2])
+  int64_t tile_rows, tile_pairs;
   uint64_t philox_seed, philox_offset;
   PhiloxKeys pk;
   MxOpts mx;
@@ -275,9 +277,16 @@ __global__ void __launch_bounds__(256) quantize_rowwise_kernel(RowwiseArgs a) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) r0[j] = r1[j] = 0;
       if (active) {
-        const uint4* p0 = reinterpret_cast<const uint4*>(a.rand_bits + row * half_cols + (col >> 1));
-        const uint4* p1 = reinterpret_cast<const uint4*>(a.rand_bits + a.rows * half_cols +
-                                                         row * half_cols + (col >> 1));
+        // full planes, or a tile repeated over the matrix (the 8 pairs of a lane never straddle a
+        // tile: tile_pairs is a multiple of 8)
+        const bool tiled = a.tile_rows != 0;
+        // 32-bit remainders (the host refuses a tiled launch whose extents do not fit 32 bits)
+        const int64_t rr = tiled ? (int64_t)((uint32_t)row % (uint32_t)a.tile_rows) : row;
+        const int64_t pp = tiled ? (int64_t)((uint32_t)(col >> 1) % (uint32_t)a.tile_pairs) : (col >> 1);
+        const int64_t pitch = tiled ? a.tile_pairs : half_cols;
+        const int64_t plane = tiled ? a.tile_rows * a.tile_pairs : a.rows * half_cols;
+        const uint4* p0 = reinterpret_cast<const uint4*>(a.rand_bits + rr * pitch + pp);
+        const uint4* p1 = reinterpret_cast<const uint4*>(a.rand_bits + plane + rr * pitch + pp);
         const uint4 a0 = __ldg(p0), a1 = __ldg(p0 + 1), b0 = __ldg(p1), b1 = __ldg(p1 + 1);
         r0[0] = a0.x; r0[1] = a0.y; r0[2] = a0.z; r0[3] = a0.w;
         r0[4] = a1.x; r0[5] = a1.y; r0[6] = a1.z; r0[7] = a1.w;
@@ -372,7 +381,8 @@ struct ColwiseArgs {
   uint8_t* scale_packed;
   int64_t ncol_tiles;   // ceil(rows / B / 4)
   const float* outer;
-  const uint32_t* rand_bits;  // [2][cols][rows/2]
+  const uint32_t* rand_bits;  // [2][cols][rows/2], or a periodic tile [2][tile_rows][tile_pairs]
+  int64_t tile_rows, tile_pairs;
   uint64_t philox_seed, philox_offset;
   PhiloxKeys pk;
   RhtParams rht;
@@ -404,6 +414,9 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
   const bool use_outer = (!F::MX) && a.outer != nullptr;
   const float outer = use_outer ? __ldg(a.outer) : 1.0f;
   const int64_t half_rows = a.rows >> 1;
+  // rows of the periodic random table for this lane's two columns (rows of the axis-last view)
+  const uint32_t tile_row0 = a.tile_rows != 0 ? (uint32_t)((uint64_t)c % (uint64_t)a.tile_rows) : 0u;
+  const uint32_t tile_row1 = a.tile_rows != 0 ? (uint32_t)((uint64_t)(c + 1) % (uint64_t)a.tile_rows) : 0u;
 
 #pragma unroll 1
   for (int it = 0; it < ITERS; ++it) {
@@ -518,14 +531,51 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
         // random words by position: r0[i]/r1[i] for column c / c+1
         uint32_t r0[16], r1[16];
         if (ROUND == ALTOB200_ROUND_SR_BITS) {
+          if (a.tile_rows != 0 && (a.tile_pairs & 7) == 0) {
+            // periodic table: the 8 pairs of these 16 rows are 8 consecutive, 32-byte aligned words of
+            // one table row in each plane (tile_pairs is a multiple of 8) -> four 16-byte loads per column
+            const uint32_t tp = (uint32_t)a.tile_pairs;
+            const uint32_t base = (uint32_t)((uint64_t)((mb + 16 * h) >> 1) % tp);
+            const uint32_t plane = (uint32_t)a.tile_rows * tp;
+            const uint32_t* t0 = a.rand_bits + tile_row0 * tp + base;
+            const uint32_t* t1 = a.rand_bits + tile_row1 * tp + base;
+            uint4 e0[2], o0[2], e1[2], o1[2];  // even / odd planes of column c and c + 1
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            r0[i] = r1[i] = 0;
-            if (ok) {
-              const int64_t plane = (int64_t)(i & 1) * a.cols * half_rows;
-              const int64_t idx = (mb + 16 * h + i) >> 1;
-              r0[i] = __ldg(a.rand_bits + plane + c * half_rows + idx);
-              r1[i] = __ldg(a.rand_bits + plane + (c + 1) * half_rows + idx);
+            for (int q = 0; q < 2; ++q) {
+              e0[q] = o0[q] = e1[q] = o1[q] = make_uint4(0u, 0u, 0u, 0u);
+              if (ok) {
+                e0[q] = __ldg(reinterpret_cast<const uint4*>(t0) + q);
+                o0[q] = __ldg(reinterpret_cast<const uint4*>(t0 + plane) + q);
+                e1[q] = __ldg(reinterpret_cast<const uint4*>(t1) + q);
+                o1[q] = __ldg(reinterpret_cast<const uint4*>(t1 + plane) + q);
+              }
+            }
+            const uint32_t ev0[8] = {e0[0].x, e0[0].y, e0[0].z, e0[0].w, e0[1].x, e0[1].y, e0[1].z, e0[1].w};
+            const uint32_t od0[8] = {o0[0].x, o0[0].y, o0[0].z, o0[0].w, o0[1].x, o0[1].y, o0[1].z, o0[1].w};
+            const uint32_t ev1[8] = {e1[0].x, e1[0].y, e1[0].z, e1[0].w, e1[1].x, e1[1].y, e1[1].z, e1[1].w};
+            const uint32_t od1[8] = {o1[0].x, o1[0].y, o1[0].z, o1[0].w, o1[1].x, o1[1].y, o1[1].z, o1[1].w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              r0[2 * j] = ev0[j]; r0[2 * j + 1] = od0[j];
+              r1[2 * j] = ev1[j]; r1[2 * j + 1] = od1[j];
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              r0[i] = r1[i] = 0;
+              if (ok) {
+                const int64_t idx = (mb + 16 * h + i) >> 1;
+                if (a.tile_rows != 0) {
+                  const int64_t plane = (int64_t)(i & 1) * a.tile_rows * a.tile_pairs;
+                  const int64_t pi = idx % a.tile_pairs;
+                  r0[i] = __ldg(a.rand_bits + plane + (int64_t)tile_row0 * a.tile_pairs + pi);
+                  r1[i] = __ldg(a.rand_bits + plane + (int64_t)tile_row1 * a.tile_pairs + pi);
+                } else {
+                  const int64_t plane = (int64_t)(i & 1) * a.cols * half_rows;
+                  r0[i] = __ldg(a.rand_bits + plane + c * half_rows + idx);
+                  r1[i] = __ldg(a.rand_bits + plane + (c + 1) * half_rows + idx);
+                }
+              }
             }
           }
         } else if (ROUND == ALTOB200_ROUND_SR_PHILOX) {
@@ -1340,6 +1390,25 @@ static int clear_packed_if_padded(void* buf, int64_t rows, int64_t ncols, cudaSt
   return ALTOB200_OK;
 }
 
+// The reference's stochastic-rounding words (alto/kernels/fp4/fp4_common/triton_fp4_ops.py:13-19):
+// every BLOCK_M x BLOCK_N tile of the quantisation-axis-last view draws
+//   r1, r2, _, _ = randint4x(seed, offset + m * (BLOCK_N / 2) + n),  m < BLOCK_M, n < BLOCK_N / 2
+// with tile-local m, n and the SAME offset in every tile, r1 for the even and r2 for the odd
+// element of pair n.  The words therefore form one [2][BLOCK_M][BLOCK_N/2] table that repeats over
+// the matrix; this kernel writes the table (one Philox call per entry pair) and the quantizers index
+// it periodically.
+__global__ void __launch_bounds__(256) philox_tile_kernel(uint32_t* out, int64_t tile_rows, int64_t tile_pairs,
+                                                          uint32_t offset, PhiloxKeys pk) {
+  const int64_t n = tile_rows * tile_pairs;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t o[4];
+    // Triton's randint4x on an int32 offset tensor: counter = (uint32(offset + i), 0, 0, 0)
+    philox4x32_10_keys(offset + (uint32_t)i, 0u, pk, o);
+    out[i] = o[0];
+    out[n + i] = o[1];
+  }
+}
+
 // clip_mode / use_uos exist for MXFP4 only, as in the reference
 static int fill_mx_opts(MxOpts* o, const altob200_quant_params* p, bool allow_dynamic) {
   o->clip = p->clip_mode;
@@ -1375,6 +1444,21 @@ size_t altob200_packed_scale_bytes(int64_t rows, int64_t ncols) {
   return (size_t)(ceil_div(rows, 128) * ceil_div(ncols, 4) * 512);
 }
 
+int altob200_philox_tile(uint64_t seed, uint64_t offset, int64_t tile_rows, int64_t tile_pairs, uint32_t* out,
+                         void* stream) {
+  if (out == nullptr || tile_rows <= 0 || tile_pairs <= 0 || tile_rows * tile_pairs > (1ll << 24))
+    return ALTOB200_EINVAL_SHAPE;
+  if (!aligned16(out)) return ALTOB200_EINVAL_ALIGN;
+  PhiloxKeys pk;
+  philox_make_keys(seed, &pk);
+  const int64_t n = tile_rows * tile_pairs;
+  int64_t blocks = ceil_div(n, 256);
+  if (blocks > 148) blocks = 148;
+  philox_tile_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(out, tile_rows, tile_pairs, (uint32_t)offset,
+                                                                        pk);
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
 int altob200_quantize_rowwise(const void* x, int64_t rows, int64_t cols, int64_t ld,
                               const altob200_quant_params* p, void* codes, void* scale_plain,
                               void* scale_packed, void* stream) {
@@ -1392,6 +1476,10 @@ int altob200_quantize_rowwise(const void* x, int64_t rows, int64_t cols, int64_t
   a.codes = (uint8_t*)codes; a.scale_plain = scale_plain; a.scale_packed = (uint8_t*)scale_packed;
   a.ncol_tiles = ceil_div(cols / B, 4);
   a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
+  a.tile_rows = p->rand_tile_rows; a.tile_pairs = p->rand_tile_pairs;
+  if ((a.tile_rows != 0) != (a.tile_pairs != 0) || a.tile_rows < 0 || a.tile_pairs % 8 != 0)
+    return ALTOB200_EINVAL_SHAPE;
+  if (a.tile_rows != 0 && (rows >= (1ll << 32) || cols >= (1ll << 32))) return ALTOB200_ELIMIT;
   a.philox_seed = p->philox_seed; a.philox_offset = p->philox_offset;
   philox_make_keys(p->philox_seed, &a.pk);
   int rc = fill_mx_opts(&a.mx, p, true);
@@ -1424,6 +1512,8 @@ int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t
   a.codes = (uint8_t*)codes; a.scale_plain = scale_plain; a.scale_packed = (uint8_t*)scale_packed;
   a.ncol_tiles = ceil_div(rows / B, 4);
   a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
+  a.tile_rows = p->rand_tile_rows; a.tile_pairs = p->rand_tile_pairs;
+  if ((a.tile_rows != 0) != (a.tile_pairs != 0) || a.tile_rows < 0 || a.tile_pairs < 0) return ALTOB200_EINVAL_SHAPE;
   a.philox_seed = p->philox_seed; a.philox_offset = p->philox_offset;
   philox_make_keys(p->philox_seed, &a.pk);
   int rc = fill_rht(&a.rht, p->rht_n, p->rht_perm, p->rht_sign);

@@ -86,9 +86,9 @@ def convert_to_nvfp4(
     caller-supplied ``outer_scale`` buffer when ``update_outer_scale`` is set.
 
     ``rand_bits`` (extension): explicit 32-bit random words [2, rows, cols/2] for ``use_sr``.
-    With ``use_sr`` and no ``rand_bits`` the kernel generates Philox-4x32-10 words from
-    (philox_seed, philox_offset); the word-to-element mapping is this library's own (one
-    Philox call per two element pairs), not Triton's.
+    With ``use_sr`` and no ``rand_bits`` the words are the reference's: Philox-4x32-10 words of
+    (philox_seed, philox_offset) laid out as its kernel lays them out (one table per launch,
+    repeated over the 64 x 64 tiles of the quantisation-axis-last view).
     """
     torch._check(
         data_hp.shape[axis] % block_size == 0,

@@ -117,6 +117,14 @@ typedef struct altob200_quant_params {
    * (tests/unittest/mxfp4/utils.py:320-358).                                          */
   int32_t clip_mode;
   int32_t use_uos;
+  /* ROUND_SR_BITS with a periodic table: when both are non-zero, rand_bits is
+   * [2][rand_tile_rows][rand_tile_pairs] and element pair (r, p) of the quantisation-axis-last
+   * view reads entry (r % rand_tile_rows, p % rand_tile_pairs).  With the table written by
+   * altob200_philox_tile this reproduces the reference kernels' stochastic rounding for a given
+   * (philox_seed, philox_offset) bit for bit.  rand_tile_pairs must be a multiple of 8 for the
+   * row-wise quantizer.                                                                  */
+  int64_t rand_tile_rows;
+  int64_t rand_tile_pairs;
 } altob200_quant_params;
 
 /*
@@ -209,6 +217,18 @@ int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t
 int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
                          const altob200_quant_params* p, void* codes_k, void* codes_t,
                          void* scale_plain, void* scale_packed_k, void* scale_packed_t,
+                         void* stream);
+
+/*
+ * The reference's table of stochastic-rounding words: out[0][m][n], out[1][m][n] = first and second
+ * word of Philox-4x32-10 with key (seed lo, seed hi) and counter (uint32(offset + m * tile_pairs + n),
+ * 0, 0, 0), which is `r1, r2, _, _ = tl.randint4x(seed, offset + m * n_pairs + n)` of
+ * alto/kernels/fp4/fp4_common/triton_fp4_ops.py:13-19.  The reference draws this same table in every
+ * BLOCK_M x BLOCK_N tile (BLOCK = min(64, extent), alto/kernels/fp4/mxfp4/mxfp_quantization.py:452-459,
+ * alto/kernels/fp4/nvfp4/nvfp_quantization.py:591-598): tile_rows = BLOCK_M, tile_pairs = BLOCK_N / 2.
+ * out: device uint32 [2][tile_rows][tile_pairs], 16-byte aligned.
+ */
+int altob200_philox_tile(uint64_t seed, uint64_t offset, int64_t tile_rows, int64_t tile_pairs, uint32_t* out,
                          void* stream);
 
 /*

@@ -252,16 +252,30 @@ def test_nvfp4_rowwise_stochastic_rounding_bits_and_philox():
     _same(q, qo, "explicit bits")
     q_rtn, _ = O.quantize_nvfp4(x, 16, -1, False, None)
     assert (q_rtn != qo).float().mean() > 0.05
+    # (seed, offset): the reference kernel's words in the reference kernel's layout
     seed, off = 987654321, 12345
-    ctr = torch.arange(256 * 256 // 2, dtype=torch.int64) + off
-    zz = torch.zeros_like(ctr)
-    o = O.philox4x32_10(ctr & 0xFFFFFFFF, ctr >> 32, zz, zz, torch.full_like(ctr, seed & 0xFFFFFFFF),
-                        torch.full_like(ctr, seed >> 32))
-    rp = torch.stack([torch.stack([o[0], o[2]], 1).reshape(256, 256), torch.stack([o[1], o[3]], 1).reshape(256, 256)])
+    rp = O.reference_sr_planes(seed, off, 256, 512)
     qo, _ = O.quantize_nvfp4(x, 16, -1, False, None, rp)
     q, _ = NV.convert_to_nvfp4(x.to(_dev()), update_outer_scale=False, use_sr=True, philox_seed=seed,
                                philox_offset=off)
     _same(q, qo, "philox")
+    # along the token axis: the view is the transposed matrix [512, 256]
+    qo, _ = O.quantize_nvfp4(x, 16, 0, False, None, O.reference_sr_planes(seed, off, 512, 256))
+    q, _ = NV.convert_to_nvfp4(x.to(_dev()), axis=0, update_outer_scale=False, use_sr=True, philox_seed=seed,
+                               philox_offset=off)
+    _same(q, qo, "philox, axis 0")
+
+
+@pytest.mark.parametrize("z,m", list(golden_cases("mxfp4sr")), ids=lambda v: v[0] if isinstance(v, tuple) else "")
+def test_mxfp4_stochastic_rounding_from_seed_and_offset_matches_reference_kernel(z, m):
+    """Same (philox_seed, philox_offset) as the reference's Triton kernel was run with -> same codes."""
+    from alto_b200 import mxfp4 as MX
+    tag, shape, dt, axis, is2d = m
+    seed, off = [int(v) for v in z["philox_seed_offset"]]
+    x = case_input(z, m).to(_dev())
+    q, s = MX.convert_to_mxfp4(x, axis=axis, use_sr=True, philox_seed=seed, philox_offset=off)
+    _same(s, z[tag + "_s"], "scales")
+    _same(q, z[tag + "_q"], "codes")
 
 
 @pytest.mark.parametrize("shape", [(128, 64), (256, 320), (1024, 2048), (144, 80)])

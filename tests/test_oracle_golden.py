@@ -39,6 +39,18 @@ def test_mxfp4_stochastic_rounding_matches_reference_kernel(z, m):
     assert (q_rtn != q).float().mean() > 0.05
 
 
+@pytest.mark.parametrize("z,m", list(golden_cases("mxfp4sr")), ids=lambda v: v[0] if isinstance(v, tuple) else "")
+def test_reference_sr_word_layout(z, m):
+    """(seed, offset) -> the per-element words the reference kernel consumed (dumped beside its codes)."""
+    tag, shape, dt, axis, is2d = m
+    seed, off = [int(v) for v in z["philox_seed_offset"]]
+    R, Cc = (shape[0], shape[1]) if axis == -1 else (shape[1], shape[0])
+    planes = O.reference_sr_planes(seed, off, R, Cc)
+    assert np.array_equal(planes.numpy().astype(np.uint32), z[tag + "_rand"])
+    q, s = O.quantize_mxfp4(case_input(z, m), 32, axis, False, planes)
+    _eq(q, z[tag + "_q"])
+
+
 def test_philox_matches_triton_randint4x():
     z, _ = load_golden()
     seed, off = [int(v) for v in z["philox_seed_offset"]]
