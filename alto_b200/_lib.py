@@ -46,6 +46,7 @@ EXPORTED_SYMBOLS = (
     "altob200_macro_block_descaling",
     "altob200_gather_rows",
     "altob200_dge_scale",
+    "altob200_deosc_accumulate",
     "altob200_gemm_blockscaled",
     "altob200_grouped_gemm_blockscaled",
     "altob200_grouped_gemm_wgrad_blockscaled",
@@ -127,6 +128,8 @@ def _declare_more(lib):
     lib.altob200_gather_rows.argtypes = [vp, i64, i64, vp, i64, vp, vp]
     lib.altob200_philox_tile.restype = C.c_int
     lib.altob200_philox_tile.argtypes = [C.c_uint64, C.c_uint64, i64, i64, vp, vp]
+    lib.altob200_deosc_accumulate.restype = C.c_int
+    lib.altob200_deosc_accumulate.argtypes = [vp, vp, vp, vp, vp, vp, i64, i32, vp]
     lib.altob200_dge_scale.restype = C.c_int
     lib.altob200_dge_scale.argtypes = [vp, i32, i64, i64, i64, vp, C.POINTER(C.c_float), vp]
 
@@ -373,6 +376,16 @@ def dge_scale(dw: torch.Tensor, codes_t: torch.Tensor, lut16: Sequence[float]) -
     lut = (C.c_float * 16)(*[float(v) for v in lut16])
     _check(lib().altob200_dge_scale(dw.data_ptr(), _dt(dw.dtype), N, K, dw.stride(0), codes_t.data_ptr(), lut,
                                     _stream()), "altob200_dge_scale")
+
+
+def deosc_accumulate(w, prev, w_qdq, prev_qdq, dist_w, dist_qdq) -> None:
+    """dist_w += |w - prev|; dist_qdq += |w_qdq - prev_qdq|; prev = w (all contiguous, same dtype and size)."""
+    ts = (w, prev, w_qdq, prev_qdq, dist_w, dist_qdq)
+    _require_cuda(*ts)
+    assert all(t.is_contiguous() and t.dtype == w.dtype and t.numel() == w.numel() for t in ts)
+    _check(lib().altob200_deosc_accumulate(w.data_ptr(), prev.data_ptr(), w_qdq.data_ptr(), prev_qdq.data_ptr(),
+                                           dist_w.data_ptr(), dist_qdq.data_ptr(), w.numel(), _dt(w.dtype), _stream()),
+           "altob200_deosc_accumulate")
 
 
 def gather_rows(src: torch.Tensor, index: torch.Tensor, out_rows: Optional[int] = None) -> torch.Tensor:

@@ -9,7 +9,7 @@ parameters of every matched ``nn.Linear`` and ``*GroupedExperts`` module with ``
 
 Parts of the reference's modifier that belong to other subsystems are refused with a clear
 error instead of being imitated: LoRA decomposition (``lora_rank > 0``), the low-precision
-attention swap, weight de-oscillation (``deosc_step > 0``) and the TorchTitan config rewriting
+attention swap and the TorchTitan config rewriting
 (``on_convert_config`` needs the TorchTitan fork; without it the call only records that routed
 experts must be padded to ``ALIGN_SIZE_M`` = 128 tokens by the dispatcher).
 """
@@ -234,9 +234,17 @@ class LowPrecisionTrainingModifier(BaseModel):
         return True
 
     def on_pre_step(self, model_parts: list, **kwargs) -> bool:
+        """From step ``deosc_step`` on, install the de-oscillation hook on the trainer's optimizers
+        (alto/modifiers/lpt/base.py:237-251)."""
+        trainer = kwargs.get("trainer", None)
         if self.deosc_step > 0:
-            raise NotImplementedError("weight de-oscillation (deosc_step > 0) is a caller of the quantizers, "
-                                      "not part of this path")
+            if trainer is None:
+                raise ValueError("Trainer must be passed to the pre_step method to enable weight de-oscillation.")
+            if trainer.step >= self.deosc_step:
+                from .deosc import DeOscillationConfig, enable_de_oscillation
+                enable_de_oscillation(trainer.optimizers, DeOscillationConfig(
+                    enable=True, period=self.deosc_period, ratio_threshold=self.deosc_ratio,
+                    log_freq=self.deosc_log_freq))
         return True
 
     def on_post_step(self, model_parts: list, **kwargs) -> bool:

@@ -300,6 +300,16 @@ int altob200_dge_scale(void* dw, int32_t dtype, int64_t N, int64_t K, int64_t ld
                        const float* lut16, void* stream);
 
 /*
+ * Weight de-oscillation bookkeeping after an optimizer step, in one pass over n elements:
+ * dist_w += |w - prev|, dist_qdq += |w_qdq - prev_qdq|, prev = w, where w_qdq / prev_qdq are the
+ * quantise-dequantise round trips of w and prev on the forward pass's grid.  Replaces the five
+ * tensor ops of _DeOscillationHook._step_param (alto/components/optimizer.py:381-386).  All arrays
+ * have `dtype`; with bf16 every intermediate is rounded to bf16 as the tensor ops round.
+ */
+int altob200_deosc_accumulate(const void* w, void* prev, const void* w_qdq, const void* prev_qdq, void* dist_w,
+                              void* dist_qdq, int64_t n, int32_t dtype, void* stream);
+
+/*
  * Row gather with zero fill: dst[i] = index[i] >= 0 ? src[index[i]] : zeros, rows of row_bytes
  * (a multiple of 16; both pointers 16-byte aligned).  The MoE token path around the grouped
  * GEMMs: sort routed rows by expert and pad each expert's run to a multiple of 128 rows (index
