@@ -371,21 +371,71 @@ def run_ours(args):
         dxh.copy_(x.grad, non_blocking=True)
         dwh.copy_(w.grad, non_blocking=True)
 
+    def timed(loop):
+        barrier()
+        e0.record()
+        loop(args.steps)
+        e1.record()
+        barrier()
+        tt = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if dist is not None:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
     e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
+    serial_ms = timed(lambda n: [e2e_step() for _ in range(n)])
+
+    # The same work with the copies of neighbouring steps overlapped, as a caller feeding batches from
+    # host memory would run it: three streams and two sets of device inputs; step i computes while the
+    # inputs of step i+1 arrive and the results of step i-1 leave.  Every step still copies its own
+    # inputs from pinned host memory and its own three results back.
+    comp = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    sets = [(x, w, dy), (torch.empty_like(x).requires_grad_(True), torch.empty_like(w).requires_grad_(True),
+                         torch.empty_like(dy))]
+    consumed = [None, None]
+
+    def pipelined(n):
+        for i in range(n):
+            b = i & 1
+            xs, ws, dys = sets[b]
+            with torch.cuda.stream(s_in):
+                if consumed[b] is not None:
+                    s_in.wait_event(consumed[b])
+                with torch.no_grad():
+                    xs.copy_(xh, non_blocking=True)
+                    ws.copy_(wh, non_blocking=True)
+                    dys.copy_(dyh, non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(s_in)
+            comp.wait_event(arrived)
+            xs.grad = None
+            ws.grad = None
+            y = NV._to_nvfp4_then_scaled_mm(xs, ws, False, True, True, use_outer_scale=True, use_hadamard=True)
+            y.backward(dys)
+            done = torch.cuda.Event()
+            done.record(comp)
+            consumed[b] = done
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                yh.copy_(y.detach(), non_blocking=True)
+                dxh.copy_(xs.grad, non_blocking=True)
+                dwh.copy_(ws.grad, non_blocking=True)
+                for t_ in (y, xs.grad, ws.grad):
+                    t_.record_stream(s_out)
+        comp.wait_stream(s_in)
+        comp.wait_stream(s_out)
+
+    pipelined(2)
+    e2e_ms = timed(pipelined)
     h2d = (x.numel() + w.numel() + dy.numel()) * 2
     d2h = (yh.numel() + dxh.numel() + dwh.numel()) * 2
     e2e = {"value": world * FLOPS_PER_STEP * args.steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps}
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+           "how": "public autograd entry point; per step H2D of x, W, dY from pinned host memory and D2H of y, dX, dW; "
+                  "copies of neighbouring steps overlap the compute (3 streams, 2 sets of device inputs)",
+           "serial_ms_per_step": serial_ms / args.steps,
+           "serial_value": world * FLOPS_PER_STEP * args.steps / (serial_ms * 1e-3) / 1e12}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
