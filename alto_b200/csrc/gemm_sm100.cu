@@ -279,8 +279,12 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, bool have_acc, flo
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
     const int64_t col0 = col_base + (int64_t)c * cols_per_unit;
-    if (lane == 0 && row0 < M && col0 < N && store_enabled) {
-      tma_store_3d(epi_warp + (store_it & 1u) * 4096u, tmap_d, (int32_t)col0, (int32_t)row0, batch);
+    if (lane == 0) {
+      if (row0 < M && col0 < N && store_enabled)
+        tma_store_3d(epi_warp + (store_it & 1u) * 4096u, tmap_d, (int32_t)col0, (int32_t)row0, batch);
+      // a group is committed for every unit, empty when the unit lies outside the output: the
+      // "all but the latest group have been read" wait before a buffer is refilled counts groups, so
+      // a skipped unit must not let the store of the other buffer pass for the latest one
       bulk_commit();
     }
     ++store_it;
