@@ -117,6 +117,12 @@ __device__ __forceinline__ float div_bf16_num(float x, float q, float r) {
   const float y2 = __fmaf_rn(e, r, y);
   return u2f((f2u(y2) & 0x7FFFFFFFu) | (f2u(x) & 0x80000000u));
 }
+// The same quotient up to the sign of a zero (for callers that take the sign from x).
+__device__ __forceinline__ float div_bf16_num_mag(float x, float q, float r) {
+  const float y = __fmul_rn(x, r);
+  const float e = __fmaf_rn(-y, q, x);
+  return __fmaf_rn(e, r, y);
+}
 
 // ---------------------------------------------------------------------------------------
 // E2M1 encode, round to nearest even, saturating.  Bit-for-bit restatement of
@@ -158,25 +164,29 @@ __device__ __forceinline__ uint32_t e2m1x2_rtn_hw(float v0, float v1) {
 // E2M1 encode with stochastic rounding from 32 random bits.  Restatement of
 //   alto/kernels/fp4/fp4_common/triton_fp4_ops.py:26-93 with USE_SR=True.
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t e2m1_sr_bits(float v, uint32_t rnd) {
-  // Branch-free; every arm is a handful of instructions and the selects keep the warp converged.
-  const uint32_t vb = f2u(v);
-  const uint32_t ab = vb & 0x7FFFFFFFu;
-  const float a = u2f(ab);
-  // normal range [1, 6): add 22 random bits below the kept mantissa bit, rebias, truncate
-  const uint32_t cn = (ab + (rnd & 0x3FFFFFu) - (126u << 23)) >> 22;
-  // E2M1-subnormal range [0, 1): 2a = k + frac with k in {0, 1}; the reference compares the random
-  // word with uint32(a * fp32(2^33 - 2)) for a < 0.5 and with uint32((2a - 1) * fp32(2^32 - 1))
-  // otherwise; both constants round to powers of two in fp32, so both thresholds are
-  // trunc(frac * 2^32), and the codes are k + (rnd <= threshold).
-  const float a2 = __fadd_rn(a, a);
-  const bool k = a2 >= 1.0f;
-  const float frac = k ? __fadd_rn(a2, -1.0f) : a2;
-  const uint32_t thr = __float2uint_rz(__fmul_rn(frac, 4294967296.0f));
-  const uint32_t cd = (rnd <= thr ? 1u : 0u) + (k ? 1u : 0u);
-  uint32_t code = a < 1.0f ? cd : cn;
-  code = a >= 6.0f ? 7u : code;
-  return (code & 0xFu) | ((vb >> 28) & 8u);
+// Arranged for instruction count (the stochastic-rounding quantizers are bound by instruction
+// issue, not by memory).  The reference rounds the normal range [1, 6) by adding 22 random bits
+// below the kept mantissa bit and truncating; in the E2M1-subnormal range [0, 1), with 2a = k + frac,
+// it compares the random word with uint32(a * fp32(2^33 - 2)) for a < 0.5 and with
+// uint32((2a - 1) * fp32(2^32 - 1)) otherwise; both constants round to powers of two in fp32, so
+// both thresholds are trunc(frac * 2^32) and the code is k + [rnd <= threshold].
+// `v` is the scaled value up to the sign of a zero; the sign
+// bit of the code is taken from `sign_bits` (the bits of the unscaled element: scales are positive).
+// With a = min(|v|, 6):
+//   normal range   code = hi32(bits(a) * 2^10 + ((rnd * 2^10) mod 2^32)) - 252: the low 22 mantissa
+//                  bits and the low 22 random bits meet in the low word, their carry rounds up, and
+//                  6.0 itself maps to 7, so saturation needs no separate test;
+//   a < 1          with T = trunc(a * 2^33) = k * 2^32 + threshold (k = [a >= 0.5]),
+//                  code = hi32(T + 1 + ~rnd) = k + [rnd <= threshold].
+// A NaN saturates to 7 (the reference's code for a NaN element is an accident of its payload).
+__device__ __forceinline__ uint32_t e2m1_sr_code(float v, uint32_t sign_bits, uint32_t rnd) {
+  const float a = fminf(fabsf(v), 6.0f);
+  const uint64_t addend = ((uint64_t)0xFFFFFF04u << 32) | (uint64_t)(rnd * 1024u);
+  const uint32_t cn = (uint32_t)(((uint64_t)f2u(a) * 1024ull + addend) >> 32);
+  const uint64_t t = __float2ull_rz(__fmul_rn(a, 8589934592.0f));
+  const uint32_t cd = (uint32_t)((t + 1ull + (uint64_t)(~rnd)) >> 32);
+  const uint32_t mag = a < 1.0f ? cd : cn;
+  return mag | ((sign_bits >> 28) & 8u);
 }
 
 // E2M1 decode to fp32 (alto/kernels/fp4/fp4_common/triton_fp4_ops.py:100-132).

@@ -14,6 +14,8 @@
 //               output row receives 128 contiguous bytes.
 //   2D        : a CTA owns 128 rows x 4 blocks of columns; segment and block maxima go
 //               through shared memory, and the tile is written in both packings.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace altob200 {
@@ -138,17 +140,39 @@ __device__ __forceinline__ BlockScale make_block_scale_opts(uint32_t amax_abs_bi
   return s;
 }
 
-template <int FMT, bool IN_BF16>
+// One element divided by its block scale.  FAST is decided once per warp (every lane's block scale
+// allows the reciprocal forms), so that the element loops carry no per-element branch; the other
+// variant divides.  Both give the correctly rounded quotient.
+template <int FMT, bool IN_BF16, bool FAST>
 __device__ __forceinline__ float scale_elem(float x, const BlockScale& s) {
-  if (Fmt<FMT>::MX) return s.fast ? __fmul_rn(x, s.r) : __fdiv_rn(x, s.q);
-  return s.fast ? div_bf16_num(x, s.q, s.r) : __fdiv_rn(x, s.q);
+  if (!FAST) return __fdiv_rn(x, s.q);
+  if (Fmt<FMT>::MX) return __fmul_rn(x, s.r);
+  return div_bf16_num(x, s.q, s.r);
 }
 
-// Quantise 2 scaled values into one FP4 byte (v0 low nibble).
-template <int ROUND>
-__device__ __forceinline__ uint32_t fp4_pair(float v0, float v1, uint32_t r0, uint32_t r1) {
-  if (ROUND == ALTOB200_ROUND_RTN) return e2m1x2_rtn_hw(v0, v1);
-  return e2m1_sr_bits(v0, r0) | (e2m1_sr_bits(v1, r1) << 4);
+// The scaled element up to the sign of a zero (the stochastic-rounding encoder takes the sign from x).
+template <int FMT, bool IN_BF16, bool FAST>
+__device__ __forceinline__ float scale_elem_mag(float x, const BlockScale& s) {
+  if (!FAST) return __fdiv_rn(x, s.q);
+  if (Fmt<FMT>::MX) return __fmul_rn(x, s.r);
+  return div_bf16_num_mag(x, s.q, s.r);
+}
+
+// Scale and quantise 2 elements into one FP4 byte (x0 in the low nibble).
+template <int FMT, bool IN_BF16, int ROUND, bool FAST>
+__device__ __forceinline__ uint32_t fp4_pair(float x0, float x1, const BlockScale& s, uint32_t r0, uint32_t r1) {
+  if (ROUND == ALTOB200_ROUND_RTN)
+    return e2m1x2_rtn_hw(scale_elem<FMT, IN_BF16, FAST>(x0, s), scale_elem<FMT, IN_BF16, FAST>(x1, s));
+  return e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(x0, s), f2u(x0), r0) |
+         (e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(x1, s), f2u(x1), r1) << 4);
+}
+
+// Runs body(std::true_type) when every lane of the warp may use the reciprocal forms, else
+// body(std::false_type); must be reached by the whole warp.
+template <class Body>
+__device__ __forceinline__ void with_uniform_fast(bool lane_fast, Body body) {
+  if (__all_sync(0xFFFFFFFFu, lane_fast)) body(std::true_type{});
+  else body(std::false_type{});
 }
 
 // Quotient and remainder with a 32-bit divide whenever the operands fit (a 64-bit divide costs
@@ -305,27 +329,30 @@ __global__ void __launch_bounds__(256) quantize_rowwise_kernel(RowwiseArgs a) {
       }
     }
 
+    with_uniform_fast(s.fast, [&](auto fast_tag) {
+      constexpr bool FAST = decltype(fast_tag)::value;
+      if (F::FP4) {
+        uint32_t lo = 0, hi = 0;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = scale_elem<FMT, IN_BF16>(v[j], s);
-
-    if (F::FP4) {
-      uint32_t lo = 0, hi = 0;
+        for (int j = 0; j < 4; ++j) {
+          lo |= fp4_pair<FMT, IN_BF16, ROUND, FAST>(v[2 * j], v[2 * j + 1], s, r0[j], r1[j]) << (8 * j);
+          hi |= fp4_pair<FMT, IN_BF16, ROUND, FAST>(v[8 + 2 * j], v[9 + 2 * j], s, r0[4 + j], r1[4 + j]) << (8 * j);
+        }
+        if (active)
+          *reinterpret_cast<uint2*>(a.codes + row * half_cols + (col >> 1)) = make_uint2(lo, hi);
+      } else {
+        uint32_t o[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        lo |= fp4_pair<ROUND>(v[2 * j], v[2 * j + 1], r0[j], r1[j]) << (8 * j);
-        hi |= fp4_pair<ROUND>(v[8 + 2 * j], v[9 + 2 * j], r0[4 + j], r1[4 + j]) << (8 * j);
+        for (int j = 0; j < 4; ++j) {
+          float q[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) q[i] = scale_elem<FMT, IN_BF16, FAST>(v[4 * j + i], s);
+          o[j] = fp8x2_rtn_hw<F::E5M2>(q[0], q[1]) | (fp8x2_rtn_hw<F::E5M2>(q[2], q[3]) << 16);
+        }
+        if (active)
+          *reinterpret_cast<uint4*>(a.codes + row * a.cols + col) = make_uint4(o[0], o[1], o[2], o[3]);
       }
-      if (active)
-        *reinterpret_cast<uint2*>(a.codes + row * half_cols + (col >> 1)) = make_uint2(lo, hi);
-    } else {
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        o[j] = fp8x2_rtn_hw<F::E5M2>(v[4 * j], v[4 * j + 1]) |
-               (fp8x2_rtn_hw<F::E5M2>(v[4 * j + 2], v[4 * j + 3]) << 16);
-      if (active)
-        *reinterpret_cast<uint4*>(a.codes + row * a.cols + col) = make_uint4(o[0], o[1], o[2], o[3]);
-    }
+    });
 
     // scales
     const int64_t kb = (chunk << 9) / F::B + lane / LPB;  // scale column of this lane
@@ -592,24 +619,28 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
             r1[4 * i] = o[0]; r1[4 * i + 1] = o[1]; r1[4 * i + 2] = o[2]; r1[4 * i + 3] = o[3];
           }
         }
-        uint64_t w0 = 0, w1 = 0;  // nibble j = code of entry j (slot order, or position order if TO_POS)
+        // nibble j = code of entry j (slot order, or position order if TO_POS), in two 32-bit halves
+        uint32_t w0h[2] = {0u, 0u}, w1h[2] = {0u, 0u};
+        with_uniform_fast(s0.fast && s1.fast, [&](auto fast_tag) {
+          constexpr bool FAST = decltype(fast_tag)::value;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float q0 = scale_elem<FMT, IN_BF16>(y0[j], s0);
-          const float q1 = scale_elem<FMT, IN_BF16>(y1[j], s1);
-          uint32_t c0, c1;
-          if (ROUND == ALTOB200_ROUND_RTN) {
-            // the hardware converter takes one value of each column per call
-            const uint32_t b = e2m1x2_rtn_hw(q0, q1);
-            c0 = b & 0xFu;
-            c1 = b >> 4;
-          } else {
-            c0 = e2m1_sr_bits(q0, r0[j]);
-            c1 = e2m1_sr_bits(q1, r1[j]);
+          for (int j = 0; j < 16; ++j) {
+            uint32_t c0, c1;
+            if (ROUND == ALTOB200_ROUND_RTN) {
+              // the hardware converter takes one value of each column per call
+              const uint32_t b = e2m1x2_rtn_hw(scale_elem<FMT, IN_BF16, FAST>(y0[j], s0),
+                                               scale_elem<FMT, IN_BF16, FAST>(y1[j], s1));
+              c0 = b & 0xFu;
+              c1 = b >> 4;
+            } else {
+              c0 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(y0[j], s0), f2u(y0[j]), r0[j]);
+              c1 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(y1[j], s1), f2u(y1[j]), r1[j]);
+            }
+            w0h[j >> 3] |= c0 << (4 * (j & 7));
+            w1h[j >> 3] |= c1 << (4 * (j & 7));
           }
-          w0 |= (uint64_t)c0 << (4 * j);
-          w1 |= (uint64_t)c1 << (4 * j);
-        }
+        });
+        const uint64_t w0 = ((uint64_t)w0h[1] << 32) | w0h[0], w1 = ((uint64_t)w1h[1] << 32) | w1h[0];
         uint64_t o0 = w0, o1 = w1;
         if (RHT && !TO_POS) {  // output position i takes slot perm[i]
           o0 = o1 = 0;
@@ -627,19 +658,22 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
       // FP8: one byte per element, no transform (the reference asserts that MXFP8 runs
       // without Hadamard, alto/kernels/dispatch/tensor.py:448-454)
       uint8_t* d = s_codes + ((size_t)blk * COL_TN + 2 * lane) * BLK_BYTES;
+      with_uniform_fast(s0.fast && s1.fast, [&](auto fast_tag) {
+        constexpr bool FAST = decltype(fast_tag)::value;
 #pragma unroll
-      for (int k = 0; k < B; k += 4) {
-        float q0[4], q1[4];
+        for (int k = 0; k < B; k += 4) {
+          float q0[4], q1[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          q0[j] = scale_elem<FMT, IN_BF16>(v0[k + j], s0);
-          q1[j] = scale_elem<FMT, IN_BF16>(v1[k + j], s1);
+          for (int j = 0; j < 4; ++j) {
+            q0[j] = scale_elem<FMT, IN_BF16, FAST>(v0[k + j], s0);
+            q1[j] = scale_elem<FMT, IN_BF16, FAST>(v1[k + j], s1);
+          }
+          *reinterpret_cast<uint32_t*>(d + k) = fp8x2_rtn_hw<F::E5M2>(q0[0], q0[1]) |
+                                                (fp8x2_rtn_hw<F::E5M2>(q0[2], q0[3]) << 16);
+          *reinterpret_cast<uint32_t*>(d + BLK_BYTES + k) =
+              fp8x2_rtn_hw<F::E5M2>(q1[0], q1[1]) | (fp8x2_rtn_hw<F::E5M2>(q1[2], q1[3]) << 16);
         }
-        *reinterpret_cast<uint32_t*>(d + k) = fp8x2_rtn_hw<F::E5M2>(q0[0], q0[1]) |
-                                              (fp8x2_rtn_hw<F::E5M2>(q0[2], q0[3]) << 16);
-        *reinterpret_cast<uint32_t*>(d + BLK_BYTES + k) =
-            fp8x2_rtn_hw<F::E5M2>(q1[0], q1[1]) | (fp8x2_rtn_hw<F::E5M2>(q1[2], q1[3]) << 16);
-      }
+      });
     }
     s_sf[(2 * lane) * NBLK + blk] = ok ? (uint8_t)s0.byte : 0;
     s_sf[(2 * lane + 1) * NBLK + blk] = ok ? (uint8_t)s1.byte : 0;
@@ -804,8 +838,11 @@ __global__ void __launch_bounds__(128 * Fmt<FMT>::B / 4) quantize_2d_kernel(Quan
 #pragma unroll
       for (int j = 0; j < 16; ++j) v[j] = round_in<IN_BF16>(__fmul_rn(v[j], 0.75f));
     }
+    with_uniform_fast(s.fast, [&](auto fast_tag) {
+      constexpr bool FAST = decltype(fast_tag)::value;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = scale_elem<FMT, IN_BF16>(v[j], s);
+      for (int j = 0; j < 16; ++j) v[j] = scale_elem<FMT, IN_BF16, FAST>(v[j], s);
+    });
     if (F::FP4) {
       uint32_t lo = 0, hi = 0;
 #pragma unroll
