@@ -381,6 +381,7 @@ struct RhtParams {
   int8_t pinv[16]; // slot k reads row pinv[k] of the block
   int8_t perm[16]; // output position i takes slot perm[i]
   float sign[16];  // sign applied to slot k after the butterfly
+  int64_t row_off[16];  // byte offset of row pinv[k] from the first row of a 16-row group (column passes)
 };
 
 __device__ __forceinline__ void hadamard16(float* z) {
@@ -451,20 +452,20 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
     const int64_t mb = m0 + (int64_t)blk * B;
     const bool ok = col_ok && mb < a.rows;  // rows % B == 0
     float v0[B], v1[B];
-    // ---- load (slot k <- row pinv[k] when the transform is on) ----
+    // ---- load (slot k <- row pinv[k] when the transform is on; the identity otherwise) ----
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(a.x) + (mb * a.ld + c) * (IN_BF16 ? 2 : 4);
+    const int64_t half_blk = 16 * a.ld * (IN_BF16 ? 2 : 4);  // second 16-row group of a 32-row block
 #pragma unroll
     for (int k = 0; k < B; ++k) {
-      const int src = RHT ? ((k & ~15) + a.rht.pinv[k & 15]) : k;
+      const uint8_t* src = base + a.rht.row_off[k & 15] + (k >= 16 ? half_blk : 0);
       float f0 = 0.f, f1 = 0.f;
       if (ok) {
         if (IN_BF16) {
-          const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(
-              reinterpret_cast<const __nv_bfloat16*>(a.x) + (mb + src) * a.ld + c));
+          const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(src));
           f0 = bf16lo_to_f32(w);
           f1 = bf16hi_to_f32(w);
         } else {
-          const float2 f = __ldg(reinterpret_cast<const float2*>(
-              reinterpret_cast<const float*>(a.x) + (mb + src) * a.ld + c));
+          const float2 f = __ldg(reinterpret_cast<const float2*>(src));
           f0 = f.x;
           f1 = f.y;
         }
@@ -479,29 +480,43 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
         hadamard16(v0 + g);
         hadamard16(v1 + g);
       }
+    }
+    // ---- scale by +-1/sqrt(16) (exact), round to the input dtype, block amax on the rounded bits ----
+    uint32_t am0 = 0, am1 = 0;
+    if (RHT && IN_BF16) {
+      // both columns of a lane travel as one packed bf16 pair: one conversion and one packed maximum
+      uint32_t acc = 0;
 #pragma unroll
       for (int k = 0; k < B; ++k) {
-        // +-1/sqrt(16) is exact; adding +0 turns a -0 product into the +0 a dot product yields
+        // the fused +0 turns a -0 product into the +0 that a dot product yields
         const float sg = 0.25f * a.rht.sign[k & 15];
-        v0[k] = __fadd_rn(__fmul_rn(v0[k], sg), 0.0f);
-        v1[k] = __fadd_rn(__fmul_rn(v1[k], sg), 0.0f);
-        if (IN_BF16) {
-          v0[k] = u2f(f32_to_bf16_bits(v0[k]) << 16);
-          v1[k] = u2f(f32_to_bf16_bits(v1[k]) << 16);
+        const __nv_bfloat162 p2 = __floats2bfloat162_rn(__fmaf_rn(v0[k], sg, 0.0f), __fmaf_rn(v1[k], sg, 0.0f));
+        const uint32_t pw = *reinterpret_cast<const uint32_t*>(&p2);
+        acc = absmax_bf16x2(acc, pw);
+        v0[k] = bf16lo_to_f32(pw);
+        v1[k] = bf16hi_to_f32(pw);
+      }
+      am0 = acc & 0xFFFFu;
+      am1 = acc >> 16;
+    } else {
+      if (RHT) {
+#pragma unroll
+        for (int k = 0; k < B; ++k) {
+          const float sg = 0.25f * a.rht.sign[k & 15];
+          v0[k] = __fmaf_rn(v0[k], sg, 0.0f);
+          v1[k] = __fmaf_rn(v1[k], sg, 0.0f);
         }
       }
-    }
-    // ---- block amax on the bits of the (possibly rounded) values ----
-    uint32_t am0 = 0, am1 = 0;
 #pragma unroll
-    for (int k = 0; k < B; ++k) {
-      const uint32_t b0 = f2u(v0[k]) & 0x7FFFFFFFu, b1 = f2u(v1[k]) & 0x7FFFFFFFu;
-      am0 = b0 > am0 ? b0 : am0;
-      am1 = b1 > am1 ? b1 : am1;
-    }
-    if (IN_BF16) {
-      am0 >>= 16;
-      am1 >>= 16;
+      for (int k = 0; k < B; ++k) {
+        const uint32_t b0 = f2u(v0[k]) & 0x7FFFFFFFu, b1 = f2u(v1[k]) & 0x7FFFFFFFu;
+        am0 = b0 > am0 ? b0 : am0;
+        am1 = b1 > am1 ? b1 : am1;
+      }
+      if (IN_BF16) {
+        am0 >>= 16;
+        am1 >>= 16;
+      }
     }
     BlockScale s0, s1;
     if (F::MX && (a.mx.clip | a.mx.uos)) {
@@ -752,176 +767,214 @@ struct Quant2dArgs {
   MxOpts mx;          // clip 0/1 and uos (the dynamic clip needs block sums and is 1-D only)
 };
 
+// 4 x 4 byte transpose: out[b] = (in[0].byte b, in[1].byte b, in[2].byte b, in[3].byte b)
+__device__ __forceinline__ void transpose4x4_bytes(const uint32_t* in, uint32_t* out) {
+  const uint32_t t0 = __byte_perm(in[0], in[1], 0x5140);  // a0 b0 a1 b1
+  const uint32_t t1 = __byte_perm(in[2], in[3], 0x5140);  // c0 d0 c1 d1
+  const uint32_t t2 = __byte_perm(in[0], in[1], 0x7362);  // a2 b2 a3 b3
+  const uint32_t t3 = __byte_perm(in[2], in[3], 0x7362);  // c2 d2 c3 d3
+  out[0] = __byte_perm(t0, t1, 0x5410);
+  out[1] = __byte_perm(t0, t1, 0x7632);
+  out[2] = __byte_perm(t2, t3, 0x5410);
+  out[3] = __byte_perm(t2, t3, 0x7632);
+}
+
+// A thread owns 16 rows x 8 columns, kept in registers from the load to both stores; a warp owns
+// 4 block columns (LC lanes) x 16 * LR rows, so block maxima need shuffles only and the kernel uses
+// no shared memory.  The K packing is written row by row (4 or 8 bytes per row per lane, 32 or 128
+// contiguous bytes per row per warp); for the transposed packing the thread's 16 x 8 codes are
+// transposed in registers (nibble merge of row pairs, then 4 x 4 byte transposes) and every column
+// receives 8 (FP4) or 16 (FP8) contiguous bytes per lane, 32 contiguous bytes per warp and column.
 template <int FMT, bool IN_BF16>
-__global__ void __launch_bounds__(128 * Fmt<FMT>::B / 4) quantize_2d_kernel(Quant2dArgs a) {
+__global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
   using F = Fmt<FMT>;
   constexpr int B = F::B;
-  constexpr int TR = 128;           // tile rows
-  constexpr int TC = 4 * B;         // tile cols (64 or 128)
-  constexpr int SEGS = TC / 16;     // 16-element segments per row (4 or 8)
-  constexpr int NBR = TR / B, NBC = 4;
-  constexpr int EB = F::FP4 ? 2 : 1;  // elements per byte
-  constexpr int KROW = TC / EB;       // bytes per tile row in K packing (+16 pad)
-  __shared__ uint32_t s_segmax[TR][SEGS];
-  __shared__ float s_q[NBR][NBC], s_r[NBR][NBC], s_plain[NBR][NBC];
-  __shared__ uint8_t s_byte[NBR][NBC], s_fast[NBR][NBC];
-  __shared__ __align__(16) uint8_t s_tile[TR][KROW + 16];
-
-  const int t = threadIdx.x;
-  const int r = t / SEGS, sg = t % SEGS;
-  const int64_t row = (int64_t)blockIdx.y * TR + r;
-  const int64_t col = (int64_t)blockIdx.x * TC + sg * 16;
-  const bool ok = row < a.rows && col < a.cols;  // cols % 16 == 0
+  constexpr int LC = B / 2;          // lanes across columns: 8 columns each, 4 block columns per warp
+  constexpr int LR = 32 / LC;        // 16-row groups per warp: 4 (B = 16) or 2 (B = 32)
+  constexpr int TR = 16 * LR, TC = 8 * LC;  // warp tile: 64 x 64 or 32 x 128
+  constexpr int ESZ = IN_BF16 ? 2 : 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t tiles_c = (a.cols + TC - 1) / TC, tiles_r = (a.rows + TR - 1) / TR;
+  const int64_t tile = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tile >= tiles_c * tiles_r) return;  // whole warps leave; nothing below synchronises the block
+  int64_t tr, tc;
+  divmod_fast(tile, tiles_c, &tr, &tc);
+  const int lc = lane % LC, lr = lane / LC;
+  const int64_t row0 = tr * TR + lr * 16, col0 = tc * TC + lc * 8;
+  const bool ok = row0 < a.rows && col0 < a.cols;  // rows % B == 0 and cols % B == 0
   const bool use_outer = (!F::MX) && a.outer != nullptr;
   const float outer = use_outer ? __ldg(a.outer) : 1.0f;
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(a.w) + (row0 * a.ld + col0) * ESZ;
+  const int64_t pitch = a.ld * ESZ;
 
-  float v[16];
+  // ---- load and block maximum ----
+  uint4 raw[IN_BF16 ? 16 : 1];  // bf16: the 16 x 8 elements stay in registers; fp32: rows are read again
   uint32_t amax_bits = 0;
   if (IN_BF16) {
-    uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
-    if (ok) {
-      const uint4* p = reinterpret_cast<const uint4*>(
-          reinterpret_cast<const __nv_bfloat16*>(a.w) + row * a.ld + col);
-      w0 = __ldg(p);
-      w1 = __ldg(p + 1);
-    }
-    const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
     uint32_t acc = 0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      acc = absmax_bf16x2(acc, w[j]);
-      v[2 * j] = bf16lo_to_f32(w[j]);
-      v[2 * j + 1] = bf16hi_to_f32(w[j]);
+    for (int i = 0; i < 16; ++i) {
+      raw[i] = ok ? __ldg(reinterpret_cast<const uint4*>(src + i * pitch)) : make_uint4(0u, 0u, 0u, 0u);
+      acc = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(acc, raw[i].x), raw[i].y), raw[i].z), raw[i].w);
     }
     amax_bits = fold_bf16x2(acc);
-  } else {
+  } else if (ok) {
+#pragma unroll 4
+    for (int i = 0; i < 16; ++i) {
+      const uint4 p = __ldg(reinterpret_cast<const uint4*>(src + i * pitch));
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(src + i * pitch) + 1);
+      const uint32_t ws[8] = {p.x, p.y, p.z, p.w, q.x, q.y, q.z, q.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (ok)
-        f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.w) + row * a.ld + col) + j);
-      v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const uint32_t b = f2u(v[j]) & 0x7FFFFFFFu;
-      amax_bits = b > amax_bits ? b : amax_bits;
-    }
-  }
-  s_segmax[r][sg] = amax_bits;
-  __syncthreads();
-  if (t < NBR * NBC) {
-    const int br = t / NBC, bc = t % NBC;
-    uint32_t m = 0;
-    for (int i = 0; i < B; ++i)
-      for (int j = 0; j < B / 16; ++j) {
-        const uint32_t x = s_segmax[br * B + i][bc * (B / 16) + j];
-        m = x > m ? x : m;
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t b = ws[j] & 0x7FFFFFFFu;
+        amax_bits = b > amax_bits ? b : amax_bits;
       }
-    const BlockScale s = (F::MX && (a.mx.clip | a.mx.uos))
-                             ? make_block_scale_opts<FMT, IN_BF16>(m, 0.0f, 0.0f, B * B, a.mx)
-                             : make_block_scale<FMT, IN_BF16>(m, use_outer, outer);
-    s_q[br][bc] = s.q; s_r[br][bc] = s.r; s_plain[br][bc] = s.plain;
-    s_byte[br][bc] = (uint8_t)s.byte; s_fast[br][bc] = s.fast ? 1 : 0;
-    const int64_t gbr = (int64_t)blockIdx.y * NBR + br, gbc = (int64_t)blockIdx.x * NBC + bc;
-    if (a.scale_plain != nullptr && gbr < a.rows / B && gbc < a.cols / B) {
-      if (F::MX) reinterpret_cast<uint8_t*>(a.scale_plain)[gbr * (a.cols / B) + gbc] = (uint8_t)s.byte;
-      else reinterpret_cast<float*>(a.scale_plain)[gbr * (a.cols / B) + gbc] = s.plain;
     }
   }
-  __syncthreads();
-  {
-    const int br = r / B, bc = (sg * 16) / B;
-    BlockScale s;
-    s.q = s_q[br][bc]; s.r = s_r[br][bc]; s.fast = s_fast[br][bc] != 0; s.byte = 0; s.plain = 0.f;
-    if (F::MX && a.mx.clip == 1) {
+  // lanes of one block: B / 8 neighbours along the columns, B / 16 row groups
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = round_in<IN_BF16>(__fmul_rn(v[j], 0.75f));
+  for (int o = 1; o < B / 8; o <<= 1) {
+    const uint32_t t = __shfl_xor_sync(0xFFFFFFFFu, amax_bits, o);
+    amax_bits = t > amax_bits ? t : amax_bits;
+  }
+  if (B == 32) {
+    const uint32_t t = __shfl_xor_sync(0xFFFFFFFFu, amax_bits, LC);
+    amax_bits = t > amax_bits ? t : amax_bits;
+  }
+  const BlockScale s = (F::MX && (a.mx.clip | a.mx.uos))
+                           ? make_block_scale_opts<FMT, IN_BF16>(amax_bits, 0.0f, 0.0f, B * B, a.mx)
+                           : make_block_scale<FMT, IN_BF16>(amax_bits, use_outer, outer);
+  const bool clip = F::MX && a.mx.clip == 1;
+
+  // ---- encode row by row, K packing ----
+  uint32_t kw[F::FP4 ? 16 : 32];  // FP4: one word per row (8 codes); FP8: two words per row (8 bytes)
+  with_uniform_fast(s.fast, [&](auto fast_tag) {
+    constexpr bool FAST = decltype(fast_tag)::value;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float v[8];
+      if (IN_BF16) {
+        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[2 * j] = bf16lo_to_f32(w[j]);
+          v[2 * j + 1] = bf16hi_to_f32(w[j]);
+        }
+      } else {
+        float4 p = make_float4(0.f, 0.f, 0.f, 0.f), q = p;
+        if (ok) {
+          p = __ldg(reinterpret_cast<const float4*>(src + i * pitch));
+          q = __ldg(reinterpret_cast<const float4*>(src + i * pitch) + 1);
+        }
+        v[0] = p.x; v[1] = p.y; v[2] = p.z; v[3] = p.w;
+        v[4] = q.x; v[5] = q.y; v[6] = q.z; v[7] = q.w;
+      }
+      if (clip) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = round_in<IN_BF16>(__fmul_rn(v[j], 0.75f));
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = scale_elem<FMT, IN_BF16, FAST>(v[j], s);
+      if (F::FP4) {
+        kw[i] = e2m1x2_rtn_hw(v[0], v[1]) | (e2m1x2_rtn_hw(v[2], v[3]) << 8) | (e2m1x2_rtn_hw(v[4], v[5]) << 16) |
+                (e2m1x2_rtn_hw(v[6], v[7]) << 24);
+        if (ok) *reinterpret_cast<uint32_t*>(a.codes_k + (row0 + i) * (a.cols >> 1) + (col0 >> 1)) = kw[i];
+      } else {
+        kw[2 * i] = fp8x2_rtn_hw<F::E5M2>(v[0], v[1]) | (fp8x2_rtn_hw<F::E5M2>(v[2], v[3]) << 16);
+        kw[2 * i + 1] = fp8x2_rtn_hw<F::E5M2>(v[4], v[5]) | (fp8x2_rtn_hw<F::E5M2>(v[6], v[7]) << 16);
+        if (ok) *reinterpret_cast<uint2*>(a.codes_k + (row0 + i) * a.cols + col0) = make_uint2(kw[2 * i], kw[2 * i + 1]);
+      }
     }
-    with_uniform_fast(s.fast, [&](auto fast_tag) {
-      constexpr bool FAST = decltype(fast_tag)::value;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = scale_elem<FMT, IN_BF16, FAST>(v[j], s);
-    });
+  });
+
+  // ---- transposed packing: column col0 + c, rows row0 .. row0 + 15 along the packed axis ----
+  if (a.codes_t != nullptr) {
     if (F::FP4) {
-      uint32_t lo = 0, hi = 0;
+      // byte j of ev[..] / od[..]: rows 2j (low nibble) and 2j + 1 of an even / odd column
+      uint32_t ev[8], od[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        lo |= e2m1x2_rtn_hw(v[2 * j], v[2 * j + 1]) << (8 * j);
-        hi |= e2m1x2_rtn_hw(v[8 + 2 * j], v[9 + 2 * j]) << (8 * j);
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t lo = kw[2 * j], hi = kw[2 * j + 1];
+        ev[j] = (lo & 0x0F0F0F0Fu) | ((hi << 4) & 0xF0F0F0F0u);  // byte b: column 2b
+        od[j] = ((lo >> 4) & 0x0F0F0F0Fu) | (hi & 0xF0F0F0F0u);  // byte b: column 2b + 1
       }
-      *reinterpret_cast<uint2*>(&s_tile[r][sg * 8]) = make_uint2(lo, hi);
-      if (ok) *reinterpret_cast<uint2*>(a.codes_k + row * (a.cols >> 1) + (col >> 1)) = make_uint2(lo, hi);
-    } else {
-      uint32_t o[4];
+      uint32_t e0[4], e1[4], o0[4], o1[4];
+      transpose4x4_bytes(ev, e0);      // e0[b]: bytes 0..3 of column 2b
+      transpose4x4_bytes(ev + 4, e1);  // e1[b]: bytes 4..7
+      transpose4x4_bytes(od, o0);
+      transpose4x4_bytes(od + 4, o1);
+      if (ok) {
+        uint8_t* dst = a.codes_t + col0 * (a.rows >> 1) + (row0 >> 1);
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        o[j] = fp8x2_rtn_hw<F::E5M2>(v[4 * j], v[4 * j + 1]) |
-               (fp8x2_rtn_hw<F::E5M2>(v[4 * j + 2], v[4 * j + 3]) << 16);
-      *reinterpret_cast<uint4*>(&s_tile[r][sg * 16]) = make_uint4(o[0], o[1], o[2], o[3]);
-      if (ok) *reinterpret_cast<uint4*>(a.codes_k + row * a.cols + col) = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int b = 0; b < 4; ++b) {
+          *reinterpret_cast<uint2*>(dst + (2 * b) * (a.rows >> 1)) = make_uint2(e0[b], e1[b]);
+          *reinterpret_cast<uint2*>(dst + (2 * b + 1) * (a.rows >> 1)) = make_uint2(o0[b], o1[b]);
+        }
+      }
+    } else {
+      // kw[2 i + h]: row i, bytes = columns 4h .. 4h + 3
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t t[4][4];  // t[g][b]: rows 4g .. 4g + 3 of column 4h + b
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t in[4] = {kw[2 * (4 * g) + h], kw[2 * (4 * g + 1) + h], kw[2 * (4 * g + 2) + h],
+                                  kw[2 * (4 * g + 3) + h]};
+          transpose4x4_bytes(in, t[g]);
+        }
+        if (ok) {
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+            *reinterpret_cast<uint4*>(a.codes_t + (col0 + 4 * h + b) * a.rows + row0) =
+                make_uint4(t[0][b], t[1][b], t[2][b], t[3][b]);
+        }
+      }
     }
   }
-  // packed scales for the K packing: one word (4 block columns) per row
-  if (a.packed_k != nullptr && sg == 0 && row < a.rows) {
-    const int br = r / B;
-    const int64_t kb = (int64_t)blockIdx.x * NBC;
+
+  // ---- scales ----
+  const bool col_ok = col0 < a.cols, row_ok = row0 < a.rows;
+  if (a.scale_plain != nullptr && ok && (lc % (B / 8)) == 0 && (lr % (B / 16)) == 0) {
+    const int64_t idx = (row0 / B) * (a.cols / B) + col0 / B;
+    if (F::MX) reinterpret_cast<uint8_t*>(a.scale_plain)[idx] = (uint8_t)s.byte;
+    else reinterpret_cast<float*>(a.scale_plain)[idx] = s.plain;
+  }
+  const uint32_t my_byte = ok ? s.byte : 0u;  // blocks outside the matrix contribute zero bytes
+  if (a.packed_k != nullptr) {
+    // one word per row: the scale bytes of the warp's 4 block columns; the rows of a group are
+    // shared out over its LC lanes
     uint32_t word = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (kb + j < a.cols / B) word |= (uint32_t)s_byte[br][j] << (8 * j);
-    if (kb < a.nct_k * 4)
-      *reinterpret_cast<uint32_t*>(a.packed_k + packed_scale_offset(row, kb, a.nct_k)) = word;
-  }
-  __syncthreads();
-  // transposed packing: output row = tile column k, 128 tile rows along the packed axis
-  if (a.codes_t != nullptr) {
-    constexpr int OUT_BYTES = TR / EB;       // bytes per output row per tile (64 or 128)
-    constexpr int CH = OUT_BYTES / 8;        // 8-byte chunks per output row
-    for (int i = t; i < TC * CH; i += blockDim.x) {
-      const int k = i / CH, ch = i - k * CH;
-      const int64_t gk = (int64_t)blockIdx.x * TC + k;
-      if (gk >= a.cols) continue;
-      uint32_t lo = 0, hi = 0;
-      if (F::FP4) {
-        // 8 output bytes = 16 tile rows; byte j pairs rows 2j (low nibble) and 2j+1
-        const int rb = ch * 16;
-        const int sh = (k & 1) * 4;
+    for (int j = 0; j < 4; ++j) word |= __shfl_sync(0xFFFFFFFFu, my_byte, lr * LC + j * (B / 8)) << (8 * j);
+    const int64_t kb = tc * 4;
+    if (row_ok) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t c0 = (s_tile[rb + 2 * j][k >> 1] >> sh) & 0xFu;
-          const uint32_t c1 = (s_tile[rb + 2 * j + 1][k >> 1] >> sh) & 0xFu;
-          const uint32_t b = c0 | (c1 << 4);
-          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
-        }
-        const int64_t grow = (int64_t)blockIdx.y * TR + rb;
-        if (grow < a.rows)  // rows % 16 == 0
-          *reinterpret_cast<uint2*>(a.codes_t + gk * (a.rows >> 1) + (grow >> 1)) = make_uint2(lo, hi);
-      } else {
-        const int rb = ch * 8;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t b = s_tile[rb + j][k];
-          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
-        }
-        const int64_t grow = (int64_t)blockIdx.y * TR + rb;
-        if (grow < a.rows)  // rows % 32 == 0
-          *reinterpret_cast<uint2*>(a.codes_t + gk * a.rows + grow) = make_uint2(lo, hi);
+      for (int i = 0; i < 16 / LC; ++i) {
+        const int64_t row = row0 + lc * (16 / LC) + i;
+        *reinterpret_cast<uint32_t*>(a.packed_k + packed_scale_offset(row, kb, a.nct_k)) = word;
       }
     }
   }
   if (a.packed_t != nullptr) {
-    // rows = tile columns (TC), scale columns = tile row blocks (NBR = 8 or 4)
-    for (int i = t; i < TC * (NBR / 4); i += blockDim.x) {
-      const int k = i / (NBR / 4), qd = i - k * (NBR / 4);
-      const int64_t gk = (int64_t)blockIdx.x * TC + k;
-      const int64_t kb = (int64_t)blockIdx.y * NBR + qd * 4;
-      if (gk >= a.cols || kb >= a.nct_t * 4) continue;
+    // rows of this layout are the matrix columns, scale columns the row blocks
+    if (LR == 4) {
+      // B = 16: the warp's 4 row groups are the 4 bytes of one word; the 8 columns of a lane are
+      // shared out over the 4 row groups
       uint32_t word = 0;
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (kb + j < a.rows / B) word |= (uint32_t)s_byte[qd * 4 + j][k / B] << (8 * j);
-      *reinterpret_cast<uint32_t*>(a.packed_t + packed_scale_offset(gk, kb, a.nct_t)) = word;
+      for (int j = 0; j < 4; ++j) word |= __shfl_sync(0xFFFFFFFFu, my_byte, j * LC + lc) << (8 * j);
+      if (col_ok) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          *reinterpret_cast<uint32_t*>(a.packed_t + packed_scale_offset(col0 + 2 * lr + e, tr * 4, a.nct_t)) = word;
+      }
+    } else {
+      // B = 32: the warp holds one row block, one byte per column
+      if (ok) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          a.packed_t[packed_scale_offset(col0 + 4 * lr + e, tr, a.nct_t)] = (uint8_t)s.byte;
+      }
     }
   }
 }
@@ -1008,56 +1061,51 @@ __global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
       }
     }
   } else {
-    // column pass: 16-row groups x 2 columns per lane, as in the column-wise quantizer
+    // column pass: 16-row groups x 2 columns per lane, as in the column-wise quantizer.  Rounding to
+    // the input dtype and the factor 1/4 are monotone in the magnitude, so the maximum is taken over
+    // the raw butterfly outputs and scaled and rounded once per thread.
     const int64_t groups = a.rows >> 4;
     const int64_t col_tiles = (a.cols + 63) >> 6;
     const int64_t n_tasks = groups * col_tiles;
     const int64_t warp0 = (int64_t)blockIdx.x * 8 + warp, n_warps = (int64_t)gridDim.x * 8;
+    uint32_t raw_rht = 0, plain16 = 0;
     for (int64_t task = warp0; task < n_tasks; task += n_warps) {
       int64_t g, ct;
       divmod_fast(task, col_tiles, &g, &ct);
       const int64_t c = (ct << 6) + 2 * lane;
       if (c >= a.cols) continue;
+      const uint8_t* base = reinterpret_cast<const uint8_t*>(a.x) + ((g << 4) * a.ld + c) * (IN_BF16 ? 2 : 4);
       float v0[16], v1[16];
 #pragma unroll
       for (int k = 0; k < 16; ++k) {
-        const int src = a.rht.pinv[k];
-        float f0, f1;
         if (IN_BF16) {
-          const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(
-              reinterpret_cast<const __nv_bfloat16*>(a.x) + ((g << 4) + src) * a.ld + c));
-          f0 = bf16lo_to_f32(w);
-          f1 = bf16hi_to_f32(w);
+          const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(base + a.rht.row_off[k]));
+          plain16 = absmax_bf16x2(plain16, w);
+          v0[k] = bf16lo_to_f32(w);
+          v1[k] = bf16hi_to_f32(w);
         } else {
-          const float2 f = __ldg(reinterpret_cast<const float2*>(
-              reinterpret_cast<const float*>(a.x) + ((g << 4) + src) * a.ld + c));
-          f0 = f.x;
-          f1 = f.y;
+          const float2 f = __ldg(reinterpret_cast<const float2*>(base + a.rht.row_off[k]));
+          const uint32_t b0 = f2u(f.x) & 0x7FFFFFFFu, b1 = f2u(f.y) & 0x7FFFFFFFu;
+          am_plain = b0 > am_plain ? b0 : am_plain;
+          am_plain = b1 > am_plain ? b1 : am_plain;
+          v0[k] = f.x;
+          v1[k] = f.y;
         }
-        const uint32_t b0 = f2u(f0) & 0x7FFFFFFFu, b1 = f2u(f1) & 0x7FFFFFFFu;
-        am_plain = b0 > am_plain ? b0 : am_plain;
-        am_plain = b1 > am_plain ? b1 : am_plain;
-        v0[k] = f0;
-        v1[k] = f1;
       }
       hadamard16(v0);
       hadamard16(v1);
 #pragma unroll
       for (int k = 0; k < 16; ++k) {
-        // the row signs of the transform do not change magnitudes
-        float y0 = __fmul_rn(v0[k], 0.25f), y1 = __fmul_rn(v1[k], 0.25f);
-        uint32_t b0, b1;
-        if (IN_BF16) {
-          b0 = (f32_to_bf16_bits(y0) & 0x7FFFu) << 16;
-          b1 = (f32_to_bf16_bits(y1) & 0x7FFFu) << 16;
-        } else {
-          b0 = f2u(y0) & 0x7FFFFFFFu;
-          b1 = f2u(y1) & 0x7FFFFFFFu;
-        }
-        am_rht = b0 > am_rht ? b0 : am_rht;
-        am_rht = b1 > am_rht ? b1 : am_rht;
+        // integer maximum of the magnitudes' bits: a NaN is larger than every number, as in torch.amax
+        const uint32_t b0 = f2u(v0[k]) & 0x7FFFFFFFu, b1 = f2u(v1[k]) & 0x7FFFFFFFu;
+        raw_rht = b0 > raw_rht ? b0 : raw_rht;
+        raw_rht = b1 > raw_rht ? b1 : raw_rht;
       }
     }
+    if (IN_BF16) am_plain = fold_bf16x2(plain16) << 16;
+    // the row signs of the transform do not change magnitudes
+    const float y = __fmul_rn(u2f(raw_rht), 0.25f);
+    am_rht = IN_BF16 ? ((f32_to_bf16_bits(y) & 0x7FFFu) << 16) : (f2u(y) & 0x7FFFFFFFu);
   }
   am_plain = warp_max_u32(am_plain);
   am_rht = warp_max_u32(am_rht);
@@ -1349,6 +1397,11 @@ static int fill_rht(RhtParams* r, int n, const int32_t* perm, const int32_t* sig
   return ALTOB200_OK;
 }
 
+// Byte offsets of the rows that feed butterfly slots 0..15, for a matrix with leading dimension `ld`.
+static void fill_rht_row_offsets(RhtParams* r, int64_t ld, int esz) {
+  for (int k = 0; k < 16; ++k) r->row_off[k] = (int64_t)r->pinv[k] * ld * esz;
+}
+
 template <int FMT, bool IN_BF16>
 static int launch_rowwise(const RowwiseArgs& a, int rounding, cudaStream_t st) {
   const int64_t tasks = a.rows * ((a.cols + 511) >> 9);
@@ -1393,9 +1446,10 @@ static int launch_colwise(const ColwiseArgs& a, int rounding, cudaStream_t st) {
 
 template <int FMT, bool IN_BF16>
 static int launch_2d(const Quant2dArgs& a, cudaStream_t st) {
-  constexpr int TC = 4 * Fmt<FMT>::B;
-  dim3 grid((unsigned)ceil_div(a.cols, TC), (unsigned)ceil_div(a.rows, 128));
-  quantize_2d_kernel<FMT, IN_BF16><<<grid, 128 * Fmt<FMT>::B / 4, 0, st>>>(a);
+  // one warp per tile of 4 block columns x (64 rows for 16-blocks, 32 rows for 32-blocks)
+  constexpr int TC = 4 * Fmt<FMT>::B, TR = 1024 / Fmt<FMT>::B;
+  const int64_t tiles = ceil_div(a.cols, TC) * ceil_div(a.rows, TR);
+  quantize_2d_kernel<FMT, IN_BF16><<<(unsigned)ceil_div(tiles, 8), 256, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 
@@ -1555,6 +1609,7 @@ int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t
   philox_make_keys(p->philox_seed, &a.pk);
   int rc = fill_rht(&a.rht, p->rht_n, p->rht_perm, p->rht_sign);
   if (rc != ALTOB200_OK) return rc;
+  fill_rht_row_offsets(&a.rht, ld, p->in_dtype == ALTOB200_DT_BF16 ? 2 : 4);
   rc = fill_mx_opts(&a.mx, p, true);
   if (rc != ALTOB200_OK) return rc;
   rc = clear_packed_if_padded(scale_packed, cols, rows / B, st);
@@ -1608,6 +1663,7 @@ int altob200_amax(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, i
   a.amax_bits = amax_bits; a.outer_scale = outer_scale; a.counter = (uint32_t*)scratch;
   int rc = fill_rht(&a.rht, rht_n, rht_perm, rht_sign);
   if (rc != ALTOB200_OK) return rc;
+  fill_rht_row_offsets(&a.rht, ld, esz);
   ALTOB200_CUDA_CHECK(cudaMemsetAsync(amax_bits, 0, 2 * sizeof(uint32_t), st));
   const int64_t work = rht_n ? (rows / 16) * ceil_div(cols, 64) / 8 + 1
                              : rows * cols / (16 / esz) / 256 + 1;
