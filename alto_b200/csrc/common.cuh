@@ -87,14 +87,19 @@ __device__ __forceinline__ float round_to_e4m3_grid(float x, uint32_t* code) {
 
 // NVFP4 block scales (inner on the E4M3 grid, quant = inner * outer).
 //   alto/kernels/fp4/nvfp4/nvfp_quantization.py:255-289
-__device__ __forceinline__ void nvfp4_block_scale(float amax, bool use_outer, float outer,
-                                                  float* inner, float* quant, uint32_t* code) {
-  if (amax != amax) amax = 0.0f;  // NaN amax -> 0
-  float raw = use_outer ? __fdiv_rn(__fdiv_rn(amax, outer), 6.0f) : __fdiv_rn(amax, 6.0f);
+// `raw` = amax / outer / 6 (or amax / 6), correctly rounded.
+__device__ __forceinline__ void nvfp4_block_scale_from_raw(float raw, bool use_outer, float outer,
+                                                           float* inner, float* quant, uint32_t* code) {
   raw = fminf(fmaxf(raw, 0.015625f), 448.0f);
   const float in = round_to_e4m3_grid(raw, code);
   *inner = in;
   *quant = use_outer ? __fmul_rn(in, outer) : in;
+}
+__device__ __forceinline__ void nvfp4_block_scale(float amax, bool use_outer, float outer,
+                                                  float* inner, float* quant, uint32_t* code) {
+  if (amax != amax) amax = 0.0f;  // NaN amax -> 0
+  const float raw = use_outer ? __fdiv_rn(__fdiv_rn(amax, outer), 6.0f) : __fdiv_rn(amax, 6.0f);
+  nvfp4_block_scale_from_raw(raw, use_outer, outer, inner, quant, code);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -121,6 +126,16 @@ __device__ __forceinline__ float div_bf16_num(float x, float q, float r) {
 __device__ __forceinline__ float div_bf16_num_mag(float x, float q, float r) {
   const float y = __fmul_rn(x, r);
   const float e = __fmaf_rn(-y, q, x);
+  return __fmaf_rn(e, r, y);
+}
+
+// x / 6 for a normal x whose quotient and residual stay normal (callers keep |x| in [2^-91, 2^120) or
+// zero): y = x * r, e = fma(-y, 6, x), y' = fma(e, r, y) with r = RN(1/6) is the correctly rounded
+// quotient for every one of the 2^23 mantissas of x (checked exhaustively in integer arithmetic).
+__device__ __forceinline__ float div_by_6(float x) {
+  const float r = 0.16666667163372040f;
+  const float y = __fmul_rn(x, r);
+  const float e = __fmaf_rn(-y, 6.0f, x);
   return __fmaf_rn(e, r, y);
 }
 
@@ -173,16 +188,16 @@ __device__ __forceinline__ uint32_t e2m1x2_rtn_hw(float v0, float v1) {
 // `v` is the scaled value up to the sign of a zero; the sign
 // bit of the code is taken from `sign_bits` (the bits of the unscaled element: scales are positive).
 // With a = min(|v|, 6):
-//   normal range   code = hi32(bits(a) * 2^10 + ((rnd * 2^10) mod 2^32)) - 252: the low 22 mantissa
-//                  bits and the low 22 random bits meet in the low word, their carry rounds up, and
-//                  6.0 itself maps to 7, so saturation needs no separate test;
+//   normal range   code = (bits(a) + (rnd & (2^22 - 1)) - (126 << 23)) >> 22: the carry out of the low
+//                  22 mantissa bits rounds up, and 6.0 itself maps to 7, so saturation needs no
+//                  separate test;
 //   a < 1          with T = trunc(a * 2^33) = k * 2^32 + threshold (k = [a >= 0.5]),
 //                  code = hi32(T + 1 + ~rnd) = k + [rnd <= threshold].
 // A NaN saturates to 7 (the reference's code for a NaN element is an accident of its payload).
 __device__ __forceinline__ uint32_t e2m1_sr_code(float v, uint32_t sign_bits, uint32_t rnd) {
   const float a = fminf(fabsf(v), 6.0f);
-  const uint64_t addend = ((uint64_t)0xFFFFFF04u << 32) | (uint64_t)(rnd * 1024u);
-  const uint32_t cn = (uint32_t)(((uint64_t)f2u(a) * 1024ull + addend) >> 32);
+  const uint32_t ab = f2u(a);
+  const uint32_t cn = (ab + (rnd & 0x3FFFFFu) - (126u << 23)) >> 22;
   const uint64_t t = __float2ull_rz(__fmul_rn(a, 8589934592.0f));
   const uint32_t cd = (uint32_t)((t + 1ull + (uint64_t)(~rnd)) >> 32);
   const uint32_t mag = a < 1.0f ? cd : cn;

@@ -59,11 +59,26 @@ struct BlockScale {
   float plain;    // NVFP4: inner scale as fp32 (plain layout)
 };
 
+// The tensor-wide outer scale of NVFP4 in the forms the block-scale arithmetic needs (per thread, once).
+struct OuterScale {
+  bool use;    // an outer scale is applied
+  float v;     // its value (1 when unused)
+  float r;     // RN(1 / v)
+  bool fast;   // v allows the reciprocal form of amax / v
+};
+__device__ __forceinline__ OuterScale make_outer_scale(bool use, const float* p) {
+  OuterScale o;
+  o.use = use;
+  o.v = use ? __ldg(p) : 1.0f;
+  o.r = __frcp_rn(o.v);
+  o.fast = div_fast_ok(o.v);
+  return o;
+}
+
 // amax_abs_bits: max over the block of (bits & 0x7FFF..) in the input dtype's bit width
 // (bf16 bits or fp32 bits); integer max propagates NaN like torch.amax does.
 template <int FMT, bool IN_BF16>
-__device__ __forceinline__ BlockScale make_block_scale(uint32_t amax_abs_bits, bool use_outer,
-                                                       float outer) {
+__device__ __forceinline__ BlockScale make_block_scale(uint32_t amax_abs_bits, const OuterScale& os) {
   using F = Fmt<FMT>;
   BlockScale s;
   if (F::MX) {
@@ -75,7 +90,15 @@ __device__ __forceinline__ BlockScale make_block_scale(uint32_t amax_abs_bits, b
     s.plain = 0.0f;
   } else {
     const float amax = IN_BF16 ? u2f(amax_abs_bits << 16) : u2f(amax_abs_bits);
-    nvfp4_block_scale(amax, use_outer, outer, &s.plain, &s.q, &s.byte);
+    // bf16 amax of 0 or in [2^-30, 2^60): amax / outer / 6 by reciprocals with one correction step each
+    // (exact, see div_bf16_num and div_by_6); everything else divides
+    const uint32_t e8 = amax_abs_bits >> 7;
+    if (IN_BF16 && (amax_abs_bits == 0u || (e8 >= 97u && e8 < 187u)) && (!os.use || os.fast)) {
+      const float t = os.use ? div_bf16_num_mag(amax, os.v, os.r) : amax;
+      nvfp4_block_scale_from_raw(div_by_6(t), os.use, os.v, &s.plain, &s.q, &s.byte);
+    } else {
+      nvfp4_block_scale(amax, os.use, os.v, &s.plain, &s.q, &s.byte);
+    }
     s.fast = IN_BF16 && div_fast_ok(s.q);
     s.r = __frcp_rn(s.q);
   }
@@ -150,6 +173,13 @@ __device__ __forceinline__ float scale_elem(float x, const BlockScale& s) {
   return div_bf16_num(x, s.q, s.r);
 }
 
+// acc | (x << sh) for disjoint bits, as one integer multiply-add.
+__device__ __forceinline__ uint32_t merge_shifted(uint32_t x, int sh, uint32_t acc) {
+  uint32_t r;
+  asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(x), "r"(1u << sh), "r"(acc));
+  return r;
+}
+
 // The scaled element up to the sign of a zero (the stochastic-rounding encoder takes the sign from x).
 template <int FMT, bool IN_BF16, bool FAST>
 __device__ __forceinline__ float scale_elem_mag(float x, const BlockScale& s) {
@@ -163,8 +193,11 @@ template <int FMT, bool IN_BF16, int ROUND, bool FAST>
 __device__ __forceinline__ uint32_t fp4_pair(float x0, float x1, const BlockScale& s, uint32_t r0, uint32_t r1) {
   if (ROUND == ALTOB200_ROUND_RTN)
     return e2m1x2_rtn_hw(scale_elem<FMT, IN_BF16, FAST>(x0, s), scale_elem<FMT, IN_BF16, FAST>(x1, s));
-  return e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(x0, s), f2u(x0), r0) |
-         (e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(x1, s), f2u(x1), r1) << 4);
+  // codes are merged with multiply-adds (disjoint bits: adding is or-ing): the integer ALU is the
+  // busiest pipe of these kernels and the multiply-add pipe has room
+  const uint32_t c0 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(x0, s), f2u(x0), r0);
+  const uint32_t c1 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(x1, s), f2u(x1), r1);
+  return merge_shifted(c1, 4, c0);
 }
 
 // Runs body(std::true_type) when every lane of the warp may use the reciprocal forms, else
@@ -215,160 +248,186 @@ struct RowwiseArgs {
   MxOpts mx;
 };
 
+// A warp task is 4 consecutive rows x 512 contiguous columns (a lane: 16 columns of each row).  The
+// loads of all four rows are issued before the first is consumed (128 bytes per lane in flight), and
+// the index arithmetic of a task (row and chunk, pointers, position in the periodic random table) is
+// paid once per 64 elements of a lane.
+// Three resident blocks per SM (at most 85 registers per thread) measured fastest: fewer registers
+// spill, more leave too few warps to cover the issue slots.
+constexpr int ROW_R = 4;
+
 template <int FMT, bool IN_BF16, int ROUND>
-__global__ void __launch_bounds__(256) quantize_rowwise_kernel(RowwiseArgs a) {
+__global__ void __launch_bounds__(256, 3) quantize_rowwise_kernel(RowwiseArgs a) {
   using F = Fmt<FMT>;
   constexpr int LPB = F::B / 16;  // lanes per block
+  constexpr int ESZ = IN_BF16 ? 2 : 4;
+  constexpr int NV = IN_BF16 ? 2 : 4;  // 16-byte vectors per lane and row
   const int lane = threadIdx.x & 31;
   const int64_t chunks_per_row = (a.cols + 511) >> 9;
-  const int64_t n_tasks = a.rows * chunks_per_row;
+  const int64_t n_tasks = ((a.rows + ROW_R - 1) / ROW_R) * chunks_per_row;
   const int64_t warp0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-  const bool use_outer = (!F::MX) && a.outer != nullptr;
-  const float outer = use_outer ? __ldg(a.outer) : 1.0f;
+  const OuterScale os = make_outer_scale((!F::MX) && a.outer != nullptr, a.outer);
   const int64_t half_cols = a.cols >> 1;
+  const int64_t nkb = a.cols / F::B;
+  const bool tiled = a.tile_rows != 0;
+  const uint32_t t_rows = (uint32_t)a.tile_rows, t_pairs = (uint32_t)a.tile_pairs;
 
   for (int64_t task = warp0; task < n_tasks; task += n_warps) {
-    int64_t row, chunk;
-    divmod_fast(task, chunks_per_row, &row, &chunk);
+    int64_t rg, chunk;
+    divmod_fast(task, chunks_per_row, &rg, &chunk);
+    const int64_t row0 = rg * ROW_R;
     const int64_t col = (chunk << 9) + lane * 16;
-    const bool active = col < a.cols;
+    const bool col_ok = col < a.cols;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + (row0 * a.ld + col) * ESZ;
+    const int64_t pitch = a.ld * ESZ;
 
-    float v[16];
-    uint32_t amax_bits = 0;
-    if (IN_BF16) {
-      uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
-      if (active) {
-        const uint4* p = reinterpret_cast<const uint4*>(
-            reinterpret_cast<const __nv_bfloat16*>(a.x) + row * a.ld + col);
-        w0 = __ldg(p);
-        w1 = __ldg(p + 1);
-      }
-      const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-      uint32_t acc = 0;
+    // ---- all loads of the task ----
+    uint4 raw[ROW_R][NV];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        acc = absmax_bf16x2(acc, w[j]);
-        v[2 * j] = bf16lo_to_f32(w[j]);
-        v[2 * j + 1] = bf16hi_to_f32(w[j]);
-      }
-      amax_bits = fold_bf16x2(acc);
-    } else {
+    for (int i = 0; i < ROW_R; ++i) {
+      const bool ok = col_ok && row0 + i < a.rows;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (active)
-          f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) +
-                                                    row * a.ld + col) + j);
-        v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
-      }
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const uint32_t b = f2u(v[j]) & 0x7FFFFFFFu;
-        amax_bits = b > amax_bits ? b : amax_bits;
-      }
+      for (int q = 0; q < NV; ++q)
+        raw[i][q] = ok ? __ldg(reinterpret_cast<const uint4*>(src + i * pitch) + q) : make_uint4(0u, 0u, 0u, 0u);
     }
-    if (LPB == 2) {
-      const uint32_t o = __shfl_xor_sync(0xFFFFFFFFu, amax_bits, 1);
-      amax_bits = o > amax_bits ? o : amax_bits;
+    // position of the task in the periodic random table (32-bit: the host refuses larger extents)
+    uint32_t rr0 = 0, pp = 0;
+    if (ROUND == ALTOB200_ROUND_SR_BITS && tiled) {
+      rr0 = (uint32_t)row0 % t_rows;
+      pp = (uint32_t)(col >> 1) % t_pairs;
     }
-    BlockScale s;
-    if (F::MX && (a.mx.clip | a.mx.uos)) {
-      float sum = 0.0f, sumsq = 0.0f;
-      if (a.mx.clip == 2) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          sum = __fadd_rn(sum, v[j]);
-          sumsq = __fadd_rn(sumsq, round_in<IN_BF16>(__fmul_rn(v[j], v[j])));
-        }
-        if (LPB == 2) {
-          sum = __fadd_rn(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, 1));
-          sumsq = __fadd_rn(sumsq, __shfl_xor_sync(0xFFFFFFFFu, sumsq, 1));
-        }
-      }
-      s = make_block_scale_opts<FMT, IN_BF16>(amax_bits, sum, sumsq, F::B, a.mx);
-      if (a.mx.clip == 1) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = round_in<IN_BF16>(__fmul_rn(v[j], 0.75f));
-      }
-    } else {
-      s = make_block_scale<FMT, IN_BF16>(amax_bits, use_outer, outer);
-    }
+    const int64_t kb = (chunk << 9) / F::B + lane / LPB;  // scale column of this lane
+    const bool holder = col_ok && (lane % LPB == 0);
 
-    // random bits (explicit mode): 8 words per plane for this lane's 8 element pairs
-    uint32_t r0[8], r1[8];
-    if (ROUND == ALTOB200_ROUND_SR_BITS) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) r0[j] = r1[j] = 0;
-      if (active) {
-        // full planes, or a tile repeated over the matrix (the 8 pairs of a lane never straddle a
-        // tile: tile_pairs is a multiple of 8)
-        const bool tiled = a.tile_rows != 0;
-        // 32-bit remainders (the host refuses a tiled launch whose extents do not fit 32 bits)
-        const int64_t rr = tiled ? (int64_t)((uint32_t)row % (uint32_t)a.tile_rows) : row;
-        const int64_t pp = tiled ? (int64_t)((uint32_t)(col >> 1) % (uint32_t)a.tile_pairs) : (col >> 1);
-        const int64_t pitch = tiled ? a.tile_pairs : half_cols;
-        const int64_t plane = tiled ? a.tile_rows * a.tile_pairs : a.rows * half_cols;
-        const uint4* p0 = reinterpret_cast<const uint4*>(a.rand_bits + rr * pitch + pp);
-        const uint4* p1 = reinterpret_cast<const uint4*>(a.rand_bits + plane + rr * pitch + pp);
-        const uint4 a0 = __ldg(p0), a1 = __ldg(p0 + 1), b0 = __ldg(p1), b1 = __ldg(p1 + 1);
+    for (int i = 0; i < ROW_R; ++i) {
+      const int64_t row = row0 + i;
+      const bool active = col_ok && row < a.rows;
+      // random words first: their (cache-resident) loads overlap the scale arithmetic below
+      uint32_t r0[8], r1[8];
+      if (ROUND == ALTOB200_ROUND_SR_BITS) {
+        // full planes [2][rows][cols/2], or a [2][tile_rows][tile_pairs] table repeated over the matrix
+        // (the 8 pairs of a lane never straddle a tile: tile_pairs is a multiple of 8)
+        uint32_t rr = rr0 + (uint32_t)i;
+        while (tiled && rr >= t_rows) rr -= t_rows;
+        const int64_t off = tiled ? (int64_t)(rr * t_pairs + pp) : row * half_cols + (col >> 1);
+        const int64_t plane = tiled ? (int64_t)(t_rows * t_pairs) : a.rows * half_cols;
+        uint4 a0 = make_uint4(0u, 0u, 0u, 0u), a1 = a0, b0 = a0, b1 = a0;
+        if (active) {
+          const uint4* p0 = reinterpret_cast<const uint4*>(a.rand_bits + off);
+          const uint4* p1 = reinterpret_cast<const uint4*>(a.rand_bits + plane + off);
+          a0 = __ldg(p0); a1 = __ldg(p0 + 1); b0 = __ldg(p1); b1 = __ldg(p1 + 1);
+        }
         r0[0] = a0.x; r0[1] = a0.y; r0[2] = a0.z; r0[3] = a0.w;
         r0[4] = a1.x; r0[5] = a1.y; r0[6] = a1.z; r0[7] = a1.w;
         r1[0] = b0.x; r1[1] = b0.y; r1[2] = b0.z; r1[3] = b0.w;
         r1[4] = b1.x; r1[5] = b1.y; r1[6] = b1.z; r1[7] = b1.w;
-      }
-    } else if (ROUND == ALTOB200_ROUND_SR_PHILOX) {
-      // one Philox call feeds two element pairs: call index = pair index / 2
-      const uint64_t q0 = a.philox_offset + (uint64_t)((row * half_cols + (col >> 1)) >> 1);
+      } else if (ROUND == ALTOB200_ROUND_SR_PHILOX) {
+        // one Philox call feeds two element pairs: call index = pair index / 2
+        const uint64_t q0 = a.philox_offset + (uint64_t)((row * half_cols + (col >> 1)) >> 1);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t o[4];
-        const uint64_t ctr = q0 + i;
-        philox4x32_10_keys((uint32_t)ctr, (uint32_t)(ctr >> 32), a.pk, o);
-        r0[2 * i] = o[0]; r1[2 * i] = o[1]; r0[2 * i + 1] = o[2]; r1[2 * i + 1] = o[3];
-      }
-    }
-
-    with_uniform_fast(s.fast, [&](auto fast_tag) {
-      constexpr bool FAST = decltype(fast_tag)::value;
-      if (F::FP4) {
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          lo |= fp4_pair<FMT, IN_BF16, ROUND, FAST>(v[2 * j], v[2 * j + 1], s, r0[j], r1[j]) << (8 * j);
-          hi |= fp4_pair<FMT, IN_BF16, ROUND, FAST>(v[8 + 2 * j], v[9 + 2 * j], s, r0[4 + j], r1[4 + j]) << (8 * j);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[4];
+          const uint64_t ctr = q0 + c;
+          philox4x32_10_keys((uint32_t)ctr, (uint32_t)(ctr >> 32), a.pk, o);
+          r0[2 * c] = o[0]; r1[2 * c] = o[1]; r0[2 * c + 1] = o[2]; r1[2 * c + 1] = o[3];
         }
-        if (active)
-          *reinterpret_cast<uint2*>(a.codes + row * half_cols + (col >> 1)) = make_uint2(lo, hi);
       } else {
-        uint32_t o[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float q[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) q[i] = scale_elem<FMT, IN_BF16, FAST>(v[4 * j + i], s);
-          o[j] = fp8x2_rtn_hw<F::E5M2>(q[0], q[1]) | (fp8x2_rtn_hw<F::E5M2>(q[2], q[3]) << 16);
-        }
-        if (active)
-          *reinterpret_cast<uint4*>(a.codes + row * a.cols + col) = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int j = 0; j < 8; ++j) r0[j] = r1[j] = 0;
       }
-    });
 
-    // scales
-    const int64_t kb = (chunk << 9) / F::B + lane / LPB;  // scale column of this lane
-    const bool holder = active && (lane % LPB == 0);
-    if (a.scale_plain != nullptr && holder) {
-      if (F::MX)
-        reinterpret_cast<uint8_t*>(a.scale_plain)[row * (a.cols / F::B) + kb] = (uint8_t)s.byte;
-      else
-        reinterpret_cast<float*>(a.scale_plain)[row * (a.cols / F::B) + kb] = s.plain;
-    }
-    if (a.scale_packed != nullptr) {
-      uint32_t word = holder ? s.byte : 0u;
-      word |= __shfl_down_sync(0xFFFFFFFFu, word, LPB) << 8;
-      word |= __shfl_down_sync(0xFFFFFFFFu, word, 2 * LPB) << 16;
-      if ((lane % (4 * LPB) == 0) && (kb < a.ncol_tiles * 4))
-        *reinterpret_cast<uint32_t*>(a.scale_packed + packed_scale_offset(row, kb, a.ncol_tiles)) = word;
+      // ---- unpack, block maximum ----
+      float v[16];
+      uint32_t amax_bits = 0;
+      if (IN_BF16) {
+        const uint32_t w[8] = {raw[i][0].x, raw[i][0].y, raw[i][0].z, raw[i][0].w,
+                               raw[i][1].x, raw[i][1].y, raw[i][1].z, raw[i][1].w};
+        uint32_t acc = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc = absmax_bf16x2(acc, w[j]);
+          v[2 * j] = bf16lo_to_f32(w[j]);
+          v[2 * j + 1] = bf16hi_to_f32(w[j]);
+        }
+        amax_bits = fold_bf16x2(acc);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          v[4 * q] = u2f(raw[i][q % NV].x); v[4 * q + 1] = u2f(raw[i][q % NV].y);
+          v[4 * q + 2] = u2f(raw[i][q % NV].z); v[4 * q + 3] = u2f(raw[i][q % NV].w);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t b = f2u(v[j]) & 0x7FFFFFFFu;
+          amax_bits = b > amax_bits ? b : amax_bits;
+        }
+      }
+      if (LPB == 2) {
+        const uint32_t o = __shfl_xor_sync(0xFFFFFFFFu, amax_bits, 1);
+        amax_bits = o > amax_bits ? o : amax_bits;
+      }
+      BlockScale s;
+      if (F::MX && (a.mx.clip | a.mx.uos)) {
+        float sum = 0.0f, sumsq = 0.0f;
+        if (a.mx.clip == 2) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            sum = __fadd_rn(sum, v[j]);
+            sumsq = __fadd_rn(sumsq, round_in<IN_BF16>(__fmul_rn(v[j], v[j])));
+          }
+          if (LPB == 2) {
+            sum = __fadd_rn(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, 1));
+            sumsq = __fadd_rn(sumsq, __shfl_xor_sync(0xFFFFFFFFu, sumsq, 1));
+          }
+        }
+        s = make_block_scale_opts<FMT, IN_BF16>(amax_bits, sum, sumsq, F::B, a.mx);
+        if (a.mx.clip == 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = round_in<IN_BF16>(__fmul_rn(v[j], 0.75f));
+        }
+      } else {
+        s = make_block_scale<FMT, IN_BF16>(amax_bits, os);
+      }
+
+      // ---- encode and store ----
+      with_uniform_fast(s.fast, [&](auto fast_tag) {
+        constexpr bool FAST = decltype(fast_tag)::value;
+        if (F::FP4) {
+          uint32_t lo = 0, hi = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            lo = merge_shifted(fp4_pair<FMT, IN_BF16, ROUND, FAST>(v[2 * j], v[2 * j + 1], s, r0[j], r1[j]), 8 * j, lo);
+            hi = merge_shifted(fp4_pair<FMT, IN_BF16, ROUND, FAST>(v[8 + 2 * j], v[9 + 2 * j], s, r0[4 + j], r1[4 + j]),
+                               8 * j, hi);
+          }
+          if (active) *reinterpret_cast<uint2*>(a.codes + row * half_cols + (col >> 1)) = make_uint2(lo, hi);
+        } else {
+          uint32_t o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float q[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) q[c] = scale_elem<FMT, IN_BF16, FAST>(v[4 * j + c], s);
+            o[j] = fp8x2_rtn_hw<F::E5M2>(q[0], q[1]) | (fp8x2_rtn_hw<F::E5M2>(q[2], q[3]) << 16);
+          }
+          if (active) *reinterpret_cast<uint4*>(a.codes + row * a.cols + col) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      });
+
+      // ---- scales ----
+      if (a.scale_plain != nullptr && holder && row < a.rows) {
+        if (F::MX) reinterpret_cast<uint8_t*>(a.scale_plain)[row * nkb + kb] = (uint8_t)s.byte;
+        else reinterpret_cast<float*>(a.scale_plain)[row * nkb + kb] = s.plain;
+      }
+      if (a.scale_packed != nullptr) {
+        uint32_t word = (holder && row < a.rows) ? s.byte : 0u;
+        word |= __shfl_down_sync(0xFFFFFFFFu, word, LPB) << 8;
+        word |= __shfl_down_sync(0xFFFFFFFFu, word, 2 * LPB) << 16;
+        if ((lane % (4 * LPB) == 0) && (kb < a.ncol_tiles * 4) && row < a.rows)
+          *reinterpret_cast<uint32_t*>(a.scale_packed + packed_scale_offset(row, kb, a.ncol_tiles)) = word;
+      }
     }
   }
 }
@@ -439,39 +498,53 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
   const int64_t n0 = (int64_t)blockIdx.x * COL_TN;
   const int64_t c = n0 + 2 * lane;  // first of this lane's two columns
   const bool col_ok = c < a.cols;   // cols is even, so c+1 is valid too
-  const bool use_outer = (!F::MX) && a.outer != nullptr;
-  const float outer = use_outer ? __ldg(a.outer) : 1.0f;
+  const OuterScale os = make_outer_scale((!F::MX) && a.outer != nullptr, a.outer);
   const int64_t half_rows = a.rows >> 1;
   // rows of the periodic random table for this lane's two columns (rows of the axis-last view)
   const uint32_t tile_row0 = a.tile_rows != 0 ? (uint32_t)((uint64_t)c % (uint64_t)a.tile_rows) : 0u;
   const uint32_t tile_row1 = a.tile_rows != 0 ? (uint32_t)((uint64_t)(c + 1) % (uint64_t)a.tile_rows) : 0u;
 
-#pragma unroll 1
+  // bf16: the words of every iteration are requested before the first is used (slot k <- row pinv[k]
+  // when the transform is on; the identity otherwise), so the second block's loads fly under the
+  // first block's arithmetic
+  constexpr int ESZ = IN_BF16 ? 2 : 4;
+  const int64_t half_blk = 16 * a.ld * ESZ;  // second 16-row group of a 32-row block
+  uint32_t pre[IN_BF16 ? ITERS : 1][IN_BF16 ? B : 1];
+  if (IN_BF16) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int64_t mb = m0 + (int64_t)(warp * ITERS + it) * B;
+      const bool ok = col_ok && mb < a.rows;
+      const uint8_t* base = reinterpret_cast<const uint8_t*>(a.x) + (mb * a.ld + c) * ESZ;
+#pragma unroll
+      for (int k = 0; k < B; ++k)
+        pre[it % (IN_BF16 ? ITERS : 1)][k % (IN_BF16 ? B : 1)] =
+            ok ? __ldg(reinterpret_cast<const uint32_t*>(base + a.rht.row_off[k & 15] + (k >= 16 ? half_blk : 0))) : 0u;
+    }
+  }
+
+#pragma unroll
   for (int it = 0; it < ITERS; ++it) {
     const int blk = warp * ITERS + it;
     const int64_t mb = m0 + (int64_t)blk * B;
     const bool ok = col_ok && mb < a.rows;  // rows % B == 0
     float v0[B], v1[B];
-    // ---- load (slot k <- row pinv[k] when the transform is on; the identity otherwise) ----
-    const uint8_t* base = reinterpret_cast<const uint8_t*>(a.x) + (mb * a.ld + c) * (IN_BF16 ? 2 : 4);
-    const int64_t half_blk = 16 * a.ld * (IN_BF16 ? 2 : 4);  // second 16-row group of a 32-row block
+    if (IN_BF16) {
 #pragma unroll
-    for (int k = 0; k < B; ++k) {
-      const uint8_t* src = base + a.rht.row_off[k & 15] + (k >= 16 ? half_blk : 0);
-      float f0 = 0.f, f1 = 0.f;
-      if (ok) {
-        if (IN_BF16) {
-          const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(src));
-          f0 = bf16lo_to_f32(w);
-          f1 = bf16hi_to_f32(w);
-        } else {
-          const float2 f = __ldg(reinterpret_cast<const float2*>(src));
-          f0 = f.x;
-          f1 = f.y;
-        }
+      for (int k = 0; k < B; ++k) {
+        const uint32_t w = pre[it % (IN_BF16 ? ITERS : 1)][k % (IN_BF16 ? B : 1)];
+        v0[k] = bf16lo_to_f32(w);
+        v1[k] = bf16hi_to_f32(w);
       }
-      v0[k] = f0;
-      v1[k] = f1;
+    } else {
+      const uint8_t* base = reinterpret_cast<const uint8_t*>(a.x) + (mb * a.ld + c) * ESZ;
+#pragma unroll
+      for (int k = 0; k < B; ++k) {
+        float2 f = make_float2(0.f, 0.f);
+        if (ok) f = __ldg(reinterpret_cast<const float2*>(base + a.rht.row_off[k & 15] + (k >= 16 ? half_blk : 0)));
+        v0[k] = f.x;
+        v1[k] = f.y;
+      }
     }
     // ---- transform: y = (H z) / sqrt(16), rounded to the input dtype ----
     if (RHT) {
@@ -540,8 +613,8 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
         }
       }
     } else {
-      s0 = make_block_scale<FMT, IN_BF16>(am0, use_outer, outer);
-      s1 = make_block_scale<FMT, IN_BF16>(am1, use_outer, outer);
+      s0 = make_block_scale<FMT, IN_BF16>(am0, os);
+      s1 = make_block_scale<FMT, IN_BF16>(am1, os);
     }
 
     // ---- quantise in slot order ----
@@ -802,8 +875,7 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
   const int lc = lane % LC, lr = lane / LC;
   const int64_t row0 = tr * TR + lr * 16, col0 = tc * TC + lc * 8;
   const bool ok = row0 < a.rows && col0 < a.cols;  // rows % B == 0 and cols % B == 0
-  const bool use_outer = (!F::MX) && a.outer != nullptr;
-  const float outer = use_outer ? __ldg(a.outer) : 1.0f;
+  const OuterScale os = make_outer_scale((!F::MX) && a.outer != nullptr, a.outer);
   const uint8_t* src = reinterpret_cast<const uint8_t*>(a.w) + (row0 * a.ld + col0) * ESZ;
   const int64_t pitch = a.ld * ESZ;
 
@@ -843,7 +915,7 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
   }
   const BlockScale s = (F::MX && (a.mx.clip | a.mx.uos))
                            ? make_block_scale_opts<FMT, IN_BF16>(amax_bits, 0.0f, 0.0f, B * B, a.mx)
-                           : make_block_scale<FMT, IN_BF16>(amax_bits, use_outer, outer);
+                           : make_block_scale<FMT, IN_BF16>(amax_bits, os);
   const bool clip = F::MX && a.mx.clip == 1;
 
   // ---- encode row by row, K packing ----
@@ -1404,7 +1476,7 @@ static void fill_rht_row_offsets(RhtParams* r, int64_t ld, int esz) {
 
 template <int FMT, bool IN_BF16>
 static int launch_rowwise(const RowwiseArgs& a, int rounding, cudaStream_t st) {
-  const int64_t tasks = a.rows * ((a.cols + 511) >> 9);
+  const int64_t tasks = ceil_div(a.rows, ROW_R) * ((a.cols + 511) >> 9);
   int64_t blocks = ceil_div(tasks, 8);
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
