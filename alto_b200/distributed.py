@@ -1,12 +1,14 @@
 """Multi-GPU forms of the low-precision linear path (one process per GPU, ``torch.distributed``).
 
-Three ways the path shards, each with exactly the exchange it needs and nothing more:
+Four ways the path shards, each with exactly the exchange it needs and nothing more:
 
 * data parallel replicas        -- every rank runs the full linear on its own batch; the only
   exchange is the all-reduce of the weight gradients (``allreduce_gradients``).
 * column-sharded linear         -- W [N, K] split along N; forward and wgrad are local, dgrad is a
   sum over ranks (``column_sharded_linear``: all-reduce of dX in backward).  N / world must be a
   multiple of 32 so that 2-D weight blocks never straddle ranks.
+* fully sharded weight          -- every rank owns rows of W, quantises them and all-gathers the 4.5-bit
+  payload instead of bf16 (``gathered_weight_linear``); dW is reduce-scattered.
 * expert parallel MoE           -- experts split across ranks, tokens exchanged by all-to-all with
   variable splits each way (``ExpertParallelDispatcher``), local rows sorted by expert and padded
   to runs of 128 for the grouped GEMMs.
@@ -33,8 +35,9 @@ import torch.distributed as dist
 
 from . import _lib as L
 
-__all__ = ["allreduce_gradients", "shard_rows", "column_sharded_linear", "ExpertParallelDispatcher",
-           "permute_pad_plan", "ALIGN_SIZE_M"]
+__all__ = ["allreduce_gradients", "shard_rows", "column_sharded_linear", "gathered_weight_linear",
+           "gather_packed_rows", "gather_columns", "interleave_gathered_columns", "outer_scale_from_amax_bits",
+           "ExpertParallelDispatcher", "permute_pad_plan", "ALIGN_SIZE_M"]
 
 ALIGN_SIZE_M = 128
 
@@ -124,6 +127,144 @@ def column_sharded_linear(x: torch.Tensor, w_shard: torch.Tensor, linear_fn: Cal
     all-reduce of the bf16 partials.  ``linear_fn(a, b)`` is one of the boundary functions with its
     recipe bound, e.g. ``lambda a, b: _to_mxfp8_then_scaled_mm(a, b, "e4m3", False, False, True)``."""
     return linear_fn(_CopyToShards.apply(x, group), w_shard)
+
+
+# ------------------------------------------------------------------------------------------
+# fully sharded weights: all-gather of the QUANTISED weight
+# ------------------------------------------------------------------------------------------
+def gather_packed_rows(local: torch.Tensor, group=None) -> torch.Tensor:
+    """Concatenation over ranks of a per-rank buffer whose rank order is its memory order: codes of a
+    row shard [n, K/2] -> [N, K/2], packed scales of a row shard with n % 128 == 0 (whole 128-row
+    tiles, tiles row-block major)."""
+    world = _world(group)
+    if world == 1:
+        return local
+    out = torch.empty(world * local.numel(), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local.contiguous().view(-1), group=group)
+    return out.view(world * local.shape[0], *local.shape[1:]) if local.dim() > 1 else out
+
+
+def interleave_gathered_columns(gathered: torch.Tensor, world: int, rows: int, inner: int) -> torch.Tensor:
+    """``gathered`` = [world, rows, inner] (rank-major all-gather of per-rank [rows, inner] buffers whose
+    columns are that rank's slice of a wider row) -> [rows, world * inner], rank slices side by side.
+
+    Used for the weight packed along N ([K, n/2] codes per rank -> [K, N/2]) and for its packed scales
+    viewed as [K/128 tile rows, tiles_per_rank * 512 bytes] (each rank owns whole tiles when its
+    n / block is a multiple of 4)."""
+    return gathered.view(world, rows, inner).permute(1, 0, 2).reshape(rows, world * inner)
+
+
+def gather_columns(local: torch.Tensor, rows: int, group=None) -> torch.Tensor:
+    world = _world(group)
+    flat = local.contiguous().view(rows, -1)
+    if world == 1:
+        return flat
+    out = torch.empty(world * flat.numel(), dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(out, flat.view(-1), group=group)
+    return interleave_gathered_columns(out, world, rows, flat.shape[1])
+
+
+def outer_scale_from_amax_bits(bits: torch.Tensor) -> torch.Tensor:
+    """NVFP4 tensorwise outer scale from the fp32 bit pattern of a tensor amax, as
+    ``compute_dynamic_outer_scale`` defines it (alto/kernels/fp4/nvfp4/nvfp_quantization.py:460-487):
+    nan_to_num(amax) / (448 * 6), at least 1e-30."""
+    amax = torch.nan_to_num(bits.view(torch.float32))
+    return (amax / (448.0 * 6.0)).clamp_min(1e-30)
+
+
+class _GatheredWeightLinear(torch.autograd.Function):
+    """y = x W^T where every rank holds the rows [r n, (r + 1) n) of W [N, K] (the layout of a fully
+    sharded data-parallel weight).  The shard is quantised locally in 2-D blocks and the 4.5-bit
+    payload (codes + scale bytes, both packings) is all-gathered instead of the bf16 weight: 3.5x
+    fewer bytes on NVLink, and numerically nothing changes, because 2-D blocks never straddle a
+    shard and the NVFP4 tensorwise scale is taken from the all-reduced (MAX) amax.
+
+    The reference gathers ``param_dtype`` weights and quantises the full tensor on every rank
+    (alto/kernels/dispatch/tensor.py:159-211); results here are bit-identical to that.
+
+    backward: dX with the gathered weight packed along N; dW [N, K] is computed in full from the
+    local batch and reduce-scattered (summed) so that every rank receives the gradient of its rows."""
+
+    @staticmethod
+    def forward(ctx, x, w_shard, group, fmt, use_outer_scale, use_sr_grad, hadamard_transform):
+        from . import _linear as E
+        world = _world(group)
+        x2 = E.as_2d_rows(x.detach())
+        w2 = E.as_2d_rows(w_shard.detach())
+        if w2.dtype != x2.dtype:
+            w2 = w2.to(x2.dtype)
+        M, K = x2.shape
+        n = w2.shape[0]
+        N = n * world
+        b = L.block_of(fmt)
+        E.check_dims("gathered-weight linear", M, K, N)
+        torch._check(n % 128 == 0 and (n // b) % 4 == 0, lambda: (
+            f"a weight shard of {n} rows cannot be gathered in quantised form: rows per rank must be a multiple "
+            f"of 128 (whole tiles of packed scales) and of {4 * b}"))
+        rht, dense = E.split_transform(hadamard_transform, False)
+        # tensorwise scale of the WHOLE weight: local amax, MAX over ranks
+        ow = None
+        if use_outer_scale:
+            bits = torch.empty(2, dtype=torch.int32, device=w2.device)
+            L.amax(w2, bits, None, E.amax_scratch(w2.device), None)
+            if world > 1:
+                dist.all_reduce(bits, op=dist.ReduceOp.MAX, group=group)  # non-negative floats order like ints
+            ow = outer_scale_from_amax_bits(bits[0:1])
+        wk_l, wt_l = E.quant_2d(w2, fmt, ow, True)
+        w_k = E.Operand(gather_packed_rows(wk_l.codes, group), gather_packed_rows(wk_l.scales, group), ow, N, K, fmt)
+        w_t = E.Operand(gather_columns(wt_l.codes, K, group),
+                        gather_columns(wt_l.scales, (K + 127) // 128, group).reshape(-1), ow, K, N, fmt)
+        ox = E.outer_scales(x2, use_outer_scale, rht)
+        x_k = E.quant_rows(x2, fmt, None if ox is None else ox[0:1], E.RTN)
+        x_m = E.cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, E.RTN)
+        y = E.gemm(x_k, w_k, x.dtype)
+        extra_x = [x_m.outer] if x_m.outer is not None else []
+        extra_w = [w_t.outer] if w_t.outer is not None else []
+        ctx.save_for_backward(x_m.codes, x_m.scales, *extra_x, w_t.codes, w_t.scales, *extra_w)
+        ctx.dims, ctx.fmt, ctx.group, ctx.n_local = (M, K, N), fmt, group, n
+        ctx.use_outer_scale, ctx.use_sr_grad, ctx.rht, ctx.dense = use_outer_scale, use_sr_grad, rht, dense
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        from . import _linear as E
+        M, K, N = ctx.dims
+        saved = ctx.saved_tensors
+        if ctx.use_outer_scale:
+            xc, xs, xo, wc, ws, wo = saved
+        else:
+            (xc, xs, wc, ws), xo, wo = saved, None, None
+        x_m = E.Operand(xc, xs, xo, K, M, ctx.fmt)
+        w_t = E.Operand(wc, ws, wo, K, N, ctx.fmt)
+        g2 = E.as_2d_rows(grad_output)
+        g_n, g_m = E.backward_operands(g2, ctx.fmt, use_2dblock_x=False, use_sr_grad=ctx.use_sr_grad,
+                                       use_outer_scale=ctx.use_outer_scale, rht=ctx.rht, dense=ctx.dense)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = E.gemm(g_n, w_t, grad_output.dtype).view(*grad_output.shape[:-1], K)
+        if ctx.needs_input_grad[1]:
+            dw_full = E.gemm(g_m, x_m, grad_output.dtype)
+            if _world(ctx.group) > 1:
+                dw = torch.empty(ctx.n_local, K, dtype=dw_full.dtype, device=dw_full.device)
+                dist.reduce_scatter_tensor(dw, dw_full, op=dist.ReduceOp.SUM, group=ctx.group)
+            else:
+                dw = dw_full
+        return dx, dw, None, None, None, None, None
+
+
+def gathered_weight_linear(x: torch.Tensor, w_shard: torch.Tensor, precision: str = "nvfp4", group=None, *,
+                           use_outer_scale: bool = False, use_sr_grad: bool = False,
+                           hadamard_transform=None) -> torch.Tensor:
+    """Linear layer over a row-sharded weight whose quantised form is all-gathered (see
+    ``_GatheredWeightLinear``).  ``precision``: "nvfp4", "mxfp4", "mxfp8_e4m3" or "mxfp8_e5m2"; weights are
+    quantised in 2-D blocks, activations and gradients in 1-D blocks."""
+    fmts = {"nvfp4": L.FMT_NVFP4, "mxfp4": L.FMT_MXFP4, "mxfp8_e4m3": L.FMT_MXFP8_E4M3, "mxfp8_e5m2": L.FMT_MXFP8_E5M2}
+    if precision not in fmts:
+        raise ValueError(f"unsupported precision {precision!r}")
+    if use_outer_scale and precision != "nvfp4":
+        raise ValueError("the tensorwise outer scale belongs to NVFP4")
+    return _GatheredWeightLinear.apply(x, w_shard, group, fmts[precision], use_outer_scale, use_sr_grad,
+                                       hadamard_transform)
 
 
 # ------------------------------------------------------------------------------------------

@@ -151,3 +151,61 @@ def _allreduce_worker(rank, world):
 
 def test_bucketed_gradient_allreduce_two_ranks():
     _spawn(_allreduce_worker)
+
+
+# ---------------------------------------------------------------------------------------------
+# all-gather of the quantised weight: assembly of the gathered buffers
+# ---------------------------------------------------------------------------------------------
+def _weight_payload(S, codes, rank, world, b):
+    """What a rank holds after quantising its row shard of W [N, K]: codes along K, packed scales of
+    both packings, codes along N.  S: plain 2-D scales [N/b, K/b]; codes: [N, K/2] stand-in bytes."""
+    from alto_b200._linear import pack_plain_scales
+    N, n = codes.shape[0], codes.shape[0] // world
+    Ssh = S[rank * n // b:(rank + 1) * n // b]
+    ck = codes[rank * n:(rank + 1) * n]
+    ct = codes.t()[:, rank * n:(rank + 1) * n].contiguous()          # stand-in for the [K, n/2] packing
+    sk = pack_plain_scales(Ssh, n, True, b)
+    st = pack_plain_scales(Ssh.t().contiguous(), S.shape[1] * b, True, b)
+    return ck, sk, ct, st
+
+
+@pytest.mark.parametrize("b,N,K,world", [(16, 512, 192, 2), (32, 1024, 256, 4), (16, 256, 64, 2)])
+def test_gathered_weight_buffers_assemble_to_the_full_tensor(b, N, K, world):
+    from alto_b200._linear import pack_plain_scales
+    g = torch.Generator().manual_seed(0)
+    S = torch.randint(1, 255, (N // b, K // b), generator=g, dtype=torch.uint8)
+    codes = torch.randint(0, 256, (N, K // 2), generator=g, dtype=torch.uint8)
+    parts = [_weight_payload(S, codes, r, world, b) for r in range(world)]
+    # rows: plain concatenation in rank order
+    assert torch.equal(torch.cat([p[0] for p in parts]), codes)
+    assert torch.equal(torch.cat([p[1] for p in parts]), pack_plain_scales(S, N, True, b))
+    # columns: rank slices side by side
+    ct = D.interleave_gathered_columns(torch.stack([p[2] for p in parts]), world, K // 2, parts[0][2].shape[1])
+    assert torch.equal(ct, codes.t().contiguous())
+    kt = (K + 127) // 128
+    st = D.interleave_gathered_columns(torch.stack([p[3].view(kt, -1) for p in parts]), world, kt,
+                                       parts[0][3].numel() // kt).reshape(-1)
+    assert torch.equal(st, pack_plain_scales(S.t().contiguous(), K, True, b))
+
+
+def test_outer_scale_from_amax_bits():
+    vals = torch.tensor([0.0, 1.0, 5000.0, float("inf"), float("nan"), 1e-38], dtype=torch.float32)
+    got = D.outer_scale_from_amax_bits(vals.view(torch.int32))
+    exp = (torch.nan_to_num(vals) / (448.0 * 6.0)).clamp_min(1e-30)
+    assert torch.equal(got, exp) and got[0].item() == pytest.approx(1e-30) and torch.isfinite(got).all()
+
+
+def _gather_worker(rank, world):
+    full = torch.arange(4 * world * 6, dtype=torch.uint8).view(4 * world, 6)
+    rows = D.gather_packed_rows(full[4 * rank:4 * rank + 4].clone())
+    assert torch.equal(rows, full)
+    wide = torch.arange(3 * 5 * world, dtype=torch.int32).view(3, 5 * world)
+    cols = D.gather_columns(wide[:, 5 * rank:5 * rank + 5].clone(), 3)
+    assert torch.equal(cols, wide)
+    bits = torch.tensor([rank + 1, 7 - rank], dtype=torch.int32)
+    dist.all_reduce(bits, op=dist.ReduceOp.MAX)
+    assert bits.tolist() == [world, 7]
+
+
+def test_quantised_weight_gathers_two_ranks():
+    _spawn(_gather_worker)

@@ -145,6 +145,25 @@ def _two_rank_worker(rank, world, port):
         out1.float().sum().backward()
         assert torch.equal(out, out1)
         assert torch.equal(xt.grad, x1.grad)
+        # ---- fully sharded weight: the quantised shard is all-gathered, dW reduce-scattered ----
+        from alto_b200 import nvfp4 as NV
+        NV.HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)
+        had = NV.HadamardFactory.create_transform(device=dev)
+        g = torch.Generator().manual_seed(9)
+        xf = torch.randn(256, 512, generator=g).bfloat16().to(dev)
+        Wf = (torch.randn(512, 512, generator=g) * 0.05).bfloat16().to(dev)
+        dyf = (torch.randn(256, 512, generator=g) * 1e-2).bfloat16().to(dev)
+        xs, ws = xf.clone().requires_grad_(True), D.shard_rows(Wf, multiple=128).clone().requires_grad_(True)
+        ys = D.gathered_weight_linear(xs, ws, "nvfp4", use_outer_scale=True, hadamard_transform=had)
+        ys.backward(dyf)
+        x1, w1 = xf.clone().requires_grad_(True), Wf.clone().requires_grad_(True)
+        NV.HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)  # same matrix
+        y1 = NV._to_nvfp4_then_scaled_mm(x1, w1, False, True, False, use_outer_scale=True, use_hadamard=True)
+        y1.backward(dyf)
+        nw = 512 // world
+        assert torch.equal(ys, y1) and torch.equal(xs.grad, x1.grad)
+        # both ranks ran the same batch: the reduce-scattered gradient is world x the single-GPU rows
+        assert torch.equal(ws.grad, (w1.grad[rank * nw:(rank + 1) * nw].float() * world).bfloat16())
         # ---- bucketed gradient all-reduce ----
         p = torch.nn.Parameter(torch.zeros(1000, device=dev))
         p.grad = torch.full_like(p, float(rank))
@@ -158,3 +177,31 @@ def _two_rank_worker(rank, world, port):
 def test_two_ranks_nccl_column_sharded_and_expert_parallel():
     import torch.multiprocessing as mp
     mp.spawn(_two_rank_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+@pytest.mark.parametrize("precision,kw", [("nvfp4", dict(use_outer_scale=True)), ("nvfp4", dict()), ("mxfp4", dict()),
+                                          ("mxfp8_e4m3", dict())])
+def test_gathered_weight_linear_single_rank_equals_the_plain_linear(precision, kw):
+    """World size 1: the gathers are identities, so the function must reproduce the boundary functions bit
+    for bit (same quantizers, same GEMMs); the 2-rank NCCL test checks the exchanges."""
+    from alto_b200 import distributed as D
+    from alto_b200 import mxfp4 as MX, mxfp8 as M8, nvfp4 as NV
+    d = torch.device("cuda")
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(128, 256, generator=g).bfloat16().to(d)
+    W = (torch.randn(384, 256, generator=g) * 0.05).bfloat16().to(d)
+    dy = (torch.randn(128, 384, generator=g) * 1e-2).bfloat16().to(d)
+    xa, wa = x.clone().requires_grad_(True), W.clone().requires_grad_(True)
+    ya = D.gathered_weight_linear(xa, wa, precision, **kw)
+    ya.backward(dy)
+    xb, wb = x.clone().requires_grad_(True), W.clone().requires_grad_(True)
+    if precision == "nvfp4":
+        yb = NV._to_nvfp4_then_scaled_mm(xb, wb, False, True, False, use_outer_scale=bool(kw))
+    elif precision == "mxfp4":
+        yb = MX._to_mxfp4_then_scaled_mm(xb, wb, False, True, False, False, "none", False)
+    else:
+        yb = M8._to_mxfp8_then_scaled_mm(xb, wb, "e4m3", False, False, True)
+    yb.backward(dy)
+    assert torch.equal(ya, yb) and torch.equal(xa.grad, xb.grad) and torch.equal(wa.grad, wb.grad)
+    with pytest.raises(RuntimeError, match="multiple"):
+        D.gathered_weight_linear(x, W[:96], precision, **kw)
