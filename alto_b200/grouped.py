@@ -26,6 +26,7 @@ import torch
 
 from . import _lib as L
 from . import _linear as E
+from . import dge
 from .hadamard import HadamardFactory, HadamardTransform
 from .nvfp4 import _check_scale_format, unwrap_weight_wrapper
 
@@ -57,7 +58,7 @@ def _stack(ops):
     return E.Operand(codes, scales, first.outer, first.rows * len(ops), first.k, first.fmt)
 
 
-def _quant_weight_stack(w3: torch.Tensor, fmt: int, use_2dblock_w: bool, use_outer_scale: bool):
+def _quant_weight_stack(w3: torch.Tensor, fmt: int, use_2dblock_w: bool, use_outer_scale: bool, use_uos: bool = False):
     """[E, N, K] -> (W along K stacked [E*N, K], W along N stacked [E*K, N]), one outer scale for all."""
     n_exp, N, K = w3.shape
     ow = E.outer_scales(w3.reshape(n_exp * N, K), use_outer_scale, None)
@@ -66,10 +67,10 @@ def _quant_weight_stack(w3: torch.Tensor, fmt: int, use_2dblock_w: bool, use_out
     for e in range(n_exp):
         we = w3[e]
         if use_2dblock_w:
-            k_op, t_op = E.quant_2d(we, fmt, outer, True)
+            k_op, t_op = E.quant_2d(we, fmt, outer, True, use_uos)
         else:
-            k_op = E.quant_rows(we, fmt, outer, E.RTN)
-            t_op = E.quant_cols(we, fmt, outer, None, E.RTN)
+            k_op = E.quant_rows(we, fmt, outer, E.RTN, use_uos)
+            t_op = E.quant_cols(we, fmt, outer, None, E.RTN, use_uos)
         ks.append(k_op)
         ts.append(t_op)
     return _stack(ks), _stack(ts)
@@ -87,7 +88,7 @@ class GroupedLinearFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, inputs, weights, offs, fmt, fmt_grad, use_2dblock_x, use_2dblock_w, use_sr_grad,
-                use_outer_scale, hadamard_transform):
+                use_outer_scale, hadamard_transform, use_uos=False, clip_mode="none", use_dge=False):
         if not inputs.is_cuda:
             raise RuntimeError("grouped GEMM runs on CUDA tensors only (no CPU fallback)")
         weights = unwrap_weight_wrapper(weights)
@@ -108,9 +109,9 @@ class GroupedLinearFunction(torch.autograd.Function):
         rht, dense = E.split_transform(hadamard_transform, False)
 
         ox = E.outer_scales(x2, use_outer_scale, rht)
-        x_k = E.quant_rows(x2, fmt, None if ox is None else ox[0:1], E.RTN)
-        x_m = E.cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, E.RTN)
-        w_k, w_t = _quant_weight_stack(w3, fmt, use_2dblock_w, use_outer_scale)
+        x_k = E.quant_rows(x2, fmt, None if ox is None else ox[0:1], E.RTN, use_uos)
+        x_m = E.cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, E.RTN, use_uos, clip_mode)
+        w_k, w_t = _quant_weight_stack(w3, fmt, use_2dblock_w, use_outer_scale, use_uos)
         y = _grouped_gemm(x_k, w_k, N, n_exp, group_expert, inputs.dtype)
 
         extra_x = [x_m.outer] if x_m.outer is not None else []
@@ -119,6 +120,7 @@ class GroupedLinearFunction(torch.autograd.Function):
         ctx.dims = (M, K, N, n_exp)
         ctx.fmt, ctx.fmt_grad = fmt, fmt_grad
         ctx.use_sr_grad, ctx.use_outer_scale, ctx.rht, ctx.dense_transform = use_sr_grad, use_outer_scale, rht, dense
+        ctx.use_uos, ctx.clip_mode, ctx.use_dge = use_uos, clip_mode, use_dge
         return y
 
     @staticmethod
@@ -134,9 +136,9 @@ class GroupedLinearFunction(torch.autograd.Function):
         g2 = E.as_2d_rows(grad_output)
         og = E.outer_scales(g2, ctx.use_outer_scale, ctx.rht)
         g_n = E.quant_rows(g2, ctx.fmt_grad, None if og is None else og[0:1],
-                           E.sr_args(ctx.use_sr_grad, "dy_n", M, N, g2.device))
+                           E.sr_args(ctx.use_sr_grad, "dy_n", M, N, g2.device), ctx.use_uos)
         g_m = E.cols_operand(g2, ctx.fmt_grad, ctx.use_outer_scale, og, ctx.rht, ctx.dense_transform,
-                             E.sr_args(ctx.use_sr_grad, "dy_m", N, M, g2.device))
+                             E.sr_args(ctx.use_sr_grad, "dy_m", N, M, g2.device), ctx.use_uos, ctx.clip_mode)
         grad_inputs = grad_weights = None
         if ctx.needs_input_grad[0]:
             grad_inputs = _grouped_gemm(g_n, w_t, K, n_exp, group_expert, grad_output.dtype)
@@ -144,7 +146,16 @@ class GroupedLinearFunction(torch.autograd.Function):
             grad_weights = torch.empty(n_exp, N, K, dtype=grad_output.dtype, device=g2.device)
             L.grouped_gemm_wgrad_blockscaled(g_m.fmt, x_m.fmt, N, K, M, n_exp, g_m.codes, g_m.scales, x_m.codes,
                                              x_m.scales, offs32, grad_weights, g_m.outer, x_m.outer)
-        return grad_inputs, grad_weights, None, None, None, None, None, None, None, None
+            if ctx.clip_mode == "static":
+                # both wgrad operands were scaled by 3/4 (mxfp_grouped_gemm/cg_backward.py:893-894)
+                grad_weights *= (16.0 / 9.0)
+            if ctx.use_dge:
+                # factor from the E2M1 code of every weight element (cg_backward.py:912-929); the codes
+                # saved for dgrad are the experts' [K, N/2] packings stacked
+                wt_codes = w_t.codes.view(n_exp, K, -1)
+                for e in range(n_exp):
+                    dge.apply_to_weight_grad(grad_weights[e], wt_codes[e])
+        return grad_inputs, grad_weights, None, None, None, None, None, None, None, None, None, None, None
 
 
 def _hadamard(use_hadamard: bool, use_2dblock_x: bool, device) -> Optional[HadamardTransform]:
@@ -155,28 +166,87 @@ def _hadamard(use_hadamard: bool, use_2dblock_x: bool, device) -> Optional[Hadam
         return HadamardFactory.create_transform(device=device)
 
 
+class GroupedMacroLinearFunction(torch.autograd.Function):
+    """MXFP4 grouped linear with two-level ("blockwise") scaling.  The macro factors are not powers of
+    two, so they cannot ride on the E8M0 scales of the block-scaled MMA; the reference refuses the
+    recipe on its FP4 matrix cores (mxfp_grouped_gemm/cg_backward.py:655) and multiplies the
+    de-quantised, de-scaled operands expert by expert in the input dtype (cg_backward.py:666-690,
+    895-908).  Same here: every scale -> quantise -> de-quantise -> descale chain runs in this
+    library's kernels on the whole buffer, the per-expert matmuls are plain bf16 GEMMs.  ``weights``
+    is canonical [E, N, K].  One host synchronisation per call (the expert boundaries)."""
+
+    @staticmethod
+    def forward(ctx, inputs, weights, offs, use_2dblock_w, use_sr_grad, hadamard_transform):
+        from .mxfp4 import _macro_qdq
+        if not inputs.is_cuda:
+            raise RuntimeError("grouped GEMM runs on CUDA tensors only (no CPU fallback)")
+        weights = unwrap_weight_wrapper(weights)
+        if weights.dtype != inputs.dtype:
+            weights = weights.to(dtype=inputs.dtype)
+        M, K = inputs.shape
+        n_exp, N, _ = weights.shape
+        E.check_dims("grouped GEMM", M, K, N)
+        x2 = inputs.detach()
+        w3 = weights.detach().contiguous()
+        bounds = [0] + [int(v) for v in offs.tolist()]
+        x_dq = _macro_qdq(x2, -1, False)
+        w_dq = torch.stack([_macro_qdq(w3[e], -1, use_2dblock_w) for e in range(n_exp)])
+        y = torch.zeros(M, N, dtype=inputs.dtype, device=inputs.device)
+        for e in range(n_exp):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                torch.matmul(x_dq[lo:hi], w_dq[e].t(), out=y[lo:hi])
+        if not use_2dblock_w:
+            w_dq = torch.stack([_macro_qdq(w3[e], 0, False) for e in range(n_exp)])
+        xm = hadamard_transform(x2, left_mul=True) if hadamard_transform is not None else x2
+        x_dq = _macro_qdq(xm, 0, False)
+        ctx.save_for_backward(x_dq, w_dq)
+        ctx.bounds, ctx.use_sr_grad, ctx.hadamard_transform = bounds, use_sr_grad, hadamard_transform
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        from .mxfp4 import _macro_qdq
+        x_dq, w_dq = ctx.saved_tensors
+        n_exp, N, K = w_dq.shape
+        g2 = grad_output.contiguous()
+        g_dq = _macro_qdq(g2, -1, False, ctx.use_sr_grad)
+        gm = ctx.hadamard_transform(g2, left_mul=True) if ctx.hadamard_transform is not None else g2
+        g_m_dq = _macro_qdq(gm, 0, False, ctx.use_sr_grad)
+        dx = torch.zeros(g2.shape[0], K, dtype=g2.dtype, device=g2.device)
+        dw = torch.zeros(n_exp, N, K, dtype=g2.dtype, device=g2.device)
+        for e in range(n_exp):
+            lo, hi = ctx.bounds[e], ctx.bounds[e + 1]
+            if hi > lo:
+                torch.matmul(g_dq[lo:hi], w_dq[e], out=dx[lo:hi])
+                torch.matmul(g_m_dq[lo:hi].t(), x_dq[lo:hi], out=dw[e])
+        return dx, dw, None, None, None, None
+
+
 def _quantize_then_mxfp_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2dblock_w: bool, use_sr_grad: bool,
                                           use_dge: bool, use_hadamard: bool, clip_mode: str,
                                           use_macro_block_scaling: bool, use_uos: bool = False) -> torch.Tensor:
-    if use_dge or use_uos or clip_mode != "none":
-        raise NotImplementedError("use_dge / use_uos / clip_mode are not implemented on the B200 path")
+    clip_mode = clip_mode or "none"
+    if clip_mode not in ("none", "static", "dynamic"):
+        raise ValueError(f"unknown clip_mode {clip_mode!r}")
+    had = _hadamard(use_hadamard, use_2dblock_x, B.device)
     if use_macro_block_scaling:
-        raise NotImplementedError("two_level_scaling='blockwise' (macro-block scaling) is not implemented inside "
-                                  "the B200 GEMM")
+        if use_dge or use_uos or clip_mode != "none" or use_2dblock_x:
+            raise NotImplementedError("macro-block scaling together with use_dge / use_uos / clip_mode / "
+                                      "use_2dblock_x is not implemented on the B200 path")
+        return GroupedMacroLinearFunction.apply(A, B.transpose(-2, -1), offs, use_2dblock_w, bool(use_sr_grad), had)
     return GroupedLinearFunction.apply(A, B.transpose(-2, -1), offs, L.FMT_MXFP4, L.FMT_MXFP4, use_2dblock_x,
-                                       use_2dblock_w, bool(use_sr_grad), False,
-                                       _hadamard(use_hadamard, use_2dblock_x, B.device))
+                                       use_2dblock_w, bool(use_sr_grad), False, had, bool(use_uos), clip_mode,
+                                       bool(use_dge))
 
 
 def _quantize_then_nvfp4_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2dblock_w: bool, use_sr_grad: bool,
                                            use_outer_scale: bool = False, use_hadamard: bool = False,
                                            use_dge: bool = False, scale_format: str = "e4m3") -> torch.Tensor:
     _check_scale_format(scale_format)
-    if use_dge:
-        raise NotImplementedError("use_dge is not implemented on the B200 path")
     return GroupedLinearFunction.apply(A, B.transpose(-2, -1), offs, L.FMT_NVFP4, L.FMT_NVFP4, use_2dblock_x,
                                        use_2dblock_w, use_sr_grad, use_outer_scale,
-                                       _hadamard(use_hadamard, use_2dblock_x, B.device))
+                                       _hadamard(use_hadamard, use_2dblock_x, B.device), False, "none", bool(use_dge))
 
 
 _FP8 = {"e4m3": L.FMT_MXFP8_E4M3, "e5m2": L.FMT_MXFP8_E5M2}

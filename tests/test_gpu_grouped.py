@@ -107,7 +107,81 @@ def test_unsupported_grouped_options_raise():
     x = torch.zeros(128, 64, dtype=torch.bfloat16, device=d)
     B = torch.zeros(1, 64, 64, dtype=torch.bfloat16, device=d)
     offs = torch.tensor([128], dtype=torch.int32, device=d)
+    with pytest.raises(NotImplementedError):   # macro-block scaling with another option
+        G._quantize_then_mxfp_scaled_grouped_mm(x, B, offs, False, True, False, False, False, "static", True)
     with pytest.raises(NotImplementedError):
-        G._quantize_then_mxfp_scaled_grouped_mm(x, B, offs, False, True, False, False, False, "none", True)
-    with pytest.raises(NotImplementedError):
-        G._quantize_then_nvfp4_scaled_grouped_mm(x, B, offs, False, True, False, use_dge=True)
+        G._quantize_then_mxfp_scaled_grouped_mm(x, B, offs, True, True, False, False, False, "none", False)
+    with pytest.raises(ValueError):
+        G._quantize_then_mxfp_scaled_grouped_mm(x, B, offs, False, True, False, False, False, "bogus", False)
+
+
+def _per_expert_dense(x, w, dy, offs, dense_fn):
+    """Dense boundary function on every expert's rows: (y, dx, dw) assembled like the grouped outputs."""
+    M, n_exp = x.shape[0], w.shape[0]
+    y = torch.zeros(M, w.shape[1], dtype=x.dtype, device=x.device)
+    dx = torch.zeros_like(x)
+    dw = torch.zeros_like(w)
+    lo = 0
+    for e in range(n_exp):
+        hi = int(offs[e])
+        if hi > lo:
+            xe, we = x[lo:hi].clone().requires_grad_(True), w[e].clone().requires_grad_(True)
+            ye = dense_fn(xe, we)
+            ye.backward(dy[lo:hi])
+            y[lo:hi], dx[lo:hi], dw[e] = ye.detach(), xe.grad, we.grad
+        lo = hi
+    return y, dx, dw
+
+
+@pytest.mark.parametrize("opts", [dict(use_uos=True), dict(clip_mode="static"), dict(clip_mode="dynamic"),
+                                  dict(use_dge=True), dict(use_dge=True, use_uos=True, clip_mode="static"),
+                                  dict(macro=True), dict(macro=True, use_2dblock_w=False, use_hadamard=True)])
+def test_mxfp4_grouped_options_equal_the_dense_function_per_expert(opts):
+    """use_uos, clip_mode, use_dge and two-level scaling in the grouped MXFP4 function.  The dense
+    function with the same options is pinned to the reference's vectors; every quantisation block of
+    the grouped call (32 rows along tokens, 16 / 32-row Hadamard groups, 128-row macro blocks) lies
+    inside one expert's run of rows, so each expert's slice must reproduce the dense call on those
+    rows: forward and dgrad bit for bit (same operands, row-local), wgrad to GEMM rounding."""
+    from alto_b200 import grouped as G
+    from alto_b200 import mxfp4 as MX
+    d = _dev()
+    x, w, dy, offs, M = _case(counts=(256, 0, 128, 384))
+    x, w, dy, offs = x.to(d), w.to(d), dy.to(d), offs.to(d)
+    macro = opts.get("macro", False)
+    w2d, had = opts.get("use_2dblock_w", True), opts.get("use_hadamard", False)
+    uos, clip, dgef = opts.get("use_uos", False), opts.get("clip_mode", "none"), opts.get("use_dge", False)
+    MX.HadamardFactory.configure(block_size=32, randomized=True, dtype=torch.float32, seed=0)
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    ya = G._quantize_then_mxfp_scaled_grouped_mm(xa, wa.transpose(-2, -1), offs, False, w2d, False, dgef, had, clip,
+                                                 macro, uos)
+    ya.backward(dy)
+
+    def dense(a, b):
+        MX.HadamardFactory.configure(block_size=32, randomized=True, dtype=torch.float32, seed=0)  # same matrix
+        return MX._to_mxfp4_then_scaled_mm(a, b, False, w2d, False, dgef, clip, had, macro, uos)
+
+    yb, dxb, dwb = _per_expert_dense(x, w, dy, offs, dense)
+    assert torch.equal(ya, yb), _rel(ya, yb.float().cpu())
+    assert torch.equal(xa.grad, dxb)
+    assert _rel(wa.grad, dwb.float().cpu()) <= 1e-3
+    assert torch.count_nonzero(ya[int(offs[-1]):]) == 0 and torch.count_nonzero(wa.grad[1]) == 0
+
+
+def test_nvfp4_grouped_dge_equals_the_dense_function_per_expert():
+    from alto_b200 import grouped as G
+    from alto_b200 import nvfp4 as NV
+    d = _dev()
+    x, w, dy, offs, M = _case(counts=(128, 256, 0, 128))
+    x, w, dy, offs = x.to(d), w.to(d), dy.to(d), offs.to(d)
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    ya = G._quantize_then_nvfp4_scaled_grouped_mm(xa, wa.transpose(-2, -1), offs, False, True, False, use_dge=True)
+    ya.backward(dy)
+    yb, dxb, dwb = _per_expert_dense(
+        x, w, dy, offs, lambda a, b: NV._to_nvfp4_then_scaled_mm(a, b, False, True, False, use_dge=True))
+    assert torch.equal(ya, yb) and torch.equal(xa.grad, dxb)
+    assert _rel(wa.grad, dwb.float().cpu()) <= 1e-3
+    # the factor is applied: without it the gradient is about five times larger
+    xn, wn = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    G._quantize_then_nvfp4_scaled_grouped_mm(xn, wn.transpose(-2, -1), offs, False, True, False).backward(dy)
+    ratio = (wn.grad[0].float().norm() / wa.grad[0].float().norm()).item()
+    assert 4.5 < ratio < 5.5
