@@ -309,10 +309,13 @@ def quantize_colwise(x, fmt, codes, scale_plain=None, scale_packed=None, *, roun
 
 
 def quantize_2d(w, fmt, codes_k, codes_t=None, scale_plain=None, scale_packed_k=None, scale_packed_t=None, *,
-                outer_scale=None, clip_mode="none", use_uos=False) -> None:
-    _require_cuda(w, codes_k, codes_t, scale_plain, scale_packed_k, scale_packed_t, outer_scale)
+                outer_scale=None, clip_mode="none", use_uos=False, rounding=ROUND_RTN, rand_bits=None,
+                rand_tile=(0, 0)) -> None:
+    """``rounding``: ROUND_RTN, or ROUND_SR_BITS (FP4) with ``rand_bits`` = words by (row, column pair) as in
+    ``quantize_rowwise``: [2, rows, cols/2], or the periodic table [2, tile_rows, tile_pairs] with ``rand_tile``."""
+    _require_cuda(w, codes_k, codes_t, scale_plain, scale_packed_k, scale_packed_t, outer_scale, rand_bits)
     assert w.dim() == 2 and w.stride(1) == 1
-    p = _params(fmt, w, ROUND_RTN, outer_scale, None, None, 0, (0, 0), clip_mode, use_uos)
+    p = _params(fmt, w, rounding, outer_scale, rand_bits, None, 0, (0, 0), clip_mode, use_uos, rand_tile)
     _check(lib().altob200_quantize_2d(w.data_ptr(), w.shape[0], w.shape[1], w.stride(0), C.byref(p),
                                       codes_k.data_ptr(), _ptr(codes_t), _ptr(scale_plain), _ptr(scale_packed_k),
                                       _ptr(scale_packed_t), _stream()),

@@ -140,14 +140,14 @@ def quant_cols(x2, fmt, outer, rht, sr: dict, use_uos: bool = False, clip_mode: 
     return Operand(codes, sf, outer, Cc, R, fmt)
 
 
-def quant_2d(x2, fmt, outer, want_t: bool, use_uos: bool = False) -> Tuple[Operand, Optional[Operand]]:
+def quant_2d(x2, fmt, outer, want_t: bool, use_uos: bool = False, sr: Optional[dict] = None) -> Tuple[Operand, Optional[Operand]]:
     R, Cc = x2.shape
     b = L.block_of(fmt)
     ck = torch.empty(R, _code_cols(fmt, Cc), dtype=torch.uint8, device=x2.device)
     sk = _packed(R, Cc // b, x2.device)
     ct = torch.empty(Cc, _code_cols(fmt, R), dtype=torch.uint8, device=x2.device) if want_t else None
     stt = _packed(Cc, R // b, x2.device) if want_t else None
-    L.quantize_2d(x2, fmt, ck, ct, None, sk, stt, outer_scale=outer, use_uos=use_uos)
+    L.quantize_2d(x2, fmt, ck, ct, None, sk, stt, outer_scale=outer, use_uos=use_uos, **(sr or {}))
     return Operand(ck, sk, outer, R, Cc, fmt), (Operand(ct, stt, outer, Cc, R, fmt) if want_t else None)
 
 
@@ -215,9 +215,9 @@ def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, r
     M, N = g2.shape
     og = outer_scales(g2, use_outer_scale, None if use_2dblock_x else rht)
     if use_2dblock_x:
-        if use_sr_grad:
-            raise NotImplementedError("stochastic rounding with use_2dblock_x=True is not implemented")
-        return quant_2d(g2, fmt, None if og is None else og[0:1], True, use_uos)
+        # quantised once; both GEMMs use the same codes (2-D scales are axis-invariant)
+        return quant_2d(g2, fmt, None if og is None else og[0:1], True, use_uos,
+                        sr_args(use_sr_grad, "dy_n", M, N, g2.device))
     g_n = quant_rows(g2, fmt, None if og is None else og[0:1], sr_args(use_sr_grad, "dy_n", M, N, g2.device),
                      use_uos)
     g_m = cols_operand(g2, fmt, use_outer_scale, og, rht, dense, sr_args(use_sr_grad, "dy_m", N, M, g2.device),

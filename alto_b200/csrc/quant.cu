@@ -838,6 +838,10 @@ struct Quant2dArgs {
   int64_t nct_k, nct_t;
   const float* outer;
   MxOpts mx;          // clip 0/1 and uos (the dynamic clip needs block sums and is 1-D only)
+  // stochastic rounding (FP4): words by (row, pair of columns) as in the row-wise quantizer: full planes
+  // [2][rows][cols/2], or a periodic table [2][tile_rows][tile_pairs]
+  const uint32_t* rand_bits;
+  int64_t tile_rows, tile_pairs;
 };
 
 // 4 x 4 byte transpose: out[b] = (in[0].byte b, in[1].byte b, in[2].byte b, in[3].byte b)
@@ -858,7 +862,7 @@ __device__ __forceinline__ void transpose4x4_bytes(const uint32_t* in, uint32_t*
 // contiguous bytes per row per warp); for the transposed packing the thread's 16 x 8 codes are
 // transposed in registers (nibble merge of row pairs, then 4 x 4 byte transposes) and every column
 // receives 8 (FP4) or 16 (FP8) contiguous bytes per lane, 32 contiguous bytes per warp and column.
-template <int FMT, bool IN_BF16>
+template <int FMT, bool IN_BF16, int ROUND>
 __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
   using F = Fmt<FMT>;
   constexpr int B = F::B;
@@ -944,6 +948,28 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
       if (clip) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = round_in<IN_BF16>(__fmul_rn(v[j], 0.75f));
+      }
+      if (F::FP4 && ROUND == ALTOB200_ROUND_SR_BITS) {
+        // the lane's 4 column pairs are 4 consecutive, 16-byte aligned words of each plane
+        const bool tiled = a.tile_rows != 0;
+        const int64_t row = row0 + i;
+        const int64_t rr = tiled ? (int64_t)((uint32_t)row % (uint32_t)a.tile_rows) : row;
+        const int64_t pp = tiled ? (int64_t)((uint32_t)(col0 >> 1) % (uint32_t)a.tile_pairs) : (col0 >> 1);
+        const int64_t pitch = tiled ? a.tile_pairs : (a.cols >> 1);
+        const int64_t plane = tiled ? a.tile_rows * a.tile_pairs : a.rows * (a.cols >> 1);
+        uint4 re = make_uint4(0u, 0u, 0u, 0u), ro = re;
+        if (ok) {
+          re = __ldg(reinterpret_cast<const uint4*>(a.rand_bits + rr * pitch + pp));
+          ro = __ldg(reinterpret_cast<const uint4*>(a.rand_bits + plane + rr * pitch + pp));
+        }
+        const uint32_t e4[4] = {re.x, re.y, re.z, re.w}, o4[4] = {ro.x, ro.y, ro.z, ro.w};
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          word = merge_shifted(fp4_pair<FMT, IN_BF16, ROUND, FAST>(v[2 * j], v[2 * j + 1], s, e4[j], o4[j]), 8 * j, word);
+        kw[i] = word;
+        if (ok) *reinterpret_cast<uint32_t*>(a.codes_k + (row0 + i) * (a.cols >> 1) + (col0 >> 1)) = kw[i];
+        continue;
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = scale_elem<FMT, IN_BF16, FAST>(v[j], s);
@@ -1517,11 +1543,17 @@ static int launch_colwise(const ColwiseArgs& a, int rounding, cudaStream_t st) {
 }
 
 template <int FMT, bool IN_BF16>
-static int launch_2d(const Quant2dArgs& a, cudaStream_t st) {
+static int launch_2d(const Quant2dArgs& a, int rounding, cudaStream_t st) {
   // one warp per tile of 4 block columns x (64 rows for 16-blocks, 32 rows for 32-blocks)
   constexpr int TC = 4 * Fmt<FMT>::B, TR = 1024 / Fmt<FMT>::B;
   const int64_t tiles = ceil_div(a.cols, TC) * ceil_div(a.rows, TR);
-  quantize_2d_kernel<FMT, IN_BF16><<<(unsigned)ceil_div(tiles, 8), 256, 0, st>>>(a);
+  const unsigned blocks = (unsigned)ceil_div(tiles, 8);
+  if (rounding == ALTOB200_ROUND_RTN)
+    quantize_2d_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN><<<blocks, 256, 0, st>>>(a);
+  else if (rounding == ALTOB200_ROUND_SR_BITS && Fmt<FMT>::FP4)
+    quantize_2d_kernel<FMT, IN_BF16, Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN><<<blocks, 256, 0, st>>>(a);
+  else
+    return ALTOB200_EUNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 
@@ -1699,7 +1731,10 @@ int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
   if (w == nullptr || p == nullptr || codes_k == nullptr) return ALTOB200_EINVAL_SHAPE;
   const int B = block_of(p->format);
   if (rows <= 0 || cols <= 0 || rows % B != 0 || cols % B != 0 || ld < cols) return ALTOB200_EINVAL_SHAPE;
-  if (p->rounding != ALTOB200_ROUND_RTN || p->rht_n != 0) return ALTOB200_EUNSUPPORTED;
+  if (p->rht_n != 0) return ALTOB200_EUNSUPPORTED;
+  if (p->rounding != ALTOB200_ROUND_RTN && p->rounding != ALTOB200_ROUND_SR_BITS) return ALTOB200_EUNSUPPORTED;
+  if (p->rounding == ALTOB200_ROUND_SR_BITS && (p->rand_bits == nullptr || !aligned16(p->rand_bits)))
+    return ALTOB200_EINVAL_SHAPE;
   const int esz = p->in_dtype == ALTOB200_DT_BF16 ? 2 : 4;
   if (!aligned16(w) || (ld * esz) % 16 != 0 || !aligned16(codes_k)) return ALTOB200_EINVAL_ALIGN;
   if (codes_t != nullptr && !aligned16(codes_t)) return ALTOB200_EINVAL_ALIGN;
@@ -1710,13 +1745,17 @@ int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
   a.packed_k = (uint8_t*)scale_packed_k; a.packed_t = (uint8_t*)scale_packed_t;
   a.nct_k = ceil_div(cols / B, 4); a.nct_t = ceil_div(rows / B, 4);
   a.outer = p->outer_scale;
+  a.rand_bits = p->rand_bits; a.tile_rows = p->rand_tile_rows; a.tile_pairs = p->rand_tile_pairs;
+  if ((a.tile_rows != 0) != (a.tile_pairs != 0) || a.tile_rows < 0 || a.tile_pairs < 0 || (a.tile_pairs & 3) != 0)
+    return ALTOB200_EINVAL_SHAPE;
   int rc = fill_mx_opts(&a.mx, p, false);
   if (rc != ALTOB200_OK) return rc;
   rc = clear_packed_if_padded(scale_packed_k, rows, cols / B, st);
   if (rc != ALTOB200_OK) return rc;
   rc = clear_packed_if_padded(scale_packed_t, cols, rows / B, st);
   if (rc != ALTOB200_OK) return rc;
-#define CALL_2D(F, BF) launch_2d<F, BF>(a, st)
+  const int rounding = p->rounding;
+#define CALL_2D(F, BF) launch_2d<F, BF>(a, rounding, st)
   DISPATCH_FMT_DT(p->format, p->in_dtype, CALL_2D);
 #undef CALL_2D
 }

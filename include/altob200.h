@@ -213,6 +213,11 @@ int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t
  *   scale_plain   : [rows/block, cols/block], may be NULL
  *   scale_packed_k: packed layout rows=rows, ncols=cols/block (2D scale broadcast per row), may be NULL
  *   scale_packed_t: packed layout rows=cols, ncols=rows/block, may be NULL
+ * Rounding: ALTOB200_ROUND_RTN, or (FP4 formats) ALTOB200_ROUND_SR_BITS with rand_bits indexed by
+ * (row, column pair) exactly as in altob200_quantize_rowwise - full planes [2][rows][cols/2] or the
+ * periodic table [2][rand_tile_rows][rand_tile_pairs], rand_tile_pairs a multiple of 4; both packings
+ * then hold the same stochastically rounded codes (the 2-D-block gradient of a use_2dblock_x linear is
+ * quantised once, alto/kernels/fp4/nvfp4/nvfp_linear.py:176-186).  No Hadamard transform.
  */
 int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
                          const altob200_quant_params* p, void* codes_k, void* codes_t,

@@ -286,3 +286,27 @@ def test_linear_shape_contracts():
     x3 = torch.randn(2, 32, 64, dtype=torch.bfloat16, device=d)
     y = NV._to_nvfp4_then_scaled_mm(x3, w, False, True, False)
     assert y.shape == (2, 32, 64) and y.dtype == torch.bfloat16
+
+
+def test_nvfp4_linear_2d_activation_blocks_with_stochastic_rounding():
+    """`use_2dblock_x=True` with `use_sr_grad=True`: the gradient is quantised once in 16 x 16 blocks
+    with stochastic rounding and feeds both backward GEMMs (alto/kernels/fp4/nvfp4/nvfp_linear.py:176-186)."""
+    from alto_b200 import nvfp4 as NV
+    M, K, N = 256, 512, 384
+    x = reference_data((M, K), torch.float32, 61, outliers=False).bfloat16()
+    w = (reference_data((N, K), torch.float32, 62, outliers=False) * 0.02).bfloat16()
+    dy = (reference_data((M, N), torch.float32, 63, outliers=False) * 1e-3).bfloat16()
+    rn = rand_u32((2, M, N // 2), 64)
+    yo, dxo, dwo = O.nvfp4_linear(x, w, dy, use_2dblock_x=True, use_2dblock_w=True, rand_dy_n=rn)
+    d = _dev()
+    xd, wd = x.to(d).requires_grad_(True), w.to(d).requires_grad_(True)
+    with NV.explicit_sr_bits(lambda name, shape, dev: {"dy_n": _u32dev(rn)}[name]):
+        y = NV._to_nvfp4_then_scaled_mm(xd, wd, True, True, True, use_outer_scale=True)
+        y.backward(dy.to(d))
+    assert _rel(y, yo.bfloat16().float()) <= REL_TOL
+    assert _rel(xd.grad, dxo.bfloat16().float()) <= REL_TOL
+    assert _rel(wd.grad, dwo.bfloat16().float()) <= REL_TOL
+    # and it differs from round-to-nearest
+    x2, w2 = x.to(d).requires_grad_(True), w.to(d).requires_grad_(True)
+    NV._to_nvfp4_then_scaled_mm(x2, w2, True, True, False, use_outer_scale=True).backward(dy.to(d))
+    assert not torch.equal(x2.grad, xd.grad)

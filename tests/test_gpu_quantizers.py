@@ -342,3 +342,61 @@ def test_contract_violations_raise_before_launch():
     with pytest.raises(L.Altob200Error) as e:
         L.quantize_rowwise(x[:, 1:33], L.FMT_NVFP4, torch.empty(64, 16, dtype=torch.uint8, device=d))
     assert e.value.status == L.E_ALIGN
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+@pytest.mark.parametrize("shape", [(256, 512), (96, 160)])
+def test_2d_blocks_with_stochastic_rounding(fmt, shape):
+    """2-D blocks quantised once with stochastic rounding (the gradient of a `use_2dblock_x` linear,
+    alto/kernels/fp4/nvfp4/nvfp_linear.py:176-186): explicit words and (seed, offset), both packings."""
+    from alto_b200 import _lib as L
+    from alto_b200 import mxfp4 as MX, nvfp4 as NV
+    R, Cc = shape
+    if fmt == "mxfp4" and (R % 32 or Cc % 32):
+        pytest.skip("32 x 32 blocks")
+    x = reference_data(shape, torch.bfloat16, 14)
+    r = rand_u32((2, R, Cc // 2), 15)
+    seed, off = 24680, 1357
+    rp = O.reference_sr_planes(seed, off, R, Cc)
+    if fmt == "nvfp4":
+        qo, so = O.quantize_nvfp4(x, 16, -1, True, None, r)
+        q, s = NV.convert_to_nvfp4(x.to(_dev()), is_2d_block=True, update_outer_scale=False, use_sr=True,
+                                   rand_bits=_u32dev(r))
+        qp_o, _ = O.quantize_nvfp4(x, 16, -1, True, None, rp)
+        qp, _ = NV.convert_to_nvfp4(x.to(_dev()), is_2d_block=True, update_outer_scale=False, use_sr=True,
+                                    philox_seed=seed, philox_offset=off)
+        q_rtn, _ = O.quantize_nvfp4(x, 16, -1, True, None)
+    else:
+        qo, so = O.quantize_mxfp4(x, 32, -1, True, r)
+        q, s = MX.convert_to_mxfp4(x.to(_dev()), is_2d_block=True, use_sr=True, rand_bits=_u32dev(r))
+        qp_o, _ = O.quantize_mxfp4(x, 32, -1, True, rp)
+        qp, _ = MX.convert_to_mxfp4(x.to(_dev()), is_2d_block=True, use_sr=True, philox_seed=seed, philox_offset=off)
+        q_rtn, _ = O.quantize_mxfp4(x, 32, -1, True)
+    _same(s, so, "scales")
+    _same(q, qo, "explicit bits")
+    _same(qp, qp_o, "philox")
+    assert (q_rtn != qo).float().mean() > 0.05
+    # the second packing holds the same codes transposed
+    fid = L.FMT_NVFP4 if fmt == "nvfp4" else L.FMT_MXFP4
+    d = _dev()
+    ck = torch.empty(R, Cc // 2, dtype=torch.uint8, device=d)
+    ct = torch.empty(Cc, R // 2, dtype=torch.uint8, device=d)
+    L.quantize_2d(x.to(d), fid, ck, ct, rounding=L.ROUND_SR_BITS, rand_bits=_u32dev(r))
+    _same(ck, qo, "K packing")
+    want_t = O.pack_nibbles(O.unpack_nibbles(qo.view(torch.uint8)).t().contiguous())
+    _same(ct, want_t, "N packing")
+    with pytest.raises(NotImplementedError):
+        NV.convert_to_nvfp4(x.to(d), axis=0, is_2d_block=True, update_outer_scale=False, use_sr=True)
+
+
+def test_mxfp4_2d_blocks_with_seeded_stochastic_rounding_match_the_reference_kernel():
+    import ast
+    from pathlib import Path
+    from alto_b200 import mxfp4 as MX
+    z = np.load(Path(__file__).resolve().parent / "golden" / "sr2d_vectors.npz")
+    seed, off = [int(v) for v in z["philox_seed_offset"]]
+    for tag, shape in ast.literal_eval(str(z["meta"])):
+        x = torch.from_numpy(z[tag + "_x"].view(np.int16)).view(torch.bfloat16).reshape(shape).to(_dev())
+        q, s = MX.convert_to_mxfp4(x, is_2d_block=True, use_sr=True, philox_seed=seed, philox_offset=off)
+        _same(s, z[tag + "_s"], tag + " scales")
+        _same(q, z[tag + "_q"], tag + " codes")

@@ -135,3 +135,22 @@ def test_reference_special_values():
     assert outer.item() == pytest.approx(1e-30) and outer.dtype == torch.float32
     q, s = O.quantize_nvfp4(zeros, outer_scale=outer)
     assert torch.isfinite(s).all() and (s * outer).min() > 1.17e-38
+
+
+def _sr2d_cases():
+    import ast
+    from pathlib import Path
+    z = np.load(Path(__file__).resolve().parent / "golden" / "sr2d_vectors.npz")
+    return z, ast.literal_eval(str(z["meta"]))
+
+
+def test_2d_blocks_with_stochastic_rounding_match_the_reference_kernel():
+    """The reference's MXFP4 kernel (interpreted) on 32 x 32 blocks with (philox_seed, philox_offset):
+    pins how its Philox words pair with the elements of a 2-D-block launch."""
+    z, meta = _sr2d_cases()
+    seed, off = [int(v) for v in z["philox_seed_offset"]]
+    for tag, shape in meta:
+        x = torch.from_numpy(z[tag + "_x"].view(np.int16)).view(torch.bfloat16).reshape(shape)
+        q, s = O.quantize_mxfp4(x, 32, -1, True, O.reference_sr_planes(seed, off, shape[0], shape[1]))
+        assert np.array_equal(q.view(torch.uint8).numpy(), z[tag + "_q"]), tag
+        assert np.array_equal(s.numpy(), z[tag + "_s"]), tag
