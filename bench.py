@@ -57,8 +57,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 GEMM_DRAM_BYTES_PER_LAUNCH = 216.5e6
 # codes + packed scales of both operands + bf16 output, mean of fprop / wgrad / dgrad
 GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (52.0e6 + 234.9e6 + 84.9e6 + 117.4e6 + 99.1e6 + 67.1e6) / 3
-CPU_SAMPLE_ROWS = 256      # token rows of the CPU sample
-CPU_SAMPLE_FEATS = 1024    # output features (rows of W) of the CPU sample
+CPU_SAMPLE_ROWS = 2048     # token rows of the CPU sample
+CPU_SAMPLE_FEATS = 2048    # output features (rows of W) of the CPU sample
+CPU_BASELINE_REPS = 10     # steps of the sample timed for `cpu_baseline` (10-20 s of host work in all)
 
 
 def load_peaks():
@@ -172,7 +173,7 @@ def cpu_baseline(rows: int, reps: int = 1):
     flops = 3 * 2 * rows * CPU_SAMPLE_FEATS * K
     return {"value": flops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"{rows} of {M} token rows x {CPU_SAMPLE_FEATS} of {N} output features (K={K} full): quantize + "
-                      f"Hadamard + dequantize + fp32 matmuls of one fwd+dgrad+wgrad step, {dt:.2f} s per step"}
+                      f"Hadamard + dequantize + fp32 matmuls of one fwd+dgrad+wgrad step, {dt:.2f} s per step, {reps} steps timed"}
 
 
 def run_reference(args):
@@ -446,7 +447,7 @@ def run_ours(args):
     }
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(CPU_SAMPLE_ROWS)
+            line["cpu_baseline"] = cpu_baseline(CPU_SAMPLE_ROWS, CPU_BASELINE_REPS)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
