@@ -140,33 +140,13 @@ __device__ __forceinline__ float div_by_6(float x) {
 }
 
 // ---------------------------------------------------------------------------------------
-// E2M1 encode, round to nearest even, saturating.  Bit-for-bit restatement of
+// E2M1 encode, round to nearest even, saturating:
 //   alto/kernels/fp4/fp4_common/triton_fp4_ops.py:26-93 with USE_SR=False.
+// Two floats -> one byte of E2M1 codes (v0 in the low nibble) with the hardware converter, which
+// computes what the reference's bit arithmetic computes for every finite input: round to nearest
+// even on the E2M1 grid including its subnormal 0.5, saturation to 6, sign of zero kept (checked
+// against the oracle on the golden vectors and on random data in the GPU tests).
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t e2m1_rtn_bits(float v) {
-  uint32_t qx = f2u(v);
-  const uint32_t s = qx & 0x80000000u;
-  qx ^= s;
-  const float a = u2f(qx);
-  uint32_t code;
-  if (a >= 6.0f) {
-    code = 7u;
-  } else if (a < 1.0f) {
-    // denormal range of E2M1: add 2^22 so that the fp32 adder rounds to a multiple of 0.5
-    const float d = __fadd_rn(a, u2f(149u << 23));
-    code = (f2u(d) - (149u << 23)) & 0xFFu;
-  } else {
-    // normal range (a NaN also lands here, as it does through the reference's masks)
-    const uint32_t mant_odd = (qx >> 22) & 1u;
-    const uint32_t n = qx + (uint32_t)((1 - 127) << 23) + ((1u << 21) - 1u) + mant_odd;
-    code = (n >> 22) & 0xFFu;
-  }
-  return (code | (s >> 28)) & 0xFFu;
-}
-
-// Two floats -> one byte of E2M1 codes (v0 in the low nibble) with the hardware
-// converter.  Identical to e2m1_rtn_bits for every finite input (round to nearest even on
-// the E2M1 grid including its subnormal 0.5, saturation to 6, sign of zero kept).
 __device__ __forceinline__ uint32_t e2m1x2_rtn_hw(float v0, float v1) {
   uint16_t r;
   asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }"
@@ -247,29 +227,12 @@ __device__ __forceinline__ float2 fp8x2_decode(uint32_t c) {
 
 // ---------------------------------------------------------------------------------------
 // Philox-4x32-10 with the counter/key convention of triton.language.randint4x(seed, offset):
-// counter = (offset_lo, offset_hi? 0, 0, 0), key = (seed_lo, seed_hi).
+// counter = (offset_lo, offset_hi, 0, 0), key = (seed_lo, seed_hi); each of the ten rounds is
+//   c0' = hi(B * c2) ^ c1 ^ k0,  c2' = hi(A * c0) ^ c3 ^ k1,  c1' = lo(B * c2),  c3' = lo(A * c0)
+// with A = 0xD2511F53, B = 0xCD9E8D57 and the key advanced by (0x9E3779B9, 0xBB67AE85) per round.
+// The ten round keys are precomputed on the host (they depend on the seed only), so that each round
+// is two wide multiplies and two three-input XORs.
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
-                                              uint32_t k0, uint32_t k1, uint32_t out[4]) {
-  const uint32_t A = 0xD2511F53u, B = 0xCD9E8D57u, KA = 0x9E3779B9u, KB = 0xBB67AE85u;
-#pragma unroll
-  for (int i = 0; i < 10; ++i) {
-    const uint32_t _c0 = c0, _c2 = c2;
-    c0 = __umulhi(B, _c2) ^ c1 ^ k0;
-    c2 = __umulhi(A, _c0) ^ c3 ^ k1;
-    c1 = B * _c2;
-    c3 = A * _c0;
-    k0 += KA;
-    k1 += KB;
-  }
-  out[0] = c0;
-  out[1] = c1;
-  out[2] = c2;
-  out[3] = c3;
-}
-
-// Same generator with the ten round keys precomputed on the host (they depend on the seed only),
-// so that each round is two wide multiplies and two three-input XORs; counter words 2 and 3 are 0.
 struct PhiloxKeys {
   uint32_t k[20];  // k[2i], k[2i+1]: key of round i
 };

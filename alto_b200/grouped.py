@@ -100,17 +100,20 @@ class GroupedLinearFunction(torch.autograd.Function):
         assert K == K2, f"inner dimensions differ: {K} vs {K2}"
         torch._check(offs is not None and offs.numel() == n_exp, lambda: "offs must hold one entry per expert")
         E.check_dims("grouped GEMM", M, K, N)
-        if use_2dblock_x:
-            raise NotImplementedError("use_2dblock_x=True is not implemented for the grouped path")
         x2 = E.as_2d_rows(inputs.detach())
         w3 = weights.detach().contiguous()
         offs32 = offs.to(torch.int32).contiguous()
         group_expert = group_experts_from_offsets(offs32, M)
         rht, dense = E.split_transform(hadamard_transform, False)
 
-        ox = E.outer_scales(x2, use_outer_scale, rht)
-        x_k = E.quant_rows(x2, fmt, None if ox is None else ox[0:1], E.RTN, use_uos)
-        x_m = E.cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, E.RTN, use_uos, clip_mode)
+        if use_2dblock_x:
+            # 2-D blocks never straddle an expert (runs of rows are multiples of 128): one pass, both packings
+            ox = E.outer_scales(x2, use_outer_scale, None)
+            x_k, x_m = E.quant_2d(x2, fmt, None if ox is None else ox[0:1], True, use_uos)
+        else:
+            ox = E.outer_scales(x2, use_outer_scale, rht)
+            x_k = E.quant_rows(x2, fmt, None if ox is None else ox[0:1], E.RTN, use_uos)
+            x_m = E.cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, E.RTN, use_uos, clip_mode)
         w_k, w_t = _quant_weight_stack(w3, fmt, use_2dblock_w, use_outer_scale, use_uos)
         y = _grouped_gemm(x_k, w_k, N, n_exp, group_expert, inputs.dtype)
 
@@ -120,7 +123,7 @@ class GroupedLinearFunction(torch.autograd.Function):
         ctx.dims = (M, K, N, n_exp)
         ctx.fmt, ctx.fmt_grad = fmt, fmt_grad
         ctx.use_sr_grad, ctx.use_outer_scale, ctx.rht, ctx.dense_transform = use_sr_grad, use_outer_scale, rht, dense
-        ctx.use_uos, ctx.clip_mode, ctx.use_dge = use_uos, clip_mode, use_dge
+        ctx.use_uos, ctx.clip_mode, ctx.use_dge, ctx.use_2dblock_x = use_uos, clip_mode, use_dge, use_2dblock_x
         return y
 
     @staticmethod
@@ -134,11 +137,16 @@ class GroupedLinearFunction(torch.autograd.Function):
         x_m = E.Operand(xc, xs, xo, K, M, ctx.fmt)
         w_t = E.Operand(wc, ws, wo, n_exp * K, N, ctx.fmt)
         g2 = E.as_2d_rows(grad_output)
-        og = E.outer_scales(g2, ctx.use_outer_scale, ctx.rht)
-        g_n = E.quant_rows(g2, ctx.fmt_grad, None if og is None else og[0:1],
-                           E.sr_args(ctx.use_sr_grad, "dy_n", M, N, g2.device), ctx.use_uos)
-        g_m = E.cols_operand(g2, ctx.fmt_grad, ctx.use_outer_scale, og, ctx.rht, ctx.dense_transform,
-                             E.sr_args(ctx.use_sr_grad, "dy_m", N, M, g2.device), ctx.use_uos, ctx.clip_mode)
+        if ctx.use_2dblock_x:
+            og = E.outer_scales(g2, ctx.use_outer_scale, None)
+            g_n, g_m = E.quant_2d(g2, ctx.fmt_grad, None if og is None else og[0:1], True, ctx.use_uos,
+                                  E.sr_args(ctx.use_sr_grad and L.is_fp4(ctx.fmt_grad), "dy_n", M, N, g2.device))
+        else:
+            og = E.outer_scales(g2, ctx.use_outer_scale, ctx.rht)
+            g_n = E.quant_rows(g2, ctx.fmt_grad, None if og is None else og[0:1],
+                               E.sr_args(ctx.use_sr_grad, "dy_n", M, N, g2.device), ctx.use_uos)
+            g_m = E.cols_operand(g2, ctx.fmt_grad, ctx.use_outer_scale, og, ctx.rht, ctx.dense_transform,
+                                 E.sr_args(ctx.use_sr_grad, "dy_m", N, M, g2.device), ctx.use_uos, ctx.clip_mode)
         grad_inputs = grad_weights = None
         if ctx.needs_input_grad[0]:
             grad_inputs = _grouped_gemm(g_n, w_t, K, n_exp, group_expert, grad_output.dtype)
@@ -176,7 +184,7 @@ class GroupedMacroLinearFunction(torch.autograd.Function):
     is canonical [E, N, K].  One host synchronisation per call (the expert boundaries)."""
 
     @staticmethod
-    def forward(ctx, inputs, weights, offs, use_2dblock_w, use_sr_grad, hadamard_transform):
+    def forward(ctx, inputs, weights, offs, use_2dblock_w, use_sr_grad, hadamard_transform, use_2dblock_x=False):
         from .mxfp4 import _macro_qdq
         if not inputs.is_cuda:
             raise RuntimeError("grouped GEMM runs on CUDA tensors only (no CPU fallback)")
@@ -189,7 +197,7 @@ class GroupedMacroLinearFunction(torch.autograd.Function):
         x2 = inputs.detach()
         w3 = weights.detach().contiguous()
         bounds = [0] + [int(v) for v in offs.tolist()]
-        x_dq = _macro_qdq(x2, -1, False)
+        x_dq = _macro_qdq(x2, -1, use_2dblock_x)
         w_dq = torch.stack([_macro_qdq(w3[e], -1, use_2dblock_w) for e in range(n_exp)])
         y = torch.zeros(M, N, dtype=inputs.dtype, device=inputs.device)
         for e in range(n_exp):
@@ -198,10 +206,12 @@ class GroupedMacroLinearFunction(torch.autograd.Function):
                 torch.matmul(x_dq[lo:hi], w_dq[e].t(), out=y[lo:hi])
         if not use_2dblock_w:
             w_dq = torch.stack([_macro_qdq(w3[e], 0, False) for e in range(n_exp)])
-        xm = hadamard_transform(x2, left_mul=True) if hadamard_transform is not None else x2
-        x_dq = _macro_qdq(xm, 0, False)
+        if not use_2dblock_x:
+            xm = hadamard_transform(x2, left_mul=True) if hadamard_transform is not None else x2
+            x_dq = _macro_qdq(xm, 0, False)
         ctx.save_for_backward(x_dq, w_dq)
         ctx.bounds, ctx.use_sr_grad, ctx.hadamard_transform = bounds, use_sr_grad, hadamard_transform
+        ctx.use_2dblock_x = use_2dblock_x
         return y
 
     @staticmethod
@@ -210,9 +220,12 @@ class GroupedMacroLinearFunction(torch.autograd.Function):
         x_dq, w_dq = ctx.saved_tensors
         n_exp, N, K = w_dq.shape
         g2 = grad_output.contiguous()
-        g_dq = _macro_qdq(g2, -1, False, ctx.use_sr_grad)
-        gm = ctx.hadamard_transform(g2, left_mul=True) if ctx.hadamard_transform is not None else g2
-        g_m_dq = _macro_qdq(gm, 0, False, ctx.use_sr_grad)
+        if ctx.use_2dblock_x:
+            g_dq = g_m_dq = _macro_qdq(g2, -1, True, ctx.use_sr_grad)
+        else:
+            g_dq = _macro_qdq(g2, -1, False, ctx.use_sr_grad)
+            gm = ctx.hadamard_transform(g2, left_mul=True) if ctx.hadamard_transform is not None else g2
+            g_m_dq = _macro_qdq(gm, 0, False, ctx.use_sr_grad)
         dx = torch.zeros(g2.shape[0], K, dtype=g2.dtype, device=g2.device)
         dw = torch.zeros(n_exp, N, K, dtype=g2.dtype, device=g2.device)
         for e in range(n_exp):
@@ -220,7 +233,7 @@ class GroupedMacroLinearFunction(torch.autograd.Function):
             if hi > lo:
                 torch.matmul(g_dq[lo:hi], w_dq[e], out=dx[lo:hi])
                 torch.matmul(g_m_dq[lo:hi].t(), x_dq[lo:hi], out=dw[e])
-        return dx, dw, None, None, None, None
+        return dx, dw, None, None, None, None, None
 
 
 def _quantize_then_mxfp_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2dblock_w: bool, use_sr_grad: bool,
@@ -231,10 +244,11 @@ def _quantize_then_mxfp_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2
         raise ValueError(f"unknown clip_mode {clip_mode!r}")
     had = _hadamard(use_hadamard, use_2dblock_x, B.device)
     if use_macro_block_scaling:
-        if use_dge or use_uos or clip_mode != "none" or use_2dblock_x:
-            raise NotImplementedError("macro-block scaling together with use_dge / use_uos / clip_mode / "
-                                      "use_2dblock_x is not implemented on the B200 path")
-        return GroupedMacroLinearFunction.apply(A, B.transpose(-2, -1), offs, use_2dblock_w, bool(use_sr_grad), had)
+        if use_dge or use_uos or clip_mode != "none":
+            raise NotImplementedError("macro-block scaling together with use_dge / use_uos / clip_mode is not "
+                                      "implemented on the B200 path")
+        return GroupedMacroLinearFunction.apply(A, B.transpose(-2, -1), offs, use_2dblock_w, bool(use_sr_grad), had,
+                                                bool(use_2dblock_x))
     return GroupedLinearFunction.apply(A, B.transpose(-2, -1), offs, L.FMT_MXFP4, L.FMT_MXFP4, use_2dblock_x,
                                        use_2dblock_w, bool(use_sr_grad), False, had, bool(use_uos), clip_mode,
                                        bool(use_dge))

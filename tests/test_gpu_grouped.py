@@ -109,8 +109,6 @@ def test_unsupported_grouped_options_raise():
     offs = torch.tensor([128], dtype=torch.int32, device=d)
     with pytest.raises(NotImplementedError):   # macro-block scaling with another option
         G._quantize_then_mxfp_scaled_grouped_mm(x, B, offs, False, True, False, False, False, "static", True)
-    with pytest.raises(NotImplementedError):
-        G._quantize_then_mxfp_scaled_grouped_mm(x, B, offs, True, True, False, False, False, "none", False)
     with pytest.raises(ValueError):
         G._quantize_then_mxfp_scaled_grouped_mm(x, B, offs, False, True, False, False, False, "bogus", False)
 
@@ -135,7 +133,9 @@ def _per_expert_dense(x, w, dy, offs, dense_fn):
 
 @pytest.mark.parametrize("opts", [dict(use_uos=True), dict(clip_mode="static"), dict(clip_mode="dynamic"),
                                   dict(use_dge=True), dict(use_dge=True, use_uos=True, clip_mode="static"),
-                                  dict(macro=True), dict(macro=True, use_2dblock_w=False, use_hadamard=True)])
+                                  dict(macro=True), dict(macro=True, use_2dblock_w=False, use_hadamard=True),
+                                  dict(use_2dblock_x=True), dict(use_2dblock_x=True, use_uos=True, use_dge=True),
+                                  dict(macro=True, use_2dblock_x=True)])
 def test_mxfp4_grouped_options_equal_the_dense_function_per_expert(opts):
     """use_uos, clip_mode, use_dge and two-level scaling in the grouped MXFP4 function.  The dense
     function with the same options is pinned to the reference's vectors; every quantisation block of
@@ -150,15 +150,16 @@ def test_mxfp4_grouped_options_equal_the_dense_function_per_expert(opts):
     macro = opts.get("macro", False)
     w2d, had = opts.get("use_2dblock_w", True), opts.get("use_hadamard", False)
     uos, clip, dgef = opts.get("use_uos", False), opts.get("clip_mode", "none"), opts.get("use_dge", False)
+    x2d = opts.get("use_2dblock_x", False)
     MX.HadamardFactory.configure(block_size=32, randomized=True, dtype=torch.float32, seed=0)
     xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
-    ya = G._quantize_then_mxfp_scaled_grouped_mm(xa, wa.transpose(-2, -1), offs, False, w2d, False, dgef, had, clip,
+    ya = G._quantize_then_mxfp_scaled_grouped_mm(xa, wa.transpose(-2, -1), offs, x2d, w2d, False, dgef, had, clip,
                                                  macro, uos)
     ya.backward(dy)
 
     def dense(a, b):
         MX.HadamardFactory.configure(block_size=32, randomized=True, dtype=torch.float32, seed=0)  # same matrix
-        return MX._to_mxfp4_then_scaled_mm(a, b, False, w2d, False, dgef, clip, had, macro, uos)
+        return MX._to_mxfp4_then_scaled_mm(a, b, x2d, w2d, False, dgef, clip, had, macro, uos)
 
     yb, dxb, dwb = _per_expert_dense(x, w, dy, offs, dense)
     assert torch.equal(ya, yb), _rel(ya, yb.float().cpu())
@@ -185,3 +186,23 @@ def test_nvfp4_grouped_dge_equals_the_dense_function_per_expert():
     G._quantize_then_nvfp4_scaled_grouped_mm(xn, wn.transpose(-2, -1), offs, False, True, False).backward(dy)
     ratio = (wn.grad[0].float().norm() / wa.grad[0].float().norm()).item()
     assert 4.5 < ratio < 5.5
+
+
+@pytest.mark.parametrize("scheme", ["nvfp4", "mxfp8"])
+def test_grouped_2d_activation_blocks_equal_the_dense_function_per_expert(scheme):
+    from alto_b200 import grouped as G
+    from alto_b200 import mxfp8 as M8, nvfp4 as NV
+    d = _dev()
+    x, w, dy, offs, M = _case(counts=(128, 256, 0, 128))
+    x, w, dy, offs = x.to(d), w.to(d), dy.to(d), offs.to(d)
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    if scheme == "nvfp4":
+        ya = G._quantize_then_nvfp4_scaled_grouped_mm(xa, wa.transpose(-2, -1), offs, True, True, False)
+        dense = lambda a, b: NV._to_nvfp4_then_scaled_mm(a, b, True, True, False)  # noqa: E731
+    else:
+        ya = G._quantize_then_mxfp8_scaled_grouped_mm(xa, wa.transpose(-2, -1), offs, use_2dblock_x=True)
+        dense = lambda a, b: M8._to_mxfp8_then_scaled_mm(a, b, "e4m3", False, True, True)  # noqa: E731
+    ya.backward(dy)
+    yb, dxb, dwb = _per_expert_dense(x, w, dy, offs, dense)
+    assert torch.equal(ya, yb) and torch.equal(xa.grad, dxb)
+    assert _rel(wa.grad, dwb.float().cpu()) <= 1e-3
