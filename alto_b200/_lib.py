@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "altob200_quantize_rowwise",
     "altob200_quantize_colwise",
     "altob200_quantize_2d",
+    "altob200_quantize_2d_batched",
     "altob200_dequantize",
     "altob200_philox_tile",
     "altob200_rht",
@@ -102,6 +103,9 @@ def _declare(lib):
         f.argtypes = [vp, i64, i64, i64, C.POINTER(QuantParams), vp, vp, vp, vp]
     lib.altob200_quantize_2d.restype = C.c_int
     lib.altob200_quantize_2d.argtypes = [vp, i64, i64, i64, C.POINTER(QuantParams), vp, vp, vp, vp, vp, vp]
+    lib.altob200_quantize_2d_batched.restype = C.c_int
+    lib.altob200_quantize_2d_batched.argtypes = [vp, i64, i64, i64, i64, i64, C.POINTER(QuantParams), vp, vp, vp, vp,
+                                                 vp, vp]
     lib.altob200_dequantize.restype = C.c_int
     lib.altob200_dequantize.argtypes = [vp, vp, vp, i32, i32, i64, i64, i32, vp, i64, vp]
     lib.altob200_rht.restype = C.c_int
@@ -320,6 +324,21 @@ def quantize_2d(w, fmt, codes_k, codes_t=None, scale_plain=None, scale_packed_k=
                                       codes_k.data_ptr(), _ptr(codes_t), _ptr(scale_plain), _ptr(scale_packed_k),
                                       _ptr(scale_packed_t), _stream()),
            "altob200_quantize_2d")
+
+
+def quantize_2d_batched(w3, fmt, codes_k, codes_t=None, scale_plain=None, scale_packed_k=None, scale_packed_t=None,
+                        *, outer_scale=None, clip_mode="none", use_uos=False, rounding=ROUND_RTN, rand_bits=None,
+                        rand_tile=(0, 0)) -> None:
+    """``w3`` [batch, rows, cols] (last dim contiguous, equal batch stride): every matrix quantised in 2-D
+    blocks by one launch; outputs are the per-matrix outputs of ``quantize_2d`` stacked along a leading
+    batch dimension.  Random words, if any, are indexed by the rows of the flattened [batch * rows, cols] view."""
+    _require_cuda(w3, codes_k, codes_t, scale_plain, scale_packed_k, scale_packed_t, outer_scale, rand_bits)
+    assert w3.dim() == 3 and w3.stride(2) == 1
+    p = _params(fmt, w3, rounding, outer_scale, rand_bits, None, 0, (0, 0), clip_mode, use_uos, rand_tile)
+    _check(lib().altob200_quantize_2d_batched(w3.data_ptr(), w3.shape[0], w3.stride(0), w3.shape[1], w3.shape[2],
+                                              w3.stride(1), C.byref(p), codes_k.data_ptr(), _ptr(codes_t),
+                                              _ptr(scale_plain), _ptr(scale_packed_k), _ptr(scale_packed_t), _stream()),
+           "altob200_quantize_2d_batched")
 
 
 def dequantize(codes, scale_plain, fmt, is_2d, rows, cols, out, outer_scale=None, static_clip=False) -> None:

@@ -56,23 +56,25 @@ def quantize(x: torch.Tensor, fmt: int, axis: int, is_2d: bool, *, outer_scale: 
         nb = x3.shape[0]
         sr = {}
         if rounding != L.ROUND_RTN:
-            # words belong to (row, column pair) of the quantisation-axis-last view; for axis=-2 that view is
-            # the transposed matrix, which this kernel does not index
-            if a != -1 or nb != 1 or not fp4:
-                raise NotImplementedError("stochastic rounding with 2D blocks is implemented for FP4, axis=-1, "
-                                          "unbatched tensors")
+            # words belong to (row, column pair) of the quantisation-axis-last view, leading dimensions
+            # flattened into its rows; for axis=-2 that view is the transposed matrix, which this kernel
+            # does not index
+            if a != -1 or not fp4:
+                raise NotImplementedError("stochastic rounding with 2D blocks is implemented for FP4 and axis=-1")
             if rounding == L.ROUND_SR_PHILOX:
-                tile = L.sr_tile_dims(M, N)
+                tile = L.sr_tile_dims(nb * M, N)
                 sr = dict(rounding=L.ROUND_SR_BITS, rand_tile=tile,
                           rand_bits=L.philox_tile(philox[0], philox[1], tile[0], tile[1], dev))
             else:
-                sr = dict(rounding=L.ROUND_SR_BITS, rand_bits=_rand_planes(rand_bits, M, N))
+                sr = dict(rounding=L.ROUND_SR_BITS, rand_bits=_rand_planes(rand_bits, nb * M, N))
         codes_k = torch.empty(nb, M, N // 2 if fp4 else N, dtype=torch.uint8, device=dev)
         codes_t = torch.empty(nb, N, M // 2 if fp4 else M, dtype=torch.uint8, device=dev) if a == -2 else None
         scales = torch.empty(nb, M // block, N // block, dtype=scale_dtype, device=dev)
-        for b in range(nb):
-            L.quantize_2d(x3[b], fmt, codes_k[b], None if codes_t is None else codes_t[b], scales[b],
+        if nb == 1:
+            L.quantize_2d(x3[0], fmt, codes_k[0], None if codes_t is None else codes_t[0], scales[0],
                           outer_scale=outer_scale, **opts, **sr)
+        else:
+            L.quantize_2d_batched(x3, fmt, codes_k, codes_t, scales, outer_scale=outer_scale, **opts, **sr)
         if a == -1:
             codes = codes_k.reshape(*lead, M, codes_k.shape[-1])
         else:  # physical [N, M/2], returned as its transpose like the reference

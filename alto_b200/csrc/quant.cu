@@ -842,6 +842,9 @@ struct Quant2dArgs {
   // [2][rows][cols/2], or a periodic table [2][tile_rows][tile_pairs]
   const uint32_t* rand_bits;
   int64_t tile_rows, tile_pairs;
+  // batch of equally shaped matrices: input stride in elements, outputs stacked contiguously; the
+  // rows of the stochastic-rounding view are the rows of all matrices, one after the other
+  int64_t batch, batch_stride, packed_k_bytes, packed_t_bytes;
 };
 
 // 4 x 4 byte transpose: out[b] = (in[0].byte b, in[1].byte b, in[2].byte b, in[3].byte b)
@@ -863,7 +866,7 @@ __device__ __forceinline__ void transpose4x4_bytes(const uint32_t* in, uint32_t*
 // transposed in registers (nibble merge of row pairs, then 4 x 4 byte transposes) and every column
 // receives 8 (FP4) or 16 (FP8) contiguous bytes per lane, 32 contiguous bytes per warp and column.
 template <int FMT, bool IN_BF16, int ROUND>
-__global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
+__global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
   using F = Fmt<FMT>;
   constexpr int B = F::B;
   constexpr int LC = B / 2;          // lanes across columns: 8 columns each, 4 block columns per warp
@@ -871,9 +874,24 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
   constexpr int TR = 16 * LR, TC = 8 * LC;  // warp tile: 64 x 64 or 32 x 128
   constexpr int ESZ = IN_BF16 ? 2 : 4;
   const int lane = threadIdx.x & 31;
-  const int64_t tiles_c = (a.cols + TC - 1) / TC, tiles_r = (a.rows + TR - 1) / TR;
-  const int64_t tile = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (tile >= tiles_c * tiles_r) return;  // whole warps leave; nothing below synchronises the block
+  const int64_t tiles_c = (a_in.cols + TC - 1) / TC, tiles_r = (a_in.rows + TR - 1) / TR;
+  const int64_t tile_all = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tile_all >= tiles_c * tiles_r * a_in.batch) return;  // whole warps leave; nothing below synchronises the block
+  int64_t bi, tile;
+  divmod_fast(tile_all, tiles_c * tiles_r, &bi, &tile);
+  // this matrix of the batch: every pointer moved to its slice, the rest of the kernel sees one matrix
+  Quant2dArgs a = a_in;
+  {
+    const int64_t code_bytes = a.rows * (F::FP4 ? (a.cols >> 1) : a.cols);
+    a.w = reinterpret_cast<const uint8_t*>(a_in.w) + bi * a.batch_stride * ESZ;
+    a.codes_k = a_in.codes_k + bi * code_bytes;
+    if (a.codes_t != nullptr) a.codes_t = a_in.codes_t + bi * code_bytes;
+    if (a.scale_plain != nullptr)
+      a.scale_plain = reinterpret_cast<uint8_t*>(a_in.scale_plain) + bi * (a.rows / B) * (a.cols / B) * (F::MX ? 1 : 4);
+    if (a.packed_k != nullptr) a.packed_k = a_in.packed_k + bi * a.packed_k_bytes;
+    if (a.packed_t != nullptr) a.packed_t = a_in.packed_t + bi * a.packed_t_bytes;
+  }
+  const int64_t sr_row_base = bi * a.rows;
   int64_t tr, tc;
   divmod_fast(tile, tiles_c, &tr, &tc);
   const int lc = lane % LC, lr = lane / LC;
@@ -952,11 +970,11 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
       if (F::FP4 && ROUND == ALTOB200_ROUND_SR_BITS) {
         // the lane's 4 column pairs are 4 consecutive, 16-byte aligned words of each plane
         const bool tiled = a.tile_rows != 0;
-        const int64_t row = row0 + i;
-        const int64_t rr = tiled ? (int64_t)((uint32_t)row % (uint32_t)a.tile_rows) : row;
+        const int64_t row = sr_row_base + row0 + i;  // row of the flattened view over the batch
+        const int64_t rr = tiled ? (int64_t)((uint64_t)row % (uint64_t)a.tile_rows) : row;
         const int64_t pp = tiled ? (int64_t)((uint32_t)(col0 >> 1) % (uint32_t)a.tile_pairs) : (col0 >> 1);
         const int64_t pitch = tiled ? a.tile_pairs : (a.cols >> 1);
-        const int64_t plane = tiled ? a.tile_rows * a.tile_pairs : a.rows * (a.cols >> 1);
+        const int64_t plane = tiled ? a.tile_rows * a.tile_pairs : a.batch * a.rows * (a.cols >> 1);
         uint4 re = make_uint4(0u, 0u, 0u, 0u), ro = re;
         if (ok) {
           re = __ldg(reinterpret_cast<const uint4*>(a.rand_bits + rr * pitch + pp));
@@ -1546,7 +1564,7 @@ template <int FMT, bool IN_BF16>
 static int launch_2d(const Quant2dArgs& a, int rounding, cudaStream_t st) {
   // one warp per tile of 4 block columns x (64 rows for 16-blocks, 32 rows for 32-blocks)
   constexpr int TC = 4 * Fmt<FMT>::B, TR = 1024 / Fmt<FMT>::B;
-  const int64_t tiles = ceil_div(a.cols, TC) * ceil_div(a.rows, TR);
+  const int64_t tiles = ceil_div(a.cols, TC) * ceil_div(a.rows, TR) * a.batch;
   const unsigned blocks = (unsigned)ceil_div(tiles, 8);
   if (rounding == ALTOB200_ROUND_RTN)
     quantize_2d_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN><<<blocks, 256, 0, st>>>(a);
@@ -1728,7 +1746,14 @@ int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
                          const altob200_quant_params* p, void* codes_k, void* codes_t,
                          void* scale_plain, void* scale_packed_k, void* scale_packed_t,
                          void* stream) {
-  if (w == nullptr || p == nullptr || codes_k == nullptr) return ALTOB200_EINVAL_SHAPE;
+  return altob200_quantize_2d_batched(w, 1, rows * ld, rows, cols, ld, p, codes_k, codes_t, scale_plain,
+                                      scale_packed_k, scale_packed_t, stream);
+}
+
+int altob200_quantize_2d_batched(const void* w, int64_t batch, int64_t batch_stride, int64_t rows, int64_t cols,
+                                 int64_t ld, const altob200_quant_params* p, void* codes_k, void* codes_t,
+                                 void* scale_plain, void* scale_packed_k, void* scale_packed_t, void* stream) {
+  if (w == nullptr || p == nullptr || codes_k == nullptr || batch <= 0) return ALTOB200_EINVAL_SHAPE;
   const int B = block_of(p->format);
   if (rows <= 0 || cols <= 0 || rows % B != 0 || cols % B != 0 || ld < cols) return ALTOB200_EINVAL_SHAPE;
   if (p->rht_n != 0) return ALTOB200_EUNSUPPORTED;
@@ -1744,16 +1769,23 @@ int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
   a.codes_k = (uint8_t*)codes_k; a.codes_t = (uint8_t*)codes_t; a.scale_plain = scale_plain;
   a.packed_k = (uint8_t*)scale_packed_k; a.packed_t = (uint8_t*)scale_packed_t;
   a.nct_k = ceil_div(cols / B, 4); a.nct_t = ceil_div(rows / B, 4);
+  a.batch = batch; a.batch_stride = batch_stride;
+  a.packed_k_bytes = altob200_packed_scale_bytes(rows, cols / B);
+  a.packed_t_bytes = altob200_packed_scale_bytes(cols, rows / B);
+  if (batch > 1 && ((batch_stride * (p->in_dtype == ALTOB200_DT_BF16 ? 2 : 4)) % 16 != 0 ||
+                    (rows * (is_fp4(p->format) ? cols / 2 : cols)) % 16 != 0))
+    return ALTOB200_EINVAL_ALIGN;
   a.outer = p->outer_scale;
   a.rand_bits = p->rand_bits; a.tile_rows = p->rand_tile_rows; a.tile_pairs = p->rand_tile_pairs;
   if ((a.tile_rows != 0) != (a.tile_pairs != 0) || a.tile_rows < 0 || a.tile_pairs < 0 || (a.tile_pairs & 3) != 0)
     return ALTOB200_EINVAL_SHAPE;
   int rc = fill_mx_opts(&a.mx, p, false);
   if (rc != ALTOB200_OK) return rc;
-  rc = clear_packed_if_padded(scale_packed_k, rows, cols / B, st);
-  if (rc != ALTOB200_OK) return rc;
-  rc = clear_packed_if_padded(scale_packed_t, cols, rows / B, st);
-  if (rc != ALTOB200_OK) return rc;
+  // padding entries of the packed layouts are zero (the kernel does not visit them)
+  if (scale_packed_k != nullptr && ((rows & 127) != 0 || ((cols / B) & 3) != 0))
+    ALTOB200_CUDA_CHECK(cudaMemsetAsync(scale_packed_k, 0, (size_t)(batch * a.packed_k_bytes), st));
+  if (scale_packed_t != nullptr && ((cols & 127) != 0 || ((rows / B) & 3) != 0))
+    ALTOB200_CUDA_CHECK(cudaMemsetAsync(scale_packed_t, 0, (size_t)(batch * a.packed_t_bytes), st));
   const int rounding = p->rounding;
 #define CALL_2D(F, BF) launch_2d<F, BF>(a, rounding, st)
   DISPATCH_FMT_DT(p->format, p->in_dtype, CALL_2D);

@@ -63,14 +63,22 @@ def _quant_weight_stack(w3: torch.Tensor, fmt: int, use_2dblock_w: bool, use_out
     n_exp, N, K = w3.shape
     ow = E.outer_scales(w3.reshape(n_exp * N, K), use_outer_scale, None)
     outer = None if ow is None else ow[0:1]
+    if use_2dblock_w:
+        # every expert in one launch; the stacked outputs are the operands of the grouped GEMMs as they are
+        b = L.block_of(fmt)
+        cc = E._code_cols(fmt, K)
+        ck = torch.empty(n_exp, N, cc, dtype=torch.uint8, device=w3.device)
+        ct = torch.empty(n_exp, K, E._code_cols(fmt, N), dtype=torch.uint8, device=w3.device)
+        sk = torch.empty(n_exp * L.packed_scale_bytes(N, K // b), dtype=torch.uint8, device=w3.device)
+        st = torch.empty(n_exp * L.packed_scale_bytes(K, N // b), dtype=torch.uint8, device=w3.device)
+        L.quantize_2d_batched(w3, fmt, ck, ct, None, sk, st, outer_scale=outer, use_uos=use_uos)
+        return (E.Operand(ck.view(n_exp * N, cc), sk, outer, n_exp * N, K, fmt),
+                E.Operand(ct.view(n_exp * K, -1), st, outer, n_exp * K, N, fmt))
     ks, ts = [], []
     for e in range(n_exp):
         we = w3[e]
-        if use_2dblock_w:
-            k_op, t_op = E.quant_2d(we, fmt, outer, True, use_uos)
-        else:
-            k_op = E.quant_rows(we, fmt, outer, E.RTN, use_uos)
-            t_op = E.quant_cols(we, fmt, outer, None, E.RTN, use_uos)
+        k_op = E.quant_rows(we, fmt, outer, E.RTN, use_uos)
+        t_op = E.quant_cols(we, fmt, outer, None, E.RTN, use_uos)
         ks.append(k_op)
         ts.append(t_op)
     return _stack(ks), _stack(ts)

@@ -225,6 +225,19 @@ int altob200_quantize_2d(const void* w, int64_t rows, int64_t cols, int64_t ld,
                          void* stream);
 
 /*
+ * The same for `batch` equally shaped matrices in one launch (the experts of a MoE weight [E, N, K],
+ * alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_backward.py:633-652): matrix b starts batch_stride
+ * elements after matrix b - 1; every output holds the per-matrix outputs of altob200_quantize_2d one
+ * after the other (codes_k [batch][rows][cols/2], codes_t [batch][cols][rows/2], scale_plain
+ * [batch][rows/block][cols/block], packed scales batch x altob200_packed_scale_bytes(..)).  With
+ * stochastic rounding the rows of the random-word view are the rows of all matrices in sequence,
+ * as in the reference's flattened view.
+ */
+int altob200_quantize_2d_batched(const void* w, int64_t batch, int64_t batch_stride, int64_t rows, int64_t cols,
+                                 int64_t ld, const altob200_quant_params* p, void* codes_k, void* codes_t,
+                                 void* scale_plain, void* scale_packed_k, void* scale_packed_t, void* stream);
+
+/*
  * The reference's table of stochastic-rounding words: out[0][m][n], out[1][m][n] = first and second
  * word of Philox-4x32-10 with key (seed lo, seed hi) and counter (uint32(offset + m * tile_pairs + n),
  * 0, 0, 0), which is `r1, r2, _, _ = tl.randint4x(seed, offset + m * n_pairs + n)` of

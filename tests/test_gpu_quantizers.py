@@ -400,3 +400,41 @@ def test_mxfp4_2d_blocks_with_seeded_stochastic_rounding_match_the_reference_ker
         q, s = MX.convert_to_mxfp4(x, is_2d_block=True, use_sr=True, philox_seed=seed, philox_offset=off)
         _same(s, z[tag + "_s"], tag + " scales")
         _same(q, z[tag + "_q"], tag + " codes")
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4", "mxfp8"])
+def test_2d_batched_launch_equals_one_launch_per_matrix(fmt):
+    """`altob200_quantize_2d_batched` (all experts of a MoE weight in one launch) against per-matrix calls,
+    every output, and batched stochastic rounding against the oracle's flattened view."""
+    from alto_b200 import _lib as L
+    from alto_b200 import mxfp4 as MX
+    fid = {"nvfp4": L.FMT_NVFP4, "mxfp4": L.FMT_MXFP4, "mxfp8": L.FMT_MXFP8_E4M3}[fmt]
+    b = L.block_of(fid)
+    nb, R, Cc = 3, 160, 96
+    if b == 32:
+        R, Cc = 160, 96
+    d = _dev()
+    x = reference_data((nb, R, Cc), torch.bfloat16, 21).to(d)
+    cc, rc = (Cc // 2, R // 2) if L.is_fp4(fid) else (Cc, R)
+    sdt = torch.float32 if fmt == "nvfp4" else torch.uint8
+
+    def bufs(n):
+        return (torch.empty(n, R, cc, dtype=torch.uint8, device=d), torch.empty(n, Cc, rc, dtype=torch.uint8, device=d),
+                torch.empty(n, R // b, Cc // b, dtype=sdt, device=d),
+                torch.zeros(n, L.packed_scale_bytes(R, Cc // b), dtype=torch.uint8, device=d),
+                torch.zeros(n, L.packed_scale_bytes(Cc, R // b), dtype=torch.uint8, device=d))
+
+    ck, ct, sp, pk, pt = bufs(nb)
+    L.quantize_2d_batched(x, fid, ck, ct, sp, pk.view(-1), pt.view(-1))
+    for i in range(nb):
+        ck1, ct1, sp1, pk1, pt1 = bufs(1)
+        L.quantize_2d(x[i], fid, ck1[0], ct1[0], sp1[0], pk1[0], pt1[0])
+        for got, exp, what in ((ck[i], ck1[0], "codes_k"), (ct[i], ct1[0], "codes_t"), (sp[i], sp1[0], "scales"),
+                               (pk[i], pk1[0], "packed_k"), (pt[i], pt1[0], "packed_t")):
+            _same(got, exp.cpu(), f"{what}[{i}]")
+    if fmt == "mxfp4":
+        r = rand_u32((2, nb * R, Cc // 2), 22)
+        qo, so = O.quantize_mxfp4(x.cpu(), 32, -1, True, r)
+        q, s = MX.convert_to_mxfp4(x, is_2d_block=True, use_sr=True, rand_bits=_u32dev(r))
+        _same(s, so, "batched SR scales")
+        _same(q, qo, "batched SR codes")
