@@ -441,6 +441,8 @@ struct RhtParams {
   int8_t perm[16]; // output position i takes slot perm[i]
   float sign[16];  // sign applied to slot k after the butterfly
   int64_t row_off[16];  // byte offset of row pinv[k] from the first row of a 16-row group (column passes)
+  float qsign[16];      // sign[k] / sqrt(16): the factor applied to slot k
+  int perm_off[16];     // pinv[k] * 2048: byte offset of slot k's row in the shared-memory position table
 };
 
 __device__ __forceinline__ void hadamard16(float* z) {
@@ -562,7 +564,7 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
 #pragma unroll
       for (int k = 0; k < B; ++k) {
         // the fused +0 turns a -0 product into the +0 that a dot product yields
-        const float sg = 0.25f * a.rht.sign[k & 15];
+        const float sg = a.rht.qsign[k & 15];
         const __nv_bfloat162 p2 = __floats2bfloat162_rn(__fmaf_rn(v0[k], sg, 0.0f), __fmaf_rn(v1[k], sg, 0.0f));
         const uint32_t pw = *reinterpret_cast<const uint32_t*>(&p2);
         acc = absmax_bf16x2(acc, pw);
@@ -575,7 +577,7 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
       if (RHT) {
 #pragma unroll
         for (int k = 0; k < B; ++k) {
-          const float sg = 0.25f * a.rht.sign[k & 15];
+          const float sg = a.rht.qsign[k & 15];
           v0[k] = __fmaf_rn(v0[k], sg, 0.0f);
           v1[k] = __fmaf_rn(v1[k], sg, 0.0f);
         }
@@ -634,8 +636,10 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
         if (TO_POS) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            s_perm[a.rht.pinv[j]][0][threadIdx.x] = y0[j];
-            s_perm[a.rht.pinv[j]][1][threadIdx.x] = y1[j];
+            // row pinv[j] of the table: 2 x 256 floats per row
+            float* dst = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(&s_perm[0][0][threadIdx.x]) + a.rht.perm_off[j]);
+            dst[0] = y0[j];
+            dst[256] = y1[j];
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -1493,7 +1497,10 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 static int fill_rht(RhtParams* r, int n, const int32_t* perm, const int32_t* sign) {
   r->n = n;
   if (n == 0) {
-    for (int i = 0; i < 16; ++i) { r->pinv[i] = (int8_t)i; r->perm[i] = (int8_t)i; r->sign[i] = 1.0f; }
+    for (int i = 0; i < 16; ++i) {
+      r->pinv[i] = (int8_t)i; r->perm[i] = (int8_t)i; r->sign[i] = 1.0f;
+      r->qsign[i] = 0.25f; r->perm_off[i] = i * 2048;
+    }
     return ALTOB200_OK;
   }
   if (n != 16) return ALTOB200_EUNSUPPORTED;
@@ -1509,6 +1516,10 @@ static int fill_rht(RhtParams* r, int n, const int32_t* perm, const int32_t* sig
     r->perm[i] = (int8_t)perm[i];
     r->pinv[perm[i]] = (int8_t)i;
     r->sign[i] = (float)sign[i];
+  }
+  for (int k = 0; k < 16; ++k) {
+    r->qsign[k] = 0.25f * r->sign[k];
+    r->perm_off[k] = (int)r->pinv[k] * 2048;
   }
   return ALTOB200_OK;
 }
