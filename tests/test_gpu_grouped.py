@@ -107,8 +107,6 @@ def test_unsupported_grouped_options_raise():
     x = torch.zeros(128, 64, dtype=torch.bfloat16, device=d)
     B = torch.zeros(1, 64, 64, dtype=torch.bfloat16, device=d)
     offs = torch.tensor([128], dtype=torch.int32, device=d)
-    with pytest.raises(NotImplementedError):   # macro-block scaling with another option
-        G._quantize_then_mxfp_scaled_grouped_mm(x, B, offs, False, True, False, False, False, "static", True)
     with pytest.raises(ValueError):
         G._quantize_then_mxfp_scaled_grouped_mm(x, B, offs, False, True, False, False, False, "bogus", False)
 
@@ -135,7 +133,9 @@ def _per_expert_dense(x, w, dy, offs, dense_fn):
                                   dict(use_dge=True), dict(use_dge=True, use_uos=True, clip_mode="static"),
                                   dict(macro=True), dict(macro=True, use_2dblock_w=False, use_hadamard=True),
                                   dict(use_2dblock_x=True), dict(use_2dblock_x=True, use_uos=True, use_dge=True),
-                                  dict(macro=True, use_2dblock_x=True)])
+                                  dict(macro=True, use_2dblock_x=True),
+                                  dict(macro=True, use_uos=True, clip_mode="static", use_dge=True),
+                                  dict(macro=True, use_2dblock_w=False, use_dge=True)])
 def test_mxfp4_grouped_options_equal_the_dense_function_per_expert(opts):
     """use_uos, clip_mode, use_dge and two-level scaling in the grouped MXFP4 function.  The dense
     function with the same options is pinned to the reference's vectors; every quantisation block of

@@ -119,6 +119,38 @@ def test_two_level_blockwise_linear_matches_oracle(use_2dblock_x, use_2dblock_w,
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("clip_mode,use_uos", [("static", False), ("none", True), ("static", True)])
+def test_two_level_blockwise_linear_with_clip_uos_and_dge(clip_mode, use_uos):
+    """clip_mode / use_uos inside the two-level flow against the oracle, and the DGE factor on top."""
+    from alto_b200 import dge
+    from alto_b200 import mxfp4 as MX
+    M, K, N = 256, 384, 128
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    dy = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    xd, wd = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    y = MX._to_mxfp4_then_scaled_mm(xd, wd, False, True, False, False, clip_mode, False, True, use_uos)
+    y.backward(dy.cuda())
+    yo, dxo, dwo = O.mxfp4_macro_linear(x, w, dy, use_2dblock_x=False, use_2dblock_w=True, clip_mode=clip_mode,
+                                        use_uos=use_uos)
+
+    def rel(a, b):
+        return ((a.float().cpu() - b).norm() / b.norm()).item()
+
+    assert rel(y, yo) <= 1e-2 and rel(xd.grad, dxo) <= 1e-2 and rel(wd.grad, dwo) <= 1e-2
+    # with use_dge the weight gradient is multiplied by the table entry of each weight code (all about 1/5)
+    x2, w2 = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    MX._to_mxfp4_then_scaled_mm(x2, w2, False, True, False, True, clip_mode, False, True, use_uos).backward(dy.cuda())
+    table = torch.tensor(dge.fp4_bin_table(torch.device("cuda"), torch.bfloat16))
+    assert 0.19 < float(table.min()) and float(table.max()) < 0.21
+    nz = wd.grad.float().abs() > 1e-3
+    ratio = (w2.grad.float()[nz] / wd.grad.float()[nz])
+    assert torch.allclose(ratio, torch.full_like(ratio, 0.2), rtol=2e-2)
+    assert torch.equal(x2.grad, xd.grad)
+
+
+@pytest.mark.gpu
 def test_refusals():
     from alto_b200.macro_block_scaling import macro_block_descaling, macro_block_scaling
     x = torch.randn(2, 4, 128, 128, device="cuda")
