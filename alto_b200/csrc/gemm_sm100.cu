@@ -622,11 +622,6 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     float alpha = 1.0f;
     if (args.alpha_a != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_a));
     if (args.alpha_b != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_b));
-    const uint32_t stage_buf = smem_u32(epi) + (uint32_t)(warp - 2) * 8192u;
-    const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;  // this lane's 128-byte row (buffer 0)
-    const uint32_t sw = (uint32_t)(lane & 7);                   // 128-byte swizzle: 16-byte chunk c -> c ^ (row & 7)
-    const int CH = args.out_bf16 ? 64 : 32;                     // output columns per 128-byte row
-    const int n_chunks = BN / CH;
     uint32_t tile_it = 0, store_it = 0;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
       const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);

@@ -991,18 +991,19 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
           word = merge_shifted(fp4_pair<FMT, IN_BF16, ROUND, FAST>(v[2 * j], v[2 * j + 1], s, e4[j], o4[j]), 8 * j, word);
         kw[i] = word;
         if (ok) *reinterpret_cast<uint32_t*>(a.codes_k + (row0 + i) * (a.cols >> 1) + (col0 >> 1)) = kw[i];
-        continue;
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = scale_elem<FMT, IN_BF16, FAST>(v[j], s);
-      if (F::FP4) {
-        kw[i] = e2m1x2_rtn_hw(v[0], v[1]) | (e2m1x2_rtn_hw(v[2], v[3]) << 8) | (e2m1x2_rtn_hw(v[4], v[5]) << 16) |
-                (e2m1x2_rtn_hw(v[6], v[7]) << 24);
-        if (ok) *reinterpret_cast<uint32_t*>(a.codes_k + (row0 + i) * (a.cols >> 1) + (col0 >> 1)) = kw[i];
       } else {
-        kw[2 * i] = fp8x2_rtn_hw<F::E5M2>(v[0], v[1]) | (fp8x2_rtn_hw<F::E5M2>(v[2], v[3]) << 16);
-        kw[2 * i + 1] = fp8x2_rtn_hw<F::E5M2>(v[4], v[5]) | (fp8x2_rtn_hw<F::E5M2>(v[6], v[7]) << 16);
-        if (ok) *reinterpret_cast<uint2*>(a.codes_k + (row0 + i) * a.cols + col0) = make_uint2(kw[2 * i], kw[2 * i + 1]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = scale_elem<FMT, IN_BF16, FAST>(v[j], s);
+        if (F::FP4) {
+          kw[i] = e2m1x2_rtn_hw(v[0], v[1]) | (e2m1x2_rtn_hw(v[2], v[3]) << 8) | (e2m1x2_rtn_hw(v[4], v[5]) << 16) |
+                  (e2m1x2_rtn_hw(v[6], v[7]) << 24);
+          if (ok) *reinterpret_cast<uint32_t*>(a.codes_k + (row0 + i) * (a.cols >> 1) + (col0 >> 1)) = kw[i];
+        } else {
+          kw[2 * i] = fp8x2_rtn_hw<F::E5M2>(v[0], v[1]) | (fp8x2_rtn_hw<F::E5M2>(v[2], v[3]) << 16);
+          kw[2 * i + 1] = fp8x2_rtn_hw<F::E5M2>(v[4], v[5]) | (fp8x2_rtn_hw<F::E5M2>(v[6], v[7]) << 16);
+          if (ok)
+            *reinterpret_cast<uint2*>(a.codes_k + (row0 + i) * a.cols + col0) = make_uint2(kw[2 * i], kw[2 * i + 1]);
+        }
       }
     }
   });

@@ -310,3 +310,30 @@ def test_nvfp4_linear_2d_activation_blocks_with_stochastic_rounding():
     x2, w2 = x.to(d).requires_grad_(True), w.to(d).requires_grad_(True)
     NV._to_nvfp4_then_scaled_mm(x2, w2, True, True, False, use_outer_scale=True).backward(dy.to(d))
     assert not torch.equal(x2.grad, xd.grad)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(4224, 5792, 384), (2176, 2912, 256)])
+def test_gemm_ragged_tiles_over_many_waves(M, N, K, out_dtype):
+    """Output extents that end inside a tile (rows inside a 256-row CTA-pair tile, columns inside a
+    256-column tile and inside a 64-column store unit) with a short K, so that every CTA runs many
+    store-heavy tiles back to back: the shape class in which a skipped store unit once let a staging
+    buffer be refilled under a store in flight.  Checked on the device against an fp32 matmul of the
+    dequantised operands, twice (the failure was a race)."""
+    from alto_b200 import _lib as L
+    ac, asf, adq = _operand(M, K, "nvfp4", 11)
+    bc, bsf, bdq = _operand(N, K, "nvfp4", 12)
+    d = _dev()
+    ref = adq.to(d) @ bdq.to(d).t()
+    if out_dtype == torch.bfloat16:
+        ref = ref.bfloat16().float()
+    args = (ac.to(d), O.pack_scale_bytes(asf).to(d), bc.to(d), O.pack_scale_bytes(bsf).to(d))
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=d)
+        L.gemm_blockscaled(0, 0, M, N, K, *args, out, None, None)
+        assert not torch.isnan(out).any()
+        # fp32: accumulation order only; bf16: at most one unit in the last place of the rounded output
+        diff = (out.float() - ref).abs()
+        tol = 1e-5 * ref.abs().max() if out_dtype == torch.float32 else ref.abs() * 2.0 ** -7 + 1e-30
+        bad = diff > tol
+        assert int(bad.sum()) == 0, f"{int(bad.sum())} entries differ, first at {torch.nonzero(bad)[:4].tolist()}"

@@ -438,3 +438,66 @@ def test_2d_batched_launch_equals_one_launch_per_matrix(fmt):
         q, s = MX.convert_to_mxfp4(x, is_2d_block=True, use_sr=True, rand_bits=_u32dev(r))
         _same(s, so, "batched SR scales")
         _same(q, qo, "batched SR codes")
+
+
+def _sweep_shapes(seed, n, block):
+    """Seeded ragged shapes: rows and columns are multiples of the block, otherwise arbitrary (not
+    multiples of the kernels' 4-row tasks, 64 / 256-row tiles or 512-column chunks)."""
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n):
+        r = int(torch.randint(1, 24, (1,), generator=g)) * block
+        c = int(torch.randint(1, 40, (1,), generator=g)) * block
+        out.append((r, c))
+    return out
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4", "mxfp8"])
+def test_ragged_shape_sweep_all_layouts(fmt):
+    """Every quantizer layout (1-D along the last axis, 1-D along the token axis, 2-D) on a seeded
+    sweep of ragged shapes, round to nearest and (FP4) stochastic rounding from (seed, offset), bit for
+    bit against the oracle.  Covers the tile edges of the row-wise (4 rows x 512 columns per task),
+    column-wise (256 x 64 tiles) and 2-D (64 x 64 / 32 x 128 warp tiles) kernels."""
+    from alto_b200 import mxfp4 as MX, mxfp8 as M8, nvfp4 as NV
+    block = 16 if fmt == "nvfp4" else 32
+    d = _dev()
+    for i, (R, Cc) in enumerate(_sweep_shapes({"nvfp4": 1, "mxfp4": 2, "mxfp8": 3}[fmt], 10, block)):
+        x = reference_data((R, Cc), torch.bfloat16, 500 + i)
+        xd = x.to(d)
+        x_all, xd_all, R_all = x, xd, R
+        for axis, is2d in ((-1, False), (0, False), (-1, True), (0, True)):
+            x, xd, R = x_all, xd_all, R_all
+            if axis == 0 and not is2d and R % 32:
+                # the token-axis quantizer writes 16-byte aligned output rows: 32 tokens per FP4 row
+                if R < 48:
+                    continue
+                R = R - 16
+                x, xd = x_all[:R].contiguous(), xd_all[:R].contiguous()
+            tag = f"{fmt} {R}x{Cc} axis={axis} 2d={is2d}"
+            if fmt == "nvfp4":
+                outer = O.compute_dynamic_outer_scale(x)
+                qo, so = O.quantize_nvfp4(x, 16, axis, is2d, outer)
+                q, s = NV.convert_to_nvfp4(xd, axis=axis, is_2d_block=is2d, outer_scale=outer.to(d),
+                                           update_outer_scale=False)
+            elif fmt == "mxfp4":
+                qo, so = O.quantize_mxfp4(x, 32, axis, is2d)
+                q, s = MX.convert_to_mxfp4(xd, axis=axis, is_2d_block=is2d)
+            else:
+                qo, so = O.quantize_mxfp8(x, 32, "e4m3", axis, is2d)
+                q, s = M8.convert_to_mxfp8(xd, mxfp_format="e4m3", axis=axis, is_2d_block=is2d)
+            _same(s, so, tag + " scales")
+            _same(q, qo, tag + " codes")
+            if fmt == "mxfp8" or (is2d and axis == 0):
+                continue
+            seed, off = 1000 + i, 77 * i
+            vr, vc = (R, Cc) if axis == -1 else (Cc, R)
+            rp = O.reference_sr_planes(seed, off, vr, vc)
+            if fmt == "nvfp4":
+                qo, _ = O.quantize_nvfp4(x, 16, axis, is2d, outer, rp)
+                q, _ = NV.convert_to_nvfp4(xd, axis=axis, is_2d_block=is2d, outer_scale=outer.to(d),
+                                           update_outer_scale=False, use_sr=True, philox_seed=seed, philox_offset=off)
+            else:
+                qo, _ = O.quantize_mxfp4(x, 32, axis, is2d, rp)
+                q, _ = MX.convert_to_mxfp4(xd, axis=axis, is_2d_block=is2d, use_sr=True, philox_seed=seed,
+                                           philox_offset=off)
+            _same(q, qo, tag + " SR codes")
