@@ -2,18 +2,19 @@
 // column-wise with the optional randomised Hadamard transform, 2D with dual packing),
 // tensor amax, dequantizers and the standalone Hadamard transform.
 //
-// Work layout (all kernels are HBM bound; every global access is a full 32-byte sector
-// or better, and every thread keeps one quantisation block or a fixed part of it in
-// registers):
-//   row-wise  : a warp owns 512 contiguous elements of one row, a lane 16 of them
-//               (two 128-bit loads for bf16).  NVFP4 blocks (16) live in one lane, MX
-//               blocks (32) in a lane pair.
-//   col-wise  : a CTA owns a 256-row x 64-column tile; a lane owns two adjacent columns
-//               of one block of rows, so the Hadamard butterfly and the block amax need
-//               no shuffles.  Codes are transposed through shared memory so that every
-//               output row receives 128 contiguous bytes.
-//   2D        : a CTA owns 128 rows x 4 blocks of columns; segment and block maxima go
-//               through shared memory, and the tile is written in both packings.
+// Work layout (every global access is a full 32-byte sector or better, and every thread keeps one
+// quantisation block or a fixed part of it in registers; the counters show all of these kernels
+// bound by instruction issue rather than by HBM):
+//   row-wise  : a warp task is 4 rows x 512 contiguous elements, a lane 16 elements of each row
+//               (two 128-bit loads per row for bf16, all issued first).  NVFP4 blocks (16) live in
+//               one lane, MX blocks (32) in a lane pair.
+//   col-wise  : a CTA owns a 128-row x 64-column tile; a lane owns two adjacent columns of one
+//               block of rows, so the Hadamard butterfly and the block amax need no shuffles.
+//               Codes are transposed through shared memory so that every output row receives 64
+//               (FP4) or 128 (FP8) contiguous bytes.
+//   2D        : a warp owns 4 block columns x 64 (or 32) rows, a thread 16 rows x 8 columns in
+//               registers; block maxima by shuffles, the second packing by an in-register
+//               transpose; no shared memory.
 #include <type_traits>
 
 #include "common.cuh"
@@ -442,7 +443,7 @@ struct RhtParams {
   float sign[16];  // sign applied to slot k after the butterfly
   int64_t row_off[16];  // byte offset of row pinv[k] from the first row of a 16-row group (column passes)
   float qsign[16];      // sign[k] / sqrt(16): the factor applied to slot k
-  int perm_off[16];     // pinv[k] * 2048: byte offset of slot k's row in the shared-memory position table
+  int perm_off[16];     // pinv[k] * 8: byte offset of slot k's row in the shared-memory position table, per thread of the CTA
 };
 
 __device__ __forceinline__ void hadamard16(float* z) {
@@ -478,22 +479,27 @@ struct ColwiseArgs {
   MxOpts mx;
 };
 
-constexpr int COL_TM = 256;  // rows per CTA tile
+// Threads per CTA = rows per CTA tile.  128 rather than 256: more, smaller CTAs per SM (four of the
+// 128-register stochastic-rounding variant instead of two), so that the start-up loads and the
+// barrier of one overlap the arithmetic of the others (measured 5-6 % on the bench's launches).
+constexpr int COL_NT = 128;
 constexpr int COL_TN = 64;   // columns per CTA tile
 
 template <int FMT, bool IN_BF16, int ROUND, bool RHT>
-__global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
+__global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a) {
   using F = Fmt<FMT>;
   constexpr int B = F::B;
+  constexpr int NT = COL_NT;   // threads per CTA
+  constexpr int COL_TM = NT;               // rows per CTA tile
   constexpr int NBLK = COL_TM / B;          // row blocks per tile (16 or 8)
-  constexpr int ITERS = NBLK / 8;           // per warp
+  constexpr int ITERS = NBLK / (NT / 32);   // per warp
   constexpr int ROW_BYTES = F::FP4 ? COL_TM / 2 : COL_TM;  // bytes per output row per tile
   constexpr int BLK_BYTES = F::FP4 ? B / 2 : B;            // bytes per block per column
   // codes staged as [block][column][BLK_BYTES]; scales as [column][NBLK]
   __shared__ __align__(16) uint8_t s_codes[COL_TN * ROW_BYTES];
   __shared__ __align__(16) uint8_t s_sf[COL_TN * NBLK];
   __shared__ float s_sf_plain[Fmt<FMT>::MX ? 1 : COL_TN * NBLK];
-  __shared__ float s_perm[(RHT && ROUND != ALTOB200_ROUND_RTN) ? 16 : 1][2][256];
+  __shared__ float s_perm[(RHT && ROUND != ALTOB200_ROUND_RTN) ? 16 : 1][2][NT];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t m0 = (int64_t)blockIdx.y * COL_TM;
@@ -636,10 +642,11 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
         if (TO_POS) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            // row pinv[j] of the table: 2 x 256 floats per row
-            float* dst = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(&s_perm[0][0][threadIdx.x]) + a.rht.perm_off[j]);
+            // row pinv[j] of the table: 2 x NT floats per row
+            float* dst = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(&s_perm[0][0][threadIdx.x]) +
+                                                  a.rht.perm_off[j] * NT);
             dst[0] = y0[j];
-            dst[256] = y1[j];
+            dst[NT] = y1[j];
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -778,7 +785,7 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
 
   // ---- write codes: output row n gets ROW_BYTES contiguous bytes, 16 bytes per thread ----
   constexpr int CHUNKS = ROW_BYTES / 16;  // 8 (FP4) or 16 (FP8) per output row
-  for (int t = threadIdx.x; t < COL_TN * CHUNKS; t += 256) {
+  for (int t = threadIdx.x; t < COL_TN * CHUNKS; t += NT) {
     const int n = t / CHUNKS, ch = t - n * CHUNKS;
     const int64_t col = n0 + n;
     const int64_t mrow = m0 + (int64_t)ch * (F::FP4 ? 32 : 16);  // first row covered by this chunk
@@ -804,7 +811,7 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
   // ---- write scales ----
   const int64_t nkb = a.rows / B;
   if (a.scale_plain != nullptr) {
-    for (int t = threadIdx.x; t < COL_TN * NBLK; t += 256) {
+    for (int t = threadIdx.x; t < COL_TN * NBLK; t += NT) {
       const int n = t / NBLK, b = t - n * NBLK;
       const int64_t col = n0 + n, kb = m0 / B + b;
       if (col < a.cols && kb < nkb) {
@@ -814,7 +821,7 @@ __global__ void __launch_bounds__(256) quantize_colwise_kernel(ColwiseArgs a) {
     }
   }
   if (a.scale_packed != nullptr) {
-    for (int t = threadIdx.x; t < COL_TN * (NBLK / 4); t += 256) {
+    for (int t = threadIdx.x; t < COL_TN * (NBLK / 4); t += NT) {
       const int n = t / (NBLK / 4), qd = t - n * (NBLK / 4);
       const int64_t col = n0 + n, kb = m0 / B + qd * 4;
       if (col < a.cols && kb < a.ncol_tiles * 4) {
@@ -1500,7 +1507,7 @@ static int fill_rht(RhtParams* r, int n, const int32_t* perm, const int32_t* sig
   if (n == 0) {
     for (int i = 0; i < 16; ++i) {
       r->pinv[i] = (int8_t)i; r->perm[i] = (int8_t)i; r->sign[i] = 1.0f;
-      r->qsign[i] = 0.25f; r->perm_off[i] = i * 2048;
+      r->qsign[i] = 0.25f; r->perm_off[i] = i * 8;
     }
     return ALTOB200_OK;
   }
@@ -1520,7 +1527,7 @@ static int fill_rht(RhtParams* r, int n, const int32_t* perm, const int32_t* sig
   }
   for (int k = 0; k < 16; ++k) {
     r->qsign[k] = 0.25f * r->sign[k];
-    r->perm_off[k] = (int)r->pinv[k] * 2048;
+    r->perm_off[k] = (int)r->pinv[k] * 8;
   }
   return ALTOB200_OK;
 }
@@ -1552,20 +1559,26 @@ static int launch_rowwise(const RowwiseArgs& a, int rounding, cudaStream_t st) {
 
 template <int FMT, bool IN_BF16>
 static int launch_colwise(const ColwiseArgs& a, int rounding, cudaStream_t st) {
-  dim3 grid((unsigned)ceil_div(a.cols, COL_TN), (unsigned)ceil_div(a.rows, COL_TM));
   const bool rht = a.rht.n != 0;
   if (!Fmt<FMT>::FP4 && (rht || rounding != ALTOB200_ROUND_RTN)) return ALTOB200_EUNSUPPORTED;
+  const unsigned gx = (unsigned)ceil_div(a.cols, COL_TN);
   if (rounding == ALTOB200_ROUND_RTN) {
-    if (rht) quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, Fmt<FMT>::FP4><<<grid, 256, 0, st>>>(a);
-    else quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, false><<<grid, 256, 0, st>>>(a);
+    constexpr int NT = COL_NT;
+    const dim3 grid(gx, (unsigned)ceil_div(a.rows, NT));
+    if (rht) quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, Fmt<FMT>::FP4><<<grid, NT, 0, st>>>(a);
+    else quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, false><<<grid, NT, 0, st>>>(a);
   } else if (rounding == ALTOB200_ROUND_SR_BITS) {
     constexpr int R = Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN;
-    if (rht) quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4><<<grid, 256, 0, st>>>(a);
-    else quantize_colwise_kernel<FMT, IN_BF16, R, false><<<grid, 256, 0, st>>>(a);
+    constexpr int NT = COL_NT;
+    const dim3 grid(gx, (unsigned)ceil_div(a.rows, NT));
+    if (rht) quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4><<<grid, NT, 0, st>>>(a);
+    else quantize_colwise_kernel<FMT, IN_BF16, R, false><<<grid, NT, 0, st>>>(a);
   } else if (rounding == ALTOB200_ROUND_SR_PHILOX) {
     constexpr int R = Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_PHILOX : ALTOB200_ROUND_RTN;
-    if (rht) quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4><<<grid, 256, 0, st>>>(a);
-    else quantize_colwise_kernel<FMT, IN_BF16, R, false><<<grid, 256, 0, st>>>(a);
+    constexpr int NT = COL_NT;
+    const dim3 grid(gx, (unsigned)ceil_div(a.rows, NT));
+    if (rht) quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4><<<grid, NT, 0, st>>>(a);
+    else quantize_colwise_kernel<FMT, IN_BF16, R, false><<<grid, NT, 0, st>>>(a);
   } else {
     return ALTOB200_EUNSUPPORTED;
   }
