@@ -876,8 +876,8 @@ __device__ __forceinline__ void transpose4x4_bytes(const uint32_t* in, uint32_t*
 // contiguous bytes per row per warp); for the transposed packing the thread's 16 x 8 codes are
 // transposed in registers (nibble merge of row pairs, then 4 x 4 byte transposes) and every column
 // receives 8 (FP4) or 16 (FP8) contiguous bytes per lane, 32 contiguous bytes per warp and column.
-template <int FMT, bool IN_BF16, int ROUND>
-__global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
+template <int FMT, bool IN_BF16, int ROUND, bool BATCHED>
+__global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
   using F = Fmt<FMT>;
   constexpr int B = F::B;
   constexpr int LC = B / 2;          // lanes across columns: 8 columns each, 4 block columns per warp
@@ -885,31 +885,22 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
   constexpr int TR = 16 * LR, TC = 8 * LC;  // warp tile: 64 x 64 or 32 x 128
   constexpr int ESZ = IN_BF16 ? 2 : 4;
   const int lane = threadIdx.x & 31;
-  const int64_t tiles_c = (a_in.cols + TC - 1) / TC, tiles_r = (a_in.rows + TR - 1) / TR;
+  const int64_t tiles_c = (a.cols + TC - 1) / TC, tiles_r = (a.rows + TR - 1) / TR;
   const int64_t tile_all = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (tile_all >= tiles_c * tiles_r * a_in.batch) return;  // whole warps leave; nothing below synchronises the block
-  int64_t bi, tile;
-  divmod_fast(tile_all, tiles_c * tiles_r, &bi, &tile);
-  // this matrix of the batch: every pointer moved to its slice, the rest of the kernel sees one matrix
-  Quant2dArgs a = a_in;
-  {
-    const int64_t code_bytes = a.rows * (F::FP4 ? (a.cols >> 1) : a.cols);
-    a.w = reinterpret_cast<const uint8_t*>(a_in.w) + bi * a.batch_stride * ESZ;
-    a.codes_k = a_in.codes_k + bi * code_bytes;
-    if (a.codes_t != nullptr) a.codes_t = a_in.codes_t + bi * code_bytes;
-    if (a.scale_plain != nullptr)
-      a.scale_plain = reinterpret_cast<uint8_t*>(a_in.scale_plain) + bi * (a.rows / B) * (a.cols / B) * (F::MX ? 1 : 4);
-    if (a.packed_k != nullptr) a.packed_k = a_in.packed_k + bi * a.packed_k_bytes;
-    if (a.packed_t != nullptr) a.packed_t = a_in.packed_t + bi * a.packed_t_bytes;
-  }
-  const int64_t sr_row_base = bi * a.rows;
+  if (tile_all >= tiles_c * tiles_r * a.batch) return;  // whole warps leave; nothing below synchronises the block
+  // matrix `bi` of the batch: its outputs follow those of matrix bi - 1, so the batch index enters the
+  // addresses as extra rows (bi * rows for the K packing, bi * cols for the transposed one)
+  // (BATCHED is a template parameter so that the single-matrix kernel carries none of this arithmetic)
+  int64_t bi = 0, tile = tile_all;
+  if (BATCHED) divmod_fast(tile_all, tiles_c * tiles_r, &bi, &tile);
+  const int64_t rows_before = BATCHED ? bi * a.rows : 0, cols_before = BATCHED ? bi * a.cols : 0;
   int64_t tr, tc;
   divmod_fast(tile, tiles_c, &tr, &tc);
   const int lc = lane % LC, lr = lane / LC;
   const int64_t row0 = tr * TR + lr * 16, col0 = tc * TC + lc * 8;
   const bool ok = row0 < a.rows && col0 < a.cols;  // rows % B == 0 and cols % B == 0
   const OuterScale os = make_outer_scale((!F::MX) && a.outer != nullptr, a.outer);
-  const uint8_t* src = reinterpret_cast<const uint8_t*>(a.w) + (row0 * a.ld + col0) * ESZ;
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(a.w) + (bi * a.batch_stride + row0 * a.ld + col0) * ESZ;
   const int64_t pitch = a.ld * ESZ;
 
   // ---- load and block maximum ----
@@ -981,7 +972,7 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
       if (F::FP4 && ROUND == ALTOB200_ROUND_SR_BITS) {
         // the lane's 4 column pairs are 4 consecutive, 16-byte aligned words of each plane
         const bool tiled = a.tile_rows != 0;
-        const int64_t row = sr_row_base + row0 + i;  // row of the flattened view over the batch
+        const int64_t row = rows_before + row0 + i;  // row of the flattened view over the batch
         const int64_t rr = tiled ? (int64_t)((uint64_t)row % (uint64_t)a.tile_rows) : row;
         const int64_t pp = tiled ? (int64_t)((uint32_t)(col0 >> 1) % (uint32_t)a.tile_pairs) : (col0 >> 1);
         const int64_t pitch = tiled ? a.tile_pairs : (a.cols >> 1);
@@ -997,19 +988,19 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
         for (int j = 0; j < 4; ++j)
           word = merge_shifted(fp4_pair<FMT, IN_BF16, ROUND, FAST>(v[2 * j], v[2 * j + 1], s, e4[j], o4[j]), 8 * j, word);
         kw[i] = word;
-        if (ok) *reinterpret_cast<uint32_t*>(a.codes_k + (row0 + i) * (a.cols >> 1) + (col0 >> 1)) = kw[i];
+        if (ok) *reinterpret_cast<uint32_t*>(a.codes_k + (rows_before + row0 + i) * (a.cols >> 1) + (col0 >> 1)) = kw[i];
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = scale_elem<FMT, IN_BF16, FAST>(v[j], s);
         if (F::FP4) {
           kw[i] = e2m1x2_rtn_hw(v[0], v[1]) | (e2m1x2_rtn_hw(v[2], v[3]) << 8) | (e2m1x2_rtn_hw(v[4], v[5]) << 16) |
                   (e2m1x2_rtn_hw(v[6], v[7]) << 24);
-          if (ok) *reinterpret_cast<uint32_t*>(a.codes_k + (row0 + i) * (a.cols >> 1) + (col0 >> 1)) = kw[i];
+          if (ok) *reinterpret_cast<uint32_t*>(a.codes_k + (rows_before + row0 + i) * (a.cols >> 1) + (col0 >> 1)) = kw[i];
         } else {
           kw[2 * i] = fp8x2_rtn_hw<F::E5M2>(v[0], v[1]) | (fp8x2_rtn_hw<F::E5M2>(v[2], v[3]) << 16);
           kw[2 * i + 1] = fp8x2_rtn_hw<F::E5M2>(v[4], v[5]) | (fp8x2_rtn_hw<F::E5M2>(v[6], v[7]) << 16);
           if (ok)
-            *reinterpret_cast<uint2*>(a.codes_k + (row0 + i) * a.cols + col0) = make_uint2(kw[2 * i], kw[2 * i + 1]);
+            *reinterpret_cast<uint2*>(a.codes_k + (rows_before + row0 + i) * a.cols + col0) = make_uint2(kw[2 * i], kw[2 * i + 1]);
         }
       }
     }
@@ -1032,7 +1023,7 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
       transpose4x4_bytes(od, o0);
       transpose4x4_bytes(od + 4, o1);
       if (ok) {
-        uint8_t* dst = a.codes_t + col0 * (a.rows >> 1) + (row0 >> 1);
+        uint8_t* dst = a.codes_t + (cols_before + col0) * (a.rows >> 1) + (row0 >> 1);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           *reinterpret_cast<uint2*>(dst + (2 * b) * (a.rows >> 1)) = make_uint2(e0[b], e1[b]);
@@ -1053,7 +1044,7 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
         if (ok) {
 #pragma unroll
           for (int b = 0; b < 4; ++b)
-            *reinterpret_cast<uint4*>(a.codes_t + (col0 + 4 * h + b) * a.rows + row0) =
+            *reinterpret_cast<uint4*>(a.codes_t + (cols_before + col0 + 4 * h + b) * a.rows + row0) =
                 make_uint4(t[0][b], t[1][b], t[2][b], t[3][b]);
         }
       }
@@ -1063,7 +1054,7 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
   // ---- scales ----
   const bool col_ok = col0 < a.cols, row_ok = row0 < a.rows;
   if (a.scale_plain != nullptr && ok && (lc % (B / 8)) == 0 && (lr % (B / 16)) == 0) {
-    const int64_t idx = (row0 / B) * (a.cols / B) + col0 / B;
+    const int64_t idx = ((rows_before + row0) / B) * (a.cols / B) + col0 / B;
     if (F::MX) reinterpret_cast<uint8_t*>(a.scale_plain)[idx] = (uint8_t)s.byte;
     else reinterpret_cast<float*>(a.scale_plain)[idx] = s.plain;
   }
@@ -1079,7 +1070,7 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
 #pragma unroll
       for (int i = 0; i < 16 / LC; ++i) {
         const int64_t row = row0 + lc * (16 / LC) + i;
-        *reinterpret_cast<uint32_t*>(a.packed_k + packed_scale_offset(row, kb, a.nct_k)) = word;
+        *reinterpret_cast<uint32_t*>(a.packed_k + bi * a.packed_k_bytes + packed_scale_offset(row, kb, a.nct_k)) = word;
       }
     }
   }
@@ -1094,14 +1085,15 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a_in) {
       if (col_ok) {
 #pragma unroll
         for (int e = 0; e < 2; ++e)
-          *reinterpret_cast<uint32_t*>(a.packed_t + packed_scale_offset(col0 + 2 * lr + e, tr * 4, a.nct_t)) = word;
+          *reinterpret_cast<uint32_t*>(a.packed_t + bi * a.packed_t_bytes +
+                                       packed_scale_offset(col0 + 2 * lr + e, tr * 4, a.nct_t)) = word;
       }
     } else {
       // B = 32: the warp holds one row block, one byte per column
       if (ok) {
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          a.packed_t[packed_scale_offset(col0 + 4 * lr + e, tr, a.nct_t)] = (uint8_t)s.byte;
+          a.packed_t[bi * a.packed_t_bytes + packed_scale_offset(col0 + 4 * lr + e, tr, a.nct_t)] = (uint8_t)s.byte;
       }
     }
   }
@@ -1591,12 +1583,17 @@ static int launch_2d(const Quant2dArgs& a, int rounding, cudaStream_t st) {
   constexpr int TC = 4 * Fmt<FMT>::B, TR = 1024 / Fmt<FMT>::B;
   const int64_t tiles = ceil_div(a.cols, TC) * ceil_div(a.rows, TR) * a.batch;
   const unsigned blocks = (unsigned)ceil_div(tiles, 8);
-  if (rounding == ALTOB200_ROUND_RTN)
-    quantize_2d_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN><<<blocks, 256, 0, st>>>(a);
-  else if (rounding == ALTOB200_ROUND_SR_BITS && Fmt<FMT>::FP4)
-    quantize_2d_kernel<FMT, IN_BF16, Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN><<<blocks, 256, 0, st>>>(a);
-  else
+  constexpr int SR = Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN;
+  const bool batched = a.batch > 1;
+  if (rounding == ALTOB200_ROUND_RTN) {
+    if (batched) quantize_2d_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, true><<<blocks, 256, 0, st>>>(a);
+    else quantize_2d_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, false><<<blocks, 256, 0, st>>>(a);
+  } else if (rounding == ALTOB200_ROUND_SR_BITS && Fmt<FMT>::FP4) {
+    if (batched) quantize_2d_kernel<FMT, IN_BF16, SR, true><<<blocks, 256, 0, st>>>(a);
+    else quantize_2d_kernel<FMT, IN_BF16, SR, false><<<blocks, 256, 0, st>>>(a);
+  } else {
     return ALTOB200_EUNSUPPORTED;
+  }
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 
