@@ -54,7 +54,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes (read + write) per GEMM launch at the default shape, from the one-pass ncu capture
 # summarised under profiles/: (123.0+193.6 + 85.0+81.6 + 127.3+47.6) MB / 3.  Part of each output is
 # still in the write-back L2 when the kernel ends; part of each input is found there.
-GEMM_DRAM_BYTES_PER_LAUNCH = 216.5e6
+GEMM_DRAM_BYTES_PER_LAUNCH = 215.3e6
 # codes + packed scales of both operands + bf16 output, mean of fprop / wgrad / dgrad
 GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (52.0e6 + 234.9e6 + 84.9e6 + 117.4e6 + 99.1e6 + 67.1e6) / 3
 CPU_SAMPLE_ROWS = 2048     # token rows of the CPU sample
