@@ -1,9 +1,10 @@
 """GPU tests of the multi-GPU forms of the path.
 
 One GPU: the row-gather kernel, and the expert-parallel dispatcher with a single rank feeding the
-grouped GEMMs.  Two GPUs (skipped when fewer are visible): two NCCL ranks as child processes --
-the column-sharded MXFP8 linear (dgrad all-reduce) and the expert-parallel MoE (two all-to-alls
-each way) against single-GPU runs of the same kernels.  NVLS is switched off in the children: a
+grouped GEMMs.  Two, four and eight GPUs (each skipped when fewer are visible): that many NCCL
+ranks as child processes -- the column-sharded MXFP8 linear (dgrad all-reduce), the expert-parallel
+MoE (two all-to-alls each way) and the fully sharded NVFP4 weight (quantised all-gather, dW
+reduce-scatter) against single-GPU runs of the same kernels.  NVLS is switched off in the children: a
 rank that dies while bound to an NVLink multicast object can fault its peers."""
 import os
 import socket
@@ -96,7 +97,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _two_rank_worker(rank, world, port):
+def _nccl_rank_worker(rank, world, port):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -108,10 +109,10 @@ def _two_rank_worker(rank, world, port):
         fn = lambda a, b: M8._to_mxfp8_then_scaled_mm(a, b, "e4m3", False, False, True)  # noqa: E731
         # ---- column-sharded MXFP8 linear ----
         g = torch.Generator().manual_seed(5)
+        n = 128                       # output features per rank (whole 32 x 32 weight blocks)
         x = torch.randn(256, 512, generator=g).bfloat16().to(dev).requires_grad_(True)
-        W = (torch.randn(256, 512, generator=g) * 0.05).bfloat16().to(dev)
-        dy = torch.randn(256, 256, generator=g).bfloat16().to(dev)
-        n = 256 // world
+        W = (torch.randn(n * world, 512, generator=g) * 0.05).bfloat16().to(dev)
+        dy = torch.randn(256, n * world, generator=g).bfloat16().to(dev)
         w_r = D.shard_rows(W).clone().requires_grad_(True)
         y_r = D.column_sharded_linear(x, w_r, fn)
         y_r.backward(dy[:, rank * n:(rank + 1) * n])
@@ -125,22 +126,23 @@ def _two_rank_worker(rank, world, port):
             partial.append(xs.grad)
             if r == rank:
                 assert torch.equal(ys, y_r) and torch.equal(ws.grad, w_r.grad)
-        want = (partial[0].float() + partial[1].float())
+        want = torch.stack([p_.float() for p_ in partial]).sum(0)
         assert torch.allclose(x.grad.float(), want, rtol=2e-2, atol=1e-2 * want.abs().max().item())
         # ---- expert-parallel MoE: every rank has its own tokens ----
         import tests.test_gpu_distributed as T_
-        xt, ids, scores, W13, W2 = T_._moe_inputs(10 + rank, 384, 256, 384, 4, 2, dev)
+        E = max(4, world)
+        xt, ids, scores, W13, W2 = T_._moe_inputs(10 + rank, 384, 256, 384, E, 2, dev)
         xt.requires_grad_(True)
-        E_local = 4 // world
-        ep = D.ExpertParallelDispatcher(4)
+        E_local = E // world
+        ep = D.ExpertParallelDispatcher(E)
         out = T_._moe(xt, ids, scores, W13[rank * E_local:(rank + 1) * E_local],
                       W2[rank * E_local:(rank + 1) * E_local], ep)
         out.float().sum().backward()
-        # the same tokens through all four experts on this GPU alone: forward and the token gradient
+        # the same tokens through all the experts on this GPU alone: forward and the token gradient
         # are row-local (row-wise MXFP8 blocks), hence bit-identical
         x1 = xt.detach().clone().requires_grad_(True)
         one = D.ExpertParallelDispatcher.__new__(D.ExpertParallelDispatcher)
-        one.group, one.world, one.rank, one.num_experts, one.local_experts, one.align = None, 1, 0, 4, 4, 128
+        one.group, one.world, one.rank, one.num_experts, one.local_experts, one.align = None, 1, 0, E, E, 128
         out1 = T_._moe(x1, ids, scores, W13, W2, one)
         out1.float().sum().backward()
         assert torch.equal(out, out1)
@@ -151,8 +153,9 @@ def _two_rank_worker(rank, world, port):
         had = NV.HadamardFactory.create_transform(device=dev)
         g = torch.Generator().manual_seed(9)
         xf = torch.randn(256, 512, generator=g).bfloat16().to(dev)
-        Wf = (torch.randn(512, 512, generator=g) * 0.05).bfloat16().to(dev)
-        dyf = (torch.randn(256, 512, generator=g) * 1e-2).bfloat16().to(dev)
+        nw = max(512 // world, 128)   # weight rows per rank (multiples of 128)
+        Wf = (torch.randn(nw * world, 512, generator=g) * 0.05).bfloat16().to(dev)
+        dyf = (torch.randn(256, nw * world, generator=g) * 1e-2).bfloat16().to(dev)
         xs, ws = xf.clone().requires_grad_(True), D.shard_rows(Wf, multiple=128).clone().requires_grad_(True)
         ys = D.gathered_weight_linear(xs, ws, "nvfp4", use_outer_scale=True, hadamard_transform=had)
         ys.backward(dyf)
@@ -160,23 +163,30 @@ def _two_rank_worker(rank, world, port):
         NV.HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)  # same matrix
         y1 = NV._to_nvfp4_then_scaled_mm(x1, w1, False, True, False, use_outer_scale=True, use_hadamard=True)
         y1.backward(dyf)
-        nw = 512 // world
         assert torch.equal(ys, y1) and torch.equal(xs.grad, x1.grad)
-        # both ranks ran the same batch: the reduce-scattered gradient is world x the single-GPU rows
-        assert torch.equal(ws.grad, (w1.grad[rank * nw:(rank + 1) * nw].float() * world).bfloat16())
+        # every rank ran the same batch: the reduce-scattered gradient is world x the single-GPU rows
+        # (bit for bit on two ranks; with more, the bf16 partial sums 3g, 5g, ... of the reduction round)
+        want_w = w1.grad[rank * nw:(rank + 1) * nw].float() * world
+        if world == 2:
+            assert torch.equal(ws.grad, want_w.bfloat16())
+        else:
+            assert torch.allclose(ws.grad.float(), want_w, rtol=2e-2, atol=0.0)
         # ---- bucketed gradient all-reduce ----
         p = torch.nn.Parameter(torch.zeros(1000, device=dev))
         p.grad = torch.full_like(p, float(rank))
-        assert D.allreduce_gradients([p]) == 1 and torch.allclose(p.grad, torch.full_like(p, 0.5))
+        assert D.allreduce_gradients([p]) == 1
+        assert torch.allclose(p.grad, torch.full_like(p, (world - 1) / 2.0))
         torch.cuda.synchronize()
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_nccl_column_sharded_and_expert_parallel():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_nccl_ranks_column_sharded_expert_parallel_and_sharded_weight(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_two_rank_worker, args=(2, _free_port()), nprocs=2, join=True)
+    mp.spawn(_nccl_rank_worker, args=(world, _free_port()), nprocs=world, join=True)
 
 
 @pytest.mark.parametrize("precision,kw", [("nvfp4", dict(use_outer_scale=True)), ("nvfp4", dict()), ("mxfp4", dict()),
