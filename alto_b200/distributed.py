@@ -270,16 +270,22 @@ def gathered_weight_linear(x: torch.Tensor, w_shard: torch.Tensor, precision: st
 # ------------------------------------------------------------------------------------------
 # expert parallel: dispatch / combine
 # ------------------------------------------------------------------------------------------
-def permute_pad_plan(recv_counts: torch.Tensor, align: int = ALIGN_SIZE_M):
+def permute_pad_plan(recv_counts: torch.Tensor, align: int = ALIGN_SIZE_M, total: Optional[int] = None,
+                     m_pad: Optional[int] = None):
     """Row plan of the local re-sort after the dispatch all-to-all.
 
-    ``recv_counts`` (CPU int64 [sources, local_experts]): rows received from each source rank for
-    each local expert; the receive buffer holds them source-major, expert-minor.  Returns CPU
-    tensors ``(index, inverse, offs)``: ``index`` int32 [M_pad] gives for every row of the
-    expert-major, padded layout its row in the receive buffer (-1 = padding row); ``inverse``
+    ``recv_counts`` (int64 [sources, local_experts], on any device): rows received from each source
+    rank for each local expert; the receive buffer holds them source-major, expert-minor.  Returns
+    tensors on the same device ``(index, inverse, offs)``: ``index`` int32 [M_pad] gives for every row
+    of the expert-major, padded layout its row in the receive buffer (-1 = padding row); ``inverse``
     int32 [rows_received] is the opposite map; ``offs`` int32 [local_experts] are the cumulative
-    padded row counts the grouped GEMMs take (every count a multiple of ``align``)."""
+    padded row counts the grouped GEMMs take (every count a multiple of ``align``).
+
+    ``total`` (rows received) and ``m_pad`` (padded rows, ``offs[-1]``) are read back from the counts
+    when not given; a caller that has the counts on the host passes both, so that a plan built on
+    the GPU needs no synchronisation of its own."""
     c = recv_counts.to(torch.int64)
+    dev = c.device
     S, E = c.shape
     per_expert = c.sum(0)
     padded = (per_expert + align - 1) // align * align
@@ -288,17 +294,20 @@ def permute_pad_plan(recv_counts: torch.Tensor, align: int = ALIGN_SIZE_M):
     recv_start = (torch.cumsum(c.reshape(-1), 0) - c.reshape(-1)).reshape(S, E)
     within = torch.cumsum(c, 0) - c                             # rows of expert e from earlier sources
     dst_start = pad_start.unsqueeze(0) + within                 # [S, E]
-    total = int(c.sum())
-    m_pad = int(offs[-1]) if E > 0 else 0
-    index = torch.full((m_pad,), -1, dtype=torch.int32)
-    inverse = torch.empty(total, dtype=torch.int32)
+    if total is None:
+        total = int(c.sum())
+    if m_pad is None:
+        m_pad = int(offs[-1]) if E > 0 else 0
+    index = torch.full((m_pad,), -1, dtype=torch.int32, device=dev)
+    inverse = torch.empty(total, dtype=torch.int32, device=dev)
     if total > 0:
         counts = c.reshape(-1)
-        block = torch.repeat_interleave(torch.arange(S * E), counts)          # block id of every received row
-        pos = torch.arange(total) - recv_start.reshape(-1)[block]             # position inside its block
+        block = torch.repeat_interleave(torch.arange(S * E, device=dev), counts,
+                                        output_size=total)                    # block id of every received row
+        pos = torch.arange(total, device=dev) - recv_start.reshape(-1)[block]  # position inside its block
         dst = dst_start.reshape(-1)[block] + pos
         inverse.copy_(dst.to(torch.int32))
-        index[dst] = torch.arange(total, dtype=torch.int32)
+        index[dst] = torch.arange(total, dtype=torch.int32, device=dev)
     return index, inverse, offs.to(torch.int32)
 
 
@@ -352,7 +361,7 @@ class _AllToAllRows(torch.autograd.Function):
 
 
 class _DispatchState:
-    __slots__ = ("k", "tokens", "inv_order", "in_splits", "out_splits", "index", "inverse", "offs")
+    __slots__ = ("k", "tokens", "inv_order", "order", "in_splits", "out_splits", "index", "inverse", "offs")
 
 
 class ExpertParallelDispatcher:
@@ -396,14 +405,19 @@ class ExpertParallelDispatcher:
             dist.all_to_all_single(recv, send.contiguous(), group=self.group)
         else:
             recv = send
-        send_h, recv_h = send.cpu(), recv.cpu()                              # the one host synchronisation
+        both = torch.stack((send, recv)).cpu()                               # the one host synchronisation
+        send_h, recv_h = both[0], both[1]
         st = _DispatchState()
         st.k, st.tokens = k, T
         st.inv_order = inv_order.to(torch.int32)
+        st.order = order.to(torch.int32)
         st.in_splits = [int(v) for v in send_h.sum(1)]
         st.out_splits = [int(v) for v in recv_h.sum(1)]
-        index, inverse, offs = permute_pad_plan(recv_h, self.align)
-        st.index, st.inverse, st.offs = index.to(dev), inverse.to(dev), offs.to(dev)
+        # The row plan is built on the GPU from the device copy of the counts; the host copy only
+        # sizes its buffers (and the all-to-all), so the host is free to run ahead again at once.
+        per_expert = recv_h.sum(0)
+        m_pad = int(((per_expert + self.align - 1) // self.align * self.align).sum())
+        st.index, st.inverse, st.offs = permute_pad_plan(recv, self.align, total=sum(st.out_splits), m_pad=m_pad)
         token_of_sorted = torch.div(order, k, rounding_mode="floor").to(torch.int32)
         rows = _ReplicateSorted.apply(x, token_of_sorted, st.inv_order, k)
         if self.world > 1:
@@ -415,9 +429,8 @@ class ExpertParallelDispatcher:
         rows = _GatherRows.apply(y_local, state.inverse, state.index)
         if self.world > 1:
             rows = _AllToAllRows.apply(rows, state.in_splits, state.out_splits, self.group)
-        # back to routed-row order (token-major, k minor): a permutation, so its own inverse map
-        order = torch.argsort(state.inv_order.to(torch.int64)).to(torch.int32)
-        routed = _GatherRows.apply(rows, state.inv_order, order)
+        # back to routed-row order (token-major, k minor): the inverse of the dispatch's sort
+        routed = _GatherRows.apply(rows, state.inv_order, state.order)
         routed = routed.view(state.tokens, state.k, routed.shape[-1])
         if scores is not None:
             routed = routed * scores.to(routed.dtype).unsqueeze(-1)

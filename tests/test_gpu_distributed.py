@@ -215,3 +215,121 @@ def test_gathered_weight_linear_single_rank_equals_the_plain_linear(precision, k
     assert torch.equal(ya, yb) and torch.equal(xa.grad, xb.grad) and torch.equal(wa.grad, wb.grad)
     with pytest.raises(RuntimeError, match="multiple"):
         D.gathered_weight_linear(x, W[:96], precision, **kw)
+
+
+# ---------------------------------------------------------------------------------------------
+# The two sharded benchmark configurations at their full sizes on 1, 2, 4 and 8 ranks
+# ---------------------------------------------------------------------------------------------
+def _swiglu_moe(x, ids, scores, W13, W2, dispatcher, gmm):
+    """Routed experts with the gate and up projections fused in W13 [E, 2H, D] and W2 [E, D, H]."""
+    xl, offs, st = dispatcher.dispatch(x, ids)
+    h = gmm(xl, W13.transpose(-2, -1), offs)
+    H = h.shape[-1] // 2
+    y = gmm(torch.nn.functional.silu(h[:, :H]) * h[:, H:], W2.transpose(-2, -1), offs)
+    return dispatcher.combine(y, st, scores)
+
+
+def _full_size_worker(rank, world, port):
+    """MXFP4 MoE (32 experts, top-4, hidden = intermediate = 2880, 16384 tokens in total, experts and
+    tokens split over the ranks) and the column-sharded MXFP8 linear (X [8192, 4096], W [4096, 4096]
+    split by output features): forward of this rank's tokens against all experts on this GPU alone,
+    finite gradients, and the step times (CUDA events, slowest rank)."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from alto_b200 import distributed as D
+        from alto_b200 import mxfp8 as M8
+        from alto_b200.grouped import _quantize_then_mxfp_scaled_grouped_mm as mx4
+        from alto_b200.hadamard import HadamardFactory
+        HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)
+
+        def gmm(A, B, offs):  # 1-D activation blocks, 2-D weight blocks, RHT on wgrad operands, SR on gradients
+            return mx4(A, B, offs, False, True, True, False, True, "none", False)
+
+        def step_time(fn, reps=5):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+
+        # ---- expert-parallel MoE ----
+        T, Dm, E, k = 16384, 2880, 32, 4
+        g = torch.Generator(device=dev).manual_seed(0)
+        logits = torch.randn(T, E, generator=g, device=dev)
+        x_all = torch.randn(T, Dm, generator=g, device=dev).bfloat16()
+        W13 = (torch.randn(E, 2 * Dm, Dm, generator=g, device=dev) * 0.02).bfloat16()
+        W2 = (torch.randn(E, Dm, Dm, generator=g, device=dev) * 0.02).bfloat16()
+        scores_all, ids_all = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+        n, El = T // world, E // world
+        x = x_all[rank * n:(rank + 1) * n].clone().requires_grad_(True)
+        ids, scores = ids_all[rank * n:(rank + 1) * n], scores_all[rank * n:(rank + 1) * n].bfloat16()
+        w13 = W13[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+        w2 = W2[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+        ep = D.ExpertParallelDispatcher(E)
+        out = _swiglu_moe(x, ids, scores, w13, w2, ep, gmm)
+        out.backward(torch.ones_like(out) * 1e-3)
+        assert torch.isfinite(out).all() and torch.isfinite(x.grad).all()
+        assert torch.isfinite(w13.grad).all() and torch.isfinite(w2.grad).all()
+        if world > 1:
+            # this rank's tokens through all 32 experts on this GPU alone: the forward is row-local
+            one = D.ExpertParallelDispatcher.__new__(D.ExpertParallelDispatcher)
+            one.group, one.world, one.rank, one.num_experts, one.local_experts, one.align = None, 1, 0, E, E, 128
+            with torch.no_grad():
+                assert torch.equal(out, _swiglu_moe(x.detach(), ids, scores, W13, W2, one, gmm))
+        del W13, W2, x_all
+
+        def moe_step():
+            x.grad = w13.grad = w2.grad = None
+            _swiglu_moe(x, ids, scores, w13, w2, ep, gmm).backward(torch.ones_like(out) * 1e-3)
+
+        t_moe = step_time(moe_step)
+        routed = T * k
+        flop_moe = 3 * 2 * routed * (2 * Dm * Dm + Dm * Dm)
+        # ---- column-sharded MXFP8 linear ----
+        fn = lambda a, b: M8._to_mxfp8_then_scaled_mm(a, b, "e4m3", False, False, True)  # noqa: E731
+        g = torch.Generator(device=dev).manual_seed(1)
+        xs = torch.randn(8192, 4096, generator=g, device=dev).bfloat16().requires_grad_(True)
+        W = (torch.randn(4096, 4096, generator=g, device=dev) * 0.02).bfloat16()
+        dy = (torch.randn(8192, 4096, generator=g, device=dev) * 1e-3).bfloat16()
+        nw = 4096 // world
+        ws = D.shard_rows(W).clone().requires_grad_(True)
+        dys = dy[:, rank * nw:(rank + 1) * nw].contiguous()
+        ys = D.column_sharded_linear(xs, ws, fn)
+        ys.backward(dys)
+        with torch.no_grad():
+            assert torch.equal(ys, fn(xs.detach(), W[rank * nw:(rank + 1) * nw]))
+        assert torch.isfinite(xs.grad).all() and torch.isfinite(ws.grad).all()
+
+        def lin_step():
+            xs.grad = ws.grad = None
+            D.column_sharded_linear(xs, ws, fn).backward(dys)
+
+        t_lin = step_time(lin_step)
+        if rank == 0:
+            print(f"\n[{world} rank(s)] MXFP4 MoE 32 experts top-4, 16384 tokens, fwd+dgrad+wgrad incl. dispatch/combine: "
+                  f"{t_moe:.2f} ms = {flop_moe / t_moe / 1e9:.0f} TFLOP/s whole job; "
+                  f"column-sharded MXFP8 linear 8192 x 4096 x 4096 fwd+dgrad+wgrad incl. dX all-reduce: "
+                  f"{t_lin:.3f} ms = {3 * 2 * 8192 * 4096 * 4096 / t_lin / 1e9:.0f} TFLOP/s whole job", flush=True)
+        torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_full_size_expert_parallel_moe_and_column_sharded_linear(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_full_size_worker, args=(world, _free_port()), nprocs=world, join=True)
