@@ -288,3 +288,66 @@ def _quantize_then_mxfp8_scaled_grouped_mm(A, B, offs, *, use_2dblock_x: bool = 
         raise NotImplementedError("MXFP8 stochastic rounding exists only as gfx950 instructions in the reference")
     return GroupedLinearFunction.apply(A, B.transpose(-2, -1), offs, _FP8[fwd_format], _FP8[bwd_grad_format],
                                        use_2dblock_x, use_2dblock_w, False, False, None)
+
+
+# ---------------------------------------------------------------------------------------------
+# Forward grouped GEMMs on operands that are already quantised
+# ---------------------------------------------------------------------------------------------
+def _grouped_forward_prequantized(fmt_a: int, fmt_b: int, inputs, expert_weights, expert_indices, input_scales,
+                                  weight_scales, trans_weights: bool, use_2dblock_x: bool, use_2dblock_w: bool,
+                                  output_dtype: torch.dtype) -> torch.Tensor:
+    """Y[m] = X[m] W[expert(m)]^T over quantised operands with plain (reference-layout) block scales.
+
+    ``inputs`` [M_buf, K] codes (FP4: two per byte along K) with scales [M_buf, K/32] (or
+    [M_buf/32, K/32] for 2-D blocks); ``expert_weights`` [E, N, K] codes (``trans_weights``) or the
+    [E, K, N] view of such a tensor, with scales [E, N, K/32] (or [E, N/32, K/32]); ``expert_indices``
+    [M_total] gives every row's expert, constant over groups of 128 rows.  Rows from M_total on are zero."""
+    torch._check(inputs.dim() == 2 and expert_weights.dim() == 3, lambda: "inputs must be 2-D, expert_weights 3-D")
+    m_buf = inputs.shape[0]
+    m_total = expert_indices.numel()
+    torch._check(m_total > 0)
+    torch._check(m_total % ALIGN_SIZE_M == 0,
+                 lambda: f"M_total ({m_total}) must be a multiple of group_size_m ({ALIGN_SIZE_M})")
+    torch._check(m_buf >= m_total, lambda: f"M_bufferlen ({m_buf}) must be >= M_total ({m_total})")
+    w = expert_weights if trans_weights else expert_weights.transpose(-2, -1)     # [E, N, K codes]
+    ws = weight_scales if trans_weights else weight_scales.transpose(-2, -1)      # [E, N or N/32, K/32]
+    n_exp, N, kc = w.shape
+    torch._check(inputs.shape[1] == kc, lambda: f"Input K ({inputs.shape[1]}) must match weight K ({kc})")
+    K = kc * 2 if L.is_fp4(fmt_a) else kc
+    block = L.block_of(fmt_a)
+    a_codes = E.as_2d_rows(inputs.view(torch.uint8))
+    b_codes = w.contiguous().view(torch.uint8).reshape(n_exp * N, kc)
+    sa = E.pack_plain_scales(input_scales, m_buf, use_2dblock_x, block)
+    sb = torch.cat([E.pack_plain_scales(ws[e], N, use_2dblock_w, block) for e in range(n_exp)])
+    n_groups = (m_buf + ALIGN_SIZE_M - 1) // ALIGN_SIZE_M
+    group_expert = torch.full((n_groups,), -1, dtype=torch.int32, device=inputs.device)
+    group_expert[:m_total // ALIGN_SIZE_M] = expert_indices.to(torch.int32)[::ALIGN_SIZE_M]
+    out = torch.empty(m_buf, N, dtype=output_dtype, device=inputs.device)
+    L.grouped_gemm_blockscaled(fmt_a, fmt_b, m_buf, N, K, n_exp, a_codes, sa, b_codes, sb, group_expert, out)
+    return out
+
+
+def mxfp4_grouped_gemm_forward(inputs, expert_weights, expert_indices, input_scales, weight_scales,
+                               trans_weights: bool = True, use_2dblock_x: bool = False, use_2dblock_w: bool = True,
+                               output_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """The reference's ``torch.ops.torchtitan.mxfp4_grouped_gemm_forward``
+    (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_forward.py:200-311) on the block-scaled tensor cores."""
+    return _grouped_forward_prequantized(L.FMT_MXFP4, L.FMT_MXFP4, inputs, expert_weights, expert_indices,
+                                         input_scales, weight_scales, trans_weights, use_2dblock_x, use_2dblock_w,
+                                         output_dtype)
+
+
+def mxfp8_grouped_gemm_forward(inputs, expert_weights, expert_indices, input_scales, weight_scales,
+                               trans_weights: bool = True, use_2dblock_x: bool = False, use_2dblock_w: bool = True,
+                               lhs_format_id: int = 0, rhs_format_id: int = 0,
+                               output_dtype: torch.dtype = torch.bfloat16,
+                               use_dot_scaled: Optional[bool] = None) -> torch.Tensor:
+    """The reference's ``torch.ops.alto.mxfp8_grouped_gemm_forward``
+    (alto/kernels/mxfp8/mxfp8_grouped_gemm/cg_forward.py:222-330); format ids 0 = e4m3, 1 = e5m2.
+    ``use_dot_scaled`` selects between the reference's two Triton code paths and has no meaning here."""
+    ids = {0: L.FMT_MXFP8_E4M3, 1: L.FMT_MXFP8_E5M2}
+    if lhs_format_id not in ids or rhs_format_id not in ids:
+        raise ValueError(f"Unsupported FP8 format id: {lhs_format_id} / {rhs_format_id}")
+    return _grouped_forward_prequantized(ids[lhs_format_id], ids[rhs_format_id], inputs, expert_weights,
+                                         expert_indices, input_scales, weight_scales, trans_weights, use_2dblock_x,
+                                         use_2dblock_w, output_dtype)

@@ -4,7 +4,12 @@ The reference exposes these as ``torch.library.triton_op`` ops with ``register_f
 -- ``torch.ops.torchtitan.{convert_to_mxfp4, convert_from_mxfp4, blockwise_mxfp4_gemm}``
 (alto/kernels/fp4/mxfp4/mxfp_quantization.py:410,548-585; mxfp_linear.py:143) and
 ``torch.ops.alto.{convert_to_nvfp4, convert_from_nvfp4, convert_to_mxfp8, convert_from_mxfp8,
-calculate_mxfp8_scales, blockwise_mxfp8_gemm}`` -- so that traced callers keep working.  The same
+calculate_mxfp8_scales, blockwise_mxfp8_gemm}`` -- so that traced callers keep working; likewise the
+forward grouped GEMMs on quantised operands, ``torchtitan::mxfp4_grouped_gemm_forward``
+(mxfp_grouped_gemm/cg_forward.py:200) and ``alto::mxfp8_grouped_gemm_forward``
+(mxfp8_grouped_gemm/cg_forward.py:222).  The reference's backward grouped ops take operands packed along
+a non-reduction axis, which the FP4 tensor cores cannot read; the autograd functions of
+``alto_b200.grouped`` quantise both packings instead, and those two ops are not registered.  The same
 ops are registered here as ``torch.library.custom_op`` around this package's functions.  By default
 they go under the namespace ``alto_b200``; a build that does not import the reference can claim the
 reference's own names with ``register("torchtitan", "alto")``.
@@ -17,6 +22,7 @@ from typing import Optional, Tuple
 
 import torch
 
+from . import grouped as _grp
 from . import mxfp4 as _mx4
 from . import mxfp8 as _mx8
 from . import nvfp4 as _nv4
@@ -185,3 +191,38 @@ def register(mxfp4_namespace: str = "alto_b200", namespace: str = "alto_b200") -
         M = a.shape[1] if trans_a else a.shape[0]
         N = b.shape[0] if trans_b else b.shape[1]
         return a.new_empty((M, N), dtype=output_dtype)
+
+    # ---------------- grouped (MoE) forward GEMMs on quantised operands ----------------
+    @op(f"{mxfp4_namespace}::mxfp4_grouped_gemm_forward", mutates_args=())
+    def mxfp4_grouped_gemm_forward(inputs: torch.Tensor, expert_weights: torch.Tensor, expert_indices: torch.Tensor,
+                                   input_scales: torch.Tensor, weight_scales: torch.Tensor,
+                                   trans_weights: bool = True, use_2dblock_x: bool = False,
+                                   use_2dblock_w: bool = True,
+                                   output_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        return _grp.mxfp4_grouped_gemm_forward(inputs, expert_weights, expert_indices, input_scales, weight_scales,
+                                               trans_weights, use_2dblock_x, use_2dblock_w, output_dtype)
+
+    @mxfp4_grouped_gemm_forward.register_fake
+    def _(inputs, expert_weights, expert_indices, input_scales, weight_scales, trans_weights=True,
+          use_2dblock_x=False, use_2dblock_w=True, output_dtype=torch.bfloat16):
+        N = expert_weights.shape[1] if trans_weights else expert_weights.shape[2]
+        return inputs.new_empty((inputs.shape[0], N), dtype=output_dtype)
+
+    @op(f"{namespace}::mxfp8_grouped_gemm_forward", mutates_args=())
+    def mxfp8_grouped_gemm_forward(inputs: torch.Tensor, expert_weights: torch.Tensor, expert_indices: torch.Tensor,
+                                   input_scales: torch.Tensor, weight_scales: torch.Tensor,
+                                   trans_weights: bool = True, use_2dblock_x: bool = False,
+                                   use_2dblock_w: bool = True, lhs_format_id: int = 0, rhs_format_id: int = 0,
+                                   output_dtype: torch.dtype = torch.bfloat16,
+                                   use_dot_scaled: Optional[bool] = None) -> torch.Tensor:
+        return _grp.mxfp8_grouped_gemm_forward(inputs, expert_weights, expert_indices, input_scales, weight_scales,
+                                               trans_weights, use_2dblock_x, use_2dblock_w, lhs_format_id,
+                                               rhs_format_id, output_dtype, use_dot_scaled)
+
+    @mxfp8_grouped_gemm_forward.register_fake
+    def _(inputs, expert_weights, expert_indices, input_scales, weight_scales, trans_weights=True,
+          use_2dblock_x=False, use_2dblock_w=True, lhs_format_id=0, rhs_format_id=0, output_dtype=torch.bfloat16,
+          use_dot_scaled=None):
+        N = expert_weights.shape[1] if trans_weights else expert_weights.shape[2]
+        return inputs.new_empty((inputs.shape[0], N), dtype=output_dtype)
+

@@ -51,6 +51,20 @@ def test_gemm_shapes():
     assert tuple(out.shape) == (96, 160) and out.dtype == torch.bfloat16   # a given as [K, M], b as [K, N]
 
 
+def test_grouped_forward_shapes():
+    ops = torch.ops.alto_b200
+    x, xs = _meta(384, 64, dtype=torch.uint8), _meta(384, 4, dtype=torch.uint8)
+    w, ws = _meta(4, 160, 64, dtype=torch.uint8), _meta(4, 5, 4, dtype=torch.uint8)
+    idx = _meta(256, dtype=torch.int32)
+    out = ops.mxfp4_grouped_gemm_forward(x, w, idx, xs, ws)
+    assert tuple(out.shape) == (384, 160) and out.dtype == torch.bfloat16
+    out = ops.mxfp4_grouped_gemm_forward(x, w.transpose(-2, -1), idx, xs, ws.transpose(-2, -1), trans_weights=False)
+    assert tuple(out.shape) == (384, 160)
+    x8, w8 = _meta(384, 128, dtype=torch.float8_e4m3fn), _meta(4, 160, 128, dtype=torch.float8_e4m3fn)
+    out = ops.mxfp8_grouped_gemm_forward(x8, w8, idx, xs, ws, output_dtype=torch.float32)
+    assert tuple(out.shape) == (384, 160) and out.dtype == torch.float32
+
+
 def test_ops_refuse_cpu_tensors():
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         torch.ops.alto_b200.convert_to_mxfp4(torch.zeros(32, 32, dtype=torch.bfloat16))

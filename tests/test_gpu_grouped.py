@@ -206,3 +206,37 @@ def test_grouped_2d_activation_blocks_equal_the_dense_function_per_expert(scheme
     yb, dxb, dwb = _per_expert_dense(x, w, dy, offs, dense)
     assert torch.equal(ya, yb) and torch.equal(xa.grad, dxb)
     assert _rel(wa.grad, dwb.float().cpu()) <= 1e-3
+
+
+@pytest.mark.parametrize("scheme", ["mxfp4", "mxfp8"])
+@pytest.mark.parametrize("use_2dblock_w,trans_weights", [(True, True), (False, True), (True, False)])
+def test_prequantized_grouped_forward_op_equals_the_quantize_then_function(scheme, use_2dblock_w, trans_weights):
+    """The registered forward ops on quantised operands (reference:
+    alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_forward.py:200, alto/kernels/mxfp8/mxfp8_grouped_gemm/cg_forward.py:222)
+    fed with the public quantizers' codes and plain scales give the forward of the quantise-then-GEMM
+    boundary function bit for bit, zero rows past the routed rows included."""
+    from alto_b200 import grouped as G, mxfp4, mxfp8, torch_ops
+    torch_ops.register()
+    x, w, _, offs, M = _case()
+    d = _dev()
+    xd, wd, offs_d = x.to(d), w.to(d), offs.to(d)
+    idx = G.create_indices_from_offsets_nosync(offs_d)
+    if scheme == "mxfp4":
+        xq, xs = mxfp4.convert_to_mxfp4(xd, axis=-1)
+        wq, ws = mxfp4.convert_to_mxfp4(wd, axis=-1, is_2d_block=use_2dblock_w)
+        want = G._quantize_then_mxfp_scaled_grouped_mm(xd, wd.transpose(-2, -1), offs_d, False, use_2dblock_w, False,
+                                                       False, False, "none", False)
+        op = torch.ops.alto_b200.mxfp4_grouped_gemm_forward
+    else:
+        xq, xs = mxfp8.convert_to_mxfp8(xd, axis=-1)
+        wq, ws = mxfp8.convert_to_mxfp8(wd, axis=-1, is_2d_block=use_2dblock_w)
+        want = G._quantize_then_mxfp8_scaled_grouped_mm(xd, wd.transpose(-2, -1), offs_d, use_2dblock_w=use_2dblock_w)
+        op = torch.ops.alto_b200.mxfp8_grouped_gemm_forward
+    if not trans_weights:
+        wq, ws = wq.transpose(-2, -1), ws.transpose(-2, -1)
+    got = op(xq, wq, idx, xs, ws, trans_weights=trans_weights, use_2dblock_w=use_2dblock_w)
+    assert got.dtype == torch.bfloat16 and got.shape == want.shape
+    assert torch.equal(got, want)
+    assert int(offs[-1]) < M and not got[int(offs[-1]):].any()
+    with pytest.raises(RuntimeError):
+        op(xq, wq, idx[:-1], xs, ws, trans_weights=trans_weights, use_2dblock_w=use_2dblock_w)
