@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own code on CPU.
 
-Needs the reference checkout (default /root/reference, or $ALTO_REFERENCE); it is therefore
+Needs the reference checkout (its path in $ALTO_REFERENCE); it is therefore
 run only where that checkout exists, and its outputs are committed.  Two sources are used:
 
 * the reference's PyTorch emulations (tests/unittest/{mxfp4,nvfp4,mxfp8}/utils.py), which its

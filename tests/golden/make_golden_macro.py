@@ -7,8 +7,8 @@ store: the interpreter truncates where the GPU rounds to nearest even, so bf16 c
 fp32 storage and rounded afterwards (see the loop below).  The file is loaded by path (the `alto`
 package itself needs a TorchTitan fork to import).
 
-Usage: python tests/golden/make_golden_macro.py      (needs the reference checkout, default
-/root/reference or $ALTO_REFERENCE; the output is committed)
+Usage: python tests/golden/make_golden_macro.py      (needs the reference checkout, its path in
+$ALTO_REFERENCE; the output is committed)
 """
 from __future__ import annotations
 

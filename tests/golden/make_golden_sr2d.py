@@ -3,7 +3,7 @@ interpreter, on 2-D (32 x 32) blocks WITH stochastic rounding from (philox_seed,
 
 This pins how the reference pairs its Philox words with the elements of a 2-D-block launch (the
 gradient of a `use_2dblock_x` linear is quantised this way, alto/kernels/fp4/mxfp4/mxfp_linear.py:447-458).
-Needs the reference checkout (default /root/reference, or $ALTO_REFERENCE); the output is committed.
+Needs the reference checkout (its path in $ALTO_REFERENCE); the output is committed.
 
 Usage: python tests/golden/make_golden_sr2d.py
 """
