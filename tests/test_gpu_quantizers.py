@@ -501,3 +501,35 @@ def test_ragged_shape_sweep_all_layouts(fmt):
                 q, _ = MX.convert_to_mxfp4(xd, axis=axis, is_2d_block=is2d, use_sr=True, philox_seed=seed,
                                            philox_offset=off)
             _same(q, qo, tag + " SR codes")
+
+
+@pytest.mark.parametrize("special", ["none", "nan", "inf", "huge"])
+def test_hadamard_amax_equals_amax_of_the_materialised_transform(special):
+    """One read of x yields the outer scales of x and of bf16(H x) (the wgrad operand): both equal
+    ``compute_dynamic_outer_scale`` (alto/kernels/fp4/nvfp4/nvfp_quantization.py:460-487) of x and of the
+    transform's own bf16 output bit for bit -- also when a NaN, an infinity (Inf - Inf inside the
+    butterfly) or an overflowing sum makes the maximum non-finite."""
+    from alto_b200 import _linear as E, nvfp4 as NV
+    from alto_b200.hadamard import HadamardFactory
+    d = _dev()
+    g = torch.Generator(device=d).manual_seed(11)
+    x = torch.randn(256, 192, generator=g, device=d).bfloat16()
+    if special == "nan":
+        x[37, 5] = float("nan")
+    elif special == "inf":
+        x[100, 64], x[101, 64] = float("inf"), float("-inf")
+    elif special == "huge":
+        x[32:48, 7] = 3.0e38
+    HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=3)
+    had = HadamardFactory.create_transform(device=d)
+    assert had.is_fused
+    got = E.outer_scales(x, True, had.device_params())
+    hx = had(x, left_mul=True)
+    assert hx.dtype == torch.bfloat16
+    want = torch.cat([NV.compute_dynamic_outer_scale(x), NV.compute_dynamic_outer_scale(hx)])
+    assert torch.equal(got, want), (got, want)
+    # the reference's expression, evaluated on the CPU (a correctly rounded division; on a CUDA device
+    # PyTorch evaluates tensor / python-scalar as a multiplication by the reciprocal, one ulp off at times)
+    ref = [torch.nan_to_num(t.float().cpu().abs().max(), nan=0.0) / (448.0 * 6.0) for t in (x, hx)]
+    ref = torch.stack([r.clamp(min=1e-30) for r in ref])
+    assert torch.equal(want.cpu(), ref.to(torch.float32)), (want, ref)
