@@ -51,6 +51,11 @@ EXPORTED_SYMBOLS = (
     "altob200_gemm_blockscaled",
     "altob200_grouped_gemm_blockscaled",
     "altob200_grouped_gemm_wgrad_blockscaled",
+    "altob200_gemm_mxfp4_two_level",
+    "altob200_grouped_gemm_mxfp4_two_level",
+    "altob200_grouped_gemm_wgrad_mxfp4_two_level",
+    "altob200_set_wait_limit_ns",
+    "altob200_selftest_wait_timeout",
 )
 
 
@@ -71,6 +76,17 @@ class QuantParams(C.Structure):
         ("use_uos", C.c_int32),
         ("rand_tile_rows", C.c_int64),
         ("rand_tile_pairs", C.c_int64),
+    ]
+
+
+class MacroScaleDesc(C.Structure):
+    """``altob200_macro_scale`` of the header: where the macro-block factor codes of an operand sit."""
+    _fields_ = [
+        ("codes", C.c_void_p),
+        ("row_stride", C.c_int64),
+        ("chunk_stride", C.c_int64),
+        ("expert_stride", C.c_int64),
+        ("row_shift", C.c_int32),
     ]
 
 
@@ -136,6 +152,17 @@ def _declare_more(lib):
     lib.altob200_deosc_accumulate.argtypes = [vp, vp, vp, vp, vp, vp, i64, i32, vp]
     lib.altob200_dge_scale.restype = C.c_int
     lib.altob200_dge_scale.argtypes = [vp, i32, i64, i64, i64, vp, C.POINTER(C.c_float), vp]
+    ms = C.POINTER(MacroScaleDesc)
+    lib.altob200_gemm_mxfp4_two_level.restype = C.c_int
+    lib.altob200_gemm_mxfp4_two_level.argtypes = [i64, i64, i64, vp, vp, ms, vp, vp, ms, C.c_float, i32, vp, i64, vp]
+    for name in ("altob200_grouped_gemm_mxfp4_two_level", "altob200_grouped_gemm_wgrad_mxfp4_two_level"):
+        f = getattr(lib, name)
+        f.restype = C.c_int
+        f.argtypes = [i64, i64, i64, i32, vp, vp, ms, vp, vp, ms, vp, C.c_float, i32, vp, i64, vp]
+    lib.altob200_set_wait_limit_ns.restype = C.c_int
+    lib.altob200_set_wait_limit_ns.argtypes = [C.c_uint64]
+    lib.altob200_selftest_wait_timeout.restype = C.c_int
+    lib.altob200_selftest_wait_timeout.argtypes = [C.c_uint64, vp]
 
 
 def lib():
@@ -454,3 +481,62 @@ def grouped_gemm_wgrad_blockscaled(fmt_a, fmt_b, M, N, K, num_experts, a_codes, 
         fmt_a, fmt_b, M, N, K, num_experts, a_codes.data_ptr(), a_scales.data_ptr(), b_codes.data_ptr(),
         b_scales.data_ptr(), k_offs.data_ptr(), _ptr(alpha_a), _ptr(alpha_b), _dt(out.dtype), out.data_ptr(),
         out.stride(1), _stream()), "altob200_grouped_gemm_wgrad_blockscaled")
+
+
+class MacroScale:
+    """Macro-block factor codes of one two-level GEMM operand: the uint8 tensor ``macro_block_scaling``
+    returned plus how (operand row, 128-chunk of the reduction axis) maps into it; see
+    ``altob200_macro_scale`` in the header."""
+
+    __slots__ = ("codes", "row_stride", "chunk_stride", "expert_stride", "row_shift")
+
+    def __init__(self, codes: torch.Tensor, row_stride: int, chunk_stride: int, row_shift: int, expert_stride: int = 0):
+        assert codes.dtype == torch.uint8 and codes.is_contiguous()
+        self.codes, self.row_stride, self.chunk_stride = codes, int(row_stride), int(chunk_stride)
+        self.row_shift, self.expert_stride = int(row_shift), int(expert_stride)
+
+    def desc(self) -> MacroScaleDesc:
+        d = MacroScaleDesc()
+        d.codes = self.codes.data_ptr()
+        d.row_stride, d.chunk_stride, d.expert_stride, d.row_shift = (self.row_stride, self.chunk_stride,
+                                                                      self.expert_stride, self.row_shift)
+        return d
+
+
+def gemm_mxfp4_two_level(M, N, K, a_codes, a_scales, a_macro: MacroScale, b_codes, b_scales, b_macro: MacroScale,
+                         out, out_scale: float = 1.0, group_expert=None, k_offs=None, num_experts: int = 0) -> None:
+    """Two-level scaled MXFP4 GEMM; ``group_expert`` selects the row-grouped form ([M, N] output, B
+    stacked per expert), ``k_offs`` the grouped weight gradient ([num_experts, M, N] output)."""
+    _require_cuda(a_codes, a_scales, a_macro.codes, b_codes, b_scales, b_macro.codes, out, group_expert, k_offs)
+    assert out.stride(-1) == 1
+    da, db = a_macro.desc(), b_macro.desc()
+    common = (a_codes.data_ptr(), a_scales.data_ptr(), C.byref(da), b_codes.data_ptr(), b_scales.data_ptr(),
+              C.byref(db))
+    if group_expert is not None:
+        assert out.dim() == 2 and group_expert.dtype == torch.int32
+        _check(lib().altob200_grouped_gemm_mxfp4_two_level(M, N, K, num_experts, *common, group_expert.data_ptr(),
+                                                           float(out_scale), _dt(out.dtype), out.data_ptr(),
+                                                           out.stride(0), _stream()),
+               "altob200_grouped_gemm_mxfp4_two_level")
+    elif k_offs is not None:
+        assert out.dim() == 3 and out.stride(0) == M * out.stride(1)
+        assert k_offs.dtype == torch.int32 and k_offs.numel() == num_experts
+        _check(lib().altob200_grouped_gemm_wgrad_mxfp4_two_level(M, N, K, num_experts, *common, k_offs.data_ptr(),
+                                                                 float(out_scale), _dt(out.dtype), out.data_ptr(),
+                                                                 out.stride(1), _stream()),
+               "altob200_grouped_gemm_wgrad_mxfp4_two_level")
+    else:
+        assert out.dim() == 2
+        _check(lib().altob200_gemm_mxfp4_two_level(M, N, K, *common, float(out_scale), _dt(out.dtype),
+                                                   out.data_ptr(), out.stride(0), _stream()),
+               "altob200_gemm_mxfp4_two_level")
+
+
+def set_wait_limit_ns(limit_ns: int) -> None:
+    """Wall-clock limit of every bounded wait inside GEMM kernels launched from now on (default 4 s)."""
+    _check(lib().altob200_set_wait_limit_ns(int(limit_ns)), "altob200_set_wait_limit_ns")
+
+
+def selftest_wait_timeout(limit_ns: int = 1_000_000) -> None:
+    """Launches the kernel whose only wait cannot be satisfied; ``status_read`` then reports the timeout."""
+    _check(lib().altob200_selftest_wait_timeout(int(limit_ns), _stream()), "altob200_selftest_wait_timeout")

@@ -90,12 +90,14 @@ RTN = dict(rounding=L.ROUND_RTN)
 
 
 class Operand:
-    """Codes + packed scales (+ NVFP4 outer scale) of one GEMM operand [rows, k], k contiguous."""
+    """Codes + packed scales (+ NVFP4 outer scale) of one GEMM operand [rows, k], k contiguous.
+    ``macro``: the operand's macro-block factor codes (``_lib.MacroScale``) in the two-level MXFP4 flow."""
 
-    __slots__ = ("codes", "scales", "outer", "rows", "k", "fmt")
+    __slots__ = ("codes", "scales", "outer", "rows", "k", "fmt", "macro")
 
-    def __init__(self, codes, scales, outer, rows, k, fmt):
+    def __init__(self, codes, scales, outer, rows, k, fmt, macro=None):
         self.codes, self.scales, self.outer, self.rows, self.k, self.fmt = codes, scales, outer, rows, k, fmt
+        self.macro = macro
 
 
 def as_2d_rows(x: torch.Tensor) -> torch.Tensor:
@@ -363,8 +365,9 @@ def linear_backward(ctx, grad_output):
         grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
     if need_dw:
         grad_weights = gemm(g_m, x_m, grad_output.dtype)
-        if ctx.clip_mode == "static":
-            # both wgrad operands were scaled by 3/4 (alto/kernels/fp4/mxfp4/mxfp_linear.py:543-544)
+        if ctx.clip_mode == "static" and not ctx.use_2dblock_x:
+            # both wgrad operands were clipped to 3/4 of their range (alto/kernels/fp4/mxfp4/mxfp_linear.py:
+            # 543-544); 2-D activation blocks take no clip mode (:310-315, 444-450), so nothing is undone there
             grad_weights *= (16.0 / 9.0)
         if ctx.use_dge:
             grad_weights = dge.apply_to_weight_grad(grad_weights, w_t.codes)

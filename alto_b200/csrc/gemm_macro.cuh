@@ -1,0 +1,535 @@
+// MXFP4 block-scaled GEMM with two-level ("macro-block") scaling, for sm_100a.
+//
+//   D[m, n] = out_scale * sum over 128-wide chunks c of K of
+//             (1 / fa[m, c]) * (1 / fb[n, c]) * sum_{k in chunk c} A[m, k] * B[n, k]
+//
+// A and B are MXFP4 operands (E2M1 codes, one E8M0 scale per 32 elements) that were quantised AFTER
+// every block of 128 elements along K had been multiplied by a factor in [1, 2) (fa, fb: eight
+// mantissa bits each, alto/kernels/fp4/mxfp4/macro_block_scaling.py:70-85).  The factors are not
+// powers of two, so they cannot ride on the E8M0 scales of the block-scaled MMA; they are constant
+// over a chunk of 128, so the tensor cores accumulate one chunk at a time into tensor memory and
+// CUDA cores fold each finished chunk into the running fp32 result, which lives in registers.
+// This replaces the reference's emulation of the recipe, dequantise -> descale -> bf16 matmul
+// (alto/kernels/fp4/mxfp4/mxfp_linear.py:337-356, mxfp_grouped_gemm/cg_backward.py:668-690).
+//
+// One CTA (512 threads = four warpgroups, persistent over 128 x 128 output tiles):
+//   warpgroup 0   warp 0: producer - per stage (128 bytes of K = two chunks) two tiled TMA loads and the
+//                 bulk copies of the stage's scale tiles; warp 1: MMA issuer - two tcgen05.mma per chunk
+//                 into one of three 128-column chunk accumulators in tensor memory, then a commit to that
+//                 accumulator's "full" barrier; warps 2, 3 idle;
+//   warpgroup 1   scale transfer shared memory -> tensor memory (as in the plain kernel);
+//   warpgroups 2, 3  fold + epilogue: each warp owns 32 rows x 64 columns of the tile in 64 registers per
+//                 thread.  Per chunk it reads the chunk accumulator (tcgen05.ld in two halves, one in
+//                 flight while the other is folded), gives it back, and adds P * (1/fa[row]) * (1/fb[col])
+//                 with packed fp32x2 arithmetic; the column factors of the chunk pass through a small
+//                 per-warp shared-memory buffer.  After the last chunk the registers are scaled,
+//                 converted, staged and TMA-stored.
+// The fold threads need ~170 registers (64 results + two half-chunk buffers of 32 + addressing), the
+// others ~40, so the warpgroups re-divide the register file with setmaxnreg (512 threads x 128 at launch).
+// Rows grouped by expert (`group_expert`) and K ranges per batch entry (`k_offs`) work as in the
+// plain kernel; every K range starts on a multiple of 128 elements, so chunks never straddle one.
+#pragma once
+// (included by gemm_sm100.cu inside namespace altob200, after the plain kernels it shares helpers with)
+
+struct MacroSide {
+  const uint8_t* codes;     // factor codes: element (row r, chunk c) at ((r >> shift) * row_stride + c * chunk_stride)
+  int64_t row_stride, chunk_stride;
+  int64_t expert_stride;    // B only: added per expert in row-group mode
+  int shift;                // 0: one factor per row; 7: one factor per 128 rows (2-D macro blocks)
+};
+
+struct MacroGemmArgs {
+  GemmArgs g;
+  MacroSide ma, mb;
+  float out_scale;
+#ifdef ALTOB200_GEMM_PROFILE
+  unsigned long long* prof;  // [gridDim.x][4 roles][8] clock sums of a -DALTOB200_GEMM_PROFILE build
+#endif
+};
+
+// Clock accounting of a profiling build: PROF_NOW() reads the SM clock, PROF_ADD(slot, t0) adds the
+// cycles since t0 to a per-thread counter; both vanish from the default build.
+#ifdef ALTOB200_GEMM_PROFILE
+#define PROF_DECL unsigned long long prof_c[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_NOW() clock64()
+#define PROF_ADD(slot, t0) prof_c[slot] += (unsigned long long)(clock64() - (t0))
+#define PROF_FLUSH(role)                                                                   \
+  if (margs.prof != nullptr)                                                               \
+    for (int i_ = 0; i_ < 8; ++i_) margs.prof[((size_t)blockIdx.x * 4 + (role)) * 8 + i_] = prof_c[i_]
+#else
+#define PROF_DECL
+#define PROF_NOW() 0
+#define PROF_ADD(slot, t0) (void)(t0)
+#define PROF_FLUSH(role)
+#endif
+
+constexpr int NUM_THREADS_MACRO = 512;
+
+struct CfgMacro {
+  static constexpr int BN = 128;
+  static constexpr int SF_TILES = Kind<KIND_MXF4>::SF_TILES;
+  static constexpr int A_BYTES = BM * STAGE_K_BYTES;
+  static constexpr int B_BYTES = BN * STAGE_K_BYTES;
+  static constexpr int SFA_BYTES = SF_TILES * 512;
+  static constexpr int SFB_BYTES = SF_TILES * 512;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 128-byte swizzle atom aligned");
+  static constexpr int SF_COLS_A = SF_TILES * 4;
+  static constexpr int SF_COLS_B = SF_TILES * 4;
+  static constexpr int STAGES = 4;
+  static constexpr int P_BUFS = 3;                              // chunk accumulators in tensor memory
+  static constexpr int FOLD_WARPS = 8;
+  static constexpr int EPI_BYTES = FOLD_WARPS * 2 * 4096;       // two staging buffers of 32 rows x 128 bytes per warp
+  static constexpr int FB_BYTES = FOLD_WARPS * 2 * 64 * 4;      // two buffers of 64 column factors per warp
+  static constexpr int RCP_BYTES = 256 * 4;                     // 1 / factor for every code
+  static constexpr int TMEM_SF_BASE = P_BUFS * BN;
+  static constexpr int TMEM_COLS_USED = TMEM_SF_BASE + STAGES * (SF_COLS_A + SF_COLS_B);
+  static_assert(TMEM_COLS_USED <= 512, "tensor memory budget");
+  static constexpr int NUM_BARS = 3 * STAGES + 2 * P_BUFS;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + EPI_BYTES + FB_BYTES + RCP_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+  // registers per thread after the warpgroups have re-divided the file: 2 x 128 x 40 + 2 x 128 x 216 = 65536
+  static constexpr int REGS_SMALL = 40, REGS_FOLD = 216;
+};
+
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// Tile description plus what the chunk loop needs: the first chunk of the K range, the number of
+// chunks, and MMAs per stage limited to the bytes that exist (also without K ranges).
+struct MacroTile {
+  TileInfo t;
+  int64_t chunk0;
+  int n_chunks;
+  int expert;
+};
+
+__device__ __forceinline__ MacroTile decode_macro_tile(const GemmArgs& args, int64_t tile, int64_t tiles_m,
+                                                       int64_t tiles_n, int k_stages_dense) {
+  MacroTile m;
+  m.t = decode_tile<KIND_MXF4, CfgMacro::BN>(args, tile, tiles_m, tiles_n, k_stages_dense);
+  m.expert = 0;
+  int64_t bytes = args.k_bytes;
+  m.chunk0 = 0;
+  if (args.k_offs != nullptr) {
+    const int64_t e = m.t.batch;
+    const int64_t k0 = e > 0 ? __ldg(args.k_offs + e - 1) : 0;
+    const int64_t k1 = __ldg(args.k_offs + e);
+    bytes = (k1 - k0) / 2;
+    m.chunk0 = k0 >> 7;
+  } else {
+    const int64_t tail = bytes - (int64_t)(m.t.k_stages - 1) * STAGE_K_BYTES;
+    m.t.last_mmas = (int)((tail + 31) / 32);
+    if (args.num_experts > 0 && !m.t.skip) m.expert = __ldg(args.group_expert + m.t.mb);
+  }
+  m.n_chunks = bytes > 0 ? (int)((bytes + 63) / 64) : 0;
+  return m;
+}
+
+// acc[16 h .. 16 h + 16) += P * (ra * fb[col]) for 32 columns of one chunk (P: raw tensor-memory words of
+// this thread's row; h must be a compile-time constant at the call site after inlining)
+__device__ __forceinline__ void fold_half(float2 (&acc)[32], int h, const uint32_t (&p)[32], float ra,
+                                          const float* fb, bool b_uniform, float rb_uniform) {
+  if (b_uniform) {
+    const float g = __fmul_rn(ra, rb_uniform);
+    const float2 g2 = make_float2(g, g);
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      acc[16 * h + j] = __ffma2_rn(make_float2(u2f(p[2 * j]), u2f(p[2 * j + 1])), g2, acc[16 * h + j]);
+  } else {
+    const float2 ra2 = make_float2(ra, ra);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 f = *reinterpret_cast<const float4*>(fb + 4 * j);
+      const float2 g0 = __fmul2_rn(ra2, make_float2(f.x, f.y));
+      const float2 g1 = __fmul2_rn(ra2, make_float2(f.z, f.w));
+      acc[16 * h + 2 * j] = __ffma2_rn(make_float2(u2f(p[4 * j]), u2f(p[4 * j + 1])), g0, acc[16 * h + 2 * j]);
+      acc[16 * h + 2 * j + 1] =
+          __ffma2_rn(make_float2(u2f(p[4 * j + 2]), u2f(p[4 * j + 3])), g1, acc[16 * h + 2 * j + 1]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS_MACRO, 1)
+gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_d, const MacroGemmArgs margs) {
+  using C = CfgMacro;
+  constexpr int BN = C::BN;
+  const GemmArgs& args = margs.g;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi = smem + C::STAGES * C::STAGE_BYTES;
+  float* fb_all = reinterpret_cast<float*>(epi + C::EPI_BYTES);
+  float* rcp_tab = reinterpret_cast<float*>(epi + C::EPI_BYTES + C::FB_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + C::EPI_BYTES + C::FB_BYTES + C::RCP_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + C::STAGES;
+  uint64_t* sf_full = bars + 2 * C::STAGES;
+  uint64_t* p_full = bars + 3 * C::STAGES;
+  uint64_t* p_empty = p_full + C::P_BUFS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_empty + C::P_BUFS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t tiles_m = (args.M + BM - 1) / BM;
+  const int64_t tiles_n = (args.N + BN - 1) / BN;
+  const int64_t n_tiles = tiles_m * tiles_n * (args.k_offs != nullptr ? args.num_batches : 1);
+  const int k_stages = (int)((args.k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+      mbar_init(&sf_full[s], 4);
+    }
+    for (int p = 0; p < C::P_BUFS; ++p) {
+      mbar_init(&p_full[p], 1);
+      mbar_init(&p_empty[p], C::FOLD_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // scale staging starts from zero: a ragged last stage never feeds uninitialised scale bytes
+  for (int s = 0; s < C::STAGES; ++s) {
+    uint32_t* z = reinterpret_cast<uint32_t*>(smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+    for (int i = threadIdx.x; i < (C::SFA_BYTES + C::SFB_BYTES) / 4; i += NUM_THREADS_MACRO) z[i] = 0u;
+  }
+  // 1 / factor(code), factor = 1 + code / 256 (exact), correctly rounded
+  if (threadIdx.x < 256) rcp_tab[threadIdx.x] = __frcp_rn(u2f((threadIdx.x << 15) + (127u << 23)));
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    setmaxnreg_dec<C::REGS_SMALL>();
+    if (warp == 0) {
+      // ------------------------------ producer ------------------------------
+      if (lane == 0) {
+        uint32_t it = 0;
+        bool alive = true;
+        PROF_DECL;
+        const long long t_all = PROF_NOW();
+        for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+          const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
+          const TileInfo& ti = mt.t;
+          if (ti.skip) continue;
+          const int64_t mb = ti.mb, nb = ti.nb;
+          for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+            const int s = it % C::STAGES;
+            const long long t0 = PROF_NOW();
+            if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 21, args.wait_ns)) {
+              alive = false;
+              break;
+            }
+            PROF_ADD(1, t0);
+            uint8_t* st = smem + s * C::STAGE_BYTES;
+            const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
+            int64_t sf_tiles = args.nct - cb0;
+            if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
+            const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
+            const int32_t kx = (int32_t)(ti.k_byte0 + (int64_t)ks * STAGE_K_BYTES);
+            if (ALTOB200_DBG(args, 4) && it >= (uint32_t)C::STAGES) {
+              mbar_arrive(&full_bar[s]);
+              continue;
+            }
+            mbar_expect_tx(&full_bar[s], C::A_BYTES + C::B_BYTES + 2 * sf_bytes);
+            tma_load_2d(st, &tmap_a, kx, (int32_t)(mb * BM), &full_bar[s]);
+            tma_load_2d(st + C::A_BYTES, &tmap_b, kx, (int32_t)ti.b_row0, &full_bar[s]);
+            bulk_load(st + C::A_BYTES + C::B_BYTES, args.sfa + (mb * args.nct + cb0) * 512, sf_bytes, &full_bar[s]);
+            bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES, ti.sfb + (nb * args.nct + cb0) * 512, sf_bytes,
+                      &full_bar[s]);
+          }
+        }
+        PROF_ADD(0, t_all);
+        PROF_FLUSH(0);
+      }
+    } else if (warp == 1) {
+      // ------------------------------ MMA issuer ------------------------------
+      if (lane == 0) {
+        uint32_t it = 0, pc = 0;
+        bool alive = true;
+        const uint32_t smem_base = smem_u32(smem);
+        PROF_DECL;
+        const long long t_all = PROF_NOW();
+        for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+          const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
+          const TileInfo& ti = mt.t;
+          if (ti.skip) continue;
+          for (int ks = 0; ks < ti.k_stages && alive; ++ks, ++it) {
+            const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
+            const int s = it % C::STAGES;
+            long long t0 = PROF_NOW();
+            if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 23, args.wait_ns)) { alive = false; break; }
+            PROF_ADD(1, t0);
+            t0 = PROF_NOW();
+            if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 25, args.wait_ns)) { alive = false; break; }
+            PROF_ADD(2, t0);
+            tc_fence_after();
+            const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;
+            const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
+            const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
+            const uint32_t a_lo = st4 | 0x10000u;
+            const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (j < n_mma && alive) {
+                const int buf = pc % C::P_BUFS;
+                if ((j & 1) == 0) {
+                  // first MMA of a chunk: its accumulator must have been drained by every fold warp
+                  const long long t1 = PROF_NOW();
+                  if (!ALTOB200_DBG(args, 128) &&
+                      !mbar_wait(&p_empty[buf], ((pc / C::P_BUFS) & 1) ^ 1, abort_flag, 22, args.wait_ns))
+                    alive = false;
+                  PROF_ADD(3, t1);
+                  tc_fence_after();
+                }
+                if (alive) {
+                  const int t = j >> 1;
+                  tc_mma<KIND_MXF4>(tmem_base + buf * BN, desc_of(DESC_SW128_HI, a_lo + 2 * j),
+                                    desc_of(DESC_SW128_HI, b_lo + 2 * j), args.idesc[j], (uint32_t)(j & 1),
+                                    sfa_t + t * 4, sfb_t + t * 4);
+                  if (ALTOB200_DBG(args, 512))  // profiling builds only: every MMA issued twice
+                    tc_mma<KIND_MXF4>(tmem_base + buf * BN, desc_of(DESC_SW128_HI, a_lo + 2 * j),
+                                      desc_of(DESC_SW128_HI, b_lo + 2 * j), args.idesc[j], 1u, sfa_t + t * 4,
+                                      sfb_t + t * 4);
+                  if ((j & 1) == 1 || j == n_mma - 1) {
+                    if (!ALTOB200_DBG(args, 256)) tc_commit(&p_full[buf]);
+                    ++pc;
+                  }
+                }
+              }
+            }
+            tc_commit(&empty_bar[s]);
+          }
+        }
+        PROF_ADD(0, t_all);
+        PROF_FLUSH(1);
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------ scale transfer ------------------------------
+    setmaxnreg_dec<C::REGS_SMALL>();
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t it = 0;
+    bool alive = true;
+    PROF_DECL;
+    const long long t_all = PROF_NOW();
+    for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+      const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
+      const TileInfo& ti = mt.t;
+      if (ti.skip) continue;
+      for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+        const int s = it % C::STAGES;
+        const long long t0 = PROF_NOW();
+        if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 26, args.wait_ns)) { alive = false; break; }
+        PROF_ADD(1, t0);
+        const uint8_t* sf = smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
+        const uint32_t sfa_t = tmem_base + lane_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
+        const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
+        if (!(ALTOB200_DBG(args, 1) && it > 0)) {
+#pragma unroll
+          for (int t = 0; t < C::SF_TILES; ++t) {
+            const uint4 a = *reinterpret_cast<const uint4*>(sf + t * 512);
+            tc_st4(sfa_t + t * 4, a.x, a.y, a.z, a.w);
+            const uint4 b = *reinterpret_cast<const uint4*>(sf + C::SFA_BYTES + t * 512);
+            tc_st4(sfb_t + t * 4, b.x, b.y, b.z, b.w);
+          }
+          tc_wait_st();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sf_full[s]);
+      }
+    }
+    PROF_ADD(0, t_all);
+    if (warp == 4 && lane == 0) { PROF_FLUSH(2); }
+  } else {
+    // ------------------------------ fold + epilogue ------------------------------
+    setmaxnreg_inc<C::REGS_FOLD>();
+    const int quad = warp & 3;                        // tensor-memory lane quarter this warp may read
+    const int half = warp >= 12 ? 1 : 0;              // columns [64 half, 64 half + 64) of the tile
+    const int fold_idx = warp - 8;
+    uint8_t* epi_warp = epi + fold_idx * 8192;
+    float* fb_warp = fb_all + fold_idx * 128;
+    const bool b_uniform = margs.mb.shift >= 7;       // one B factor per 128-column tile and chunk
+    const bool out_bf16 = args.out_bf16 != 0;
+    const uint32_t my_row = smem_u32(epi_warp) + (uint32_t)lane * 128u;
+    const uint32_t sw = (uint32_t)(lane & 7);
+    const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 64;
+    uint32_t pc = 0, store_it = 0;
+    bool alive = true;
+    PROF_DECL;
+    const long long t_all = PROF_NOW();
+    for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+      const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
+      const TileInfo& ti = mt.t;
+      float2 acc[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] = make_float2(0.0f, 0.0f);
+      if (!ti.skip) {
+        // factor codes of this thread's row of A and of the two columns of B this lane stages
+        int64_t m = ti.mb * BM + quad * 32 + lane;
+        if (m >= args.M) m = args.M - 1;
+        int64_t n0 = ti.nb * BN + half * 64 + 2 * lane, n1 = n0 + 1;
+        if (n0 >= args.N) n0 = args.N - 1;
+        if (n1 >= args.N) n1 = args.N - 1;
+        const uint8_t* pa = margs.ma.codes + (m >> margs.ma.shift) * margs.ma.row_stride +
+                            mt.chunk0 * margs.ma.chunk_stride;
+        const uint8_t* pbase = margs.mb.codes + (int64_t)mt.expert * margs.mb.expert_stride +
+                               mt.chunk0 * margs.mb.chunk_stride;
+        const uint8_t* pb0 = pbase + (n0 >> margs.mb.shift) * margs.mb.row_stride;
+        const uint8_t* pb1 = pbase + (n1 >> margs.mb.shift) * margs.mb.row_stride;
+        const int nch = mt.n_chunks;
+        uint32_t ca = __ldg(pa), cb0 = __ldg(pb0), cb1 = __ldg(pb1);
+        uint32_t ra_[32], rb_[32];   // chunk accumulator words: columns [0, 32) and [32, 64) of this warp's 64
+
+        // Prologue of the tile: the first half of chunk 0 is requested.
+        if (nch > 0 && !ALTOB200_DBG(args, 256)) {
+          const int buf = pc % C::P_BUFS;
+          const long long t0 = PROF_NOW();
+          alive = mbar_wait(&p_full[buf], (pc / C::P_BUFS) & 1, abort_flag, 24, args.wait_ns);
+          PROF_ADD(4, t0);
+          tc_fence_after();
+          if (alive) tc_ld32(t_row + buf * BN, ra_);
+        }
+        // Per chunk the two halves are loaded one behind the other, so that a tensor-memory load is always
+        // in flight while the other half is folded; the first half of chunk c + 1 is requested as soon as
+        // chunk c has left tensor memory.
+        for (int c = 0; c < nch && alive; ++c) {
+          if (ALTOB200_DBG(args, 256)) { ++pc; continue; }
+          if (ALTOB200_DBG(args, 64)) {
+            // profiling builds only: the chunk is handed straight back (tensor-core time of the chunked mainloop)
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_empty[pc % C::P_BUFS]);
+            ++pc;
+            if (c + 1 < nch) {
+              alive = mbar_wait(&p_full[pc % C::P_BUFS], (pc / C::P_BUFS) & 1, abort_flag, 24, args.wait_ns);
+              tc_fence_after();
+            }
+            continue;
+          }
+          long long t0 = PROF_NOW();
+          const float ra = rcp_tab[ca], rb0 = rcp_tab[cb0], rb1 = rcp_tab[cb1];
+          if (c + 1 < nch) {  // the next chunk's codes are in flight during this chunk's arithmetic
+            ca = __ldg(pa + (int64_t)(c + 1) * margs.ma.chunk_stride);
+            cb0 = __ldg(pb0 + (int64_t)(c + 1) * margs.mb.chunk_stride);
+            cb1 = __ldg(pb1 + (int64_t)(c + 1) * margs.mb.chunk_stride);
+          }
+          float* fb = fb_warp + (c & 1) * 64;
+          if (!b_uniform) {
+            reinterpret_cast<float2*>(fb)[lane] = make_float2(rb0, rb1);
+            __syncwarp();
+          }
+          PROF_ADD(6, t0);
+          const uint32_t t_p = t_row + (pc % C::P_BUFS) * BN;
+          t0 = PROF_NOW();
+          tc_wait_ld();                 // first half of chunk c is in ra_
+          PROF_ADD(1, t0);
+          tc_ld32(t_p + 32, rb_);
+          t0 = PROF_NOW();
+          fold_half(acc, 0, ra_, ra, fb, b_uniform, rb0);
+          PROF_ADD(3, t0);
+          t0 = PROF_NOW();
+          tc_wait_ld();                 // second half is in rb_: chunk c has left tensor memory
+          PROF_ADD(1, t0);
+          t0 = PROF_NOW();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_empty[pc % C::P_BUFS]);
+          ++pc;
+          PROF_ADD(7, t0);
+          if (c + 1 < nch) {
+            const int buf = pc % C::P_BUFS;
+            t0 = PROF_NOW();
+            alive = mbar_wait(&p_full[buf], (pc / C::P_BUFS) & 1, abort_flag, 24, args.wait_ns);
+            PROF_ADD(2, t0);
+            tc_fence_after();
+            if (alive) tc_ld32(t_row + buf * BN, ra_);
+          }
+          t0 = PROF_NOW();
+          fold_half(acc, 1, rb_, ra, fb + 32, b_uniform, rb0);
+          PROF_ADD(3, t0);
+        }
+        if (!alive) {
+          tc_wait_ld();
+          break;
+        }
+      }
+      // ---- epilogue of the tile: this warp's 32 rows x 64 columns ----
+      const long long t_epi = PROF_NOW();
+      const float os = margs.out_scale;
+      const int64_t row0 = ti.mb * BM + quad * 32;
+      const int64_t col_base = ti.nb * BN + half * 64;
+      auto hand_over = [&](int64_t col0) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          if (row0 < args.M && col0 < args.N)
+            tma_store_3d(epi_warp + (store_it & 1u) * 4096u, &tmap_d, (int32_t)col0, (int32_t)row0, ti.batch);
+          bulk_commit();  // one group per unit, empty or not: the wait below counts groups
+        }
+        ++store_it;
+      };
+      if (out_bf16) {
+        if (lane == 0) bulk_wait_read<1>();  // the store issued two units ago has finished reading this buffer
+        __syncwarp();
+        const uint32_t buf = my_row + (store_it & 1u) * 4096u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 v = acc[4 * j + q];
+            const __nv_bfloat162 p2 = __floats2bfloat162_rn(__fmul_rn(v.x, os), __fmul_rn(v.y, os));
+            o[q] = *reinterpret_cast<const uint32_t*>(&p2);
+          }
+          st_shared_v4(buf + ((((uint32_t)j) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+        }
+        hand_over(col_base);
+      } else {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (lane == 0) bulk_wait_read<1>();
+          __syncwarp();
+          const uint32_t buf = my_row + (store_it & 1u) * 4096u;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float2 v0 = acc[u * 16 + 2 * j], v1 = acc[u * 16 + 2 * j + 1];
+            st_shared_v4(buf + ((((uint32_t)j) ^ sw) << 4), f2u(__fmul_rn(v0.x, os)), f2u(__fmul_rn(v0.y, os)),
+                         f2u(__fmul_rn(v1.x, os)), f2u(__fmul_rn(v1.y, os)));
+          }
+          hand_over(col_base + u * 32);
+        }
+      }
+      PROF_ADD(5, t_epi);
+    }
+    if (lane == 0) bulk_wait_all();
+    PROF_ADD(0, t_all);
+    if (warp == 8 && lane == 0) { PROF_FLUSH(3); }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}

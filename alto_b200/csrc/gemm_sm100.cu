@@ -29,6 +29,8 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace altob200 {
@@ -39,7 +41,7 @@ constexpr int BM = 128;
 constexpr int STAGE_K_BYTES = 128;
 constexpr int NUM_THREADS = 320;  // producer, MMA issuer, 4 epilogue warps, 4 scale-transfer warps
 constexpr int NUM_THREADS_PAIR = 448;  // pair kernel: 4 more epilogue warps (each group drains 128 columns)
-constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // 4 s per wait
+constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // default limit of one wait: 4 s
 
 enum { KIND_NVF4 = 0, KIND_MXF4 = 1, KIND_MXF8 = 2 };
 
@@ -82,11 +84,19 @@ struct GemmArgs {
   int num_batches;
   int group_m;           // row tiles per raster group (see decode_tile)
   uint32_t idesc[4];    // instruction descriptors of the four MMAs of a stage
-  // profiling switches (env ALTOB200_GEMM_DEBUG, results are then WRONG): 1 = copy scales only in the
-  // first stage of a tile, 2 = skip the global stores, 4 = stop loading operands once the ring is full,
-  // 8 = the epilogue returns the accumulator without reading it (mainloop-only time)
+  uint64_t wait_ns;     // limit of every mbarrier wait (wall clock)
+#ifdef ALTOB200_GEMM_PROFILE
+  // profiling switches of a -DALTOB200_GEMM_PROFILE build only (env ALTOB200_GEMM_DEBUG; results are
+  // then WRONG): 1 = copy scales only in the first stage of a tile, 2 = skip the global stores, 4 = stop
+  // loading operands once the ring is full, 8 = the epilogue returns the accumulator without reading it
   int debug;
+#endif
 };
+#ifdef ALTOB200_GEMM_PROFILE
+#define ALTOB200_DBG(a, bit) (((a).debug & (bit)) != 0)
+#else
+#define ALTOB200_DBG(a, bit) false
+#endif
 
 // ---------------------------------------------------------------------------------------
 // PTX wrappers
@@ -121,20 +131,25 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 // Bounded wait.  Returns false (and raises the abort flag) when the limit passes or when
-// another role already aborted.
+// another role already aborted.  The wall clock (%globaltimer, a slow read) is consulted only
+// every 64 failed polls, and for the first time after 64 of them, so a wait that is satisfied
+// soon never pays for a timer read; the limit is counted from that first read.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int site) {
+                                          int site, uint64_t limit_ns, int kernel_id = 1) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3FFu) == 0) {
+    if ((++spins & 0x3Fu) == 0) {
       if (*abort_flag != 0) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         if (atomicCAS(&g_status[0], 0, ALTOB200_ETIMEOUT_DEVICE) == 0) {
-          g_status[1] = 1;  // kernel id: gemm
+          g_status[1] = kernel_id;  // 1 = a GEMM kernel, 9 = the wait self-test
           g_status[2] = (int)blockIdx.x;
           g_status[3] = site;
         }
@@ -518,13 +533,13 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (nb_valid > C::NB) nb_valid = C::NB;
         for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int s = it % C::STAGES;
-          if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 1)) { alive = false; break; }
+          if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 1, args.wait_ns)) { alive = false; break; }
           uint8_t* st = smem + s * C::STAGE_BYTES;
           const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
           int64_t sf_tiles = args.nct - cb0;
           if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
           const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
-          if ((args.debug & 4) && it >= (uint32_t)C::STAGES) {
+          if (ALTOB200_DBG(args, 4) && it >= (uint32_t)C::STAGES) {
             mbar_arrive(&full_bar[s]);
             continue;
           }
@@ -552,14 +567,14 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
         if (ti.skip) continue;
         const int acc = tile_it % C::ACC_STAGES;
-        if (!mbar_wait(&acc_empty[acc], ((tile_it / C::ACC_STAGES) & 1) ^ 1, abort_flag, 2)) break;
+        if (!mbar_wait(&acc_empty[acc], ((tile_it / C::ACC_STAGES) & 1) ^ 1, abort_flag, 2, args.wait_ns)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
           const int s = it % C::STAGES;
-          if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 3)) { alive = false; break; }
-          if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 5)) { alive = false; break; }
+          if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 3, args.wait_ns)) { alive = false; break; }
+          if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 5, args.wait_ns)) { alive = false; break; }
           tc_fence_after();
           const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;  // stage address / 16
           const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
@@ -594,11 +609,11 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       if (ti.skip) continue;
       for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
         const int s = it % C::STAGES;
-        if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 6)) { alive = false; break; }
+        if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 6, args.wait_ns)) { alive = false; break; }
         const uint8_t* sf = smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
         const uint32_t sfa_t = tmem_base + lane_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
         const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
-        if (!((args.debug & 1) && ks > 0)) {
+        if (!(ALTOB200_DBG(args, 1) && ks > 0)) {
 #pragma unroll
           for (int t = 0; t < C::SF_TILES; ++t) {
             const uint4 a = *reinterpret_cast<const uint4*>(sf + t * 512);
@@ -630,11 +645,11 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       const bool pad_group = ti.skip;
       const int acc = tile_it % C::ACC_STAGES;
       if (!pad_group) {
-        if (!mbar_wait(&acc_full[acc], (tile_it / C::ACC_STAGES) & 1, abort_flag, 4)) break;
+        if (!mbar_wait(&acc_full[acc], (tile_it / C::ACC_STAGES) & 1, abort_flag, 4, args.wait_ns)) break;
         tc_fence_after();
       }
       const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
-      if ((args.debug & 8) && !pad_group) {
+      if (ALTOB200_DBG(args, 8) && !pad_group) {
         // profiling only: hand the accumulator straight back (mainloop-only time, output unwritten)
         tc_fence_before();
         __syncwarp();
@@ -643,7 +658,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         continue;
       }
       epilogue_tile<BN>(t_acc, !pad_group, alpha, args.out_bf16 != 0, epi + (warp - 2) * 8192, lane, &tmap_d, row0,
-                        nb * BN, ti.batch, args.M, args.N, !(args.debug & 2), !(args.debug & 32), store_it,
+                        nb * BN, ti.batch, args.M, args.N, !ALTOB200_DBG(args, 2), !ALTOB200_DBG(args, 32), store_it,
                         [&]() { mbar_arrive(&acc_empty[acc]); });
       if (!pad_group) ++tile_it;
     }
@@ -841,7 +856,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
         if (nb_valid > C::NB) nb_valid = C::NB;
         for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int s = it % C::STAGES;
-          if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 11)) { alive = false; break; }
+          if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 11, args.wait_ns)) { alive = false; break; }
           uint8_t* st = smem + s * C::STAGE_BYTES;
           const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
           int64_t sf_tiles = args.nct - cb0;
@@ -875,14 +890,14 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
       for (int64_t tile = pair; tile < n_tiles && alive; tile += n_pairs) {
         const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
         if (ti.skip) continue;
-        if (!mbar_wait(acc_empty, (tile_it & 1) ^ 1, abort_flag, 12)) break;
+        if (!mbar_wait(acc_empty, (tile_it & 1) ^ 1, abort_flag, 12, args.wait_ns)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base;
         for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
           const int s = it % C::STAGES;
-          if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 13)) { alive = false; break; }
-          if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 15)) { alive = false; break; }
+          if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 13, args.wait_ns)) { alive = false; break; }
+          if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 15, args.wait_ns)) { alive = false; break; }
           tc_fence_after();
           const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;
           const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
@@ -912,7 +927,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
       if (ti.skip) continue;
       for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
         const int s = it % C::STAGES;
-        if (!mbar_wait(&sfs_full[s], (it / C::STAGES) & 1, abort_flag, 16)) { alive = false; break; }
+        if (!mbar_wait(&sfs_full[s], (it / C::STAGES) & 1, abort_flag, 16, args.wait_ns)) { alive = false; break; }
         const uint8_t* sf = smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
         const uint32_t sfa_t = tmem_base + lane_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
         const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
@@ -953,11 +968,11 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
       const int64_t row0 = (ti.mb * 2 + rank) * BM + quad * 32;
       const bool pad_group = ti.skip;
       if (!pad_group) {
-        if (!mbar_wait(acc_full, tile_it & 1, abort_flag, 14)) break;
+        if (!mbar_wait(acc_full, tile_it & 1, abort_flag, 14, args.wait_ns)) break;
         tc_fence_after();
       }
       const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 128;
-      if ((args.debug & 8) && !pad_group) {
+      if (ALTOB200_DBG(args, 8) && !pad_group) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
@@ -968,7 +983,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
         continue;
       }
       epilogue_tile<128>(t_acc, !pad_group, alpha, OUT_BF16, epi + epi_idx * 8192, lane, &tmap_d, row0,
-                         nb * BN + half * 128, ti.batch, args.M, args.N, !(args.debug & 2), !(args.debug & 32),
+                         nb * BN + half * 128, ti.batch, args.M, args.N, !ALTOB200_DBG(args, 2), !ALTOB200_DBG(args, 32),
                          store_it, [&]() {
                            if (leader) mbar_arrive(acc_empty);
                            else mbar_arrive_cluster_relaxed(acc_empty_leader);
@@ -989,9 +1004,32 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
   }
 }
 
+#include "gemm_macro.cuh"
+
+// ---------------------------------------------------------------------------------------
+// self-test of the bounded wait: one CTA, one thread waits on an mbarrier nobody arrives on
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32, 1) wait_selftest_kernel(uint64_t limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // phase 0 never completes (no arrival is ever made): the wait runs into its limit, records
+  // {kernel 9, block, site 99} in the status word and returns false; the kernel then ends normally
+  if (threadIdx.x == 0) (void)mbar_wait(&bar, 0, &abort_flag, 99, limit_ns, 9);
+  __syncthreads();
+}
+
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
+static std::atomic<uint64_t> g_wait_limit_ns{WAIT_LIMIT_NS};
+static uint64_t wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1061,26 +1099,44 @@ static uint32_t make_idesc(int kind, int fmt_a, int fmt_b, int m, int n, int sf_
   return d;
 }
 
+// Per-device launch state.  A process may drive several GPUs (one context each): the dynamic
+// shared-memory attribute of a kernel, the SM count and the number of resident clusters belong to
+// the device that is current at the launch, so they are kept per device ordinal.  Entries are
+// written with relaxed atomics: concurrent first calls compute the same values.
+constexpr int MAX_DEVICES = 64;
+static int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -1;
+  return dev;
+}
 static int sm_count_gemm() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 148;
+  static std::atomic<int> n[MAX_DEVICES];
+  const int dev = current_device();
+  if (dev < 0) return 148;
+  int v = n[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev].store(v, std::memory_order_relaxed);
   }
-  return n;
+  return v;
+}
+// Sets the dynamic shared-memory limit of `kernel` once per device.
+template <class K>
+static int ensure_smem_attr(K kernel, int bytes, std::atomic<int>* done /*[MAX_DEVICES]*/) {
+  const int dev = current_device();
+  if (dev >= 0 && done[dev].load(std::memory_order_relaxed) != 0) return ALTOB200_OK;
+  ALTOB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (dev >= 0) done[dev].store(1, std::memory_order_relaxed);
+  return ALTOB200_OK;
 }
 
 template <int KIND, int BN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmArgs& args,
                        cudaStream_t st) {
   using C = Cfg<KIND, BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    ALTOB200_CUDA_CHECK(cudaFuncSetAttribute(gemm_blockscaled_kernel<KIND, BN>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    attr_set = true;
-  }
+  static std::atomic<int> attr_set[MAX_DEVICES];
+  const int rc = ensure_smem_attr(gemm_blockscaled_kernel<KIND, BN>, C::SMEM_BYTES, attr_set);
+  if (rc != ALTOB200_OK) return rc;
   const int64_t tiles = ceil_div(args.M, BM) * ceil_div(args.N, BN) * (args.k_offs != nullptr ? args.num_batches : 1);
   int64_t grid = sm_count_gemm();
   if (grid > tiles) grid = tiles;
@@ -1093,7 +1149,9 @@ template <int KIND, bool OUT_BF16>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmArgs& args,
                             cudaStream_t st) {
   using C = CfgPair<KIND>;
-  static int max_clusters = 0;  // 0 = not asked yet, < 0 = the device cannot run the pair kernel
+  static std::atomic<int> clusters_of[MAX_DEVICES];  // 0 = not asked yet, < 0 = the device cannot run the pair kernel
+  const int dev = current_device();
+  int max_clusters = dev >= 0 ? clusters_of[dev].load(std::memory_order_relaxed) : 0;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1116,7 +1174,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     } else {
       max_clusters = n;
     }
-    if (args.debug & 16) fprintf(stderr, "altob200: pair kernel, %d clusters of 2 resident\n", max_clusters);
+    if (dev >= 0) clusters_of[dev].store(max_clusters, std::memory_order_relaxed);
   }
   if (max_clusters < 0) return ALTOB200_EUNSUPPORTED;
   const int64_t tiles =
@@ -1203,16 +1261,19 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
     gm = ceil_div(tiles_m, n_groups);
     g.group_m = (int)gm;
   }
+  g.wait_ns = wait_limit_ns();
   for (int j = 0; j < 4; ++j) {
     const int sf_id = kind == KIND_NVF4 ? 0 : (kind == KIND_MXF4 ? (j & 1) * 2 : j);
     g.idesc[j] = make_idesc(kind, format_a, format_b, use_pair ? 2 * BM : BM, BN, sf_id);
   }
+#ifdef ALTOB200_GEMM_PROFILE
   static int debug_flags = -1;
   if (debug_flags < 0) {
     const char* e = getenv("ALTOB200_GEMM_DEBUG");
     debug_flags = e ? atoi(e) : 0;
   }
   g.debug = debug_flags;
+#endif
   cudaStream_t st = (cudaStream_t)stream;
   if (use_pair) {
     const bool obf = g.out_bf16 != 0;
@@ -1233,6 +1294,92 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
     default: LAUNCH(KIND_MXF8);
   }
 #undef LAUNCH
+}
+
+static int launch_gemm_macro(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                             const MacroGemmArgs& margs, cudaStream_t st) {
+  using C = CfgMacro;
+  static std::atomic<int> attr_set[MAX_DEVICES];
+  const int rc = ensure_smem_attr(gemm_macro_kernel, C::SMEM_BYTES, attr_set);
+  if (rc != ALTOB200_OK) return rc;
+  const GemmArgs& a = margs.g;
+  const int64_t tiles = ceil_div(a.M, BM) * ceil_div(a.N, C::BN) * (a.k_offs != nullptr ? a.num_batches : 1);
+  int64_t grid = sm_count_gemm();
+  if (grid > tiles) grid = tiles;
+  gemm_macro_kernel<<<(unsigned)grid, NUM_THREADS_MACRO, C::SMEM_BYTES, st>>>(ta, tb, td, margs);
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+static int gemm_macro_common(int64_t M, int64_t N, int64_t K, int32_t num_experts, const void* a_codes,
+                             const void* a_scales, const altob200_macro_scale* a_macro, const void* b_codes,
+                             const void* b_scales, const altob200_macro_scale* b_macro, const int32_t* group_expert,
+                             const int32_t* k_offs, float out_scale, int32_t out_dtype, void* d, int64_t ldd,
+                             void* stream) {
+  if (a_codes == nullptr || b_codes == nullptr || a_scales == nullptr || b_scales == nullptr || d == nullptr ||
+      a_macro == nullptr || b_macro == nullptr || a_macro->codes == nullptr || b_macro->codes == nullptr)
+    return ALTOB200_EINVAL_SHAPE;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || ldd < N) return ALTOB200_EINVAL_SHAPE;
+  if (group_expert != nullptr && k_offs != nullptr) return ALTOB200_EINVAL_SHAPE;
+  if ((group_expert != nullptr || k_offs != nullptr) && num_experts <= 0) return ALTOB200_EINVAL_SHAPE;
+  if ((a_macro->row_shift != 0 && a_macro->row_shift != 7) || (b_macro->row_shift != 0 && b_macro->row_shift != 7))
+    return ALTOB200_EINVAL_SHAPE;
+  const int64_t k_bytes = K / 2;
+  if (k_bytes % 16 != 0) return ALTOB200_EINVAL_SHAPE;
+  const int osz = out_dtype == ALTOB200_DT_BF16 ? 2 : 4;
+  if ((reinterpret_cast<uintptr_t>(a_codes) & 15) || (reinterpret_cast<uintptr_t>(b_codes) & 15) ||
+      (reinterpret_cast<uintptr_t>(a_scales) & 15) || (reinterpret_cast<uintptr_t>(b_scales) & 15) ||
+      (reinterpret_cast<uintptr_t>(d) & 15) || (ldd * osz) % 16 != 0)
+    return ALTOB200_EINVAL_ALIGN;
+  const bool row_groups = group_expert != nullptr;
+  const int64_t b_rows = N * (row_groups ? num_experts : 1);
+  if (M >= (1ll << 31) || b_rows >= (1ll << 31) || k_bytes >= (1ll << 31)) return ALTOB200_ELIMIT;
+
+  CUtensorMap ta, tb, td;
+  int rc = make_tmap(&ta, a_codes, M, k_bytes, BM);
+  if (rc != ALTOB200_OK) return rc;
+  rc = make_tmap(&tb, b_codes, b_rows, k_bytes, CfgMacro::BN);
+  if (rc != ALTOB200_OK) return rc;
+  rc = make_tmap_out(&td, d, k_offs != nullptr ? num_experts : 1, M, N, ldd, out_dtype == ALTOB200_DT_BF16);
+  if (rc != ALTOB200_OK) return rc;
+
+  MacroGemmArgs m;
+  GemmArgs& g = m.g;
+  g.M = M; g.N = N; g.K = K; g.k_bytes = k_bytes;
+  g.sfa = (const uint8_t*)a_scales; g.sfb = (const uint8_t*)b_scales;
+  g.nct = ceil_div(K / 32, 4);
+  g.alpha_a = nullptr; g.alpha_b = nullptr;
+  g.d = d; g.ldd = ldd; g.out_bf16 = out_dtype == ALTOB200_DT_BF16;
+  g.num_experts = row_groups ? num_experts : 0; g.group_expert = group_expert;
+  g.sfb_expert_stride = (int64_t)altob200_packed_scale_bytes(N, K / 32);
+  g.k_offs = k_offs; g.num_batches = k_offs != nullptr ? num_experts : 1;
+  {
+    const int64_t tiles_m = ceil_div(M, BM);
+    int64_t gm = 8;
+    if (gm > tiles_m) gm = tiles_m;
+    const int64_t n_groups = ceil_div(tiles_m, gm);
+    g.group_m = (int)ceil_div(tiles_m, n_groups);
+  }
+  g.wait_ns = wait_limit_ns();
+  for (int j = 0; j < 4; ++j)
+    g.idesc[j] = make_idesc(KIND_MXF4, ALTOB200_FMT_MXFP4, ALTOB200_FMT_MXFP4, BM, CfgMacro::BN, (j & 1) * 2);
+#ifdef ALTOB200_GEMM_PROFILE
+  {
+    const char* e = getenv("ALTOB200_GEMM_DEBUG");
+    g.debug = e ? atoi(e) : 0;
+  }
+#endif
+  m.ma.codes = a_macro->codes; m.ma.row_stride = a_macro->row_stride; m.ma.chunk_stride = a_macro->chunk_stride;
+  m.ma.expert_stride = 0; m.ma.shift = a_macro->row_shift;
+  m.mb.codes = b_macro->codes; m.mb.row_stride = b_macro->row_stride; m.mb.chunk_stride = b_macro->chunk_stride;
+  m.mb.expert_stride = row_groups ? b_macro->expert_stride : 0; m.mb.shift = b_macro->row_shift;
+  m.out_scale = out_scale;
+#ifdef ALTOB200_GEMM_PROFILE
+  {
+    const char* e = getenv("ALTOB200_MACRO_PROF_PTR");  // device address of the clock table, set by the probe script
+    m.prof = e ? reinterpret_cast<unsigned long long*>(strtoull(e, nullptr, 0)) : nullptr;
+  }
+#endif
+  return launch_gemm_macro(ta, tb, td, m, (cudaStream_t)stream);
 }
 
 }  // namespace altob200
@@ -1268,6 +1415,47 @@ int altob200_grouped_gemm_wgrad_blockscaled(int32_t format_a, int32_t format_b, 
   if (num_experts <= 0 || k_offs == nullptr) return ALTOB200_EINVAL_SHAPE;
   return gemm_common(format_a, format_b, M, N, K, 0, a_codes, a_scales, b_codes, b_scales, nullptr, alpha_a,
                      alpha_b, out_dtype, d, ldd, stream, k_offs, num_experts);
+}
+
+int altob200_gemm_mxfp4_two_level(int64_t M, int64_t N, int64_t K, const void* a_codes, const void* a_scales,
+                                  const altob200_macro_scale* a_macro, const void* b_codes, const void* b_scales,
+                                  const altob200_macro_scale* b_macro, float out_scale, int32_t out_dtype, void* d,
+                                  int64_t ldd, void* stream) {
+  return gemm_macro_common(M, N, K, 0, a_codes, a_scales, a_macro, b_codes, b_scales, b_macro, nullptr, nullptr,
+                           out_scale, out_dtype, d, ldd, stream);
+}
+
+int altob200_grouped_gemm_mxfp4_two_level(int64_t M, int64_t N, int64_t K, int32_t num_experts, const void* a_codes,
+                                          const void* a_scales, const altob200_macro_scale* a_macro,
+                                          const void* b_codes, const void* b_scales,
+                                          const altob200_macro_scale* b_macro, const int32_t* group_expert,
+                                          float out_scale, int32_t out_dtype, void* d, int64_t ldd, void* stream) {
+  if (num_experts <= 0 || group_expert == nullptr) return ALTOB200_EINVAL_SHAPE;
+  return gemm_macro_common(M, N, K, num_experts, a_codes, a_scales, a_macro, b_codes, b_scales, b_macro,
+                           group_expert, nullptr, out_scale, out_dtype, d, ldd, stream);
+}
+
+int altob200_grouped_gemm_wgrad_mxfp4_two_level(int64_t M, int64_t N, int64_t K, int32_t num_experts,
+                                                const void* a_codes, const void* a_scales,
+                                                const altob200_macro_scale* a_macro, const void* b_codes,
+                                                const void* b_scales, const altob200_macro_scale* b_macro,
+                                                const int32_t* k_offs, float out_scale, int32_t out_dtype, void* d,
+                                                int64_t ldd, void* stream) {
+  if (num_experts <= 0 || k_offs == nullptr) return ALTOB200_EINVAL_SHAPE;
+  return gemm_macro_common(M, N, K, num_experts, a_codes, a_scales, a_macro, b_codes, b_scales, b_macro, nullptr,
+                           k_offs, out_scale, out_dtype, d, ldd, stream);
+}
+
+int altob200_set_wait_limit_ns(uint64_t limit_ns) {
+  if (limit_ns == 0) return ALTOB200_EINVAL_SHAPE;
+  g_wait_limit_ns.store(limit_ns, std::memory_order_relaxed);
+  return ALTOB200_OK;
+}
+
+int altob200_selftest_wait_timeout(uint64_t limit_ns, void* stream) {
+  if (limit_ns == 0 || limit_ns > 1000000000ull) return ALTOB200_EINVAL_SHAPE;  // at most one second
+  wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit_ns);
+  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 
 int altob200_status_read(void* stream, int32_t detail[4]) {

@@ -17,6 +17,8 @@
 //               transpose; no shared memory.
 #include <type_traits>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace altob200 {
@@ -1914,17 +1916,23 @@ int altob200_amax_noalloc(const void* x, int32_t in_dtype, int64_t rows, int64_t
   if (rows > ALTOB200_NOALLOC_MAX_BYTES / esz / cols) return ALTOB200_ELIMIT;
   // Set-up, once per device, with that device current: the array's name is only a host-side
   // handle, the kernel needs the device address behind it.
-  static void* scratch_of_device[64] = {nullptr};
+  // The cache is atomic because the first calls on a device may come from two host threads at
+  // once (they would store the same address).  The address stays valid for the life of the
+  // device's context; after cudaDeviceReset it must not be used, so a process that resets a
+  // device must not call this entry point on it again.
+  static std::atomic<void*> scratch_of_device[64];
   int dev = 0;
   ALTOB200_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return ALTOB200_ELIMIT;
-  if (scratch_of_device[dev] == nullptr) {
+  void* cached = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (cached == nullptr) {
     void* ptr = nullptr;
     ALTOB200_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
     if (ptr == nullptr) return ALTOB200_ECUDA;
-    scratch_of_device[dev] = ptr;
+    scratch_of_device[dev].store(ptr, std::memory_order_release);
+    cached = ptr;
   }
-  NoallocScratch* scratch = reinterpret_cast<NoallocScratch*>(scratch_of_device[dev]);
+  NoallocScratch* scratch = reinterpret_cast<NoallocScratch*>(cached);
   cudaStream_t st = (cudaStream_t)stream;
   // the counter must start at zero even if an earlier launch never finished
   ALTOB200_CUDA_CHECK(cudaMemsetAsync(&scratch->counter, 0, sizeof(uint32_t), st));

@@ -162,8 +162,9 @@ class GroupedLinearFunction(torch.autograd.Function):
             grad_weights = torch.empty(n_exp, N, K, dtype=grad_output.dtype, device=g2.device)
             L.grouped_gemm_wgrad_blockscaled(g_m.fmt, x_m.fmt, N, K, M, n_exp, g_m.codes, g_m.scales, x_m.codes,
                                              x_m.scales, offs32, grad_weights, g_m.outer, x_m.outer)
-            if ctx.clip_mode == "static":
-                # both wgrad operands were scaled by 3/4 (mxfp_grouped_gemm/cg_backward.py:893-894)
+            if ctx.clip_mode == "static" and not ctx.use_2dblock_x:
+                # both wgrad operands were clipped to 3/4 of their range (mxfp_grouped_gemm/cg_backward.py:
+                # 893-894); 2-D activation blocks are quantised without a clip mode
                 grad_weights *= (16.0 / 9.0)
             if ctx.use_dge:
                 # factor from the E2M1 code of every weight element (cg_backward.py:912-929); the codes
@@ -182,76 +183,6 @@ def _hadamard(use_hadamard: bool, use_2dblock_x: bool, device) -> Optional[Hadam
         return HadamardFactory.create_transform(device=device)
 
 
-class GroupedMacroLinearFunction(torch.autograd.Function):
-    """MXFP4 grouped linear with two-level ("blockwise") scaling.  The macro factors are not powers of
-    two, so they cannot ride on the E8M0 scales of the block-scaled MMA; the reference refuses the
-    recipe on its FP4 matrix cores (mxfp_grouped_gemm/cg_backward.py:655) and multiplies the
-    de-quantised, de-scaled operands expert by expert in the input dtype (cg_backward.py:666-690,
-    895-908).  Same here: every scale -> quantise -> de-quantise -> descale chain runs in this
-    library's kernels on the whole buffer, the per-expert matmuls are plain bf16 GEMMs.  ``weights``
-    is canonical [E, N, K].  One host synchronisation per call (the expert boundaries)."""
-
-    @staticmethod
-    def forward(ctx, inputs, weights, offs, use_2dblock_w, use_sr_grad, hadamard_transform, use_2dblock_x=False,
-                clip_mode="none", use_uos=False, use_dge=False):
-        from .mxfp4 import _macro_qdq
-        if not inputs.is_cuda:
-            raise RuntimeError("grouped GEMM runs on CUDA tensors only (no CPU fallback)")
-        weights = unwrap_weight_wrapper(weights)
-        if weights.dtype != inputs.dtype:
-            weights = weights.to(dtype=inputs.dtype)
-        M, K = inputs.shape
-        n_exp, N, _ = weights.shape
-        E.check_dims("grouped GEMM", M, K, N)
-        x2 = inputs.detach()
-        w3 = weights.detach().contiguous()
-        bounds = [0] + [int(v) for v in offs.tolist()]
-        x_dq = _macro_qdq(x2, -1, use_2dblock_x, use_uos=use_uos)
-        w_axis = -1 if use_2dblock_w else 0
-        pairs = [_macro_qdq(w3[e], -1, use_2dblock_w, use_uos=use_uos, return_codes=True) for e in range(n_exp)]
-        w_dq = torch.stack([p[0] for p in pairs])
-        y = torch.zeros(M, N, dtype=inputs.dtype, device=inputs.device)
-        for e in range(n_exp):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                torch.matmul(x_dq[lo:hi], w_dq[e].t(), out=y[lo:hi])
-        if not use_2dblock_w:
-            pairs = [_macro_qdq(w3[e], 0, False, use_uos=use_uos, return_codes=True) for e in range(n_exp)]
-            w_dq = torch.stack([p[0] for p in pairs])
-        if not use_2dblock_x:
-            xm = hadamard_transform(x2, left_mul=True) if hadamard_transform is not None else x2
-            x_dq = _macro_qdq(xm, 0, False, clip_mode=clip_mode, use_uos=use_uos)
-        w_q = [torch.stack([p[1] for p in pairs])] if use_dge else []
-        ctx.save_for_backward(x_dq, w_dq, *w_q)
-        ctx.bounds, ctx.use_sr_grad, ctx.hadamard_transform = bounds, use_sr_grad, hadamard_transform
-        ctx.use_2dblock_x, ctx.clip_mode, ctx.use_uos, ctx.use_dge = use_2dblock_x, clip_mode, use_uos, use_dge
-        ctx.w_packed_axis = -1 if w_axis == -1 else 1    # axis of the stacked [E, ...] codes
-        return y
-
-    @staticmethod
-    def backward(ctx, grad_output):
-        from .mxfp4 import _dge_factor_from_codes, _macro_qdq
-        x_dq, w_dq = ctx.saved_tensors[:2]
-        n_exp, N, K = w_dq.shape
-        g2 = grad_output.contiguous()
-        if ctx.use_2dblock_x:
-            g_dq = g_m_dq = _macro_qdq(g2, -1, True, ctx.use_sr_grad, use_uos=ctx.use_uos)
-        else:
-            g_dq = _macro_qdq(g2, -1, False, ctx.use_sr_grad, use_uos=ctx.use_uos)
-            gm = ctx.hadamard_transform(g2, left_mul=True) if ctx.hadamard_transform is not None else g2
-            g_m_dq = _macro_qdq(gm, 0, False, ctx.use_sr_grad, clip_mode=ctx.clip_mode, use_uos=ctx.use_uos)
-        dx = torch.zeros(g2.shape[0], K, dtype=g2.dtype, device=g2.device)
-        dw = torch.zeros(n_exp, N, K, dtype=g2.dtype, device=g2.device)
-        for e in range(n_exp):
-            lo, hi = ctx.bounds[e], ctx.bounds[e + 1]
-            if hi > lo:
-                torch.matmul(g_dq[lo:hi], w_dq[e], out=dx[lo:hi])
-                torch.matmul(g_m_dq[lo:hi].t(), x_dq[lo:hi], out=dw[e])
-        if ctx.use_dge:
-            dw = dw * _dge_factor_from_codes(ctx.saved_tensors[2], ctx.w_packed_axis, dw.dtype).to(dw.dtype)
-        return dx, dw, None, None, None, None, None, None, None, None
-
-
 def _quantize_then_mxfp_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2dblock_w: bool, use_sr_grad: bool,
                                           use_dge: bool, use_hadamard: bool, clip_mode: str,
                                           use_macro_block_scaling: bool, use_uos: bool = False) -> torch.Tensor:
@@ -260,8 +191,9 @@ def _quantize_then_mxfp_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2
         raise ValueError(f"unknown clip_mode {clip_mode!r}")
     had = _hadamard(use_hadamard, use_2dblock_x, B.device)
     if use_macro_block_scaling:
-        return GroupedMacroLinearFunction.apply(A, B.transpose(-2, -1), offs, use_2dblock_w, bool(use_sr_grad), had,
-                                                bool(use_2dblock_x), clip_mode, bool(use_uos), bool(use_dge))
+        from ._two_level import GroupedTwoLevelFunction
+        return GroupedTwoLevelFunction.apply(A, B.transpose(-2, -1), offs, bool(use_2dblock_w), bool(use_sr_grad), had,
+                                             bool(use_2dblock_x), clip_mode, bool(use_uos), bool(use_dge))
     return GroupedLinearFunction.apply(A, B.transpose(-2, -1), offs, L.FMT_MXFP4, L.FMT_MXFP4, use_2dblock_x,
                                        use_2dblock_w, bool(use_sr_grad), False, had, bool(use_uos), clip_mode,
                                        bool(use_dge))

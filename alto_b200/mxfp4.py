@@ -14,6 +14,7 @@ import torch
 from . import _lib as L
 from . import _linear as E
 from . import _quant as Q
+from . import _two_level as T
 from .hadamard import HadamardFactory, HadamardTransform
 from .macro_block_scaling import macro_block_descaling, macro_block_scaling
 from .nvfp4 import unwrap_weight_wrapper
@@ -117,80 +118,17 @@ def blockwise_mxfp4_gemm(
 
 def _macro_qdq(t: torch.Tensor, axis: int, is_2d: bool, use_sr: bool = False, clip_mode: str = "none",
                use_uos: bool = False, return_codes: bool = False):
-    """macro-block scale -> MXFP4 quantise -> dequantise -> macro-block descale, in t's dtype: what
-    the reference's two-level ("blockwise") MXFP4 recipe feeds its matmuls
-    (alto/kernels/fp4/mxfp4/mxfp_linear.py:301-302, 335-354).  ``clip_mode`` goes to the quantizer and
-    the dequantizer (the static clip is undone there), ``use_uos`` to the quantizer."""
+    """macro-block scale -> MXFP4 quantise -> dequantise -> macro-block descale, in t's dtype: the
+    operand values the reference's two-level ("blockwise") MXFP4 recipe feeds its emulation matmuls
+    (alto/kernels/fp4/mxfp4/mxfp_linear.py:301-302, 335-354).  Not on the linear path here (the
+    two-level GEMM consumes the codes and factors directly); kept as a public composition of the
+    four ops.  ``clip_mode`` goes to the quantizer and the dequantizer (the static clip is undone
+    there), ``use_uos`` to the quantizer."""
     scaled, mbs = macro_block_scaling(t, axis=axis, use_2d_block=is_2d)
     q, s = convert_to_mxfp4(scaled, axis=axis, is_2d_block=is_2d, use_sr=use_sr, clip_mode=clip_mode, use_uos=use_uos)
     dq = convert_from_mxfp4(q, s, t.dtype, axis=axis, is_2d_block=is_2d, clip_mode=clip_mode)
     out = macro_block_descaling(dq, mbs, axis=axis, use_2d_block=is_2d)
     return (out, q) if return_codes else out
-
-
-def _dge_factor_from_codes(q: torch.Tensor, packed_axis: int, dtype: torch.dtype) -> torch.Tensor:
-    """Per-element DGE factor of a weight from its packed E2M1 codes (two per byte along ``packed_axis``):
-    the table of ``alto_b200.dge`` gathered with tensor ops, for the flows that hold no GEMM operand."""
-    from . import dge
-    table = torch.tensor(dge.fp4_bin_table(q.device, dtype), dtype=torch.float32, device=q.device)
-    b = q.view(torch.uint8).movedim(packed_axis, -1)
-    codes = torch.stack([b & 0xF, b >> 4], dim=-1).reshape(*b.shape[:-1], b.shape[-1] * 2)
-    return table[codes.long()].movedim(-1, packed_axis)
-
-
-def _macro_forward(ctx, x, weight, use_2dblock_x, use_2dblock_w, use_sr_grad, hadamard_transform,
-                   clip_mode: str = "none", use_uos: bool = False, use_dge: bool = False):
-    """Two-level scaled forward.  The macro factors are not powers of two and differ per row and
-    per 128 columns, so they cannot ride on the E8M0 scales of the block-scaled MMA; the reference
-    itself refuses this recipe on its FP4 matrix cores and multiplies the de-quantised, de-scaled
-    operands in the input dtype (alto/kernels/fp4/mxfp4/mxfp_linear.py:321-356).  Same here: the
-    quantise / de-quantise chain runs in this library's kernels, the matmul is a plain bf16 GEMM.
-    Options as in the reference's flow: ``use_uos`` on every operand, ``clip_mode`` on the two
-    token-axis operands (:383-390, 491-498), the DGE factor from the codes of the weight operand of
-    dgrad (:546-566)."""
-    original_shape = x.shape
-    x2 = x.detach().reshape(-1, original_shape[-1])
-    w2 = weight.detach()
-    M, K = x2.shape
-    N = w2.shape[0]
-    E.check_dims("MXFP4LinearFunction", M, K, N)
-    x_dq = _macro_qdq(x2, -1, use_2dblock_x, use_uos=use_uos)
-    w_dq, w_q = _macro_qdq(w2, -1, use_2dblock_w, use_uos=use_uos, return_codes=True)
-    w_packed_axis = -1
-    y = x_dq @ w_dq.t()
-    if not use_2dblock_w:
-        w_dq, w_q = _macro_qdq(w2, 0, False, use_uos=use_uos, return_codes=True)
-        w_packed_axis = 0
-    if not use_2dblock_x:
-        xm = hadamard_transform(x2, left_mul=True) if hadamard_transform is not None else x2
-        x_dq = _macro_qdq(xm, 0, False, clip_mode=clip_mode, use_uos=use_uos)
-    ctx.save_for_backward(x_dq, w_dq, *([w_q] if use_dge else []))
-    ctx.macro = True
-    ctx.use_2dblock_x = use_2dblock_x
-    ctx.use_sr_grad = use_sr_grad
-    ctx.hadamard_transform = hadamard_transform
-    ctx.clip_mode, ctx.use_uos, ctx.use_dge, ctx.w_packed_axis = clip_mode, use_uos, use_dge, w_packed_axis
-    return y.view(*original_shape[:-1], N)
-
-
-def _macro_backward(ctx, grad_output):
-    """alto/kernels/fp4/mxfp4/mxfp_linear.py:436-566, the branch without FP4 matrix cores."""
-    x_dq, w_dq = ctx.saved_tensors[:2]
-    original_shape = grad_output.shape
-    g2 = grad_output.reshape(-1, original_shape[-1])
-    if ctx.use_2dblock_x:
-        g_dq = _macro_qdq(g2, -1, True, ctx.use_sr_grad, use_uos=ctx.use_uos)
-        g_m_dq = g_dq
-    else:
-        g_dq = _macro_qdq(g2, -1, False, ctx.use_sr_grad, use_uos=ctx.use_uos)
-        gm = ctx.hadamard_transform(g2, left_mul=True) if ctx.hadamard_transform is not None else g2
-        g_m_dq = _macro_qdq(gm, 0, False, ctx.use_sr_grad, clip_mode=ctx.clip_mode, use_uos=ctx.use_uos)
-    grad_inputs = g_dq @ w_dq
-    grad_weights = g_m_dq.t() @ x_dq
-    if ctx.use_dge:
-        grad_weights = grad_weights * _dge_factor_from_codes(ctx.saved_tensors[2], ctx.w_packed_axis,
-                                                             grad_weights.dtype).to(grad_weights.dtype)
-    return grad_inputs.view(*original_shape[:-1], -1), grad_weights
 
 
 class MXFP4LinearFunction(torch.autograd.Function):
@@ -207,10 +145,9 @@ class MXFP4LinearFunction(torch.autograd.Function):
             weight = weight.to(dtype=x.dtype)
         ctx.macro = False
         if use_macro_block_scaling:
-            if not x.is_cuda:
-                raise RuntimeError("MXFP4LinearFunction runs on CUDA tensors only (no CPU fallback)")
-            return _macro_forward(ctx, x, weight, use_2dblock_x, use_2dblock_w, bool(use_sr_grad),
-                                  hadamard_transform, clip_mode, bool(use_uos), bool(use_dge))
+            ctx.macro = True
+            return T.linear_forward(ctx, x, weight, bool(use_2dblock_x), bool(use_2dblock_w), bool(use_sr_grad),
+                                    hadamard_transform, clip_mode, bool(use_uos), bool(use_dge))
         return E.linear_forward(ctx, "MXFP4LinearFunction", x, weight, L.FMT_MXFP4, use_2dblock_x=use_2dblock_x,
                                 use_2dblock_w=use_2dblock_w, use_sr_grad=bool(use_sr_grad), use_outer_scale=False,
                                 hadamard_transform=hadamard_transform, use_uos=bool(use_uos), clip_mode=clip_mode,
@@ -218,7 +155,7 @@ class MXFP4LinearFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        gi, gw = _macro_backward(ctx, grad_output) if ctx.macro else E.linear_backward(ctx, grad_output)
+        gi, gw = T.linear_backward(ctx, grad_output) if ctx.macro else E.linear_backward(ctx, grad_output)
         return gi, gw, None, None, None, None, None, None, None, None
 
 

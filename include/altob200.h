@@ -163,8 +163,9 @@ int altob200_amax(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, i
  *  - the input is limited to ALTOB200_NOALLOC_MAX_BYTES (one array slot per 64 KiB
  *    of input); larger inputs are refused with ALTOB200_ELIMIT before any launch;
  *  - the first call on each device looks up the array's device address
- *    (cudaGetSymbolAddress, with that device current); make that first call before
- *    starting any stream capture;
+ *    (cudaGetSymbolAddress, with that device current) and keeps it; make that first
+ *    call before starting any stream capture, and do not call again on a device
+ *    after cudaDeviceReset in the same process (the kept address is then stale);
  *  - all calls on one device share the array: two calls whose kernels may overlap on
  *    the GPU (different streams, no dependency between them) race and give wrong
  *    results; calls on one stream are safe, and each call resets what it needs.
@@ -390,6 +391,89 @@ int altob200_grouped_gemm_wgrad_blockscaled(int32_t format_a, int32_t format_b, 
                                             const void* b_codes, const void* b_scales, const int32_t* k_offs,
                                             const float* alpha_a, const float* alpha_b, int32_t out_dtype,
                                             void* d, int64_t ldd, void* stream);
+
+/*
+ * Macro-block factors of one MXFP4 operand [rows, K] of the two-level GEMMs below: the uint8 codes
+ * altob200_macro_block_scaling wrote (factor = 1 + code / 256 in [1, 2), one per 128 elements of K).
+ * The code of (row r, chunk c = k / 128) sits at
+ *     codes[(r >> row_shift) * row_stride + c * chunk_stride  (+ expert * expert_stride)]
+ * so that every scale tensor of the reference can be passed as it is, without a transposed copy:
+ *   blocks along the operand's K axis, one per row   [rows, ceil(K/128)]             -> shift 0, strides (ceil(K/128), 1)
+ *   128 x 128 tiles of an operand stored [rows, K]   [ceil(rows/128), ceil(K/128)]   -> shift 7, strides (ceil(K/128), 1)
+ *   128 x 128 tiles of the TRANSPOSED operand (W along N for dgrad: rows = in-features,
+ *   K = out-features, tiles indexed [out/128, in/128])                               -> shift 7, strides (1, ceil(rows/128))
+ * `expert_stride` (B operand of the row-grouped form only) is the distance between two experts' code
+ * matrices.
+ */
+typedef struct altob200_macro_scale {
+  const uint8_t* codes;
+  int64_t row_stride;
+  int64_t chunk_stride;
+  int64_t expert_stride;
+  int32_t row_shift; /* 0 or 7 */
+} altob200_macro_scale;
+
+/*
+ * MXFP4 GEMM with two-level ("blockwise" macro-block) scaling on tcgen05:
+ *   D[m, n] = out_scale * sum over chunks c of 128 along K of
+ *             (sum_{k in c} A[m, k] * B[n, k]) / (fa[m, c] * fb[n, c])
+ * Operand layouts as altob200_gemm_blockscaled (format MXFP4 on both sides).  Each chunk is
+ * accumulated by the block-scaled MMA in tensor memory and folded into an fp32 result in registers
+ * with the reciprocal factors.  Replaces the flow the reference uses where no matrix core takes the
+ * macro factors: macro_block_descaling of the de-quantised operands followed by a bf16 matmul
+ * (alto/kernels/fp4/mxfp4/mxfp_linear.py:337-356 forward, :496-547 backward;
+ * alto/kernels/fp4/mxfp4/macro_block_scaling.py:100-146).  `out_scale` is a host float (1, or 16/9
+ * for a weight gradient whose two operands were clipped statically, mxfp_linear.py:543-544).
+ * K must be a multiple of 32; a last chunk shorter than 128 takes the factor of its own code.
+ */
+int altob200_gemm_mxfp4_two_level(int64_t M, int64_t N, int64_t K, const void* a_codes, const void* a_scales,
+                                  const altob200_macro_scale* a_macro, const void* b_codes, const void* b_scales,
+                                  const altob200_macro_scale* b_macro, float out_scale, int32_t out_dtype, void* d,
+                                  int64_t ldd, void* stream);
+
+/*
+ * Row-grouped (MoE forward / dgrad) form of the above: `group_expert` as in
+ * altob200_grouped_gemm_blockscaled, B and its scales stacked per expert, `b_macro->expert_stride`
+ * between the experts' factor codes.  Replaces cg_grouped_gemm_forward / cg_grouped_gemm_backward_inputs
+ * on de-scaled operands (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_backward.py:668-690, 897-901).
+ */
+int altob200_grouped_gemm_mxfp4_two_level(int64_t M, int64_t N, int64_t K, int32_t num_experts, const void* a_codes,
+                                          const void* a_scales, const altob200_macro_scale* a_macro,
+                                          const void* b_codes, const void* b_scales,
+                                          const altob200_macro_scale* b_macro, const int32_t* group_expert,
+                                          float out_scale, int32_t out_dtype, void* d, int64_t ldd, void* stream);
+
+/*
+ * Grouped weight gradient with two-level scaling: as altob200_grouped_gemm_wgrad_blockscaled, the
+ * shared reduction axis (tokens, length K) cut into per-expert ranges by `k_offs`; chunk c of the
+ * factor codes is the absolute 128-token block c of the buffer.  Replaces
+ * cg_grouped_gemm_backward_weights on de-scaled operands
+ * (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_backward.py:902-909).
+ */
+int altob200_grouped_gemm_wgrad_mxfp4_two_level(int64_t M, int64_t N, int64_t K, int32_t num_experts,
+                                                const void* a_codes, const void* a_scales,
+                                                const altob200_macro_scale* a_macro, const void* b_codes,
+                                                const void* b_scales, const altob200_macro_scale* b_macro,
+                                                const int32_t* k_offs, float out_scale, int32_t out_dtype, void* d,
+                                                int64_t ldd, void* stream);
+
+/*
+ * Failure detection of the GEMM kernels.  Every mbarrier wait inside them is bounded by a wall-clock
+ * limit (default 4 s); a wait that runs out records {kernel, block, site} in the status word that
+ * altob200_status_read returns, and the kernel leaves through its normal teardown.
+ * altob200_set_wait_limit_ns changes the limit for later launches of this process.  The reference
+ * has no counterpart (its Triton kernels do not wait on one another).
+ */
+int altob200_set_wait_limit_ns(uint64_t limit_ns);
+
+/*
+ * Launches one small kernel whose single wait can never be satisfied (an mbarrier on which nobody
+ * arrives) with the given limit (at most 1e9 ns).  Nothing faults and nothing is left running: the
+ * wait gives up after `limit_ns`, and the next altob200_status_read on the stream returns
+ * ALTOB200_ETIMEOUT_DEVICE with detail {9, 0, 99, 0}, the one after that 0.  For tests of the
+ * host-side handling of a device timeout.  No counterpart in the reference.
+ */
+int altob200_selftest_wait_timeout(uint64_t limit_ns, void* stream);
 
 #ifdef __cplusplus
 }

@@ -337,3 +337,30 @@ def test_gemm_ragged_tiles_over_many_waves(M, N, K, out_dtype):
         tol = 1e-5 * ref.abs().max() if out_dtype == torch.float32 else ref.abs() * 2.0 ** -7 + 1e-30
         bad = diff > tol
         assert int(bad.sum()) == 0, f"{int(bad.sum())} entries differ, first at {torch.nonzero(bad)[:4].tolist()}"
+
+
+def test_bounded_device_wait_times_out_and_is_reported():
+    """Failure detection without a fault: a kernel whose only wait can never be satisfied (an mbarrier
+    nobody arrives on) gives up after its limit, leaves through its normal exit, and the status word
+    reports ETIMEOUT with {kernel, block, site}; the word is sticky until read, then clear; the
+    context stays usable."""
+    from alto_b200 import _lib as L
+    st, _ = L.status_read()
+    assert st == 0
+    L.selftest_wait_timeout(1_000_000)          # 1 ms
+    st, detail = L.status_read()
+    assert st == L.E_TIMEOUT, (st, detail)
+    assert detail[:3] == [9, 0, 99]
+    assert "wait" in L.status_string(st) or "time" in L.status_string(st).lower()
+    st, detail = L.status_read()
+    assert st == 0 and detail[:3] == [0, 0, 0]
+    # the context is intact: a real GEMM still runs and the limit can be changed and restored
+    L.set_wait_limit_ns(2_000_000_000)
+    a = torch.randn(128, 128, device="cuda").bfloat16()
+    from alto_b200 import mxfp4 as MX
+    y = MX._to_mxfp4_then_scaled_mm(a, a, False, True, False, False, "none", False)
+    assert torch.isfinite(y.float()).all()
+    L.set_wait_limit_ns(4_000_000_000)
+    assert L.status_read()[0] == 0
+    with pytest.raises(L.Altob200Error):
+        L.selftest_wait_timeout(5_000_000_000)  # limits above one second are refused

@@ -79,6 +79,50 @@ def test_grouped_gemm_matches_oracle(scheme, use_2dblock_w):
     assert torch.all(dw[1] == 0), "an expert without tokens must get a zero weight gradient"
 
 
+@pytest.mark.parametrize("use_2dblock_x,use_2dblock_w,use_hadamard,use_sr", [
+    (False, True, True, True),      # the MoE recipe: 2-D weight blocks, rotated token-axis operands, SR gradients
+    (False, False, False, False), (True, True, False, True)])
+@pytest.mark.parametrize("K,N", [(256, 384), (320, 288)])
+def test_two_level_grouped_gemm_matches_oracle(use_2dblock_x, use_2dblock_w, use_hadamard, use_sr, K, N):
+    """MXFP4 grouped forward, dgrad and wgrad with two-level (macro-block) scaling on the tensor cores
+    against the oracle's whole-buffer chains and per-expert fp32 contractions
+    (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_backward.py:631-909).  K = 320 and N = 288 end in chunks
+    shorter than 128 and in ragged output tiles; one expert has no tokens; rows past offs[-1] are padding."""
+    from alto_b200 import _lib as L
+    from alto_b200 import _linear as E, grouped as G
+    from alto_b200.hadamard import HadamardFactory
+    x, w, dy, offs, M = _case(K=K, N=N)
+    n_exp = w.shape[0]
+    d = _dev()
+    xd = x.to(d).requires_grad_(True)
+    B = w.to(d).transpose(-2, -1).contiguous().requires_grad_(True)
+    W_had = None
+    if use_hadamard:
+        HadamardFactory.configure(block_size=32, randomized=True, dtype=torch.float32, seed=0)
+        W_had = HadamardFactory.create_transform(device=d).matrix().cpu()
+        HadamardFactory.configure(block_size=32, randomized=True, dtype=torch.float32, seed=0)
+    rn = rm = None
+    if use_sr:
+        rn, rm = rand_u32((2, M, N // 2), 51), rand_u32((2, N, M // 2), 52)
+    bits = {"dy_n": None if rn is None else _u32dev(rn), "dy_m": None if rm is None else _u32dev(rm)}
+    with E.explicit_sr_bits(lambda name, shape, dev: bits[name]):
+        y = G._quantize_then_mxfp_scaled_grouped_mm(xd, B, offs.to(d), use_2dblock_x, use_2dblock_w, use_sr, False,
+                                                    use_hadamard, "none", True)
+        y.backward(dy.to(d))
+    st, detail = L.status_read()
+    assert st == 0, detail
+    yo, dxo, dwo = O.mxfp4_macro_grouped_linear(x, w, offs, dy, use_2dblock_x=use_2dblock_x,
+                                                use_2dblock_w=use_2dblock_w, W_had=W_had,
+                                                operand_dtype=torch.float32, rand_dy_n=rn, rand_dy_m=rm)
+    dw = B.grad.transpose(-2, -1)
+    assert _rel(y, yo.bfloat16().float()) <= REL_TOL
+    assert _rel(xd.grad, dxo.bfloat16().float()) <= REL_TOL
+    assert _rel(dw, dwo.bfloat16().float()) <= REL_TOL
+    last = int(offs[-1])
+    assert torch.all(y[last:] == 0) and torch.all(xd.grad[last:] == 0)
+    assert torch.all(dw[1] == 0), "an expert without tokens must get a zero weight gradient"
+
+
 def test_single_expert_equals_dense_linear():
     """tests/unittest/nvfp4/test_nvfp_grouped_gemm.py:384-420."""
     from alto_b200 import grouped as G, nvfp4 as NV

@@ -84,38 +84,90 @@ def test_macro_qdq_chain_is_bit_exact(axis, is2d):
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
 
 
+def _rel(a, b):
+    return ((a.detach().float().cpu() - b).norm() / b.norm()).item()
+
+
+def _u32dev(r):
+    return torch.from_numpy((r.numpy() & 0xFFFFFFFF).astype(np.uint32).view(np.int32)).cuda()
+
+
+# Two tolerances.  1e-3: against the dequantise-to-fp32, descale-in-fp32, fp32-matmul definition of the
+# contraction (the bar for every block-scaled GEMM of this library); the kernel folds exact chunk sums
+# with fp32 reciprocal factors, so what is left is fp32 rounding and the bf16 output.  1e-2: against the
+# reference's emulation of the recipe, which rounds every de-scaled operand to bf16 before its matmul
+# (alto/kernels/fp4/mxfp4/mxfp_linear.py:337-356); that rounding alone moves the result by about 2e-3,
+# and the reference's own test of this recipe uses rtol 1e-2.
+TOL_FP32_DEFINITION = 1e-3
+TOL_BF16_EMULATION = 1e-2
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("use_2dblock_x,use_2dblock_w,use_hadamard", [(False, True, True), (False, False, False),
-                                                                      (True, True, False)])
-def test_two_level_blockwise_linear_matches_oracle(use_2dblock_x, use_2dblock_w, use_hadamard):
-    """two_level_scaling='blockwise': operands are bit-identical to the oracle's, so the only
-    difference is the bf16 GEMM's accumulation order and output rounding (rel. Frobenius 1e-2 =
-    a few bf16 ulps; the reference's own test of this recipe uses rtol 1e-2)."""
+@pytest.mark.parametrize("shape", [(256, 384, 128), (256, 320, 160), (384, 576, 288)])
+@pytest.mark.parametrize("use_2dblock_x,use_2dblock_w,use_hadamard,use_sr", [
+    (False, True, True, False), (False, False, False, False), (True, True, False, False),
+    (False, True, True, True), (True, False, False, True)])
+def test_two_level_blockwise_linear_matches_oracle(shape, use_2dblock_x, use_2dblock_w, use_hadamard, use_sr):
+    """two_level_scaling='blockwise' on the tensor cores: forward, dgrad and wgrad against the oracle.
+    Shapes include reduction axes that end in a chunk shorter than 128 (320, 576, 160, 288) and
+    outputs whose last 128 x 128 tile is ragged."""
+    from alto_b200 import _lib as L
+    from alto_b200 import _linear as E
     from alto_b200 import mxfp4 as MX
     from alto_b200.hadamard import HadamardFactory
-    M, K, N = 256, 384, 128
+    from tests.helpers import rand_u32
+    M, K, N = shape
     g = torch.Generator().manual_seed(11)
-    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    x = (torch.randn(M, K, generator=g) * torch.exp(torch.randn(M, 1, generator=g))).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
     dy = torch.randn(M, N, generator=g).to(torch.bfloat16)
     HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=3)
     xd = x.cuda().requires_grad_(True)
     wd = w.cuda().requires_grad_(True)
-    y = MX._to_mxfp4_then_scaled_mm(xd, wd, use_2dblock_x, use_2dblock_w, False, False, "none", use_hadamard,
-                                    use_macro_block_scaling=True)
-    y.backward(dy.cuda())
+    rn = rm = None
+    if use_sr:
+        rn, rm = rand_u32((2, M, N // 2), 41), rand_u32((2, N, M // 2), 42)
+    bits = {"dy_n": None if rn is None else _u32dev(rn), "dy_m": None if rm is None else _u32dev(rm)}
+    with E.explicit_sr_bits(lambda name, shp, dev: bits[name]):
+        y = MX._to_mxfp4_then_scaled_mm(xd, wd, use_2dblock_x, use_2dblock_w, use_sr, False, "none", use_hadamard,
+                                        use_macro_block_scaling=True)
+        y.backward(dy.cuda())
+    st, detail = L.status_read()
+    assert st == 0, detail
     W_had = None
     if use_hadamard:
         HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=3)
         W_had = HadamardFactory.create_transform(device=torch.device("cuda")).matrix().cpu()
-    yo, dxo, dwo = O.mxfp4_macro_linear(x, w, dy, use_2dblock_x=use_2dblock_x, use_2dblock_w=use_2dblock_w,
-                                        W_had=W_had)
-
-    def rel(a, b):
-        return ((a.float().cpu() - b).norm() / b.norm()).item()
-
+    kw = dict(use_2dblock_x=use_2dblock_x, use_2dblock_w=use_2dblock_w, W_had=W_had, rand_dy_n=rn, rand_dy_m=rm)
     assert y.dtype == torch.bfloat16 and y.shape == (M, N)
-    assert rel(y, yo) <= 1e-2 and rel(xd.grad, dxo) <= 1e-2 and rel(wd.grad, dwo) <= 1e-2
+    yo, dxo, dwo = O.mxfp4_macro_linear(x, w, dy, operand_dtype=torch.float32, **kw)
+    assert _rel(y, yo.bfloat16().float()) <= TOL_FP32_DEFINITION
+    assert _rel(xd.grad, dxo.bfloat16().float()) <= TOL_FP32_DEFINITION
+    assert _rel(wd.grad, dwo.bfloat16().float()) <= TOL_FP32_DEFINITION
+    yo, dxo, dwo = O.mxfp4_macro_linear(x, w, dy, **kw)
+    assert _rel(y, yo) <= TOL_BF16_EMULATION and _rel(xd.grad, dxo) <= TOL_BF16_EMULATION
+    assert _rel(wd.grad, dwo) <= TOL_BF16_EMULATION
+
+
+@pytest.mark.gpu
+def test_two_level_gemm_fp32_output_and_factor_layouts():
+    """The C-ABI GEMM alone with fp32 output, factor codes per row on one side and per 128 x 128 tile
+    (read through the transposed strides) on the other, against float64 arithmetic on the codes."""
+    from alto_b200 import _lib as L
+    from alto_b200 import _two_level as T
+    g = torch.Generator().manual_seed(21)
+    M, K, N = 200 + 56, 448, 320
+    a = (torch.randn(M, K, generator=g) * torch.exp(torch.randn(M, 1, generator=g))).bfloat16()
+    b = torch.randn(K, N, generator=g).bfloat16()          # B^T is the operand: rows n, reduction k
+    a_op = T.rows_operand(a.cuda(), False)
+    _, b_op = T.tiles_operands(b.cuda(), False)              # operand [N, K] of the 2-D quantised [K, N] tensor
+    out = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    L.gemm_mxfp4_two_level(M, N, K, a_op.codes, a_op.scales, a_op.macro, b_op.codes, b_op.scales, b_op.macro, out,
+                           out_scale=0.5)
+    a_dq = O.macro_qdq(a, -1, False, out_dtype=torch.float32).double()
+    b_dq = O.macro_qdq(b, -1, True, out_dtype=torch.float32).double()
+    want = 0.5 * (a_dq @ b_dq)
+    assert ((out.cpu().double() - want).norm() / want.norm()).item() <= 1e-5
 
 
 @pytest.mark.gpu
@@ -133,12 +185,10 @@ def test_two_level_blockwise_linear_with_clip_uos_and_dge(clip_mode, use_uos):
     y = MX._to_mxfp4_then_scaled_mm(xd, wd, False, True, False, False, clip_mode, False, True, use_uos)
     y.backward(dy.cuda())
     yo, dxo, dwo = O.mxfp4_macro_linear(x, w, dy, use_2dblock_x=False, use_2dblock_w=True, clip_mode=clip_mode,
-                                        use_uos=use_uos)
-
-    def rel(a, b):
-        return ((a.float().cpu() - b).norm() / b.norm()).item()
-
-    assert rel(y, yo) <= 1e-2 and rel(xd.grad, dxo) <= 1e-2 and rel(wd.grad, dwo) <= 1e-2
+                                        use_uos=use_uos, operand_dtype=torch.float32)
+    assert _rel(y, yo.bfloat16().float()) <= TOL_FP32_DEFINITION
+    assert _rel(xd.grad, dxo.bfloat16().float()) <= TOL_FP32_DEFINITION
+    assert _rel(wd.grad, dwo.bfloat16().float()) <= TOL_FP32_DEFINITION
     # with use_dge the weight gradient is multiplied by the table entry of each weight code (all about 1/5)
     x2, w2 = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
     MX._to_mxfp4_then_scaled_mm(x2, w2, False, True, False, True, clip_mode, False, True, use_uos).backward(dy.cuda())

@@ -101,3 +101,34 @@ def test_mxfp4_linear_with_options_matches_oracle(clip, uos):
     assert rel(y, yo.bfloat16().float()) <= 1e-3
     assert rel(xd.grad, dxo.bfloat16().float()) <= 1e-3
     assert rel(wd.grad, dwo.bfloat16().float()) <= 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("grouped", [False, True])
+def test_static_clip_with_2d_activation_blocks_leaves_the_weight_gradient_unscaled(grouped):
+    """With use_2dblock_x the activations and gradients are quantised once in 32 x 32 blocks and no
+    operand takes the clip mode (alto/kernels/fp4/mxfp4/mxfp_linear.py:310-315, 436-452), so the
+    16/9 that undoes the static clip of the 1-D token-axis operands must not be applied to dW."""
+    from alto_b200 import grouped as G
+    from alto_b200 import mxfp4 as MX
+    M, K, N = 256, 256, 128
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    dy = torch.randn(M, N, generator=g).bfloat16()
+    xd, wd = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    if grouped:
+        offs = torch.tensor([M], dtype=torch.int32, device="cuda")
+        B = wd.unsqueeze(0).transpose(-2, -1)
+        y = G._quantize_then_mxfp_scaled_grouped_mm(xd, B, offs, True, True, False, False, False, "static", False)
+    else:
+        y = MX._to_mxfp4_then_scaled_mm(xd, wd, True, True, False, False, "static", False, False, False)
+    y.backward(dy.cuda())
+
+    def qdq(t):
+        q, s = O.quantize_mxfp4(t, 32, -1, True)
+        return O.dequantize_mxfp4(q, s, torch.float32, 32, -1, True)
+
+    dwo = qdq(dy).t() @ qdq(x)
+    rel = ((wd.grad.float().cpu() - dwo.bfloat16().float()).norm() / dwo.norm()).item()
+    assert rel <= 1e-3, rel

@@ -44,6 +44,12 @@ def test_noalloc_amax_matches_regular_entry_point_twice_in_a_row():
         torch.cuda.synchronize()
         assert torch.equal(got_bits, want_bits), (got_bits, want_bits)
         assert torch.equal(got_outer, want_outer), (got_outer, want_outer)
+        # and against plain tensor arithmetic, independent of this library: the fp32 bit pattern of
+        # max |x| and the outer scale max(amax / (448 * 6), 1e-30) divided on the CPU (correctly rounded)
+        amax = x.abs().amax().float().cpu()
+        assert got_bits.cpu().item() == amax.view(torch.int32).item()
+        want = torch.clamp(amax / (448.0 * 6.0), min=1e-30)
+        assert got_outer.cpu().view(torch.int32).item() == want.view(torch.int32).item()
     # a strided view (leading dimension larger than the row) and a NaN, which must give amax 0 ->
     # the floor of the outer scale, exactly like the regular entry point
     x3 = x1[:, :2048]
