@@ -16,7 +16,8 @@
 //   warpgroup 0   warp 0: producer - per stage (128 bytes of K = two chunks) two tiled TMA loads and the
 //                 bulk copies of the stage's scale tiles; warp 1: MMA issuer - two tcgen05.mma per chunk
 //                 into one of three 128-column chunk accumulators in tensor memory, then a commit to that
-//                 accumulator's "full" barrier; warps 2, 3 idle;
+//                 accumulator's "full" barrier; warp 2: waits on the shared-memory barriers for the MMA issuer
+//                 and releases it once per stage through a named barrier; warp 3 idle;
 //   warpgroup 1   scale transfer shared memory -> tensor memory (as in the plain kernel);
 //   warpgroups 2, 3  fold + epilogue: each warp owns 32 rows x 64 columns of the tile in 64 registers per
 //                 thread.  Per chunk it reads the chunk accumulator (tcgen05.ld in two halves, one in
@@ -56,7 +57,12 @@ struct MacroGemmArgs {
 #define PROF_FLUSH(role)                                                                   \
   if (margs.prof != nullptr)                                                               \
     for (int i_ = 0; i_ < 8; ++i_) margs.prof[((size_t)blockIdx.x * 4 + (role)) * 8 + i_] = prof_c[i_]
+// event trace of CTA 0: clock of event k of step idx (< 128) of a role, after the per-CTA sums
+#define PROF_TRACE(role, idx, k)                                                            \
+  if (margs.prof != nullptr && blockIdx.x == 0 && (idx) < 128u)                              \
+  margs.prof[(size_t)gridDim.x * 32 + (((role) * 128 + (idx)) * 4 + (k))] = (unsigned long long)clock64()
 #else
+#define PROF_TRACE(role, idx, k)
 #define PROF_DECL
 #define PROF_NOW() 0
 #define PROF_ADD(slot, t0) (void)(t0)
@@ -93,15 +99,6 @@ struct CfgMacro {
   // registers per thread after the warpgroups have re-divided the file: 2 x 128 x 40 + 2 x 128 x 216 = 65536
   static constexpr int REGS_SMALL = 40, REGS_FOLD = 216;
 };
-
-template <int N>
-__device__ __forceinline__ void setmaxnreg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void setmaxnreg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
 
 // Tile description plus what the chunk loop needs: the first chunk of the K range, the number of
 // chunks, and MMAs per stage limited to the bytes that exist (also without K ranges).
@@ -217,36 +214,43 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
   if (warp < 4) {
     setmaxnreg_dec<C::REGS_SMALL>();
+    // Producer and MMA issuer: the WHOLE warp runs the loop and waits on the barriers, one elected lane
+    // issues the TMA / tcgen05 instructions.  Those instructions take their operands (descriptors,
+    // addresses, coordinates) from uniform registers; computed by a converged warp from kernel parameters
+    // and loop counters they are uniform values from the start, whereas the same arithmetic inside an
+    // `if (lane == 0)` region yields per-thread values that have to be moved to uniform registers one by
+    // one in front of every instruction (measured: ~270 cycles per tcgen05.mma).
     if (warp == 0) {
       // ------------------------------ producer ------------------------------
-      if (lane == 0) {
-        uint32_t it = 0;
-        bool alive = true;
-        PROF_DECL;
-        const long long t_all = PROF_NOW();
-        for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-          const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
-          const TileInfo& ti = mt.t;
-          if (ti.skip) continue;
-          const int64_t mb = ti.mb, nb = ti.nb;
-          for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
-            const int s = it % C::STAGES;
-            const long long t0 = PROF_NOW();
-            if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 21, args.wait_ns)) {
-              alive = false;
-              break;
-            }
-            PROF_ADD(1, t0);
-            uint8_t* st = smem + s * C::STAGE_BYTES;
-            const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
-            int64_t sf_tiles = args.nct - cb0;
-            if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
-            const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
-            const int32_t kx = (int32_t)(ti.k_byte0 + (int64_t)ks * STAGE_K_BYTES);
-            if (ALTOB200_DBG(args, 4) && it >= (uint32_t)C::STAGES) {
-              mbar_arrive(&full_bar[s]);
-              continue;
-            }
+      const bool elected = elect_one();
+      uint32_t it = 0;
+      bool alive = true;
+      PROF_DECL;
+      const long long t_all = PROF_NOW();
+      for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+        const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
+        const TileInfo& ti = mt.t;
+        if (ti.skip) continue;
+        const int64_t mb = ti.mb, nb = ti.nb;
+        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+          const int s = it % C::STAGES;
+          const long long t0 = PROF_NOW();
+          alive = __all_sync(0xFFFFFFFFu,
+                             mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 21, args.wait_ns));
+          if (!alive) break;
+          PROF_ADD(1, t0);
+          if (lane == 0) { PROF_TRACE(0, it, 0); }
+          uint8_t* st = smem + s * C::STAGE_BYTES;
+          const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
+          int64_t sf_tiles = args.nct - cb0;
+          if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
+          const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
+          const int32_t kx = (int32_t)(ti.k_byte0 + (int64_t)ks * STAGE_K_BYTES);
+          if (ALTOB200_DBG(args, 4) && it >= (uint32_t)C::STAGES) {
+            if (elected) mbar_arrive(&full_bar[s]);
+            continue;
+          }
+          if (elected) {
             mbar_expect_tx(&full_bar[s], C::A_BYTES + C::B_BYTES + 2 * sf_bytes);
             tma_load_2d(st, &tmap_a, kx, (int32_t)(mb * BM), &full_bar[s]);
             tma_load_2d(st + C::A_BYTES, &tmap_b, kx, (int32_t)ti.b_row0, &full_bar[s]);
@@ -255,70 +259,76 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                       &full_bar[s]);
           }
         }
-        PROF_ADD(0, t_all);
-        PROF_FLUSH(0);
       }
+      PROF_ADD(0, t_all);
+      if (lane == 0) { PROF_FLUSH(0); }
     } else if (warp == 1) {
       // ------------------------------ MMA issuer ------------------------------
-      if (lane == 0) {
-        uint32_t it = 0, pc = 0;
-        bool alive = true;
-        const uint32_t smem_base = smem_u32(smem);
-        PROF_DECL;
-        const long long t_all = PROF_NOW();
-        for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-          const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
-          const TileInfo& ti = mt.t;
-          if (ti.skip) continue;
-          for (int ks = 0; ks < ti.k_stages && alive; ++ks, ++it) {
-            const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
-            const int s = it % C::STAGES;
-            long long t0 = PROF_NOW();
-            if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 23, args.wait_ns)) { alive = false; break; }
-            PROF_ADD(1, t0);
-            t0 = PROF_NOW();
-            if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 25, args.wait_ns)) { alive = false; break; }
-            PROF_ADD(2, t0);
-            tc_fence_after();
-            const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;
-            const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
-            const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
-            const uint32_t a_lo = st4 | 0x10000u;
-            const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
+      // Never waits on a shared-memory barrier itself (such a wait between two tcgen05.mma costs ~150
+      // cycles during which the tensor pipe idles): warp 2 waits and meets this warp at named barrier
+      // 1 + stage.
+      const bool elected = elect_one();
+      uint32_t it = 0, pc = 0;
+      bool alive = true;
+      const uint32_t smem_base = smem_u32(smem);
+      PROF_DECL;
+      const long long t_all = PROF_NOW();
+      for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+        const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
+        const TileInfo& ti = mt.t;
+        if (ti.skip) continue;
+        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+          const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
+          const int s = it % C::STAGES;
+          const long long t0 = PROF_NOW();
+          // operands and scales of the stage are in place and the chunk accumulators it writes are drained
+          if (named_barrier_or(1 + s, 64, false)) { alive = false; break; }
+          PROF_ADD(1, t0);
+          tc_fence_after();
+          const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;
+          const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
+          const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
+          const uint32_t a_lo = st4 | 0x10000u;
+          const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
+          const uint32_t buf0 = pc % C::P_BUFS, buf1 = (pc + 1) % C::P_BUFS;
+          if (elected) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              if (j < n_mma && alive) {
-                const int buf = pc % C::P_BUFS;
-                if ((j & 1) == 0) {
-                  // first MMA of a chunk: its accumulator must have been drained by every fold warp
-                  const long long t1 = PROF_NOW();
-                  if (!ALTOB200_DBG(args, 128) &&
-                      !mbar_wait(&p_empty[buf], ((pc / C::P_BUFS) & 1) ^ 1, abort_flag, 22, args.wait_ns))
-                    alive = false;
-                  PROF_ADD(3, t1);
-                  tc_fence_after();
-                }
-                if (alive) {
-                  const int t = j >> 1;
-                  tc_mma<KIND_MXF4>(tmem_base + buf * BN, desc_of(DESC_SW128_HI, a_lo + 2 * j),
-                                    desc_of(DESC_SW128_HI, b_lo + 2 * j), args.idesc[j], (uint32_t)(j & 1),
-                                    sfa_t + t * 4, sfb_t + t * 4);
-                  if (ALTOB200_DBG(args, 512))  // profiling builds only: every MMA issued twice
-                    tc_mma<KIND_MXF4>(tmem_base + buf * BN, desc_of(DESC_SW128_HI, a_lo + 2 * j),
-                                      desc_of(DESC_SW128_HI, b_lo + 2 * j), args.idesc[j], 1u, sfa_t + t * 4,
-                                      sfb_t + t * 4);
-                  if ((j & 1) == 1 || j == n_mma - 1) {
-                    if (!ALTOB200_DBG(args, 256)) tc_commit(&p_full[buf]);
-                    ++pc;
-                  }
-                }
+              if (j < n_mma) {
+                const uint32_t buf = (j < 2) ? buf0 : buf1;
+                tc_mma<KIND_MXF4>(tmem_base + buf * BN, desc_of(DESC_SW128_HI, a_lo + 2 * j),
+                                  desc_of(DESC_SW128_HI, b_lo + 2 * j), args.idesc[j], (uint32_t)(j & 1),
+                                  sfa_t + (j >> 1) * 4, sfb_t + (j >> 1) * 4);
+                if ((j & 1) == 1 || j == n_mma - 1) tc_commit(&p_full[buf]);
               }
             }
             tc_commit(&empty_bar[s]);
           }
+          __syncwarp();
+          pc += (uint32_t)((n_mma + 1) >> 1);
         }
-        PROF_ADD(0, t_all);
-        PROF_FLUSH(1);
+      }
+      PROF_ADD(0, t_all);
+      if (lane == 0) { PROF_FLUSH(1); }
+    } else if (warp == 2) {
+      // ------------------------------ wait warp ------------------------------
+      uint32_t it = 0, pc = 0;
+      bool alive = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+        const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
+        const TileInfo& ti = mt.t;
+        if (ti.skip) continue;
+        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+          const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
+          const int n_chunks = (n_mma + 1) >> 1;
+          const int s = it % C::STAGES;
+          bool ok = mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 23, args.wait_ns);
+          ok = ok && mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 25, args.wait_ns);
+          for (int c = 0; c < n_chunks; ++c, ++pc)
+            ok = ok && mbar_wait(&p_empty[pc % C::P_BUFS], ((pc / C::P_BUFS) & 1) ^ 1, abort_flag, 22, args.wait_ns);
+          const bool failed = !__all_sync(0xFFFFFFFFu, ok);
+          if (named_barrier_or(1 + s, 64, failed)) { alive = false; break; }
+        }
       }
     }
   } else if (warp < 8) {
@@ -338,6 +348,7 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const long long t0 = PROF_NOW();
         if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 26, args.wait_ns)) { alive = false; break; }
         PROF_ADD(1, t0);
+        if (warp == 4 && lane == 0) { PROF_TRACE(2, it, 0); }
         const uint8_t* sf = smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
         const uint32_t sfa_t = tmem_base + lane_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
         const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
@@ -354,6 +365,7 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sf_full[s]);
+        if (warp == 4 && lane == 0) { PROF_TRACE(2, it, 1); }
       }
     }
     PROF_ADD(0, t_all);
@@ -439,6 +451,7 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
           PROF_ADD(6, t0);
           const uint32_t t_p = t_row + (pc % C::P_BUFS) * BN;
+          if (warp == 8 && lane == 0) { PROF_TRACE(3, pc, 0); }
           t0 = PROF_NOW();
           tc_wait_ld();                 // first half of chunk c is in ra_
           PROF_ADD(1, t0);
@@ -453,6 +466,7 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&p_empty[pc % C::P_BUFS]);
+          if (warp == 8 && lane == 0) { PROF_TRACE(3, pc, 1); }
           ++pc;
           PROF_ADD(7, t0);
           if (c + 1 < nch) {

@@ -40,7 +40,7 @@ __device__ int g_status[4] = {0, 0, 0, 0};
 constexpr int BM = 128;
 constexpr int STAGE_K_BYTES = 128;
 constexpr int NUM_THREADS = 320;  // producer, MMA issuer, 4 epilogue warps, 4 scale-transfer warps
-constexpr int NUM_THREADS_PAIR = 448;  // pair kernel: 4 more epilogue warps (each group drains 128 columns)
+constexpr int NUM_THREADS_PAIR = 512;  // pair kernel: four warpgroups (see the kernel)
 constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // default limit of one wait: 4 s
 
 enum { KIND_NVF4 = 0, KIND_MXF4 = 1, KIND_MXF8 = 2 };
@@ -118,7 +118,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
+#ifdef ALTOB200_WAIT_SPIN
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -131,22 +135,22 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 // Bounded wait.  Returns false (and raises the abort flag) when the limit passes or when
-// another role already aborted.  The wall clock (%globaltimer, a slow read) is consulted only
-// every 64 failed polls, and for the first time after 64 of them, so a wait that is satisfied
-// soon never pays for a timer read; the limit is counted from that first read.
+// another role already aborted.  The limit is counted on the SM's cycle counter (a register
+// read); %globaltimer is far too slow to read inside a wait that is on the critical path of
+// every pipeline stage.  `limit_ns` is converted at 2 cycles per nanosecond, the most an SM of
+// this part runs at, so the wait gives up no earlier than limit_ns and no later than about
+// twice that at the lowest sustained clocks.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int site, uint64_t limit_ns, int kernel_id = 1) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = 0;
+  const long long t0 = clock64();
+  const long long limit_cycles = (long long)(limit_ns * 2ull);
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3Fu) == 0) {
+    if ((++spins & 0x1Fu) == 0) {
       if (*abort_flag != 0) return false;
-      const uint64_t now = globaltimer_ns();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > limit_ns) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         if (atomicCAS(&g_status[0], 0, ALTOB200_ETIMEOUT_DEVICE) == 0) {
           g_status[1] = kernel_id;  // 1 = a GEMM kernel, 9 = the wait self-test
@@ -157,6 +161,43 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       }
     }
   }
+}
+
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xFFFFFFFF;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// Named-barrier rendezvous of `count` threads (whole warps) with an OR over a predicate: every
+// participant learns whether any of them reports a failure.  A hardware barrier, not shared memory:
+// it costs the MMA-issuing warp a few tens of cycles where an mbarrier wait between tcgen05.mma
+// instructions costs ~150 (measured), during which the tensor pipe idles because tcgen05.mma does not
+// run ahead of the issuing thread's other instructions.
+__device__ __forceinline__ bool named_barrier_or(int id, int count, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(count), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
@@ -281,9 +322,9 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
 // The tensor-memory load of unit c+1 is in flight while unit c is scaled, converted, written to the
 // 128-byte-swizzled staging buffer and handed to a TMA store; `release` (the arrival that gives the
 // accumulator back to the MMA issuer) runs as soon as the last load has landed, before the last unit
-// is converted.  Two 4 KB staging buffers per warp alternate; `store_it` carries the alternation
+// is converted.  NBUF 4 KB staging buffers per warp alternate; `store_it` carries the alternation
 // across tiles.
-template <int BN, class Release>
+template <int BN, int NBUF, class Release>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, bool have_acc, float alpha, bool out_bf16,
                                               uint8_t* epi_warp, int lane, const CUtensorMap* tmap_d, int64_t row0,
                                               int64_t col_base, int batch, int64_t M, int64_t N, bool store_enabled,
@@ -296,7 +337,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, bool have_acc, flo
     const int64_t col0 = col_base + (int64_t)c * cols_per_unit;
     if (lane == 0) {
       if (row0 < M && col0 < N && store_enabled)
-        tma_store_3d(epi_warp + (store_it & 1u) * 4096u, tmap_d, (int32_t)col0, (int32_t)row0, batch);
+        tma_store_3d(epi_warp + (store_it % NBUF) * 4096u, tmap_d, (int32_t)col0, (int32_t)row0, batch);
       // a group is committed for every unit, empty when the unit lies outside the output: the
       // "all but the latest group have been read" wait before a buffer is refilled counts groups, so
       // a skipped unit must not let the store of the other buffer pass for the latest one
@@ -328,10 +369,10 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, bool have_acc, flo
       }
       if (h == 0) {
         // the TMA store issued two chunks ago from this buffer must have finished reading it
-        if (lane == 0) bulk_wait_read<1>();
+        if (lane == 0) bulk_wait_read<NBUF - 1>();
         __syncwarp();
       }
-      const uint32_t buf = my_row + (store_it & 1u) * 4096u;
+      const uint32_t buf = my_row + (store_it % NBUF) * 4096u;
       if (convert_enabled)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -367,9 +408,9 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, bool have_acc, flo
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = 0u;
       }
-      if (lane == 0) bulk_wait_read<1>();
+      if (lane == 0) bulk_wait_read<NBUF - 1>();
       __syncwarp();
-      const uint32_t buf = my_row + (store_it & 1u) * 4096u;
+      const uint32_t buf = my_row + (store_it % NBUF) * 4096u;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         st_shared_v4(buf + ((((uint32_t)j) ^ sw) << 4), f2u(__fmul_rn(u2f(r[4 * j]), alpha)),
@@ -657,7 +698,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         ++tile_it;
         continue;
       }
-      epilogue_tile<BN>(t_acc, !pad_group, alpha, args.out_bf16 != 0, epi + (warp - 2) * 8192, lane, &tmap_d, row0,
+      epilogue_tile<BN, 2>(t_acc, !pad_group, alpha, args.out_bf16 != 0, epi + (warp - 2) * 8192, lane, &tmap_d, row0,
                         nb * BN, ti.batch, args.M, args.N, !ALTOB200_DBG(args, 2), !ALTOB200_DBG(args, 32), store_it,
                         [&]() { mbar_arrive(&acc_empty[acc]); });
       if (!pad_group) ++tile_it;
@@ -772,9 +813,12 @@ struct CfgPair {
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024 * 1024;
   static constexpr int SF_COLS_A = SF_TILES * 4;
   static constexpr int SF_COLS_B = SF_TILES * 4 * NB;
-  static constexpr int STAGES = 4;
+  static constexpr int STAGES = 4;                           // (a fifth stage was measured: no gain)
   static constexpr int EPI_WARPS = 8;                        // two warps per tensor-memory lane quarter
-  static constexpr int EPI_BYTES = EPI_WARPS * 2 * 4096;
+  static constexpr int EPI_BUFS = 2;                         // 4 KB staging buffers per epilogue warp
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * 4096;
+  // registers per thread after the warpgroups have re-divided the file: 2 x 128 x 56 + 2 x 128 x 200 = 65536
+  static constexpr int REGS_SMALL = 56, REGS_EPI = 200;
   static constexpr int TMEM_SF_BASE = BN;
   static constexpr int TMEM_COLS_USED = TMEM_SF_BASE + STAGES * (SF_COLS_A + SF_COLS_B);
   static_assert(TMEM_COLS_USED <= 512, "tensor memory budget");
@@ -842,9 +886,14 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp < 4) {
+  setmaxnreg_dec<C::REGS_SMALL>();
   if (warp == 0) {
     // ------------------------------ producer (each CTA loads its own halves) ------------------------------
-    if (lane == 0) {
+    // Whole warp in the loop, one elected lane issues: the copy instructions take uniform operands (see
+    // the MMA issuer below).
+    {
+      const bool elected = elect_one();
       uint32_t it = 0;
       bool alive = true;
       for (int64_t tile = pair; tile < n_tiles && alive; tile += n_pairs) {
@@ -854,71 +903,129 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
         const int64_t nb = ti.nb;
         int nb_valid = (int)(n_row_blocks - nb * C::NB);
         if (nb_valid > C::NB) nb_valid = C::NB;
+        // a CTA whose rows of A lie past M has no scale row block to load; its rows are never stored
+        const bool sfa_exists = mb * BM < args.M;
+        const uint8_t* sfa_row = args.sfa + mb * args.nct * 512;
         for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int s = it % C::STAGES;
-          if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 11, args.wait_ns)) { alive = false; break; }
+          alive = __all_sync(0xFFFFFFFFu,
+                             mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 11, args.wait_ns));
+          if (!alive) break;
           uint8_t* st = smem + s * C::STAGE_BYTES;
           const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
           int64_t sf_tiles = args.nct - cb0;
           if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
           const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
           const int32_t kx = (int32_t)(ti.k_byte0 + (int64_t)ks * STAGE_K_BYTES);
-          // a CTA whose rows of A lie past M has no scale row block to load; its rows are never stored
-          const bool sfa_exists = mb * BM < args.M;
-          if (leader) mbar_expect_tx(&full_bar[s], 2 * (C::A_BYTES + C::B_BYTES));
-          mbar_expect_tx(&sfs_full[s], sf_bytes * ((sfa_exists ? 1 : 0) + nb_valid));
-          const uint32_t full_leader = mapa_u32(smem_u32(&full_bar[s]), 0);
-          tma_load_2d_pair(st, &tmap_a, kx, (int32_t)(mb * BM), full_leader);
-          tma_load_2d_pair(st + C::A_BYTES, &tmap_b, kx, (int32_t)(ti.b_row0 + rank * 128), full_leader);
-          if (sfa_exists)
-            bulk_load(st + C::A_BYTES + C::B_BYTES, args.sfa + (mb * args.nct + cb0) * 512, sf_bytes, &sfs_full[s]);
+          if (ALTOB200_DBG(args, 4) && it >= (uint32_t)C::STAGES) {
+            // profiling builds only: nothing is loaded once the ring has been filled
+            if (elected) {
+              if (leader) mbar_arrive(&full_bar[s]);
+              mbar_arrive(&sfs_full[s]);
+            }
+            continue;
+          }
+          if (elected) {
+            if (leader) mbar_expect_tx(&full_bar[s], 2 * (C::A_BYTES + C::B_BYTES));
+            mbar_expect_tx(&sfs_full[s], sf_bytes * ((sfa_exists ? 1 : 0) + nb_valid));
+            const uint32_t full_leader = mapa_u32(smem_u32(&full_bar[s]), 0);
+            tma_load_2d_pair(st, &tmap_a, kx, (int32_t)(mb * BM), full_leader);
+            tma_load_2d_pair(st + C::A_BYTES, &tmap_b, kx, (int32_t)(ti.b_row0 + rank * 128), full_leader);
+            if (sfa_exists) bulk_load(st + C::A_BYTES + C::B_BYTES, sfa_row + cb0 * 512, sf_bytes, &sfs_full[s]);
 #pragma unroll
-          for (int j = 0; j < C::NB; ++j)
-            if (j < nb_valid)
-              bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + j * C::SFA_BYTES,
-                        ti.sfb + ((nb * C::NB + j) * args.nct + cb0) * 512, sf_bytes, &sfs_full[s]);
+            for (int j = 0; j < C::NB; ++j)
+              if (j < nb_valid)
+                bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + j * C::SFA_BYTES,
+                          ti.sfb + ((nb * C::NB + j) * args.nct + cb0) * 512, sf_bytes, &sfs_full[s]);
+          }
+          __syncwarp();
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
-    if (lane == 0 && leader) {
-      uint32_t it = 0, tile_it = 0;
+    // The whole warp runs the loop (so that descriptors and addresses are warp-uniform values), one
+    // elected lane issues.  It never waits on a shared-memory barrier itself: warp 2 does and meets it
+    // at named barrier 1 + stage.  Between two tcgen05.mma nothing but their operand arithmetic runs.
+    if (leader) {
+      const bool elected = elect_one();
+      uint32_t it = 0;
       bool alive = true;
       const uint32_t smem_base = smem_u32(smem);
-      const uint32_t idesc[4] = {args.idesc[0], args.idesc[1], args.idesc[2], args.idesc[3]};
+#ifdef ALTOB200_GEMM_PROFILE
+      long long pk_mma = 0, pk_bar = 0, pk_n = 0;
+      const long long pk_t0 = clock64();
+#endif
       for (int64_t tile = pair; tile < n_tiles && alive; tile += n_pairs) {
         const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
         if (ti.skip) continue;
-        if (!mbar_wait(acc_empty, (tile_it & 1) ^ 1, abort_flag, 12, args.wait_ns)) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base;
         for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
           const int s = it % C::STAGES;
-          if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 13, args.wait_ns)) { alive = false; break; }
-          if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 15, args.wait_ns)) { alive = false; break; }
-          tc_fence_after();
+          // operands and scales of the stage are in place (and, at ks == 0, the accumulator is free)
+#ifdef ALTOB200_GEMM_PROFILE
+          const long long pk_a = clock64();
+#endif
+          if (named_barrier_or(1 + s, 64, false)) { alive = false; break; }
+          if (!ALTOB200_DBG(args, 2048)) tc_fence_after();
           const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;
           const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
           const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
           const uint32_t a_lo = st4 | 0x10000u;
           const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
+#ifdef ALTOB200_GEMM_PROFILE
+          const long long pk_b = clock64();
+          pk_bar += pk_b - pk_a;
+#endif
+          if (elected) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int t = (KIND == KIND_NVF4) ? j : (KIND == KIND_MXF4 ? (j >> 1) : 0);
-            if (j < n_mma)
-              tc_mma_pair<KIND>(d_tmem, desc_of(DESC_SW128_HI, a_lo + 2 * j), desc_of(DESC_SW128_HI, b_lo + 2 * j),
-                                idesc[j], (ks | j) != 0 ? 1u : 0u, sfa_t + t * 4, sfb_t + t * 4 * C::NB);
+            for (int j = 0; j < 4; ++j) {
+              const int t = (KIND == KIND_NVF4) ? j : (KIND == KIND_MXF4 ? (j >> 1) : 0);
+              if (j < n_mma)
+                tc_mma_pair<KIND>(tmem_base, desc_of(DESC_SW128_HI, a_lo + 2 * j), desc_of(DESC_SW128_HI, b_lo + 2 * j),
+                                  args.idesc[j], (ks | j) != 0 ? 1u : 0u, sfa_t + t * 4, sfb_t + t * 4 * C::NB);
+            }
+            tc_commit_pair(&empty_bar[s]);
           }
-          tc_commit_pair(&empty_bar[s]);
+          __syncwarp();
+#ifdef ALTOB200_GEMM_PROFILE
+          pk_mma += clock64() - pk_b;
+          pk_n += 1;
+#endif
         }
-        if (alive) tc_commit_pair(acc_full);
+        if (alive && elected) tc_commit_pair(acc_full);
+        __syncwarp();
+      }
+#ifdef ALTOB200_GEMM_PROFILE
+      if (blockIdx.x == 0 && lane == 0 && (args.debug & 16384))
+        printf("pair MMA warp: %lld stages, per stage: total %lld, barrier+fence+address %lld, issue of 4 MMAs + commit %lld cycles\n", pk_n,
+               (clock64() - pk_t0) / (pk_n > 0 ? pk_n : 1), pk_bar / (pk_n > 0 ? pk_n : 1), pk_mma / (pk_n > 0 ? pk_n : 1));
+#endif
+    }
+  } else if (warp == 2) {
+    // ------------------------------ wait warp (leader CTA only) ------------------------------
+    // Waits on the shared-memory barriers on behalf of the MMA issuer and releases it per stage.
+    if (leader) {
+      uint32_t it = 0, tile_it = 0;
+      bool alive = true;
+      for (int64_t tile = pair; tile < n_tiles && alive; tile += n_pairs) {
+        const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+        if (ti.skip) continue;
+        bool ok = mbar_wait(acc_empty, (tile_it & 1) ^ 1, abort_flag, 12, args.wait_ns);
+        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+          const int s = it % C::STAGES;
+          ok = ok && mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 13, args.wait_ns);
+          ok = ok && mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 15, args.wait_ns);
+          const bool failed = !__all_sync(0xFFFFFFFFu, ok);
+          if (named_barrier_or(1 + s, 64, failed)) { alive = false; break; }
+        }
         ++tile_it;
       }
     }
-  } else if (warp >= 6 && warp < 10) {
+  }  // warp 3 idles: it completes warpgroup 0
+  } else if (warp < 8) {
     // ------------------------------ scale transfer (each CTA into its own tensor memory) ------------------------------
+    setmaxnreg_dec<C::REGS_SMALL>();
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t it = 0;
     bool alive = true;
@@ -952,27 +1059,39 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
     }
   } else {
     // ------------------------------ epilogue (each CTA stores its own 128 rows) ------------------------------
-    // Warps 2-5 drain columns [0, 128) of the accumulator, warps 10-13 columns [128, 256); a warp may
-    // read the tensor-memory lane quarter (warp index mod 4).
+    // Warps 8-11 drain columns [0, 128) of the accumulator, warps 12-15 columns [128, 256); a warp may
+    // read the tensor-memory lane quarter (warp index mod 4).  A warp first pulls its 32 rows x 128
+    // columns into registers (four loads in flight, one wait) and hands the accumulator back, so the
+    // next tile's MMAs start after one tensor-memory read; scaling, conversion, staging and the TMA
+    // stores then run under that tile's mainloop.
+    setmaxnreg_inc<C::REGS_EPI>();
     const int quad = warp & 3;
-    const int half = warp >= 10 ? 1 : 0;
-    const int epi_idx = half * 4 + (warp - (half ? 10 : 2));
+    const int half = warp >= 12 ? 1 : 0;
+    const int epi_idx = warp - 8;
+    uint8_t* epi_warp = epi + epi_idx * (C::EPI_BUFS * 4096);
     float alpha = 1.0f;
     if (args.alpha_a != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_a));
     if (args.alpha_b != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_b));
     const uint32_t acc_empty_leader = mapa_u32(smem_u32(acc_empty), 0);
+    const uint32_t my_row = smem_u32(epi_warp) + (uint32_t)lane * 128u;
+    const uint32_t sw = (uint32_t)(lane & 7);
+    const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 128;
     uint32_t tile_it = 0, store_it = 0;
     for (int64_t tile = pair; tile < n_tiles; tile += n_pairs) {
       const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
-      const int64_t nb = ti.nb;
       const int64_t row0 = (ti.mb * 2 + rank) * BM + quad * 32;
-      const bool pad_group = ti.skip;
-      if (!pad_group) {
+      const int64_t col_base = ti.nb * BN + half * 128;
+      uint32_t r[128];
+      if (!ti.skip) {
         if (!mbar_wait(acc_full, tile_it & 1, abort_flag, 14, args.wait_ns)) break;
         tc_fence_after();
-      }
-      const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 128;
-      if (ALTOB200_DBG(args, 8) && !pad_group) {
+        if (!ALTOB200_DBG(args, 8)) {
+          tc_ld32(t_acc, r);
+          tc_ld32(t_acc + 32, r + 32);
+          tc_ld32(t_acc + 64, r + 64);
+          tc_ld32(t_acc + 96, r + 96);
+          tc_wait_ld();
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
@@ -980,15 +1099,43 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
           else mbar_arrive_cluster_relaxed(acc_empty_leader);
         }
         ++tile_it;
-        continue;
+        if (ALTOB200_DBG(args, 8)) continue;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 128; ++q) r[q] = 0u;
       }
-      epilogue_tile<128>(t_acc, !pad_group, alpha, OUT_BF16, epi + epi_idx * 8192, lane, &tmap_d, row0,
-                         nb * BN + half * 128, ti.batch, args.M, args.N, !ALTOB200_DBG(args, 2), !ALTOB200_DBG(args, 32),
-                         store_it, [&]() {
-                           if (leader) mbar_arrive(acc_empty);
-                           else mbar_arrive_cluster_relaxed(acc_empty_leader);
-                         });
-      if (!pad_group) ++tile_it;
+      constexpr int UNIT_COLS = OUT_BF16 ? 64 : 32;   // one 128-byte output row chunk
+#pragma unroll
+      for (int u = 0; u < 128 / UNIT_COLS; ++u) {
+        if (lane == 0) bulk_wait_read<C::EPI_BUFS - 1>();  // the store that last used this buffer has read it
+        __syncwarp();
+        const uint32_t buf = my_row + (store_it % C::EPI_BUFS) * 4096u;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint32_t o[4];
+          if (OUT_BF16) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __nv_bfloat162 p2 = __floats2bfloat162_rn(__fmul_rn(u2f(r[u * 64 + q * 8 + 2 * e]), alpha),
+                                                              __fmul_rn(u2f(r[u * 64 + q * 8 + 2 * e + 1]), alpha));
+              o[e] = *reinterpret_cast<const uint32_t*>(&p2);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = f2u(__fmul_rn(u2f(r[u * 32 + q * 4 + e]), alpha));
+          }
+          st_shared_v4(buf + ((((uint32_t)q) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        const int64_t col0 = col_base + (int64_t)u * UNIT_COLS;
+        if (lane == 0) {
+          if (row0 < args.M && col0 < args.N && !ALTOB200_DBG(args, 2))
+            tma_store_3d(epi_warp + (store_it % C::EPI_BUFS) * 4096u, &tmap_d, (int32_t)col0, (int32_t)row0, ti.batch);
+          bulk_commit();  // one group per unit, empty or not: the wait above counts groups
+        }
+        ++store_it;
+      }
     }
     if (lane == 0) bulk_wait_all();
   }
@@ -1267,12 +1414,10 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
     g.idesc[j] = make_idesc(kind, format_a, format_b, use_pair ? 2 * BM : BM, BN, sf_id);
   }
 #ifdef ALTOB200_GEMM_PROFILE
-  static int debug_flags = -1;
-  if (debug_flags < 0) {
-    const char* e = getenv("ALTOB200_GEMM_DEBUG");
-    debug_flags = e ? atoi(e) : 0;
+  {
+    const char* e = getenv("ALTOB200_GEMM_DEBUG");  // read at every call: probe scripts change it between calls
+    g.debug = e ? atoi(e) : 0;
   }
-  g.debug = debug_flags;
 #endif
   cudaStream_t st = (cudaStream_t)stream;
   if (use_pair) {
