@@ -39,7 +39,7 @@ __device__ int g_status[4] = {0, 0, 0, 0};
 
 constexpr int BM = 128;
 constexpr int STAGE_K_BYTES = 128;
-constexpr int NUM_THREADS = 320;  // producer, MMA issuer, 4 epilogue warps, 4 scale-transfer warps
+constexpr int NUM_THREADS = 352;  // producer, MMA issuer, 4 epilogue warps, 4 scale-transfer warps, the wait warp
 constexpr int NUM_THREADS_PAIR = 512;  // pair kernel: four warpgroups (see the kernel)
 constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // default limit of one wait: 4 s
 
@@ -562,29 +562,33 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool alive = true;
-      for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-        const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
-        if (ti.skip) continue;  // nothing to load: the epilogue writes zeros
-        const int64_t mb = ti.mb, nb = ti.nb;
-        // 128-row blocks of B that exist (the last tile of a ragged N has fewer)
-        int nb_valid = (int)(n_row_blocks - nb * C::NB);
-        if (nb_valid > C::NB) nb_valid = C::NB;
-        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
-          const int s = it % C::STAGES;
-          if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 1, args.wait_ns)) { alive = false; break; }
-          uint8_t* st = smem + s * C::STAGE_BYTES;
-          const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
-          int64_t sf_tiles = args.nct - cb0;
-          if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
-          const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
-          if (ALTOB200_DBG(args, 4) && it >= (uint32_t)C::STAGES) {
-            mbar_arrive(&full_bar[s]);
-            continue;
-          }
-          const int32_t kx = (int32_t)(ti.k_byte0 + (int64_t)ks * STAGE_K_BYTES);
+    // Whole warp in the loop, one elected lane issues (uniform operands; see the CTA-pair kernel).
+    const bool elected = elect_one();
+    uint32_t it = 0;
+    bool alive = true;
+    for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+      const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+      if (ti.skip) continue;  // nothing to load: the epilogue writes zeros
+      const int64_t mb = ti.mb, nb = ti.nb;
+      // 128-row blocks of B that exist (the last tile of a ragged N has fewer)
+      int nb_valid = (int)(n_row_blocks - nb * C::NB);
+      if (nb_valid > C::NB) nb_valid = C::NB;
+      for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+        const int s = it % C::STAGES;
+        alive = __all_sync(0xFFFFFFFFu,
+                           mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1, abort_flag, 1, args.wait_ns));
+        if (!alive) break;
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        const int64_t cb0 = ti.sf_tile0 + (int64_t)ks * C::SF_TILES;
+        int64_t sf_tiles = args.nct - cb0;
+        if (sf_tiles > C::SF_TILES) sf_tiles = C::SF_TILES;
+        const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
+        if (ALTOB200_DBG(args, 4) && it >= (uint32_t)C::STAGES) {
+          if (elected) mbar_arrive(&full_bar[s]);
+          continue;
+        }
+        const int32_t kx = (int32_t)(ti.k_byte0 + (int64_t)ks * STAGE_K_BYTES);
+        if (elected) {
           mbar_expect_tx(&full_bar[s], C::A_BYTES + C::B_BYTES + sf_bytes * (1 + nb_valid));
           tma_load_2d(st, &tmap_a, kx, (int32_t)(mb * BM), &full_bar[s]);
           tma_load_2d(st + C::A_BYTES, &tmap_b, kx, (int32_t)ti.b_row0, &full_bar[s]);
@@ -595,50 +599,70 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
               bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + j * C::SFA_BYTES,
                         ti.sfb + ((nb * C::NB + j) * args.nct + cb0) * 512, sf_bytes, &full_bar[s]);
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      uint32_t it = 0, tile_it = 0;
-      bool alive = true;
-      const uint32_t smem_base = smem_u32(smem);
-      const uint32_t idesc[4] = {args.idesc[0], args.idesc[1], args.idesc[2], args.idesc[3]};
-      for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-        const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
-        if (ti.skip) continue;
-        const int acc = tile_it % C::ACC_STAGES;
-        if (!mbar_wait(&acc_empty[acc], ((tile_it / C::ACC_STAGES) & 1) ^ 1, abort_flag, 2, args.wait_ns)) break;
+    // Whole warp, elected lane issues; the shared-memory barriers are waited on by warp 10, which
+    // releases this warp once per stage through named barrier 1 + stage (see the CTA-pair kernel).
+    const bool elected = elect_one();
+    uint32_t it = 0, tile_it = 0;
+    bool alive = true;
+    const uint32_t smem_base = smem_u32(smem);
+    for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+      const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+      if (ti.skip) continue;
+      const int acc = tile_it % C::ACC_STAGES;
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+        const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
+        const int s = it % C::STAGES;
+        if (named_barrier_or(1 + s, 64, false)) { alive = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
-          const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
-          const int s = it % C::STAGES;
-          if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 3, args.wait_ns)) { alive = false; break; }
-          if (!mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 5, args.wait_ns)) { alive = false; break; }
-          tc_fence_after();
-          const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;  // stage address / 16
-          const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
-          const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
-          const uint32_t a_lo = st4 | 0x10000u;
-          const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
+        const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;  // stage address / 16
+        const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
+        const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
+        const uint32_t a_lo = st4 | 0x10000u;
+        const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
+        if (elected) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             // MMA j covers bytes [32j, 32j+32) of the stage; its scale tile and byte offset
             // inside the tile depend on how many scales one MMA consumes.
             const int t = (KIND == KIND_NVF4) ? j : (KIND == KIND_MXF4 ? (j >> 1) : 0);
             if (j < n_mma)
-            tc_mma<KIND>(d_tmem, desc_of(DESC_SW128_HI, a_lo + 2 * j), desc_of(DESC_SW128_HI, b_lo + 2 * j), idesc[j],
-                         (ks | j) != 0 ? 1u : 0u, sfa_t + t * 4, sfb_t + t * 4 * C::NB);
+              tc_mma<KIND>(d_tmem, desc_of(DESC_SW128_HI, a_lo + 2 * j), desc_of(DESC_SW128_HI, b_lo + 2 * j),
+                           args.idesc[j], (ks | j) != 0 ? 1u : 0u, sfa_t + t * 4, sfb_t + t * 4 * C::NB);
           }
           tc_commit(&empty_bar[s]);
         }
-        if (alive) tc_commit(&acc_full[acc]);
-        ++tile_it;
+        __syncwarp();
       }
+      if (alive && elected) tc_commit(&acc_full[acc]);
+      __syncwarp();
+      ++tile_it;
+    }
+  } else if (warp == 10) {
+    // ------------------------------ wait warp ------------------------------
+    uint32_t it = 0, tile_it = 0;
+    bool alive = true;
+    for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+      const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
+      if (ti.skip) continue;
+      const int acc = tile_it % C::ACC_STAGES;
+      bool ok = mbar_wait(&acc_empty[acc], ((tile_it / C::ACC_STAGES) & 1) ^ 1, abort_flag, 2, args.wait_ns);
+      for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
+        const int s = it % C::STAGES;
+        ok = ok && mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 3, args.wait_ns);
+        ok = ok && mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 5, args.wait_ns);
+        const bool failed = !__all_sync(0xFFFFFFFFu, ok);
+        if (named_barrier_or(1 + s, 64, failed)) { alive = false; break; }
+      }
+      ++tile_it;
     }
   } else if (warp >= 6) {
-    // ------------------------------ scale transfer ------------------------------
+    // ------------------------------ scale transfer (warps 6..9) ------------------------------
     // Tile t of A -> columns [4t, 4t+4) of the stage's A-scale area; tile t of B row block j ->
     // columns [4 NB t + 4 j, +4) of its B-scale area.  Lane l of every quarter holds scale row
     // l of each 512-byte tile (16 bytes = 4 columns), i.e. the 4x replicated layout the MMA reads.
