@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the low-precision linear hot path on B200.
 
-Workload (BASELINE.json configs[1]): NVFP4 linear forward + dgrad + wgrad at the Llama-3-8B
+Workload: NVFP4 linear forward + dgrad + wgrad at the Llama-3-8B
 MLP-up shape -- X[8192,4096] ~ N(0,1), W[14336,4096] ~ N(0,0.02), dY[8192,14336] ~ N(0,1e-3),
 bf16; E4M3 block-16 scales + FP32 tensorwise outer scale; W in 16x16 blocks; 16-point
 randomised Hadamard on the wgrad operands; stochastic rounding of the gradients.  Data are
@@ -51,12 +51,15 @@ CONFIG = {
                "quantizers to a side stream; not faster with the CTA-pair GEMM)",
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# DRAM bytes (read + write) per GEMM launch at the default shape, from the one-pass ncu capture
-# summarised under profiles/: (123.0+193.6 + 85.0+81.6 + 127.3+47.6) MB / 3.  Part of each output is
+# DRAM bytes (read + write) per GEMM launch at the default shape: ncu dram__bytes_read.sum +
+# dram__bytes_write.sum from a one-pass capture of this command, mean of the step's three launches
+# (fprop 113.3 + 192.4, dgrad 127.5 + 47.2, wgrad 85.2 + 80.5 MB read + written).  Part of each output is
 # still in the write-back L2 when the kernel ends; part of each input is found there.
-GEMM_DRAM_BYTES_PER_LAUNCH = 215.3e6
-# codes + packed scales of both operands + bf16 output, mean of fprop / wgrad / dgrad
+GEMM_DRAM_BYTES_PER_LAUNCH = (113.3e6 + 192.4e6 + 127.5e6 + 47.2e6 + 85.2e6 + 80.5e6) / 3
+# algorithmic bytes per launch: codes + packed scales of both operands + bf16 output, mean of the three
 GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (52.0e6 + 234.9e6 + 84.9e6 + 117.4e6 + 99.1e6 + 67.1e6) / 3
+NOMINAL_FP4_TFLOPS = 9000.0  # dense FP4 tensor peak of the part (datasheet)
+SUSTAINED_SECONDS = 3.0      # length of the sustained leg
 CPU_SAMPLE_ROWS = 2048     # token rows of the CPU sample
 CPU_SAMPLE_FEATS = 2048    # output features (rows of W) of the CPU sample
 CPU_BASELINE_REPS = 10     # steps of the sample timed for `cpu_baseline` (10-20 s of host work in all)
@@ -342,17 +345,88 @@ def run_ours(args):
             kernels[name] = {"launches_per_step": d["launches"] // args.steps, "avg_ms": avg_ms,
                              "gbs": d["work"] / d["launches"] / (avg_ms * 1e-3) / 1e9,
                              "frac_of_hbm_peak": d["work"] / d["launches"] / (avg_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-    fp4_peak = 4.0 * peaks["bf16_tflops_sustained"]
+    # Denominator of the tensor roofline: the dense FP4 proxy 4 x measured cuBLAS bf16 throughput.  The
+    # measured file holds a burst figure (a kernel timed alone at full clocks) and a sustained one (seconds
+    # under the power cap); which of them applies is decided by the clocks this run actually saw.
+    burst_peak, sustained_peak = 4.0 * peaks["bf16_tflops"], 4.0 * peaks["bf16_tflops_sustained"]
+    at_max_clock = bool(clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz")
+                        and clocks["sm_mhz"] >= 0.97 * clocks["sm_max_mhz"])
+    fp4_peak = burst_peak if (at_max_clock or clocks is None or not clocks.get("sm_mhz")) else sustained_peak
     default_shape = (M, K, N) == (8192, 4096, 14336)
     gemm_tf = kernels["gemm"]["tflops"]
     roofline = {"bound": "tensor", "achieved": gemm_tf, "peak": fp4_peak, "unit": "TFLOP/s",
                 "frac": gemm_tf / fp4_peak, "traffic": GEMM_DRAM_BYTES_PER_LAUNCH if default_shape else None,
+                "frac_of_burst_proxy": gemm_tf / burst_peak, "frac_of_sustained_proxy": gemm_tf / sustained_peak,
+                "frac_of_nominal": gemm_tf / NOMINAL_FP4_TFLOPS,
                 "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one-pass capture of this "
-                                  "command, mean of the step's three GEMM launches "
-                                  "(profiles/launch_list_nvfp4_linear_bench.md); algorithmic operand + output "
+                                  "command, mean of the step's three GEMM launches; algorithmic operand + output "
                                   f"bytes per launch {GEMM_ALGORITHMIC_BYTES_PER_LAUNCH:.4g}",
                 "kernel": "gemm_blockscaled_pair_kernel<NVF4,bf16> (tcgen05 cta_group::2; 3 launches per step, 962 GFLOP each)",
-                "peak_source": f"4 x {peak_src} sustained bf16 cuBLAS throughput (dense FP4 proxy); nominal dense FP4 9000"}
+                "peak_source": f"4 x {peak_src} cuBLAS bf16 throughput (dense FP4 proxy), "
+                               f"{'burst' if fp4_peak == burst_peak else 'sustained'} figure because the median SM "
+                               f"clock of the timed region was {'at' if fp4_peak == burst_peak else 'below'} the maximum; "
+                               f"nominal dense FP4 {NOMINAL_FP4_TFLOPS:.0f}"}
+
+    # ---- sustained leg: the same step back to back for seconds, clocks sampled throughout ----
+    sustained = None
+    if not args.no_sustained:
+        barrier()
+        samp2 = ClockSampler(local)
+        if rank == 0:
+            samp2.start()
+        n_sus = 0
+        es, ee = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        chunk = max(50, int(0.25 / max(ms / args.steps * 1e-3, 1e-6)))   # ~0.25 s of steps between host checks
+        t_wall = time.perf_counter()
+        es.record()
+        while True:
+            for _ in range(chunk):
+                step()
+            n_sus += chunk
+            torch.cuda.synchronize()
+            if time.perf_counter() - t_wall >= SUSTAINED_SECONDS:
+                break
+        ee.record()
+        torch.cuda.synchronize()
+        sus_ms = es.elapsed_time(ee)
+        c2 = samp2.stop() if rank == 0 else None
+        ts = torch.tensor([sus_ms / n_sus], device=dev)
+        if dist is not None:
+            dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+        per_step = float(ts.item())
+        sustained = {"seconds": sus_ms * 1e-3, "steps": n_sus, "ms_per_step": per_step,
+                     "value": world * FLOPS_PER_STEP / (per_step * 1e-3) / 1e12, "unit": UNIT, "clocks": c2,
+                     "ms_x_median_mhz": (per_step * c2["sm_mhz"]) if (c2 and c2.get("sm_mhz")) else None,
+                     "frac_of_sustained_proxy_whole_step": FLOPS_PER_STEP / (per_step * 1e-3) / 1e12 / sustained_peak}
+
+    # ---- the other recipes the target names, same shape, device-timed (not the headline) ----
+    extra = {}
+    if default_shape and not args.no_extra:
+        from alto_b200 import mxfp4 as MX
+
+        def time_fn(fn, reps=10):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps
+
+        def mx_step(macro):
+            x.grad = None
+            w.grad = None
+            MX._to_mxfp4_then_scaled_mm(x, w, False, True, True, False, "none", True, macro).backward(dy)
+
+        for name, macro in (("mxfp4_linear", False), ("mxfp4_two_level_linear", True)):
+            t_ms = time_fn(lambda: mx_step(macro))
+            extra[name] = {"ms_per_step": t_ms, "tflops": FLOPS_PER_STEP / (t_ms * 1e-3) / 1e12,
+                           "recipe": "MXFP4 1D-32 activations/grads, 2D 32x32 weights, RHT-16 on wgrad operands, SR on "
+                                     "gradients" + (", 128 macro-block two-level scale (folded in the GEMM)" if macro else "")}
+        NV.HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)
 
     # ---- end to end through the public API with host buffers ----
     xh = x.detach().cpu().pin_memory()
@@ -443,14 +517,120 @@ def run_ours(args):
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "nvfp4 (e2m1 codes, e4m3 scales, fp32 accumulate)", "data": "synthetic", "config": CONFIG,
         "frac_of_fp4_peak": value / world / fp4_peak, "roofline": roofline, "kernels": kernels, "e2e": e2e,
-        "gpu_launches": launches, "clocks": clocks,
+        "gpu_launches": launches, "clocks": clocks, "sustained": sustained, "extra": extra,
     }
+    if world > 1 and not args.no_sharded:
+        line["sharded"] = run_sharded(dist, dev, rank, world)
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(CPU_SAMPLE_ROWS, CPU_BASELINE_REPS)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------
+# N > 1: the two configurations with a real exchange step (expert-parallel MoE, column-sharded linear)
+# ------------------------------------------------------------------------------------------
+def run_sharded(dist, dev, rank, world):
+    """After the replica headline: (a) the MXFP4 MoE layer at the GPT-OSS-20B shape (32 experts, top-4, hidden
+    = intermediate = 2880, 16384 tokens in all; 2-D weight blocks with the 128 macro-block two-level scale,
+    RHT-32 on the token-axis operands, SR on gradients), experts and tokens split over the ranks, dispatch
+    and combine by NCCL all-to-all; (b) the MXFP8 linear 8192 x 4096 x 4096 with W split by output features and
+    dX all-reduced.  Total work is fixed (strong scaling).  Times are CUDA events, slowest rank; parity is each
+    rank's forward against the same rows computed on that GPU alone with all experts / its weight shard."""
+    from alto_b200 import distributed as D
+    from alto_b200 import mxfp8 as M8
+    from alto_b200.grouped import _quantize_then_mxfp_scaled_grouped_mm as mx4
+    from alto_b200.hadamard import HadamardFactory
+
+    def gmm(A, B, offs):
+        HadamardFactory.configure(block_size=32, randomized=True, dtype=torch.float32, seed=0)
+        return mx4(A, B, offs, False, True, True, False, True, "none", True)
+
+    def moe(x, ids, scores, W13, W2, dispatcher):
+        xl, offs, st = dispatcher.dispatch(x, ids)
+        h = gmm(xl, W13.transpose(-2, -1), offs)
+        H = h.shape[-1] // 2
+        y = gmm(torch.nn.functional.silu(h[:, :H]) * h[:, H:], W2.transpose(-2, -1), offs)
+        return dispatcher.combine(y, st, scores)
+
+    def step_time(fn, reps=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / reps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_ok(flag):
+        t = torch.tensor([1 if flag else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    T, Dm, E, k = 16384, 2880, 32, 4
+    g = torch.Generator(device=dev).manual_seed(0)
+    logits = torch.randn(T, E, generator=g, device=dev)
+    x_all = torch.randn(T, Dm, generator=g, device=dev).bfloat16()
+    W13 = (torch.randn(E, 2 * Dm, Dm, generator=g, device=dev) * 0.02).bfloat16()
+    W2 = (torch.randn(E, Dm, Dm, generator=g, device=dev) * 0.02).bfloat16()
+    scores_all, ids_all = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    n, El = T // world, E // world
+    x = x_all[rank * n:(rank + 1) * n].clone().requires_grad_(True)
+    ids, scores = ids_all[rank * n:(rank + 1) * n], scores_all[rank * n:(rank + 1) * n].bfloat16()
+    w13 = W13[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    w2 = W2[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    ep = D.ExpertParallelDispatcher(E)
+    out = moe(x, ids, scores, w13, w2, ep)
+    one = D.ExpertParallelDispatcher.__new__(D.ExpertParallelDispatcher)
+    one.group, one.world, one.rank, one.num_experts, one.local_experts, one.align = None, 1, 0, E, E, 128
+    with torch.no_grad():
+        ep_ok = all_ok(torch.equal(out, moe(x.detach(), ids, scores, W13, W2, one)))
+    del W13, W2, x_all
+    g_out = torch.ones_like(out) * 1e-3
+
+    def moe_step():
+        x.grad = w13.grad = w2.grad = None
+        moe(x, ids, scores, w13, w2, ep).backward(g_out)
+
+    t_moe = step_time(moe_step)
+    ep_ok = ep_ok and all_ok(bool(torch.isfinite(x.grad).all() and torch.isfinite(w13.grad).all()))
+    flop_moe = 3 * 2 * T * k * (2 * Dm * Dm + Dm * Dm)
+    # rows that leave a rank: every routed row whose expert lives elsewhere, both ways, forward and backward
+    a2a_bytes = int(T * k * Dm * 2 * (world - 1) / world) * 4
+
+    fn = lambda a, b: M8._to_mxfp8_then_scaled_mm(a, b, "e4m3", False, False, True)  # noqa: E731
+    g = torch.Generator(device=dev).manual_seed(1)
+    xs = torch.randn(8192, 4096, generator=g, device=dev).bfloat16().requires_grad_(True)
+    W = (torch.randn(4096, 4096, generator=g, device=dev) * 0.02).bfloat16()
+    dy = (torch.randn(8192, 4096, generator=g, device=dev) * 1e-3).bfloat16()
+    nw = 4096 // world
+    ws = D.shard_rows(W).clone().requires_grad_(True)
+    dys = dy[:, rank * nw:(rank + 1) * nw].contiguous()
+    ys = D.column_sharded_linear(xs, ws, fn)
+    with torch.no_grad():
+        col_ok = all_ok(torch.equal(ys, fn(xs.detach(), W[rank * nw:(rank + 1) * nw])))
+
+    def lin_step():
+        xs.grad = ws.grad = None
+        D.column_sharded_linear(xs, ws, fn).backward(dys)
+
+    t_lin = step_time(lin_step)
+    col_ok = col_ok and all_ok(bool(torch.isfinite(xs.grad).all() and torch.isfinite(ws.grad).all()))
+    return {"scaling": "strong (total work fixed)",
+            "ep_moe_ms": t_moe, "ep_moe_tflops": flop_moe / (t_moe * 1e-3) / 1e12, "ep_parity_ok": ep_ok,
+            "ep_recipe": "MXFP4, 2D weight blocks + 128 macro-block two-level scale, RHT-32, SR; W13 + SwiGLU + W2, "
+                         "fwd + dgrad + wgrad with dispatch and combine",
+            "a2a_bytes": a2a_bytes,
+            "col_ms": t_lin, "col_tflops": 3 * 2 * 8192 * 4096 * 4096 / (t_lin * 1e-3) / 1e12, "col_parity_ok": col_ok,
+            "allreduce_bytes": 8192 * 4096 * 2}
 
 
 def main():
@@ -460,6 +640,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long sustained leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the MXFP4 recipes at the same shape")
+    ap.add_argument("--no-sharded", action="store_true", help="N > 1: skip the expert-parallel and column-sharded runs")
     ap.add_argument("--shape", default=None, metavar="M,K,N",
                     help="run the same step at another shape (profiling captures on a small case); the "
                          "headline workload is the default")
