@@ -283,3 +283,143 @@ def mxfp8_grouped_gemm_forward(inputs, expert_weights, expert_indices, input_sca
     return _grouped_forward_prequantized(ids[lhs_format_id], ids[rhs_format_id], inputs, expert_weights,
                                          expert_indices, input_scales, weight_scales, trans_weights, use_2dblock_x,
                                          use_2dblock_w, output_dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# Backward grouped GEMMs on operands that are already quantised
+# ---------------------------------------------------------------------------------------------
+def _offsets_from_indices(expert_indices: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Cumulative rows per expert (int32 [E]) from the per-row expert ids; device ops only."""
+    counts = torch.bincount(expert_indices.to(torch.int64), minlength=num_experts)[:num_experts]
+    return torch.cumsum(counts, 0).to(torch.int32)
+
+
+def _check_group_rows(m_buf: int, m_total: int) -> None:
+    torch._check(m_total > 0)
+    torch._check(m_total % ALIGN_SIZE_M == 0,
+                 lambda: f"M_total ({m_total}) must be a multiple of group_size_m ({ALIGN_SIZE_M})")
+    torch._check(m_buf >= m_total, lambda: f"M_bufferlen ({m_buf}) must be >= M_total ({m_total})")
+
+
+def _grouped_backward_inputs_prequantized(fmt_a: int, fmt_b: int, grad_output, expert_weights, expert_indices, go_scales,
+                                          expert_weight_scales, trans_weights: bool, use_2dblock_x: bool,
+                                          use_2dblock_w: bool, output_dtype: torch.dtype) -> torch.Tensor:
+    """dX[m] = dY[m] W[expert(m)] over quantised operands with plain scales.  ``grad_output`` [M_buf, N]
+    codes along N; ``expert_weights`` the codes of W quantised along N (the reduction axis of this GEMM):
+    [E, N, K] (FP4: [E, N/2, K]) when ``trans_weights``, else the [E, K, N] view of such a tensor, with
+    scales [E, N/32, K] (or [E, N/32, K/32] for 2-D blocks).  The tensor cores read operands with the
+    reduction axis contiguous, so the weight codes are transposed once here (data movement only)."""
+    torch._check(grad_output.dim() == 2 and expert_weights.dim() == 3,
+                 lambda: "grad_output must be 2-D, expert_weights 3-D")
+    m_buf, m_total = grad_output.shape[0], expert_indices.numel()
+    _check_group_rows(m_buf, m_total)
+    w = expert_weights if trans_weights else expert_weights.transpose(-2, -1)        # [E, N codes, K]
+    ws = expert_weight_scales if trans_weights else expert_weight_scales.transpose(-2, -1)   # [E, N/32, K or K/32]
+    n_exp, n_codes, K = w.shape
+    fp4 = L.is_fp4(fmt_a)
+    N = n_codes * 2 if fp4 else n_codes
+    torch._check(grad_output.shape[1] == n_codes,
+                 lambda: f"grad_output N ({grad_output.shape[1]}) must match weight N ({n_codes})")
+    block = L.block_of(fmt_a)
+    a_codes = E.as_2d_rows(grad_output.view(torch.uint8))
+    b_codes = w.view(torch.uint8).transpose(-2, -1).contiguous().reshape(n_exp * K, n_codes)   # [E*K, N codes]
+    sa = E.pack_plain_scales(go_scales, m_buf, use_2dblock_x, block)
+    wst = ws.transpose(-2, -1)                                                        # [E, K or K/32, N/32]
+    sb = torch.cat([E.pack_plain_scales(wst[e].contiguous(), K, use_2dblock_w, block) for e in range(n_exp)])
+    n_groups = (m_buf + ALIGN_SIZE_M - 1) // ALIGN_SIZE_M
+    group_expert = torch.full((n_groups,), -1, dtype=torch.int32, device=grad_output.device)
+    group_expert[:m_total // ALIGN_SIZE_M] = expert_indices.to(torch.int32)[::ALIGN_SIZE_M]
+    out = torch.empty(m_buf, K, dtype=output_dtype, device=grad_output.device)
+    L.grouped_gemm_blockscaled(fmt_a, fmt_b, m_buf, K, N, n_exp, a_codes, sa, b_codes, sb, group_expert, out)
+    return out
+
+
+def _grouped_backward_weights_prequantized(fmt_a: int, fmt_b: int, grad_output, inputs, expert_indices, num_experts: int,
+                                           go_scales, input_scales, trans_weights: bool, use_2dblock_go: bool,
+                                           use_2dblock_x: bool, output_dtype: torch.dtype) -> torch.Tensor:
+    """dW[e] = sum over the rows of expert e of dY[m]^T X[m] over operands quantised along the token axis:
+    ``grad_output`` [M_buf, N] and ``inputs`` [M_buf, K] codes (FP4: [M_buf/2, .], two tokens per byte) with
+    scales [M_buf/32, N] and [M_buf/32, K] (or [M_buf/32, ./32] for 2-D blocks).  Returns [E, N, K]
+    (``trans_weights``) or its [E, K, N] view.  Both code matrices are transposed once so that the token
+    axis is contiguous (data movement only); each expert's token range comes from ``expert_indices``."""
+    torch._check(grad_output.dim() == 2 and inputs.dim() == 2, lambda: "grad_output and inputs must be 2-D")
+    fp4 = L.is_fp4(fmt_a)
+    m_codes, N = grad_output.shape
+    m_codes_x, K = inputs.shape
+    torch._check(m_codes == m_codes_x, lambda: f"inputs M ({m_codes_x}) must match grad_output M ({m_codes})")
+    m_buf = m_codes * 2 if fp4 else m_codes
+    _check_group_rows(m_buf, expert_indices.numel())
+    block = L.block_of(fmt_a)
+    a_codes = grad_output.view(torch.uint8).t().contiguous()          # [N, M codes]
+    b_codes = inputs.view(torch.uint8).t().contiguous()               # [K, M codes]
+    sa = E.pack_plain_scales(go_scales.t().contiguous(), N, use_2dblock_go, block)
+    sb = E.pack_plain_scales(input_scales.t().contiguous(), K, use_2dblock_x, block)
+    offs = _offsets_from_indices(expert_indices, num_experts)
+    out = torch.empty(num_experts, N, K, dtype=output_dtype, device=grad_output.device)
+    L.grouped_gemm_wgrad_blockscaled(fmt_a, fmt_b, N, K, m_buf, num_experts, a_codes, sa, b_codes, sb, offs, out)
+    return out if trans_weights else out.transpose(-2, -1)
+
+
+def mxfp4_grouped_gemm_backward_inputs(grad_output, expert_weights, expert_indices, go_scales, expert_weight_scales,
+                                       trans_weights: bool = True, use_2dblock_x: bool = False,
+                                       use_2dblock_w: bool = True, k_pack_w: bool = True,
+                                       output_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """The reference's ``torch.ops.torchtitan.mxfp4_grouped_gemm_backward_inputs``
+    (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_backward.py:500-597) for weights packed along the
+    reduction axis N (``k_pack_w=True``); the other packing cannot feed the FP4 tensor cores."""
+    if not k_pack_w:
+        raise NotImplementedError("weights packed along a non-reduction axis cannot feed the tcgen05 FP4 MMA; "
+                                  "quantise along N (or in 2-D blocks, packed along N) and pass k_pack_w=True")
+    return _grouped_backward_inputs_prequantized(L.FMT_MXFP4, L.FMT_MXFP4, grad_output, expert_weights, expert_indices,
+                                                 go_scales, expert_weight_scales, trans_weights, use_2dblock_x,
+                                                 use_2dblock_w, output_dtype)
+
+
+def mxfp4_grouped_gemm_backward_weights(grad_output, inputs, expert_indices, num_experts: int, go_scales, input_scales,
+                                        trans_weights: bool = True, use_2dblock_go: bool = False,
+                                        use_2dblock_x: bool = True, k_pack_go: bool = True, k_pack_x: bool = True,
+                                        output_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """The reference's ``torch.ops.torchtitan.mxfp4_grouped_gemm_backward_weights``
+    (alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_backward.py:398-497) for operands packed along the token
+    axis (``k_pack_go = k_pack_x = True``)."""
+    if not (k_pack_go and k_pack_x):
+        raise NotImplementedError("operands packed along a non-reduction axis cannot feed the tcgen05 FP4 MMA; "
+                                  "quantise along the token axis and pass k_pack_go = k_pack_x = True")
+    return _grouped_backward_weights_prequantized(L.FMT_MXFP4, L.FMT_MXFP4, grad_output, inputs, expert_indices,
+                                                  num_experts, go_scales, input_scales, trans_weights, use_2dblock_go,
+                                                  use_2dblock_x, output_dtype)
+
+
+_FP8_IDS = {0: L.FMT_MXFP8_E4M3, 1: L.FMT_MXFP8_E5M2}
+
+
+def _fp8_ids(lhs_format_id: int, rhs_format_id: int):
+    if lhs_format_id not in _FP8_IDS or rhs_format_id not in _FP8_IDS:
+        raise ValueError(f"Unsupported FP8 format id: {lhs_format_id} / {rhs_format_id}")
+    return _FP8_IDS[lhs_format_id], _FP8_IDS[rhs_format_id]
+
+
+def mxfp8_grouped_gemm_backward_inputs(grad_output, expert_weights, expert_indices, go_scales, expert_weight_scales,
+                                       trans_weights: bool = True, use_2dblock_x: bool = False,
+                                       use_2dblock_w: bool = True, lhs_format_id: int = 0, rhs_format_id: int = 0,
+                                       output_dtype: torch.dtype = torch.bfloat16,
+                                       use_dot_scaled: Optional[bool] = None) -> torch.Tensor:
+    """The reference's ``torch.ops.alto.mxfp8_grouped_gemm_backward_inputs``
+    (alto/kernels/mxfp8/mxfp8_grouped_gemm/cg_backward.py:313-413); format ids 0 = e4m3, 1 = e5m2."""
+    fa, fb = _fp8_ids(lhs_format_id, rhs_format_id)
+    return _grouped_backward_inputs_prequantized(fa, fb, grad_output, expert_weights, expert_indices, go_scales,
+                                                 expert_weight_scales, trans_weights, use_2dblock_x, use_2dblock_w,
+                                                 output_dtype)
+
+
+def mxfp8_grouped_gemm_backward_weights(grad_output, inputs, expert_indices, num_experts: int, go_scales, input_scales,
+                                        trans_weights: bool = True, use_2dblock_go: bool = False,
+                                        use_2dblock_x: bool = False, lhs_format_id: int = 0, rhs_format_id: int = 0,
+                                        output_dtype: torch.dtype = torch.bfloat16,
+                                        use_dot_scaled: Optional[bool] = None) -> torch.Tensor:
+    """The reference's ``torch.ops.alto.mxfp8_grouped_gemm_backward_weights``
+    (alto/kernels/mxfp8/mxfp8_grouped_gemm/cg_backward.py:416-513)."""
+    fa, fb = _fp8_ids(lhs_format_id, rhs_format_id)
+    return _grouped_backward_weights_prequantized(fa, fb, grad_output, inputs, expert_indices, num_experts, go_scales,
+                                                  input_scales, trans_weights, use_2dblock_go, use_2dblock_x,
+                                                  output_dtype)

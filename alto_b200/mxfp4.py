@@ -84,12 +84,12 @@ def blockwise_mxfp4_gemm(
     a_s: torch.Tensor,
     b: torch.Tensor,
     b_s: torch.Tensor,
-    trans_a: bool = False,
-    trans_b: bool = False,
-    k_pack_a: bool = True,
-    k_pack_b: bool = True,
     use_2dblock_a: bool = False,
     use_2dblock_b: bool = False,
+    k_pack_a: bool = True,
+    k_pack_b: bool = True,
+    trans_a: bool = False,
+    trans_b: bool = False,
     block_size: int = BLOCK_SIZE_DEFAULT,
     output_dtype: torch.dtype = torch.float32,
 ) -> torch.Tensor:

@@ -5,11 +5,11 @@ The reference exposes these as ``torch.library.triton_op`` ops with ``register_f
 (alto/kernels/fp4/mxfp4/mxfp_quantization.py:410,548-585; mxfp_linear.py:143) and
 ``torch.ops.alto.{convert_to_nvfp4, convert_from_nvfp4, convert_to_mxfp8, convert_from_mxfp8,
 calculate_mxfp8_scales, blockwise_mxfp8_gemm}`` -- so that traced callers keep working; likewise the
-forward grouped GEMMs on quantised operands, ``torchtitan::mxfp4_grouped_gemm_forward``
-(mxfp_grouped_gemm/cg_forward.py:200) and ``alto::mxfp8_grouped_gemm_forward``
-(mxfp8_grouped_gemm/cg_forward.py:222).  The reference's backward grouped ops take operands packed along
-a non-reduction axis, which the FP4 tensor cores cannot read; the autograd functions of
-``alto_b200.grouped`` quantise both packings instead, and those two ops are not registered.  The same
+grouped GEMMs on quantised operands, ``torchtitan::mxfp4_grouped_gemm_{forward, backward_inputs,
+backward_weights}`` (mxfp_grouped_gemm/cg_forward.py:200, cg_backward.py:398, 500) and
+``alto::mxfp8_grouped_gemm_{forward, backward_inputs, backward_weights}`` (mxfp8_grouped_gemm/cg_forward.py:222,
+cg_backward.py:313, 416).  The MXFP4 backward ops serve operands packed along the reduction axis
+(``k_pack_* = True``); the reference's other packing cannot feed the FP4 tensor cores and raises.  The same
 ops are registered here as ``torch.library.custom_op`` around this package's functions.  By default
 they go under the namespace ``alto_b200``; a build that does not import the reference can claim the
 reference's own names with ``register("torchtitan", "alto")``.
@@ -95,15 +95,16 @@ def register(mxfp4_namespace: str = "alto_b200", namespace: str = "alto_b200") -
 
     @op(f"{mxfp4_namespace}::blockwise_mxfp4_gemm", mutates_args=())
     def blockwise_mxfp4_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch.Tensor,
-                             trans_a: bool = False, trans_b: bool = False, k_pack_a: bool = True,
-                             k_pack_b: bool = True, use_2dblock_a: bool = False, use_2dblock_b: bool = False,
+                             use_2dblock_a: bool = False, use_2dblock_b: bool = False, k_pack_a: bool = True,
+                             k_pack_b: bool = True, trans_a: bool = False, trans_b: bool = False,
                              block_size: int = 32, output_dtype: torch.dtype = torch.float32) -> torch.Tensor:
-        return _mx4.blockwise_mxfp4_gemm(a, a_s, b, b_s, trans_a, trans_b, k_pack_a, k_pack_b, use_2dblock_a,
-                                         use_2dblock_b, block_size, output_dtype)
+        return _mx4.blockwise_mxfp4_gemm(a, a_s, b, b_s, use_2dblock_a=use_2dblock_a, use_2dblock_b=use_2dblock_b,
+                                         k_pack_a=k_pack_a, k_pack_b=k_pack_b, trans_a=trans_a, trans_b=trans_b,
+                                         block_size=block_size, output_dtype=output_dtype)
 
     @blockwise_mxfp4_gemm.register_fake
-    def _(a, a_s, b, b_s, trans_a=False, trans_b=False, k_pack_a=True, k_pack_b=True, use_2dblock_a=False,
-          use_2dblock_b=False, block_size=32, output_dtype=torch.float32):
+    def _(a, a_s, b, b_s, use_2dblock_a=False, use_2dblock_b=False, k_pack_a=True, k_pack_b=True, trans_a=False,
+          trans_b=False, block_size=32, output_dtype=torch.float32):
         M = a.shape[1] if trans_a else a.shape[0]
         N = b.shape[0] if trans_b else b.shape[1]
         return a.new_empty((M, N), dtype=output_dtype)
@@ -225,4 +226,81 @@ def register(mxfp4_namespace: str = "alto_b200", namespace: str = "alto_b200") -
           use_dot_scaled=None):
         N = expert_weights.shape[1] if trans_weights else expert_weights.shape[2]
         return inputs.new_empty((inputs.shape[0], N), dtype=output_dtype)
+
+    # ---------------- grouped (MoE) backward GEMMs on quantised operands ----------------
+    def _dx_shape(grad_output, expert_weights, trans_weights):
+        K = expert_weights.shape[2] if trans_weights else expert_weights.shape[1]
+        return (grad_output.shape[0], K)
+
+    @op(f"{mxfp4_namespace}::mxfp4_grouped_gemm_backward_inputs", mutates_args=())
+    def mxfp4_grouped_gemm_backward_inputs(grad_output: torch.Tensor, expert_weights: torch.Tensor,
+                                           expert_indices: torch.Tensor, go_scales: torch.Tensor,
+                                           expert_weight_scales: torch.Tensor, trans_weights: bool = True,
+                                           use_2dblock_x: bool = False, use_2dblock_w: bool = True,
+                                           k_pack_w: bool = True,
+                                           output_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        return _grp.mxfp4_grouped_gemm_backward_inputs(grad_output, expert_weights, expert_indices, go_scales,
+                                                       expert_weight_scales, trans_weights, use_2dblock_x,
+                                                       use_2dblock_w, k_pack_w, output_dtype)
+
+    @mxfp4_grouped_gemm_backward_inputs.register_fake
+    def _(grad_output, expert_weights, expert_indices, go_scales, expert_weight_scales, trans_weights=True,
+          use_2dblock_x=False, use_2dblock_w=True, k_pack_w=True, output_dtype=torch.bfloat16):
+        return grad_output.new_empty(_dx_shape(grad_output, expert_weights, trans_weights), dtype=output_dtype)
+
+    @op(f"{mxfp4_namespace}::mxfp4_grouped_gemm_backward_weights", mutates_args=())
+    def mxfp4_grouped_gemm_backward_weights(grad_output: torch.Tensor, inputs: torch.Tensor,
+                                            expert_indices: torch.Tensor, num_experts: int, go_scales: torch.Tensor,
+                                            input_scales: torch.Tensor, trans_weights: bool = True,
+                                            use_2dblock_go: bool = False, use_2dblock_x: bool = True,
+                                            k_pack_go: bool = True, k_pack_x: bool = True,
+                                            output_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        return _grp.mxfp4_grouped_gemm_backward_weights(grad_output, inputs, expert_indices, num_experts, go_scales,
+                                                        input_scales, trans_weights, use_2dblock_go, use_2dblock_x,
+                                                        k_pack_go, k_pack_x, output_dtype).contiguous()
+
+    @mxfp4_grouped_gemm_backward_weights.register_fake
+    def _(grad_output, inputs, expert_indices, num_experts, go_scales, input_scales, trans_weights=True,
+          use_2dblock_go=False, use_2dblock_x=True, k_pack_go=True, k_pack_x=True, output_dtype=torch.bfloat16):
+        N, K = grad_output.shape[1], inputs.shape[1]
+        return grad_output.new_empty((num_experts, N, K) if trans_weights else (num_experts, K, N), dtype=output_dtype)
+
+    @op(f"{namespace}::mxfp8_grouped_gemm_backward_inputs", mutates_args=())
+    def mxfp8_grouped_gemm_backward_inputs(grad_output: torch.Tensor, expert_weights: torch.Tensor,
+                                           expert_indices: torch.Tensor, go_scales: torch.Tensor,
+                                           expert_weight_scales: torch.Tensor, trans_weights: bool = True,
+                                           use_2dblock_x: bool = False, use_2dblock_w: bool = True,
+                                           lhs_format_id: int = 0, rhs_format_id: int = 0,
+                                           output_dtype: torch.dtype = torch.bfloat16,
+                                           use_dot_scaled: Optional[bool] = None) -> torch.Tensor:
+        return _grp.mxfp8_grouped_gemm_backward_inputs(grad_output, expert_weights, expert_indices, go_scales,
+                                                       expert_weight_scales, trans_weights, use_2dblock_x,
+                                                       use_2dblock_w, lhs_format_id, rhs_format_id, output_dtype,
+                                                       use_dot_scaled)
+
+    @mxfp8_grouped_gemm_backward_inputs.register_fake
+    def _(grad_output, expert_weights, expert_indices, go_scales, expert_weight_scales, trans_weights=True,
+          use_2dblock_x=False, use_2dblock_w=True, lhs_format_id=0, rhs_format_id=0, output_dtype=torch.bfloat16,
+          use_dot_scaled=None):
+        return grad_output.new_empty(_dx_shape(grad_output, expert_weights, trans_weights), dtype=output_dtype)
+
+    @op(f"{namespace}::mxfp8_grouped_gemm_backward_weights", mutates_args=())
+    def mxfp8_grouped_gemm_backward_weights(grad_output: torch.Tensor, inputs: torch.Tensor,
+                                            expert_indices: torch.Tensor, num_experts: int, go_scales: torch.Tensor,
+                                            input_scales: torch.Tensor, trans_weights: bool = True,
+                                            use_2dblock_go: bool = False, use_2dblock_x: bool = False,
+                                            lhs_format_id: int = 0, rhs_format_id: int = 0,
+                                            output_dtype: torch.dtype = torch.bfloat16,
+                                            use_dot_scaled: Optional[bool] = None) -> torch.Tensor:
+        return _grp.mxfp8_grouped_gemm_backward_weights(grad_output, inputs, expert_indices, num_experts, go_scales,
+                                                        input_scales, trans_weights, use_2dblock_go, use_2dblock_x,
+                                                        lhs_format_id, rhs_format_id, output_dtype,
+                                                        use_dot_scaled).contiguous()
+
+    @mxfp8_grouped_gemm_backward_weights.register_fake
+    def _(grad_output, inputs, expert_indices, num_experts, go_scales, input_scales, trans_weights=True,
+          use_2dblock_go=False, use_2dblock_x=False, lhs_format_id=0, rhs_format_id=0, output_dtype=torch.bfloat16,
+          use_dot_scaled=None):
+        N, K = grad_output.shape[1], inputs.shape[1]
+        return grad_output.new_empty((num_experts, N, K) if trans_weights else (num_experts, K, N), dtype=output_dtype)
 

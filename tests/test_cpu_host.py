@@ -112,3 +112,24 @@ def test_oracle_gemm_definition_and_linear_consistency():
     ref = dy.float().t() @ x.float()
     snr = 10 * torch.log10(ref.pow(2).sum() / (dw - ref).pow(2).sum())
     assert snr > 9.0
+
+
+def test_boundary_signatures_match_the_reference():
+    """Parameter names, order, kinds and defaults of every boundary callable equal the reference's, as
+    read from its source by tests/golden/make_boundary_signatures.py.  Two quantizers carry one extra
+    trailing parameter (``rand_bits``: explicit random words for stochastic rounding)."""
+    import importlib
+    import inspect
+    import json
+    from pathlib import Path
+    table = json.loads((Path(__file__).resolve().parent / "golden" / "boundary_signatures.json").read_text())
+    assert len(table) >= 25
+    allowed_extra = {"convert_to_mxfp4": ["rand_bits"], "convert_to_nvfp4": ["rand_bits"]}
+    for entry in table:
+        fn = getattr(importlib.import_module(entry["module"]), entry["function"])
+        mine = [[n, "keyword_only" if p.kind == p.KEYWORD_ONLY else "positional",
+                 "<required>" if p.default is p.empty else repr(p.default)]
+                for n, p in inspect.signature(fn).parameters.items()]
+        ref = entry["params"]
+        assert mine[:len(ref)] == ref, (entry["function"], ref, mine)
+        assert [m[0] for m in mine[len(ref):]] == allowed_extra.get(entry["function"], []), entry["function"]

@@ -65,6 +65,30 @@ def test_grouped_forward_shapes():
     assert tuple(out.shape) == (384, 160) and out.dtype == torch.float32
 
 
+def test_grouped_backward_shapes():
+    ops = torch.ops.alto_b200
+    idx = _meta(256, dtype=torch.int32)
+    go8, x8 = _meta(384, 160, dtype=torch.float8_e4m3fn), _meta(384, 128, dtype=torch.float8_e4m3fn)
+    w8 = _meta(4, 160, 128, dtype=torch.float8_e4m3fn)
+    out = ops.mxfp8_grouped_gemm_backward_inputs(go8, w8, idx, _meta(384, 5, dtype=torch.uint8),
+                                                 _meta(4, 5, 4, dtype=torch.uint8))
+    assert tuple(out.shape) == (384, 128) and out.dtype == torch.bfloat16
+    out = ops.mxfp8_grouped_gemm_backward_weights(go8, x8, idx, 4, _meta(12, 160, dtype=torch.uint8),
+                                                  _meta(12, 128, dtype=torch.uint8))
+    assert tuple(out.shape) == (4, 160, 128)
+    out = ops.mxfp8_grouped_gemm_backward_weights(go8, x8, idx, 4, _meta(12, 160, dtype=torch.uint8),
+                                                  _meta(12, 128, dtype=torch.uint8), trans_weights=False)
+    assert tuple(out.shape) == (4, 128, 160)
+    go4, w4 = _meta(384, 80, dtype=torch.uint8), _meta(4, 80, 128, dtype=torch.uint8)    # packed along N
+    out = ops.mxfp4_grouped_gemm_backward_inputs(go4, w4, idx, _meta(384, 5, dtype=torch.uint8),
+                                                 _meta(4, 5, 4, dtype=torch.uint8))
+    assert tuple(out.shape) == (384, 128)
+    gom, xm = _meta(192, 160, dtype=torch.uint8), _meta(192, 128, dtype=torch.uint8)      # packed along tokens
+    out = ops.mxfp4_grouped_gemm_backward_weights(gom, xm, idx, 4, _meta(12, 160, dtype=torch.uint8),
+                                                  _meta(12, 128, dtype=torch.uint8), use_2dblock_x=False)
+    assert tuple(out.shape) == (4, 160, 128)
+
+
 def test_ops_refuse_cpu_tensors():
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         torch.ops.alto_b200.convert_to_mxfp4(torch.zeros(32, 32, dtype=torch.bfloat16))

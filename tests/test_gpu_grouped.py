@@ -284,3 +284,48 @@ def test_prequantized_grouped_forward_op_equals_the_quantize_then_function(schem
     assert int(offs[-1]) < M and not got[int(offs[-1]):].any()
     with pytest.raises(RuntimeError):
         op(xq, wq, idx[:-1], xs, ws, trans_weights=trans_weights, use_2dblock_w=use_2dblock_w)
+
+
+@pytest.mark.parametrize("scheme", ["mxfp4", "mxfp8"])
+@pytest.mark.parametrize("use_2dblock_w,trans_weights", [(True, True), (False, True), (True, False)])
+def test_prequantized_grouped_backward_ops_equal_the_autograd_gradients(scheme, use_2dblock_w, trans_weights):
+    """The registered backward ops on quantised operands (reference:
+    alto/kernels/fp4/mxfp4/mxfp_grouped_gemm/cg_backward.py:398, 500;
+    alto/kernels/mxfp8/mxfp8_grouped_gemm/cg_backward.py:313, 416) fed with the public quantizers' codes and
+    plain scales reproduce dX and dW of the quantise-then-GEMM boundary function bit for bit (RTN, no
+    Hadamard): the same codes reach the same kernels."""
+    from alto_b200 import grouped as G, mxfp4, mxfp8, torch_ops
+    torch_ops.register()
+    x, w, dy, offs, M = _case()
+    d = _dev()
+    xd, wd, dyd, offs_d = x.to(d), w.to(d), dy.to(d), offs.to(d)
+    n_exp = wd.shape[0]
+    idx = G.create_indices_from_offsets_nosync(offs_d)
+    xa, wa = xd.clone().requires_grad_(True), wd.clone().requires_grad_(True)
+    if scheme == "mxfp4":
+        ya = G._quantize_then_mxfp_scaled_grouped_mm(xa, wa.transpose(-2, -1), offs_d, False, use_2dblock_w, False,
+                                                     False, False, "none", False)
+        conv, ops = mxfp4.convert_to_mxfp4, torch.ops.alto_b200
+        dx_op, dw_op = ops.mxfp4_grouped_gemm_backward_inputs, ops.mxfp4_grouped_gemm_backward_weights
+    else:
+        ya = G._quantize_then_mxfp8_scaled_grouped_mm(xa, wa.transpose(-2, -1), offs_d, use_2dblock_w=use_2dblock_w)
+        conv, ops = mxfp8.convert_to_mxfp8, torch.ops.alto_b200
+        dx_op, dw_op = ops.mxfp8_grouped_gemm_backward_inputs, ops.mxfp8_grouped_gemm_backward_weights
+    ya.backward(dyd)
+    # dgrad operands: dY along N; W along N (axis -2 of [E, N, K]), or its 2-D quantisation
+    gq, gs = conv(dyd, axis=-1)
+    wq, ws = conv(wd, axis=-2, is_2d_block=use_2dblock_w)
+    if not trans_weights:
+        wq, ws = wq.transpose(-2, -1), ws.transpose(-2, -1)
+    dx = dx_op(gq, wq, idx, gs, ws, trans_weights=trans_weights, use_2dblock_w=use_2dblock_w)
+    assert dx.dtype == torch.bfloat16 and torch.equal(dx, xa.grad)
+    # wgrad operands: dY and X along the token axis
+    gmq, gms = conv(dyd, axis=0)
+    xmq, xms = conv(xd, axis=0)
+    dw = dw_op(gmq, xmq, idx, n_exp, gms, xms, trans_weights=trans_weights, use_2dblock_x=False)
+    want = wa.grad if trans_weights else wa.grad.transpose(-2, -1)
+    assert dw.shape == want.shape and torch.equal(dw, want)
+    assert not dx[int(offs[-1]):].any() and not wa.grad[1].any()
+    if scheme == "mxfp4":
+        with pytest.raises(NotImplementedError):
+            dx_op(gq, wq, idx, gs, ws, trans_weights=trans_weights, use_2dblock_w=use_2dblock_w, k_pack_w=False)
