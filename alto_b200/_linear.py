@@ -192,6 +192,51 @@ def cols_operand(t2, fmt, use_outer_scale, o, rht, dense, sr: dict, use_uos: boo
     return quant_cols(t2, fmt, o_m, rht, sr, use_uos, clip_mode)
 
 
+class PrequantizedWeight:
+    """A weight [N, K] that exists only as its two GEMM operands (W along K for fprop, W along N for dgrad),
+    e.g. assembled from an all-gather of quantised shards.  It stands in for the weight tensor inside the
+    linear functions: ``shape`` / ``dtype`` describe the weight it was quantised from, ``detach`` and ``to``
+    return it unchanged (there is nothing left to convert)."""
+
+    __slots__ = ("w_k", "w_t", "shape", "dtype", "fmt", "is_2d")
+
+    def __init__(self, w_k: Operand, w_t: Operand, shape, dtype, fmt: int, is_2d: bool = True):
+        self.w_k, self.w_t, self.shape, self.dtype, self.fmt, self.is_2d = w_k, w_t, tuple(shape), dtype, fmt, is_2d
+
+    def detach(self):
+        return self
+
+    def to(self, *args, **kwargs):
+        return self
+
+    def dim(self):
+        return len(self.shape)
+
+
+def activation_operands(x2, fmt, *, use_2dblock_x, use_outer_scale, rht, dense=None, use_uos=False, clip_mode="none"):
+    """(x_k, x_m): X along K (fprop) and X along M after the optional Hadamard rotation (wgrad)."""
+    ox = outer_scales(x2, use_outer_scale, None if use_2dblock_x else rht)
+    if use_2dblock_x:
+        return quant_2d(x2, fmt, None if ox is None else ox[0:1], True, use_uos)
+    x_k = quant_rows(x2, fmt, None if ox is None else ox[0:1], RTN, use_uos)
+    x_m = cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, RTN, use_uos, clip_mode)
+    return x_k, x_m
+
+
+def weight_operands(w2, fmt, *, use_2dblock_w, use_outer_scale, use_uos=False):
+    """(w_k, w_t): W along K (fprop) and W along N (dgrad)."""
+    if isinstance(w2, PrequantizedWeight):
+        torch._check(w2.fmt == fmt and w2.is_2d == bool(use_2dblock_w), lambda: (
+            "the pre-quantised weight was built for another recipe than the one this linear runs"))
+        return w2.w_k, w2.w_t
+    ow = outer_scales(w2, use_outer_scale, None)
+    if use_2dblock_w:
+        return quant_2d(w2, fmt, None if ow is None else ow[0:1], True, use_uos)
+    w_k = quant_rows(w2, fmt, None if ow is None else ow[0:1], RTN, use_uos)
+    w_t = quant_cols(w2, fmt, None if ow is None else ow[0:1], None, RTN, use_uos)
+    return w_k, w_t
+
+
 def forward_operands(x2, w2, fmt, *, use_2dblock_x, use_2dblock_w, use_outer_scale, rht, dense=None,
                      use_uos=False, clip_mode="none"):
     """Returns (x_k, x_m, w_k, w_t): X along K (fprop), X along M after the optional Hadamard
@@ -199,18 +244,9 @@ def forward_operands(x2, w2, fmt, *, use_2dblock_x, use_2dblock_w, use_outer_sca
     # Every pass over one tensor is launched before the first pass over the other: X at the benchmark
     # shapes (64 MiB) stays in the 126 MB L2 between its amax pass and its two quantizers, and W's
     # quantizer finds the tail of W that its amax pass left there.
-    ox = outer_scales(x2, use_outer_scale, None if use_2dblock_x else rht)
-    if use_2dblock_x:
-        x_k, x_m = quant_2d(x2, fmt, None if ox is None else ox[0:1], True, use_uos)
-    else:
-        x_k = quant_rows(x2, fmt, None if ox is None else ox[0:1], RTN, use_uos)
-        x_m = cols_operand(x2, fmt, use_outer_scale, ox, rht, dense, RTN, use_uos, clip_mode)
-    ow = outer_scales(w2, use_outer_scale, None)
-    if use_2dblock_w:
-        w_k, w_t = quant_2d(w2, fmt, None if ow is None else ow[0:1], True, use_uos)
-    else:
-        w_k = quant_rows(w2, fmt, None if ow is None else ow[0:1], RTN, use_uos)
-        w_t = quant_cols(w2, fmt, None if ow is None else ow[0:1], None, RTN, use_uos)
+    x_k, x_m = activation_operands(x2, fmt, use_2dblock_x=use_2dblock_x, use_outer_scale=use_outer_scale, rht=rht,
+                                   dense=dense, use_uos=use_uos, clip_mode=clip_mode)
+    w_k, w_t = weight_operands(w2, fmt, use_2dblock_w=use_2dblock_w, use_outer_scale=use_outer_scale, use_uos=use_uos)
     return x_k, x_m, w_k, w_t
 
 
@@ -269,14 +305,15 @@ def linear_forward(ctx, name: str, x, weight, fmt, *, use_2dblock_x, use_2dblock
         raise RuntimeError(f"{name} runs on CUDA tensors only (no CPU fallback)")
     original_shape = x.shape
     x2 = as_2d_rows(x.detach())
-    w2 = as_2d_rows(weight.detach())
+    pre = isinstance(weight, PrequantizedWeight)
+    w2 = weight if pre else as_2d_rows(weight.detach())
     M, K = x2.shape
     N = w2.shape[0]
     check_dims(name, M, K, N)
     rht, dense = split_transform(hadamard_transform, use_2dblock_x)
     ctx.xm_ready = None
     plain = not use_uos and clip_mode == "none"
-    if OVERLAP and not use_2dblock_x and dense is None and plain:
+    if OVERLAP and not use_2dblock_x and dense is None and plain and not pre:
         main = torch.cuda.current_stream(x2.device)
         side = _side_stream(x2.device)
         ox = outer_scales(x2, use_outer_scale, rht)

@@ -85,23 +85,46 @@ if hasattr(torch.ops, "c10d") and hasattr(torch.ops.c10d, "scatter_"):
 gemm_ops = ("linear", "mm.default", "matmul.default", "addmm.default", "matmul")
 
 
+def _rewrap(cls, value, config):
+    """Plain tensors inside ``value`` (a tensor or a container of tensors) become ``cls`` wrappers."""
+    return pytree.tree_map_only(torch.Tensor, lambda t: cls(t, config), value)
+
+
 class TrainingWeightWrapperBaseTensor(torch.Tensor):
-    """Wrapper subclass holding the high-precision weight in ``_data`` and the recipe in ``config``."""
+    """A parameter's data together with its quantisation recipe.
+
+    The wrapper has the shape, dtype and device of the high-precision weight, which it keeps in
+    ``_data``; ``config`` is the ``TrainingOpConfig`` the GEMM subclasses below act on.  The role is that of
+    the reference's class of the same name (alto/kernels/dispatch/tensor.py:53-211): house-keeping ops
+    (views, copies, slices, detach ...) keep the wrapper so that parameter sharding and checkpointing see
+    a weight that behaves like a tensor, any other op sees the plain data, and a GEMM that arrives below
+    autograd is refused.
+
+    One state has no counterpart in the reference: after a *quantised* FSDP all-gather the unsharded
+    wrapper holds no high-precision data at all, only the two GEMM operands of the full weight
+    (``_prequant``, a ``_linear.PrequantizedWeight``); ``_data`` is then an empty tensor and only GEMMs
+    (and the FSDP hooks) may touch the wrapper."""
 
     config: Optional[TrainingOpConfig] = None
+    _prequant = None
 
     @staticmethod
-    def __new__(cls, tensor: torch.Tensor, config: TrainingOpConfig):
-        self = torch.Tensor._make_wrapper_subclass(
+    def __new__(cls, tensor: torch.Tensor, config: TrainingOpConfig, prequant=None):
+        if prequant is not None:
+            shape = torch.Size(prequant.shape)
+            strides = tuple(torch.empty(shape, device="meta").stride())
+            return torch.Tensor._make_wrapper_subclass(
+                cls, shape, strides=strides, storage_offset=0, dtype=prequant.dtype, layout=torch.strided,
+                device=prequant.w_k.codes.device, requires_grad=tensor.requires_grad)
+        return torch.Tensor._make_wrapper_subclass(
             cls, tensor.size(), strides=tensor.stride(), storage_offset=tensor.storage_offset(),
             memory_format=suggest_memory_format(tensor), dtype=tensor.dtype, layout=tensor.layout,
             device=tensor.device, pin_memory=tensor.is_pinned(), requires_grad=tensor.requires_grad)
-        self.config = config
-        return self
 
-    def __init__(self, tensor: torch.Tensor, config: TrainingOpConfig):
+    def __init__(self, tensor: torch.Tensor, config: TrainingOpConfig, prequant=None):
         self._data = tensor
         self.config = config
+        self._prequant = prequant
 
     @classmethod
     def __torch_function__(cls, func, types, args, kwargs={}):
@@ -111,35 +134,41 @@ class TrainingWeightWrapperBaseTensor(torch.Tensor):
 
     @classmethod
     def __torch_dispatch__(cls, func, types, args, kwargs={}):
-        config = None
-
-        def unwrap(t):
-            nonlocal config
-            if config is None:
-                config = t.config
-            else:
-                assert t.config == config, (
-                    "All TrainingWeightWrapperBaseTensor instances must have the same config, but found "
-                    f"{t.config} and {config}")
-            return t._data
-
-        args_u, kwargs_u = pytree.tree_map_only(TrainingWeightWrapperBaseTensor, unwrap, (args, kwargs or {}))
-        assert config is not None, (
+        kwargs = kwargs or {}
+        flat, _ = pytree.tree_flatten((args, kwargs))
+        wrappers = [t for t in flat if isinstance(t, TrainingWeightWrapperBaseTensor)]
+        assert wrappers, (
             f"__torch_dispatch__ called on {func.__name__} without any TrainingWeightWrapperBaseTensor arguments")
-        if func == torch.ops.aten.detach.default:
-            return cls(args_u[0], config)
+        config = wrappers[0].config
+        for t in wrappers[1:]:
+            assert t.config == config, (
+                "All TrainingWeightWrapperBaseTensor instances must have the same config, but found "
+                f"{t.config} and {config}")
+        if any(t._prequant is not None for t in wrappers):
+            w = wrappers[0]
+            same_view = func in (torch.ops.aten.detach.default, torch.ops.aten.alias.default) or (
+                func in (torch.ops.aten.as_strided.default, torch.ops.aten.view.default)
+                and tuple(args[1]) == tuple(w.shape)
+                and (func != torch.ops.aten.as_strided.default or tuple(args[2]) == tuple(w.stride())))
+            if same_view:       # FSDP re-views the unsharded parameter with its own size and stride
+                return cls(w._data, config, w._prequant)
+            raise RuntimeError(f"{func.__name__} on a weight that exists only in quantised form (after a quantised "
+                               "all-gather); only GEMMs may use it")
+        plain_args, plain_kwargs = pytree.tree_map_only(TrainingWeightWrapperBaseTensor, lambda t: t._data,
+                                                        (args, kwargs))
         if func.__name__ in gemm_ops or func.__name__ == "_grouped_mm":
             raise ValueError("You have reached the __torch_dispatch__ method of low-precision GEMMs, "
                              "which does not support Autograd Function."
                              "This is commonly caused by unsupported tensor parallel.")
-        out = func(*args_u, **kwargs_u)
-        if func not in _ops_to_preserve_subclass:
-            return out
-        return pytree.tree_map_only(torch.Tensor, lambda x: cls(x, config), out)
+        result = func(*plain_args, **plain_kwargs)
+        keeps_wrapper = func == torch.ops.aten.detach.default or func in _ops_to_preserve_subclass
+        return _rewrap(cls, result, config) if keeps_wrapper else result
 
     def __repr__(self):
-        return f"{type(self).__name__}(data={self._data}, config={self.config})"
+        what = "quantised operands" if self._prequant is not None else f"data={self._data}"
+        return f"{type(self).__name__}({what}, config={self.config})"
 
+    # -- the traceable-wrapper-subclass protocol (names and forms prescribed by PyTorch) --
     def __tensor_flatten__(self):
         return ["_data"], {"config": self.config}
 
@@ -150,34 +179,141 @@ class TrainingWeightWrapperBaseTensor(torch.Tensor):
     def untyped_storage(self):
         return self._data.untyped_storage()
 
-    # FSDP2 extension hooks: the high-precision weight is all-gathered in the mixed-precision
-    # parameter dtype; quantisation happens per step on the gathered weight
-    # (alto/kernels/dispatch/tensor.py:159-211).
+    # -- FSDP2 extension hooks ------------------------------------------------------------------------
+    # The reference all-gathers the weight in the mixed-precision parameter dtype and quantises the whole
+    # tensor on every rank, every step (alto/kernels/dispatch/tensor.py:159-211).  When the recipe
+    # quantises weights in 2-D blocks and the shard boundaries fall on block and scale-tile boundaries,
+    # the shard is quantised HERE, before the gather, and the 4.5-bit (FP4) or 8.25-bit (FP8) payload
+    # of both GEMM operands travels instead: the gathered operands equal those of the unsharded weight bit
+    # for bit, because no block straddles a shard and the NVFP4 tensorwise scale comes from the MAX
+    # all-reduce of the shards' amax.  Otherwise the high-precision gather of the reference is used.
     def fsdp_pre_all_gather(self, mesh, outer_size, outer_stride, module, mp_policy):
-        return (self._data.to(mp_policy.param_dtype),), ()
+        import alto_b200.dispatch as D
+        data = self._data.to(mp_policy.param_dtype) if mp_policy.param_dtype is not None else self._data
+        plan = D.quantized_gather_plan(data, self.config, mesh)
+        if plan is None:
+            return (data,), None
+        payload, meta = D.quantize_shard_for_gather(data, self.config, plan)
+        return payload, meta
 
     def fsdp_post_all_gather(self, all_gather_outputs: Tuple[torch.Tensor, ...], metadata: Any,
                              param_dtype: torch.dtype, *, out: Optional[torch.Tensor] = None):
-        (data,) = all_gather_outputs
+        import alto_b200.dispatch as D
+        target = None
         if out is not None:
             from torch.distributed._tensor import DTensor
-            if isinstance(out, TrainingWeightWrapperBaseTensor):
-                out_data = out._data
-                out.config = self.config
-            elif isinstance(out, DTensor) and isinstance(out._local_tensor, TrainingWeightWrapperBaseTensor):
-                out_data = out._local_tensor._data
-                out._local_tensor.config = self.config
-            else:
+            target = out._local_tensor if isinstance(out, DTensor) else out
+            if not isinstance(target, TrainingWeightWrapperBaseTensor):
                 raise RuntimeError(
                     "expect out to be TrainingWeightWrapperBaseTensor or DTensor with "
                     f"local_tensor=TrainingWeightWrapperBaseTensor, but got {type(out)}")
+            target.config = self.config
+        if metadata is not None:
+            pre = D.assemble_gathered_weight(all_gather_outputs, metadata,
+                                             None if target is None else target._prequant)
+            if target is not None:
+                target._prequant = pre
+                return
+            empty = self._data.new_empty(0, dtype=pre.dtype).requires_grad_(self.requires_grad)
+            return type(self)(empty, self.config, pre), tuple(all_gather_outputs)
+        (data,) = all_gather_outputs
+        if target is not None:
+            # FSDP hands back the tensor it was given last time: same storage when no cast was needed
             if data.dtype == param_dtype:
-                assert data.untyped_storage().data_ptr() == out_data.untyped_storage().data_ptr()
+                assert data.untyped_storage().data_ptr() == target._data.untyped_storage().data_ptr()
             else:
-                assert out_data.dtype == param_dtype, f"{out_data.dtype} {param_dtype}"
-                out_data.copy_(data)
+                assert target._data.dtype == param_dtype, f"{target._data.dtype} {param_dtype}"
+                target._data.copy_(data)
             return
         return type(self)(data, self.config), (data,)
+
+
+# ---------------------------------------------------------------------------------------------
+# quantised FSDP all-gather: plan, shard quantisation, assembly
+# ---------------------------------------------------------------------------------------------
+_GATHER_FMT = {"nvfp4": 0, "mxfp4": 1, "mxfp8_e4m3": 2, "mxfp8_e5m2": 3}      # _lib.FMT_*
+
+#: set to False to keep the reference's high-precision all-gather everywhere
+QUANTIZED_ALL_GATHER = True
+
+
+def _shard_group(mesh):
+    if mesh is None:
+        return None, 1
+    group = mesh.get_group(mesh.ndim - 1) if mesh.ndim > 1 else mesh.get_group()
+    return group, torch.distributed.get_world_size(group)
+
+
+def quantized_gather_plan(data: torch.Tensor, config: TrainingOpConfig, mesh):
+    """-> dict(group, world, fmt, block, n, K) when this weight shard can travel in quantised form, else
+    None: a 2-D weight [n, K] sharded by rows, 2-D weight blocks, no two-level *blockwise* scaling (its
+    macro factors are not part of the payload), and every shard made of whole 128-row scale tiles."""
+    if not QUANTIZED_ALL_GATHER or config is None or not config.use_2dblock_w:
+        return None
+    if config.precision not in _GATHER_FMT or config.two_level_scaling == "blockwise":
+        return None
+    if data.dim() != 2 or not data.is_cuda or data.dtype not in (torch.bfloat16, torch.float32):
+        return None
+    group, world = _shard_group(mesh)
+    if world == 1:
+        return None     # nothing travels; FSDP2's single-rank path also takes only one all-gather input
+    fmt = _GATHER_FMT[config.precision]
+    block = 16 if fmt == 0 else 32
+    n, K = data.shape
+    if n == 0 or n % 128 != 0 or (n // block) % 4 != 0 or K % 128 != 0:
+        return None
+    return dict(group=group, world=world, fmt=fmt, block=block, n=n, K=K)
+
+
+def quantize_shard_for_gather(data: torch.Tensor, config: TrainingOpConfig, plan):
+    """-> ((codes_k, scales_k, codes_t, scales_t [, outer]), metadata): both GEMM operands of the shard."""
+    from . import _lib as L
+    from . import _linear as E
+    from . import distributed as Dist
+    w2 = E.as_2d_rows(data.detach())
+    outer = None
+    if config.precision == "nvfp4" and config.two_level_scaling == "tensorwise":
+        bits = torch.empty(2, dtype=torch.int32, device=w2.device)
+        L.amax(w2, bits, None, E.amax_scratch(w2.device), None)
+        if plan["world"] > 1:
+            torch.distributed.all_reduce(bits, op=torch.distributed.ReduceOp.MAX, group=plan["group"])
+        outer = Dist.outer_scale_from_amax_bits(bits[0:1])
+    w_k, w_t = E.quant_2d(w2, plan["fmt"], outer, True, bool(config.use_uos))
+    payload = [w_k.codes.view(-1), w_k.scales.view(-1), w_t.codes.view(-1), w_t.scales.view(-1)]
+    if outer is not None:
+        payload.append(outer.view(torch.uint8))     # identical on every rank; rides along as four bytes
+    meta = dict(world=plan["world"], fmt=plan["fmt"], block=plan["block"], n=plan["n"], K=plan["K"],
+                dtype=data.dtype, has_outer=outer is not None)
+    return tuple(payload), meta
+
+
+def assemble_gathered_weight(outputs, meta, reuse=None):
+    """Rank-major all-gather outputs of ``quantize_shard_for_gather`` -> ``PrequantizedWeight`` of the whole
+    weight [world * n, K].  W along K: the ranks' code rows and scale tiles are already in row order.  W
+    along N: every rank holds a column slice, so codes and scale tiles are interleaved rank by rank.
+    ``reuse``: the object returned for the previous gather; its interleaved buffers are refilled in place."""
+    from . import _linear as E
+    from . import distributed as Dist
+    world, n, K, fmt = meta["world"], meta["n"], meta["K"], meta["fmt"]
+    N = world * n
+    fp4 = fmt in (0, 1)
+    ck = outputs[0].view(N, K // 2 if fp4 else K)
+    sk = outputs[1].view(-1)
+    ct = Dist.interleave_gathered_columns(outputs[2], world, K, (n // 2) if fp4 else n)
+    st = Dist.interleave_gathered_columns(outputs[3], world, (K + 127) // 128, outputs[3].numel() // world //
+                                          ((K + 127) // 128)).reshape(-1)
+    outer = None
+    if meta["has_outer"]:
+        outer = outputs[4].view(-1)[:4].clone().view(torch.float32)
+    if reuse is not None:
+        reuse.w_k.codes, reuse.w_k.scales, reuse.w_k.outer = ck, sk, outer
+        reuse.w_t.codes.copy_(ct)
+        reuse.w_t.scales.copy_(st)
+        reuse.w_t.outer = outer
+        return reuse
+    w_k = E.Operand(ck, sk, outer, N, K, fmt)
+    w_t = E.Operand(ct.contiguous(), st.contiguous(), outer, K, N, fmt)
+    return E.PrequantizedWeight(w_k, w_t, (N, K), meta["dtype"], fmt, True)
 
 
 def _split_gemm_args(func, args):

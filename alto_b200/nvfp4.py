@@ -43,6 +43,9 @@ def unwrap_weight_wrapper(weight: torch.Tensor) -> torch.Tensor:
     """alto/kernels/fp4/fp4_common/tensor_wrappers.py:8-30."""
     if type(weight) is torch.Tensor:
         return weight
+    pre = getattr(weight, "_prequant", None)
+    if pre is not None:          # a wrapper that holds only the quantised operands (quantised all-gather)
+        return pre
     if hasattr(weight, "_data"):
         return weight._data
     return weight.as_subclass(torch.Tensor)

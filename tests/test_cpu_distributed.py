@@ -209,3 +209,84 @@ def _gather_worker(rank, world):
 
 def test_quantised_weight_gathers_two_ranks():
     _spawn(_gather_worker)
+
+
+# ---------------------------------------------------------------------------------------------
+# The wrapper's FSDP hooks: pre-all-gather payload of a row shard -> gather -> assembled operands
+# ---------------------------------------------------------------------------------------------
+def _cpu_quantize_shard(data, config, plan):
+    """CPU stand-in for ``dispatch.quantize_shard_for_gather`` built on the oracle: MXFP4 in 32 x 32 blocks,
+    both packings, packed scales (tests may use the oracle; the product hook runs the CUDA quantizer)."""
+    from oracle import alto_oracle as O
+    from alto_b200._linear import pack_plain_scales
+    n, K = data.shape
+    q, s = O.quantize_mxfp4(data, 32, -1, True)                       # [n, K/2], [n/32, K/32]
+    qt, _ = O.quantize_mxfp4(data.t().contiguous(), 32, -1, True)     # [K, n/2]
+    payload = (q.reshape(-1), pack_plain_scales(s, n, True, 32), qt.reshape(-1),
+               pack_plain_scales(s.t().contiguous(), K, True, 32))
+    meta = dict(world=plan["world"], fmt=1, block=32, n=n, K=K, dtype=data.dtype, has_outer=False)
+    return payload, meta
+
+
+def _fsdp_hook_worker(rank, world):
+    from types import SimpleNamespace
+    from alto_b200 import dispatch as Dp
+    from alto_b200._linear import pack_plain_scales
+    from oracle import alto_oracle as O
+    N, K = 256 * world, 256
+    g = torch.Generator().manual_seed(3)
+    W = torch.randn(N, K, generator=g).bfloat16()
+    cfg = Dp.TrainingOpConfig(precision="mxfp4", use_2dblock_x=False, use_2dblock_w=True, use_hadamard=False,
+                              use_sr_grad=False, use_dge=False)
+    n = N // world
+    shard = Dp.MXFP4TrainingWeightWrapperTensor(W[rank * n:(rank + 1) * n].clone(), cfg)
+    # the product plan wants CUDA data; everything else of it is exercised as it is
+    real_plan = Dp.quantized_gather_plan
+    Dp.quantized_gather_plan = lambda data, config, mesh: dict(group=None, world=world, fmt=1, block=32,
+                                                               n=data.shape[0], K=data.shape[1])
+    Dp.quantize_shard_for_gather = _cpu_quantize_shard
+    try:
+        policy = SimpleNamespace(param_dtype=torch.bfloat16)
+        payload, meta = shard.fsdp_pre_all_gather(None, torch.Size([N, K]), (K, 1), None, policy)
+        assert len(payload) == 4 and all(p.dtype == torch.uint8 for p in payload)
+        gathered = []
+        for p in payload:                                            # what FSDP's all-gather does, per input
+            out = torch.empty(world * p.numel(), dtype=p.dtype)
+            dist.all_gather_into_tensor(out, p.contiguous().view(-1))
+            gathered.append(out)
+        full, inner = shard.fsdp_post_all_gather(tuple(gathered), meta, torch.bfloat16)
+        assert isinstance(full, Dp.MXFP4TrainingWeightWrapperTensor) and full.shape == (N, K)
+        assert full.dtype == torch.bfloat16 and len(inner) == 4
+        pre = full._prequant
+        q, s = O.quantize_mxfp4(W, 32, -1, True)
+        qt, _ = O.quantize_mxfp4(W.t().contiguous(), 32, -1, True)
+        assert torch.equal(pre.w_k.codes, q) and torch.equal(pre.w_t.codes, qt)
+        assert torch.equal(pre.w_k.scales, pack_plain_scales(s, N, True, 32))
+        assert torch.equal(pre.w_t.scales, pack_plain_scales(s.t().contiguous(), K, True, 32))
+        assert (pre.w_k.rows, pre.w_k.k, pre.w_t.rows, pre.w_t.k) == (N, K, K, N)
+        # second gather into the same unsharded parameter: operands are refilled in place
+        W2 = (W.float() * 0.5 + 1.0).bfloat16()
+        shard2 = Dp.MXFP4TrainingWeightWrapperTensor(W2[rank * n:(rank + 1) * n].clone(), cfg)
+        payload2, meta2 = shard2.fsdp_pre_all_gather(None, torch.Size([N, K]), (K, 1), None, policy)
+        for out, p in zip(gathered, payload2):
+            dist.all_gather_into_tensor(out, p.contiguous().view(-1))
+        t_codes = pre.w_t.codes
+        assert shard2.fsdp_post_all_gather(tuple(gathered), meta2, torch.bfloat16, out=full) is None
+        q2, _ = O.quantize_mxfp4(W2, 32, -1, True)
+        qt2, _ = O.quantize_mxfp4(W2.t().contiguous(), 32, -1, True)
+        assert full._prequant is pre and pre.w_t.codes is t_codes
+        assert torch.equal(pre.w_k.codes, q2) and torch.equal(pre.w_t.codes, qt2)
+        # only identity re-views and detach are allowed on a weight that exists in quantised form
+        assert torch.as_strided(full, full.shape, full.stride())._prequant is pre
+        with pytest.raises(RuntimeError, match="quantised form"):
+            full.t()
+        # shards that do not end on scale-tile boundaries keep the high-precision gather of the reference
+        Dp.quantized_gather_plan = real_plan
+        (hp,), none_meta = shard.fsdp_pre_all_gather(None, torch.Size([N, K]), (K, 1), None, policy)
+        assert none_meta is None and hp.dtype == torch.bfloat16 and hp.shape == (n, K)
+    finally:
+        Dp.quantized_gather_plan = real_plan
+
+
+def test_fsdp_hooks_gather_quantised_operands_two_ranks():
+    _spawn(_fsdp_hook_worker)

@@ -333,3 +333,87 @@ def test_full_size_expert_parallel_moe_and_column_sharded_linear(world):
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     mp.spawn(_full_size_worker, args=(world, _free_port()), nprocs=world, join=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# FSDP2 (`fully_shard`) over wrapped parameters: the all-gather carries the quantised weight
+# ---------------------------------------------------------------------------------------------
+def _fsdp_worker(rank, world, port, precision, two_level):
+    """A Linear whose weight was wrapped by ``swap_params`` under ``fully_shard``: the pre / post all-gather
+    hooks of the wrapper quantise the row shard and gather the operands.  Forward must equal the
+    unsharded boundary function bit for bit (2-D blocks never straddle a shard), dX too, and the
+    reduce-scattered weight gradient must be the mean over ranks of the single-GPU gradients."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from torch.distributed.fsdp import fully_shard
+        from alto_b200 import dispatch as D
+        from alto_b200 import mxfp8 as M8, nvfp4 as NV
+        N, K, M = 512, 256, 128
+        g = torch.Generator().manual_seed(7)
+        W = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(dev)
+        xs = [torch.randn(M, K, generator=g).bfloat16().to(dev) for _ in range(world)]
+        dys = [(torch.randn(M, N, generator=g) * 1e-2).bfloat16().to(dev) for _ in range(world)]
+        cfg = D.TrainingOpConfig(precision=precision, use_2dblock_x=False, use_2dblock_w=True, use_hadamard=False,
+                                 use_sr_grad=False, use_dge=False, two_level_scaling=two_level)
+        lin = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            lin.weight.copy_(W)
+        calls = {"n": 0}
+        real = D.quantize_shard_for_gather
+
+        def counting(*a, **k):
+            calls["n"] += 1
+            return real(*a, **k)
+
+        D.quantize_shard_for_gather = counting
+        D.swap_params(lin, config=cfg)
+        fully_shard(lin)
+
+        def ref(a, w):
+            if precision == "nvfp4":
+                return NV._to_nvfp4_then_scaled_mm(a, w, False, True, False, use_outer_scale=two_level == "tensorwise")
+            return M8._to_mxfp8_then_scaled_mm(a, w, "e4m3", False, False, True)
+
+        for it in range(2):                      # second pass: the hooks refill the operands in place
+            x = xs[rank].clone().requires_grad_(True)
+            y = lin(x)
+            y.backward(dys[rank])
+            wr = W.clone().requires_grad_(True)
+            xr = xs[rank].clone().requires_grad_(True)
+            yr = ref(xr, wr)
+            yr.backward(dys[rank])
+            assert torch.equal(y, yr), f"forward differs on pass {it}"
+            assert torch.equal(x.grad, xr.grad), f"dX differs on pass {it}"
+            # mean over ranks of the full single-GPU weight gradients, this rank's rows
+            dws = []
+            for r in range(world):
+                w_ = W.clone().requires_grad_(True)
+                ref(xs[r].clone(), w_).backward(dys[r])
+                dws.append(w_.grad.float())
+            want = (sum(dws) / world)[rank * (N // world):(rank + 1) * (N // world)]
+            got = lin.weight.grad
+            got = got.to_local() if hasattr(got, "to_local") else got
+            got = got._data if hasattr(got, "_data") else got
+            assert got.shape == want.shape
+            assert ((got.float() - want).norm() / want.norm()).item() <= 1e-2
+            lin.weight.grad = None
+        if world > 1:
+            assert calls["n"] >= 2, "the quantised all-gather was not taken"
+        else:
+            assert calls["n"] == 0      # one rank: nothing to gather, the weight stays in high precision
+        torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+@pytest.mark.parametrize("precision,two_level", [("nvfp4", "tensorwise"), ("mxfp8_e4m3", "none")])
+def test_fully_shard_gathers_the_quantised_weight(world, precision, two_level):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_fsdp_worker, args=(world, _free_port(), precision, two_level), nprocs=world, join=True)
