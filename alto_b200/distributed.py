@@ -54,40 +54,56 @@ def _rank(group) -> int:
 # data parallel: all-reduce of weight gradients
 # ------------------------------------------------------------------------------------------
 def allreduce_gradients(params: Sequence[torch.Tensor], group=None, bucket_bytes: int = 64 << 20,
-                        average: bool = True) -> int:
+                        average: bool = True, max_in_flight: int = 2) -> int:
     """Sums (or averages) ``p.grad`` over the ranks of ``group`` in buckets of ``bucket_bytes``:
     each bucket is one flat all-reduce, issued asynchronously so that copy-in of the next bucket
     overlaps the reduction of the previous one.  Returns the number of collectives issued.
 
+    The bucket plan is a function of the parameter list alone (shapes and dtypes), not of which
+    gradients exist on this rank: a parameter without a gradient contributes zeros, so every rank
+    issues the same collectives.  At most ``max_in_flight`` flat buffers are alive at a time (the
+    oldest bucket is waited for and scattered back before another one is flattened), which bounds
+    the extra memory at ``max_in_flight * bucket_bytes`` instead of a copy of all gradients.
+
     Buckets are sized for launch latency and overlap, not for link count: NVSwitch gives every
     peer full bandwidth, and NCCL reduces inside the switch when it can."""
     world = _world(group)
-    grads = [p.grad for p in params if p.grad is not None]
-    if world == 1 or not grads:
+    params = [p for p in params if p.requires_grad]
+    if world == 1 or not params:
         return 0
     buckets: List[List[torch.Tensor]] = [[]]
     size = 0
-    for g in grads:
-        nbytes = g.numel() * g.element_size()
-        if buckets[-1] and (size + nbytes > bucket_bytes or g.dtype != buckets[-1][0].dtype):
+    for p in params:
+        nbytes = p.numel() * p.element_size()
+        if buckets[-1] and (size + nbytes > bucket_bytes or p.dtype != buckets[-1][0].dtype):
             buckets.append([])
             size = 0
-        buckets[-1].append(g)
+        buckets[-1].append(p)
         size += nbytes
-    pending = []
-    for b in buckets:
-        flat = torch.cat([g.reshape(-1) for g in b])
-        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=True)
-        pending.append((work, flat, b))
-    for work, flat, b in pending:
+
+    def finish(work, flat, bucket):
         work.wait()
         if average:
             flat.div_(world)
         off = 0
-        for g in b:
-            g.copy_(flat[off:off + g.numel()].view_as(g))
-            off += g.numel()
-    return len(pending)
+        for p in bucket:
+            piece = flat[off:off + p.numel()].view(p.shape)
+            if p.grad is None:
+                p.grad = piece.clone()
+            else:
+                p.grad.copy_(piece)
+            off += p.numel()
+
+    pending = []
+    for b in buckets:
+        if len(pending) >= max_in_flight:
+            finish(*pending.pop(0))
+        flat = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1) for p in b])
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=True)
+        pending.append((work, flat, b))
+    for item in pending:
+        finish(*item)
+    return len(buckets)
 
 
 # ------------------------------------------------------------------------------------------
@@ -279,7 +295,7 @@ def permute_pad_plan(recv_counts: torch.Tensor, align: int = ALIGN_SIZE_M, total
     tensors on the same device ``(index, inverse, offs)``: ``index`` int32 [M_pad] gives for every row
     of the expert-major, padded layout its row in the receive buffer (-1 = padding row); ``inverse``
     int32 [rows_received] is the opposite map; ``offs`` int32 [local_experts] are the cumulative
-    padded row counts the grouped GEMMs take (every count a multiple of ``align``).
+    padded row counts the grouped GEMMs take (every count a multiple of ``align`` and at least ``align``).
 
     ``total`` (rows received) and ``m_pad`` (padded rows, ``offs[-1]``) are read back from the counts
     when not given; a caller that has the counts on the host passes both, so that a plan built on
@@ -288,7 +304,9 @@ def permute_pad_plan(recv_counts: torch.Tensor, align: int = ALIGN_SIZE_M, total
     dev = c.device
     S, E = c.shape
     per_expert = c.sum(0)
-    padded = (per_expert + align - 1) // align * align
+    # an expert without rows still gets one aligned run of padding, as TorchTitan's permute step gives it:
+    # a rank whose experts received nothing then has a non-empty buffer and takes part in every exchange
+    padded = ((per_expert + align - 1) // align * align).clamp(min=align)
     offs = torch.cumsum(padded, 0)
     pad_start = offs - padded                                   # [E]
     recv_start = (torch.cumsum(c.reshape(-1), 0) - c.reshape(-1)).reshape(S, E)
@@ -416,7 +434,7 @@ class ExpertParallelDispatcher:
         # The row plan is built on the GPU from the device copy of the counts; the host copy only
         # sizes its buffers (and the all-to-all), so the host is free to run ahead again at once.
         per_expert = recv_h.sum(0)
-        m_pad = int(((per_expert + self.align - 1) // self.align * self.align).sum())
+        m_pad = int(((per_expert + self.align - 1) // self.align * self.align).clamp(min=self.align).sum())
         st.index, st.inverse, st.offs = permute_pad_plan(recv, self.align, total=sum(st.out_splits), m_pad=m_pad)
         token_of_sorted = torch.div(order, k, rounding_mode="floor").to(torch.int32)
         rows = _ReplicateSorted.apply(x, token_of_sorted, st.inv_order, k)

@@ -46,18 +46,21 @@ def _spawn(fn, *args, world=2):
 def test_permute_pad_plan_layout():
     c = torch.tensor([[3, 0, 130], [2, 0, 1]])        # 2 sources x 3 local experts
     index, inverse, offs = D.permute_pad_plan(c, 128)
-    assert offs.tolist() == [128, 128, 128 + 256]
-    assert index.numel() == 384 and inverse.numel() == 136
+    # expert 1 received nothing and still gets one aligned run of padding (TorchTitan's permute step
+    # clamps every expert to the alignment)
+    assert offs.tolist() == [128, 256, 256 + 256]
+    assert index.numel() == 512 and inverse.numel() == 136
     # expert 0: 3 rows of source 0 (receive rows 0..2) then 2 rows of source 1 (rows 133, 134)
-    assert index[:5].tolist() == [0, 1, 2, 133, 134] and (index[5:128] == -1).all()
-    # expert 2 starts at 128: 130 rows of source 0 (receive rows 3..132) then row 135 of source 1
-    assert index[128:258].tolist() == list(range(3, 133)) and index[258].item() == 135
-    assert (index[259:] == -1).all()
+    assert index[:5].tolist() == [0, 1, 2, 133, 134] and (index[5:256] == -1).all()
+    # expert 2 starts at 256: 130 rows of source 0 (receive rows 3..132) then row 135 of source 1
+    assert index[256:386].tolist() == list(range(3, 133)) and index[386].item() == 135
+    assert (index[387:] == -1).all()
     ok = index >= 0
     assert torch.equal(inverse[index[ok].long()].long(), torch.nonzero(ok).squeeze(1))
-    # no rows at all
+    # no rows at all: every expert is one run of padding, so a rank that received nothing still has a
+    # buffer the grouped GEMMs accept and stays in step with its peers
     index, inverse, offs = D.permute_pad_plan(torch.zeros(2, 3, dtype=torch.int64))
-    assert index.numel() == 0 and inverse.numel() == 0 and offs.tolist() == [0, 0, 0]
+    assert index.numel() == 384 and (index == -1).all() and inverse.numel() == 0 and offs.tolist() == [128, 256, 384]
 
 
 def _experts(x_local, offs, W):
@@ -142,11 +145,15 @@ def _allreduce_worker(rank, world):
     ps = [torch.nn.Parameter(torch.zeros(n)) for n in (10, 1000, 7)]
     for i, p in enumerate(ps):
         p.grad = torch.full_like(p, float(rank + 1 + i))
-    ps.append(torch.nn.Parameter(torch.zeros(3)))  # no grad: skipped
-    n = D.allreduce_gradients(ps, bucket_bytes=4032)
-    assert n == 2  # 40 B | 4000 B + 28 B: the second tensor does not fit beside the first
+    ps.append(torch.nn.Parameter(torch.zeros(3)))             # a gradient on rank 1 only: zeros elsewhere
+    if rank == 1:
+        ps[3].grad = torch.full((3,), 4.0)
+    ps.append(torch.nn.Parameter(torch.zeros(2), requires_grad=False))   # frozen: not part of the plan
+    n = D.allreduce_gradients(ps, bucket_bytes=4032, max_in_flight=1)
+    assert n == 2  # 40 B | 4000 B + 28 B + 12 B: the same plan on both ranks whatever gradients exist
     for i, p in enumerate(ps[:3]):
         assert torch.allclose(p.grad, torch.full_like(p, (1 + i + 2 + i) / 2))
+    assert torch.allclose(ps[3].grad, torch.full((3,), 2.0)) and ps[4].grad is None
 
 
 def test_bucketed_gradient_allreduce_two_ranks():
