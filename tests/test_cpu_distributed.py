@@ -150,7 +150,7 @@ def _allreduce_worker(rank, world):
         ps[3].grad = torch.full((3,), 4.0)
     ps.append(torch.nn.Parameter(torch.zeros(2), requires_grad=False))   # frozen: not part of the plan
     n = D.allreduce_gradients(ps, bucket_bytes=4032, max_in_flight=1)
-    assert n == 2  # 40 B | 4000 B + 28 B + 12 B: the same plan on both ranks whatever gradients exist
+    assert n == 3  # 40 B | 4000 B + 28 B | 12 B: the same plan on both ranks whatever gradients exist
     for i, p in enumerate(ps[:3]):
         assert torch.allclose(p.grad, torch.full_like(p, (1 + i + 2 + i) / 2))
     assert torch.allclose(ps[3].grad, torch.full((3,), 2.0)) and ps[4].grad is None
