@@ -9,6 +9,8 @@ engine's device thread).
 from __future__ import annotations
 
 import ctypes as C
+import functools
+import os
 import threading
 from pathlib import Path
 from typing import Optional, Sequence
@@ -77,6 +79,32 @@ class QuantParams(C.Structure):
         ("rand_tile_rows", C.c_int64),
         ("rand_tile_pairs", C.c_int64),
     ]
+
+
+# ---------------------------------------------------------------------------------------
+# tracing: NVTX ranges around the boundary calls (off unless ALTO_B200_NVTX=1)
+# ---------------------------------------------------------------------------------------
+NVTX = os.environ.get("ALTO_B200_NVTX", "0") == "1"
+
+
+def traced(name: str):
+    """Decorator: the call runs inside an NVTX range ``alto_b200::<name>`` when tracing is switched on
+    (environment variable ALTO_B200_NVTX=1, read at import); otherwise the function is returned as it is,
+    so the default path pays nothing.  Ranges nest: a linear shows its quantizers and GEMMs below it in a
+    timeline."""
+    def wrap(fn):
+        if not NVTX:
+            return fn
+
+        @functools.wraps(fn)
+        def inner(*args, **kwargs):
+            torch.cuda.nvtx.range_push(f"alto_b200::{name}")
+            try:
+                return fn(*args, **kwargs)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        return inner
+    return wrap
 
 
 class MacroScaleDesc(C.Structure):

@@ -183,6 +183,7 @@ def _hadamard(use_hadamard: bool, use_2dblock_x: bool, device) -> Optional[Hadam
         return HadamardFactory.create_transform(device=device)
 
 
+@L.traced("mxfp4_grouped_mm")
 def _quantize_then_mxfp_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2dblock_w: bool, use_sr_grad: bool,
                                           use_dge: bool, use_hadamard: bool, clip_mode: str,
                                           use_macro_block_scaling: bool, use_uos: bool = False) -> torch.Tensor:
@@ -199,6 +200,7 @@ def _quantize_then_mxfp_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2
                                        bool(use_dge))
 
 
+@L.traced("nvfp4_grouped_mm")
 def _quantize_then_nvfp4_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_2dblock_w: bool, use_sr_grad: bool,
                                            use_outer_scale: bool = False, use_hadamard: bool = False,
                                            use_dge: bool = False, scale_format: str = "e4m3") -> torch.Tensor:
@@ -211,6 +213,7 @@ def _quantize_then_nvfp4_scaled_grouped_mm(A, B, offs, use_2dblock_x: bool, use_
 _FP8 = {"e4m3": L.FMT_MXFP8_E4M3, "e5m2": L.FMT_MXFP8_E5M2}
 
 
+@L.traced("mxfp8_grouped_mm")
 def _quantize_then_mxfp8_scaled_grouped_mm(A, B, offs, *, use_2dblock_x: bool = False, use_2dblock_w: bool = True,
                                            use_sr_grad: bool = False, fwd_format: str = "e4m3",
                                            bwd_grad_format: str = "e4m3") -> torch.Tensor:

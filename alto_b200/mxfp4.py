@@ -29,6 +29,7 @@ def _check_options(clip_mode: str, use_uos: bool, is_2d_block: bool = False) -> 
         raise NotImplementedError("clip_mode='dynamic' with 2-D blocks is not implemented on the B200 path")
 
 
+@L.traced("convert_to_mxfp4")
 def convert_to_mxfp4(
     data_hp: torch.Tensor,
     block_size: int = BLOCK_SIZE_DEFAULT,
@@ -159,6 +160,7 @@ class MXFP4LinearFunction(torch.autograd.Function):
         return gi, gw, None, None, None, None, None, None, None, None
 
 
+@L.traced("mxfp4_linear")
 def _to_mxfp4_then_scaled_mm(
     a: torch.Tensor,
     b: torch.Tensor,

@@ -25,6 +25,7 @@ _FMT = {"e4m3": L.FMT_MXFP8_E4M3, "e5m2": L.FMT_MXFP8_E5M2}
 _FMT_OF_DTYPE = {torch.float8_e4m3fn: L.FMT_MXFP8_E4M3, torch.float8_e5m2: L.FMT_MXFP8_E5M2}
 
 
+@L.traced("convert_to_mxfp8")
 def convert_to_mxfp8(
     data_hp: torch.Tensor,
     block_size: int = BLOCK_SIZE_DEFAULT,
@@ -142,6 +143,7 @@ class MXFP8LinearFunction(torch.autograd.Function):
         return gi, gw, None, None, None, None
 
 
+@L.traced("mxfp8_linear")
 def _to_mxfp8_then_scaled_mm(
     a: torch.Tensor,
     b: torch.Tensor,

@@ -71,6 +71,7 @@ def compute_dynamic_outer_scale(data_hp: torch.Tensor, scale_format: str = "e4m3
     return outer[:1]
 
 
+@L.traced("convert_to_nvfp4")
 def convert_to_nvfp4(
     data_hp: torch.Tensor,
     block_size: int = BLOCK_SIZE_DEFAULT,
@@ -205,6 +206,7 @@ class NVFP4LinearFunction(torch.autograd.Function):
         return grad_inputs, grad_weights, None, None, None, None, None, None, None
 
 
+@L.traced("nvfp4_linear")
 def _to_nvfp4_then_scaled_mm(
     a: torch.Tensor,
     b: torch.Tensor,

@@ -133,3 +133,26 @@ def test_boundary_signatures_match_the_reference():
         ref = entry["params"]
         assert mine[:len(ref)] == ref, (entry["function"], ref, mine)
         assert [m[0] for m in mine[len(ref):]] == allowed_extra.get(entry["function"], []), entry["function"]
+
+
+def test_nvtx_ranges_wrap_boundary_calls_only_when_asked(monkeypatch):
+    """Tracing: with ALTO_B200_NVTX=1 a boundary call runs inside a named NVTX range (pushed and popped
+    even when the call raises); without it the decorator returns the function untouched."""
+    from alto_b200 import _lib as L
+
+    def f(a, b=2):
+        if a < 0:
+            raise ValueError("neg")
+        return a + b
+
+    monkeypatch.setattr(L, "NVTX", False)
+    assert L.traced("plain")(f) is f
+    events = []
+    monkeypatch.setattr(L, "NVTX", True)
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: events.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: events.append(("pop",)))
+    g = L.traced("unit")(f)
+    assert g(1, b=3) == 4 and g.__name__ == "f"
+    with pytest.raises(ValueError):
+        g(-1)
+    assert events == [("push", "alto_b200::unit"), ("pop",), ("push", "alto_b200::unit"), ("pop",)]
