@@ -278,6 +278,7 @@ def run_ours(args):
     timer.wrap(L, "quantize_2d", "quantize_2d",
                lambda x, *a, **k: x.numel() * (2 + 2 * (0.5 + 1.0 / 16)))
     timer.wrap(L, "gemm_blockscaled", "gemm", lambda fa, fb, m, n, k, *a, **kw: 2.0 * m * n * k)
+    timer.wrap(L, "gemm_mxfp4_two_level", "gemm", lambda m, n, k, *a, **kw: 2.0 * m * n * k)
 
     g = torch.Generator(device=dev).manual_seed(rank)
     gw = torch.Generator(device=dev).manual_seed(12345)  # identical weights on every rank
@@ -288,7 +289,12 @@ def run_ours(args):
     def step():
         x.grad = None
         w.grad = None
-        y = NV._to_nvfp4_then_scaled_mm(x, w, False, True, True, use_outer_scale=True, use_hadamard=True)
+        if args.recipe == "nvfp4":
+            y = NV._to_nvfp4_then_scaled_mm(x, w, False, True, True, use_outer_scale=True, use_hadamard=True)
+        else:   # profiling captures of the other recipes on a small case; never the headline
+            from alto_b200 import mxfp4 as MXR
+            y = MXR._to_mxfp4_then_scaled_mm(x, w, False, True, True, False, "none", True,
+                                             args.recipe == "mxfp4_two_level")
         y.backward(dy)
         return y
 
@@ -643,6 +649,8 @@ def main():
     ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long sustained leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the MXFP4 recipes at the same shape")
     ap.add_argument("--no-sharded", action="store_true", help="N > 1: skip the expert-parallel and column-sharded runs")
+    ap.add_argument("--recipe", default="nvfp4", choices=["nvfp4", "mxfp4", "mxfp4_two_level"],
+                    help="nvfp4 is the headline; the others exist for profiling captures of their kernels")
     ap.add_argument("--shape", default=None, metavar="M,K,N",
                     help="run the same step at another shape (profiling captures on a small case); the "
                          "headline workload is the default")
@@ -653,6 +661,9 @@ def main():
         FLOPS_PER_STEP = 3 * 2 * M * N * K
         CONFIG["shape"] = {"M": M, "K": K, "N": N}
         CONFIG["workload"] = f"NOT the headline workload: same NVFP4 step at M={M} K={K} N={N}"
+    if args.recipe != "nvfp4":
+        CONFIG["workload"] = f"NOT the headline workload: {args.recipe} step at M={M} K={K} N={N}"
+        args.no_extra = True
     if args.impl == "reference":
         run_reference(args)
     else:
