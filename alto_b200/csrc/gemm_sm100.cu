@@ -825,13 +825,18 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, ui
   }
 }
 
-template <int KIND>
+// BN_ = 256: one accumulator stage (256 + scale columns fill the tensor memory).  BN_ = 192: two
+// accumulator stages, so that a tile's epilogue runs under the next tile's mainloop; a 192-column
+// tile starts either on a 128-row block of B scales or 64 rows into one, so its scale columns start
+// at word 0 or word 2 of the two blocks kept in tensor memory.
+template <int KIND, int BN_>
 struct CfgPair {
-  static constexpr int BN = 256;                             // columns of the pair's tile
+  static constexpr int BN = BN_;                             // columns of the pair's tile
+  static constexpr int ACC_STAGES = BN_ == 256 ? 1 : 2;
   static constexpr int SF_TILES = Kind<KIND>::SF_TILES;
-  static constexpr int NB = 2;                               // 128-row blocks of B scales (all 256 columns)
+  static constexpr int NB = 2;                               // 128-row blocks of B scales that a tile touches
   static constexpr int A_BYTES = BM * STAGE_K_BYTES;         // this CTA's 128 rows of A
-  static constexpr int B_BYTES = 128 * STAGE_K_BYTES;        // this CTA's half of the B tile
+  static constexpr int B_BYTES = (BN_ / 2) * STAGE_K_BYTES;  // this CTA's half of the B tile
   static constexpr int SFA_BYTES = SF_TILES * 512;
   static constexpr int SFB_BYTES = NB * SF_TILES * 512;
   static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + 1023) / 1024 * 1024;
@@ -842,21 +847,27 @@ struct CfgPair {
   static constexpr int EPI_BUFS = 2;                         // 4 KB staging buffers per epilogue warp
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * 4096;
   // registers per thread after the warpgroups have re-divided the file: 2 x 128 x 56 + 2 x 128 x 200 = 65536
-  static constexpr int REGS_SMALL = 56, REGS_EPI = 200;
-  static constexpr int TMEM_SF_BASE = BN;
-  static constexpr int TMEM_COLS_USED = TMEM_SF_BASE + STAGES * (SF_COLS_A + SF_COLS_B);
+  static constexpr int REGS_SMALL = BN_ == 256 ? 56 : 72, REGS_EPI = BN_ == 256 ? 200 : 184;
+  static constexpr int TMEM_SF_BASE = ACC_STAGES * BN;
+  static constexpr int SF_COLS = SF_COLS_A + SF_COLS_B;
+  // scale slots in tensor memory: one per operand stage if they fit, else as many as do (a slot is
+  // then reused as soon as the MMAs of the stage that read it have completed)
+  static constexpr int SF_SLOTS = (512 - TMEM_SF_BASE) / SF_COLS < STAGES ? (512 - TMEM_SF_BASE) / SF_COLS : STAGES;
+  static_assert(SF_SLOTS >= 2, "tensor memory budget");
+  static constexpr int TMEM_COLS_USED = TMEM_SF_BASE + SF_SLOTS * SF_COLS;
   static_assert(TMEM_COLS_USED <= 512, "tensor memory budget");
-  static constexpr int NUM_BARS = 5 * STAGES + 2;
+  static constexpr int HALF_COLS = BN / 2;                    // columns drained by one epilogue warp
+  static constexpr int NUM_BARS = 4 * STAGES + 2 * ACC_STAGES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 512 /*barriers*/;
   static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
-template <int KIND, bool OUT_BF16>
+template <int KIND, bool OUT_BF16, int BN_>
 __global__ void __launch_bounds__(NUM_THREADS_PAIR, 1)
 gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                              const __grid_constant__ CUtensorMap tmap_d, const GemmArgs args) {
-  using C = CfgPair<KIND>;
+  using C = CfgPair<KIND, BN_>;
   constexpr int BN = C::BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -867,8 +878,8 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
   uint64_t* sfs_full = bars + 2 * C::STAGES;
   uint64_t* sf_full = bars + 3 * C::STAGES;
   uint64_t* acc_full = bars + 4 * C::STAGES;
-  uint64_t* acc_empty = acc_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  uint64_t* acc_empty = acc_full + C::ACC_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::ACC_STAGES);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -888,8 +899,10 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
       mbar_init(&sfs_full[s], 1);
       mbar_init(&sf_full[s], 8);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 2 * C::EPI_WARPS);
+    for (int a = 0; a < C::ACC_STAGES; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 2 * C::EPI_WARPS);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -924,8 +937,8 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
         const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
         if (ti.skip) continue;
         const int64_t mb = ti.mb * 2 + rank;          // this CTA's 128-row block of A
-        const int64_t nb = ti.nb;
-        int nb_valid = (int)(n_row_blocks - nb * C::NB);
+        const int64_t sfb_blk0 = (ti.nb * BN) >> 7;   // first 128-row block of B scales under this tile
+        int nb_valid = (int)(n_row_blocks - sfb_blk0);
         if (nb_valid > C::NB) nb_valid = C::NB;
         // a CTA whose rows of A lie past M has no scale row block to load; its rows are never stored
         const bool sfa_exists = mb * BM < args.M;
@@ -954,13 +967,13 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
             mbar_expect_tx(&sfs_full[s], sf_bytes * ((sfa_exists ? 1 : 0) + nb_valid));
             const uint32_t full_leader = mapa_u32(smem_u32(&full_bar[s]), 0);
             tma_load_2d_pair(st, &tmap_a, kx, (int32_t)(mb * BM), full_leader);
-            tma_load_2d_pair(st + C::A_BYTES, &tmap_b, kx, (int32_t)(ti.b_row0 + rank * 128), full_leader);
+            tma_load_2d_pair(st + C::A_BYTES, &tmap_b, kx, (int32_t)(ti.b_row0 + rank * (BN / 2)), full_leader);
             if (sfa_exists) bulk_load(st + C::A_BYTES + C::B_BYTES, sfa_row + cb0 * 512, sf_bytes, &sfs_full[s]);
 #pragma unroll
             for (int j = 0; j < C::NB; ++j)
               if (j < nb_valid)
                 bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + j * C::SFA_BYTES,
-                          ti.sfb + ((nb * C::NB + j) * args.nct + cb0) * 512, sf_bytes, &sfs_full[s]);
+                          ti.sfb + ((sfb_blk0 + j) * args.nct + cb0) * 512, sf_bytes, &sfs_full[s]);
           }
           __syncwarp();
         }
@@ -973,7 +986,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
     // at named barrier 1 + stage.  Between two tcgen05.mma nothing but their operand arithmetic runs.
     if (leader) {
       const bool elected = elect_one();
-      uint32_t it = 0;
+      uint32_t it = 0, tile_it = 0;
       bool alive = true;
       const uint32_t smem_base = smem_u32(smem);
 #ifdef ALTOB200_GEMM_PROFILE
@@ -983,6 +996,10 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
       for (int64_t tile = pair; tile < n_tiles && alive; tile += n_pairs) {
         const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
         if (ti.skip) continue;
+        const uint32_t acc = tile_it % C::ACC_STAGES;
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        // scale columns of B start at word 0 of the first block, or 64 rows (2 words) into it
+        const uint32_t sfb_off = (uint32_t)((ti.nb * BN) & 127) >> 5;
         for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
           const int s = it % C::STAGES;
@@ -993,8 +1010,8 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
           if (named_barrier_or(1 + s, 64, false)) { alive = false; break; }
           if (!ALTOB200_DBG(args, 2048)) tc_fence_after();
           const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;
-          const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
-          const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
+          const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + (it % C::SF_SLOTS) * C::SF_COLS;
+          const uint32_t sfb_t = sfa_t + C::SF_COLS_A + sfb_off;
           const uint32_t a_lo = st4 | 0x10000u;
           const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
 #ifdef ALTOB200_GEMM_PROFILE
@@ -1006,7 +1023,7 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
             for (int j = 0; j < 4; ++j) {
               const int t = (KIND == KIND_NVF4) ? j : (KIND == KIND_MXF4 ? (j >> 1) : 0);
               if (j < n_mma)
-                tc_mma_pair<KIND>(tmem_base, desc_of(DESC_SW128_HI, a_lo + 2 * j), desc_of(DESC_SW128_HI, b_lo + 2 * j),
+                tc_mma_pair<KIND>(d_tmem, desc_of(DESC_SW128_HI, a_lo + 2 * j), desc_of(DESC_SW128_HI, b_lo + 2 * j),
                                   args.idesc[j], (ks | j) != 0 ? 1u : 0u, sfa_t + t * 4, sfb_t + t * 4 * C::NB);
             }
             tc_commit_pair(&empty_bar[s]);
@@ -1017,8 +1034,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
           pk_n += 1;
 #endif
         }
-        if (alive && elected) tc_commit_pair(acc_full);
+        if (alive && elected) tc_commit_pair(&acc_full[acc]);
         __syncwarp();
+        ++tile_it;
       }
 #ifdef ALTOB200_GEMM_PROFILE
       if (blockIdx.x == 0 && lane == 0 && (args.debug & 16384))
@@ -1035,7 +1053,8 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
       for (int64_t tile = pair; tile < n_tiles && alive; tile += n_pairs) {
         const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
         if (ti.skip) continue;
-        bool ok = mbar_wait(acc_empty, (tile_it & 1) ^ 1, abort_flag, 12, args.wait_ns);
+        bool ok = mbar_wait(&acc_empty[tile_it % C::ACC_STAGES], ((tile_it / C::ACC_STAGES) & 1) ^ 1, abort_flag, 12,
+                            args.wait_ns);
         for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int s = it % C::STAGES;
           ok = ok && mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 13, args.wait_ns);
@@ -1059,8 +1078,18 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
       for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
         const int s = it % C::STAGES;
         if (!mbar_wait(&sfs_full[s], (it / C::STAGES) & 1, abort_flag, 16, args.wait_ns)) { alive = false; break; }
+        if (C::SF_SLOTS < C::STAGES && it >= (uint32_t)C::SF_SLOTS) {
+          // fewer scale slots than operand stages: the slot is free once the MMAs that read it have
+          // completed, which is what frees the operand stage of that earlier step as well
+          const uint32_t prev = it - C::SF_SLOTS;
+          if (!mbar_wait(&empty_bar[prev % C::STAGES], (prev / C::STAGES) & 1, abort_flag, 17, args.wait_ns)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+        }
         const uint8_t* sf = smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
-        const uint32_t sfa_t = tmem_base + lane_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
+        const uint32_t sfa_t = tmem_base + lane_base + C::TMEM_SF_BASE + (it % C::SF_SLOTS) * C::SF_COLS;
         const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
 #pragma unroll
         for (int t = 0; t < C::SF_TILES; ++t) {
@@ -1083,12 +1112,21 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
     }
   } else {
     // ------------------------------ epilogue (each CTA stores its own 128 rows) ------------------------------
-    // Warps 8-11 drain columns [0, 128) of the accumulator, warps 12-15 columns [128, 256); a warp may
-    // read the tensor-memory lane quarter (warp index mod 4).  A warp first pulls its 32 rows x 128
-    // columns into registers (four loads in flight, one wait) and hands the accumulator back, so the
-    // next tile's MMAs start after one tensor-memory read; scaling, conversion, staging and the TMA
-    // stores then run under that tile's mainloop.
+    // Warps 8-11 drain the first half of the accumulator's columns, warps 12-15 the second half; a
+    // warp may read the tensor-memory lane quarter (warp index mod 4).  A warp first pulls its 32 rows
+    // x BN/2 columns into registers (all loads in flight, one wait) and hands the accumulator back;
+    // scaling, conversion, staging and the TMA stores then run under the next mainloop (with two
+    // accumulator stages the tensor-memory read itself is under the next tile's mainloop as well).
     setmaxnreg_inc<C::REGS_EPI>();
+    constexpr int HC = C::HALF_COLS;
+    // one staged unit = 32 rows x UNIT_BYTES: 128-byte rows (128-byte swizzle) when they divide the
+    // half tile, else 64-byte rows (64-byte swizzle; the output tensor map is built to match)
+    constexpr int ESZ = OUT_BF16 ? 2 : 4;
+    constexpr int UNIT_BYTES = (HC * ESZ) % 128 == 0 ? 128 : 64;
+    constexpr int UNIT_COLS = UNIT_BYTES / ESZ;
+    constexpr int N_UNITS = HC / UNIT_COLS;
+    constexpr int CHUNKS = UNIT_BYTES / 16;       // 16-byte chunks per staged row
+    constexpr int CHUNK_COLS = 16 / ESZ;
     const int quad = warp & 3;
     const int half = warp >= 12 ? 1 : 0;
     const int epi_idx = warp - 8;
@@ -1096,57 +1134,55 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
     float alpha = 1.0f;
     if (args.alpha_a != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_a));
     if (args.alpha_b != nullptr) alpha = __fmul_rn(alpha, __ldg(args.alpha_b));
-    const uint32_t acc_empty_leader = mapa_u32(smem_u32(acc_empty), 0);
-    const uint32_t my_row = smem_u32(epi_warp) + (uint32_t)lane * 128u;
-    const uint32_t sw = (uint32_t)(lane & 7);
-    const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 128;
+    const uint32_t my_row = smem_u32(epi_warp) + (uint32_t)lane * (uint32_t)UNIT_BYTES;
+    const uint32_t sw = UNIT_BYTES == 128 ? (uint32_t)(lane & 7) : (uint32_t)((lane >> 1) & 3);
     uint32_t tile_it = 0, store_it = 0;
     for (int64_t tile = pair; tile < n_tiles; tile += n_pairs) {
       const TileInfo ti = decode_tile<KIND, BN>(args, tile, tiles_m, tiles_n, k_stages);
       const int64_t row0 = (ti.mb * 2 + rank) * BM + quad * 32;
-      const int64_t col_base = ti.nb * BN + half * 128;
-      uint32_t r[128];
+      const int64_t col_base = ti.nb * BN + half * HC;
+      uint32_t r[HC];
       if (!ti.skip) {
-        if (!mbar_wait(acc_full, tile_it & 1, abort_flag, 14, args.wait_ns)) break;
+        const uint32_t acc = tile_it % C::ACC_STAGES;
+        if (!mbar_wait(&acc_full[acc], (tile_it / C::ACC_STAGES) & 1, abort_flag, 14, args.wait_ns)) break;
         tc_fence_after();
         if (!ALTOB200_DBG(args, 8)) {
-          tc_ld32(t_acc, r);
-          tc_ld32(t_acc + 32, r + 32);
-          tc_ld32(t_acc + 64, r + 64);
-          tc_ld32(t_acc + 96, r + 96);
+          const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + half * HC;
+#pragma unroll
+          for (int c = 0; c < HC / 32; ++c) tc_ld32(t_acc + c * 32, r + c * 32);
           tc_wait_ld();
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          if (leader) mbar_arrive(acc_empty);
-          else mbar_arrive_cluster_relaxed(acc_empty_leader);
+          if (leader) mbar_arrive(&acc_empty[acc]);
+          else mbar_arrive_cluster_relaxed(mapa_u32(smem_u32(&acc_empty[acc]), 0));
         }
         ++tile_it;
         if (ALTOB200_DBG(args, 8)) continue;
       } else {
 #pragma unroll
-        for (int q = 0; q < 128; ++q) r[q] = 0u;
+        for (int q = 0; q < HC; ++q) r[q] = 0u;
       }
-      constexpr int UNIT_COLS = OUT_BF16 ? 64 : 32;   // one 128-byte output row chunk
 #pragma unroll
-      for (int u = 0; u < 128 / UNIT_COLS; ++u) {
+      for (int u = 0; u < N_UNITS; ++u) {
         if (lane == 0) bulk_wait_read<C::EPI_BUFS - 1>();  // the store that last used this buffer has read it
         __syncwarp();
         const uint32_t buf = my_row + (store_it % C::EPI_BUFS) * 4096u;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < CHUNKS; ++q) {
           uint32_t o[4];
           if (OUT_BF16) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const __nv_bfloat162 p2 = __floats2bfloat162_rn(__fmul_rn(u2f(r[u * 64 + q * 8 + 2 * e]), alpha),
-                                                              __fmul_rn(u2f(r[u * 64 + q * 8 + 2 * e + 1]), alpha));
+              const __nv_bfloat162 p2 =
+                  __floats2bfloat162_rn(__fmul_rn(u2f(r[u * UNIT_COLS + q * CHUNK_COLS + 2 * e]), alpha),
+                                        __fmul_rn(u2f(r[u * UNIT_COLS + q * CHUNK_COLS + 2 * e + 1]), alpha));
               o[e] = *reinterpret_cast<const uint32_t*>(&p2);
             }
           } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) o[e] = f2u(__fmul_rn(u2f(r[u * 32 + q * 4 + e]), alpha));
+            for (int e = 0; e < 4; ++e) o[e] = f2u(__fmul_rn(u2f(r[u * UNIT_COLS + q * CHUNK_COLS + e]), alpha));
           }
           st_shared_v4(buf + ((((uint32_t)q) ^ sw) << 4), o[0], o[1], o[2], o[3]);
         }
@@ -1217,18 +1253,21 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 3D tensor map of the output [batches, M, N] (bf16 or fp32): box of 1 x 32 rows x 128 bytes,
-// 128-byte swizzle.  The batch coordinate keeps a ragged tile of one batch entry out of the next.
-static int make_tmap_out(CUtensorMap* m, void* base, int64_t batches, int64_t M, int64_t N, int64_t ldd, bool bf16) {
+// 3D tensor map of the output [batches, M, N] (bf16 or fp32): box of 1 x 32 rows x 128 bytes with
+// the 128-byte swizzle, or x 64 bytes with the 64-byte swizzle (epilogues whose column share is not
+// a multiple of 128 bytes).  The batch coordinate keeps a ragged tile of one batch entry out of the next.
+static int make_tmap_out(CUtensorMap* m, void* base, int64_t batches, int64_t M, int64_t N, int64_t ldd, bool bf16,
+                         int row_bytes = 128) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return ALTOB200_ECUDA;
   const int esz = bf16 ? 2 : 4;
   cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)batches};
   cuuint64_t strides[2] = {(cuuint64_t)(ldd * esz), (cuuint64_t)(M * ldd * esz)};
-  cuuint32_t box[3] = {(cuuint32_t)(128 / esz), 32u, 1u};
+  cuuint32_t box[3] = {(cuuint32_t)(row_bytes / esz), 32u, 1u};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? ALTOB200_OK : ALTOB200_ECUDA;
 }
@@ -1316,10 +1355,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
 }
 
 // CTA-pair kernel: clusters of two CTAs, as many clusters as the device can hold at once.
-template <int KIND, bool OUT_BF16>
+template <int KIND, bool OUT_BF16, int BN_>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmArgs& args,
                             cudaStream_t st) {
-  using C = CfgPair<KIND>;
+  using C = CfgPair<KIND, BN_>;
   static std::atomic<int> clusters_of[MAX_DEVICES];  // 0 = not asked yet, < 0 = the device cannot run the pair kernel
   const int dev = current_device();
   int max_clusters = dev >= 0 ? clusters_of[dev].load(std::memory_order_relaxed) : 0;
@@ -1335,11 +1374,11 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (max_clusters == 0) {
-    ALTOB200_CUDA_CHECK(cudaFuncSetAttribute(gemm_blockscaled_pair_kernel<KIND, OUT_BF16>,
+    ALTOB200_CUDA_CHECK(cudaFuncSetAttribute(gemm_blockscaled_pair_kernel<KIND, OUT_BF16, BN_>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     cfg.gridDim = dim3(2 * (unsigned)sm_count_gemm(), 1, 1);
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_blockscaled_pair_kernel<KIND, OUT_BF16>, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_blockscaled_pair_kernel<KIND, OUT_BF16, BN_>, &cfg) != cudaSuccess || n <= 0) {
       (void)cudaGetLastError();
       max_clusters = -1;
     } else {
@@ -1353,8 +1392,19 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
   int64_t clusters = max_clusters;
   if (clusters > tiles) clusters = tiles;
   cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, OUT_BF16>, ta, tb, td, args);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_blockscaled_pair_kernel<KIND, OUT_BF16, BN_>, ta, tb, td, args);
   return e == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+}
+
+// Columns of the CTA-pair tile: 192 (two accumulator stages) or 256 (one); ALTOB200_PAIR_BN overrides.
+static int pair_tile_n() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ALTOB200_PAIR_BN");
+    const int n = e ? atoi(e) : 0;
+    v = (n == 192 || n == 256) ? n : 256;
+  }
+  return v;
 }
 
 static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N, int64_t K, int32_t num_experts,
@@ -1384,7 +1434,7 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
   if (M >= (1ll << 31) || N * (num_experts > 0 ? num_experts : 1) >= (1ll << 31) || k_bytes >= (1ll << 31))
     return ALTOB200_ELIMIT;
 
-  const int BN = N <= 128 ? 128 : 256;
+  int BN = N <= 128 ? 128 : 256;
   // The CTA-pair kernel serves dense and K-range problems; rows grouped by expert in runs of 128
   // could put two experts' rows into one 256-row pair tile, so that mode stays on the single-CTA
   // kernel.  ALTOB200_GEMM_PAIR=0 forces the single-CTA kernel everywhere.
@@ -1394,14 +1444,16 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
     pair_env = e ? atoi(e) : 1;
   }
   const bool use_pair = pair_env != 0 && num_experts == 0 && N > 128 && M > 128;
+  if (use_pair && pair_tile_n() == 192) BN = 192;
   const int64_t b_rows = N * (num_experts > 0 ? num_experts : 1);
   CUtensorMap ta, tb;
   int rc = make_tmap(&ta, a_codes, M, k_bytes, BM);
   if (rc != ALTOB200_OK) return rc;
-  rc = make_tmap(&tb, b_codes, b_rows, k_bytes, use_pair ? 128 : BN);
+  rc = make_tmap(&tb, b_codes, b_rows, k_bytes, use_pair ? BN / 2 : BN);
   if (rc != ALTOB200_OK) return rc;
   CUtensorMap td;
-  rc = make_tmap_out(&td, d, k_offs != nullptr ? num_batches : 1, M, N, ldd, out_dtype == ALTOB200_DT_BF16);
+  rc = make_tmap_out(&td, d, k_offs != nullptr ? num_batches : 1, M, N, ldd, out_dtype == ALTOB200_DT_BF16,
+                     (use_pair && BN == 192 && out_dtype == ALTOB200_DT_BF16) ? 64 : 128);
   if (rc != ALTOB200_OK) return rc;
 
   GemmArgs g;
@@ -1446,14 +1498,17 @@ static int gemm_common(int32_t format_a, int32_t format_b, int64_t M, int64_t N,
   cudaStream_t st = (cudaStream_t)stream;
   if (use_pair) {
     const bool obf = g.out_bf16 != 0;
+#define LAUNCH_PAIR(KD)                                                                                        \
+  return BN == 192 ? (obf ? launch_gemm_pair<KD, true, 192>(ta, tb, td, g, st)                                \
+                          : launch_gemm_pair<KD, false, 192>(ta, tb, td, g, st))                              \
+                   : (obf ? launch_gemm_pair<KD, true, 256>(ta, tb, td, g, st)                                \
+                          : launch_gemm_pair<KD, false, 256>(ta, tb, td, g, st))
     switch (kind) {
-      case KIND_NVF4: return obf ? launch_gemm_pair<KIND_NVF4, true>(ta, tb, td, g, st)
-                                 : launch_gemm_pair<KIND_NVF4, false>(ta, tb, td, g, st);
-      case KIND_MXF4: return obf ? launch_gemm_pair<KIND_MXF4, true>(ta, tb, td, g, st)
-                                 : launch_gemm_pair<KIND_MXF4, false>(ta, tb, td, g, st);
-      default: return obf ? launch_gemm_pair<KIND_MXF8, true>(ta, tb, td, g, st)
-                          : launch_gemm_pair<KIND_MXF8, false>(ta, tb, td, g, st);
+      case KIND_NVF4: LAUNCH_PAIR(KIND_NVF4);
+      case KIND_MXF4: LAUNCH_PAIR(KIND_MXF4);
+      default: LAUNCH_PAIR(KIND_MXF8);
     }
+#undef LAUNCH_PAIR
   }
 #define LAUNCH(KD)                                                    \
   return BN == 128 ? launch_gemm<KD, 128>(ta, tb, td, g, st) : launch_gemm<KD, 256>(ta, tb, td, g, st)

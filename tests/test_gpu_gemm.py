@@ -364,3 +364,20 @@ def test_bounded_device_wait_times_out_and_is_reported():
     assert L.status_read()[0] == 0
     with pytest.raises(L.Altob200Error):
         L.selftest_wait_timeout(5_000_000_000)  # limits above one second are refused
+
+
+def test_pair_tile_of_192_columns_with_two_accumulator_stages():
+    """The CTA-pair kernel also exists with a 256 x 192 tile and two accumulator stages (scale columns of
+    B then start at word 0 or word 2 of a 128-row block, 64-byte store rows for bf16).  It is slower
+    than the 256 x 256 tile on every measured shape and is not the default; ALTOB200_PAIR_BN=192 selects
+    it when the library is loaded, so the raw-GEMM and ragged-tile cases are re-run in a child process."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, ALTOB200_PAIR_BN="192")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_gpu_gemm.py", "-q", "-x", "-m", "gpu", "-k",
+                        "matches_dequantised_fp32_matmul or ragged_tiles or mixed_fp8"],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
