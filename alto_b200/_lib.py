@@ -48,6 +48,8 @@ EXPORTED_SYMBOLS = (
     "altob200_macro_block_scaling",
     "altob200_macro_block_descaling",
     "altob200_gather_rows",
+    "altob200_swiglu_forward",
+    "altob200_swiglu_backward",
     "altob200_dge_scale",
     "altob200_deosc_accumulate",
     "altob200_gemm_blockscaled",
@@ -174,6 +176,10 @@ def _declare_more(lib):
     lib.altob200_rht_dense.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i64, vp]
     lib.altob200_gather_rows.restype = C.c_int
     lib.altob200_gather_rows.argtypes = [vp, i64, i64, vp, i64, vp, vp]
+    lib.altob200_swiglu_forward.restype = C.c_int
+    lib.altob200_swiglu_forward.argtypes = [vp, i64, i64, i64, vp, vp]
+    lib.altob200_swiglu_backward.restype = C.c_int
+    lib.altob200_swiglu_backward.argtypes = [vp, vp, i64, i64, i64, vp, vp]
     lib.altob200_philox_tile.restype = C.c_int
     lib.altob200_philox_tile.argtypes = [C.c_uint64, C.c_uint64, i64, i64, vp, vp]
     lib.altob200_deosc_accumulate.restype = C.c_int
@@ -475,6 +481,29 @@ def gather_rows(src: torch.Tensor, index: torch.Tensor, out_rows: Optional[int] 
     _check(lib().altob200_gather_rows(src.data_ptr(), src.shape[0], src.shape[1] * src.element_size(),
                                       index.data_ptr(), n, out.data_ptr(), _stream()), "altob200_gather_rows")
     return out
+
+
+def swiglu_forward(h: torch.Tensor) -> torch.Tensor:
+    """h: [rows, 2H] bf16 contiguous (gate | up) -> bf16(bf16(silu(gate)) * up), [rows, H]."""
+    _require_cuda(h)
+    assert h.dim() == 2 and h.is_contiguous() and h.dtype == torch.bfloat16 and h.shape[1] % 2 == 0
+    rows, H = h.shape[0], h.shape[1] // 2
+    out = torch.empty(rows, H, dtype=h.dtype, device=h.device)
+    _check(lib().altob200_swiglu_forward(h.data_ptr(), rows, H, 2 * H, out.data_ptr(), _stream()),
+           "altob200_swiglu_forward")
+    return out
+
+
+def swiglu_backward(h: torch.Tensor, grad_out: torch.Tensor) -> torch.Tensor:
+    """Gradient of swiglu_forward with respect to h, [rows, 2H] bf16."""
+    _require_cuda(h, grad_out)
+    assert h.dim() == 2 and h.is_contiguous() and h.dtype == torch.bfloat16
+    rows, H = h.shape[0], h.shape[1] // 2
+    assert grad_out.shape == (rows, H) and grad_out.is_contiguous() and grad_out.dtype == torch.bfloat16
+    grad_h = torch.empty_like(h)
+    _check(lib().altob200_swiglu_backward(h.data_ptr(), grad_out.data_ptr(), rows, H, 2 * H, grad_h.data_ptr(),
+                                          _stream()), "altob200_swiglu_backward")
+    return grad_h
 
 
 def gemm_blockscaled(fmt_a, fmt_b, M, N, K, a_codes, a_scales, b_codes, b_scales, out, alpha_a=None,

@@ -14,7 +14,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libaltob200.so"
-SOURCES = ["quant.cu", "macro_scale.cu", "rht_dense.cu", "rows.cu", "dge.cu", "deosc.cu", "gemm_sm100.cu"]
+SOURCES = ["quant.cu", "macro_scale.cu", "rht_dense.cu", "rows.cu", "swiglu.cu", "dge.cu", "deosc.cu", "gemm_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -10,9 +10,11 @@
 //   alto/kernels/fp4/mxfp4/macro_block_scaling.py:35-96 and :100-146.
 // Elements past the end of a ragged last block do not take part in the amax.
 //
-// Work layout: 1D - a warp owns one (row, block) task, a lane 4 contiguous elements; the block
-// maximum is a warp shuffle reduction.  2D - a CTA of 256 threads owns one tile, a warp 16 rows;
-// the tile maximum goes through shared memory.  Both are one read and one write per element.
+// Work layout: 1D - a warp task is 4 rows x 256 columns: a lane holds 8 contiguous elements of
+// each row (all loads issued before the first is used), a block is 16 lanes wide and its maximum
+// a half-warp shuffle reduction (rows that do not allow 8-wide accesses take a one-block-per-warp
+// variant with 4 elements per lane).  2D - a CTA of 256 threads owns one tile, a warp 16 rows; the
+// tile maximum goes through shared memory.  Both are one read and one write per element.
 #include "common.cuh"
 
 namespace altob200 {
@@ -23,6 +25,7 @@ struct MacroArgs {
   uint8_t* scale;      // 1D: [batch, rows, nblk]   2D: [batch, ceil(rows/128), nblk]
   int64_t batch, rows, cols, nblk;
   int vec;             // rows start on a 4-element boundary: 4-wide loads and stores are legal
+  int wide;            // rows are a multiple of 8 elements and 32-byte (fp32) / 16-byte (bf16) aligned
 };
 
 __device__ __forceinline__ float macro_factor_from_amax(float amax, uint32_t* code) {
@@ -111,6 +114,79 @@ __global__ void __launch_bounds__(256) macro_scale_1d_kernel(MacroArgs a) {
   }
 }
 
+// ---- 1D, rows of a multiple of 8 elements: a warp task is 4 rows x 256 columns ----
+template <bool IN_BF16, bool DESCALE>
+__global__ void __launch_bounds__(256) macro_scale_1d_wide_kernel(MacroArgs a) {
+  constexpr int R = 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t n_rows = a.batch * a.rows;
+  const int64_t chunks = (a.cols + 255) >> 8;
+  const int64_t n_tasks = ((n_rows + R - 1) / R) * chunks;
+  const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = (int64_t)gridDim.x * 8;
+  for (int64_t task = warp0; task < n_tasks; task += n_warps) {
+    const int64_t rg = task / chunks, chunk = task - rg * chunks;
+    const int64_t row0 = rg * R;
+    const int64_t col = (chunk << 8) + lane * 8;
+    const int64_t blk = (chunk << 1) + (lane >> 4);
+    const bool col_ok = col < a.cols;   // cols is a multiple of 8: a lane's 8 elements exist together
+    float v[R][8];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const bool ok = col_ok && row0 + i < n_rows;
+      const int64_t off = (row0 + i) * a.cols + col;
+      if (IN_BF16) {
+        const uint4 w = ok ? __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.x) + off))
+                           : make_uint4(0u, 0u, 0u, 0u);
+        v[i][0] = bf16lo_to_f32(w.x); v[i][1] = bf16hi_to_f32(w.x); v[i][2] = bf16lo_to_f32(w.y); v[i][3] = bf16hi_to_f32(w.y);
+        v[i][4] = bf16lo_to_f32(w.z); v[i][5] = bf16hi_to_f32(w.z); v[i][6] = bf16lo_to_f32(w.w); v[i][7] = bf16hi_to_f32(w.w);
+      } else {
+        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) + off);
+        const float4 f0 = ok ? __ldg(p) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 f1 = ok ? __ldg(p + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[i][0] = f0.x; v[i][1] = f0.y; v[i][2] = f0.z; v[i][3] = f0.w;
+        v[i][4] = f1.x; v[i][5] = f1.y; v[i][6] = f1.z; v[i][7] = f1.w;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int64_t row = row0 + i;
+      const bool ok = col_ok && row < n_rows;
+      float f;
+      if (DESCALE) {
+        f = macro_factor_from_code(ok ? a.scale[row * a.nblk + blk] : 0u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = __fdiv_rn(v[i][j], f);
+      } else {
+        float m = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[i][j]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        uint32_t code;
+        f = macro_factor_from_amax(m, &code);
+        if (ok && (lane & 15) == 0) a.scale[row * a.nblk + blk] = (uint8_t)code;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = __fmul_rn(v[i][j], f);
+      }
+      if (ok) {
+        const int64_t off = row * a.cols + col;
+        if (IN_BF16) {
+          uint4 o;
+          o.x = f32_to_bf16_bits(v[i][0]) | (f32_to_bf16_bits(v[i][1]) << 16);
+          o.y = f32_to_bf16_bits(v[i][2]) | (f32_to_bf16_bits(v[i][3]) << 16);
+          o.z = f32_to_bf16_bits(v[i][4]) | (f32_to_bf16_bits(v[i][5]) << 16);
+          o.w = f32_to_bf16_bits(v[i][6]) | (f32_to_bf16_bits(v[i][7]) << 16);
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.y) + off) = o;
+        } else {
+          float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + off);
+          p[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          p[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        }
+      }
+    }
+  }
+}
+
 // ---- 2D and column blocks: one CTA per 128 x 128 tile ----
 // COLS = false: one factor per tile.  COLS = true: one factor per column of the tile (blocks of
 // 128 run down the rows, the reference's axis=0 on a matrix); scale is [batch, cols, ceil(rows/128)].
@@ -185,6 +261,12 @@ __global__ void __launch_bounds__(256) macro_scale_tile_kernel(MacroArgs a) {
 template <bool BF, bool DESCALE>
 static void launch_mode(const MacroArgs& a, int32_t mode, cudaStream_t st) {
   if (mode == 0) {
+    if (a.wide) {
+      int64_t blocks = ceil_div(ceil_div(a.batch * a.rows, 4) * ceil_div(a.cols, 256), 8);
+      if (blocks > 148 * 8) blocks = 148 * 8;
+      macro_scale_1d_wide_kernel<BF, DESCALE><<<(unsigned)blocks, 256, 0, st>>>(a);
+      return;
+    }
     int64_t blocks = ceil_div(a.batch * a.rows * a.nblk, 8);
     if (blocks > 148 * 16) blocks = 148 * 16;
     macro_scale_1d_kernel<BF, DESCALE><<<(unsigned)blocks, 256, 0, st>>>(a);
@@ -203,6 +285,7 @@ static int macro_launch(const void* x, int32_t dtype, int64_t batch, int64_t row
   MacroArgs a;
   // 4-wide accesses need every row to start on a 4-element boundary; otherwise element accesses
   a.vec = (cols % 4 == 0) && !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15);
+  a.wide = (cols % 8 == 0) && !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15);
   a.x = x; a.y = y; a.scale = scale; a.batch = batch; a.rows = rows; a.cols = cols; a.nblk = ceil_div(cols, 128);
   if (mode < 0 || mode > 2) return ALTOB200_EUNSUPPORTED;
   if (mode != 0 && (ceil_div(rows, 128) > 65535 || batch > 65535)) return ALTOB200_ELIMIT;

@@ -564,6 +564,7 @@ def run_sharded(dist, dev, rank, world):
     from alto_b200 import mxfp8 as M8
     from alto_b200.grouped import _quantize_then_mxfp_scaled_grouped_mm as mx4
     from alto_b200.hadamard import HadamardFactory
+    from alto_b200.swiglu import swiglu
 
     def gmm(A, B, offs):
         HadamardFactory.configure(block_size=32, randomized=True, dtype=torch.float32, seed=0)
@@ -572,8 +573,7 @@ def run_sharded(dist, dev, rank, world):
     def moe(x, ids, scores, W13, W2, dispatcher):
         xl, offs, st = dispatcher.dispatch(x, ids)
         h = gmm(xl, W13.transpose(-2, -1), offs)
-        H = h.shape[-1] // 2
-        y = gmm(torch.nn.functional.silu(h[:, :H]) * h[:, H:], W2.transpose(-2, -1), offs)
+        y = gmm(swiglu(h), W2.transpose(-2, -1), offs)
         return dispatcher.combine(y, st, scores)
 
     def step_time(fn, reps=5):

@@ -341,6 +341,19 @@ int altob200_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes, c
                          int64_t out_rows, void* dst, void* stream);
 
 /*
+ * SwiGLU between the two grouped GEMMs of an expert MLP, bf16.  h is [rows, 2H] with row stride
+ * ld_h elements (gate in columns [0, H), up in [H, 2H)); forward writes out [rows, H] =
+ * bf16(bf16(silu(gate)) * up); backward takes grad_out [rows, H] and writes grad_h [rows, 2H]
+ * (same row stride) with the roundings of the tensor-op form silu(h[:, :H]) * h[:, H:] and its
+ * autograd.  The module that holds this activation in the reference's setting is the
+ * GroupedExperts of its TorchTitan fork (converted at alto/modifiers/lpt/base.py:186-187).
+ * H and ld_h multiples of 8, pointers 16-byte aligned.
+ */
+int altob200_swiglu_forward(const void* h, int64_t rows, int64_t H, int64_t ld_h, void* out, void* stream);
+int altob200_swiglu_backward(const void* h, const void* grad_out, int64_t rows, int64_t H, int64_t ld_h,
+                             void* grad_h, void* stream);
+
+/*
  * Block-scaled GEMM on tcgen05:  D[m, n] = alpha * sum_k A[m, k] * B[n, k]
  * with A and B both stored reduction-axis-contiguous ("NT"), packed scales, fp32
  * accumulation in tensor memory.  Replaces blockwise_mxfp4_gemm

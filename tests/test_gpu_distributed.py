@@ -223,9 +223,9 @@ def test_gathered_weight_linear_single_rank_equals_the_plain_linear(precision, k
 def _swiglu_moe(x, ids, scores, W13, W2, dispatcher, gmm):
     """Routed experts with the gate and up projections fused in W13 [E, 2H, D] and W2 [E, D, H]."""
     xl, offs, st = dispatcher.dispatch(x, ids)
+    from alto_b200.swiglu import swiglu
     h = gmm(xl, W13.transpose(-2, -1), offs)
-    H = h.shape[-1] // 2
-    y = gmm(torch.nn.functional.silu(h[:, :H]) * h[:, H:], W2.transpose(-2, -1), offs)
+    y = gmm(swiglu(h), W2.transpose(-2, -1), offs)
     return dispatcher.combine(y, st, scores)
 
 
