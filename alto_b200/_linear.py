@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import contextlib
 import os
+import threading
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -273,12 +274,8 @@ def backward_operands(g2, fmt, *, use_2dblock_x, use_sr_grad, use_outer_scale, r
 #: stream right after that GEMM:
 #:   forward : fprop GEMM   ||  X along M (needed only in backward)
 #:   backward: wgrad GEMM   ||  dY along N (needed by the dgrad GEMM that follows)
-#: Results are identical; only the launch order differs.  This paid off (1.72 -> 1.57 ms per bench
-#: step) while the GEMM was the 320-thread single-CTA kernel, next to which a quantizer CTA is
-#: resident on the same SM.  The CTA-pair GEMM takes a whole SM (448 threads x 128 registers), so a
-#: concurrent quantizer can only take SMs away from it, and its static tile schedule then waits for
-#: the clusters that started late: measured 1.58-1.73 ms with the side stream against 1.57 ms
-#: without.  Hence off by default; ALTO_B200_OVERLAP=1 turns it on.
+#: Results are identical; only the launch order differs.  Off by default (ALTO_B200_OVERLAP=1 turns it
+#: on): the CTA-pair GEMM fills every SM, so a concurrent quantizer can only take SMs away from it.
 OVERLAP = os.environ.get("ALTO_B200_OVERLAP", "0") == "1"
 _side_streams = {}
 
@@ -289,6 +286,23 @@ def _side_stream(device: torch.device) -> torch.cuda.Stream:
         s = torch.cuda.Stream(device=device)
         _side_streams[device.index] = s
     return s
+
+
+# A caller that shards the weight by output features must sum the partial dX of all ranks; it can
+# start that all-reduce as soon as the dgrad GEMM has been launched and let it run beside the wgrad
+# quantizer and GEMM.  The hook is armed on the autograd thread right before the linear's backward runs
+# (``distributed._ArmDxAllReduce``) and taken by that backward; it receives the contiguous dX [M, K].
+_dx_hook = threading.local()
+
+
+def set_dx_ready_hook(fn) -> None:
+    _dx_hook.fn = fn
+
+
+def take_dx_ready_hook():
+    fn = getattr(_dx_hook, "fn", None)
+    _dx_hook.fn = None
+    return fn
 
 
 def _keep_for(stream, *tensors) -> None:
@@ -395,9 +409,24 @@ def linear_backward(ctx, grad_output):
         if ctx.use_dge:
             grad_weights = dge.apply_to_weight_grad(grad_weights, w_t.codes)
         return grad_inputs, grad_weights
-    g_n, g_m = backward_operands(g2, ctx.fmt, use_2dblock_x=ctx.use_2dblock_x, use_sr_grad=ctx.use_sr_grad,
-                                 use_outer_scale=ctx.use_outer_scale, rht=ctx.rht, dense=ctx.dense_transform,
-                                 use_uos=ctx.use_uos, clip_mode=ctx.clip_mode)
+    dx_hook = take_dx_ready_hook()
+    if dx_hook is not None and need_dx and not ctx.use_2dblock_x:
+        # dgrad first, with only the operand it needs; the hook (an asynchronous all-reduce of dX) then runs
+        # beside the second quantizer of dY and the wgrad GEMM.  Random words are drawn in the usual order.
+        og = outer_scales(g2, ctx.use_outer_scale, ctx.rht)
+        sr_n = sr_args(ctx.use_sr_grad, "dy_n", M, N, g2.device)
+        sr_m = sr_args(ctx.use_sr_grad, "dy_m", N, M, g2.device)
+        g_n = quant_rows(g2, ctx.fmt, None if og is None else og[0:1], sr_n, ctx.use_uos)
+        dx2 = gemm(g_n, w_t, grad_output.dtype)
+        dx_hook(dx2)
+        grad_inputs = dx2.view(*original_shape[:-1], K)
+        need_dx = False
+        g_m = cols_operand(g2, ctx.fmt, ctx.use_outer_scale, og, ctx.rht, ctx.dense_transform, sr_m, ctx.use_uos,
+                           ctx.clip_mode) if need_dw else None
+    else:
+        g_n, g_m = backward_operands(g2, ctx.fmt, use_2dblock_x=ctx.use_2dblock_x, use_sr_grad=ctx.use_sr_grad,
+                                     use_outer_scale=ctx.use_outer_scale, rht=ctx.rht, dense=ctx.dense_transform,
+                                     use_uos=ctx.use_uos, clip_mode=ctx.clip_mode)
     if need_dx:
         grad_inputs = gemm(g_n, w_t, grad_output.dtype).view(*original_shape[:-1], K)
     if need_dw:

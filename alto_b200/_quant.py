@@ -57,10 +57,17 @@ def quantize(x: torch.Tensor, fmt: int, axis: int, is_2d: bool, *, outer_scale: 
         sr = {}
         if rounding != L.ROUND_RTN:
             # words belong to (row, column pair) of the quantisation-axis-last view, leading dimensions
-            # flattened into its rows; for axis=-2 that view is the transposed matrix, which this kernel
-            # does not index
-            if a != -1 or not fp4:
-                raise NotImplementedError("stochastic rounding with 2D blocks is implemented for FP4 and axis=-1")
+            # flattened into its rows
+            if not fp4:
+                raise NotImplementedError("stochastic rounding is implemented for the FP4 formats")
+            if a == -2:
+                # that view is the transposed matrix: quantise a transposed copy along its last axis (2-D
+                # blocks are symmetric) and hand the results back as transposed views, which is what the
+                # reference does with a strided view (alto/kernels/fp4/mxfp4/mxfp_quantization.py:439, 484)
+                ct, st = quantize(x.transpose(-1, -2).contiguous(), fmt, -1, True, outer_scale=outer_scale,
+                                  rounding=rounding, rand_bits=rand_bits, philox=philox, clip_mode=clip_mode,
+                                  use_uos=use_uos)
+                return ct.transpose(-1, -2), st.transpose(-1, -2)
             if rounding == L.ROUND_SR_PHILOX:
                 tile = L.sr_tile_dims(nb * M, N)
                 sr = dict(rounding=L.ROUND_SR_BITS, rand_tile=tile,

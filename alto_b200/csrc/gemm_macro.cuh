@@ -69,7 +69,7 @@ struct MacroGemmArgs {
 #define PROF_FLUSH(role)
 #endif
 
-constexpr int NUM_THREADS_MACRO = 512;
+constexpr int NUM_THREADS_MACRO = 768;
 
 struct CfgMacro {
   static constexpr int BN = 128;
@@ -84,9 +84,11 @@ struct CfgMacro {
   static constexpr int SF_COLS_B = SF_TILES * 4;
   static constexpr int STAGES = 4;
   static constexpr int P_BUFS = 3;                              // chunk accumulators in tensor memory
-  static constexpr int FOLD_WARPS = 8;
-  static constexpr int EPI_BYTES = FOLD_WARPS * 2 * 4096;       // two staging buffers of 32 rows x 128 bytes per warp
-  static constexpr int FB_BYTES = FOLD_WARPS * 2 * 64 * 4;      // two buffers of 64 column factors per warp
+  static constexpr int FOLD_WARPS = 16;                         // four per tensor-memory lane quarter, 32 columns each
+  static constexpr int FOLD_COLS = BN / (FOLD_WARPS / 4);
+  static constexpr int EPI_WARP_BYTES = 4096;                   // bf16: two buffers of 32 rows x 64 bytes; fp32: one of 32 x 128
+  static constexpr int EPI_BYTES = FOLD_WARPS * EPI_WARP_BYTES;
+  static constexpr int FB_BYTES = FOLD_WARPS * 2 * FOLD_COLS * 4;  // two buffers of 32 column factors per warp
   static constexpr int RCP_BYTES = 256 * 4;                     // 1 / factor for every code
   static constexpr int TMEM_SF_BASE = P_BUFS * BN;
   static constexpr int TMEM_COLS_USED = TMEM_SF_BASE + STAGES * (SF_COLS_A + SF_COLS_B);
@@ -96,8 +98,15 @@ struct CfgMacro {
       STAGES * STAGE_BYTES + EPI_BYTES + FB_BYTES + RCP_BYTES + 1024 /*align*/ + 512 /*barriers*/;
   static_assert(NUM_BARS * 8 + 16 <= 512, "barrier area");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
-  // registers per thread after the warpgroups have re-divided the file: 2 x 128 x 40 + 2 x 128 x 216 = 65536
-  static constexpr int REGS_SMALL = 40, REGS_FOLD = 216;
+  // Registers per thread after the warpgroups have re-divided the file.  The CTA is launched with 80
+  // registers per thread (65536 / 768 rounded down to a multiple of 8, what ptxas reports for this
+  // kernel); setmaxnreg.inc can only take what setmaxnreg.dec has released INSIDE the CTA and blocks
+  // for ever otherwise, so the two must balance exactly: 2 x 128 x 48 + 4 x 128 x 96 = 768 x 80.
+  static constexpr int REGS_LAUNCH = 80;
+  static constexpr int REGS_SMALL = 48, REGS_FOLD = 96;
+  static_assert(2 * 128 * REGS_SMALL + (FOLD_WARPS / 4) * 128 * REGS_FOLD == NUM_THREADS_MACRO * REGS_LAUNCH,
+                "setmaxnreg budget must balance");
+  static_assert(NUM_THREADS_MACRO == (8 + FOLD_WARPS) * 32, "role layout");
 };
 
 // Tile description plus what the chunk loop needs: the first chunk of the K range, the number of
@@ -131,16 +140,16 @@ __device__ __forceinline__ MacroTile decode_macro_tile(const GemmArgs& args, int
   return m;
 }
 
-// acc[16 h .. 16 h + 16) += P * (ra * fb[col]) for 32 columns of one chunk (P: raw tensor-memory words of
-// this thread's row; h must be a compile-time constant at the call site after inlining)
-__device__ __forceinline__ void fold_half(float2 (&acc)[32], int h, const uint32_t (&p)[32], float ra,
-                                          const float* fb, bool b_uniform, float rb_uniform) {
+// acc += P * (ra * fb[col]) for the 32 columns of one chunk that a fold warp owns (P: raw tensor-memory
+// words of this thread's row)
+__device__ __forceinline__ void fold_cols(float2 (&acc)[16], const uint32_t (&p)[32], float ra, const float* fb,
+                                          bool b_uniform, float rb_uniform) {
   if (b_uniform) {
     const float g = __fmul_rn(ra, rb_uniform);
     const float2 g2 = make_float2(g, g);
 #pragma unroll
     for (int j = 0; j < 16; ++j)
-      acc[16 * h + j] = __ffma2_rn(make_float2(u2f(p[2 * j]), u2f(p[2 * j + 1])), g2, acc[16 * h + j]);
+      acc[j] = __ffma2_rn(make_float2(u2f(p[2 * j]), u2f(p[2 * j + 1])), g2, acc[j]);
   } else {
     const float2 ra2 = make_float2(ra, ra);
 #pragma unroll
@@ -148,9 +157,8 @@ __device__ __forceinline__ void fold_half(float2 (&acc)[32], int h, const uint32
       const float4 f = *reinterpret_cast<const float4*>(fb + 4 * j);
       const float2 g0 = __fmul2_rn(ra2, make_float2(f.x, f.y));
       const float2 g1 = __fmul2_rn(ra2, make_float2(f.z, f.w));
-      acc[16 * h + 2 * j] = __ffma2_rn(make_float2(u2f(p[4 * j]), u2f(p[4 * j + 1])), g0, acc[16 * h + 2 * j]);
-      acc[16 * h + 2 * j + 1] =
-          __ffma2_rn(make_float2(u2f(p[4 * j + 2]), u2f(p[4 * j + 3])), g1, acc[16 * h + 2 * j + 1]);
+      acc[2 * j] = __ffma2_rn(make_float2(u2f(p[4 * j]), u2f(p[4 * j + 1])), g0, acc[2 * j]);
+      acc[2 * j + 1] = __ffma2_rn(make_float2(u2f(p[4 * j + 2]), u2f(p[4 * j + 3])), g1, acc[2 * j + 1]);
     }
   }
 }
@@ -372,17 +380,20 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (warp == 4 && lane == 0) { PROF_FLUSH(2); }
   } else {
     // ------------------------------ fold + epilogue ------------------------------
+    // Sixteen warps, four per tensor-memory lane quarter, each 32 rows x 32 columns of the tile.  What
+    // bounds the fold is the latency of the tensor-memory load (a warp has one in flight and waits for
+    // it), so the chunk is spread over as many warps as the register file carries: 64 KB per chunk are
+    // in flight at once, and the four warps of a scheduler cover each other's waits.
     setmaxnreg_inc<C::REGS_FOLD>();
+    constexpr int FC = C::FOLD_COLS;
     const int quad = warp & 3;                        // tensor-memory lane quarter this warp may read
-    const int half = warp >= 12 ? 1 : 0;              // columns [64 half, 64 half + 64) of the tile
+    const int cq = (warp - 8) >> 2;                   // columns [32 cq, 32 cq + 32) of the tile
     const int fold_idx = warp - 8;
-    uint8_t* epi_warp = epi + fold_idx * 8192;
-    float* fb_warp = fb_all + fold_idx * 128;
+    uint8_t* epi_warp = epi + fold_idx * C::EPI_WARP_BYTES;
+    float* fb_warp = fb_all + fold_idx * (2 * FC);
     const bool b_uniform = margs.mb.shift >= 7;       // one B factor per 128-column tile and chunk
     const bool out_bf16 = args.out_bf16 != 0;
-    const uint32_t my_row = smem_u32(epi_warp) + (uint32_t)lane * 128u;
-    const uint32_t sw = (uint32_t)(lane & 7);
-    const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + half * 64;
+    const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + cq * FC;
     uint32_t pc = 0, store_it = 0;
     bool alive = true;
     PROF_DECL;
@@ -390,123 +401,77 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     for (int64_t tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
       const MacroTile mt = decode_macro_tile(args, tile, tiles_m, tiles_n, k_stages);
       const TileInfo& ti = mt.t;
-      float2 acc[32];
+      float2 acc[FC / 2];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) acc[j] = make_float2(0.0f, 0.0f);
+      for (int j = 0; j < FC / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
       if (!ti.skip) {
-        // factor codes of this thread's row of A and of the two columns of B this lane stages
+        // factor codes of this thread's row of A and of the column of B this lane stages
         int64_t m = ti.mb * BM + quad * 32 + lane;
         if (m >= args.M) m = args.M - 1;
-        int64_t n0 = ti.nb * BN + half * 64 + 2 * lane, n1 = n0 + 1;
+        int64_t n0 = ti.nb * BN + cq * FC + lane;
         if (n0 >= args.N) n0 = args.N - 1;
-        if (n1 >= args.N) n1 = args.N - 1;
         const uint8_t* pa = margs.ma.codes + (m >> margs.ma.shift) * margs.ma.row_stride +
                             mt.chunk0 * margs.ma.chunk_stride;
-        const uint8_t* pbase = margs.mb.codes + (int64_t)mt.expert * margs.mb.expert_stride +
-                               mt.chunk0 * margs.mb.chunk_stride;
-        const uint8_t* pb0 = pbase + (n0 >> margs.mb.shift) * margs.mb.row_stride;
-        const uint8_t* pb1 = pbase + (n1 >> margs.mb.shift) * margs.mb.row_stride;
+        const uint8_t* pb = margs.mb.codes + (int64_t)mt.expert * margs.mb.expert_stride +
+                            mt.chunk0 * margs.mb.chunk_stride + (n0 >> margs.mb.shift) * margs.mb.row_stride;
         const int nch = mt.n_chunks;
-        uint32_t ca = __ldg(pa), cb0 = __ldg(pb0), cb1 = __ldg(pb1);
-        uint32_t ra_[32], rb_[32];   // chunk accumulator words: columns [0, 32) and [32, 64) of this warp's 64
-
-        // Prologue of the tile: the first half of chunk 0 is requested.
-        if (nch > 0 && !ALTOB200_DBG(args, 256)) {
-          const int buf = pc % C::P_BUFS;
-          const long long t0 = PROF_NOW();
-          alive = mbar_wait(&p_full[buf], (pc / C::P_BUFS) & 1, abort_flag, 24, args.wait_ns);
-          PROF_ADD(4, t0);
-          tc_fence_after();
-          if (alive) tc_ld32(t_row + buf * BN, ra_);
-        }
-        // Per chunk the two halves are loaded one behind the other, so that a tensor-memory load is always
-        // in flight while the other half is folded; the first half of chunk c + 1 is requested as soon as
-        // chunk c has left tensor memory.
+        uint32_t ca = __ldg(pa), cb = __ldg(pb);
+        uint32_t p[FC];   // chunk accumulator words of this thread's row
         for (int c = 0; c < nch && alive; ++c) {
           if (ALTOB200_DBG(args, 256)) { ++pc; continue; }
-          if (ALTOB200_DBG(args, 64)) {
-            // profiling builds only: the chunk is handed straight back (tensor-core time of the chunked mainloop)
-            tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_empty[pc % C::P_BUFS]);
-            ++pc;
-            if (c + 1 < nch) {
-              alive = mbar_wait(&p_full[pc % C::P_BUFS], (pc / C::P_BUFS) & 1, abort_flag, 24, args.wait_ns);
-              tc_fence_after();
-            }
-            continue;
-          }
+          const int buf = pc % C::P_BUFS;
           long long t0 = PROF_NOW();
-          const float ra = rcp_tab[ca], rb0 = rcp_tab[cb0], rb1 = rcp_tab[cb1];
-          if (c + 1 < nch) {  // the next chunk's codes are in flight during this chunk's arithmetic
+          alive = mbar_wait(&p_full[buf], (pc / C::P_BUFS) & 1, abort_flag, 24, args.wait_ns);
+          PROF_ADD(2, t0);
+          if (!alive) break;
+          tc_fence_after();
+          if (warp == 8 && lane == 0) { PROF_TRACE(3, pc, 0); }
+          tc_ld32(t_row + buf * BN, p);
+          // under the load: this chunk's factors, the next chunk's codes
+          t0 = PROF_NOW();
+          const float ra = rcp_tab[ca], rb = rcp_tab[cb];
+          if (c + 1 < nch) {
             ca = __ldg(pa + (int64_t)(c + 1) * margs.ma.chunk_stride);
-            cb0 = __ldg(pb0 + (int64_t)(c + 1) * margs.mb.chunk_stride);
-            cb1 = __ldg(pb1 + (int64_t)(c + 1) * margs.mb.chunk_stride);
+            cb = __ldg(pb + (int64_t)(c + 1) * margs.mb.chunk_stride);
           }
-          float* fb = fb_warp + (c & 1) * 64;
+          float* fb = fb_warp + (c & 1) * FC;
           if (!b_uniform) {
-            reinterpret_cast<float2*>(fb)[lane] = make_float2(rb0, rb1);
+            fb[lane] = rb;
             __syncwarp();
           }
           PROF_ADD(6, t0);
-          const uint32_t t_p = t_row + (pc % C::P_BUFS) * BN;
-          if (warp == 8 && lane == 0) { PROF_TRACE(3, pc, 0); }
           t0 = PROF_NOW();
-          tc_wait_ld();                 // first half of chunk c is in ra_
-          PROF_ADD(1, t0);
-          tc_ld32(t_p + 32, rb_);
-          t0 = PROF_NOW();
-          fold_half(acc, 0, ra_, ra, fb, b_uniform, rb0);
-          PROF_ADD(3, t0);
-          t0 = PROF_NOW();
-          tc_wait_ld();                 // second half is in rb_: chunk c has left tensor memory
+          tc_wait_ld();                 // the chunk has left tensor memory
           PROF_ADD(1, t0);
           t0 = PROF_NOW();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&p_empty[pc % C::P_BUFS]);
+          if (lane == 0) mbar_arrive(&p_empty[buf]);
           if (warp == 8 && lane == 0) { PROF_TRACE(3, pc, 1); }
           ++pc;
           PROF_ADD(7, t0);
-          if (c + 1 < nch) {
-            const int buf = pc % C::P_BUFS;
-            t0 = PROF_NOW();
-            alive = mbar_wait(&p_full[buf], (pc / C::P_BUFS) & 1, abort_flag, 24, args.wait_ns);
-            PROF_ADD(2, t0);
-            tc_fence_after();
-            if (alive) tc_ld32(t_row + buf * BN, ra_);
-          }
+          if (ALTOB200_DBG(args, 64)) continue;   // profiling builds only: chunks are handed straight back
           t0 = PROF_NOW();
-          fold_half(acc, 1, rb_, ra, fb + 32, b_uniform, rb0);
+          fold_cols(acc, p, ra, fb, b_uniform, rb);
           PROF_ADD(3, t0);
         }
-        if (!alive) {
-          tc_wait_ld();
-          break;
-        }
+        if (!alive) break;
       }
-      // ---- epilogue of the tile: this warp's 32 rows x 64 columns ----
+      // ---- epilogue of the tile: this warp's 32 rows x 32 columns ----
       const long long t_epi = PROF_NOW();
       const float os = margs.out_scale;
       const int64_t row0 = ti.mb * BM + quad * 32;
-      const int64_t col_base = ti.nb * BN + half * 64;
-      auto hand_over = [&](int64_t col0) {
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          if (row0 < args.M && col0 < args.N)
-            tma_store_3d(epi_warp + (store_it & 1u) * 4096u, &tmap_d, (int32_t)col0, (int32_t)row0, ti.batch);
-          bulk_commit();  // one group per unit, empty or not: the wait below counts groups
-        }
-        ++store_it;
-      };
+      const int64_t col0 = ti.nb * BN + cq * FC;
+      uint32_t buf;
       if (out_bf16) {
-        if (lane == 0) bulk_wait_read<1>();  // the store issued two units ago has finished reading this buffer
+        // 64-byte rows (64-byte swizzle: chunk index ^ bits 1-2 of the row), two buffers
+        if (lane == 0) bulk_wait_read<1>();  // the store issued two tiles ago has finished reading this buffer
         __syncwarp();
-        const uint32_t buf = my_row + (store_it & 1u) * 4096u;
+        buf = (store_it & 1u) * 2048u;
+        const uint32_t row = smem_u32(epi_warp) + buf + (uint32_t)lane * 64u;
+        const uint32_t sw = (uint32_t)((lane >> 1) & 3);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
           uint32_t o[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -514,24 +479,30 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const __nv_bfloat162 p2 = __floats2bfloat162_rn(__fmul_rn(v.x, os), __fmul_rn(v.y, os));
             o[q] = *reinterpret_cast<const uint32_t*>(&p2);
           }
-          st_shared_v4(buf + ((((uint32_t)j) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+          st_shared_v4(row + ((((uint32_t)j) ^ sw) << 4), o[0], o[1], o[2], o[3]);
         }
-        hand_over(col_base);
       } else {
+        // 128-byte rows (128-byte swizzle), one buffer
+        if (lane == 0) bulk_wait_read<0>();
+        __syncwarp();
+        buf = 0u;
+        const uint32_t row = smem_u32(epi_warp) + (uint32_t)lane * 128u;
+        const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          if (lane == 0) bulk_wait_read<1>();
-          __syncwarp();
-          const uint32_t buf = my_row + (store_it & 1u) * 4096u;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float2 v0 = acc[u * 16 + 2 * j], v1 = acc[u * 16 + 2 * j + 1];
-            st_shared_v4(buf + ((((uint32_t)j) ^ sw) << 4), f2u(__fmul_rn(v0.x, os)), f2u(__fmul_rn(v0.y, os)),
-                         f2u(__fmul_rn(v1.x, os)), f2u(__fmul_rn(v1.y, os)));
-          }
-          hand_over(col_base + u * 32);
+        for (int j = 0; j < 8; ++j) {
+          const float2 v0 = acc[2 * j], v1 = acc[2 * j + 1];
+          st_shared_v4(row + ((((uint32_t)j) ^ sw) << 4), f2u(__fmul_rn(v0.x, os)), f2u(__fmul_rn(v0.y, os)),
+                       f2u(__fmul_rn(v1.x, os)), f2u(__fmul_rn(v1.y, os)));
         }
       }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        if (row0 < args.M && col0 < args.N)
+          tma_store_3d(epi_warp + buf, &tmap_d, (int32_t)col0, (int32_t)row0, ti.batch);
+        bulk_commit();  // one group per tile, empty or not: the waits above count groups
+      }
+      ++store_it;
       PROF_ADD(5, t_epi);
     }
     if (lane == 0) bulk_wait_all();

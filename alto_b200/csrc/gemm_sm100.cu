@@ -848,6 +848,8 @@ struct CfgPair {
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * 4096;
   // registers per thread after the warpgroups have re-divided the file: 2 x 128 x 56 + 2 x 128 x 200 = 65536
   static constexpr int REGS_SMALL = BN_ == 256 ? 56 : 72, REGS_EPI = BN_ == 256 ? 200 : 184;
+  // setmaxnreg.inc takes only what setmaxnreg.dec released inside the CTA (launched at 128 per thread)
+  static_assert(REGS_SMALL + REGS_EPI == 2 * 128, "setmaxnreg budget must balance");
   static constexpr int TMEM_SF_BASE = ACC_STAGES * BN;
   static constexpr int SF_COLS = SF_COLS_A + SF_COLS_B;
   // scale slots in tensor memory: one per operand stage if they fit, else as many as do (a slot is
@@ -1563,7 +1565,9 @@ static int gemm_macro_common(int64_t M, int64_t N, int64_t K, int32_t num_expert
   if (rc != ALTOB200_OK) return rc;
   rc = make_tmap(&tb, b_codes, b_rows, k_bytes, CfgMacro::BN);
   if (rc != ALTOB200_OK) return rc;
-  rc = make_tmap_out(&td, d, k_offs != nullptr ? num_experts : 1, M, N, ldd, out_dtype == ALTOB200_DT_BF16);
+  // a fold warp stores 32 columns per row: 64 bytes of bf16 (64-byte swizzle) or 128 bytes of fp32
+  rc = make_tmap_out(&td, d, k_offs != nullptr ? num_experts : 1, M, N, ldd, out_dtype == ALTOB200_DT_BF16,
+                     out_dtype == ALTOB200_DT_BF16 ? 64 : 128);
   if (rc != ALTOB200_OK) return rc;
 
   MacroGemmArgs m;

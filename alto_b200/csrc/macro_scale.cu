@@ -258,6 +258,93 @@ __global__ void __launch_bounds__(256) macro_scale_tile_kernel(MacroArgs a) {
   }
 }
 
+// ---- 2D and column blocks, bf16 with 4-wide accesses: the tile stays packed in registers ----
+// Same work split as above (a warp 16 rows, a lane 4 columns), but the 16 x 4 elements are kept as
+// the 32 words they were loaded as and the maxima are taken on the packed bit patterns (|bf16| orders
+// like its integer bits), which leaves room for four CTAs per SM instead of two: the kernel is a plain
+// stream, and what limits it is the number of bytes in flight.
+template <bool DESCALE, bool COLS>
+__global__ void __launch_bounds__(256, 4) macro_scale_tile_bf16_kernel(MacroArgs a) {
+  __shared__ __align__(16) uint2 s_max[COLS ? 8 * 32 : 8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t b = blockIdx.z, tm = blockIdx.y, tn = blockIdx.x;
+  const int64_t mtiles = (a.rows + 127) / 128;
+  const int64_t col = tn * 128 + lane * 4;
+  const bool col_ok = col < a.cols;   // cols is a multiple of 4: a lane's 4 elements exist together
+  const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.x);
+  uint2 raw[16];
+  uint2 acc = make_uint2(0u, 0u);     // packed per-column maxima of |x| bit patterns
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int64_t r = tm * 128 + warp * 16 + i;
+    raw[i] = (col_ok && r < a.rows) ? __ldg(reinterpret_cast<const uint2*>(src + (b * a.rows + r) * a.cols + col))
+                                    : make_uint2(0u, 0u);
+    acc.x = __vmaxu2(acc.x, raw[i].x & 0x7FFF7FFFu);
+    acc.y = __vmaxu2(acc.y, raw[i].y & 0x7FFF7FFFu);
+  }
+  float f[4];
+  if (COLS) {
+    if (DESCALE) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        f[j] = col_ok ? macro_factor_from_code(a.scale[(b * a.cols + col + j) * mtiles + tm]) : 1.0f;
+    } else {
+      s_max[warp * 32 + lane] = acc;
+      __syncthreads();
+      uint2 t = s_max[lane];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) {
+        const uint2 o = s_max[w * 32 + lane];
+        t.x = __vmaxu2(t.x, o.x);
+        t.y = __vmaxu2(t.y, o.y);
+      }
+      const float m[4] = {u2f(t.x << 16), u2f(t.x & 0xFFFF0000u), u2f(t.y << 16), u2f(t.y & 0xFFFF0000u)};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t code;
+        f[j] = macro_factor_from_amax(m[j], &code);
+        if (warp == 0 && col_ok) a.scale[(b * a.cols + col + j) * mtiles + tm] = (uint8_t)code;
+      }
+    }
+  } else {
+    const int64_t sidx = (b * mtiles + tm) * a.nblk + tn;
+    float ft;
+    if (DESCALE) {
+      ft = macro_factor_from_code(a.scale[sidx]);
+    } else {
+      uint32_t m2 = __vmaxu2(acc.x, acc.y);
+      m2 = __vmaxu2(m2, m2 >> 16) & 0xFFFFu;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const uint32_t t = __shfl_xor_sync(0xFFFFFFFFu, m2, o);
+        m2 = t > m2 ? t : m2;
+      }
+      if (lane == 0) s_max[warp].x = m2;
+      __syncthreads();
+      uint32_t t = s_max[0].x;
+#pragma unroll
+      for (int i = 1; i < 8; ++i) t = s_max[i].x > t ? s_max[i].x : t;
+      uint32_t code;
+      ft = macro_factor_from_amax(u2f(t << 16), &code);
+      if (threadIdx.x == 0) a.scale[sidx] = (uint8_t)code;
+    }
+    f[0] = f[1] = f[2] = f[3] = ft;
+  }
+  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.y);
+  if (!col_ok) return;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int64_t r = tm * 128 + warp * 16 + i;
+    if (r >= a.rows) break;
+    float v[4] = {bf16lo_to_f32(raw[i].x), bf16hi_to_f32(raw[i].x), bf16lo_to_f32(raw[i].y), bf16hi_to_f32(raw[i].y)};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = DESCALE ? __fdiv_rn(v[j], f[j]) : __fmul_rn(v[j], f[j]);
+    const uint32_t lo = f32_to_bf16_bits(v[0]) | (f32_to_bf16_bits(v[1]) << 16);
+    const uint32_t hi = f32_to_bf16_bits(v[2]) | (f32_to_bf16_bits(v[3]) << 16);
+    *reinterpret_cast<uint2*>(dst + (b * a.rows + r) * a.cols + col) = make_uint2(lo, hi);
+  }
+}
+
 template <bool BF, bool DESCALE>
 static void launch_mode(const MacroArgs& a, int32_t mode, cudaStream_t st) {
   if (mode == 0) {
@@ -272,6 +359,11 @@ static void launch_mode(const MacroArgs& a, int32_t mode, cudaStream_t st) {
     macro_scale_1d_kernel<BF, DESCALE><<<(unsigned)blocks, 256, 0, st>>>(a);
   } else {
     dim3 grid((unsigned)a.nblk, (unsigned)ceil_div(a.rows, 128), (unsigned)a.batch);
+    if (BF && a.vec) {
+      if (mode == 1) macro_scale_tile_bf16_kernel<DESCALE, false><<<grid, 256, 0, st>>>(a);
+      else macro_scale_tile_bf16_kernel<DESCALE, true><<<grid, 256, 0, st>>>(a);
+      return;
+    }
     if (mode == 1) macro_scale_tile_kernel<BF, DESCALE, false><<<grid, 256, 0, st>>>(a);
     else macro_scale_tile_kernel<BF, DESCALE, true><<<grid, 256, 0, st>>>(a);
   }

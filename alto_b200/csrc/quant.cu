@@ -850,7 +850,7 @@ struct Quant2dArgs {
   uint8_t* packed_t;  // rows=cols, ncols=rows/B
   int64_t nct_k, nct_t;
   const float* outer;
-  MxOpts mx;          // clip 0/1 and uos (the dynamic clip needs block sums and is 1-D only)
+  MxOpts mx;          // clip 0/1/2 and uos
   // stochastic rounding (FP4): words by (row, pair of columns) as in the row-wise quantizer: full planes
   // [2][rows][cols/2], or a periodic table [2][tile_rows][tile_pairs]
   const uint32_t* rand_bits;
@@ -908,6 +908,9 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
   // ---- load and block maximum ----
   uint4 raw[IN_BF16 ? 16 : 1];  // bf16: the 16 x 8 elements stay in registers; fp32: rows are read again
   uint32_t amax_bits = 0;
+  // the dynamic clip (MX formats) takes the block's sum and sum of squares instead of its maximum
+  const bool stats = F::MX && a.mx.clip == 2;
+  float sum = 0.0f, sumsq = 0.0f;
   if (IN_BF16) {
     uint32_t acc = 0;
 #pragma unroll
@@ -916,6 +919,18 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
       acc = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(acc, raw[i].x), raw[i].y), raw[i].z), raw[i].w);
     }
     amax_bits = fold_bf16x2(acc);
+    if (stats) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = bf16lo_to_f32(w[j]), hi = bf16hi_to_f32(w[j]);
+          sum = __fadd_rn(__fadd_rn(sum, lo), hi);
+          sumsq = __fadd_rn(__fadd_rn(sumsq, round_in<true>(__fmul_rn(lo, lo))), round_in<true>(__fmul_rn(hi, hi)));
+        }
+      }
+    }
   } else if (ok) {
 #pragma unroll 4
     for (int i = 0; i < 16; ++i) {
@@ -926,6 +941,10 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
       for (int j = 0; j < 8; ++j) {
         const uint32_t b = ws[j] & 0x7FFFFFFFu;
         amax_bits = b > amax_bits ? b : amax_bits;
+        if (stats) {
+          sum = __fadd_rn(sum, u2f(ws[j]));
+          sumsq = __fadd_rn(sumsq, __fmul_rn(u2f(ws[j]), u2f(ws[j])));
+        }
       }
     }
   }
@@ -934,13 +953,21 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
   for (int o = 1; o < B / 8; o <<= 1) {
     const uint32_t t = __shfl_xor_sync(0xFFFFFFFFu, amax_bits, o);
     amax_bits = t > amax_bits ? t : amax_bits;
+    if (stats) {   // uniform: a launch argument
+      sum = __fadd_rn(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, o));
+      sumsq = __fadd_rn(sumsq, __shfl_xor_sync(0xFFFFFFFFu, sumsq, o));
+    }
   }
   if (B == 32) {
     const uint32_t t = __shfl_xor_sync(0xFFFFFFFFu, amax_bits, LC);
     amax_bits = t > amax_bits ? t : amax_bits;
+    if (stats) {
+      sum = __fadd_rn(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, LC));
+      sumsq = __fadd_rn(sumsq, __shfl_xor_sync(0xFFFFFFFFu, sumsq, LC));
+    }
   }
   const BlockScale s = (F::MX && (a.mx.clip | a.mx.uos))
-                           ? make_block_scale_opts<FMT, IN_BF16>(amax_bits, 0.0f, 0.0f, B * B, a.mx)
+                           ? make_block_scale_opts<FMT, IN_BF16>(amax_bits, sum, sumsq, B * B, a.mx)
                            : make_block_scale<FMT, IN_BF16>(amax_bits, os);
   const bool clip = F::MX && a.mx.clip == 1;
 
@@ -1803,7 +1830,7 @@ int altob200_quantize_2d_batched(const void* w, int64_t batch, int64_t batch_str
   a.rand_bits = p->rand_bits; a.tile_rows = p->rand_tile_rows; a.tile_pairs = p->rand_tile_pairs;
   if ((a.tile_rows != 0) != (a.tile_pairs != 0) || a.tile_rows < 0 || a.tile_pairs < 0 || (a.tile_pairs & 3) != 0)
     return ALTOB200_EINVAL_SHAPE;
-  int rc = fill_mx_opts(&a.mx, p, false);
+  int rc = fill_mx_opts(&a.mx, p, true);
   if (rc != ALTOB200_OK) return rc;
   // padding entries of the packed layouts are zero (the kernel does not visit them)
   if (scale_packed_k != nullptr && ((rows & 127) != 0 || ((cols / B) & 3) != 0))

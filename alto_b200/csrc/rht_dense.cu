@@ -9,9 +9,10 @@
 // every other matrix (the reference's default block size 32 uses a table matrix that is not of
 // Sylvester type), at n multiply-adds per element.
 //
-// A thread owns two adjacent columns of one n-row block: the 2n inputs sit in registers, W is read
-// from shared memory four entries at a time (all threads of a warp read the same address), every
-// output row is produced, scaled, converted and stored at once.  Exact while the partial sums are
+// A thread owns two adjacent columns of one n-row block: the 2n inputs sit in registers as pairs, so
+// that one packed fp32 multiply-add (fma.rn.f32x2) serves both columns; W is read from shared memory
+// four entries at a time (all threads of a warp read the same address), every output row is
+// produced, scaled, converted and stored at once.  Exact while the partial sums are
 // exact (entries of W are +-1); the accumulation order is j = 0 .. n-1.
 #include <math.h>
 
@@ -40,7 +41,7 @@ __global__ void __launch_bounds__(128) rht_dense_kernel(RhtDenseArgs a) {
     const int64_t c = (ct << 8) + 2 * threadIdx.x;
     if (c >= a.cols) continue;
     const bool two = c + 1 < a.cols;
-    float x0[N], x1[N];
+    float2 xs[N];   // the two columns of a row side by side: one packed multiply-add serves both
 #pragma unroll
     for (int j = 0; j < N; ++j) {
       const int64_t off = (g * N + j) * a.ld + c;
@@ -48,33 +49,30 @@ __global__ void __launch_bounds__(128) rht_dense_kernel(RhtDenseArgs a) {
         const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(a.x) + off;
         if (two) {
           const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(p));
-          x0[j] = bf16lo_to_f32(w);
-          x1[j] = bf16hi_to_f32(w);
+          xs[j] = make_float2(bf16lo_to_f32(w), bf16hi_to_f32(w));
         } else {
-          x0[j] = __bfloat162float(*p);
-          x1[j] = 0.0f;
+          xs[j] = make_float2(__bfloat162float(*p), 0.0f);
         }
       } else {
         const float* p = reinterpret_cast<const float*>(a.x) + off;
-        x0[j] = __ldg(p);
-        x1[j] = two ? __ldg(p + 1) : 0.0f;
+        xs[j] = make_float2(__ldg(p), two ? __ldg(p + 1) : 0.0f);
       }
     }
 #pragma unroll 2
     for (int i = 0; i < N; ++i) {
-      float acc0 = 0.0f, acc1 = 0.0f;
+      float2 acc = make_float2(0.0f, 0.0f);
       const float4* wr = reinterpret_cast<const float4*>(s_w + i * N);
 #pragma unroll
       for (int q = 0; q < N / 4; ++q) {
         const float4 w = wr[q];
-        acc0 = __fmaf_rn(w.x, x0[4 * q], acc0);     acc1 = __fmaf_rn(w.x, x1[4 * q], acc1);
-        acc0 = __fmaf_rn(w.y, x0[4 * q + 1], acc0); acc1 = __fmaf_rn(w.y, x1[4 * q + 1], acc1);
-        acc0 = __fmaf_rn(w.z, x0[4 * q + 2], acc0); acc1 = __fmaf_rn(w.z, x1[4 * q + 2], acc1);
-        acc0 = __fmaf_rn(w.w, x0[4 * q + 3], acc0); acc1 = __fmaf_rn(w.w, x1[4 * q + 3], acc1);
+        acc = __ffma2_rn(make_float2(w.x, w.x), xs[4 * q], acc);
+        acc = __ffma2_rn(make_float2(w.y, w.y), xs[4 * q + 1], acc);
+        acc = __ffma2_rn(make_float2(w.z, w.z), xs[4 * q + 2], acc);
+        acc = __ffma2_rn(make_float2(w.w, w.w), xs[4 * q + 3], acc);
       }
       // adding +0.0 turns a -0.0 sum into +0.0, as the matmul's accumulation from zero does
-      const float y0 = __fmul_rn(__fadd_rn(acc0, 0.0f), a.inv_scale);
-      const float y1 = __fmul_rn(__fadd_rn(acc1, 0.0f), a.inv_scale);
+      const float y0 = __fmul_rn(__fadd_rn(acc.x, 0.0f), a.inv_scale);
+      const float y1 = __fmul_rn(__fadd_rn(acc.y, 0.0f), a.inv_scale);
       const int64_t off = (g * N + i) * a.ld_y + c;
       if (IN_BF16) {
         __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(a.y) + off;

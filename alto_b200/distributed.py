@@ -119,30 +119,79 @@ def shard_rows(w: torch.Tensor, group=None, multiple: int = 32) -> torch.Tensor:
     return w[rank * n:(rank + 1) * n]
 
 
+class _DxReduction:
+    """The all-reduce of one backward pass's partial dX, started inside the linear's backward."""
+
+    def __init__(self):
+        self.work = None
+        self.tensor = None
+
+
 class _CopyToShards(torch.autograd.Function):
     """Identity in forward; in backward the partial input gradients of the shards are summed."""
 
     @staticmethod
-    def forward(ctx, x, group):
+    def forward(ctx, x, group, pending):
         ctx.group = group
+        ctx.pending = pending
         return x.view_as(x)
 
     @staticmethod
     def backward(ctx, grad):
-        if _world(ctx.group) > 1:
+        from . import _linear as E
+        E.take_dx_ready_hook()          # a linear that did not take the hook must not leave it armed
+        p = ctx.pending
+        if p is not None and p.work is not None:
+            # started right after the dgrad GEMM; it ran beside the wgrad quantizer and GEMM
+            p.work.wait()
+            grad = p.tensor.view(grad.shape)
+            p.work = p.tensor = None
+        elif _world(ctx.group) > 1:
             grad = grad.contiguous()
             dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=ctx.group)
-        return grad, None
+        return grad, None, None
 
 
-def column_sharded_linear(x: torch.Tensor, w_shard: torch.Tensor, linear_fn: Callable, group=None) -> torch.Tensor:
+class _ArmDxAllReduce(torch.autograd.Function):
+    """Identity on the linear's output; its backward runs right before the linear's and arms the hook
+    through which that backward hands over dX as soon as the dgrad GEMM is in the stream."""
+
+    @staticmethod
+    def forward(ctx, y, group, pending):
+        ctx.group = group
+        ctx.pending = pending
+        return y.view_as(y)
+
+    @staticmethod
+    def backward(ctx, grad):
+        from . import _linear as E
+        group, pending = ctx.group, ctx.pending
+
+        def start(dx: torch.Tensor) -> None:
+            pending.tensor = dx
+            pending.work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
+
+        E.set_dx_ready_hook(start)
+        return grad, None, None
+
+
+def column_sharded_linear(x: torch.Tensor, w_shard: torch.Tensor, linear_fn: Callable, group=None,
+                          overlap_dx_reduction: bool = True) -> torch.Tensor:
     """Y_r = linear_fn(x, W_r) with W_r this rank's [N / world, K] shard; x is replicated.
 
     Forward has no exchange (the concatenation of the Y_r along N is implicit in the sharding of
     whatever consumes them), wgrad is local (dY_r, x), and dgrad dX = sum_r dY_r W_r is one
-    all-reduce of the bf16 partials.  ``linear_fn(a, b)`` is one of the boundary functions with its
-    recipe bound, e.g. ``lambda a, b: _to_mxfp8_then_scaled_mm(a, b, "e4m3", False, False, True)``."""
-    return linear_fn(_CopyToShards.apply(x, group), w_shard)
+    all-reduce of the bf16 partials.  With ``overlap_dx_reduction`` the all-reduce is issued
+    asynchronously right after the dgrad GEMM and waited for at the end of the backward, so that it
+    runs beside the second quantizer of dY and the wgrad GEMM (a linear function that is not one of
+    this package's simply ignores the request and the all-reduce happens after its backward).
+    ``linear_fn(a, b)`` is one of the boundary functions with its recipe bound, e.g.
+    ``lambda a, b: _to_mxfp8_then_scaled_mm(a, b, "e4m3", False, False, True)``."""
+    if _world(group) == 1 or not overlap_dx_reduction or not x.is_cuda:
+        return linear_fn(_CopyToShards.apply(x, group, None), w_shard)
+    pending = _DxReduction()
+    y = linear_fn(_CopyToShards.apply(x, group, pending), w_shard)
+    return _ArmDxAllReduce.apply(y, group, pending)
 
 
 # ------------------------------------------------------------------------------------------

@@ -25,8 +25,6 @@ BLOCK_SIZE_DEFAULT = 32
 def _check_options(clip_mode: str, use_uos: bool, is_2d_block: bool = False) -> None:
     if clip_mode not in ("none", "static", "dynamic"):
         raise ValueError(f"Invalid clip mode: {clip_mode}")
-    if clip_mode == "dynamic" and is_2d_block:
-        raise NotImplementedError("clip_mode='dynamic' with 2-D blocks is not implemented on the B200 path")
 
 
 @L.traced("convert_to_mxfp4")

@@ -33,6 +33,9 @@ CASES = [  # shape, dtype, axis, is_2d, clip_mode, use_uos, pattern
     ((64, 128), torch.float32, -1, False, "dynamic", False, "random"),
     ((64, 128), torch.float32, 0, False, "dynamic", False, "lognormal"),
     ((64, 128), torch.float32, -1, False, "dynamic", True, "random"),
+    ((64, 128), torch.float32, -1, True, "dynamic", False, "random"),
+    ((128, 64), torch.float32, 0, True, "dynamic", False, "lognormal"),
+    ((64, 64), torch.float32, -1, True, "dynamic", True, "random"),
 ]
 
 

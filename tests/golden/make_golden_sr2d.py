@@ -28,15 +28,15 @@ def main():
     seed, off = 2468, 1357
     out = {"philox_seed_offset": np.array([seed, off], dtype=np.int64)}
     meta = []
-    for j, shape in enumerate([(64, 64), (128, 192)]):
+    for j, (shape, axis) in enumerate([((64, 64), -1), ((128, 192), -1), ((128, 64), 0), ((2, 64, 96), -2)]):
         x = (G.data(shape, torch.float32, 700 + j) * 1.5).to(torch.bfloat16)
-        q, s = ref_to_mxfp4_triton(x, axis=-1, is_2d_block=True, use_asm=False, use_sr=True, philox_seed=seed,
+        q, s = ref_to_mxfp4_triton(x, axis=axis, is_2d_block=True, use_asm=False, use_sr=True, philox_seed=seed,
                                    philox_offset=off)
         tag = f"sr2d_{j}"
         out[tag + "_x"] = G.bits_of(x)
-        out[tag + "_q"] = q.contiguous().view(torch.uint8).numpy()
+        out[tag + "_q"] = q.contiguous().view(torch.uint8).numpy()   # logical shape (a transposed view for axis 0 / -2)
         out[tag + "_s"] = s.contiguous().numpy()
-        meta.append((tag, list(shape)))
+        meta.append((tag, list(shape), axis))
     out["meta"] = np.array(repr(meta))
     np.savez_compressed(G.OUT / "sr2d_vectors.npz", **out)
     print("wrote", G.OUT / "sr2d_vectors.npz", [m[0] for m in meta])

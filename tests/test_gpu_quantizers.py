@@ -385,8 +385,17 @@ def test_2d_blocks_with_stochastic_rounding(fmt, shape):
     _same(ck, qo, "K packing")
     want_t = O.pack_nibbles(O.unpack_nibbles(qo.view(torch.uint8)).t().contiguous())
     _same(ct, want_t, "N packing")
-    with pytest.raises(NotImplementedError):
-        NV.convert_to_nvfp4(x.to(d), axis=0, is_2d_block=True, update_outer_scale=False, use_sr=True)
+    # along axis 0 the words belong to the transposed view: the same codes as quantising x^T along its last axis
+    rt = rand_u32((2, Cc, R // 2), 78)
+    qa, sa = NV.convert_to_nvfp4(x.to(d), axis=0, is_2d_block=True, update_outer_scale=False, use_sr=True,
+                                 rand_bits=_u32dev(rt)) if fmt == "nvfp4" else \
+        MX.convert_to_mxfp4(x.to(d), axis=0, is_2d_block=True, use_sr=True, rand_bits=_u32dev(rt))
+    if fmt == "nvfp4":
+        qr, sr_ = O.quantize_nvfp4(x, 16, 0, True, None, rt)
+    else:
+        qr, sr_ = O.quantize_mxfp4(x, 32, 0, True, rt)
+    _same(qa.contiguous(), qr.contiguous(), "axis-0 codes")
+    _same(sa.contiguous(), sr_.contiguous(), "axis-0 scales")
 
 
 def test_mxfp4_2d_blocks_with_seeded_stochastic_rounding_match_the_reference_kernel():
@@ -395,11 +404,11 @@ def test_mxfp4_2d_blocks_with_seeded_stochastic_rounding_match_the_reference_ker
     from alto_b200 import mxfp4 as MX
     z = np.load(Path(__file__).resolve().parent / "golden" / "sr2d_vectors.npz")
     seed, off = [int(v) for v in z["philox_seed_offset"]]
-    for tag, shape in ast.literal_eval(str(z["meta"])):
+    for tag, shape, axis in ast.literal_eval(str(z["meta"])):
         x = torch.from_numpy(z[tag + "_x"].view(np.int16)).view(torch.bfloat16).reshape(shape).to(_dev())
-        q, s = MX.convert_to_mxfp4(x, is_2d_block=True, use_sr=True, philox_seed=seed, philox_offset=off)
-        _same(s, z[tag + "_s"], tag + " scales")
-        _same(q, z[tag + "_q"], tag + " codes")
+        q, s = MX.convert_to_mxfp4(x, axis=axis, is_2d_block=True, use_sr=True, philox_seed=seed, philox_offset=off)
+        _same(s.contiguous(), z[tag + "_s"], tag + " scales")
+        _same(q.contiguous(), z[tag + "_q"], tag + " codes")
 
 
 @pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4", "mxfp8"])

@@ -63,8 +63,13 @@ def test_dynamic_clip_bf16_mean_error_and_refusals():
     dq = MX.convert_from_mxfp4(q, s, torch.bfloat16, clip_mode="dynamic").cpu()
     dqo = O.dequantize_mxfp4(qo, so, torch.bfloat16, 32, -1, False, "dynamic")
     assert (dq.float() - dqo.float()).abs().mean().item() < 0.5
-    with pytest.raises(NotImplementedError):
-        MX.convert_to_mxfp4(x.cuda(), is_2d_block=True, clip_mode="dynamic")
+    # 2-D blocks: the statistics run over the 32 x 32 tile
+    q2, s2 = MX.convert_to_mxfp4(x.cuda(), is_2d_block=True, clip_mode="dynamic")
+    q2o, s2o = O.quantize_mxfp4(x, 32, -1, True, None, "dynamic", False)
+    assert (s2.cpu().int() - s2o.int()).abs().max().item() <= 1
+    dq2 = MX.convert_from_mxfp4(q2, s2, torch.bfloat16, is_2d_block=True, clip_mode="dynamic").cpu()
+    dq2o = O.dequantize_mxfp4(q2o, s2o, torch.bfloat16, 32, -1, True, "dynamic")
+    assert (dq2.float() - dq2o.float()).abs().mean().item() < 0.5
     with pytest.raises(ValueError):
         MX.convert_to_mxfp4(x.cuda(), clip_mode="sometimes")
 

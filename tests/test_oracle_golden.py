@@ -149,8 +149,11 @@ def test_2d_blocks_with_stochastic_rounding_match_the_reference_kernel():
     pins how its Philox words pair with the elements of a 2-D-block launch."""
     z, meta = _sr2d_cases()
     seed, off = [int(v) for v in z["philox_seed_offset"]]
-    for tag, shape in meta:
+    for tag, shape, axis in meta:
         x = torch.from_numpy(z[tag + "_x"].view(np.int16)).view(torch.bfloat16).reshape(shape)
-        q, s = O.quantize_mxfp4(x, 32, -1, True, O.reference_sr_planes(seed, off, shape[0], shape[1]))
-        assert np.array_equal(q.view(torch.uint8).numpy(), z[tag + "_q"]), tag
-        assert np.array_equal(s.numpy(), z[tag + "_s"]), tag
+        # words are indexed in the view with the quantisation axis last, leading dimensions flattened into rows
+        view = x.transpose(axis, -1).shape
+        planes = O.reference_sr_planes(seed, off, int(np.prod(view[:-1])), view[-1])
+        q, s = O.quantize_mxfp4(x, 32, axis, True, planes)
+        assert np.array_equal(q.contiguous().view(torch.uint8).numpy(), z[tag + "_q"]), tag
+        assert np.array_equal(s.contiguous().numpy(), z[tag + "_s"]), tag
