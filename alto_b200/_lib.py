@@ -48,6 +48,8 @@ EXPORTED_SYMBOLS = (
     "altob200_macro_block_scaling",
     "altob200_macro_block_descaling",
     "altob200_gather_rows",
+    "altob200_combine_rows",
+    "altob200_spread_rows",
     "altob200_swiglu_forward",
     "altob200_swiglu_backward",
     "altob200_dge_scale",
@@ -176,6 +178,10 @@ def _declare_more(lib):
     lib.altob200_rht_dense.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, i64, vp]
     lib.altob200_gather_rows.restype = C.c_int
     lib.altob200_gather_rows.argtypes = [vp, i64, i64, vp, i64, vp, vp]
+    lib.altob200_combine_rows.restype = C.c_int
+    lib.altob200_combine_rows.argtypes = [vp, i64, i64, vp, vp, i64, i32, vp, vp]
+    lib.altob200_spread_rows.restype = C.c_int
+    lib.altob200_spread_rows.argtypes = [vp, i64, i32, i64, vp, vp, i64, vp, vp]
     lib.altob200_swiglu_forward.restype = C.c_int
     lib.altob200_swiglu_forward.argtypes = [vp, i64, i64, i64, vp, vp]
     lib.altob200_swiglu_backward.restype = C.c_int
@@ -480,6 +486,32 @@ def gather_rows(src: torch.Tensor, index: torch.Tensor, out_rows: Optional[int] 
     out = torch.empty(n, src.shape[1], dtype=src.dtype, device=src.device)
     _check(lib().altob200_gather_rows(src.data_ptr(), src.shape[0], src.shape[1] * src.element_size(),
                                       index.data_ptr(), n, out.data_ptr(), _stream()), "altob200_gather_rows")
+    return out
+
+
+def combine_rows(rows: torch.Tensor, index: torch.Tensor, scores: Optional[torch.Tensor], tokens: int, k: int) -> torch.Tensor:
+    """out[t] = sum_j rows[index[t k + j]] * scores[t, j] (bf16 roundings of the tensor-op form); [tokens, D]."""
+    _require_cuda(rows, index, scores)
+    assert rows.dim() == 2 and rows.is_contiguous() and rows.dtype == torch.bfloat16
+    assert index.dtype == torch.int32 and index.is_contiguous() and index.numel() == tokens * k
+    assert scores is None or (scores.dtype == torch.bfloat16 and scores.is_contiguous() and scores.numel() == tokens * k)
+    out = torch.empty(tokens, rows.shape[1], dtype=rows.dtype, device=rows.device)
+    _check(lib().altob200_combine_rows(rows.data_ptr(), rows.shape[0], rows.shape[1] * 2, index.data_ptr(),
+                                       None if scores is None else scores.data_ptr(), tokens, k, out.data_ptr(),
+                                       _stream()), "altob200_combine_rows")
+    return out
+
+
+def spread_rows(grad_out: torch.Tensor, position: torch.Tensor, scores: Optional[torch.Tensor], k: int) -> torch.Tensor:
+    """grad_rows[r] = grad_out[position[r] // k] * scores.flat[position[r]], zero rows where position[r] < 0."""
+    _require_cuda(grad_out, position, scores)
+    assert grad_out.dim() == 2 and grad_out.is_contiguous() and grad_out.dtype == torch.bfloat16
+    assert position.dtype == torch.int32 and position.is_contiguous()
+    n = position.numel()
+    out = torch.empty(n, grad_out.shape[1], dtype=grad_out.dtype, device=grad_out.device)
+    _check(lib().altob200_spread_rows(grad_out.data_ptr(), grad_out.shape[0], k, grad_out.shape[1] * 2,
+                                      position.data_ptr(), None if scores is None else scores.data_ptr(), n,
+                                      out.data_ptr(), _stream()), "altob200_spread_rows")
     return out
 
 

@@ -176,7 +176,7 @@ class _ArmDxAllReduce(torch.autograd.Function):
 
 
 def column_sharded_linear(x: torch.Tensor, w_shard: torch.Tensor, linear_fn: Callable, group=None,
-                          overlap_dx_reduction: bool = True) -> torch.Tensor:
+                          overlap_dx_reduction: bool = False) -> torch.Tensor:
     """Y_r = linear_fn(x, W_r) with W_r this rank's [N / world, K] shard; x is replicated.
 
     Forward has no exchange (the concatenation of the Y_r along N is implicit in the sharding of
@@ -184,7 +184,8 @@ def column_sharded_linear(x: torch.Tensor, w_shard: torch.Tensor, linear_fn: Cal
     all-reduce of the bf16 partials.  With ``overlap_dx_reduction`` the all-reduce is issued
     asynchronously right after the dgrad GEMM and waited for at the end of the backward, so that it
     runs beside the second quantizer of dY and the wgrad GEMM (a linear function that is not one of
-    this package's simply ignores the request and the all-reduce happens after its backward).
+    this package's simply ignores the request and the all-reduce happens after its backward).  Off
+    by default: the persistent GEMM wants every SM, and a collective kernel beside it takes some.
     ``linear_fn(a, b)`` is one of the boundary functions with its recipe bound, e.g.
     ``lambda a, b: _to_mxfp8_then_scaled_mm(a, b, "e4m3", False, False, True)``."""
     if _world(group) == 1 or not overlap_dx_reduction or not x.is_cuda:
@@ -393,6 +394,33 @@ class _GatherRows(torch.autograd.Function):
         return L.gather_rows(grad.contiguous(), inverse), None, None
 
 
+class _CombineRows(torch.autograd.Function):
+    """out[t] = sum_j rows[index[t k + j]] * scores[t, j]: the last gather of the combine, the weighting
+    by the routing scores and the sum over the k routed rows of a token in one pass.  ``position`` is
+    the opposite map (row -> routed slot).  Gradients: rows by the spread kernel; scores (when they
+    require one) as the dot products of the gathered rows with the token's output gradient."""
+
+    @staticmethod
+    def forward(ctx, rows, index, position, scores, tokens, k):
+        rows = rows.contiguous()
+        sc = None if scores is None else scores.to(rows.dtype).contiguous()
+        ctx.save_for_backward(rows, index, position, sc)
+        ctx.tokens, ctx.k = tokens, k
+        ctx.scores_dtype = None if scores is None else scores.dtype
+        return L.combine_rows(rows, index, sc, tokens, k)
+
+    @staticmethod
+    def backward(ctx, grad):
+        rows, index, position, sc = ctx.saved_tensors
+        grad = grad.contiguous()
+        g_rows = L.spread_rows(grad, position, sc, ctx.k) if ctx.needs_input_grad[0] else None
+        g_scores = None
+        if sc is not None and ctx.needs_input_grad[3]:
+            routed = L.gather_rows(rows, index).view(ctx.tokens, ctx.k, -1)
+            g_scores = (routed.float() * grad.float().unsqueeze(1)).sum(-1).to(ctx.scores_dtype)
+        return g_rows, None, None, g_scores, None, None
+
+
 class _ReplicateSorted(torch.autograd.Function):
     """Routed rows sorted by expert: out[i] = x[order[i] // k].  A token feeds k routed rows, so the
     gradient gathers the routed rows back into token order and sums each token's k rows."""
@@ -406,7 +434,11 @@ class _ReplicateSorted(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         (inv_order,) = ctx.saved_tensors
-        g = L.gather_rows(grad.contiguous(), inv_order)
+        grad = grad.contiguous()
+        if grad.dtype == torch.bfloat16 and (grad.shape[-1] * 2) % 16 == 0:
+            # gather and sum over the k routed rows of a token in one pass
+            return L.combine_rows(grad, inv_order, None, inv_order.numel() // ctx.k, ctx.k), None, None, None
+        g = L.gather_rows(grad, inv_order)
         return g.view(-1, ctx.k, g.shape[-1]).sum(1).to(grad.dtype), None, None, None
 
 
@@ -496,7 +528,10 @@ class ExpertParallelDispatcher:
         rows = _GatherRows.apply(y_local, state.inverse, state.index)
         if self.world > 1:
             rows = _AllToAllRows.apply(rows, state.in_splits, state.out_splits, self.group)
-        # back to routed-row order (token-major, k minor): the inverse of the dispatch's sort
+        # back to routed-row order (token-major, k minor: the inverse of the dispatch's sort), weighted by
+        # the routing scores and summed over each token's k rows
+        if rows.dtype == torch.bfloat16 and (rows.shape[-1] * 2) % 16 == 0:
+            return _CombineRows.apply(rows, state.inv_order, state.order, scores, state.tokens, state.k)
         routed = _GatherRows.apply(rows, state.inv_order, state.order)
         routed = routed.view(state.tokens, state.k, routed.shape[-1])
         if scores is not None:

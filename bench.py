@@ -639,11 +639,13 @@ def run_sharded(dist, dev, rank, world):
     with torch.no_grad():
         col_ok = all_ok(torch.equal(ys, fn(xs.detach(), W[rank * nw:(rank + 1) * nw])))
 
-    def lin_step():
+    def lin_step(overlap=False):
         xs.grad = ws.grad = None
-        D.column_sharded_linear(xs, ws, fn).backward(dys)
+        D.column_sharded_linear(xs, ws, fn, overlap_dx_reduction=overlap).backward(dys)
 
     t_lin = step_time(lin_step)
+    # the same step with the dX all-reduce started right after the dgrad GEMM, beside the wgrad side
+    t_lin_overlap = step_time(lambda: lin_step(True))
     col_ok = col_ok and all_ok(bool(torch.isfinite(xs.grad).all() and torch.isfinite(ws.grad).all()))
     return {"scaling": "strong (total work fixed)",
             "ep_moe_ms": t_moe, "ep_moe_tflops": flop_moe / (t_moe * 1e-3) / 1e12, "ep_parity_ok": ep_ok,
@@ -651,6 +653,7 @@ def run_sharded(dist, dev, rank, world):
                          "fwd + dgrad + wgrad with dispatch and combine",
             "a2a_bytes": a2a_bytes,
             "col_ms": t_lin, "col_tflops": 3 * 2 * 8192 * 4096 * 4096 / (t_lin * 1e-3) / 1e12, "col_parity_ok": col_ok,
+            "col_ms_allreduce_beside_wgrad": t_lin_overlap,
             "allreduce_bytes": 8192 * 4096 * 2}
 
 

@@ -341,6 +341,24 @@ int altob200_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes, c
                          int64_t out_rows, void* dst, void* stream);
 
 /*
+ * Weighted combine of the k routed rows of every token, bf16 (the end of the MoE token path, same
+ * call sites as altob200_gather_rows):
+ *   out[t] = bf16( sum_j f32( bf16( rows[index[t k + j]] * scores[t k + j] ) ) ),  j = 0 .. k-1
+ * i.e. a row gather, the multiplication by the routing scores and the sum over k in one pass, with
+ * the roundings of the tensor-op form.  index: device int32 [tokens * k], entries outside
+ * [0, n_rows) contribute nothing; scores: device bf16 [tokens * k] or NULL (weights of one).
+ * altob200_spread_rows is its gradient with respect to the rows:
+ *   grad_rows[r] = bf16( grad_out[position[r] / k] * scores[position[r]] ),  zero rows where position[r] < 0,
+ * with position: device int32 [n_rows], the routed slot t k + j that row r feeds.
+ * row_bytes a multiple of 16, pointers 16-byte aligned.
+ */
+int altob200_combine_rows(const void* rows, int64_t n_rows, int64_t row_bytes, const int32_t* index,
+                          const void* scores, int64_t tokens, int32_t k, void* out, void* stream);
+int altob200_spread_rows(const void* grad_out, int64_t tokens, int32_t k, int64_t row_bytes,
+                         const int32_t* position, const void* scores, int64_t n_rows, void* grad_rows,
+                         void* stream);
+
+/*
  * SwiGLU between the two grouped GEMMs of an expert MLP, bf16.  h is [rows, 2H] with row stride
  * ld_h elements (gate in columns [0, H), up in [H, 2H)); forward writes out [rows, H] =
  * bf16(bf16(silu(gate)) * up); backward takes grad_out [rows, H] and writes grad_h [rows, 2H]
