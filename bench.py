@@ -435,12 +435,15 @@ def run_ours(args):
         NV.HadamardFactory.configure(block_size=16, randomized=True, dtype=torch.float32, seed=0)
 
     # ---- end to end through the public API with host buffers ----
-    xh = x.detach().cpu().pin_memory()
-    wh = w.detach().cpu().pin_memory()
-    dyh = dy.cpu().pin_memory()
-    yh = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
-    dxh = torch.empty(M, K, dtype=torch.bfloat16).pin_memory()
-    dwh = torch.empty(N, K, dtype=torch.bfloat16).pin_memory()
+    # one pinned buffer per direction (x | W | dY in, y | dX | dW out); the per-tensor views serve the serial leg
+    n_x, n_w, n_dy = x.numel(), w.numel(), dy.numel()
+    hin = torch.empty(n_x + n_w + n_dy, dtype=torch.bfloat16).pin_memory()
+    hout = torch.empty(n_dy + n_x + n_w, dtype=torch.bfloat16).pin_memory()
+    xh, wh, dyh = hin[:n_x].view(M, K), hin[n_x:n_x + n_w].view(N, K), hin[n_x + n_w:].view(M, N)
+    yh, dxh, dwh = hout[:n_dy].view(M, N), hout[n_dy:n_dy + n_x].view(M, K), hout[n_dy + n_x:].view(N, K)
+    xh.copy_(x.detach())
+    wh.copy_(w.detach())
+    dyh.copy_(dy)
 
     def e2e_step():
         with torch.no_grad():
@@ -472,12 +475,6 @@ def run_ours(args):
     # inputs from pinned host memory and its own three results back.  Each direction moves ONE
     # contiguous buffer per step (x | W | dY in, y | dX | dW out): with both directions busy one
     # 419 MB copy each way took 8.4 ms on this box, three copies each way 9.2 ms.
-    n_x, n_w, n_dy = x.numel(), w.numel(), dy.numel()
-    hin = torch.empty(n_x + n_w + n_dy, dtype=torch.bfloat16).pin_memory()
-    hin[:n_x].copy_(xh.view(-1))
-    hin[n_x:n_x + n_w].copy_(wh.view(-1))
-    hin[n_x + n_w:].copy_(dyh.view(-1))
-    hout = torch.empty(n_dy + n_x + n_w, dtype=torch.bfloat16).pin_memory()
     comp = torch.cuda.current_stream(dev)
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     din = [torch.empty(n_x + n_w + n_dy, dtype=torch.bfloat16, device=dev) for _ in range(2)]
