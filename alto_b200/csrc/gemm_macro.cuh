@@ -288,32 +288,38 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int ks = 0; ks < ti.k_stages; ++ks, ++it) {
           const int n_mma = (ks == ti.k_stages - 1) ? ti.last_mmas : 4;
           const int s = it % C::STAGES;
-          const long long t0 = PROF_NOW();
-          // operands and scales of the stage are in place and the chunk accumulators it writes are drained
-          if (named_barrier_or(1 + s, 64, false)) { alive = false; break; }
-          PROF_ADD(1, t0);
-          tc_fence_after();
           const uint32_t st4 = (smem_base + (uint32_t)s * C::STAGE_BYTES) >> 4;
           const uint32_t sfa_t = tmem_base + C::TMEM_SF_BASE + s * (C::SF_COLS_A + C::SF_COLS_B);
           const uint32_t sfb_t = sfa_t + C::SF_COLS_A;
           const uint32_t a_lo = st4 | 0x10000u;
           const uint32_t b_lo = a_lo + (C::A_BYTES >> 4);
-          const uint32_t buf0 = pc % C::P_BUFS, buf1 = (pc + 1) % C::P_BUFS;
-          if (elected) {
+          // The issuer is released per chunk (two MMAs), not per stage: a stage holds two chunks and only
+          // three chunk accumulators exist, so a release per stage would wait for the fold of the previous
+          // stage's FIRST chunk and leave one chunk of overlap instead of three.
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (j < n_mma) {
-                const uint32_t buf = (j < 2) ? buf0 : buf1;
-                tc_mma<KIND_MXF4>(tmem_base + buf * BN, desc_of(DESC_SW128_HI, a_lo + 2 * j),
-                                  desc_of(DESC_SW128_HI, b_lo + 2 * j), args.idesc[j], (uint32_t)(j & 1),
-                                  sfa_t + (j >> 1) * 4, sfb_t + (j >> 1) * 4);
-                if ((j & 1) == 1 || j == n_mma - 1) tc_commit(&p_full[buf]);
+          for (int h = 0; h < 2; ++h) {
+            if (2 * h >= n_mma) break;
+            const long long t0 = PROF_NOW();
+            // operands and scales of the stage are in place and this chunk's accumulator is drained
+            if (named_barrier_or(1 + 2 * s + h, 64, false)) { alive = false; break; }
+            PROF_ADD(1, t0);
+            tc_fence_after();
+            const uint32_t buf = pc % C::P_BUFS;
+            if (elected) {
+#pragma unroll
+              for (int j = 2 * h; j < 2 * h + 2; ++j) {
+                if (j < n_mma)
+                  tc_mma<KIND_MXF4>(tmem_base + buf * BN, desc_of(DESC_SW128_HI, a_lo + 2 * j),
+                                    desc_of(DESC_SW128_HI, b_lo + 2 * j), args.idesc[j], (uint32_t)(j & 1),
+                                    sfa_t + h * 4, sfb_t + h * 4);
               }
+              tc_commit(&p_full[buf]);
+              if (2 * h + 2 >= n_mma) tc_commit(&empty_bar[s]);
             }
-            tc_commit(&empty_bar[s]);
+            __syncwarp();
+            ++pc;
           }
-          __syncwarp();
-          pc += (uint32_t)((n_mma + 1) >> 1);
+          if (!alive) break;
         }
       }
       PROF_ADD(0, t_all);
@@ -332,10 +338,12 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const int s = it % C::STAGES;
           bool ok = mbar_wait(&full_bar[s], (it / C::STAGES) & 1, abort_flag, 23, args.wait_ns);
           ok = ok && mbar_wait(&sf_full[s], (it / C::STAGES) & 1, abort_flag, 25, args.wait_ns);
-          for (int c = 0; c < n_chunks; ++c, ++pc)
+          for (int c = 0; c < n_chunks && alive; ++c, ++pc) {
             ok = ok && mbar_wait(&p_empty[pc % C::P_BUFS], ((pc / C::P_BUFS) & 1) ^ 1, abort_flag, 22, args.wait_ns);
-          const bool failed = !__all_sync(0xFFFFFFFFu, ok);
-          if (named_barrier_or(1 + s, 64, failed)) { alive = false; break; }
+            const bool failed = !__all_sync(0xFFFFFFFFu, ok);
+            if (named_barrier_or(1 + 2 * s + c, 64, failed)) alive = false;
+          }
+          if (!alive) break;
         }
       }
     }
