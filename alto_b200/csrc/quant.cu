@@ -1134,9 +1134,9 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
 struct AmaxArgs {
   const void* x;
   int64_t rows, cols, ld;
-  uint32_t* amax_bits;   // [2], zero on entry
+  uint32_t* amax_bits;   // [2], written by the last block
   float* outer_scale;    // [2] or NULL
-  uint32_t* counter;     // scratch, zero on entry, zero on exit
+  uint32_t* counter;     // scratch [4]: ticket counter, running maxima; zero on entry, zero on exit
   RhtParams rht;
 };
 
@@ -1269,13 +1269,17 @@ __global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
       p = s_red[0][i] > p ? s_red[0][i] : p;
       h = s_red[1][i] > h ? s_red[1][i] : h;
     }
-    atomicMax(a.amax_bits, p);
-    if (RHT) atomicMax(a.amax_bits + 1, h);
+    // the running maxima live in the scratch words behind the counter, so that the result buffer needs
+    // no clearing launch in front of the kernel; the last block moves them out and leaves the scratch zero
+    atomicMax(a.counter + 1, p);
+    if (RHT) atomicMax(a.counter + 2, h);
     __threadfence();
     const uint32_t ticket = atomicAdd(a.counter, 1u);
     if (ticket == gridDim.x - 1) {
       __threadfence();
-      const uint32_t fp = atomicMax(a.amax_bits, 0u), fh = atomicMax(a.amax_bits + 1, 0u);
+      const uint32_t fp = atomicExch(a.counter + 1, 0u), fh = RHT ? atomicExch(a.counter + 2, 0u) : 0u;
+      a.amax_bits[0] = fp;
+      a.amax_bits[1] = fh;
       if (a.outer_scale != nullptr) {
         a.outer_scale[0] = outer_from_amax_bits(fp);
         if (RHT) a.outer_scale[1] = outer_from_amax_bits(fh);
@@ -1858,7 +1862,6 @@ int altob200_amax(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, i
   int rc = fill_rht(&a.rht, rht_n, rht_perm, rht_sign);
   if (rc != ALTOB200_OK) return rc;
   fill_rht_row_offsets(&a.rht, ld, esz);
-  ALTOB200_CUDA_CHECK(cudaMemsetAsync(amax_bits, 0, 2 * sizeof(uint32_t), st));
   const int64_t work = rht_n ? (rows / 16) * ceil_div(cols, 64) / 8 + 1
                              : rows * cols / (16 / esz) / 256 + 1;
   int64_t blocks = work;

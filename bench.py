@@ -472,9 +472,9 @@ def run_ours(args):
     # The same work with the copies of neighbouring steps overlapped, as a caller feeding batches from
     # host memory would run it: three streams and two sets of device buffers; step i computes while the
     # inputs of step i+1 arrive and the results of step i-1 leave.  Every step still copies its own
-    # inputs from pinned host memory and its own three results back.  Each direction moves ONE
-    # contiguous buffer per step (x | W | dY in, y | dX | dW out): with both directions busy one
-    # 419 MB copy each way took 8.4 ms on this box, three copies each way 9.2 ms.
+    # inputs from pinned host memory and its own three results back.  Each direction moves one
+    # contiguous buffer per step (x | W | dY in, y | dX | dW out); --e2e-copies 3 moves the three
+    # tensors separately (no measurable difference on one box: the leg is bound by the PCIe link).
     comp = torch.cuda.current_stream(dev)
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     din = [torch.empty(n_x + n_w + n_dy, dtype=torch.bfloat16, device=dev) for _ in range(2)]
@@ -491,7 +491,11 @@ def run_ours(args):
             with torch.cuda.stream(s_in):
                 if consumed[b] is not None:
                     s_in.wait_event(consumed[b])
-                din[b].copy_(hin, non_blocking=True)
+                if args.e2e_copies == 1:
+                    din[b].copy_(hin, non_blocking=True)
+                else:   # one copy per tensor, for comparison on the same box
+                    for lo, hi in ((0, n_x), (n_x, n_x + n_w), (n_x + n_w, n_x + n_w + n_dy)):
+                        din[b][lo:hi].copy_(hin[lo:hi], non_blocking=True)
                 arrived = torch.cuda.Event()
                 arrived.record(s_in)
             comp.wait_event(arrived)
@@ -511,7 +515,11 @@ def run_ours(args):
             consumed[b] = done
             with torch.cuda.stream(s_out):
                 s_out.wait_event(done)
-                hout.copy_(o, non_blocking=True)
+                if args.e2e_copies == 1:
+                    hout.copy_(o, non_blocking=True)
+                else:
+                    for lo, hi in ((0, n_dy), (n_dy, n_dy + n_x), (n_dy + n_x, n_dy + n_x + n_w)):
+                        hout[lo:hi].copy_(o[lo:hi], non_blocking=True)
                 gone = torch.cuda.Event()
                 gone.record(s_out)
                 left[b] = gone
@@ -664,6 +672,8 @@ def main():
     ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long sustained leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the MXFP4 recipes at the same shape")
     ap.add_argument("--no-sharded", action="store_true", help="N > 1: skip the expert-parallel and column-sharded runs")
+    ap.add_argument("--e2e-copies", type=int, default=1, choices=[1, 3],
+                    help="host<->device copies per direction and step in the end-to-end leg (1: one contiguous buffer)")
     ap.add_argument("--recipe", default="nvfp4", choices=["nvfp4", "mxfp4", "mxfp4_two_level"],
                     help="nvfp4 is the headline; the others exist for profiling captures of their kernels")
     ap.add_argument("--shape", default=None, metavar="M,K,N",

@@ -137,7 +137,10 @@ typedef struct altob200_quant_params {
  *  outer_scale[i] <- max(amax_i / (448 * 6), 1e-30) for i in {0,1} when non-NULL
  *
  * `scratch` is device memory of at least ALTOB200_AMAX_SCRATCH_BYTES that must be
- * zero before the first call; the kernel leaves it zeroed again.
+ * zero before the first call; the kernel leaves it zeroed again (a ticket counter and the
+ * running maxima live there, so amax_bits need not be cleared and no launch precedes the
+ * kernel; amax_bits[1] is written as 0 without a transform).  Calls that share a scratch
+ * buffer must be ordered on one stream.
  */
 #define ALTOB200_AMAX_SCRATCH_BYTES 16
 int altob200_amax(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, int64_t ld,
