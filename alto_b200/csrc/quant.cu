@@ -511,8 +511,10 @@ __global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a)
   const OuterScale os = make_outer_scale((!F::MX) && a.outer != nullptr, a.outer);
   const int64_t half_rows = a.rows >> 1;
   // rows of the periodic random table for this lane's two columns (rows of the axis-last view)
-  const uint32_t tile_row0 = a.tile_rows != 0 ? (uint32_t)((uint64_t)c % (uint64_t)a.tile_rows) : 0u;
-  const uint32_t tile_row1 = a.tile_rows != 0 ? (uint32_t)((uint64_t)(c + 1) % (uint64_t)a.tile_rows) : 0u;
+  // (32-bit arithmetic: with a periodic table the host refuses extents of 2^32 and more; a 64-bit
+  // modulo is ~70 instructions, several per thread of a CTA that handles 64 elements per thread)
+  const uint32_t tile_row0 = a.tile_rows != 0 ? (uint32_t)c % (uint32_t)a.tile_rows : 0u;
+  const uint32_t tile_row1 = a.tile_rows != 0 ? (tile_row0 + 1u == (uint32_t)a.tile_rows ? 0u : tile_row0 + 1u) : 0u;
 
   // bf16: the words of every iteration are requested before the first is used (slot k <- row pinv[k]
   // when the transform is on; the identity otherwise), so the second block's loads fly under the
@@ -663,7 +665,7 @@ __global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a)
             // periodic table: the 8 pairs of these 16 rows are 8 consecutive, 32-byte aligned words of
             // one table row in each plane (tile_pairs is a multiple of 8) -> four 16-byte loads per column
             const uint32_t tp = (uint32_t)a.tile_pairs;
-            const uint32_t base = (uint32_t)((uint64_t)((mb + 16 * h) >> 1) % tp);
+            const uint32_t base = (uint32_t)((mb + 16 * h) >> 1) % tp;
             const uint32_t plane = (uint32_t)a.tile_rows * tp;
             const uint32_t* t0 = a.rand_bits + tile_row0 * tp + base;
             const uint32_t* t1 = a.rand_bits + tile_row1 * tp + base;
@@ -1002,7 +1004,10 @@ __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
         // the lane's 4 column pairs are 4 consecutive, 16-byte aligned words of each plane
         const bool tiled = a.tile_rows != 0;
         const int64_t row = rows_before + row0 + i;  // row of the flattened view over the batch
-        const int64_t rr = tiled ? (int64_t)((uint64_t)row % (uint64_t)a.tile_rows) : row;
+        // (a 64-bit modulo only where the flattened row index needs it: it costs ~70 instructions)
+        const int64_t rr = !tiled ? row
+                           : ((uint64_t)row >> 32) == 0 ? (int64_t)((uint32_t)row % (uint32_t)a.tile_rows)
+                                                        : (int64_t)((uint64_t)row % (uint64_t)a.tile_rows);
         const int64_t pp = tiled ? (int64_t)((uint32_t)(col0 >> 1) % (uint32_t)a.tile_pairs) : (col0 >> 1);
         const int64_t pitch = tiled ? a.tile_pairs : (a.cols >> 1);
         const int64_t plane = tiled ? a.tile_rows * a.tile_pairs : a.batch * a.rows * (a.cols >> 1);
@@ -1782,6 +1787,9 @@ int altob200_quantize_colwise(const void* x, int64_t rows, int64_t cols, int64_t
   a.outer = p->outer_scale; a.rand_bits = p->rand_bits;
   a.tile_rows = p->rand_tile_rows; a.tile_pairs = p->rand_tile_pairs;
   if ((a.tile_rows != 0) != (a.tile_pairs != 0) || a.tile_rows < 0 || a.tile_pairs < 0) return ALTOB200_EINVAL_SHAPE;
+  if (a.tile_rows != 0 && (rows >= (1ll << 32) || cols >= (1ll << 32) || a.tile_rows >= (1ll << 32) ||
+                           a.tile_pairs >= (1ll << 32)))
+    return ALTOB200_ELIMIT;
   a.philox_seed = p->philox_seed; a.philox_offset = p->philox_offset;
   philox_make_keys(p->philox_seed, &a.pk);
   int rc = fill_rht(&a.rht, p->rht_n, p->rht_perm, p->rht_sign);
@@ -1834,6 +1842,7 @@ int altob200_quantize_2d_batched(const void* w, int64_t batch, int64_t batch_str
   a.rand_bits = p->rand_bits; a.tile_rows = p->rand_tile_rows; a.tile_pairs = p->rand_tile_pairs;
   if ((a.tile_rows != 0) != (a.tile_pairs != 0) || a.tile_rows < 0 || a.tile_pairs < 0 || (a.tile_pairs & 3) != 0)
     return ALTOB200_EINVAL_SHAPE;
+  if (a.tile_rows >= (1ll << 32) || a.tile_pairs >= (1ll << 32)) return ALTOB200_ELIMIT;
   int rc = fill_mx_opts(&a.mx, p, true);
   if (rc != ALTOB200_OK) return rc;
   // padding entries of the packed layouts are zero (the kernel does not visit them)
