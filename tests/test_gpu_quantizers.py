@@ -166,6 +166,16 @@ def test_dense_hadamard_kernel(n):
     yf = torch.empty_like(xf)
     L.rht_dense(xf, yf, W.to(_dev()))
     assert torch.allclose(yf.cpu(), O.rht_apply(xf.cpu(), W), rtol=1e-6, atol=1e-6)
+    # bf16 at the shapes that take the tensor-core form of the 32-point transform (rows of whole 16-byte
+    # chunks; a last column tile that is not full; in place) and at one that does not (odd width)
+    for shape in ((96, 264), (64, 2880), (32, 8), (64, 36)):
+        xb = reference_data(shape, torch.bfloat16, 4321 + shape[1]).to(_dev())
+        yb = torch.empty_like(xb)
+        L.rht_dense(xb, yb, W.to(_dev()))
+        want = O.rht_apply(xb.cpu(), W)
+        assert torch.equal(yb.cpu().view(torch.int16), want.view(torch.int16)), shape
+        L.rht_dense(xb, xb, W.to(_dev()))
+        assert torch.equal(xb, yb), shape
     HadamardFactory.configure(block_size=16, seed=0)
 
 
