@@ -403,6 +403,7 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const bool out_bf16 = args.out_bf16 != 0;
     const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + cq * FC;
     uint32_t pc = 0, store_it = 0;
+    uint32_t p_buf = 0, p_phase = 0;                  // position in the ring of chunk accumulators, its phase
     bool alive = true;
     PROF_DECL;
     const long long t_all = PROF_NOW();
@@ -425,22 +426,27 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int nch = mt.n_chunks;
         uint32_t ca = __ldg(pa), cb = __ldg(pb);
         uint32_t p[FC];   // chunk accumulator words of this thread's row
-        for (int c = 0; c < nch && alive; ++c) {
-          if (ALTOB200_DBG(args, 256)) { ++pc; continue; }
-          const int buf = pc % C::P_BUFS;
+        // The loop body is what bounds the kernel (instruction issue of sixteen of these warps), so the
+        // ring position and its phase are carried instead of divided out, the code pointers advance by
+        // their strides, and the two barrier addresses are 32-bit shared-memory addresses.
+        const int64_t sa = margs.ma.chunk_stride, sb = margs.mb.chunk_stride;
+        for (int c = 0; c < nch; ++c) {
+          if (ALTOB200_DBG(args, 256)) continue;
           long long t0 = PROF_NOW();
-          alive = mbar_wait(&p_full[buf], (pc / C::P_BUFS) & 1, abort_flag, 24, args.wait_ns);
+          alive = mbar_wait(&p_full[p_buf], p_phase, abort_flag, 24, args.wait_ns);
           PROF_ADD(2, t0);
           if (!alive) break;
           tc_fence_after();
           if (warp == 8 && lane == 0) { PROF_TRACE(3, pc, 0); }
-          tc_ld32(t_row + buf * BN, p);
+          tc_ld32(t_row + p_buf * BN, p);
           // under the load: this chunk's factors, the next chunk's codes
           t0 = PROF_NOW();
           const float ra = rcp_tab[ca], rb = rcp_tab[cb];
+          pa += sa;
+          pb += sb;
           if (c + 1 < nch) {
-            ca = __ldg(pa + (int64_t)(c + 1) * margs.ma.chunk_stride);
-            cb = __ldg(pb + (int64_t)(c + 1) * margs.mb.chunk_stride);
+            ca = __ldg(pa);
+            cb = __ldg(pb);
           }
           float* fb = fb_warp + (c & 1) * FC;
           if (!b_uniform) {
@@ -454,9 +460,13 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           t0 = PROF_NOW();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&p_empty[buf]);
+          if (lane == 0) mbar_arrive(&p_empty[p_buf]);
           if (warp == 8 && lane == 0) { PROF_TRACE(3, pc, 1); }
           ++pc;
+          if (++p_buf == C::P_BUFS) {
+            p_buf = 0;
+            p_phase ^= 1u;
+          }
           PROF_ADD(7, t0);
           if (ALTOB200_DBG(args, 64)) continue;   // profiling builds only: chunks are handed straight back
           t0 = PROF_NOW();
