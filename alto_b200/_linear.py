@@ -385,6 +385,7 @@ def linear_backward(ctx, grad_output):
         main.wait_event(ctx.xm_ready)
     need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
     grad_inputs = grad_weights = None
+    dx_hook = take_dx_ready_hook()      # always taken here, so that an armed hook never outlives this backward
     plain = not ctx.use_uos and ctx.clip_mode == "none"
     if OVERLAP and not ctx.use_2dblock_x and need_dx and need_dw and ctx.dense_transform is None and plain:
         fmt, rht = ctx.fmt, ctx.rht
@@ -409,7 +410,6 @@ def linear_backward(ctx, grad_output):
         if ctx.use_dge:
             grad_weights = dge.apply_to_weight_grad(grad_weights, w_t.codes)
         return grad_inputs, grad_weights
-    dx_hook = take_dx_ready_hook()
     if dx_hook is not None and need_dx and not ctx.use_2dblock_x:
         # dgrad first, with only the operand it needs; the hook (an asynchronous all-reduce of dX) then runs
         # beside the second quantizer of dY and the wgrad GEMM.  Random words are drawn in the usual order.

@@ -134,6 +134,7 @@ def linear_forward(ctx, x, weight, use_2dblock_x: bool, use_2dblock_w: bool, use
 
 
 def linear_backward(ctx, grad_output):
+    E.take_dx_ready_hook()   # this backward does not hand dX over early; a caller's all-reduce follows it
     M, K, N = ctx.dims
     x_m, w_t = _load_macro(ctx, (K, M), (K, N))
     original_shape = grad_output.shape
