@@ -219,6 +219,7 @@ gemm_macro_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();   // set-up done; global memory from here on (programmatic dependent launch)
 
   if (warp < 4) {
     setmaxnreg_dec<C::REGS_SMALL>();

@@ -559,6 +559,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // barriers, tensor memory and the zeroed scale staging are set up: from here on global memory is read
+  // and written, which has to wait for the kernel in front of this one (programmatic dependent launch)
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
@@ -924,6 +927,9 @@ gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const _
   cluster_sync_all();   // the peer's barriers are initialised before anything can arrive on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // barriers, tensor memory and the zeroed scale staging are set up: from here on global memory is read
+  // and written, which has to wait for the kernel in front of this one (programmatic dependent launch)
+  grid_dependency_wait();
 
   if (warp < 4) {
   setmaxnreg_dec<C::REGS_SMALL>();
@@ -1352,8 +1358,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   const int64_t tiles = ceil_div(args.M, BM) * ceil_div(args.N, BN) * (args.k_offs != nullptr ? args.num_batches : 1);
   int64_t grid = sm_count_gemm();
   if (grid > tiles) grid = tiles;
-  gemm_blockscaled_kernel<KIND, BN><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, td, args);
-  return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
+  const cudaError_t e = launch_after(gemm_blockscaled_kernel<KIND, BN>, dim3((unsigned)grid), dim3(NUM_THREADS), C::SMEM_BYTES, st,
+                                     ta, tb, td, args);
+  return e == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 
 // CTA-pair kernel: clusters of two CTAs, as many clusters as the device can hold at once.
@@ -1365,16 +1372,18 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
   const int dev = current_device();
   int max_clusters = dev >= 0 ? clusters_of[dev].load(std::memory_order_relaxed) : 0;
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see launch_after()
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.blockDim = dim3(NUM_THREADS_PAIR, 1, 1);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = st;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   if (max_clusters == 0) {
     ALTOB200_CUDA_CHECK(cudaFuncSetAttribute(gemm_blockscaled_pair_kernel<KIND, OUT_BF16, BN_>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -1531,7 +1540,7 @@ static int launch_gemm_macro(const CUtensorMap& ta, const CUtensorMap& tb, const
   const int64_t tiles = ceil_div(a.M, BM) * ceil_div(a.N, C::BN) * (a.k_offs != nullptr ? a.num_batches : 1);
   int64_t grid = sm_count_gemm();
   if (grid > tiles) grid = tiles;
-  gemm_macro_kernel<<<(unsigned)grid, NUM_THREADS_MACRO, C::SMEM_BYTES, st>>>(ta, tb, td, margs);
+  (void)launch_after(gemm_macro_kernel, dim3((unsigned)grid), dim3(NUM_THREADS_MACRO), C::SMEM_BYTES, st, ta, tb, td, margs);
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 

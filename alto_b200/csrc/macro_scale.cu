@@ -86,6 +86,7 @@ __device__ __forceinline__ float warp_max_f32(float v) {
 // ---- 1D: one warp per (row, 128-column block) ----
 template <bool IN_BF16, bool DESCALE>
 __global__ void __launch_bounds__(256) macro_scale_1d_kernel(MacroArgs a) {
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int64_t n_tasks = a.batch * a.rows * a.nblk;
   const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = (int64_t)gridDim.x * 8;
@@ -117,6 +118,7 @@ __global__ void __launch_bounds__(256) macro_scale_1d_kernel(MacroArgs a) {
 // ---- 1D, rows of a multiple of 8 elements: a warp task is 4 rows x 256 columns ----
 template <bool IN_BF16, bool DESCALE>
 __global__ void __launch_bounds__(256) macro_scale_1d_wide_kernel(MacroArgs a) {
+  grid_dependency_wait();
   constexpr int R = 4;
   const int lane = threadIdx.x & 31;
   const int64_t n_rows = a.batch * a.rows;
@@ -192,6 +194,7 @@ __global__ void __launch_bounds__(256) macro_scale_1d_wide_kernel(MacroArgs a) {
 // 128 run down the rows, the reference's axis=0 on a matrix); scale is [batch, cols, ceil(rows/128)].
 template <bool IN_BF16, bool DESCALE, bool COLS>
 __global__ void __launch_bounds__(256) macro_scale_tile_kernel(MacroArgs a) {
+  grid_dependency_wait();
   __shared__ float s_max[COLS ? 8 * 128 : 8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t b = blockIdx.z, tm = blockIdx.y, tn = blockIdx.x;
@@ -265,6 +268,7 @@ __global__ void __launch_bounds__(256) macro_scale_tile_kernel(MacroArgs a) {
 // stream, and what limits it is the number of bytes in flight.
 template <bool DESCALE, bool COLS>
 __global__ void __launch_bounds__(256, 4) macro_scale_tile_bf16_kernel(MacroArgs a) {
+  grid_dependency_wait();
   __shared__ __align__(16) uint2 s_max[COLS ? 8 * 32 : 8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t b = blockIdx.z, tm = blockIdx.y, tn = blockIdx.x;
@@ -351,21 +355,21 @@ static void launch_mode(const MacroArgs& a, int32_t mode, cudaStream_t st) {
     if (a.wide) {
       int64_t blocks = ceil_div(ceil_div(a.batch * a.rows, 4) * ceil_div(a.cols, 256), 8);
       if (blocks > 148 * 8) blocks = 148 * 8;
-      macro_scale_1d_wide_kernel<BF, DESCALE><<<(unsigned)blocks, 256, 0, st>>>(a);
+      (void)launch_after(macro_scale_1d_wide_kernel<BF, DESCALE>, dim3((unsigned)blocks), dim3(256), 0, st, a);
       return;
     }
     int64_t blocks = ceil_div(a.batch * a.rows * a.nblk, 8);
     if (blocks > 148 * 16) blocks = 148 * 16;
-    macro_scale_1d_kernel<BF, DESCALE><<<(unsigned)blocks, 256, 0, st>>>(a);
+    (void)launch_after(macro_scale_1d_kernel<BF, DESCALE>, dim3((unsigned)blocks), dim3(256), 0, st, a);
   } else {
     dim3 grid((unsigned)a.nblk, (unsigned)ceil_div(a.rows, 128), (unsigned)a.batch);
     if (BF && a.vec) {
-      if (mode == 1) macro_scale_tile_bf16_kernel<DESCALE, false><<<grid, 256, 0, st>>>(a);
-      else macro_scale_tile_bf16_kernel<DESCALE, true><<<grid, 256, 0, st>>>(a);
+      if (mode == 1) (void)launch_after(macro_scale_tile_bf16_kernel<DESCALE, false>, dim3(grid), dim3(256), 0, st, a);
+      else (void)launch_after(macro_scale_tile_bf16_kernel<DESCALE, true>, dim3(grid), dim3(256), 0, st, a);
       return;
     }
-    if (mode == 1) macro_scale_tile_kernel<BF, DESCALE, false><<<grid, 256, 0, st>>>(a);
-    else macro_scale_tile_kernel<BF, DESCALE, true><<<grid, 256, 0, st>>>(a);
+    if (mode == 1) (void)launch_after(macro_scale_tile_kernel<BF, DESCALE, false>, dim3(grid), dim3(256), 0, st, a);
+    else (void)launch_after(macro_scale_tile_kernel<BF, DESCALE, true>, dim3(grid), dim3(256), 0, st, a);
   }
 }
 

@@ -261,6 +261,7 @@ constexpr int ROW_R = 4;
 
 template <int FMT, bool IN_BF16, int ROUND>
 __global__ void __launch_bounds__(256, 3) quantize_rowwise_kernel(RowwiseArgs a) {
+  grid_dependency_wait();
   using F = Fmt<FMT>;
   constexpr int LPB = F::B / 16;  // lanes per block
   constexpr int ESZ = IN_BF16 ? 2 : 4;
@@ -489,6 +490,7 @@ constexpr int COL_TN = 64;   // columns per CTA tile
 
 template <int FMT, bool IN_BF16, int ROUND, bool RHT>
 __global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a) {
+  grid_dependency_wait();
   using F = Fmt<FMT>;
   constexpr int B = F::B;
   constexpr int NT = COL_NT;   // threads per CTA
@@ -882,6 +884,7 @@ __device__ __forceinline__ void transpose4x4_bytes(const uint32_t* in, uint32_t*
 // receives 8 (FP4) or 16 (FP8) contiguous bytes per lane, 32 contiguous bytes per warp and column.
 template <int FMT, bool IN_BF16, int ROUND, bool BATCHED>
 __global__ void __launch_bounds__(256) quantize_2d_kernel(Quant2dArgs a) {
+  grid_dependency_wait();
   using F = Fmt<FMT>;
   constexpr int B = F::B;
   constexpr int LC = B / 2;          // lanes across columns: 8 columns each, 4 block columns per warp
@@ -1165,6 +1168,7 @@ __device__ __forceinline__ float outer_from_amax_bits(uint32_t bits) {
 
 template <bool IN_BF16, bool RHT>
 __global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
+  grid_dependency_wait();
   __shared__ uint32_t s_red[2][8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t am_plain = 0, am_rht = 0;
@@ -1402,6 +1406,7 @@ struct DequantArgs {
 
 template <int FMT, bool OUT_BF16>
 __global__ void __launch_bounds__(256) dequantize_kernel(DequantArgs a) {
+  grid_dependency_wait();
   using F = Fmt<FMT>;
   const int64_t segs_per_row = a.cols >> 4;
   const int64_t total = a.rows * segs_per_row;
@@ -1470,6 +1475,7 @@ struct RhtArgs {
 
 template <bool IN_BF16>
 __global__ void __launch_bounds__(256) rht_kernel(RhtArgs a) {
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t groups = a.rows >> 4;
   const int64_t col_tiles = (a.cols + 63) >> 6;
@@ -1575,13 +1581,11 @@ static int launch_rowwise(const RowwiseArgs& a, int rounding, cudaStream_t st) {
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   if (rounding == ALTOB200_ROUND_RTN)
-    quantize_rowwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN><<<(unsigned)blocks, 256, 0, st>>>(a);
+    (void)launch_after(quantize_rowwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN>, dim3((unsigned)blocks), dim3(256), 0, st, a);
   else if (rounding == ALTOB200_ROUND_SR_BITS && Fmt<FMT>::FP4)
-    quantize_rowwise_kernel<FMT, IN_BF16, Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN>
-        <<<(unsigned)blocks, 256, 0, st>>>(a);
+    (void)launch_after(quantize_rowwise_kernel<FMT, IN_BF16, Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN>, dim3((unsigned)blocks), dim3(256), 0, st, a);
   else if (rounding == ALTOB200_ROUND_SR_PHILOX && Fmt<FMT>::FP4)
-    quantize_rowwise_kernel<FMT, IN_BF16, Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_PHILOX : ALTOB200_ROUND_RTN>
-        <<<(unsigned)blocks, 256, 0, st>>>(a);
+    (void)launch_after(quantize_rowwise_kernel<FMT, IN_BF16, Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_PHILOX : ALTOB200_ROUND_RTN>, dim3((unsigned)blocks), dim3(256), 0, st, a);
   else
     return ALTOB200_EUNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
@@ -1595,20 +1599,20 @@ static int launch_colwise(const ColwiseArgs& a, int rounding, cudaStream_t st) {
   if (rounding == ALTOB200_ROUND_RTN) {
     constexpr int NT = COL_NT;
     const dim3 grid(gx, (unsigned)ceil_div(a.rows, NT));
-    if (rht) quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, Fmt<FMT>::FP4><<<grid, NT, 0, st>>>(a);
-    else quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, false><<<grid, NT, 0, st>>>(a);
+    if (rht) (void)launch_after(quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, Fmt<FMT>::FP4>, dim3(grid), dim3(NT), 0, st, a);
+    else (void)launch_after(quantize_colwise_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, false>, dim3(grid), dim3(NT), 0, st, a);
   } else if (rounding == ALTOB200_ROUND_SR_BITS) {
     constexpr int R = Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN;
     constexpr int NT = COL_NT;
     const dim3 grid(gx, (unsigned)ceil_div(a.rows, NT));
-    if (rht) quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4><<<grid, NT, 0, st>>>(a);
-    else quantize_colwise_kernel<FMT, IN_BF16, R, false><<<grid, NT, 0, st>>>(a);
+    if (rht) (void)launch_after(quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4>, dim3(grid), dim3(NT), 0, st, a);
+    else (void)launch_after(quantize_colwise_kernel<FMT, IN_BF16, R, false>, dim3(grid), dim3(NT), 0, st, a);
   } else if (rounding == ALTOB200_ROUND_SR_PHILOX) {
     constexpr int R = Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_PHILOX : ALTOB200_ROUND_RTN;
     constexpr int NT = COL_NT;
     const dim3 grid(gx, (unsigned)ceil_div(a.rows, NT));
-    if (rht) quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4><<<grid, NT, 0, st>>>(a);
-    else quantize_colwise_kernel<FMT, IN_BF16, R, false><<<grid, NT, 0, st>>>(a);
+    if (rht) (void)launch_after(quantize_colwise_kernel<FMT, IN_BF16, R, Fmt<FMT>::FP4>, dim3(grid), dim3(NT), 0, st, a);
+    else (void)launch_after(quantize_colwise_kernel<FMT, IN_BF16, R, false>, dim3(grid), dim3(NT), 0, st, a);
   } else {
     return ALTOB200_EUNSUPPORTED;
   }
@@ -1624,11 +1628,11 @@ static int launch_2d(const Quant2dArgs& a, int rounding, cudaStream_t st) {
   constexpr int SR = Fmt<FMT>::FP4 ? ALTOB200_ROUND_SR_BITS : ALTOB200_ROUND_RTN;
   const bool batched = a.batch > 1;
   if (rounding == ALTOB200_ROUND_RTN) {
-    if (batched) quantize_2d_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, true><<<blocks, 256, 0, st>>>(a);
-    else quantize_2d_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, false><<<blocks, 256, 0, st>>>(a);
+    if (batched) (void)launch_after(quantize_2d_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, true>, dim3(blocks), dim3(256), 0, st, a);
+    else (void)launch_after(quantize_2d_kernel<FMT, IN_BF16, ALTOB200_ROUND_RTN, false>, dim3(blocks), dim3(256), 0, st, a);
   } else if (rounding == ALTOB200_ROUND_SR_BITS && Fmt<FMT>::FP4) {
-    if (batched) quantize_2d_kernel<FMT, IN_BF16, SR, true><<<blocks, 256, 0, st>>>(a);
-    else quantize_2d_kernel<FMT, IN_BF16, SR, false><<<blocks, 256, 0, st>>>(a);
+    if (batched) (void)launch_after(quantize_2d_kernel<FMT, IN_BF16, SR, true>, dim3(blocks), dim3(256), 0, st, a);
+    else (void)launch_after(quantize_2d_kernel<FMT, IN_BF16, SR, false>, dim3(blocks), dim3(256), 0, st, a);
   } else {
     return ALTOB200_EUNSUPPORTED;
   }
@@ -1672,6 +1676,7 @@ static int clear_packed_if_padded(void* buf, int64_t rows, int64_t ncols, cudaSt
 // it periodically.
 __global__ void __launch_bounds__(256) philox_tile_kernel(uint32_t* out, int64_t tile_rows, int64_t tile_pairs,
                                                           uint32_t offset, PhiloxKeys pk) {
+  grid_dependency_wait();
   const int64_t n = tile_rows * tile_pairs;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     uint32_t o[4];
@@ -1727,7 +1732,7 @@ int altob200_philox_tile(uint64_t seed, uint64_t offset, int64_t tile_rows, int6
   const int64_t n = tile_rows * tile_pairs;
   int64_t blocks = ceil_div(n, 256);
   if (blocks > 148) blocks = 148;
-  philox_tile_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(out, tile_rows, tile_pairs, (uint32_t)offset,
+  (void)launch_after(philox_tile_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, out, tile_rows, tile_pairs, (uint32_t)offset,
                                                                         pk);
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
@@ -1878,11 +1883,11 @@ int altob200_amax(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, i
   if (blocks > cap) blocks = cap;
   const bool bf = in_dtype == ALTOB200_DT_BF16;
   if (rht_n) {
-    if (bf) amax_kernel<true, true><<<(unsigned)blocks, 256, 0, st>>>(a);
-    else amax_kernel<false, true><<<(unsigned)blocks, 256, 0, st>>>(a);
+    if (bf) (void)launch_after(amax_kernel<true, true>, dim3((unsigned)blocks), dim3(256), 0, st, a);
+    else (void)launch_after(amax_kernel<false, true>, dim3((unsigned)blocks), dim3(256), 0, st, a);
   } else {
-    if (bf) amax_kernel<true, false><<<(unsigned)blocks, 256, 0, st>>>(a);
-    else amax_kernel<false, false><<<(unsigned)blocks, 256, 0, st>>>(a);
+    if (bf) (void)launch_after(amax_kernel<true, false>, dim3((unsigned)blocks), dim3(256), 0, st, a);
+    else (void)launch_after(amax_kernel<false, false>, dim3((unsigned)blocks), dim3(256), 0, st, a);
   }
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
@@ -1907,8 +1912,8 @@ int altob200_dequantize(const void* codes, const void* scale_plain, const float*
   if (blocks > cap) blocks = cap;
   const bool bf = out_dtype == ALTOB200_DT_BF16;
 #define LAUNCH_DQ(F)                                                              \
-  if (bf) dequantize_kernel<F, true><<<(unsigned)blocks, 256, 0, st>>>(a);        \
-  else dequantize_kernel<F, false><<<(unsigned)blocks, 256, 0, st>>>(a);          \
+  if (bf) (void)launch_after(dequantize_kernel<F, true>, dim3((unsigned)blocks), dim3(256), 0, st, a);        \
+  else (void)launch_after(dequantize_kernel<F, false>, dim3((unsigned)blocks), dim3(256), 0, st, a);          \
   break;
   switch (format) {
     case ALTOB200_FMT_NVFP4: LAUNCH_DQ(ALTOB200_FMT_NVFP4)
@@ -1939,8 +1944,8 @@ int altob200_rht(const void* x, int32_t dtype, int64_t rows, int64_t cols, int64
   int64_t blocks = (rows / 16) * ceil_div(cols, 64) / 8 + 1;
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  if (dtype == ALTOB200_DT_BF16) rht_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(a);
-  else rht_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(a);
+  if (dtype == ALTOB200_DT_BF16) (void)launch_after(rht_kernel<true>, dim3((unsigned)blocks), dim3(256), 0, st, a);
+  else (void)launch_after(rht_kernel<false>, dim3((unsigned)blocks), dim3(256), 0, st, a);
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
 

@@ -30,6 +30,7 @@ struct RhtDenseArgs {
 
 template <int N, bool IN_BF16>
 __global__ void __launch_bounds__(128) rht_dense_kernel(RhtDenseArgs a) {
+  grid_dependency_wait();
   __shared__ __align__(16) float s_w[N * N];
   for (int i = threadIdx.x; i < N * N; i += 128) s_w[i] = a.w[i];
   __syncthreads();
@@ -107,6 +108,7 @@ __device__ __forceinline__ uint32_t pack_bf16_exact(float lo, float hi) {
 }
 
 __global__ void __launch_bounds__(128) rht32_mma_kernel(RhtDenseArgs a) {
+  grid_dependency_wait();
   __shared__ __align__(16) uint8_t s_tile[32 * MMA_PITCH];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // A fragments of W (two 16-row tiles x two 16-column tiles), mma.m16n8k16 row-major layout
@@ -192,8 +194,8 @@ static void launch_rht_dense(const RhtDenseArgs& a, bool bf16, cudaStream_t st) 
   const int64_t n_tasks = (a.rows / N) * ((a.cols + 255) >> 8);
   int64_t blocks = n_tasks < 148 * 8 ? n_tasks : 148 * 8;
   if (blocks < 1) blocks = 1;
-  if (bf16) rht_dense_kernel<N, true><<<(unsigned)blocks, 128, 0, st>>>(a);
-  else rht_dense_kernel<N, false><<<(unsigned)blocks, 128, 0, st>>>(a);
+  if (bf16) (void)launch_after(rht_dense_kernel<N, true>, dim3((unsigned)blocks), dim3(128), 0, st, a);
+  else (void)launch_after(rht_dense_kernel<N, false>, dim3((unsigned)blocks), dim3(128), 0, st, a);
 }
 
 }  // namespace altob200
@@ -218,7 +220,7 @@ extern "C" int altob200_rht_dense(const void* x, int32_t dtype, int64_t rows, in
   if (n == 32 && bf16 && vec) {
     const int64_t n_tasks = (rows / 32) * ((cols + 255) >> 8);
     int64_t blocks = n_tasks < 148 * 12 ? n_tasks : 148 * 12;
-    rht32_mma_kernel<<<(unsigned)blocks, 128, 0, st>>>(a);
+    (void)launch_after(rht32_mma_kernel, dim3((unsigned)blocks), dim3(128), 0, st, a);
   } else if (n == 16) launch_rht_dense<16>(a, bf16, st);
   else if (n == 32) launch_rht_dense<32>(a, bf16, st);
   else launch_rht_dense<64>(a, bf16, st);

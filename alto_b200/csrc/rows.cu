@@ -16,6 +16,7 @@ namespace altob200 {
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ src, int64_t src_rows,
                                                           int64_t row_vec, const int32_t* __restrict__ index,
                                                           int64_t out_rows, uint4* __restrict__ dst) {
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = (int64_t)gridDim.x * 8;
   for (int64_t r = warp0; r < out_rows; r += n_warps) {
@@ -38,6 +39,7 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(const uint4* __restri
                                                            const int32_t* __restrict__ index,
                                                            const __nv_bfloat16* __restrict__ scores, int64_t T, int k,
                                                            uint4* __restrict__ out) {
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = (int64_t)gridDim.x * 8;
   for (int64_t t = warp0; t < T; t += n_warps) {
@@ -73,6 +75,7 @@ __global__ void __launch_bounds__(256) spread_rows_kernel(const uint4* __restric
                                                           int64_t row_vec, const int32_t* __restrict__ position,
                                                           const __nv_bfloat16* __restrict__ scores, int64_t n_rows,
                                                           uint4* __restrict__ grad_rows) {
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = (int64_t)gridDim.x * 8;
   for (int64_t r = warp0; r < n_rows; r += n_warps) {
@@ -108,7 +111,7 @@ extern "C" int altob200_gather_rows(const void* src, int64_t src_rows, int64_t r
     return ALTOB200_EINVAL_ALIGN;
   int64_t blocks = ceil_div(out_rows, 8);
   if (blocks > 148 * 8) blocks = 148 * 8;
-  gather_rows_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+  (void)launch_after(gather_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 
       reinterpret_cast<const uint4*>(src), src_rows, row_bytes / 16, index, out_rows, reinterpret_cast<uint4*>(dst));
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
@@ -123,7 +126,7 @@ extern "C" int altob200_combine_rows(const void* rows, int64_t n_rows, int64_t r
     return ALTOB200_EINVAL_ALIGN;
   int64_t blocks = ceil_div(tokens, 8);
   if (blocks > 148 * 8) blocks = 148 * 8;
-  combine_rows_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+  (void)launch_after(combine_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 
       reinterpret_cast<const uint4*>(rows), n_rows, row_bytes / 16, index, reinterpret_cast<const __nv_bfloat16*>(scores),
       tokens, k, reinterpret_cast<uint4*>(out));
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
@@ -141,7 +144,7 @@ extern "C" int altob200_spread_rows(const void* grad_out, int64_t tokens, int32_
     return ALTOB200_EINVAL_ALIGN;
   int64_t blocks = ceil_div(n_rows, 8);
   if (blocks > 148 * 8) blocks = 148 * 8;
-  spread_rows_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+  (void)launch_after(spread_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 
       reinterpret_cast<const uint4*>(grad_out), tokens, k, row_bytes / 16, position,
       reinterpret_cast<const __nv_bfloat16*>(scores), n_rows, reinterpret_cast<uint4*>(grad_rows));
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;

@@ -37,6 +37,7 @@ template <bool BACKWARD>
 __global__ void __launch_bounds__(256) swiglu_kernel(const uint4* __restrict__ h, const uint4* __restrict__ go,
                                                      int64_t rows, int64_t hv /* H / 8 */, int64_t ldv /* ld_h / 8 */,
                                                      uint4* __restrict__ out) {
+  grid_dependency_wait();
   const int64_t n = rows * hv;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / hv, c = i - r * hv;
@@ -75,10 +76,10 @@ static int swiglu_launch(const void* h, const void* go, int64_t rows, int64_t H,
   int64_t blocks = ceil_div(rows * (H / 8), 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (backward)
-    swiglu_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(h), reinterpret_cast<const uint4*>(go),
+    (void)launch_after(swiglu_kernel<true>, dim3((unsigned)blocks), dim3(256), 0, st, reinterpret_cast<const uint4*>(h), reinterpret_cast<const uint4*>(go),
                                                           rows, H / 8, ld_h / 8, reinterpret_cast<uint4*>(out));
   else
-    swiglu_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(h), nullptr, rows, H / 8, ld_h / 8,
+    (void)launch_after(swiglu_kernel<false>, dim3((unsigned)blocks), dim3(256), 0, st, reinterpret_cast<const uint4*>(h), nullptr, rows, H / 8, ld_h / 8,
                                                            reinterpret_cast<uint4*>(out));
   return cudaGetLastError() == cudaSuccess ? ALTOB200_OK : ALTOB200_ECUDA;
 }
