@@ -381,3 +381,19 @@ def test_pair_tile_of_192_columns_with_two_accumulator_stages():
                        cwd=root, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert " passed" in r.stdout
+
+
+def test_plain_launches_give_the_same_results():
+    """Kernels are normally launched with programmatic stream serialisation (each waits for its
+    predecessor when it first touches global memory); ALTOB200_PDL=0 launches them the plain way.  The
+    linear and quantizer parity cases are re-run that way in a child process."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, ALTOB200_PDL="0")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "pytest", "tests/test_gpu_gemm.py", "tests/test_gpu_quantizers.py", "-q", "-x",
+                        "-m", "gpu", "-k", "linear_matches_oracle or rowwise or colwise or ragged_tiles"],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
