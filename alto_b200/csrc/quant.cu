@@ -463,6 +463,31 @@ __device__ __forceinline__ void hadamard16(float* z) {
   }
 }
 
+// The same butterfly on the two columns of a lane at once, as packed fp32 operations (one instruction
+// per pair of sums): a - b is fma(b, -1, a), which rounds once like the subtraction.
+__device__ __forceinline__ void hadamard16_pair(float* za, float* zb) {
+  float2 z[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) z[i] = make_float2(za[i], zb[i]);
+  const float2 neg = make_float2(-1.0f, -1.0f);
+#pragma unroll
+  for (int h = 1; h < 16; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if ((i & h) == 0) {
+        const float2 a = z[i], b = z[i + h];
+        z[i] = __fadd2_rn(a, b);
+        z[i + h] = __ffma2_rn(b, neg, a);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    za[i] = z[i].x;
+    zb[i] = z[i].y;
+  }
+}
+
 // =======================================================================================
 // Column-wise quantizer (axis 0) with optional Hadamard transform
 // =======================================================================================
@@ -564,8 +589,7 @@ __global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a)
     if (RHT) {
 #pragma unroll
       for (int g = 0; g < B; g += 16) {
-        hadamard16(v0 + g);
-        hadamard16(v1 + g);
+        hadamard16_pair(v0 + g, v1 + g);
       }
     }
     // ---- scale by +-1/sqrt(16) (exact), round to the input dtype, block amax on the rounded bits ----
@@ -1250,8 +1274,7 @@ __global__ void __launch_bounds__(256) amax_kernel(AmaxArgs a) {
           v1[k] = f.y;
         }
       }
-      hadamard16(v0);
-      hadamard16(v1);
+      hadamard16_pair(v0, v1);
 #pragma unroll
       for (int k = 0; k < 16; ++k) {
         // integer maximum of the magnitudes' bits: a NaN is larger than every number, as in torch.amax
