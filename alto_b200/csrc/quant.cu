@@ -191,6 +191,18 @@ __device__ __forceinline__ float scale_elem_mag(float x, const BlockScale& s) {
   return div_bf16_num_mag(x, s.q, s.r);
 }
 
+// Two elements of two different blocks divided by their block scales at once (reciprocal forms only;
+// magnitudes up to the sign of a zero, as scale_elem_mag): x * r for the power-of-two scales of the MX
+// formats, else y = x r, e = fma(y, -q, x), y + e r - the three roundings of div_bf16_num_mag per element.
+template <int FMT>
+__device__ __forceinline__ float2 scale_pair_mag(float2 x, const BlockScale& s0, const BlockScale& s1) {
+  const float2 r = make_float2(s0.r, s1.r);
+  const float2 y = __fmul2_rn(x, r);
+  if (Fmt<FMT>::MX) return y;
+  const float2 e = __ffma2_rn(y, make_float2(-s0.q, -s1.q), x);
+  return __ffma2_rn(e, r, y);
+}
+
 // Scale and quantise 2 elements into one FP4 byte (x0 in the low nibble).
 template <int FMT, bool IN_BF16, int ROUND, bool FAST>
 __device__ __forceinline__ uint32_t fp4_pair(float x0, float x1, const BlockScale& s, uint32_t r0, uint32_t r1) {
@@ -601,7 +613,8 @@ __global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a)
       for (int k = 0; k < B; ++k) {
         // the fused +0 turns a -0 product into the +0 that a dot product yields
         const float sg = a.rht.qsign[k & 15];
-        const __nv_bfloat162 p2 = __floats2bfloat162_rn(__fmaf_rn(v0[k], sg, 0.0f), __fmaf_rn(v1[k], sg, 0.0f));
+        const float2 sc = __ffma2_rn(make_float2(v0[k], v1[k]), make_float2(sg, sg), make_float2(0.0f, 0.0f));
+        const __nv_bfloat162 p2 = __floats2bfloat162_rn(sc.x, sc.y);
         const uint32_t pw = *reinterpret_cast<const uint32_t*>(&p2);
         acc = absmax_bf16x2(acc, pw);
         v0[k] = bf16lo_to_f32(pw);
@@ -761,6 +774,11 @@ __global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a)
                                                scale_elem<FMT, IN_BF16, FAST>(y1[j], s1));
               c0 = b & 0xFu;
               c1 = b >> 4;
+            } else if (FAST) {
+              // both columns' quotients with packed operations (the same three roundings per element)
+              const float2 q = scale_pair_mag<FMT>(make_float2(y0[j], y1[j]), s0, s1);
+              c0 = e2m1_sr_code(q.x, f2u(y0[j]), r0[j]);
+              c1 = e2m1_sr_code(q.y, f2u(y1[j]), r1[j]);
             } else {
               c0 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(y0[j], s0), f2u(y0[j]), r0[j]);
               c1 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(y1[j], s1), f2u(y1[j]), r1[j]);
