@@ -540,7 +540,7 @@ __global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a)
   __shared__ __align__(16) uint8_t s_codes[COL_TN * ROW_BYTES];
   __shared__ __align__(16) uint8_t s_sf[COL_TN * NBLK];
   __shared__ float s_sf_plain[Fmt<FMT>::MX ? 1 : COL_TN * NBLK];
-  __shared__ float s_perm[(RHT && ROUND != ALTOB200_ROUND_RTN) ? 16 : 1][2][NT];
+  __shared__ float2 s_perm[(RHT && ROUND != ALTOB200_ROUND_RTN) ? 16 : 1][NT];   // (column c, column c + 1) per thread
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t m0 = (int64_t)blockIdx.y * COL_TM;
@@ -685,16 +685,16 @@ __global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a)
         if (TO_POS) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            // row pinv[j] of the table: 2 x NT floats per row
-            float* dst = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(&s_perm[0][0][threadIdx.x]) +
-                                                  a.rht.perm_off[j] * NT);
-            dst[0] = y0[j];
-            dst[NT] = y1[j];
+            // row pinv[j] of the table (NT pairs of 8 bytes per row): both columns in one 8-byte access
+            float2* dst = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(&s_perm[0][threadIdx.x]) +
+                                                    a.rht.perm_off[j] * NT);
+            *dst = make_float2(y0[j], y1[j]);
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            y0[j] = s_perm[j][0][threadIdx.x];
-            y1[j] = s_perm[j][1][threadIdx.x];
+            const float2 t = s_perm[j][threadIdx.x];
+            y0[j] = t.x;
+            y1[j] = t.y;
           }
         }
         // random words by position: r0[i]/r1[i] for column c / c+1
