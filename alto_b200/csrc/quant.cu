@@ -783,8 +783,9 @@ __global__ void __launch_bounds__(COL_NT) quantize_colwise_kernel(ColwiseArgs a)
               c0 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(y0[j], s0), f2u(y0[j]), r0[j]);
               c1 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(y1[j], s1), f2u(y1[j]), r1[j]);
             }
-            w0h[j >> 3] |= c0 << (4 * (j & 7));
-            w1h[j >> 3] |= c1 << (4 * (j & 7));
+            // disjoint bits: adding is or-ing, and the multiply-add pipe has room where the ALU pipe has not
+            w0h[j >> 3] = merge_shifted(c0, 4 * (j & 7), w0h[j >> 3]);
+            w1h[j >> 3] = merge_shifted(c1, 4 * (j & 7), w1h[j >> 3]);
           }
         });
         const uint64_t w0 = ((uint64_t)w0h[1] << 32) | w0h[0], w1 = ((uint64_t)w1h[1] << 32) | w1h[0];
