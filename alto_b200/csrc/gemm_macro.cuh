@@ -12,21 +12,21 @@
 // This replaces the reference's emulation of the recipe, dequantise -> descale -> bf16 matmul
 // (alto/kernels/fp4/mxfp4/mxfp_linear.py:337-356, mxfp_grouped_gemm/cg_backward.py:668-690).
 //
-// One CTA (512 threads = four warpgroups, persistent over 128 x 128 output tiles):
+// One CTA (768 threads = six warpgroups, persistent over 128 x 128 output tiles):
 //   warpgroup 0   warp 0: producer - per stage (128 bytes of K = two chunks) two tiled TMA loads and the
 //                 bulk copies of the stage's scale tiles; warp 1: MMA issuer - two tcgen05.mma per chunk
 //                 into one of three 128-column chunk accumulators in tensor memory, then a commit to that
 //                 accumulator's "full" barrier; warp 2: waits on the shared-memory barriers for the MMA issuer
-//                 and releases it once per stage through a named barrier; warp 3 idle;
+//                 and releases it once per CHUNK through a named barrier; warp 3 idle;
 //   warpgroup 1   scale transfer shared memory -> tensor memory (as in the plain kernel);
-//   warpgroups 2, 3  fold + epilogue: each warp owns 32 rows x 64 columns of the tile in 64 registers per
-//                 thread.  Per chunk it reads the chunk accumulator (tcgen05.ld in two halves, one in
-//                 flight while the other is folded), gives it back, and adds P * (1/fa[row]) * (1/fb[col])
-//                 with packed fp32x2 arithmetic; the column factors of the chunk pass through a small
-//                 per-warp shared-memory buffer.  After the last chunk the registers are scaled,
-//                 converted, staged and TMA-stored.
-// The fold threads need ~170 registers (64 results + two half-chunk buffers of 32 + addressing), the
-// others ~40, so the warpgroups re-divide the register file with setmaxnreg (512 threads x 128 at launch).
+//   warpgroups 2-5  fold + epilogue: sixteen warps, four per tensor-memory lane quarter, each 32 rows x 32
+//                 columns of the tile in 32 registers per thread.  Per chunk a warp reads its slice of the
+//                 chunk accumulator (one tcgen05.ld), gives the accumulator back, and adds
+//                 P * (1/fa[row]) * (1/fb[col]) with packed fp32x2 arithmetic; the column factors of the
+//                 chunk pass through a small per-warp shared-memory buffer.  After the last chunk the
+//                 registers are scaled, converted, staged and TMA-stored.
+// The warpgroups re-divide the register file with setmaxnreg (768 threads x 80 at launch -> 48 for the
+// small roles, 96 for the fold warps; the two must balance exactly, see CfgMacro).
 // Rows grouped by expert (`group_expert`) and K ranges per batch entry (`k_offs`) work as in the
 // plain kernel; every K range starts on a multiple of 128 elements, so chunks never straddle one.
 #pragma once
