@@ -4,27 +4,31 @@
 // FP8: one byte per element) and carry one scale per 16 (NVFP4, UE4M3) or 32 (MXFP4 /
 // MXFP8, UE8M0) elements in the packed layout described in altob200.h.
 //
-// Structure of one CTA (320 threads, persistent over output tiles of 128 x BN):
-//   warp 0      : producer.  One elected lane issues, per k-stage, two tiled TMA loads
-//                 (A: 128 rows x 128 bytes, B: BN rows x 128 bytes, 128-byte swizzle) and
-//                 the bulk copies of the stage's scale tiles, all completing on the
-//                 stage's "full" mbarrier.
-//   warp 1      : MMA issuer.  Owns tensor memory (512 columns).  Per stage one thread issues
-//                 four tcgen05.mma (each consumes 32 bytes of K per row), then commits to
-//                 the stage's "empty" mbarrier; after the last stage of a tile it commits
-//                 to the accumulator's "full" mbarrier.
-//   warps 6..9  : scale transfer.  Each warp owns one 32-lane quarter of tensor memory and,
-//                 per stage, moves the stage's scale tiles shared memory -> registers ->
-//                 tensor memory (tcgen05.st), then arrives on the stage's "scales ready"
-//                 mbarrier.  (A tcgen05.cp in the MMA issuer's stream costs a pipeline
-//                 bubble of ~500 cycles per stage at every copy -> MMA boundary; measured.)
-//   warps 2..5  : epilogue.  Each warp reads its 32-lane quarter of the accumulator with
-//                 tcgen05.ld, multiplies by alpha, converts, writes 32 rows x 128 bytes into a
-//                 128-byte-swizzled staging buffer and hands it to a TMA store (which also
-//                 clips ragged M/N edges); two staging buffers per warp keep stores in flight.
-// Every mbarrier wait is bounded by a wall-clock limit; a wait that gives up records
-// {kernel, block, site} in a device status word, raises a CTA-wide abort flag, and all
-// roles fall through to the common teardown that frees tensor memory.
+// Structure of one CTA of the single-CTA kernel (352 threads, persistent over output tiles of 128 x BN):
+//   warp 0      : producer.  The whole warp runs the loop, one elected lane issues, per k-stage, two
+//                 tiled TMA loads (A: 128 rows x 128 bytes, B: BN rows x 128 bytes, 128-byte swizzle)
+//                 and the bulk copies of the stage's scale tiles, all completing on the stage's "full"
+//                 mbarrier.
+//   warp 1      : MMA issuer.  Owns tensor memory (512 columns).  Per stage one elected lane issues
+//                 four tcgen05.mma (each consumes 32 bytes of K per row), then commits to the stage's
+//                 "empty" mbarrier; after the last stage of a tile it commits to the accumulator's
+//                 "full" mbarrier.  It never waits on an mbarrier itself (that leaves the tensor pipe
+//                 idle for ~150 cycles per wait): warp 10 does and releases it through a named barrier.
+//   warps 6..9  : scale transfer.  Each warp owns one 32-lane quarter of tensor memory and, per stage,
+//                 moves the stage's scale tiles shared memory -> registers -> tensor memory
+//                 (tcgen05.st), then arrives on the stage's "scales ready" mbarrier.  (A tcgen05.cp in
+//                 the MMA issuer's stream costs a pipeline bubble of ~500 cycles per stage.)
+//   warps 2..5  : epilogue.  Each warp reads its 32-lane quarter of the accumulator with tcgen05.ld,
+//                 multiplies by alpha, converts, writes 32 rows x 128 bytes into a 128-byte-swizzled
+//                 staging buffer and hands it to a TMA store (which also clips ragged M/N edges); two
+//                 staging buffers per warp keep stores in flight.
+//   warp 10     : waits on the stage's barriers on behalf of the MMA issuer.
+// The CTA-pair kernel (cta_group::2, 256 x 256 tiles, 512 threads) and the two-level MXFP4 kernel
+// (gemm_macro.cuh) have the same roles; their layouts are described at the kernels.
+// Every mbarrier wait is bounded by a cycle count; a wait that gives up records {kernel, block, site}
+// in a device status word, raises a CTA-wide abort flag, and all roles fall through to the common
+// teardown that frees tensor memory.  All kernels are launched with programmatic stream serialisation
+// and wait for the kernel in front of them after their set-up (see launch_after in common.cuh).
 #include <cuda.h>
 #include <stdio.h>
 #include <stdlib.h>
