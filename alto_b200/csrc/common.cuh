@@ -205,12 +205,17 @@ __device__ __forceinline__ uint32_t e2m1x2_rtn_hw(float v0, float v1) {
 //   a < 1          with T = trunc(a * 2^33) = k * 2^32 + threshold (k = [a >= 0.5]),
 //                  code = hi32(T + 1 + ~rnd) = k + [rnd <= threshold].
 // A NaN saturates to 7 (the reference's code for a NaN element is an accident of its payload).
+// COMPARE selects how the sub-one threshold is evaluated (same value): the 64-bit carry form above, or
+// T.hi + [T.lo >= rnd]; the row-wise kernel is faster with the compare, the column-wise one with the carry.
+template <bool COMPARE = false>
 __device__ __forceinline__ uint32_t e2m1_sr_code(float v, uint32_t sign_bits, uint32_t rnd) {
   const float a = fminf(fabsf(v), 6.0f);
   const uint32_t ab = f2u(a);
   const uint32_t cn = (ab + (rnd & 0x3FFFFFu) - (126u << 23)) >> 22;
   const uint64_t t = __float2ull_rz(__fmul_rn(a, 8589934592.0f));
-  const uint32_t cd = (uint32_t)((t + 1ull + (uint64_t)(~rnd)) >> 32);
+  // hi32(T + 1 + ~rnd) = hi32(T + 2^32 - rnd) = T.hi + [T.lo >= rnd]
+  const uint32_t cd = COMPARE ? (uint32_t)(t >> 32) + ((uint32_t)t >= rnd ? 1u : 0u)
+                              : (uint32_t)((t + 1ull + (uint64_t)(~rnd)) >> 32);
   const uint32_t mag = a < 1.0f ? cd : cn;
   return mag | ((sign_bits >> 28) & 8u);
 }

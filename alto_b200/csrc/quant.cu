@@ -210,8 +210,8 @@ __device__ __forceinline__ uint32_t fp4_pair(float x0, float x1, const BlockScal
     return e2m1x2_rtn_hw(scale_elem<FMT, IN_BF16, FAST>(x0, s), scale_elem<FMT, IN_BF16, FAST>(x1, s));
   // codes are merged with multiply-adds (disjoint bits: adding is or-ing): the integer ALU is the
   // busiest pipe of these kernels and the multiply-add pipe has room
-  const uint32_t c0 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(x0, s), f2u(x0), r0);
-  const uint32_t c1 = e2m1_sr_code(scale_elem_mag<FMT, IN_BF16, FAST>(x1, s), f2u(x1), r1);
+  const uint32_t c0 = e2m1_sr_code<true>(scale_elem_mag<FMT, IN_BF16, FAST>(x0, s), f2u(x0), r0);
+  const uint32_t c1 = e2m1_sr_code<true>(scale_elem_mag<FMT, IN_BF16, FAST>(x1, s), f2u(x1), r1);
   return merge_shifted(c1, 4, c0);
 }
 
