@@ -217,7 +217,10 @@ __device__ __forceinline__ uint32_t e2m1_sr_code(float v, uint32_t sign_bits, ui
   const uint32_t cd = COMPARE ? (uint32_t)(t >> 32) + ((uint32_t)t >= rnd ? 1u : 0u)
                               : (uint32_t)((t + 1ull + (uint64_t)(~rnd)) >> 32);
   const uint32_t mag = a < 1.0f ? cd : cn;
-  return mag | ((sign_bits >> 28) & 8u);
+  // sign into bit 3 with one shift and one multiply-add (disjoint bits): the ALU pipe is the busy one
+  uint32_t r;
+  asm("mad.lo.u32 %0, %1, 8, %2;" : "=r"(r) : "r"(sign_bits >> 31), "r"(mag));
+  return r;
 }
 
 // E2M1 decode to fp32 (alto/kernels/fp4/fp4_common/triton_fp4_ops.py:100-132).
